@@ -1,0 +1,226 @@
+/*
+ * aspa_b200.h — C ABI of libaspa_b200.so: the sm_100a kernels behind the ASPA
+ * attention hot path (router, token/head selection, row packing, RoPE +
+ * head-major relayout, INT8 per-head quantisation, shortlist planning,
+ * gathered attention, prototype EMA, chunk selection and merge).
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer owned by the caller unless it is marked
+ *     "host"; nothing is allocated or freed inside the library except by the
+ *     functions that say so; scratch memory is passed in by the caller;
+ *   - `stream` is a cudaStream_t passed as void*; work is enqueued on it and is
+ *     valid in stream order; no call synchronises the device;
+ *   - every function returns 0 on success or a negative ASPA_ERR_* code;
+ *     aspa_last_error_string() describes the last failure of the calling thread;
+ *   - dtype codes: ASPA_F32 = 0, ASPA_BF16 = 1, ASPA_I8 = 2;
+ *   - "bh" means the flattened (batch, head) index b * H + h, "row" means one
+ *     active (bh, token) pair; rows are grouped by bh and ascend in token order.
+ *
+ * Each entry point cites the reference code it replaces, as path:line inside
+ * the reference project (aspa.py = src/proteus_attention/models/aspa.py,
+ * sa.py = src/proteus_attention/kernels/sparse_attn.py,
+ * cs.py = src/proteus_attention/tools/chunked_shortlist.py,
+ * cpp = src/proteus_attention/kernels/aspa_cuda/aspa_cuda.cpp).
+ */
+#ifndef ASPA_B200_H
+#define ASPA_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ASPA_F32 0
+#define ASPA_BF16 1
+#define ASPA_I8 2
+
+#define ASPA_OK 0
+#define ASPA_ERR_ARG (-1)      /* bad size, dtype or null pointer */
+#define ASPA_ERR_UNSUPPORTED (-2)
+#define ASPA_ERR_CUDA (-3)     /* a CUDA runtime call failed */
+#define ASPA_ERR_TIMEOUT (-4)  /* a bounded device-side wait ran out */
+
+/* Output layouts of the attention kernels. */
+#define ASPA_OUT_HEAD_MAJOR 0  /* out[(bh * T + t) * D + d]            (sa.py:1646) */
+#define ASPA_OUT_TOKEN_MAJOR 1 /* out[((b * T + t) * H + h) * D + d]   (aspa.py:1806-1807, 1845) */
+
+const char* aspa_last_error_string(void);
+int aspa_version(void);
+
+/* Router: gate probabilities, prototype similarity, blend scalar and token
+ * importance for n = B*T tokens in one pass over x.
+ * Replaces SwitchRouter.forward (aspa.py:149-157), _route_tokens
+ * (aspa.py:628-690) and the importance blend (aspa.py:1521-1530).
+ *   x            (n, C) of x_dtype (F32 or BF16); w_router (G, C) same dtype
+ *   proto_hat    (G, C) fp32 rows of L2-normalised prototypes, or NULL (prototypes off)
+ *   conf_eps     (G) fp32 = routing_confidence + 1e-6, or NULL
+ *   usage_bias   (G) fp32 = softmax(-(usage+1e-6)), or NULL when usage_boost == 0
+ *   gate_probs   (n, G) fp32 out; importance (n) fp32 out;
+ *   proto_sim, blend (n) fp32 out, may be NULL when proto_hat is NULL
+ *   proto_span   = (float)max(1e-6, 1 - proto_threshold), formed in double on the host like the reference
+ *   stat_partials (3 * ceil(n/64)) fp32 scratch/out: per-tile sums of proto_sim, blend and
+ *                count(blend > 0); may be NULL
+ */
+int aspa_router_fwd(const void* x, int x_dtype, int64_t n, int C, const void* w_router, int G,
+                    const float* proto_hat, const float* conf_eps, const float* usage_bias,
+                    float proto_temp, float proto_threshold, float proto_span, float proto_blend,
+                    float usage_boost, float* gate_probs, float* importance, float* proto_sim, float* blend,
+                    float* stat_partials, void* stream);
+
+/* L2-normalise the G prototype rows (F.normalize(..., eps=1e-6), aspa.py:639-640). */
+int aspa_normalize_rows(const float* src, int rows, int cols, float eps, float* dst, void* stream);
+
+/* Token keep: per batch row, mark the `need` most important tokens (ties to the
+ * lowest index), everything >= threshold when threshold > 0, and the first
+ * `guard` tokens.  Replaces _select_active_tokens (aspa.py:790-842).
+ *   importance (B, T) fp32; token_mask (B, T) uint8 out; kept (B) int32 out.  */
+int aspa_token_select(const float* importance, int B, int T, int need, float threshold, int guard,
+                      uint8_t* token_mask, int32_t* kept, void* stream);
+
+/* Column sums of gate_probs mapped to heads, then the nucleus head count and the
+ * blended per-token head budget, all on the device.
+ * Replaces _nucleus_head_count (aspa.py:749-780) and the budget blend (aspa.py:1575-1586).
+ *   gate_probs (n, G); gate_to_head (G) int32; scratch: (H * ceil(n/1024)) fp32
+ *   k_out (2) int32 out: [0] = heads per token (topk), [1] = adaptive (nucleus) budget */
+int aspa_head_budget(const float* gate_probs, int64_t n, int G, const int32_t* gate_to_head, int H,
+                     double top_p, int dense_k, int h_active_min, int linear_head_k, double alpha,
+                     float* scratch, int32_t* k_out, void* stream);
+
+/* Per-token top-k heads (ties to the lowest head) and the (B,T) x H activity bit
+ * mask ANDed with the token mask.  Replaces aspa.py:1540-1542, 1590-1598.
+ *   k_dev: device int32 holding k, or NULL to use k_host; kmax = row width of the outputs
+ *   head_bits (n) uint64 out; top_idx (n, kmax) int32 out; top_score (n, kmax) fp32 out
+ *   stat_partials (2 * ceil(n/256)) fp32 out: per-block sum of selected scores and
+ *   sum of gate entropy; may be NULL */
+int aspa_head_select(const float* gate_probs, int64_t n, int G, const int32_t* gate_to_head, int H,
+                     int k_host, const int32_t* k_dev, int kmax, const uint8_t* token_mask,
+                     uint64_t* head_bits, int32_t* top_idx, float* top_score, float* stat_partials,
+                     void* stream);
+
+/* Row packing: (bh, token) rows grouped by bh, tokens ascending.
+ * Replaces _pack_active_rows (sa.py:924-947; cpp:47-75).
+ *   head_bits (B*T) uint64; row_offsets (B*H + 1) int32 out; token_idx (capacity) int32 out
+ *   seg_scratch: (B*H * ceil(T/256) + 1) int32 scratch
+ *   Returns the scratch size in int32 elements from aspa_pack_rows_scratch(). */
+int64_t aspa_pack_rows_scratch(int B, int H, int T);
+int aspa_pack_rows(const uint64_t* head_bits, int B, int T, int H, int32_t* seg_scratch,
+                   int32_t* row_offsets, int32_t* token_idx, int64_t capacity, void* stream);
+
+/* Pack a (heads, T) uint8 activity mask (the functional API's active_mask). */
+int aspa_pack_mask(const uint8_t* mask, int heads, int T, int32_t* seg_scratch, int32_t* row_offsets,
+                   int32_t* token_idx, int64_t capacity, void* stream);
+
+/* RoPE tables: cos/sin (T, D/2) fp32 holding values rounded to `dtype`
+ * (aspa.py:576-604).  inv_freq (D/2) fp32 comes from the host so that it is
+ * bit-identical to the reference's buffer (aspa.py:241-246). */
+int aspa_rope_table(const float* inv_freq, int T, int D, int dtype, float* cos_t, float* sin_t, void* stream);
+
+/* RoPE on q,k + split of the fused QKV projection into head-major q,k,v.
+ * Replaces _apply_rope_embedding (aspa.py:606-618) and the permutes (aspa.py:1644-1656).
+ *   qkv (B, T, 3*H*D) of dtype; q,k,v (B*H, T, D) same dtype out
+ *   cos_t/sin_t NULL = no rotation; amax (3, B*H) fp32 in/out or NULL: running max |.| of q,k,v
+ *   per bh (caller zeroes it), feeding the INT8 quantiser. */
+int aspa_rope_relayout(const void* qkv, int dtype, int B, int T, int H, int D, const float* cos_t,
+                       const float* sin_t, void* q, void* k, void* v, float* amax, void* stream);
+
+/* max |x| per head of a (heads, T*D) tensor (aspa.py:1328). amax is overwritten. */
+int aspa_head_amax(const void* x, int dtype, int heads, int64_t per_head, float* amax, void* stream);
+
+/* Symmetric per-head INT8: scale = max(amax/127, 1e-6); q = clamp(rint(x/scale), +-127).
+ * Replaces _quantize_per_head_int8 in "max" mode (aspa.py:1312-1363). */
+int aspa_quantize_int8(const void* x, int dtype, int heads, int64_t per_head, const float* amax,
+                       int8_t* out, float* scales, void* stream);
+
+/* Structural description of every row's candidate set (sa.py:457-596 without
+ * materialising the (N, L) table).  Row t attends to
+ *   - local:   keys max(0, t-window+1) .. t      (window == 0: only t itself)
+ *   - anchors: max(t - j*anchor_stride, 0), j = 1..anchor_slots
+ *   - proto:   the min(t+1, proto_cap) best prototype scores among keys <= t
+ * de-duplicated.  The caller guarantees window + anchor_slots + proto_cap <= L,
+ * so the reference's "keep the L smallest" cut never triggers. */
+typedef struct {
+  int32_t window;
+  int32_t anchor_slots;
+  int32_t anchor_stride;
+  int32_t proto_cap;          /* 0 = no prototype piece */
+  int32_t proto_block;        /* tokens per plan block (128) */
+  int32_t proto_list_stride;  /* int32 entries per block list = proto_cap + proto_block */
+  const int32_t* proto_lists; /* (B, nblk, proto_list_stride): key ids, best first, -1 padded */
+  const int32_t* proto_limit; /* (B, T): per token, number of leading list entries to scan */
+} aspa_shortlist_plan;
+
+/* Build proto_lists / proto_limit from per-token prototype scores (B, T).
+ * Replaces _shortlist_prepare_proto_candidates[_grouped] (sa.py:260-373): block-wise prefix top-k.
+ *   scratch bytes from aspa_proto_plan_scratch(). */
+int64_t aspa_proto_plan_scratch(int B, int T, int proto_cap);
+int aspa_proto_plan(const float* proto_scores, int B, int T, int proto_cap, void* scratch,
+                    int32_t* proto_lists, int32_t* proto_limit, void* stream);
+
+/* Explicit candidate table, exactly as build_packed_shortlist_candidates returns it
+ * (sa.py:457-596): (N, L) int64 ascending unique ids padded with the row id, and lengths (N) int64.
+ *   rows (N) int64; row_batch (N) int64 or NULL; proto_scores (Bp, seq_len) fp32 or NULL
+ *   caps < 0 mean "not given" (the reference's None).  */
+int aspa_build_candidates(const int64_t* rows, const int64_t* row_batch, int64_t N, int seq_len, int L,
+                          int linear_window, int anchor_stride, int use_local, int use_anchors,
+                          const float* proto_scores, int local_cap, int anchor_cap, int proto_cap,
+                          int64_t* cand_out, int64_t* len_out, void* stream);
+
+/* Attention over packed rows.  One call covers the three shapes of the
+ * reference op (aspa_sparse_attention, sa.py:1373-1646; _fallback_sparse_attention
+ * sa.py:950-1046; Triton kernel sa.py:597-919; cpp:118-343):
+ *   - cand != NULL: explicit (N, L) candidate table + lengths;
+ *   - plan != NULL: candidates generated on the fly from the structural plan;
+ *   - neither: every key 0..t (or 0..max token of the head when add_mask is given).
+ * q,k,v (heads, T, D) of qkv_dtype (F32, BF16 or I8 with per-head fp32 scales);
+ * add_mask optional (T, T) fp32 additive mask (sa.py:997-1000, 1018-1021);
+ * out of out_dtype in out_layout; rows of inactive (bh, token) pairs are NOT
+ * written — the caller zero-fills `out` first.  H is only used by the
+ * token-major layout.  max_rows = largest per-head row count (grid sizing).
+ * workspace: aspa_attn_workspace_bytes(total_rows, D) bytes (partial softmax
+ * state exchanged between the window pass and the extras pass). */
+int64_t aspa_attn_workspace_bytes(int64_t total_rows, int D);
+int aspa_gather_attn_fwd(const void* q, const void* k, const void* v, int qkv_dtype, const float* q_scale,
+                         const float* k_scale, const float* v_scale, int heads, int T, int D, int H,
+                         const int32_t* row_offsets, const int32_t* token_idx, int max_rows,
+                         int64_t total_rows, const int64_t* cand, const int64_t* cand_len, int L,
+                         const aspa_shortlist_plan* plan, const float* add_mask, void* out, int out_dtype,
+                         int out_layout, void* workspace, void* stream);
+
+/* Prototype EMA (aspa.py:692-718): counts = sum_t probs; mean = probs^T x / counts;
+ * prototypes, usage and confidence updated in place for gates with counts > 1e-6.
+ *   scratch: aspa_proto_ema_scratch() bytes. Returns via updated (1) int32 the number of gates touched. */
+int64_t aspa_proto_ema_scratch(int64_t n, int C, int G);
+int aspa_proto_ema_update(const void* x, int x_dtype, int64_t n, int C, const float* gate_probs, int G,
+                          double decay, float* prototypes, float* usage, float* confidence, void* scratch,
+                          int32_t* updated, void* stream);
+
+/* Chunk promotion (cs.py:140-208): softmax mass over masked importance, nucleus
+ * count, top-`budget` tokens.  One chunk per call.
+ *   importance (T) fp32, token_mask (T) uint8 or NULL, offset added to indices
+ *   out_scores (budget) fp32, out_idx (budget) int64, out_count (1) int32 — count valid entries,
+ *   in score-descending order (ties by index). */
+int aspa_chunk_select(const float* importance, const uint8_t* token_mask, int T, int budget, float top_p,
+                      int64_t offset, float* out_scores, int64_t* out_idx, int32_t* out_count, void* stream);
+
+/* Merge of all chunks' promotions (cs.py:211-254): one representative score per
+ * unique index (the lowest, as the reference's sort key does), the max_tokens
+ * best of them, ascending index order.
+ *   scores/indices (n): entries with index < 0 are ignored; seq_len bounds the indices
+ *   table: (seq_len) uint32 scratch; keep_idx (max_tokens) int64, keep_scores (max_tokens) fp32,
+ *   keep_count (1) int32 out. */
+int aspa_merge_finalise(const float* scores, const int64_t* indices, int64_t n, int64_t seq_len,
+                        int max_tokens, uint32_t* table, int64_t* keep_idx, float* keep_scores,
+                        int32_t* keep_count, void* stream);
+
+/* Gather rows src[idx[i], :] -> dst[i, :] (cs.py:688-689). row_bytes multiple of 16. */
+int aspa_gather_rows(const void* src, const int64_t* idx, const int32_t* count_dev, int64_t max_rows,
+                     int64_t row_bytes, void* dst, void* stream);
+
+/* Deterministic sum of per-block partials: out[j] = sum_i partials[j * n_blocks + i]. */
+int aspa_reduce_partials(const float* partials, int n_series, int64_t n_blocks, float* out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ASPA_B200_H */

@@ -1,0 +1,906 @@
+"""ASPA attention layer on the sm_100a kernels.
+
+Drop-in for the reference classes in ``src/proteus_attention/models/aspa.py``:
+``ModelConfig`` (:33-72), ``AdaptiveSparseAttention`` (:170-1932),
+``AdaptiveSparseProtoAttention`` (:1935-1944) and ``AdaptiveSparseAttentionBlock``
+(:1947-1990).  Constructor knobs, attribute names read by callers and
+controllers, ``state_dict`` keys, mode selection and the telemetry dictionaries
+follow the reference; the arithmetic runs in libaspa_b200.so.
+
+Differences that are deliberate:
+  * forward only (the reference's kernel path has no autograd either); attention
+    dropout and the KV memory bank raise ``NotImplementedError``;
+  * one device-to-host read per call (a small statistics record) instead of the
+    reference's ~20 ``.item()`` calls; it is issued before the QKV projection and
+    waited on after it, so the GPU does not idle;
+  * float buffers (RoPE frequencies, prototypes, EMAs) stay fp32 under ``.to(bfloat16)``;
+  * ties in top-k selections go to the lowest index.
+"""
+from __future__ import annotations
+
+import math
+import time
+import warnings
+from typing import Any, Dict, Optional, Tuple
+
+import numpy as np
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from . import _native as N
+from . import ops
+from .sparse_attn import BACKEND_NAME, _record_backend, attention_packed, get_last_backend_info
+
+
+class ModelConfig:
+    """Attribute bag with the reference's defaults (aspa.py:42-64)."""
+
+    _DEFAULTS: Dict[str, Any] = {
+        "vocab_size": 0, "n_ctx": 0, "n_layer": 0, "n_head": 1, "d_model": 0, "p_dropout": 0.0, "bias": False,
+        "attn_variant": "standard", "moe_n_experts": 0, "attn_mode": "auto", "attn_linear_L": 512,
+        "attn_linear_window": 512, "attn_linear_anchor_stride": 256, "attn_linear_head_k": 2,
+        "attn_linear_switch_ctx": 20000, "attn_linear_latency_budget_ms": None,
+        "attn_linear_policy": "local+anchors", "attn_use_rope": True, "attn_rope_base": 10000.0,
+        "attn_router_top_p": 0.9,
+    }
+
+    def __init__(self, **kwargs: Any) -> None:
+        data = dict(self._DEFAULTS)
+        data.update(kwargs)
+        self.__dict__.update(data)
+
+    def to_dict(self) -> Dict[str, Any]:
+        return dict(self.__dict__)
+
+
+class LayerNorm(nn.Module):
+    def __init__(self, ndim: int, bias: bool, eps: float = 1e-5) -> None:
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(ndim))
+        self.bias = nn.Parameter(torch.zeros(ndim)) if bias else None
+        self.eps = eps
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return F.layer_norm(x, x.shape[-1:], self.weight, self.bias, eps=self.eps)
+
+
+class RMSNorm(nn.Module):
+    def __init__(self, ndim: int, eps: float = 1e-6) -> None:
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(ndim))
+        self.eps = eps
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.weight * (x * torch.rsqrt(x.pow(2).mean(dim=-1, keepdim=True) + self.eps))
+
+
+def _build_norm(config: ModelConfig) -> nn.Module:
+    kind = str(getattr(config, "norm_type", "layernorm") or "layernorm").lower()
+    eps = float(getattr(config, "norm_eps", 1e-5))
+    if kind == "rmsnorm":
+        return RMSNorm(config.d_model, eps=eps)
+    return LayerNorm(config.d_model, bias=bool(getattr(config, "bias", False)), eps=eps)
+
+
+class MLP(nn.Module):
+    def __init__(self, config: ModelConfig) -> None:
+        super().__init__()
+        hidden = int(getattr(config, "mlp_hidden_mult", 4)) * config.d_model
+        self.fc1 = nn.Linear(config.d_model, hidden, bias=bool(config.bias))
+        self.act = nn.GELU()
+        self.fc2 = nn.Linear(hidden, config.d_model, bias=bool(config.bias))
+        self.dropout = nn.Dropout(config.p_dropout)
+        self.last_aux_loss: Optional[torch.Tensor] = None
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.dropout(self.fc2(self.act(self.fc1(x))))
+
+
+class SwitchRouter(nn.Module):
+    """Holds the router weight (``head_router.linear.weight``); the product and softmax run inside
+    the fused router kernel, so ``forward`` here exists only for API compatibility."""
+
+    def __init__(self, d_model: int, n_gates: int, noise_std: float = 0.0) -> None:
+        super().__init__()
+        self.linear = nn.Linear(d_model, n_gates, bias=False)
+        self.noise_std = float(noise_std)
+
+    def forward(self, x: torch.Tensor):
+        probs = F.softmax(self.linear(x), dim=-1)
+        scores, indices = torch.max(probs, dim=-1)
+        return indices, scores, probs
+
+
+# ---- config parsing helpers ------------------------------------------------------------------
+def _num(config, name, default, kind=float):
+    """``kind(getattr(config, name, default) or default)`` — zero and None select the default."""
+    return kind(getattr(config, name, default) or default)
+
+
+def _policy_tokens(raw: str):
+    parts = {p.strip() for p in raw.replace("|", ",").replace("+", ",").split(",") if p.strip()}
+    return parts or {"local", "anchors"}
+
+
+def _py_round_f32(value: float) -> int:
+    """round() of a value first rounded to fp32, half to even — what ``torch.full(.., fp32).round()`` gives."""
+    return int(np.rint(np.float32(value)))
+
+
+class AdaptiveSparseAttention(nn.Module):
+    """Adaptive Sparse Proto Attention layer; ``forward(x: (B, T, C)) -> (B, T, C)``."""
+
+    def __init__(self, config: ModelConfig):
+        super().__init__()
+        g = lambda name, default=None: getattr(config, name, default)  # noqa: E731
+        self.d_model = int(config.d_model)
+        self.bias = bool(g("bias", False))
+        heads = int(g("attn_h_total", 0) or g("n_head", 1) or 1)
+        if heads <= 0:
+            heads = max(1, int(g("n_head", 1)))
+        self.h_total = heads
+        if self.d_model % heads != 0:
+            raise ValueError("d_model must be divisible by the total number of attention heads (attn_h_total)")
+        if heads > 64:
+            raise ValueError("the sm_100a kernels support at most 64 heads per layer")
+        act = int(g("attn_h_active", 0))
+        if act <= 0 or act > heads:
+            act = max(1, min(4, heads))
+        lo, hi = int(g("attn_h_active_min", 0) or 0), int(g("attn_h_active_max", 0) or 0)
+        hi = max(1, min(hi if hi > 0 else min(16, heads), heads))
+        lo = max(1, min(lo if lo > 0 else max(1, min(2, hi)), hi))
+        self.h_active_min, self.h_active_max = lo, hi
+        self.h_active = max(lo, min(act, hi))
+        try:
+            curve = float(g("attn_active_curve")) if g("attn_active_curve") is not None else 0.25
+        except (TypeError, ValueError):
+            curve = 0.25
+        self.h_active_curve = curve if curve > 0.0 else 1.0
+        self.force_dense_when_full = bool(g("attn_force_dense_when_full", False))
+        self.d_head = self.d_model // heads
+        self.use_rope = bool(g("attn_use_rope", True))
+        base = _num(config, "attn_rope_base", 10000.0)
+        self.rope_base = base if base > 0.0 else 10000.0
+        if self.use_rope and self.d_head % 2 != 0:
+            warnings.warn("Disabling RoPE because attention head dimension is not even.", RuntimeWarning)
+            self.use_rope = False
+        inv_freq = 1.0 / (self.rope_base ** (torch.arange(0, self.d_head, 2, dtype=torch.float32) / max(self.d_head, 1)))
+        self.register_buffer("_rope_inv_freq", inv_freq, persistent=False)
+        self._rope_cache: Dict[Tuple[str, int, str], Tuple[int, torch.Tensor, torch.Tensor]] = {}
+
+        self.dropout = nn.Dropout(config.p_dropout)
+        self.use_sdpa = bool(g("use_sdpa", True))
+        self.router_reg_lambda = _num(config, "attn_router_lambda", 0.0) if g("attn_router_lambda", 0.0) else 0.0
+        self.router_reg_beta = _num(config, "attn_router_beta", 1.0)
+        self.router_reg_mode = str(g("attn_router_reg_mode", "entropy"))
+        try:
+            top_p = float(g("attn_router_top_p", 0.0))
+        except (TypeError, ValueError):
+            top_p = 0.0
+        self.router_top_p = max(0.0, min(top_p if math.isfinite(top_p) else 0.0, 1.0))
+        mode = str(g("attn_mode", "auto") or "auto").lower()
+        self.mode_setting = mode if mode in {"auto", "subquad", "linear"} else "auto"
+
+        # shortlist sizing
+        self.linear_L = max(1, _num(config, "attn_linear_L", 512, int))
+        sched = str(g("attn_linear_L_schedule", "fixed") or "fixed").lower()
+        self.linear_L_schedule = sched if sched in {"fixed", "sqrt", "log", "mem_cap"} else "fixed"
+        self.linear_L_base = max(1, _num(config, "attn_linear_L_base", self.linear_L, int))
+        self.linear_L_min = max(1, _num(config, "attn_linear_L_min", min(64, self.linear_L_base), int))
+        lmax = g("attn_linear_L_max", self.linear_L)
+        self.linear_L_max = max(self.linear_L_min, int(lmax if lmax is not None else self.linear_L))
+        self.linear_L_scale_init = max(0.1, _num(config, "attn_linear_L_scale", 1.0))
+        self.linear_L_scale_max = _num(config, "attn_linear_L_scale_max", max(1.0, self.linear_L_scale_init))
+        self._linear_scale_min = max(0.05, self.linear_L_min / max(1.0, self.linear_L_base))
+        self._linear_L_scale_runtime = self.linear_L_scale_init
+        self.linear_latency_shrink = min(max(_num(config, "attn_linear_latency_shrink", 0.8), 0.1), 0.99)
+        self.linear_latency_growth = max(1.0, _num(config, "attn_linear_latency_growth", 1.05))
+        mb = g("attn_linear_mem_budget_mb")
+        self.linear_mem_budget_mb = float(mb) if mb is not None else None
+        fl = max(0.0, min(1.0, _num(config, "attn_linear_piece_local_frac", 0.6)))
+        fa = max(0.0, min(1.0, _num(config, "attn_linear_piece_anchor_frac", 0.3)))
+        fp = max(0.0, min(1.0, float(g("attn_linear_piece_proto_frac", max(0.0, 1.0 - fl - fa)))))
+        fl, fa, fp = self._normalise_fracs(fl, fa, fp)
+        window = _num(config, "attn_linear_window", self.linear_L_base, int)
+        self.linear_window_base = max(1, window if window > 0 else self.linear_L_base)
+        self.linear_window = self.linear_window_base
+        self.linear_anchor_stride = max(0, int(g("attn_linear_anchor_stride", g("attn_linear_anchors_every", 256)) or 0))
+        self.linear_head_k = max(1, min(_num(config, "attn_linear_head_k", 2, int), heads))
+        self.linear_switch_ctx = max(0, _num(config, "attn_linear_switch_ctx", 20000, int))
+        lb = g("attn_linear_latency_budget_ms")
+        self.linear_latency_budget_ms = float(lb) if lb is not None else None
+        tokens = _policy_tokens(str(g("attn_linear_policy", "local+anchors") or "local+anchors").lower())
+        self.linear_policy_tokens = tokens
+        self.linear_use_anchors = bool(tokens & {"anchors", "anchor", "global"})
+        self.linear_use_proto = bool(tokens & {"proto", "prototype", "semantic", "dna"})
+        self.linear_use_local = bool(tokens & {"local", "window"}) or not (self.linear_use_anchors or self.linear_use_proto)
+        fl = fl if self.linear_use_local else 0.0
+        fa = fa if self.linear_use_anchors else 0.0
+        fp = fp if self.linear_use_proto else 0.0
+        if fl + fa + fp <= 0.0:
+            fl, fa, fp = 1.0, 0.0, 0.0
+        else:
+            tot = fl + fa + fp
+            fl, fa = fl / tot, fa / tot
+            fp = max(0.0, 1.0 - fl - fa)
+        self.linear_piece_local_frac, self.linear_piece_anchor_frac, self.linear_piece_proto_frac = fl, fa, fp
+        self._linear_runtime: Optional[dict] = None
+        self._linear_runtime_seq_len: Optional[int] = None
+        self._linear_runtime_alpha: Optional[float] = None
+        self._current_alpha: float = 0.0
+        try:
+            cutoff = float(g("attn_dense_alpha_cutoff", 0.0))
+        except (TypeError, ValueError):
+            cutoff = 0.25
+        self.dense_alpha_cutoff = float(max(0.0, min(0.95, cutoff)))
+
+        self.memory_enabled = bool(g("attn_memory_enable", False)) and int(g("attn_memory_slots", 0) or 0) > 0
+        self.quantize_sparse_int8 = bool(g("attn_quantize_int8", False))
+        qmode = str(g("attn_quantize_int8_mode", "max") or "max").lower()
+        self.quantize_sparse_int8_mode = qmode if qmode in {"max", "percentile", "ema_percentile"} else "max"
+        self.quantize_sparse_int8_percentile = min(max(_num(config, "attn_quantize_int8_percentile", 1.0), 0.0), 1.0)
+        self.quantize_sparse_int8_ema_decay = min(max(_num(config, "attn_quantize_int8_ema_decay", 0.9), 0.0), 0.9999)
+
+        seq_low, seq_high = _num(config, "attn_active_seq_low", 0, int), _num(config, "attn_active_seq_high", 0, int)
+        if seq_low <= 0:
+            seq_low = max(64, self.d_head)
+        if seq_high <= 0:
+            seq_high = int(g("n_ctx", 0) or (seq_low * 4))
+        self.seq_low, self.seq_high = seq_low, max(seq_high, seq_low)
+        hint = g("attn_small_seq_dense")
+        try:
+            dense_cut = int(hint) if hint is not None else max(0, self.seq_low // 2)
+        except (TypeError, ValueError):
+            dense_cut = max(0, self.seq_low // 2)
+        self.small_seq_dense = max(0, dense_cut)
+        self._density_ema: Optional[float] = None
+        self._last_density: Optional[float] = None
+        self._last_target_k: Optional[int] = None
+        dt = g("attn_force_dense_threshold")
+        dt = float(dt) if dt is not None else None
+        self._dense_threshold: Optional[float] = dt if (dt is not None and dt > 0.0) else None
+
+        gates = int(g("attn_gates", 0))
+        if gates <= 0:
+            gates = max(heads, self.h_active_max, self.h_active) * 2
+        self.attn_gates = max(gates, heads, self.h_active_max)
+        if self.attn_gates > 64:
+            raise ValueError("the sm_100a router supports at most 64 gates")
+        self.head_router = SwitchRouter(self.d_model, self.attn_gates, noise_std=float(g("attn_router_noise_std", 0.01)))
+        idx = torch.arange(self.attn_gates, dtype=torch.long)
+        gate_to_head = torch.clamp((idx * heads) // max(self.attn_gates, 1), 0, heads - 1)
+        self.register_buffer("gate_to_head", gate_to_head, persistent=False)
+        self.register_buffer("gate_to_head_onehot", F.one_hot(gate_to_head, num_classes=heads).to(torch.float32),
+                             persistent=False)
+        self.register_buffer("_gate_to_head_i32", gate_to_head.to(torch.int32), persistent=False)
+        self._shortlist_alpha_override: Optional[float] = None
+
+        self.qkv = nn.Linear(self.d_model, 3 * self.d_model, bias=self.bias)
+        self.proj = nn.Linear(self.d_model, self.d_model, bias=self.bias)
+
+        self.last_head_stats: Optional[dict] = None
+        self._last_sparse_state: Optional[dict] = None
+        self.last_aux_loss: Optional[torch.Tensor] = None
+        self.last_router_reg: Optional[torch.Tensor] = None
+        self._latency_ema: Optional[float] = None
+        self.track_latency = bool(g("attn_track_latency", True))
+        self.proto_enabled = bool(g("attn_proto_enable", False))
+        self.proto_decay = float(g("attn_proto_decay", 0.97))
+        self.proto_threshold = float(g("attn_proto_threshold", 0.25))
+        self.proto_blend = float(g("attn_proto_blend", 0.6))
+        self.proto_temp = float(max(g("attn_proto_temp", 0.2), 1e-3))
+        self.proto_usage_boost = float(max(g("attn_proto_usage_boost", 0.0), 0.0))
+        self.proto_init_scale = float(g("attn_proto_init_scale", 0.02))
+        if self.proto_enabled:
+            self.register_buffer("routing_prototypes",
+                                 torch.randn(self.attn_gates, self.d_model, dtype=torch.float32) * self.proto_init_scale)
+            self.register_buffer("routing_usage_ema", torch.zeros(self.attn_gates, dtype=torch.float32))
+            self.register_buffer("routing_confidence", torch.zeros(self.attn_gates, dtype=torch.float32))
+        else:
+            self.routing_prototypes = None  # type: ignore[assignment]
+            self.routing_usage_ema = None  # type: ignore[assignment]
+            self.routing_confidence = None  # type: ignore[assignment]
+        self._last_proto_stats: Optional[dict] = None
+        self.token_sparse = bool(g("attn_token_sparse", False))
+        self.token_keep_ratio_base = min(max(_num(config, "attn_token_keep_ratio", 1.0), 0.0), 1.0)
+        self._token_keep_ratio_runtime: Optional[float] = None
+        ks = str(g("attn_linear_token_keep_schedule", "sqrt") or "sqrt").lower()
+        self.linear_token_keep_schedule = ks if ks in {"fixed", "sqrt", "log"} else "sqrt"
+        self.linear_token_keep_ratio_min = min(max(_num(config, "attn_linear_token_keep_min_ratio", 0.2), 0.0),
+                                               self.token_keep_ratio_base)
+        self.linear_token_keep_ratio_ref = _num(config, "attn_linear_token_keep_ref", 2048, int)
+        keep_min = max(0, _num(config, "attn_token_keep_min", 0, int))
+        guard = max(0, _num(config, "attn_token_keep_guard", 1, int))
+        self.token_keep_guard = guard
+        self.token_keep_min = max(keep_min, guard if self.token_sparse else keep_min)
+        self.token_keep_threshold = float(max(0.0, _num(config, "attn_token_keep_threshold", 0.0)))
+        self._last_token_importance: Optional[torch.Tensor] = None
+        self._last_token_mask: Optional[torch.Tensor] = None
+        self._last_token_blend: Optional[torch.Tensor] = None
+        self._last_token_similarity: Optional[torch.Tensor] = None
+        self._last_shortlist_backend_info: Optional[Dict[str, object]] = None
+        self._last_batch_size: Optional[int] = None
+        self.last_head_consensus: Optional[torch.Tensor] = None
+        self._identity_pack: Dict[Tuple[int, int, str], Tuple[torch.Tensor, torch.Tensor]] = {}
+        self._pin: Optional[torch.Tensor] = None
+
+    # float buffers keep fp32 whatever dtype the module is cast to (see module docstring)
+    def _apply(self, fn, *args, **kwargs):
+        keep = {n: b for n, b in self.named_buffers(recurse=False) if b is not None and b.dtype == torch.float32}
+        super()._apply(fn, *args, **kwargs)
+        for name, old in keep.items():
+            new = getattr(self, name)
+            if new.dtype != torch.float32:
+                setattr(self, name, old.to(device=new.device))
+        self._rope_cache.clear()
+        self._identity_pack.clear()
+        self._pin = None
+        return self
+
+    @staticmethod
+    def _normalise_fracs(fl: float, fa: float, fp: float):
+        tot = fl + fa + fp
+        if tot <= 0.0:
+            return 1.0, 0.0, 0.0
+        fl, fa = fl / tot, fa / tot
+        return fl, fa, max(0.0, 1.0 - fl - fa)
+
+    # ---- host-side schedules (reference aspa.py:731-747, 844-930, 1037-1173) --------------------
+    def _choose_active_k(self, seq_len: int) -> int:
+        if seq_len <= self.seq_low:
+            k = self.h_active_max
+        elif seq_len >= self.seq_high:
+            k = self.h_active_min
+        else:
+            r = float(seq_len - self.seq_low) / float(max(1, self.seq_high - self.seq_low))
+            if self.h_active_curve != 1.0:
+                r = max(0.0, min(1.0, r)) ** self.h_active_curve
+            k = int(math.floor(self.h_active_max - r * (self.h_active_max - self.h_active_min) + 1e-6))
+        k = max(self.h_active_min, min(k, self.h_active_max))
+        self._last_target_k = k
+        return k
+
+    def _update_density(self, value: float) -> None:
+        value = float(max(0.0, value))
+        self._last_density = value
+        self._density_ema = value if self._density_ema is None else 0.8 * self._density_ema + 0.2 * value
+
+    def _density_threshold(self) -> Optional[float]:
+        return self._dense_threshold
+
+    def _set_linear_scale(self, value: float) -> None:
+        lo = self._linear_scale_min
+        self._linear_L_scale_runtime = float(min(max(value, lo), max(lo, self.linear_L_scale_max)))
+        self._linear_runtime_seq_len = None
+        self._linear_runtime_alpha = None
+
+    def adjust_linear_L_scale(self, factor: float) -> None:
+        """Multiply the shortlist-length scale (used by controllers)."""
+        if factor == 0.0:
+            return
+        self._set_linear_scale(self._linear_L_scale_runtime * factor)
+
+    def _linear_token_keep_ratio(self, seq_len: int) -> float:
+        if not self.token_sparse:
+            return self.token_keep_ratio_base
+        ref, base, seq = max(1, self.linear_token_keep_ratio_ref), self.token_keep_ratio_base, max(1, int(seq_len))
+        if self.linear_token_keep_schedule == "sqrt":
+            r = base * math.sqrt(ref / float(seq))
+        elif self.linear_token_keep_schedule == "log":
+            r = base * (math.log2(ref + 1.0) / math.log2(seq + 1.0))
+        else:
+            r = base
+        return float(max(min(base, self.linear_token_keep_ratio_min), min(base, r)))
+
+    def _get_shortlist_alpha(self, seq_len: int) -> float:
+        if self._shortlist_alpha_override is not None:
+            return float(max(0.0, min(1.0, self._shortlist_alpha_override)))
+        seq_len = int(max(1, seq_len))
+        low = max(1, int(self.seq_low))
+        high = max(low + 1, int(self.linear_switch_ctx)) if self.linear_switch_ctx > 0 else max(low + 1, seq_len)
+        if seq_len <= low:
+            return 0.0
+        if seq_len >= high:
+            return 1.0
+        return float((seq_len - low) / (high - low))
+
+    def _compute_cvt_alpha(self, seq_len: int) -> float:
+        seq_len = int(max(1, seq_len))
+        alpha = {"linear": 1.0, "subquad": 0.0}.get(self.mode_setting)
+        if alpha is None:
+            alpha = self._get_shortlist_alpha(seq_len)
+        if self.linear_latency_budget_ms is not None and self._latency_ema is not None:
+            budget, lat = self.linear_latency_budget_ms, self._latency_ema
+            if lat > budget * 1.05:
+                if self._linear_L_scale_runtime > self._linear_scale_min + 1e-3:
+                    self.adjust_linear_L_scale(self.linear_latency_shrink)
+                alpha = 1.0
+            elif lat < budget * 0.80 and seq_len < max(1, self.linear_switch_ctx):
+                if self._linear_L_scale_runtime < self.linear_L_scale_max:
+                    self.adjust_linear_L_scale(self.linear_latency_growth)
+                alpha = min(alpha, 0.0)
+        if self.linear_switch_ctx > 0:
+            if self._current_alpha >= 0.95 and seq_len >= max(1, int(self.linear_switch_ctx * 0.75)):
+                alpha = max(alpha, 0.95)
+            if seq_len >= self.linear_switch_ctx:
+                alpha = 1.0
+        return float(max(0.0, min(1.0, alpha)))
+
+    def set_shortlist_alpha(self, value: float) -> None:
+        """Externally pin the dense<->shortlist slider (0 = dense, 1 = linear)."""
+        self._shortlist_alpha_override = float(max(0.0, min(1.0, value)))
+        self._linear_runtime = None
+        self._linear_runtime_seq_len = None
+        self._linear_runtime_alpha = None
+
+    def _compute_effective_linear_params(self, seq_len: int, batch_size: Optional[int], alpha: float) -> dict:
+        seq_len = max(1, int(seq_len))
+        coeff = float(max(1.0, self.linear_L_base))
+        sched = self.linear_L_schedule
+        if sched == "sqrt":
+            base_val = coeff * math.sqrt(float(seq_len))
+        elif sched == "log":
+            base_val = coeff * math.log2(float(seq_len) + 1.0)
+        elif sched == "mem_cap" and self.linear_mem_budget_mb:
+            heads_est = max(1, int(getattr(self, "_last_target_k", self.linear_head_k)))
+            batch_est = max(1, int(batch_size) if batch_size is not None else 1)
+            denom = heads_est * batch_est * seq_len * max(1, self.d_head) * 8
+            cap_mem = int(self.linear_mem_budget_mb * 1024 * 1024 // denom) if denom > 0 else self.linear_L_max
+            base_val = max(1, min(cap_mem, self.linear_L_max))
+        else:
+            base_val = coeff
+        clampL = lambda v: max(self.linear_L_min, min(self.linear_L_max, v))  # noqa: E731
+        eff = clampL(int(math.ceil(self._linear_L_scale_runtime * max(1.0, base_val))))
+        window = min(self.linear_window_base, eff)
+        dense_cap = clampL(int(min(seq_len, max(self.linear_L_min, self.linear_window_base + seq_len // 32))))
+        eff = clampL(int(alpha * eff + (1.0 - alpha) * dense_cap))
+        window_dense = max(1, min(seq_len, max(self.linear_window_base, seq_len // 8)))
+        window = max(1, min(eff, int(alpha * window + (1.0 - alpha) * window_dense)))
+        use = (self.linear_use_local, self.linear_use_anchors, self.linear_use_proto)
+        dense_w = (0.85, 0.10, 0.05)
+        target_w = (self.linear_piece_local_frac, self.linear_piece_anchor_frac, self.linear_piece_proto_frac)
+        w = [(1.0 - alpha) * (dense_w[i] if use[i] else 0.0) + alpha * (target_w[i] if use[i] else 0.0) for i in range(3)]
+        tw = w[0] + w[1] + w[2]
+        if tw <= 0.0:
+            w, tw = [1.0, 0.0, 0.0], 1.0
+        wl, wa = w[0] / tw, w[1] / tw
+        weights = (wl, wa, max(0.0, 1.0 - wl - wa))
+        caps = [int(round(eff * weights[i])) if use[i] else 0 for i in range(3)]
+        total = sum(caps)
+        if total > eff and total > 0:
+            caps = [int(max(0, math.floor(c * (eff / total)))) for c in caps]
+            total = sum(caps)
+        remaining = eff - total
+        for i in range(3):
+            if remaining <= 0:
+                break
+            if use[i]:
+                caps[i] += 1
+                remaining -= 1
+        if remaining > 0:
+            caps[0 if use[0] else 1 if use[1] else 2] += remaining
+        if use[0]:
+            caps[0] = min(caps[0], window)
+            if caps[0] <= 0 and eff > 0:
+                caps[0] = min(window, max(1, eff // 4))
+        return {"effective_L": eff, "local_cap": max(0, int(caps[0])), "anchor_cap": max(0, int(caps[1])),
+                "proto_cap": max(0, int(caps[2])), "window": max(1, int(window)), "shortlist_alpha": float(alpha)}
+
+    def _prepare_linear_runtime(self, seq_len: int, batch_size: Optional[int], alpha: float) -> dict:
+        if (self._linear_runtime is not None and self._linear_runtime_seq_len == seq_len
+                and self._linear_runtime_alpha is not None and abs(self._linear_runtime_alpha - float(alpha)) < 1e-4):
+            return self._linear_runtime
+        alpha = float(max(0.0, min(1.0, alpha)))
+        p = self._compute_effective_linear_params(seq_len, batch_size, alpha)
+        self.linear_L, self.linear_window = p["effective_L"], p["window"]
+        rt = dict(p, anchor_stride=self.linear_anchor_stride)
+        self._linear_runtime, self._linear_runtime_seq_len, self._linear_runtime_alpha = rt, seq_len, alpha
+        return rt
+
+    # ---- device helpers ---------------------------------------------------------------------------
+    def _rope_factors(self, seq_len: int, device: torch.device, dtype: torch.dtype):
+        """fp32 (T, D/2) cos/sin tables whose values are rounded to ``dtype`` (reference aspa.py:576-604)."""
+        if seq_len <= 0:
+            raise ValueError("RoPE requires a positive sequence length.")
+        key = (device.type, int(device.index) if device.index is not None else -1, str(dtype))
+        cached = self._rope_cache.get(key)
+        if cached is None or cached[0] < seq_len:
+            cos, sin = ops.rope_table(self._rope_inv_freq.to(device), seq_len, self.d_head, dtype)
+            cached = (seq_len, cos, sin)
+            self._rope_cache[key] = cached
+        return cached[1][:seq_len], cached[2][:seq_len]
+
+    def _identity_rows(self, B: int, T: int, device: torch.device):
+        key = (B, T, str(device))
+        hit = self._identity_pack.get(key)
+        if hit is None:
+            HT = B * self.h_total
+            hit = (torch.arange(0, (HT + 1) * T, T, device=device, dtype=torch.int32),
+                   torch.arange(T, device=device, dtype=torch.int32).repeat(HT))
+            self._identity_pack = {key: hit}
+        return hit
+
+    def _project_qkv(self, x: torch.Tensor, want_amax: bool = False):
+        B, T, _ = x.shape
+        qkv = self.qkv(x)
+        cos = sin = None
+        if self.use_rope:
+            cos, sin = self._rope_factors(T, x.device, x.dtype)
+        return ops.rope_relayout(qkv.contiguous(), self.h_total, self.d_head, cos, sin, want_amax)
+
+    def _check_input(self, x: torch.Tensor) -> None:
+        if not x.is_cuda:
+            raise RuntimeError("proteus_flux_attention_b200 has no CPU path: move the module and input to a CUDA device")
+        if x.dtype not in (torch.float32, torch.bfloat16):
+            raise TypeError("ASPA kernels take float32 or bfloat16 activations")
+        if self.qkv.weight.dtype != x.dtype:
+            raise TypeError(f"activation dtype {x.dtype} does not match the layer weights ({self.qkv.weight.dtype})")
+        if self.memory_enabled:
+            raise NotImplementedError("the KV memory bank (attn_memory_enable) is not built in the sm_100a path yet")
+        if self.training and self.dropout.p > 0.0:
+            raise NotImplementedError("attention dropout is not implemented in the sm_100a kernels (forward-only build)")
+
+    def _forward_dense_fastpath(self, x: torch.Tensor) -> torch.Tensor:
+        """Causal attention over every head for short sequences (reference aspa.py:1365-1440)."""
+        B, T, C = x.shape
+        q, k, v, _ = self._project_qkv(x)
+        offs, tok = self._identity_rows(B, T, x.device)
+        out = torch.zeros((B, T, C), dtype=x.dtype, device=x.device)
+        attention_packed(q, k, v, row_offsets=offs, token_idx=tok, max_rows=T, total_rows=B * self.h_total * T,
+                         H=self.h_total, out=out, out_layout=N.OUT_TOKEN_MAJOR)
+        y = self.dropout(self.proj(out))
+        thr = None if self._dense_threshold is None else float(self._dense_threshold)
+        self._last_target_k = self.h_total
+        self._last_sparse_state = {"mode": "dense_fastpath", "backend": BACKEND_NAME, "max_rows": T, "density": 1.0,
+                                   "target_k": self.h_total, "force_dense_threshold": thr,
+                                   "cutoff": int(self.small_seq_dense), "quantized": False, "token_keep_fraction": 1.0}
+        self._update_density(1.0)
+        self.last_head_stats = {
+            "top_k": int(self.h_total), "mean_gate_prob": 1.0, "router_entropy": 0.0,
+            "mean_active_per_token": float(self.h_total), "unique_heads": int(self.h_total), "active_fraction": 1.0,
+            "max_active_rows": int(T), "max_active_density": 1.0, "target_k": int(self.h_total), "seq_len": int(T),
+            "active_min": int(self.h_active_min), "active_max": int(self.h_active_max), "force_dense_threshold": thr,
+            "active_curve": float(self.h_active_curve), "token_keep_fraction": 1.0,
+            "router_top_p": float(self.router_top_p), "nucleus_k": int(self.h_total), "top_a_consensus": True}
+        self.last_router_reg = None
+        return y
+
+    # ---- forward ------------------------------------------------------------------------------------
+    @torch.no_grad()
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        self._check_input(x)
+        x = x.contiguous()
+        B, T, C = x.shape
+        dev = x.device
+        H, D, G = self.h_total, self.d_head, self.attn_gates
+        self.last_aux_loss = None
+        self._last_token_importance = self._last_token_mask = self._last_token_blend = None
+        if not self.proto_enabled:
+            self._last_token_similarity = None
+        t_start = ev0 = None
+        if self.track_latency:
+            ev0 = torch.cuda.Event(enable_timing=True)
+            ev0.record()
+            t_start = time.perf_counter()
+        self._last_batch_size = B
+
+        if self.small_seq_dense and T <= self.small_seq_dense:
+            y = self._forward_dense_fastpath(x)
+            self._finalize_latency("dense_fastpath", ev0, t_start)
+            return y
+
+        alpha = self._compute_cvt_alpha(T)
+        self._current_alpha = alpha
+        if self.token_sparse:
+            ratio = (1.0 - alpha) * float(self.token_keep_ratio_base) + alpha * float(self._linear_token_keep_ratio(T))
+            self._token_keep_ratio_runtime = float(max(0.0, min(1.0, ratio)))
+        else:
+            self._token_keep_ratio_runtime = None
+
+        # 1. router
+        x2d = x.view(B * T, C)
+        proto_hat = conf_eps = usage_bias = None
+        use_proto = self.proto_enabled and self.routing_prototypes is not None
+        if use_proto:
+            proto_hat = ops.normalize_rows(self.routing_prototypes)
+            if self.routing_confidence is not None:
+                conf_eps = (self.routing_confidence + 1e-6).to(torch.float32)
+            if self.proto_usage_boost > 0.0 and self.routing_usage_ema is not None:
+                usage_bias = torch.softmax(-(self.routing_usage_ema + 1e-6), dim=0).to(torch.float32)
+        gate, imp, sim, bs, proto_sums = ops.router_fwd(
+            x2d, self.head_router.linear.weight.contiguous(), proto_hat, conf_eps, usage_bias, temp=self.proto_temp,
+            threshold=self.proto_threshold, span=max(1e-6, 1.0 - self.proto_threshold), blend=self.proto_blend,
+            usage_boost=self.proto_usage_boost)
+        self._last_token_similarity = sim.view(B, T) if sim is not None else None
+        self._last_token_blend = bs.view(B, T) if bs is not None else None
+        self._last_token_importance = imp.view(B, T)
+
+        # 2. token keep
+        token_mask_u8 = kept = None
+        if self.token_sparse:
+            ratio = float(self._token_keep_ratio_runtime)
+            if ratio >= 0.999 and self.token_keep_threshold <= 0.0:
+                token_mask_u8 = torch.ones((B, T), dtype=torch.uint8, device=dev)
+                kept = torch.full((B,), T, dtype=torch.int32, device=dev)
+            else:
+                guard = min(max(0, self.token_keep_guard), T)
+                min_keep = max(min(max(0, self.token_keep_min), T), guard)
+                need = _py_round_f32(ratio * T)
+                if min_keep > 0:
+                    need = max(need, min_keep)
+                need = max(1, min(need, T))
+                token_mask_u8, kept = ops.token_select(self._last_token_importance, need, self.token_keep_threshold, guard)
+            self._last_token_mask = token_mask_u8.view(torch.bool)
+
+        # 3. head budget and per-token head choice
+        dense_k = self._choose_active_k(T)
+        k_dev = None
+        adaptive_host: Optional[int] = dense_k
+        if self.router_top_p > 0.0 and dense_k > self.h_active_min and dense_k > 1:
+            k_dev = ops.head_budget(gate, self._gate_to_head_i32, H, top_p=self.router_top_p, dense_k=dense_k,
+                                    h_min=self.h_active_min, linear_head_k=self.linear_head_k, alpha=alpha)
+            adaptive_host = None
+        k_host = 0
+        if k_dev is None:
+            adaptive = max(self.h_active_min, dense_k) if self.router_top_p > 0.0 else dense_k
+            lin_k = max(1, min(adaptive, self.linear_head_k))
+            k_host = min(adaptive, max(1, int(round((1.0 - alpha) * float(adaptive) + alpha * float(lin_k)))))
+            adaptive_host = adaptive
+        head_bits, top_idx, top_score, head_sums = ops.head_select(
+            gate, self._gate_to_head_i32, H, k_host=k_host, k_dev=k_dev, kmax=dense_k,
+            token_mask=token_mask_u8.view(-1) if token_mask_u8 is not None else None)
+        capacity = B * T * dense_k
+        row_offsets, token_idx = ops.pack_rows(head_bits, B, T, H, capacity)
+
+        # 4. one statistics record to the host, fetched while the projection runs
+        rec_parts = [row_offsets.to(torch.float64)]
+        rec_parts.append(kept.to(torch.float64) if kept is not None else torch.full((B,), float(T), dtype=torch.float64, device=dev))
+        rec_parts.append(k_dev.to(torch.float64) if k_dev is not None else torch.tensor([float(k_host), float(adaptive_host)], dtype=torch.float64, device=dev))
+        rec_parts.append(head_sums.to(torch.float64))
+        rec_parts.append(proto_sums.to(torch.float64) if proto_sums is not None else torch.zeros(3, dtype=torch.float64, device=dev))
+        rec_dev = torch.cat(rec_parts)
+        if self._pin is None or self._pin.numel() != rec_dev.numel():
+            self._pin = torch.empty(rec_dev.numel(), dtype=torch.float64, pin_memory=True)
+        self._pin.copy_(rec_dev, non_blocking=True)
+        ev_rec = torch.cuda.Event()
+        ev_rec.record()
+
+        # 5. projection + RoPE + head-major relayout (does not depend on the record)
+        use_quant = bool(self.quantize_sparse_int8 and not self.training)
+        q, k, v, amax = self._project_qkv(x, want_amax=use_quant and self.quantize_sparse_int8_mode == "max")
+
+        ev_rec.synchronize()
+        rec = self._pin.tolist()
+        nbh = B * H
+        offs_host = [int(vv) for vv in rec[: nbh + 1]]
+        kept_host = [int(vv) for vv in rec[nbh + 1: nbh + 1 + B]]
+        p0 = nbh + 1 + B
+        topk, adaptive_topk = int(rec[p0]), int(rec[p0 + 1])
+        score_sum, entropy_sum = rec[p0 + 2], rec[p0 + 3]
+        sim_sum, bs_sum, bs_pos = rec[p0 + 4], rec[p0 + 5], rec[p0 + 6]
+        counts = [offs_host[i + 1] - offs_host[i] for i in range(nbh)]
+        total_rows = offs_host[-1]
+        max_rows_est = max(counts) if counts else 0
+        total_active_heads = sum(1 for c in counts if c > 0)
+        token_keep_fraction = float(sum(kept_host)) / float(B * T) if self.token_sparse else 1.0
+        self._last_target_k = topk
+        if topk <= 0:
+            raise RuntimeError("ASPA requires at least one active head per token")
+        density_est = float(max_rows_est) / float(max(1, T))
+        self._update_density(density_est)
+        density_threshold = self._density_threshold()
+        all_rows_active = total_rows == nbh * T
+        force_dense, dense_reason = False, None
+        if alpha <= self.dense_alpha_cutoff and not self.quantize_sparse_int8:
+            force_dense, dense_reason = True, "alpha"
+        if density_threshold is not None and density_est >= density_threshold:
+            force_dense, dense_reason = True, dense_reason or "density"
+        elif all_rows_active and self.force_dense_when_full:
+            force_dense, dense_reason = True, dense_reason or "full"
+        if alpha >= 0.95:
+            dense_reason = None if dense_reason == "alpha" else dense_reason
+            force_dense = False
+        if use_proto:
+            n_tok = float(B * T)
+            self._last_proto_stats = {"max_sim_mean": sim_sum / n_tok, "blend_mean": bs_sum / n_tok,
+                                      "active_tokens": int(round(bs_pos))}
+        else:
+            self._last_proto_stats = None
+
+        # 6. attention
+        out = torch.zeros((B, T, C), dtype=x.dtype, device=dev)
+        exec_mode = "sparse"
+        common_state = {"density": density_est, "target_k": int(topk),
+                        "force_dense_threshold": None if density_threshold is None else float(density_threshold),
+                        "quantized": False, "token_keep_fraction": float(token_keep_fraction),
+                        "mode_setting": self.mode_setting, "mode_selected": f"cvt(alpha={alpha:.2f})",
+                        "shortlist_alpha": float(alpha)}
+        if force_dense:
+            if token_mask_u8 is None:
+                d_offs, d_tok = self._identity_rows(B, T, dev)
+                d_total, d_max = nbh * T, T
+            else:  # every head, kept tokens only: rows of dropped tokens are zero either way (aspa.py:1841-1842)
+                all_bits = torch.where(token_mask_u8.view(-1) != 0, torch.full((), (1 << H) - 1 if H < 64 else -1, dtype=torch.int64, device=dev),
+                                       torch.zeros((), dtype=torch.int64, device=dev))
+                d_offs, d_tok = ops.pack_rows(all_bits, B, T, H, B * T * H)
+                d_total, d_max = H * sum(kept_host), max(kept_host)
+            if d_total > 0:
+                attention_packed(q, k, v, row_offsets=d_offs, token_idx=d_tok, max_rows=d_max, total_rows=d_total, H=H,
+                                 out=out, out_layout=N.OUT_TOKEN_MAJOR)
+            _record_backend(BACKEND_NAME, device=str(dev), heads=nbh, tokens=T, max_rows=int(d_max))
+            mode_str = "dense_alpha" if dense_reason == "alpha" else ("dense" if total_active_heads == nbh else "dense_auto")
+            exec_mode = mode_str
+            self._last_sparse_state = dict(common_state, mode=mode_str, backend=BACKEND_NAME, max_rows=max_rows_est,
+                                           dense_reason=dense_reason)
+        elif total_rows == 0:
+            dense_reason = None
+            self._last_sparse_state = dict(common_state, mode="dense", backend="not_invoked", max_rows=max_rows_est,
+                                           dense_reason=None)
+        else:
+            dense_reason = None
+            runtime = self._prepare_linear_runtime(T, B, alpha)
+            L = runtime["effective_L"]
+            win = min(runtime["window"], L, runtime["local_cap"]) if (self.linear_use_local and runtime["local_cap"] > 0) else 0
+            slots = 0
+            if self.linear_use_anchors and runtime["anchor_stride"] > 0 and runtime["anchor_cap"] > 0:
+                slots = min(runtime["anchor_cap"], L, max(1, T))
+            pcap = 0
+            if self.linear_use_proto and sim is not None and runtime["proto_cap"] > 0:
+                pcap = min(L, runtime["proto_cap"], T)
+            scales = None
+            qa, ka, va = q, k, v
+            if use_quant:
+                if self.quantize_sparse_int8_mode != "max" and self.quantize_sparse_int8_percentile < 1.0:
+                    raise NotImplementedError("INT8 percentile scaling below 1.0 is not built in the sm_100a path")
+                if amax is None:
+                    amax = torch.stack([ops.head_amax(t_) for t_ in (q, k, v)])
+                qa, s_q = ops.quantize_int8(q, amax[0].contiguous())
+                ka, s_k = ops.quantize_int8(k, amax[1].contiguous())
+                va, s_v = ops.quantize_int8(v, amax[2].contiguous())
+                scales = (s_q, s_k, s_v)
+            tok_used = token_idx[:total_rows] if total_rows < token_idx.numel() else token_idx
+            if max(win, 1) + slots + pcap <= L:
+                lists = limits = None
+                if pcap > 0:
+                    lists, limits = ops.proto_plan(self._last_token_similarity.contiguous(), pcap)
+                plan = ops.make_plan(win, slots, runtime["anchor_stride"], pcap, lists, limits)
+                attention_packed(qa, ka, va, row_offsets=row_offsets, token_idx=tok_used, max_rows=max_rows_est,
+                                 total_rows=total_rows, H=H, scales=scales, plan=plan, out=out,
+                                 out_layout=N.OUT_TOKEN_MAJOR)
+                path = "planned"
+            else:  # the candidate pieces can overflow L: use the exact table builder
+                rows64 = tok_used.to(torch.int64)
+                counts_t = (row_offsets[1:] - row_offsets[:-1]).long()
+                bids = None
+                if pcap > 0:
+                    bids = torch.repeat_interleave(torch.arange(nbh, device=dev) // H, counts_t, output_size=total_rows)
+                cand, lens = ops.build_candidates(
+                    rows64, bids, T, L, linear_window=runtime["window"], anchor_stride=runtime["anchor_stride"],
+                    use_local=self.linear_use_local, use_anchors=self.linear_use_anchors,
+                    proto_scores=self._last_token_similarity.contiguous() if pcap > 0 else None,
+                    local_cap=runtime["local_cap"], anchor_cap=runtime["anchor_cap"], proto_cap=runtime["proto_cap"])
+                attention_packed(qa, ka, va, row_offsets=row_offsets, token_idx=tok_used, max_rows=max_rows_est,
+                                 total_rows=total_rows, H=H, scales=scales, cand=cand, cand_len=lens, out=out,
+                                 out_layout=N.OUT_TOKEN_MAJOR)
+                path = "table"
+            _record_backend(BACKEND_NAME, device=str(dev), heads=nbh, tokens=T, max_rows=int(max_rows_est),
+                            quantized=bool(use_quant), candidates=path)
+            self._last_shortlist_backend_info = get_last_backend_info()
+            exec_mode = "shortlist"
+            active_heads = [i for i, c in enumerate(counts) if c > 0]
+            state = dict(common_state, mode="shortlist", backend=BACKEND_NAME, max_rows=int(max_rows_est),
+                         cache_hit=False, token_idx=tok_used, row_offsets_all=row_offsets,
+                         active_head_indices=torch.tensor(active_heads, dtype=torch.long, device=dev),
+                         row_offsets=torch.tensor([offs_host[i] for i in active_heads] + [total_rows], dtype=torch.int32, device=dev),
+                         linear_L=int(self.linear_L), linear_window=int(self.linear_window),
+                         linear_anchor_stride=int(self.linear_anchor_stride), linear_shortlist_backend=BACKEND_NAME)
+            self._last_sparse_state = state
+
+        self.last_head_consensus = None if self.training else out
+        y = self.dropout(self.proj(out))
+
+        # 7. telemetry from the host record
+        n_tok = float(B * T)
+        denom = max(float(total_rows), 1.0)
+        unique_heads = len({i % H for i, c in enumerate(counts) if c > 0})
+        stats = {
+            "top_k": int(topk), "mean_gate_prob": float(score_sum / denom), "router_entropy": float(entropy_sum / n_tok),
+            "mean_active_per_token": float(total_rows / n_tok), "unique_heads": int(unique_heads),
+            "active_fraction": float(total_rows / (n_tok * H)), "max_active_rows": int(max_rows_est),
+            "max_active_density": float(density_est), "target_k": int(self._last_target_k or topk), "seq_len": int(T),
+            "active_min": int(self.h_active_min), "active_max": int(self.h_active_max),
+            "force_dense_threshold": None if density_threshold is None else float(density_threshold),
+            "active_curve": float(self.h_active_curve), "token_keep_fraction": float(token_keep_fraction),
+            "mode": exec_mode, "mode_selected": f"cvt(alpha={alpha:.2f})", "shortlist_alpha": float(alpha),
+            "router_top_p": float(self.router_top_p), "nucleus_k": int(adaptive_topk), "top_a_consensus": True}
+        if dense_reason is not None:
+            stats["dense_reason"] = dense_reason
+        if alpha > 0.0:
+            stats.update(linear_L=int(self.linear_L), linear_window=int(self.linear_window),
+                         linear_anchor_stride=int(self.linear_anchor_stride), linear_shortlist_backend=BACKEND_NAME)
+        if self._last_proto_stats:
+            stats["proto"] = dict(self._last_proto_stats)
+            stats["dna"] = dict(self._last_proto_stats)
+        self.last_head_stats = stats
+        self.last_router_reg = self._router_regulariser(gate, B, T) if self.router_reg_lambda > 0.0 else None
+        self._top_head_indices, self._top_head_scores = top_idx.view(B, T, -1), top_score.view(B, T, -1)
+        self._last_gate_probs = gate.view(B, T, G)
+
+        # 8. prototype EMA (runs in eval mode too, aspa.py:1917); a decay of exactly 1 leaves the state untouched
+        if use_proto and self.routing_usage_ema is not None and self.routing_confidence is not None \
+                and self.proto_decay != 1.0:
+            upd = ops.proto_ema_update(x2d, gate, self.proto_decay, self.routing_prototypes, self.routing_usage_ema,
+                                       self.routing_confidence)
+            self._last_proto_updated = upd
+        self._finalize_latency(f"cvt(alpha={alpha:.2f})::{exec_mode}", ev0, t_start)
+        return y
+
+    def _router_regulariser(self, gate: torch.Tensor, B: int, T: int) -> Optional[torch.Tensor]:
+        parts = {p.strip() for p in str(self.router_reg_mode or "").lower().replace("|", ",").replace("+", ",").split(",")
+                 if p.strip()} or {"entropy"}
+        terms = []
+        if parts & {"entropy", "ent"}:
+            terms.append((gate.clamp_min(1e-9).log() * gate).sum(dim=-1).mean())
+        if parts & {"l1", "l_1"}:
+            terms.append((gate.sum(dim=-1) ** self.router_reg_beta).mean())
+        if not terms:
+            return None
+        total = terms[0]
+        for t_ in terms[1:]:
+            total = total + t_
+        return self.router_reg_lambda * total
+
+    def _finalize_latency(self, label: str, ev0, t_start) -> Optional[float]:
+        latency = None
+        if self.track_latency and ev0 is not None:
+            ev1 = torch.cuda.Event(enable_timing=True)
+            ev1.record()
+            ev1.synchronize()
+            latency = float(ev0.elapsed_time(ev1))
+            self._latency_ema = latency if self._latency_ema is None else 0.8 * self._latency_ema + 0.2 * latency
+        for d in (self.last_head_stats, self._last_sparse_state):
+            if d is not None:
+                if latency is not None:
+                    d["latency_ms"] = latency
+                d["mode_selected"] = label
+        if self.last_head_stats is not None:
+            self.last_head_stats["mode_setting"] = self.mode_setting
+        return latency
+
+
+class AdaptiveSparseProtoAttention(AdaptiveSparseAttention):
+    """The layer with prototype-guided routing switched on (reference aspa.py:1935-1944)."""
+
+    def __init__(self, config: ModelConfig):
+        if not getattr(config, "attn_proto_enable", False):
+            try:
+                setattr(config, "attn_proto_enable", True)
+            except Exception:
+                pass
+        super().__init__(config)
+
+
+class AdaptiveSparseAttentionBlock(nn.Module):
+    """Pre-norm transformer block around the layer (reference aspa.py:1947-1990)."""
+
+    def __init__(self, config: ModelConfig):
+        super().__init__()
+        self.ln1 = _build_norm(config)
+        cls = AdaptiveSparseProtoAttention if bool(getattr(config, "attn_proto_enable", False)) else AdaptiveSparseAttention
+        self.attn = cls(config)
+        self.ln2 = _build_norm(config)
+        self.mlp = MLP(config)
+        self._is_moe = False
+        self.last_aux_loss = self.last_moe_stats = self.last_router_reg = None
+        self.last_head_stats = self.last_sparse_state = None
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        x = x + self.attn(self.ln1(x))
+        x = x + self.mlp(self.ln2(x))
+        self.last_aux_loss = getattr(self.mlp, "last_aux_loss", None)
+        self.last_router_reg = getattr(self.attn, "last_router_reg", None)
+        self.last_moe_stats = None
+        self.last_head_stats = getattr(self.attn, "last_head_stats", None)
+        self.last_sparse_state = getattr(self.attn, "_last_sparse_state", None)
+        return x

@@ -1,0 +1,423 @@
+"""Two-pass chunked shortlist pipeline on the sm_100a kernels.
+
+Same public surface as the reference tool
+(src/proteus_attention/tools/chunked_shortlist.py): ``ChunkedShortlistConfig``
+(:314-366), ``ChunkedShortlistRunner.run`` (:382-827), ``ChunkedShortlistResult``
+(:300-311), ``ChunkedShortlistMetrics`` (:276-297), ``ChunkSummary`` (:265-273).
+
+Pass 1 runs the chunk layer over every chunk, promotes up to ``per_chunk_budget``
+tokens per chunk by router importance (nucleus count + top-k, on the device) and
+writes fixed-size ``(score, index)`` records.  The records of all chunks are merged
+(``aspa_merge_finalise``), the kept rows are gathered into the reduced sequence and
+pass 2 runs a fresh layer over it.
+
+What is different from the reference, on purpose:
+  * scoring always uses router importance (the reference silently switches to L2-norm
+    scoring when its importance tensor is not on a CUDA device, :149-154, :632-647);
+  * the sequence stays resident in HBM when it is given as a CUDA tensor; a CPU tensor is
+    streamed chunk by chunk through pinned double buffers on a copy stream;
+  * no host synchronisation per chunk: per-chunk summaries are built after the loop from
+    one device-to-host copy;
+  * chunks can be sharded over the ranks of a ``torch.distributed`` process group: rank r
+    owns a contiguous range of chunks, records and kept rows are exchanged with
+    all-gather, the merge and pass 2 run replicated (see ``distributed.py``).
+"""
+from __future__ import annotations
+
+import logging
+import math
+import time
+from dataclasses import dataclass, field
+from pathlib import Path
+from typing import Any, Dict, List, Literal, Optional, Sequence, Tuple
+
+import torch
+
+from . import distributed as dist_utils
+from . import ops
+from .aspa import AdaptiveSparseAttention, ModelConfig
+from .sparse_attn import get_last_backend_info
+
+LOGGER = logging.getLogger(__name__)
+MAX_SHORTLIST_CHUNK_TOKENS = 65_536
+BYTES_PER_MB = 1024.0 * 1024.0
+
+
+def _build_model_config(seq_len: int, d_model: int, *, heads: int, sparse_ratio: float, shortlist_alpha: float,
+                        router_top_p: float) -> ModelConfig:
+    """Layer configuration used for both passes (reference :88-137)."""
+    return ModelConfig(
+        vocab_size=0, n_ctx=seq_len, n_layer=1, n_head=heads, d_model=d_model, p_dropout=0.0, bias=False,
+        attn_variant="aspa", attn_h_total=heads, attn_h_active=heads, attn_h_active_min=heads,
+        attn_h_active_max=heads, attn_active_seq_low=max(128, seq_len // 4), attn_active_seq_high=seq_len,
+        attn_mode="linear", attn_token_sparse=True, attn_token_keep_ratio=max(0.0, min(1.0, sparse_ratio)),
+        attn_token_keep_min=max(4, int(seq_len * sparse_ratio * 0.5)), attn_token_keep_guard=4,
+        attn_token_keep_threshold=0.0, attn_linear_L=256, attn_linear_L_base=256, attn_linear_L_min=64,
+        attn_linear_L_max=256, attn_linear_switch_ctx=max(512, min(seq_len, 4096)),
+        attn_linear_policy="local+anchors", attn_proto_enable=True, attn_proto_threshold=0.2, attn_proto_blend=0.5,
+        attn_proto_temp=0.3, attn_linear_token_keep_schedule="sqrt", attn_linear_token_keep_min_ratio=0.05,
+        attn_track_latency=False, attn_small_seq_dense=0, use_sdpa=False, attn_shortlist_alpha=shortlist_alpha,
+        attn_router_top_p=router_top_p)
+
+
+def _sanitize_mapping(mapping: Dict[str, Any]) -> Dict[str, Any]:
+    out: Dict[str, Any] = {}
+    for key, value in mapping.items():
+        if isinstance(value, torch.Tensor):
+            out[key] = value.detach().cpu().item() if value.numel() == 1 else value.detach().cpu().tolist()
+        elif isinstance(value, dict):
+            out[key] = _sanitize_mapping(value)
+        else:
+            out[key] = value
+    return out
+
+
+@dataclass
+class ChunkSummary:
+    index: int
+    start: int
+    end: int
+    promoted: Sequence[int] = field(default_factory=list)
+    scores: Sequence[float] = field(default_factory=list)
+
+
+@dataclass
+class ChunkedShortlistMetrics:
+    original_tokens: int
+    retained_tokens: int
+    retention_ratio: float
+    chunk_count: int
+    device: str
+    chunk_time_ms: Optional[float] = None
+    final_time_ms: Optional[float] = None
+    total_time_ms: Optional[float] = None
+    peak_memory_mb: Optional[float] = None
+    used_fallback: bool = False
+    chunk_tokens_per_s: Optional[float] = None
+    final_tokens_per_s: Optional[float] = None
+    total_tokens_per_s: Optional[float] = None
+    storage_mode: str = "cpu"
+    host_required_mb: Optional[float] = None
+    host_allocated_mb: Optional[float] = None
+    host_limit_mb: Optional[float] = None
+    storage_reason: Optional[str] = None
+    world_size: int = 1
+
+
+@dataclass
+class ChunkedShortlistResult:
+    keep_indices: torch.Tensor
+    keep_scores: torch.Tensor
+    reduced_sequence: torch.Tensor
+    metrics: ChunkedShortlistMetrics
+    chunks: Sequence[ChunkSummary]
+    final_output: Optional[torch.Tensor] = None
+    final_stats: Optional[Dict[str, Any]] = None
+    backend_info: Optional[Dict[str, Any]] = None
+
+
+@dataclass
+class ChunkedShortlistConfig:
+    seq_len: int
+    d_model: int
+    chunk_len: int
+    buffer_tokens: int
+    per_chunk_budget: int
+    device: torch.device
+    heads: int = 8
+    nucleus_top_p: float = 0.9
+    chunk_sparse_ratio: float = 0.05
+    final_sparse_ratio: float = 0.5
+    seed: Optional[int] = 7
+    report_latency: bool = False
+    progress: bool = False
+    run_final_pass: bool = True
+    shortlist_alpha: float = 1.0
+    storage: Literal["cpu", "disk", "auto", "device"] = "auto"
+    temp_dir: Optional[Path] = None
+    ram_limit_bytes: Optional[int] = None
+    # --- additions of this implementation ---
+    freeze_prototypes: bool = False      # EMA decay 1.0 in pass 1: chunks become independent (needed for sharding)
+    pass1_full_forward: bool = True      # False: pass 1 runs only router + token keep (its attention output is unused)
+    warmup: bool = True                  # the reference's untimed warm-up forward on noise (:583-589)
+    collect_summaries: bool = True       # build per-chunk python lists after the loop
+
+    def validate(self) -> None:
+        if self.seq_len <= 0:
+            raise ValueError("seq_len must be positive.")
+        if self.d_model <= 0:
+            raise ValueError("d_model must be positive.")
+        if self.chunk_len <= 0:
+            raise ValueError("chunk_len must be positive.")
+        if self.chunk_len > MAX_SHORTLIST_CHUNK_TOKENS:
+            raise ValueError(f"chunk_len={self.chunk_len} exceeds MAX_SHORTLIST_CHUNK_TOKENS={MAX_SHORTLIST_CHUNK_TOKENS}.")
+        if self.buffer_tokens <= 0:
+            raise ValueError("buffer_tokens must be positive.")
+        if self.per_chunk_budget <= 0:
+            raise ValueError("per_chunk_budget must be positive.")
+        if not (0.0 < float(self.nucleus_top_p) <= 1.0):
+            raise ValueError("nucleus_top_p must be within (0, 1].")
+        if self.chunk_sparse_ratio <= 0.0:
+            raise ValueError("chunk_sparse_ratio must be positive.")
+        if self.final_sparse_ratio <= 0.0:
+            raise ValueError("final_sparse_ratio must be positive.")
+        if not (0.0 <= self.shortlist_alpha <= 1.0):
+            raise ValueError("shortlist_alpha must be within [0, 1].")
+        if self.storage not in {"cpu", "disk", "auto", "device"}:
+            raise ValueError("storage must be 'cpu', 'disk', 'auto' or 'device'.")
+        if self.ram_limit_bytes is not None and self.ram_limit_bytes <= 0:
+            raise ValueError("ram_limit_bytes must be positive when provided.")
+
+
+class _ChunkFeeder:
+    """Hands out (1, len, C) device views of the chunks this rank owns."""
+
+    def __init__(self, source: torch.Tensor, local_start: int, device: torch.device, chunk_len: int):
+        self.src = source
+        self.off = local_start  # global index of source[:, 0]
+        self.device = device
+        self.on_device = source.is_cuda
+        if not self.on_device:
+            self.copy_stream = torch.cuda.Stream(device=device)
+            shape = (1, chunk_len, source.size(2))
+            self.stage = [torch.empty(shape, dtype=source.dtype, pin_memory=True) for _ in range(2)]
+            self.dev = [torch.empty(shape, dtype=source.dtype, device=device) for _ in range(2)]
+            self.ready = [torch.cuda.Event() for _ in range(2)]
+            self.consumed = [torch.cuda.Event() for _ in range(2)]
+            self.prefetched: Dict[int, int] = {}
+
+    def _issue(self, slot: int, start: int, end: int) -> None:
+        n = end - start
+        self.ready[slot].synchronize()  # the previous upload out of this pinned buffer has finished
+        self.stage[slot][:, :n].copy_(self.src[:, start - self.off:end - self.off])
+        with torch.cuda.stream(self.copy_stream):
+            self.copy_stream.wait_event(self.consumed[slot])
+            self.dev[slot][:, :n].copy_(self.stage[slot][:, :n], non_blocking=True)
+            self.ready[slot].record(self.copy_stream)
+
+    def get(self, i: int, start: int, end: int, nxt: Optional[Tuple[int, int]]) -> torch.Tensor:
+        if self.on_device:
+            return self.src[:, start - self.off:end - self.off]
+        slot = i % 2
+        if self.prefetched.pop(i, None) is None:
+            self._issue(slot, start, end)
+        if nxt is not None:
+            self._issue((i + 1) % 2, nxt[0], nxt[1])
+            self.prefetched[i + 1] = (i + 1) % 2
+        torch.cuda.current_stream().wait_event(self.ready[slot])
+        return self.dev[slot][:, :end - start]
+
+    def done(self, i: int) -> None:
+        if not self.on_device:
+            self.consumed[i % 2].record(torch.cuda.current_stream())
+
+
+class ChunkedShortlistRunner:
+    def __init__(self, config: ChunkedShortlistConfig, *, logger: Optional[logging.Logger] = None,
+                 process_group: Any = None) -> None:
+        self.config = config
+        self.config.validate()
+        self.logger = logger or LOGGER
+        self.group = process_group
+
+    def _make_layer(self, seq_len: int, ratio: float, dtype: torch.dtype, state: Optional[Dict[str, torch.Tensor]],
+                    frozen: bool) -> AdaptiveSparseAttention:
+        cfg = self.config
+        mc = _build_model_config(seq_len, cfg.d_model, heads=cfg.heads, sparse_ratio=ratio,
+                                 shortlist_alpha=cfg.shortlist_alpha, router_top_p=cfg.nucleus_top_p)
+        if frozen:
+            mc.attn_proto_decay = 1.0
+        layer = AdaptiveSparseAttention(mc)
+        if state is not None:
+            layer.load_state_dict(state)
+        layer = layer.to(device=cfg.device, dtype=dtype).eval()
+        layer.use_sdpa = False
+        layer.set_shortlist_alpha(float(cfg.shortlist_alpha))
+        return layer
+
+    @staticmethod
+    def _score_only(layer: AdaptiveSparseAttention, x: torch.Tensor) -> None:
+        """Router + token keep + prototype EMA of one chunk, without the attention whose output pass 1 discards."""
+        B, T, C = x.shape
+        alpha = layer._compute_cvt_alpha(T)
+        layer._current_alpha = alpha
+        ratio = (1.0 - alpha) * float(layer.token_keep_ratio_base) + alpha * float(layer._linear_token_keep_ratio(T))
+        ratio = float(max(0.0, min(1.0, ratio)))
+        x2d = x.contiguous().view(B * T, C)
+        proto_hat = ops.normalize_rows(layer.routing_prototypes)
+        conf_eps = (layer.routing_confidence + 1e-6).to(torch.float32)
+        gate, imp, sim, bs, _ = ops.router_fwd(
+            x2d, layer.head_router.linear.weight.contiguous(), proto_hat, conf_eps, None, temp=layer.proto_temp,
+            threshold=layer.proto_threshold, span=max(1e-6, 1.0 - layer.proto_threshold), blend=layer.proto_blend,
+            usage_boost=0.0, want_stats=False)
+        layer._last_token_importance = imp.view(B, T)
+        guard = min(max(0, layer.token_keep_guard), T)
+        min_keep = max(min(max(0, layer.token_keep_min), T), guard)
+        from .aspa import _py_round_f32
+        need = max(1, min(max(_py_round_f32(ratio * T), min_keep), T))
+        if ratio >= 0.999 and layer.token_keep_threshold <= 0.0:
+            mask = torch.ones((B, T), dtype=torch.uint8, device=x.device)
+        else:
+            mask, _ = ops.token_select(layer._last_token_importance, need, layer.token_keep_threshold, guard)
+        layer._last_token_mask = mask.view(torch.bool)
+        if layer.proto_decay != 1.0:
+            ops.proto_ema_update(x2d, gate, layer.proto_decay, layer.routing_prototypes, layer.routing_usage_ema,
+                                 layer.routing_confidence)
+
+    def run(self, sequence: Optional[torch.Tensor] = None, *, chunk_state: Optional[Dict[str, torch.Tensor]] = None,
+            final_state: Optional[Dict[str, torch.Tensor]] = None, warmup_input: Optional[torch.Tensor] = None,
+            sequence_is_local_shard: bool = False) -> ChunkedShortlistResult:
+        """Run both passes.  ``sequence``: (1, T, C) on the host or the device; ``None`` generates seeded noise as
+        the reference does.  ``chunk_state`` / ``final_state`` optionally supply the layers' ``state_dict`` (the
+        reference draws fresh random weights inside ``run``; ranks of a sharded run must agree on them).  With
+        ``sequence_is_local_shard`` the tensor holds only the chunks this rank owns."""
+        cfg = self.config
+        device = torch.device(cfg.device)
+        if device.type != "cuda":
+            raise RuntimeError("proteus_flux_attention_b200 has no CPU path: ChunkedShortlistConfig.device must be a CUDA device")
+        world, rank = dist_utils.world_and_rank(self.group)
+        if world > 1 and not cfg.freeze_prototypes:
+            raise ValueError("sharding chunks over ranks needs freeze_prototypes=True (chunks must be independent)")
+        n_chunks = math.ceil(cfg.seq_len / cfg.chunk_len)
+        c_lo, c_hi = dist_utils.partition_chunks(n_chunks, world, rank)
+        local_start = c_lo * cfg.chunk_len
+
+        if sequence is not None:
+            if sequence.dim() != 3:
+                raise ValueError("sequence tensor must have shape (B, T, D)")
+            if sequence.size(2) != cfg.d_model:
+                raise ValueError(f"sequence hidden size {sequence.size(2)} does not match d_model={cfg.d_model}")
+            if sequence.size(0) != 1:
+                raise ValueError("Chunked Shortlist runner currently expects batch size of 1.")
+            if not sequence_is_local_shard:
+                if sequence.size(1) < cfg.seq_len:
+                    raise ValueError(f"sequence length {sequence.size(1)} smaller than configured seq_len {cfg.seq_len}")
+                sequence = sequence[:, :cfg.seq_len].detach()
+                source, source_off = sequence, 0
+            else:
+                source, source_off = sequence.detach(), local_start
+            base_dtype = sequence.dtype
+        else:
+            base_dtype = torch.get_default_dtype()
+            gen = torch.Generator(device="cpu")
+            if cfg.seed is not None:
+                gen.manual_seed(int(cfg.seed))
+            source = torch.randn(1, cfg.seq_len, cfg.d_model, generator=gen, device="cpu").to(base_dtype)
+            source_off = 0
+        if cfg.storage == "device" and not source.is_cuda:
+            source = source.to(device)
+        storage_mode = "device" if source.is_cuda else "cpu"
+        host_bytes = int(cfg.seq_len * cfg.d_model * source.element_size())
+
+        chunk_model = self._make_layer(cfg.chunk_len, cfg.chunk_sparse_ratio, base_dtype, chunk_state, cfg.freeze_prototypes)
+        if cfg.warmup:
+            dummy = warmup_input.to(device=device, dtype=base_dtype) if warmup_input is not None else \
+                torch.randn(1, cfg.chunk_len, cfg.d_model, device=device, dtype=base_dtype)
+            chunk_model(dummy)
+            torch.cuda.synchronize(device)
+
+        n_local = c_hi - c_lo
+        budget = cfg.per_chunk_budget
+        rec_scores = torch.zeros((max(n_local, 1), budget), dtype=torch.float32, device=device)
+        rec_idx = torch.full((max(n_local, 1), budget), -1, dtype=torch.int64, device=device)
+        rec_count = torch.zeros((max(n_local, 1),), dtype=torch.int32, device=device)
+        feeder = _ChunkFeeder(source, source_off, device, cfg.chunk_len)
+
+        ev_a = torch.cuda.Event(enable_timing=True)
+        ev_b = torch.cuda.Event(enable_timing=True)
+        ev_c = torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        ev_a.record()
+        bounds = [(c * cfg.chunk_len, min(cfg.seq_len, (c + 1) * cfg.chunk_len)) for c in range(c_lo, c_hi)]
+        for i, (start, end) in enumerate(bounds):
+            xc = feeder.get(i, start, end, bounds[i + 1] if i + 1 < len(bounds) else None)
+            if cfg.pass1_full_forward:
+                chunk_model(xc)
+            else:
+                self._score_only(chunk_model, xc)
+            feeder.done(i)
+            mask = chunk_model._last_token_mask
+            ops.chunk_select(chunk_model._last_token_importance.view(-1),
+                             mask.view(torch.uint8).view(-1) if mask is not None else None, budget,
+                             cfg.nucleus_top_p, start, rec_scores[i], rec_idx[i], rec_count[i:i + 1])
+
+        # exchange: every rank ends up with the records of all chunks, in chunk order
+        all_scores, all_idx, all_count = dist_utils.all_gather_records(self.group, rec_scores, rec_idx, rec_count,
+                                                                      n_chunks, world)
+        keep_idx, keep_sc, keep_count = ops.merge_finalise(all_scores.view(-1), all_idx.view(-1), cfg.seq_len,
+                                                           cfg.buffer_tokens)
+        ev_b.record()
+        k_host = int(keep_count.item())
+        if k_host == 0:
+            raise RuntimeError("Chunked pipeline selected zero tokens; adjust per_chunk_budget or sparse ratios.")
+        keep_idx, keep_sc = keep_idx[:k_host], keep_sc[:k_host]
+        reduced = self._gather_reduced(source, source_off, keep_idx, k_host, device, world, rank, c_lo, c_hi)
+        chunk_time_ms = None
+        final_output = final_stats = backend_info = None
+        final_time_ms = peak_mb = None
+        if cfg.run_final_pass:
+            final_model = self._make_layer(k_host, cfg.final_sparse_ratio, base_dtype, final_state, cfg.freeze_prototypes)
+            torch.cuda.reset_peak_memory_stats(device)
+            final_output = final_model(reduced).detach()
+            backend_info = get_last_backend_info()
+            final_stats = _sanitize_mapping(dict(final_model.last_head_stats or {}))
+            st = {k: v for k, v in (final_model._last_sparse_state or {}).items() if not isinstance(v, torch.Tensor)}
+            if st:
+                final_stats["sparse_state"] = _sanitize_mapping(st)
+        ev_c.record()
+        torch.cuda.synchronize(device)
+        t1 = time.perf_counter()
+        chunk_time_ms = float(ev_a.elapsed_time(ev_b))
+        if cfg.run_final_pass:
+            final_time_ms = float(ev_b.elapsed_time(ev_c))
+            peak_mb = torch.cuda.max_memory_allocated(device) / BYTES_PER_MB
+        total_s = t1 - t0
+
+        summaries: List[ChunkSummary] = []
+        if cfg.collect_summaries:
+            sc_h, ix_h, ct_h = all_scores.cpu(), all_idx.cpu(), all_count.cpu().tolist()
+            for c in range(n_chunks):
+                n = int(ct_h[c])
+                if n == 0:
+                    continue
+                summaries.append(ChunkSummary(index=c, start=c * cfg.chunk_len, end=min(cfg.seq_len, (c + 1) * cfg.chunk_len),
+                                              promoted=ix_h[c, :n].tolist(), scores=sc_h[c, :n].tolist()))
+        metrics = ChunkedShortlistMetrics(
+            original_tokens=cfg.seq_len, retained_tokens=k_host, retention_ratio=float(k_host / max(cfg.seq_len, 1)),
+            chunk_count=len(summaries) if cfg.collect_summaries else n_chunks, device=str(device),
+            chunk_time_ms=chunk_time_ms, final_time_ms=final_time_ms, total_time_ms=float(total_s * 1e3),
+            peak_memory_mb=peak_mb, used_fallback=False,
+            chunk_tokens_per_s=float(cfg.seq_len * 1e3 / chunk_time_ms) if chunk_time_ms and chunk_time_ms > 0 else None,
+            final_tokens_per_s=float(k_host * 1e3 / final_time_ms) if final_time_ms and final_time_ms > 0 else None,
+            total_tokens_per_s=float(cfg.seq_len / total_s) if total_s > 0 else None, storage_mode=storage_mode,
+            host_required_mb=host_bytes / BYTES_PER_MB, host_allocated_mb=None if source.is_cuda else host_bytes / BYTES_PER_MB,
+            host_limit_mb=None, storage_reason=None, world_size=world)
+        self.logger.info("Chunked Shortlist retained %s/%s tokens (%.3f) across %s chunks", metrics.retained_tokens,
+                         metrics.original_tokens, metrics.retention_ratio, n_chunks)
+        return ChunkedShortlistResult(keep_indices=keep_idx.to("cpu"), keep_scores=keep_sc.to("cpu"),
+                                      reduced_sequence=reduced, metrics=metrics, chunks=summaries,
+                                      final_output=final_output, final_stats=final_stats, backend_info=backend_info)
+
+    def _gather_reduced(self, source: torch.Tensor, source_off: int, keep_idx: torch.Tensor, k: int,
+                        device: torch.device, world: int, rank: int, c_lo: int, c_hi: int) -> torch.Tensor:
+        """(1, k, C) rows of the kept tokens, in ascending index order (reference :688-689)."""
+        cfg = self.config
+        full_local = source_off == 0 and source.size(1) >= cfg.seq_len
+        if full_local:
+            if source.is_cuda:
+                return ops.gather_rows(source[0], keep_idx, None, k).unsqueeze(0)
+            return source[:, keep_idx.cpu()].to(device, non_blocking=True)
+        # sharded input: every rank contributes the kept rows that fall inside its own chunks
+        lo, hi = c_lo * cfg.chunk_len, min(cfg.seq_len, c_hi * cfg.chunk_len)
+        mine = (keep_idx >= lo) & (keep_idx < hi)
+        local_idx = (keep_idx[mine] - source_off)
+        if source.is_cuda:
+            rows = ops.gather_rows(source[0], local_idx.contiguous(), None, int(local_idx.numel())) if local_idx.numel() else \
+                source.new_zeros((0, cfg.d_model))
+        else:
+            rows = source[0, local_idx.cpu()].to(device)
+        return dist_utils.all_gather_rows(self.group, rows, k, world).unsqueeze(0)
+
+
+__all__ = ["ChunkedShortlistConfig", "ChunkedShortlistMetrics", "ChunkedShortlistResult", "ChunkedShortlistRunner",
+           "ChunkSummary", "MAX_SHORTLIST_CHUNK_TOKENS"]

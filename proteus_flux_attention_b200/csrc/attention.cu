@@ -1,0 +1,586 @@
+// Attention over packed (head, token) rows.
+//
+//  * attn_rows_kernel   — one warp per row, fp32 math on CUDA cores, any head_dim <= 256, any input dtype.
+//                         Candidate keys come from an explicit table, from the structural shortlist plan
+//                         (local window + strided anchors + prototype picks, de-duplicated on the fly) or
+//                         are "every key <= t".  Also runs as the second pass that adds the gathered extras
+//                         (anchors, prototype picks) to the partial softmax state of the window pass.
+//  * attn_window_kernel — bf16 tensor-core pass over the contiguous local window: a CTA owns 64
+//                         consecutive packed rows of one head, streams the union key range through shared
+//                         memory in 64-key tiles, S = Q K^T and O += P V on mma m16n8k16 with fp32
+//                         accumulation and per-row window masking (rows are sparse tokens, so 16-row MMA
+//                         groups keep the masked-out fraction small).  INT8 inputs are widened to bf16 while
+//                         staging (|v| <= 127 is exact in bf16, dot products of 64 such terms are exact in fp32).
+#include "common.cuh"
+
+namespace aspa {
+
+struct AttnParams {
+  const void* q;
+  const void* k;
+  const void* v;
+  const float* q_scale;
+  const float* k_scale;
+  const float* v_scale;
+  int heads, T, D, H;
+  const int32_t* row_offsets;
+  const int32_t* token_idx;
+  const int64_t* cand;
+  const int64_t* cand_len;
+  int L;
+  int has_plan;
+  aspa_shortlist_plan plan;
+  const float* add_mask;
+  void* out;
+  int out_dtype, out_layout;
+  float scale;
+  float* ws_m;  // [total_rows] running max (natural-log domain, already scaled)
+  float* ws_l;  // [total_rows] running denominator
+  float* ws_o;  // [total_rows][D] unnormalised output
+  int extras_only;  // second pass: skip the local window, merge with ws_*
+  int write_partial;  // window pass: write ws_* instead of the final output
+};
+
+__device__ __forceinline__ int64_t out_index(const AttnParams& p, int bh, int t, int d) {
+  if (p.out_layout == ASPA_OUT_HEAD_MAJOR) return ((int64_t)bh * p.T + t) * p.D + d;
+  const int b = bh / p.H, h = bh % p.H;
+  return (((int64_t)b * p.T + t) * p.H + h) * p.D + d;
+}
+
+__device__ __forceinline__ void store_out(const AttnParams& p, int64_t idx, float v) {
+  if (p.out_dtype == ASPA_BF16)
+    reinterpret_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16_rn(v);
+  else
+    reinterpret_cast<float*>(p.out)[idx] = v;
+}
+
+// ------------------------------------------------------------------------------------------------
+// generic kernel
+// ------------------------------------------------------------------------------------------------
+constexpr int GEN_WARPS = 8;
+constexpr int GEN_MAXD = 256;
+
+template <typename T>
+__device__ __forceinline__ float dot_row(const T* __restrict__ krow, const float* __restrict__ qs, int D) {
+  float acc = 0.f;
+  if (sizeof(T) == 2 && (D & 7) == 0) {
+    const uint4* kv = reinterpret_cast<const uint4*>(krow);
+    for (int c = 0; c < D / 8; ++c) {
+      const uint4 raw = kv[c];
+      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(h2[i]);
+        acc = fmaf(f.x, qs[c * 8 + 2 * i], acc);
+        acc = fmaf(f.y, qs[c * 8 + 2 * i + 1], acc);
+      }
+    }
+  } else if (sizeof(T) == 4 && (D & 3) == 0) {
+    const float4* kv = reinterpret_cast<const float4*>(krow);
+    for (int c = 0; c < D / 4; ++c) {
+      const float4 f = kv[c];
+      acc = fmaf(f.x, qs[c * 4], acc);
+      acc = fmaf(f.y, qs[c * 4 + 1], acc);
+      acc = fmaf(f.z, qs[c * 4 + 2], acc);
+      acc = fmaf(f.w, qs[c * 4 + 3], acc);
+    }
+  } else if (sizeof(T) == 1 && (D & 7) == 0) {
+    const uint2* kv = reinterpret_cast<const uint2*>(krow);
+    for (int c = 0; c < D / 8; ++c) {
+      const uint2 raw = kv[c];
+      const int8_t* b = reinterpret_cast<const int8_t*>(&raw);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc = fmaf((float)b[i], qs[c * 8 + i], acc);
+    }
+  } else {
+    for (int d = 0; d < D; ++d) acc = fmaf(ld_as_float<T>(krow, d), qs[d], acc);
+  }
+  return acc;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(GEN_WARPS * 32) attn_rows_kernel(const AttnParams p) {
+  __shared__ float qs_all[GEN_WARPS][GEN_MAXD];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bh = blockIdx.y;
+  const int start = p.row_offsets[bh];
+  const int cnt = p.row_offsets[bh + 1] - start;
+  const int r = blockIdx.x * GEN_WARPS + warp;
+  if (r >= cnt) return;
+  const int64_t grow = (int64_t)start + r;
+  const int t = p.token_idx[grow];
+  const int D = p.D, Tn = p.T;
+  const T* qh = reinterpret_cast<const T*>(p.q) + (int64_t)bh * Tn * D;
+  const T* kh = reinterpret_cast<const T*>(p.k) + (int64_t)bh * Tn * D;
+  const T* vh = reinterpret_cast<const T*>(p.v) + (int64_t)bh * Tn * D;
+  float* qs = qs_all[warp];
+  for (int d = lane; d < D; d += 32) qs[d] = ld_as_float<T>(qh, (int64_t)t * D + d);
+  __syncwarp();
+  float sc = p.scale;
+  float vscale = 1.f;
+  if (sizeof(T) == 1) {
+    sc *= p.q_scale[bh] * p.k_scale[bh];
+    vscale = p.v_scale[bh];
+  }
+
+  // virtual candidate space
+  const bool explicit_c = p.cand != nullptr;
+  const bool planned = !explicit_c && p.has_plan;
+  int n_loc = 0, loc_start = 0, n_anchor = 0, n_proto = 0, n_virtual = 0, v_begin = 0;
+  const int32_t* plist = nullptr;
+  int astride = 1, j0 = 0;
+  bool anchor_clamps = false;
+  if (explicit_c) {
+    long long len = p.cand_len[grow];
+    n_virtual = (int)max(1LL, min(len, (long long)p.L));
+  } else if (planned) {
+    n_loc = p.plan.window > 0 ? min(t + 1, p.plan.window) : 1;
+    loc_start = t - n_loc + 1;
+    astride = max(1, p.plan.anchor_stride);
+    n_anchor = p.plan.anchor_stride > 0 ? p.plan.anchor_slots : 0;
+    j0 = t / astride + 1;  // first anchor slot that clamps to key 0
+    anchor_clamps = n_anchor > 0 && (t - (long long)n_anchor * astride) < 0;
+    if (p.plan.proto_cap > 0 && p.plan.proto_lists != nullptr) {
+      const int b = bh / p.H;
+      const int nblk = (Tn + p.plan.proto_block - 1) / p.plan.proto_block;
+      plist = p.plan.proto_lists + ((int64_t)b * nblk + t / p.plan.proto_block) * p.plan.proto_list_stride;
+      n_proto = p.plan.proto_limit[(int64_t)b * Tn + t];
+    }
+    n_virtual = n_loc + n_anchor + n_proto;
+    v_begin = p.extras_only ? n_loc : 0;
+  } else {
+    const int max_tok = p.token_idx[start + cnt - 1];
+    n_virtual = p.add_mask ? max_tok + 1 : t + 1;
+  }
+
+  float m = -INFINITY, l = 0.f;
+  float acc[GEN_MAXD / 32];
+#pragma unroll
+  for (int i = 0; i < GEN_MAXD / 32; ++i) acc[i] = 0.f;
+
+  for (int c0 = v_begin; c0 < n_virtual; c0 += 32) {
+    const int c = c0 + lane;
+    int idx = -1;
+    if (c < n_virtual) {
+      if (explicit_c) {
+        long long raw = p.cand[grow * p.L + c];
+        idx = (int)min(max(raw, 0LL), (long long)Tn - 1);
+      } else if (planned) {
+        if (c < n_loc) {
+          idx = loc_start + c;
+        } else if (c < n_loc + n_anchor) {
+          const int j = c - n_loc + 1;
+          const long long a = (long long)t - (long long)j * astride;
+          if (a >= 0) {
+            if (a < loc_start) idx = (int)a;
+          } else if (j == j0 && (t % astride) != 0 && loc_start > 0) {
+            idx = 0;
+          }
+        } else {
+          const int u = plist[c - n_loc - n_anchor];
+          if (u >= 0 && u < loc_start) {
+            bool is_anchor = false;
+            if (n_anchor > 0) {
+              const int dlt = t - u;
+              if (dlt % astride == 0 && dlt / astride >= 1 && dlt / astride <= n_anchor) is_anchor = true;
+              if (u == 0 && anchor_clamps) is_anchor = true;
+            }
+            if (!is_anchor) idx = u;
+          }
+        }
+      } else {
+        idx = c;
+      }
+    }
+    float s = -INFINITY;
+    if (idx >= 0) {
+      s = dot_row<T>(kh + (int64_t)idx * D, qs, D) * sc;
+      if (p.add_mask) s += p.add_mask[(int64_t)t * Tn + idx];
+    }
+    const float m_new = fmaxf(m, warp_max(s));
+    if (m_new == -INFINITY) continue;  // nothing valid yet (warp-uniform)
+    const float pr = (s == -INFINITY) ? 0.f : __expf(s - m_new);
+    const float corr = (m == -INFINITY) ? 0.f : __expf(m - m_new);
+    l = l * corr + warp_sum(pr);
+    m = m_new;
+#pragma unroll
+    for (int i = 0; i < GEN_MAXD / 32; ++i) acc[i] *= corr;
+    const unsigned live = __ballot_sync(0xffffffffu, pr > 0.f);
+    for (unsigned rem = live; rem; rem &= rem - 1) {
+      const int src = __ffs(rem) - 1;
+      const float pc = __shfl_sync(0xffffffffu, pr, src);
+      const int ic = __shfl_sync(0xffffffffu, idx, src);
+      const T* vrow = vh + (int64_t)ic * D;
+#pragma unroll
+      for (int i = 0; i < GEN_MAXD / 32; ++i) {
+        const int d = lane + 32 * i;
+        if (d < D) acc[i] = fmaf(pc, ld_as_float<T>(vrow, d), acc[i]);
+      }
+    }
+  }
+
+  if (p.extras_only) {
+    const float m1 = p.ws_m[grow], l1 = p.ws_l[grow];
+    const float mm = fmaxf(m, m1);
+    const float c1 = (m1 == -INFINITY) ? 0.f : __expf(m1 - mm);
+    const float c2 = (m == -INFINITY) ? 0.f : __expf(m - mm);
+    const float lt = l1 * c1 + l * c2;
+    const float inv = lt > 0.f ? 1.f / lt : 0.f;
+#pragma unroll
+    for (int i = 0; i < GEN_MAXD / 32; ++i) {
+      const int d = lane + 32 * i;
+      if (d < D) {
+        // the window pass stores raw P.V (no value scale); acc here is raw too
+        const float o = (p.ws_o[grow * D + d] * c1 + acc[i] * c2) * inv * vscale;
+        store_out(p, out_index(p, bh, t, d), o);
+      }
+    }
+    return;
+  }
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+  for (int i = 0; i < GEN_MAXD / 32; ++i) {
+    const int d = lane + 32 * i;
+    if (d < D) store_out(p, out_index(p, bh, t, d), acc[i] * inv * vscale);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// tensor-core window kernel (D = 64, bf16 or int8 inputs)
+// ------------------------------------------------------------------------------------------------
+constexpr int WK_ROWS = 64;   // packed rows per CTA
+constexpr int WK_KEYS = 64;   // keys per tile
+constexpr int WK_D = 64;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* ptr) { return (uint32_t)__cvta_generic_to_shared(ptr); }
+
+// 64x64 bf16 tile, rows of 128 B = 8 chunks of 16 B; chunk c of row r lives at chunk (c ^ (r & 7)).
+__device__ __forceinline__ int swz(int row, int chunk) { return row * 128 + ((chunk ^ (row & 7)) << 4); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// 8 consecutive elements of a row -> one 16-byte bf16 chunk
+template <typename T>
+__device__ __forceinline__ uint4 load_chunk(const T* row, int chunk);
+template <>
+__device__ __forceinline__ uint4 load_chunk<__nv_bfloat16>(const __nv_bfloat16* row, int chunk) {
+  return reinterpret_cast<const uint4*>(row)[chunk];
+}
+template <>
+__device__ __forceinline__ uint4 load_chunk<int8_t>(const int8_t* row, int chunk) {
+  const uint2 raw = reinterpret_cast<const uint2*>(row)[chunk];
+  const int8_t* b = reinterpret_cast<const int8_t*>(&raw);
+  uint4 o;
+  o.x = pack_bf16((float)b[0], (float)b[1]);
+  o.y = pack_bf16((float)b[2], (float)b[3]);
+  o.z = pack_bf16((float)b[4], (float)b[5]);
+  o.w = pack_bf16((float)b[6], (float)b[7]);
+  return o;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128) attn_window_kernel(const AttnParams p) {
+  __shared__ __align__(1024) unsigned char q_s[WK_ROWS * 128];
+  __shared__ __align__(1024) unsigned char k_s[WK_KEYS * 128];
+  __shared__ __align__(1024) unsigned char v_s[WK_KEYS * 128];
+  __shared__ int ts[WK_ROWS];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int bh = blockIdx.y;
+  const int start = p.row_offsets[bh];
+  const int cnt = p.row_offsets[bh + 1] - start;
+  const int r0 = blockIdx.x * WK_ROWS;
+  if (r0 >= cnt) return;
+  const int nrows = min(WK_ROWS, cnt - r0);
+  const int Tn = p.T;
+  const int window = p.has_plan ? (p.plan.window > 0 ? p.plan.window : 1) : (Tn + 1);  // no plan = causal
+  const T* qh = reinterpret_cast<const T*>(p.q) + (int64_t)bh * Tn * WK_D;
+  const T* kh = reinterpret_cast<const T*>(p.k) + (int64_t)bh * Tn * WK_D;
+  const T* vh = reinterpret_cast<const T*>(p.v) + (int64_t)bh * Tn * WK_D;
+
+  if (tid < WK_ROWS) ts[tid] = tid < nrows ? p.token_idx[start + r0 + tid] : -1;
+  __syncthreads();
+  // Q rows (gathered) -> swizzled shared tile
+  for (int c = tid; c < WK_ROWS * 8; c += 128) {
+    const int row = c >> 3, ch = c & 7;
+    uint4 val = make_uint4(0, 0, 0, 0);
+    if (ts[row] >= 0) val = load_chunk<T>(qh + (int64_t)ts[row] * WK_D, ch);
+    *reinterpret_cast<uint4*>(q_s + swz(row, ch)) = val;
+  }
+  const int t_first = ts[0], t_last = ts[nrows - 1];
+  const int lo = max(0, t_first - window + 1);
+  const int kt_begin = lo / WK_KEYS, kt_end = t_last / WK_KEYS;  // inclusive
+
+  // this warp's rows
+  const int wr0 = warp * 16;
+  const int g = lane >> 2, qd = lane & 3;
+  const int tg0 = ts[wr0 + g], tg1 = ts[wr0 + g + 8];
+  int w_first = -1, w_last = -1;
+  for (int i = 0; i < 16; ++i) {
+    const int tt = ts[wr0 + i];
+    if (tt >= 0) {
+      if (w_first < 0) w_first = tt;
+      w_last = tt;
+    }
+  }
+  const int w_lo = w_first < 0 ? 0 : max(0, w_first - window + 1);
+
+  float sc_log2 = p.scale * 1.4426950408889634f;
+  if (sizeof(T) == 1) sc_log2 *= p.q_scale[bh] * p.k_scale[bh];
+
+  __syncthreads();
+  uint32_t qa[4][4];
+  {
+    const int row = wr0 + (lane & 7) + 8 * ((lane >> 3) & 1);
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks)
+      ldmatrix_x4(smem_u32(q_s + swz(row, ks * 2 + (lane >> 4))), qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3]);
+  }
+
+  float o[8][4];
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[j][e] = 0.f;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+  // register prefetch of the first tile
+  uint4 kreg[4], vreg[4];
+  auto fetch = [&](int kt) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int c = tid + 128 * i;
+      const int row = c >> 3, ch = c & 7;
+      const int key = kt * WK_KEYS + row;
+      if (key < Tn) {
+        kreg[i] = load_chunk<T>(kh + (int64_t)key * WK_D, ch);
+        vreg[i] = load_chunk<T>(vh + (int64_t)key * WK_D, ch);
+      } else {
+        kreg[i] = make_uint4(0, 0, 0, 0);
+        vreg[i] = make_uint4(0, 0, 0, 0);
+      }
+    }
+  };
+  fetch(kt_begin);
+
+  for (int kt = kt_begin; kt <= kt_end; ++kt) {
+    __syncthreads();  // previous tile fully consumed
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int c = tid + 128 * i;
+      const int row = c >> 3, ch = c & 7;
+      *reinterpret_cast<uint4*>(k_s + swz(row, ch)) = kreg[i];
+      *reinterpret_cast<uint4*>(v_s + swz(row, ch)) = vreg[i];
+    }
+    __syncthreads();
+    if (kt < kt_end) fetch(kt + 1);
+
+    const int kb = kt * WK_KEYS;
+    if (w_first < 0 || kb > w_last || kb + WK_KEYS - 1 < w_lo) continue;  // tile outside this warp's rows
+
+    float s[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+#pragma unroll
+      for (int jp = 0; jp < 4; ++jp) {  // pairs of 8-key n-tiles
+        uint32_t b0, b1, b2, b3;
+        const int krow = jp * 16 + (lane & 7) + 8 * (lane >> 4);
+        ldmatrix_x4(smem_u32(k_s + swz(krow, ks * 2 + ((lane >> 3) & 1))), b0, b1, b2, b3);
+        mma_bf16(s[2 * jp], qa[ks], b0, b1);
+        mma_bf16(s[2 * jp + 1], qa[ks], b2, b3);
+      }
+    }
+    // mask + online softmax (base-2 domain)
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = kb + 8 * j + qd * 2 + (e & 1);
+        const int tt = (e < 2) ? tg0 : tg1;
+        const bool ok = tt >= 0 && key <= tt && key > tt - window;
+        const float val = ok ? s[j][e] * sc_log2 : -INFINITY;
+        s[j][e] = val;
+        if (e < 2) mx0 = fmaxf(mx0, val); else mx1 = fmaxf(mx1, val);
+      }
+    }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+    const float cr0 = (m0 == -INFINITY) ? 0.f : exp2f(m0 - mn0);
+    const float cr1 = (m1 == -INFINITY) ? 0.f : exp2f(m1 - mn1);
+    const float base0 = (mn0 == -INFINITY) ? 0.f : mn0, base1 = (mn1 == -INFINITY) ? 0.f : mn1;
+    m0 = mn0;
+    m1 = mn1;
+    l0 *= cr0;
+    l1 *= cr1;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      o[j][0] *= cr0; o[j][1] *= cr0; o[j][2] *= cr1; o[j][3] *= cr1;
+      s[j][0] = exp2f(s[j][0] - base0);
+      s[j][1] = exp2f(s[j][1] - base0);
+      s[j][2] = exp2f(s[j][2] - base1);
+      s[j][3] = exp2f(s[j][3] - base1);
+      l0 += s[j][0] + s[j][1];
+      l1 += s[j][2] + s[j][3];
+    }
+    // O += P V
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {  // 16 keys per step
+      uint32_t pa[4];
+      pa[0] = pack_bf16(s[2 * ks][0], s[2 * ks][1]);
+      pa[1] = pack_bf16(s[2 * ks][2], s[2 * ks][3]);
+      pa[2] = pack_bf16(s[2 * ks + 1][0], s[2 * ks + 1][1]);
+      pa[3] = pack_bf16(s[2 * ks + 1][2], s[2 * ks + 1][3]);
+#pragma unroll
+      for (int jp = 0; jp < 4; ++jp) {  // pairs of 8-wide d tiles
+        uint32_t b0, b1, b2, b3;
+        const int vrow = ks * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);
+        ldmatrix_x4_trans(smem_u32(v_s + swz(vrow, jp * 2 + (lane >> 4))), b0, b1, b2, b3);
+        mma_bf16(o[2 * jp], pa, b0, b1);
+        mma_bf16(o[2 * jp + 1], pa, b2, b3);
+      }
+    }
+  }
+
+  // finish: quad-reduce the denominators
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  const float ln2 = 0.6931471805599453f;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int tt = half ? tg1 : tg0;
+    if (tt < 0) continue;
+    const int64_t grow = (int64_t)start + r0 + wr0 + g + 8 * half;
+    const float mm = half ? m1 : m0, ll = half ? l1 : l0;
+    if (p.write_partial) {
+      if (qd == 0) {
+        p.ws_m[grow] = (mm == -INFINITY) ? -INFINITY : mm * ln2;  // back to the natural-log domain
+        p.ws_l[grow] = ll;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float2 pr = make_float2(o[j][2 * half], o[j][2 * half + 1]);
+        *reinterpret_cast<float2*>(p.ws_o + grow * WK_D + 8 * j + qd * 2) = pr;
+      }
+    } else {
+      float inv = ll > 0.f ? 1.f / ll : 0.f;
+      if (sizeof(T) == 1) inv *= p.v_scale[bh];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int d = 8 * j + qd * 2;
+        const int64_t oi = out_index(p, bh, tt, d);
+        const float a = o[j][2 * half] * inv, b = o[j][2 * half + 1] * inv;
+        if (p.out_dtype == ASPA_BF16)
+          *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(p.out) + oi) = __floats2bfloat162_rn(a, b);
+        else
+          *reinterpret_cast<float2*>(reinterpret_cast<float*>(p.out) + oi) = make_float2(a, b);
+      }
+    }
+  }
+}
+
+}  // namespace aspa
+
+using namespace aspa;
+
+extern "C" int64_t aspa_attn_workspace_bytes(int64_t total_rows, int D) {
+  return (int64_t)sizeof(float) * total_rows * (D + 2);
+}
+
+template <typename T>
+static void launch_generic(const AttnParams& p, int max_rows, cudaStream_t st) {
+  const dim3 grid((unsigned)ceil_div(max_rows, GEN_WARPS), p.heads);
+  attn_rows_kernel<T><<<grid, GEN_WARPS * 32, 0, st>>>(p);
+}
+template <typename T>
+static void launch_window(const AttnParams& p, int max_rows, cudaStream_t st) {
+  const dim3 grid((unsigned)ceil_div(max_rows, WK_ROWS), p.heads);
+  attn_window_kernel<T><<<grid, 128, 0, st>>>(p);
+}
+
+extern "C" int aspa_gather_attn_fwd(const void* q, const void* k, const void* v, int qkv_dtype, const float* q_scale,
+                                    const float* k_scale, const float* v_scale, int heads, int T, int D, int H,
+                                    const int32_t* row_offsets, const int32_t* token_idx, int max_rows,
+                                    int64_t total_rows, const int64_t* cand, const int64_t* cand_len, int L,
+                                    const aspa_shortlist_plan* plan, const float* add_mask, void* out, int out_dtype,
+                                    int out_layout, void* workspace, void* stream) {
+  ASPA_CHECK_ARG(q && k && v && row_offsets && token_idx && out, "null pointer");
+  ASPA_CHECK_ARG(heads > 0 && T > 0 && D > 0 && D <= GEN_MAXD, "head_dim must be in [1, 256]");
+  ASPA_CHECK_ARG(qkv_dtype == ASPA_F32 || qkv_dtype == ASPA_BF16 || qkv_dtype == ASPA_I8, "bad qkv dtype");
+  ASPA_CHECK_ARG(out_dtype == ASPA_F32 || out_dtype == ASPA_BF16, "bad out dtype");
+  ASPA_CHECK_ARG(out_layout == ASPA_OUT_HEAD_MAJOR || (out_layout == ASPA_OUT_TOKEN_MAJOR && H > 0 && heads % H == 0),
+                 "token-major output needs H dividing heads");
+  if (qkv_dtype == ASPA_I8) ASPA_CHECK_ARG(q_scale && k_scale && v_scale, "int8 inputs need q/k/v scales");
+  ASPA_CHECK_ARG((cand == nullptr) == (cand_len == nullptr), "candidates and lengths come together");
+  if (cand) ASPA_CHECK_ARG(L > 0, "candidate width must be positive");
+  if (max_rows <= 0 || total_rows <= 0) return ASPA_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+
+  AttnParams p{};
+  p.q = q; p.k = k; p.v = v;
+  p.q_scale = q_scale; p.k_scale = k_scale; p.v_scale = v_scale;
+  p.heads = heads; p.T = T; p.D = D; p.H = H > 0 ? H : heads;
+  p.row_offsets = row_offsets; p.token_idx = token_idx;
+  p.cand = cand; p.cand_len = cand_len; p.L = L;
+  p.has_plan = (plan != nullptr && cand == nullptr) ? 1 : 0;
+  if (p.has_plan) p.plan = *plan;
+  p.add_mask = add_mask;
+  p.out = out; p.out_dtype = out_dtype; p.out_layout = out_layout;
+  p.scale = 1.0f / sqrtf((float)D);
+  p.ws_m = p.ws_l = p.ws_o = nullptr;
+
+  const bool tensor_ok = D == WK_D && (qkv_dtype == ASPA_BF16 || qkv_dtype == ASPA_I8) && cand == nullptr &&
+                         add_mask == nullptr;
+  if (tensor_ok) {
+    const bool extras = p.has_plan && ((plan->anchor_slots > 0 && plan->anchor_stride > 0) ||
+                                       (plan->proto_cap > 0 && plan->proto_lists != nullptr));
+    if (extras) {
+      ASPA_CHECK_ARG(workspace != nullptr, "workspace required when anchors or prototype picks are on");
+      float* w = reinterpret_cast<float*>(workspace);
+      p.ws_m = w;
+      p.ws_l = w + total_rows;
+      p.ws_o = w + 2 * total_rows;
+      p.write_partial = 1;
+    }
+    if (qkv_dtype == ASPA_BF16) launch_window<__nv_bfloat16>(p, max_rows, st); else launch_window<int8_t>(p, max_rows, st);
+    ASPA_CHECK_LAUNCH();
+    if (extras) {
+      p.write_partial = 0;
+      p.extras_only = 1;
+      if (qkv_dtype == ASPA_BF16) launch_generic<__nv_bfloat16>(p, max_rows, st); else launch_generic<int8_t>(p, max_rows, st);
+      ASPA_CHECK_LAUNCH();
+    }
+    return ASPA_OK;
+  }
+  if (qkv_dtype == ASPA_F32) launch_generic<float>(p, max_rows, st);
+  else if (qkv_dtype == ASPA_BF16) launch_generic<__nv_bfloat16>(p, max_rows, st);
+  else launch_generic<int8_t>(p, max_rows, st);
+  ASPA_CHECK_LAUNCH();
+  return ASPA_OK;
+}

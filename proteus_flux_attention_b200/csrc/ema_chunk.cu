@@ -1,0 +1,431 @@
+// Prototype EMA update, chunk promotion (nucleus + top-budget) and the global merge of the chunked
+// shortlist pipeline.
+#include "common.cuh"
+
+namespace aspa {
+
+// ------------------------------------------------------------------------------------------------
+// Prototype EMA: weighted[g][c] = sum_t probs[t][g] * x[t][c]
+// ------------------------------------------------------------------------------------------------
+constexpr int EMA_TOK = 512;   // tokens per CTA
+constexpr int EMA_CH = 128;    // channels per CTA (one per thread)
+
+template <typename T, int GT>
+__global__ void __launch_bounds__(EMA_CH) ema_partial_kernel(const T* __restrict__ x, int64_t n, int C,
+                                                             const float* __restrict__ gate_probs, int G,
+                                                             float* __restrict__ part_w /*[nchunk][G][C]*/,
+                                                             float* __restrict__ part_c /*[nchunk][G]*/) {
+  __shared__ float ps[64][GT];  // 64 tokens of gate probs at a time
+  const int chunk = blockIdx.x;
+  const int c = blockIdx.y * EMA_CH + threadIdx.x;
+  const int64_t t0 = (int64_t)chunk * EMA_TOK;
+  const int64_t t1 = min(n, t0 + EMA_TOK);
+  float acc[GT];
+  float cnt[GT];
+#pragma unroll
+  for (int g = 0; g < GT; ++g) acc[g] = 0.f, cnt[g] = 0.f;
+  for (int64_t tb = t0; tb < t1; tb += 64) {
+    const int nt = (int)min((int64_t)64, t1 - tb);
+    __syncthreads();
+    for (int i = threadIdx.x; i < 64 * GT; i += EMA_CH) {
+      const int tt = i / GT, g = i % GT;
+      ps[tt][g] = (tt < nt && g < G) ? gate_probs[(tb + tt) * G + g] : 0.f;
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nt; ++tt) {
+      const float xv = c < C ? ld_as_float<T>(x, (tb + tt) * C + c) : 0.f;
+#pragma unroll
+      for (int g = 0; g < GT; ++g) acc[g] = fmaf(ps[tt][g], xv, acc[g]);
+    }
+    if (blockIdx.y == 0 && threadIdx.x == 0) {
+      for (int tt = 0; tt < nt; ++tt)
+#pragma unroll
+        for (int g = 0; g < GT; ++g) cnt[g] += ps[tt][g];
+    }
+  }
+  if (c < C) {
+#pragma unroll
+    for (int g = 0; g < GT; ++g)
+      if (g < G) part_w[((int64_t)chunk * G + g) * C + c] = acc[g];
+  }
+  if (blockIdx.y == 0 && threadIdx.x == 0) {
+#pragma unroll
+    for (int g = 0; g < GT; ++g)
+      if (g < G) part_c[(int64_t)chunk * G + g] = cnt[g];
+  }
+}
+
+__global__ void __launch_bounds__(256) ema_apply_kernel(const float* __restrict__ part_w,
+                                                        const float* __restrict__ part_c, int64_t nchunk, int C,
+                                                        int G, float decay, float om, float* __restrict__ protos,
+                                                        float* __restrict__ usage, float* __restrict__ conf,
+                                                        int32_t* __restrict__ updated) {
+  // grid (ceil(C/256), G).  Fixed summation order over chunks.
+  const int g = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  __shared__ float count_s;
+  if (threadIdx.x == 0) {
+    float cs = 0.f;
+    for (int64_t k = 0; k < nchunk; ++k) cs += part_c[k * G + g];
+    count_s = cs;
+  }
+  __syncthreads();
+  const float count = count_s;
+  const bool on = count > 1e-6f;
+  if (c < C && on) {
+    float w = 0.f;
+    for (int64_t k = 0; k < nchunk; ++k) w += part_w[(k * G + g) * C + c];
+    const float mean = __fdiv_rn(w, count);
+    const int64_t i = (int64_t)g * C + c;
+    protos[i] = __fadd_rn(__fmul_rn(protos[i], decay), __fmul_rn(mean, om));
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    float u = __fmul_rn(usage[g], decay), cf = __fmul_rn(conf[g], decay);
+    if (on) {
+      u = __fadd_rn(u, __fmul_rn(count, om));
+      cf = __fadd_rn(cf, om);
+      if (updated) atomicAdd(updated, 1);
+    }
+    usage[g] = u;
+    conf[g] = cf;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Chunk promotion
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float safe_score(const float* imp, const uint8_t* mask, int i) {
+  float s = imp[i];
+  if (mask && !mask[i]) s = -INFINITY;
+  return isfinite(s) ? s : -1e9f;
+}
+
+__device__ void bitonic_u64(unsigned long long* a, int n) {
+  for (int k = 2; k <= n; k <<= 1)
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const int ixj = i ^ j;
+        if (ixj > i) {
+          const unsigned long long x = a[i], y = a[ixj];
+          if ((x > y) == ((i & k) == 0)) {
+            a[i] = y;
+            a[ixj] = x;
+          }
+        }
+      }
+      __syncthreads();
+    }
+}
+
+__global__ void __launch_bounds__(1024) chunk_select_kernel(const float* __restrict__ imp,
+                                                            const uint8_t* __restrict__ mask, int T, int budget,
+                                                            float top_p, int64_t offset, int P2,
+                                                            float* __restrict__ out_scores,
+                                                            int64_t* __restrict__ out_idx,
+                                                            int32_t* __restrict__ out_count) {
+  extern __shared__ unsigned long long keys[];  // [P2] sort keys, then reused
+  __shared__ int hist[256];
+  __shared__ int sh[4];
+  __shared__ int scan_tmp[33];
+  __shared__ float redf[33];
+  const int limit = min(budget, T);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  // any finite score at all?  max and softmax denominator over the safe scores
+  float mx = -INFINITY;
+  int nfinite = 0;
+  for (int i = tid; i < T; i += blockDim.x) {
+    float raw = imp[i];
+    if (mask && !mask[i]) raw = -INFINITY;
+    nfinite += isfinite(raw) ? 1 : 0;
+    mx = fmaxf(mx, isfinite(raw) ? raw : -1e9f);
+  }
+  mx = warp_max(mx);
+  if (lane == 0) redf[warp] = mx;
+  __syncthreads();
+  if (tid == 0) {
+    float m = redf[0];
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w) m = fmaxf(m, redf[w]);
+    redf[32] = m;
+  }
+  __syncthreads();
+  mx = redf[32];
+  int tot_fin;
+  block_exclusive_scan(nfinite, scan_tmp, &tot_fin);
+  if (tot_fin == 0 || limit <= 0) {
+    if (tid == 0) out_count[0] = 0;
+    return;
+  }
+  float sum = 0.f;
+  for (int i = tid; i < T; i += blockDim.x) sum += expf(safe_score(imp, mask, i) - mx);
+  sum = warp_sum(sum);
+  __syncthreads();
+  if (lane == 0) redf[warp] = sum;
+  __syncthreads();
+  if (tid == 0) {
+    float s = 0.f;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) s += redf[w];
+    redf[32] = s;
+  }
+  __syncthreads();
+  sum = redf[32];
+
+  // radix select of the `limit` best safe scores, ties to the lowest index
+  uint32_t prefix = 0, pmask = 0;
+  int remaining = limit;
+  for (int shift = 24; shift >= 0; shift -= 8) {
+    for (int i = tid; i < 256; i += blockDim.x) hist[i] = 0;
+    __syncthreads();
+    for (int i = tid; i < T; i += blockDim.x) {
+      const uint32_t k = float_key(safe_score(imp, mask, i));
+      if ((k & pmask) == prefix) atomicAdd(&hist[(k >> shift) & 255u], 1);
+    }
+    __syncthreads();
+    if (tid == 0) {
+      int acc = 0, b = 255;
+      for (; b > 0; --b) {
+        if (acc + hist[b] >= remaining) break;
+        acc += hist[b];
+      }
+      sh[0] = b;
+      sh[1] = remaining - acc;
+    }
+    __syncthreads();
+    prefix |= ((uint32_t)sh[0]) << shift;
+    pmask |= 255u << shift;
+    remaining = sh[1];
+    __syncthreads();
+  }
+  for (int i = tid; i < P2; i += blockDim.x) keys[i] = ~0ull;
+  __syncthreads();
+  int ties_seen = 0, written = 0;
+  for (int base = 0; base < T; base += blockDim.x) {
+    const int i = base + tid;
+    uint32_t k = 0;
+    bool gt = false, tie = false;
+    if (i < T) {
+      k = float_key(safe_score(imp, mask, i));
+      gt = k > prefix;
+      tie = k == prefix;
+    }
+    int tt, to;
+    const int rank_t = block_exclusive_scan(tie ? 1 : 0, scan_tmp, &tt);
+    const bool on = gt || (tie && ties_seen + rank_t < remaining);
+    const int pos = block_exclusive_scan(on ? 1 : 0, scan_tmp, &to);
+    if (on) keys[written + pos] = ((unsigned long long)(~k) << 32) | (unsigned)i;
+    written += to;
+    ties_seen += tt;
+  }
+  __syncthreads();
+  bitonic_u64(keys, P2);
+  // cumulative softmax mass over the sorted picks (parallel scan, limit <= P2)
+  int keep = limit;
+  if (top_p < 1.0f) {
+    float running = 0.f;
+    int below = 0;
+    for (int base = 0; base < limit; base += blockDim.x) {
+      const int i = base + tid;
+      float pr = 0.f;
+      if (i < limit) {
+        const float sc = key_float(~(uint32_t)(keys[i] >> 32));
+        pr = __fdiv_rn(expf(sc - mx), sum);
+      }
+      // inclusive scan of pr across the block
+      float inc = pr;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float t = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += t;
+      }
+      __syncthreads();
+      if (lane == 31) redf[warp] = inc;
+      __syncthreads();
+      if (warp == 0) {
+        float w = lane < (int)(blockDim.x >> 5) ? redf[lane] : 0.f;
+        float winc = w;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const float t = __shfl_up_sync(0xffffffffu, winc, o);
+          if (lane >= o) winc += t;
+        }
+        redf[lane] = winc - w;
+        if (lane == 31) redf[32] = winc;
+      }
+      __syncthreads();
+      const float mass = running + redf[warp] + inc;
+      int tb;
+      block_exclusive_scan((i < limit && mass < top_p) ? 1 : 0, scan_tmp, &tb);
+      below += tb;
+      running += redf[32];
+      __syncthreads();
+    }
+    keep = below;
+    if (keep < T) keep += 1;
+    keep = max(1, keep);
+    keep = min(limit, keep);
+  }
+  // masked / non-finite picks sort last (their safe score is -1e9): drop them
+  int nvalid = 0;
+  for (int base = 0; base < keep; base += blockDim.x) {
+    const int i = base + tid;
+    bool ok = false;
+    int idx = 0;
+    float raw = 0.f;
+    if (i < keep) {
+      idx = (int)(keys[i] & 0xffffffffu);
+      raw = imp[idx];
+      ok = isfinite(raw) && !(mask && !mask[idx]);
+    }
+    int tv;
+    const int pos = block_exclusive_scan(ok ? 1 : 0, scan_tmp, &tv);
+    if (ok) {
+      out_scores[nvalid + pos] = raw;
+      out_idx[nvalid + pos] = (int64_t)idx + offset;
+    }
+    nvalid += tv;
+  }
+  if (tid == 0) out_count[0] = nvalid;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Global merge
+// ------------------------------------------------------------------------------------------------
+__global__ void merge_scatter_kernel(const float* __restrict__ scores, const int64_t* __restrict__ indices,
+                                     int64_t n, int64_t seq_len, uint32_t* __restrict__ table) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int64_t idx = indices[i];
+  if (idx < 0 || idx >= seq_len) return;
+  // a duplicated index is represented by its lowest score; key 0 is reserved for "absent"
+  atomicMin(&table[idx], max(float_key(scores[i]), 1u));
+}
+
+__global__ void __launch_bounds__(1024) merge_select_kernel(const uint32_t* __restrict__ table, int64_t seq_len,
+                                                            int max_tokens, int64_t* __restrict__ keep_idx,
+                                                            float* __restrict__ keep_scores,
+                                                            int32_t* __restrict__ keep_count) {
+  __shared__ int hist[256];
+  __shared__ int sh[4];
+  __shared__ int scan_tmp[33];
+  const int tid = threadIdx.x;
+  auto key_at = [table](int64_t i) { const uint32_t k = table[i]; return k == 0xffffffffu ? 0u : k; };
+  int present = 0;
+  for (int64_t i = tid; i < seq_len; i += blockDim.x) present += key_at(i) != 0u ? 1 : 0;
+  int n_present;
+  block_exclusive_scan(present, scan_tmp, &n_present);
+  const int need = min(max_tokens, n_present);
+  if (need <= 0) {
+    if (tid == 0) keep_count[0] = 0;
+    return;
+  }
+  uint32_t prefix = 0, pmask = 0;
+  int remaining = need;
+  for (int shift = 24; shift >= 0; shift -= 8) {
+    for (int i = tid; i < 256; i += blockDim.x) hist[i] = 0;
+    __syncthreads();
+    for (int64_t i = tid; i < seq_len; i += blockDim.x) {
+      const uint32_t k = key_at(i);
+      if (k != 0u && (k & pmask) == prefix) atomicAdd(&hist[(k >> shift) & 255u], 1);
+    }
+    __syncthreads();
+    if (tid == 0) {
+      int acc = 0, b = 255;
+      for (; b > 0; --b) {
+        if (acc + hist[b] >= remaining) break;
+        acc += hist[b];
+      }
+      sh[0] = b;
+      sh[1] = remaining - acc;
+    }
+    __syncthreads();
+    prefix |= ((uint32_t)sh[0]) << shift;
+    pmask |= 255u << shift;
+    remaining = sh[1];
+    __syncthreads();
+  }
+  int ties_seen = 0, written = 0;
+  for (int64_t base = 0; base < seq_len; base += blockDim.x) {
+    const int64_t i = base + tid;
+    uint32_t k = 0;
+    if (i < seq_len) k = key_at(i);
+    const bool gt = k != 0u && k > prefix, tie = k != 0u && k == prefix;
+    int tt, to;
+    const int rank_t = block_exclusive_scan(tie ? 1 : 0, scan_tmp, &tt);
+    const bool on = gt || (tie && ties_seen + rank_t < remaining);
+    const int pos = block_exclusive_scan(on ? 1 : 0, scan_tmp, &to);
+    if (on) {
+      keep_idx[written + pos] = i;
+      keep_scores[written + pos] = key_float(k);
+    }
+    written += to;
+    ties_seen += tt;
+  }
+  if (tid == 0) keep_count[0] = written;
+}
+
+}  // namespace aspa
+
+using namespace aspa;
+
+extern "C" int64_t aspa_proto_ema_scratch(int64_t n, int C, int G) {
+  const int64_t nchunk = ceil_div(n, EMA_TOK);
+  return (int64_t)sizeof(float) * (nchunk * G * C + nchunk * G);
+}
+
+template <typename T>
+static int ema_launch(const T* x, int64_t n, int C, const float* gp, int G, float* pw, float* pc, cudaStream_t st) {
+  const dim3 grid((unsigned)ceil_div(n, EMA_TOK), (unsigned)ceil_div(C, EMA_CH));
+  if (G <= 8) ema_partial_kernel<T, 8><<<grid, EMA_CH, 0, st>>>(x, n, C, gp, G, pw, pc);
+  else if (G <= 16) ema_partial_kernel<T, 16><<<grid, EMA_CH, 0, st>>>(x, n, C, gp, G, pw, pc);
+  else if (G <= 32) ema_partial_kernel<T, 32><<<grid, EMA_CH, 0, st>>>(x, n, C, gp, G, pw, pc);
+  else ema_partial_kernel<T, 64><<<grid, EMA_CH, 0, st>>>(x, n, C, gp, G, pw, pc);
+  return 0;
+}
+
+extern "C" int aspa_proto_ema_update(const void* x, int x_dtype, int64_t n, int C, const float* gate_probs, int G,
+                                     double decay, float* prototypes, float* usage, float* confidence, void* scratch,
+                                     int32_t* updated, void* stream) {
+  ASPA_CHECK_ARG(x && gate_probs && prototypes && usage && confidence && scratch, "null pointer");
+  ASPA_CHECK_ARG(n > 0 && C > 0 && G > 0 && G <= 64, "bad sizes (G <= 64)");
+  ASPA_CHECK_ARG(x_dtype == ASPA_F32 || x_dtype == ASPA_BF16, "x must be fp32 or bf16");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t nchunk = ceil_div(n, EMA_TOK);
+  float* pw = reinterpret_cast<float*>(scratch);
+  float* pc = pw + nchunk * G * C;
+  if (updated) cudaMemsetAsync(updated, 0, sizeof(int32_t), st);
+  if (x_dtype == ASPA_F32) ema_launch<float>((const float*)x, n, C, gate_probs, G, pw, pc, st);
+  else ema_launch<__nv_bfloat16>((const __nv_bfloat16*)x, n, C, gate_probs, G, pw, pc, st);
+  ASPA_CHECK_LAUNCH();
+  ema_apply_kernel<<<dim3((unsigned)ceil_div(C, 256), G), 256, 0, st>>>(pw, pc, nchunk, C, G, (float)decay, (float)(1.0 - decay), prototypes, usage,
+                                                                       confidence, updated);
+  ASPA_CHECK_LAUNCH();
+  return ASPA_OK;
+}
+
+extern "C" int aspa_chunk_select(const float* importance, const uint8_t* token_mask, int T, int budget, float top_p,
+                                 int64_t offset, float* out_scores, int64_t* out_idx, int32_t* out_count,
+                                 void* stream) {
+  ASPA_CHECK_ARG(importance && out_scores && out_idx && out_count, "null pointer");
+  ASPA_CHECK_ARG(T > 0 && budget > 0, "bad sizes");
+  int P2 = 2;
+  while (P2 < std::min(budget, T)) P2 <<= 1;
+  const size_t smem = sizeof(unsigned long long) * P2;
+  ASPA_CHECK_ARG(smem <= 200 * 1024, "per-chunk budget too large (max 25600)");
+  cudaFuncSetAttribute(chunk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  chunk_select_kernel<<<1, 1024, smem, (cudaStream_t)stream>>>(importance, token_mask, T, budget, top_p, offset, P2,
+                                                              out_scores, out_idx, out_count);
+  ASPA_CHECK_LAUNCH();
+  return ASPA_OK;
+}
+
+extern "C" int aspa_merge_finalise(const float* scores, const int64_t* indices, int64_t n, int64_t seq_len,
+                                   int max_tokens, uint32_t* table, int64_t* keep_idx, float* keep_scores,
+                                   int32_t* keep_count, void* stream) {
+  ASPA_CHECK_ARG(scores && indices && table && keep_idx && keep_scores && keep_count, "null pointer");
+  ASPA_CHECK_ARG(n >= 0 && seq_len > 0 && max_tokens > 0, "bad sizes");
+  cudaStream_t st = (cudaStream_t)stream;
+  cudaMemsetAsync(table, 0xff, sizeof(uint32_t) * seq_len, st);
+  if (n > 0) merge_scatter_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, st>>>(scores, indices, n, seq_len, table);
+  merge_select_kernel<<<1, 1024, 0, st>>>(table, seq_len, max_tokens, keep_idx, keep_scores, keep_count);
+  ASPA_CHECK_LAUNCH();
+  return ASPA_OK;
+}

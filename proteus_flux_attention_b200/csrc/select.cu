@@ -1,0 +1,414 @@
+// Token keep (radix select), head budget, per-token head top-k and row packing.
+#include "common.cuh"
+
+namespace aspa {
+
+// ---------------------------------------------------------------------------------------------
+// Radix select helper: one CTA finds the key of rank `need` (1-based, descending) among `n` floats
+// and how many entries equal to it must still be taken.  Keys stream from global/L2 once per pass.
+// ---------------------------------------------------------------------------------------------
+struct SelectResult {
+  uint32_t thr_key;  // key of the need-th largest element
+  int take_ties;     // number of entries == thr_key to accept (lowest indices first)
+};
+
+template <typename KeyFn>
+__device__ SelectResult block_radix_select(int n, int need, KeyFn key_of, int* hist /*256*/, int* sh /*4*/) {
+  uint32_t prefix = 0, mask = 0;
+  int remaining = need;
+  for (int shift = 24; shift >= 0; shift -= 8) {
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      const uint32_t k = key_of(i);
+      if ((k & mask) == prefix) atomicAdd(&hist[(k >> shift) & 255u], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int acc = 0, b = 255;
+      for (; b > 0; --b) {
+        if (acc + hist[b] >= remaining) break;
+        acc += hist[b];
+      }
+      sh[0] = b;
+      sh[1] = remaining - acc;
+    }
+    __syncthreads();
+    prefix |= ((uint32_t)sh[0]) << shift;
+    mask |= 255u << shift;
+    remaining = sh[1];
+    __syncthreads();
+  }
+  SelectResult r;
+  r.thr_key = prefix;
+  r.take_ties = remaining;
+  return r;
+}
+
+__global__ void __launch_bounds__(1024) token_select_kernel(const float* __restrict__ importance, int T, int need0,
+                                                            float threshold, int guard,
+                                                            uint8_t* __restrict__ token_mask,
+                                                            int32_t* __restrict__ kept) {
+  __shared__ int hist[256];
+  __shared__ int sh[4];
+  __shared__ int scan_tmp[33];
+  const float* imp = importance + (int64_t)blockIdx.x * T;
+  uint8_t* out = token_mask + (int64_t)blockIdx.x * T;
+  int need = need0;
+  if (threshold > 0.f) {
+    int c = 0;
+    for (int i = threadIdx.x; i < T; i += blockDim.x) c += imp[i] >= threshold ? 1 : 0;
+    int tot;
+    block_exclusive_scan(c, scan_tmp, &tot);
+    need = max(need, tot);
+  }
+  need = max(need, guard);
+  need = min(max(1, need), T);
+  if (need >= T) {
+    for (int i = threadIdx.x; i < T; i += blockDim.x) out[i] = 1;
+    if (threadIdx.x == 0) kept[blockIdx.x] = T;
+    return;
+  }
+  auto key_of = [imp](int i) { return float_key(imp[i]); };
+  const SelectResult sel = block_radix_select(T, need, key_of, hist, sh);
+  int ties_seen = 0, kept_total = 0;
+  for (int base = 0; base < T; base += blockDim.x) {
+    const int i = base + threadIdx.x;
+    uint32_t k = 0;
+    bool tie = false, gt = false;
+    if (i < T) {
+      k = float_key(imp[i]);
+      gt = k > sel.thr_key;
+      tie = k == sel.thr_key;
+    }
+    int tot;
+    const int rank = block_exclusive_scan(tie ? 1 : 0, scan_tmp, &tot);
+    if (i < T) {
+      bool on = gt || (tie && (ties_seen + rank) < sel.take_ties);
+      if (threshold > 0.f && imp[i] >= threshold) on = true;
+      if (i < guard) on = true;
+      out[i] = on ? 1 : 0;
+      kept_total += on ? 1 : 0;
+    }
+    ties_seen += tot;
+  }
+  int tot;
+  block_exclusive_scan(kept_total, scan_tmp, &tot);
+  if (threadIdx.x == 0) kept[blockIdx.x] = tot;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Head budget
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) head_colsum_kernel(const float* __restrict__ gate_probs, int64_t n, int G,
+                                                          const int32_t* __restrict__ gate_to_head, int H,
+                                                          float* __restrict__ partials /*[H][nblk]*/) {
+  // block handles 1024 tokens; thread t sums gate column (t % G) over a strided subset, then shared tree per head
+  const int64_t t0 = (int64_t)blockIdx.x * 1024;
+  const int64_t t1 = min(n, t0 + 1024);
+  const int lanes_per_tok = G;  // consecutive threads read consecutive gates of a token
+  const int toks_per_iter = blockDim.x / lanes_per_tok;
+  const int g = threadIdx.x % lanes_per_tok, sub = threadIdx.x / lanes_per_tok;
+  float acc = 0.f;
+  if (sub < toks_per_iter)
+    for (int64_t t = t0 + sub; t < t1; t += toks_per_iter) acc += gate_probs[t * G + g];
+  // deterministic: each (g, sub) writes its own slot, then one thread per head adds in fixed order
+  __shared__ float slots[256];
+  slots[threadIdx.x] = (sub < toks_per_iter) ? acc : 0.f;
+  __syncthreads();
+  if (threadIdx.x < H) {
+    float s = 0.f;
+    for (int gg = 0; gg < G; ++gg)
+      if (gate_to_head[gg] == (int)threadIdx.x)
+        for (int sb = 0; sb < toks_per_iter; ++sb) s += slots[sb * lanes_per_tok + gg];
+    partials[(int64_t)threadIdx.x * gridDim.x + blockIdx.x] = s;
+  }
+}
+
+__global__ void head_budget_kernel(const float* __restrict__ partials, int64_t nblk, int H, double n_tokens,
+                                   double top_p, int dense_k, int h_active_min, int linear_head_k, double alpha,
+                                   int32_t* __restrict__ k_out) {
+  __shared__ float mean[64];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  for (int h = w; h < H; h += (blockDim.x >> 5)) {
+    float a = 0.f;
+    for (int64_t i = lane; i < nblk; i += 32) a += partials[(int64_t)h * nblk + i];
+    a = warp_sum(a);
+    if (lane == 0) {
+      float m = (float)((double)a / n_tokens);
+      mean[h] = isfinite(m) ? m : 0.f;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int nucleus = 1;
+    if (dense_k <= 1) {
+      nucleus = max(1, dense_k);
+    } else {
+      float total = 0.f;
+      for (int h = 0; h < H; ++h) total += mean[h];
+      if (total > 0.f) {
+        // selection sort descending (H <= 64)
+        float v[64];
+        for (int h = 0; h < H; ++h) v[h] = mean[h];
+        for (int i = 0; i < H; ++i) {
+          int b = i;
+          for (int j = i + 1; j < H; ++j)
+            if (v[j] > v[b]) b = j;
+          float t = v[i];
+          v[i] = v[b];
+          v[b] = t;
+        }
+        const float target = (float)((double)total * top_p);  // double product, compared in fp32
+        float c = 0.f;
+        int keep = 0;
+        for (int h = 0; h < H; ++h) {
+          c += v[h];
+          if (c < target) ++keep;
+        }
+        if (keep < H) ++keep;
+        nucleus = min(dense_k, max(1, keep));
+      }
+    }
+    const int adaptive = max(h_active_min, min(dense_k, nucleus));
+    const int lin = max(1, min(adaptive, linear_head_k));
+    const double blended = (1.0 - alpha) * (double)adaptive + alpha * (double)lin;
+    int topk = max(1, (int)rint(blended));  // rint = round-half-to-even, as Python's round()
+    topk = min(adaptive, topk);
+    k_out[0] = topk;
+    k_out[1] = adaptive;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Per-token head top-k
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) head_select_kernel(const float* __restrict__ gate_probs, int64_t n, int G,
+                                                          const int32_t* __restrict__ gate_to_head, int H,
+                                                          int k_host, const int32_t* __restrict__ k_dev, int kmax,
+                                                          const uint8_t* __restrict__ token_mask,
+                                                          uint64_t* __restrict__ head_bits,
+                                                          int32_t* __restrict__ top_idx,
+                                                          float* __restrict__ top_score,
+                                                          float* __restrict__ stat_partials) {
+  __shared__ int g2h[128];
+  __shared__ float red[2][8];
+  for (int i = threadIdx.x; i < G; i += blockDim.x) g2h[i] = gate_to_head[i];
+  __syncthreads();
+  const int k = min(k_dev ? k_dev[0] : k_host, kmax);
+  const int64_t tok = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  float score_sum = 0.f, ent = 0.f;
+  if (tok < n) {
+    float hp[64];
+#pragma unroll 8
+    for (int h = 0; h < 64; ++h) hp[h] = 0.f;
+    const float* gp = gate_probs + tok * G;
+    for (int g = 0; g < G; ++g) {
+      const float p = gp[g];
+      ent -= logf(fmaxf(p, 1e-9f)) * p;
+      const int h = g2h[g];
+      // dynamic register indexing would spill; H <= 64 keeps this small enough for local memory
+      hp[h] += p;
+    }
+    uint64_t bits = 0;
+    for (int j = 0; j < kmax; ++j) {
+      int best = -1;
+      float bv = -INFINITY;
+      if (j < k) {
+        for (int h = 0; h < H; ++h)
+          if (!((bits >> h) & 1ull) && hp[h] > bv) {
+            bv = hp[h];
+            best = h;
+          }
+        if (best >= 0) {
+          bits |= 1ull << best;
+          score_sum += bv;
+        }
+      }
+      if (top_idx) top_idx[tok * kmax + j] = best;
+      if (top_score) top_score[tok * kmax + j] = best >= 0 ? bv : 0.f;
+    }
+    if (token_mask && !token_mask[tok]) bits = 0;
+    head_bits[tok] = bits;
+  }
+  if (stat_partials) {
+    score_sum = warp_sum(score_sum);
+    ent = warp_sum(ent);
+    if ((threadIdx.x & 31) == 0) {
+      red[0][threadIdx.x >> 5] = score_sum;
+      red[1][threadIdx.x >> 5] = ent;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float a = 0.f, b = 0.f;
+      for (int w = 0; w < 8; ++w) {
+        a += red[0][w];
+        b += red[1][w];
+      }
+      stat_partials[blockIdx.x] = a;
+      stat_partials[gridDim.x + blockIdx.x] = b;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Row packing.  Segment = 256 consecutive tokens of one batch element.
+// seg_counts[(b*H + h) * nseg + seg] = rows of head h in the segment; an exclusive scan in that order
+// gives every (bh, seg) its first output slot, so rows come out grouped by bh and token-ascending.
+// ---------------------------------------------------------------------------------------------
+constexpr int PK_SEG = 256;
+
+template <bool kFromBits>
+__device__ __forceinline__ uint64_t load_bits(const void* src, int heads_per_batch, int b, int T, int t) {
+  if (kFromBits) return reinterpret_cast<const uint64_t*>(src)[(int64_t)b * T + t];
+  // uint8 mask (heads, T) with a single "batch": bit h set when mask[h][t] != 0 (heads <= 64 per pass)
+  const uint8_t* m = reinterpret_cast<const uint8_t*>(src);
+  uint64_t bits = 0;
+  for (int h = 0; h < heads_per_batch; ++h) bits |= (uint64_t)(m[((int64_t)b * heads_per_batch + h) * T + t] != 0) << h;
+  return bits;
+}
+
+template <bool kFromBits>
+__global__ void __launch_bounds__(PK_SEG) pack_count_kernel(const void* __restrict__ src, int T, int H, int nseg,
+                                                            int32_t* __restrict__ seg_counts) {
+  __shared__ int cnt[64];
+  const int seg = blockIdx.x, b = blockIdx.y;
+  for (int i = threadIdx.x; i < 64; i += blockDim.x) cnt[i] = 0;
+  __syncthreads();
+  const int t = seg * PK_SEG + threadIdx.x;
+  const uint64_t bits = t < T ? load_bits<kFromBits>(src, H, b, T, t) : 0ull;
+  for (int h = 0; h < H; ++h) {
+    const unsigned bal = __ballot_sync(0xffffffffu, (bits >> h) & 1ull);
+    if ((threadIdx.x & 31) == 0 && bal) atomicAdd(&cnt[h], __popc(bal));
+  }
+  __syncthreads();
+  for (int h = threadIdx.x; h < H; h += blockDim.x) seg_counts[((int64_t)b * H + h) * nseg + seg] = cnt[h];
+}
+
+__global__ void __launch_bounds__(1024) pack_scan_kernel(int32_t* __restrict__ seg_counts, int64_t n_entries,
+                                                         int nseg, int32_t* __restrict__ row_offsets, int n_heads) {
+  // single CTA, in-place exclusive scan; row_offsets[bh] = scanned value at (bh, seg 0)
+  __shared__ int tmp[33];
+  int running = 0;
+  for (int64_t base = 0; base < n_entries; base += blockDim.x) {
+    const int64_t i = base + threadIdx.x;
+    const int v = i < n_entries ? seg_counts[i] : 0;
+    int tot;
+    const int ex = block_exclusive_scan(v, tmp, &tot);
+    if (i < n_entries) {
+      seg_counts[i] = running + ex;
+      if (i % nseg == 0) row_offsets[i / nseg] = running + ex;
+    }
+    running += tot;
+  }
+  if (threadIdx.x == 0) {
+    row_offsets[n_heads] = running;
+    seg_counts[n_entries] = running;
+  }
+}
+
+template <bool kFromBits>
+__global__ void __launch_bounds__(PK_SEG) pack_fill_kernel(const void* __restrict__ src, int T, int H, int nseg,
+                                                           const int32_t* __restrict__ seg_offsets,
+                                                           int32_t* __restrict__ token_idx, int64_t capacity) {
+  __shared__ int wcnt[PK_SEG / 32][64];
+  const int seg = blockIdx.x, b = blockIdx.y;
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int t = seg * PK_SEG + threadIdx.x;
+  const uint64_t bits = t < T ? load_bits<kFromBits>(src, H, b, T, t) : 0ull;
+  for (int h = 0; h < H; ++h) {
+    const unsigned bal = __ballot_sync(0xffffffffu, (bits >> h) & 1ull);
+    if (lane == 0) wcnt[w][h] = __popc(bal);
+  }
+  __syncthreads();
+  for (int h = 0; h < H; ++h) {
+    const unsigned bal = __ballot_sync(0xffffffffu, (bits >> h) & 1ull);
+    if ((bits >> h) & 1ull) {
+      int before = 0;
+      for (int ww = 0; ww < w; ++ww) before += wcnt[ww][h];
+      const int64_t pos = (int64_t)seg_offsets[((int64_t)b * H + h) * nseg + seg] + before +
+                          __popc(bal & ((1u << lane) - 1u));
+      if (pos < capacity) token_idx[pos] = t;
+    }
+  }
+}
+
+}  // namespace aspa
+
+using namespace aspa;
+
+extern "C" int aspa_token_select(const float* importance, int B, int T, int need, float threshold, int guard,
+                                 uint8_t* token_mask, int32_t* kept, void* stream) {
+  ASPA_CHECK_ARG(importance && token_mask && kept, "null pointer");
+  ASPA_CHECK_ARG(B > 0 && T > 0, "bad sizes");
+  token_select_kernel<<<B, 1024, 0, (cudaStream_t)stream>>>(importance, T, need, threshold, guard, token_mask, kept);
+  ASPA_CHECK_LAUNCH();
+  return ASPA_OK;
+}
+
+extern "C" int aspa_head_budget(const float* gate_probs, int64_t n, int G, const int32_t* gate_to_head, int H,
+                                double top_p, int dense_k, int h_active_min, int linear_head_k, double alpha,
+                                float* scratch, int32_t* k_out, void* stream) {
+  ASPA_CHECK_ARG(gate_probs && gate_to_head && scratch && k_out, "null pointer");
+  ASPA_CHECK_ARG(n > 0 && G > 0 && G <= 128 && H > 0 && H <= 64, "bad sizes (G <= 128, H <= 64)");
+  const int64_t nblk = ceil_div(n, 1024);
+  head_colsum_kernel<<<(unsigned)nblk, 256, 0, (cudaStream_t)stream>>>(gate_probs, n, G, gate_to_head, H, scratch);
+  ASPA_CHECK_LAUNCH();
+  head_budget_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(scratch, nblk, H, (double)n, top_p, dense_k, h_active_min,
+                                                          linear_head_k, alpha, k_out);
+  ASPA_CHECK_LAUNCH();
+  return ASPA_OK;
+}
+
+extern "C" int aspa_head_select(const float* gate_probs, int64_t n, int G, const int32_t* gate_to_head, int H,
+                                int k_host, const int32_t* k_dev, int kmax, const uint8_t* token_mask,
+                                uint64_t* head_bits, int32_t* top_idx, float* top_score, float* stat_partials,
+                                void* stream) {
+  ASPA_CHECK_ARG(gate_probs && gate_to_head && head_bits, "null pointer");
+  ASPA_CHECK_ARG(n > 0 && G > 0 && G <= 128 && H > 0 && H <= 64 && kmax > 0 && kmax <= H, "bad sizes");
+  head_select_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, (cudaStream_t)stream>>>(
+      gate_probs, n, G, gate_to_head, H, k_host, k_dev, kmax, token_mask, head_bits, top_idx, top_score,
+      stat_partials);
+  ASPA_CHECK_LAUNCH();
+  return ASPA_OK;
+}
+
+extern "C" int64_t aspa_pack_rows_scratch(int B, int H, int T) {
+  return (int64_t)B * H * ceil_div(T, PK_SEG) + 1;
+}
+
+template <bool kFromBits>
+static int pack_impl(const void* src, int B, int T, int H, int32_t* seg_scratch, int32_t* row_offsets,
+                     int32_t* token_idx, int64_t capacity, cudaStream_t st) {
+  const int nseg = (int)ceil_div(T, PK_SEG);
+  const dim3 grid(nseg, B);
+  pack_count_kernel<kFromBits><<<grid, PK_SEG, 0, st>>>(src, T, H, nseg, seg_scratch);
+  pack_scan_kernel<<<1, 1024, 0, st>>>(seg_scratch, (int64_t)B * H * nseg, nseg, row_offsets, B * H);
+  pack_fill_kernel<kFromBits><<<grid, PK_SEG, 0, st>>>(src, T, H, nseg, seg_scratch, token_idx, capacity);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error("pack_rows: launch failed: %s", cudaGetErrorString(e));
+    return ASPA_ERR_CUDA;
+  }
+  return ASPA_OK;
+}
+
+extern "C" int aspa_pack_rows(const uint64_t* head_bits, int B, int T, int H, int32_t* seg_scratch,
+                              int32_t* row_offsets, int32_t* token_idx, int64_t capacity, void* stream) {
+  ASPA_CHECK_ARG(head_bits && seg_scratch && row_offsets && token_idx, "null pointer");
+  ASPA_CHECK_ARG(B > 0 && T > 0 && H > 0 && H <= 64, "bad sizes (H <= 64)");
+  return pack_impl<true>(head_bits, B, T, H, seg_scratch, row_offsets, token_idx, capacity, (cudaStream_t)stream);
+}
+
+extern "C" int aspa_pack_mask(const uint8_t* mask, int heads, int T, int32_t* seg_scratch, int32_t* row_offsets,
+                              int32_t* token_idx, int64_t capacity, void* stream) {
+  ASPA_CHECK_ARG(mask && seg_scratch && row_offsets && token_idx, "null pointer");
+  ASPA_CHECK_ARG(heads > 0 && T > 0, "bad sizes");
+  // heads may exceed 64: treat every group of <= 64 heads as one "batch" of the bit-mask packer.
+  // Groups must be equal-sized for the (b*H + h) indexing, so use the largest divisor of heads <= 64.
+  int hp = 1;
+  for (int d = 1; d <= 64 && d <= heads; ++d)
+    if (heads % d == 0) hp = d;
+  return pack_impl<false>(mask, heads / hp, T, hp, seg_scratch, row_offsets, token_idx, capacity,
+                          (cudaStream_t)stream);
+}

@@ -1,0 +1,88 @@
+"""Chunk sharding for the chunked shortlist pipeline: one process per GPU, chunks split into
+contiguous ranges, fixed-size promotion records and kept rows exchanged with all-gather
+(NCCL over NVLink on GPUs; the same code runs over gloo on CPU tensors in the tests).
+
+The reference has no distributed code; the single-device run with frozen prototypes is the
+definition these functions must reproduce.  Received data always lands in this rank's own memory
+before any kernel reads it: no kernel here touches peer memory."""
+from __future__ import annotations
+
+from typing import Any, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def world_and_rank(group: Any = None) -> Tuple[int, int]:
+    if not (dist.is_available() and dist.is_initialized()):
+        return 1, 0
+    return dist.get_world_size(group), dist.get_rank(group)
+
+
+def partition_chunks(n_chunks: int, world: int, rank: int) -> Tuple[int, int]:
+    """Contiguous chunk range [lo, hi) of ``rank``; the first ``n_chunks % world`` ranks get one extra."""
+    if world <= 0 or not (0 <= rank < world):
+        raise ValueError("bad world/rank")
+    base, extra = divmod(n_chunks, world)
+    lo = rank * base + min(rank, extra)
+    return lo, lo + base + (1 if rank < extra else 0)
+
+
+def max_chunks_per_rank(n_chunks: int, world: int) -> int:
+    return -(-n_chunks // world)
+
+
+def all_gather_records(group: Any, scores: torch.Tensor, idx: torch.Tensor, count: torch.Tensor, n_chunks: int,
+                       world: int):
+    """Local (n_local, budget) records -> (n_chunks, budget) records of every chunk, in chunk order.
+
+    Ranks may own different chunk counts; each pads to the per-rank maximum with empty records
+    (index -1, count 0) so one fixed-size all-gather suffices, then the padding is dropped."""
+    if world == 1:
+        return scores, idx, count
+    rank = dist.get_rank(group)
+    budget = scores.size(1)
+    cap = max_chunks_per_rank(n_chunks, world)
+    lo, hi = partition_chunks(n_chunks, world, rank)
+    n_local = hi - lo
+
+    def pad(t: torch.Tensor, fill) -> torch.Tensor:
+        out = torch.full((cap,) + tuple(t.shape[1:]), fill, dtype=t.dtype, device=t.device)
+        out[:n_local] = t[:n_local]
+        return out
+
+    sends = [pad(scores, 0.0), pad(idx, -1), pad(count, 0)]
+    outs = []
+    for s in sends:
+        # concatenated (not stacked) layout: the form every backend accepts
+        recv = torch.empty((world * s.shape[0],) + tuple(s.shape[1:]), dtype=s.dtype, device=s.device)
+        dist.all_gather_into_tensor(recv, s.contiguous(), group=group)
+        outs.append(recv)
+    keep = []
+    for r in range(world):
+        rlo, rhi = partition_chunks(n_chunks, world, r)
+        keep.extend(r * cap + j for j in range(rhi - rlo))
+    sel = torch.tensor(keep, dtype=torch.long, device=scores.device)
+    return (outs[0].view(world * cap, budget)[sel].contiguous(), outs[1].view(world * cap, budget)[sel].contiguous(),
+            outs[2].view(world * cap)[sel].contiguous())
+
+
+def all_gather_rows(group: Any, rows: torch.Tensor, total: int, world: int) -> torch.Tensor:
+    """Concatenate per-rank row blocks (rank order) into the (total, C) reduced sequence.
+
+    Kept indices ascend and every rank owns a contiguous index range, so rank order is index order."""
+    if world == 1:
+        return rows
+    n = torch.tensor([rows.size(0)], dtype=torch.int64, device=rows.device)
+    counts = torch.empty(world, dtype=torch.int64, device=rows.device)
+    dist.all_gather_into_tensor(counts, n, group=group)
+    counts_h = counts.tolist()
+    cap = max(counts_h)
+    send = rows.new_zeros((cap, rows.size(1)))
+    send[: rows.size(0)] = rows
+    recv = rows.new_empty((world * cap, rows.size(1)))
+    dist.all_gather_into_tensor(recv, send, group=group)
+    out = torch.cat([recv[r * cap: r * cap + counts_h[r]] for r in range(world)], dim=0)
+    if out.size(0) != total:
+        raise RuntimeError(f"ranks contributed {out.size(0)} kept rows, expected {total}")
+    return out

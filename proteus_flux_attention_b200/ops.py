@@ -1,0 +1,255 @@
+"""Thin tensor-level wrappers over the C ABI: allocate outputs with torch, pass raw
+pointers, raise on a non-zero status.  Everything here runs on the current CUDA
+stream and never synchronises."""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Tuple
+
+import torch
+
+from . import _native as N
+
+
+def _empty(shape, dtype, device):
+    return torch.empty(shape, dtype=dtype, device=device)
+
+
+def normalize_rows(p: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    p = p.to(torch.float32).contiguous()
+    out = torch.empty_like(p)
+    N.check(N.lib().aspa_normalize_rows(N.ptr(p), p.size(0), p.size(1), eps, N.ptr(out), N.stream()), "normalize_rows")
+    return out
+
+
+def reduce_partials(partials: torch.Tensor, n_series: int) -> torch.Tensor:
+    n_blocks = partials.numel() // n_series
+    out = _empty((n_series,), torch.float32, partials.device)
+    N.check(N.lib().aspa_reduce_partials(N.ptr(partials), n_series, n_blocks, N.ptr(out), N.stream()), "reduce_partials")
+    return out
+
+
+def router_fwd(x2d: torch.Tensor, w_router: torch.Tensor, proto_hat: Optional[torch.Tensor],
+               conf_eps: Optional[torch.Tensor], usage_bias: Optional[torch.Tensor], *, temp: float,
+               threshold: float, span: float, blend: float, usage_boost: float, want_stats: bool = True):
+    """x2d (n, C) fp32/bf16 -> gate (n, G) fp32, importance (n), sim (n)|None, blend (n)|None, stats (3,)|None."""
+    n, Cdim = x2d.shape
+    G = w_router.size(0)
+    dev = x2d.device
+    gate = _empty((n, G), torch.float32, dev)
+    imp = _empty((n,), torch.float32, dev)
+    has_proto = proto_hat is not None
+    sim = _empty((n,), torch.float32, dev) if has_proto else None
+    bs = _empty((n,), torch.float32, dev) if has_proto else None
+    ntile = (n + 63) // 64
+    partials = _empty((3 * ntile,), torch.float32, dev) if (want_stats and has_proto) else None
+    N.check(N.lib().aspa_router_fwd(
+        N.ptr(x2d), N.dtype_code(x2d.dtype), n, Cdim, N.ptr(w_router), G, N.ptr(proto_hat), N.ptr(conf_eps),
+        N.ptr(usage_bias), temp, threshold, span, blend, usage_boost, N.ptr(gate), N.ptr(imp), N.ptr(sim), N.ptr(bs),
+        N.ptr(partials), N.stream()), "router_fwd")
+    stats = reduce_partials(partials, 3) if partials is not None else None
+    return gate, imp, sim, bs, stats
+
+
+def token_select(importance: torch.Tensor, need: int, threshold: float, guard: int):
+    B, T = importance.shape
+    mask = _empty((B, T), torch.uint8, importance.device)
+    kept = _empty((B,), torch.int32, importance.device)
+    N.check(N.lib().aspa_token_select(N.ptr(importance), B, T, int(need), float(threshold), int(guard), N.ptr(mask),
+                                      N.ptr(kept), N.stream()), "token_select")
+    return mask, kept
+
+
+def head_budget(gate: torch.Tensor, g2h: torch.Tensor, H: int, *, top_p: float, dense_k: int, h_min: int,
+                linear_head_k: int, alpha: float) -> torch.Tensor:
+    n, G = gate.shape
+    scratch = _empty((H * ((n + 1023) // 1024),), torch.float32, gate.device)
+    k_out = _empty((2,), torch.int32, gate.device)
+    N.check(N.lib().aspa_head_budget(N.ptr(gate), n, G, N.ptr(g2h), H, float(top_p), int(dense_k), int(h_min),
+                                     int(linear_head_k), float(alpha), N.ptr(scratch), N.ptr(k_out), N.stream()),
+            "head_budget")
+    return k_out
+
+
+def head_select(gate: torch.Tensor, g2h: torch.Tensor, H: int, *, k_host: int, k_dev: Optional[torch.Tensor],
+                kmax: int, token_mask: Optional[torch.Tensor], want_stats: bool = True):
+    n, G = gate.shape
+    dev = gate.device
+    bits = _empty((n,), torch.int64, dev)  # uint64 bit masks stored in an int64 tensor
+    top_idx = _empty((n, kmax), torch.int32, dev)
+    top_score = _empty((n, kmax), torch.float32, dev)
+    nblk = (n + 255) // 256
+    partials = _empty((2 * nblk,), torch.float32, dev) if want_stats else None
+    N.check(N.lib().aspa_head_select(N.ptr(gate), n, G, N.ptr(g2h), H, int(k_host), N.ptr(k_dev), int(kmax),
+                                     N.ptr(token_mask), N.ptr(bits), N.ptr(top_idx), N.ptr(top_score),
+                                     N.ptr(partials), N.stream()), "head_select")
+    stats = reduce_partials(partials, 2) if partials is not None else None
+    return bits, top_idx, top_score, stats
+
+
+def pack_rows(head_bits: torch.Tensor, B: int, T: int, H: int, capacity: int):
+    dev = head_bits.device
+    scratch = _empty((int(N.lib().aspa_pack_rows_scratch(B, H, T)),), torch.int32, dev)
+    offs = _empty((B * H + 1,), torch.int32, dev)
+    tok = _empty((max(1, capacity),), torch.int32, dev)
+    N.check(N.lib().aspa_pack_rows(N.ptr(head_bits), B, T, H, N.ptr(scratch), N.ptr(offs), N.ptr(tok), capacity,
+                                   N.stream()), "pack_rows")
+    return offs, tok
+
+
+def pack_mask(mask_u8: torch.Tensor):
+    heads, T = mask_u8.shape
+    dev = mask_u8.device
+    scratch = _empty((heads * ((T + 255) // 256) + 1,), torch.int32, dev)
+    offs = _empty((heads + 1,), torch.int32, dev)
+    tok = _empty((heads * T,), torch.int32, dev)
+    N.check(N.lib().aspa_pack_mask(N.ptr(mask_u8), heads, T, N.ptr(scratch), N.ptr(offs), N.ptr(tok), heads * T,
+                                   N.stream()), "pack_mask")
+    return offs, tok
+
+
+def rope_table(inv_freq: torch.Tensor, T: int, D: int, dtype: torch.dtype):
+    dev = inv_freq.device
+    cos = _empty((T, D // 2), torch.float32, dev)
+    sin = _empty((T, D // 2), torch.float32, dev)
+    N.check(N.lib().aspa_rope_table(N.ptr(inv_freq), T, D, N.dtype_code(dtype), N.ptr(cos), N.ptr(sin), N.stream()),
+            "rope_table")
+    return cos, sin
+
+
+def rope_relayout(qkv: torch.Tensor, H: int, D: int, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
+                  want_amax: bool = False):
+    B, T, _ = qkv.shape
+    dev = qkv.device
+    q = _empty((B * H, T, D), qkv.dtype, dev)
+    k = torch.empty_like(q)
+    v = torch.empty_like(q)
+    amax = torch.zeros((3, B * H), dtype=torch.float32, device=dev) if want_amax else None
+    N.check(N.lib().aspa_rope_relayout(N.ptr(qkv), N.dtype_code(qkv.dtype), B, T, H, D, N.ptr(cos), N.ptr(sin),
+                                       N.ptr(q), N.ptr(k), N.ptr(v), N.ptr(amax), N.stream()), "rope_relayout")
+    return q, k, v, amax
+
+
+def head_amax(x: torch.Tensor) -> torch.Tensor:
+    heads = x.size(0)
+    amax = _empty((heads,), torch.float32, x.device)
+    N.check(N.lib().aspa_head_amax(N.ptr(x), N.dtype_code(x.dtype), heads, x.numel() // heads, N.ptr(amax),
+                                   N.stream()), "head_amax")
+    return amax
+
+
+def quantize_int8(x: torch.Tensor, amax: torch.Tensor):
+    heads = x.size(0)
+    out = _empty(x.shape, torch.int8, x.device)
+    scales = _empty((heads,), torch.float32, x.device)
+    N.check(N.lib().aspa_quantize_int8(N.ptr(x), N.dtype_code(x.dtype), heads, x.numel() // heads, N.ptr(amax),
+                                       N.ptr(out), N.ptr(scales), N.stream()), "quantize_int8")
+    return out, scales
+
+
+PROTO_BLOCK = 128
+
+
+def proto_plan(scores: torch.Tensor, cap: int):
+    """scores (B, T) fp32 -> lists (B, nblk, cap+128) int32, limits (B, T) int32."""
+    B, T = scores.shape
+    dev = scores.device
+    nblk = (T + PROTO_BLOCK - 1) // PROTO_BLOCK
+    lists = _empty((B, nblk, cap + PROTO_BLOCK), torch.int32, dev)
+    limits = _empty((B, T), torch.int32, dev)
+    scratch = _empty((max(16, int(N.lib().aspa_proto_plan_scratch(B, T, cap))),), torch.uint8, dev)
+    N.check(N.lib().aspa_proto_plan(N.ptr(scores), B, T, int(cap), N.ptr(scratch), N.ptr(lists), N.ptr(limits),
+                                    N.stream()), "proto_plan")
+    return lists, limits
+
+
+def make_plan(window: int, anchor_slots: int, anchor_stride: int, proto_cap: int = 0,
+              lists: Optional[torch.Tensor] = None, limits: Optional[torch.Tensor] = None) -> N.ShortlistPlan:
+    p = N.ShortlistPlan()
+    p.window, p.anchor_slots, p.anchor_stride = int(window), int(anchor_slots), int(anchor_stride)
+    p.proto_cap = int(proto_cap) if lists is not None else 0
+    p.proto_block = PROTO_BLOCK
+    p.proto_list_stride = int(proto_cap) + PROTO_BLOCK
+    p.proto_lists = lists.data_ptr() if lists is not None else None
+    p.proto_limit = limits.data_ptr() if limits is not None else None
+    return p
+
+
+def build_candidates(rows: torch.Tensor, row_batch: Optional[torch.Tensor], seq_len: int, L: int, *,
+                     linear_window: int, anchor_stride: int, use_local: bool, use_anchors: bool,
+                     proto_scores: Optional[torch.Tensor], local_cap: Optional[int], anchor_cap: Optional[int],
+                     proto_cap: Optional[int]):
+    n = rows.numel()
+    dev = rows.device
+    cand = _empty((n, L), torch.int64, dev)
+    lens = _empty((n,), torch.int64, dev)
+
+    def cap(v):
+        return -1 if v is None else max(0, int(v))
+
+    N.check(N.lib().aspa_build_candidates(
+        N.ptr(rows), N.ptr(row_batch), n, int(seq_len), int(L), int(linear_window), int(anchor_stride),
+        int(bool(use_local)), int(bool(use_anchors)), N.ptr(proto_scores), cap(local_cap), cap(anchor_cap),
+        cap(proto_cap), N.ptr(cand), N.ptr(lens), N.stream()), "build_candidates")
+    return cand, lens
+
+
+def gather_attn(q, k, v, *, scales: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]], H: int,
+                row_offsets: torch.Tensor, token_idx: torch.Tensor, max_rows: int, total_rows: int,
+                cand: Optional[torch.Tensor] = None, cand_len: Optional[torch.Tensor] = None,
+                plan: Optional[N.ShortlistPlan] = None, add_mask: Optional[torch.Tensor] = None,
+                out: torch.Tensor, out_layout: int):
+    """Launch the attention kernels; `out` must be zero-filled by the caller."""
+    heads, T, D = q.shape
+    ws = None
+    nbytes = int(N.lib().aspa_attn_workspace_bytes(int(total_rows), D))
+    if plan is not None and cand is None and nbytes > 0:
+        ws = _empty((nbytes,), torch.uint8, q.device)
+    qs, ks, vs = scales if scales is not None else (None, None, None)
+    L = cand.size(1) if cand is not None else 0
+    N.check(N.lib().aspa_gather_attn_fwd(
+        N.ptr(q), N.ptr(k), N.ptr(v), N.dtype_code(q.dtype), N.ptr(qs), N.ptr(ks), N.ptr(vs), heads, T, D, int(H),
+        N.ptr(row_offsets), N.ptr(token_idx), int(max_rows), int(total_rows), N.ptr(cand), N.ptr(cand_len), int(L),
+        C.byref(plan) if plan is not None else None, N.ptr(add_mask), N.ptr(out), N.dtype_code(out.dtype),
+        int(out_layout), N.ptr(ws), N.stream()), "gather_attn_fwd")
+    return out
+
+
+def proto_ema_update(x2d: torch.Tensor, gate: torch.Tensor, decay: float, protos: torch.Tensor,
+                     usage: torch.Tensor, conf: torch.Tensor) -> torch.Tensor:
+    n, Cdim = x2d.shape
+    G = gate.size(1)
+    nbytes = int(N.lib().aspa_proto_ema_scratch(n, Cdim, G))
+    scratch = _empty((nbytes,), torch.uint8, x2d.device)
+    updated = _empty((1,), torch.int32, x2d.device)
+    N.check(N.lib().aspa_proto_ema_update(N.ptr(x2d), N.dtype_code(x2d.dtype), n, Cdim, N.ptr(gate), G, float(decay),
+                                          N.ptr(protos), N.ptr(usage), N.ptr(conf), N.ptr(scratch), N.ptr(updated),
+                                          N.stream()), "proto_ema_update")
+    return updated
+
+
+def chunk_select(importance: torch.Tensor, token_mask: Optional[torch.Tensor], budget: int, top_p: float, offset: int,
+                 out_scores: torch.Tensor, out_idx: torch.Tensor, out_count: torch.Tensor) -> None:
+    T = importance.numel()
+    N.check(N.lib().aspa_chunk_select(N.ptr(importance), N.ptr(token_mask), T, int(budget), float(top_p), int(offset),
+                                      N.ptr(out_scores), N.ptr(out_idx), N.ptr(out_count), N.stream()), "chunk_select")
+
+
+def merge_finalise(scores: torch.Tensor, indices: torch.Tensor, seq_len: int, max_tokens: int):
+    dev = scores.device
+    table = _empty((seq_len,), torch.int32, dev)
+    keep_idx = _empty((max_tokens,), torch.int64, dev)
+    keep_sc = _empty((max_tokens,), torch.float32, dev)
+    count = _empty((1,), torch.int32, dev)
+    N.check(N.lib().aspa_merge_finalise(N.ptr(scores), N.ptr(indices), scores.numel(), int(seq_len), int(max_tokens),
+                                        N.ptr(table), N.ptr(keep_idx), N.ptr(keep_sc), N.ptr(count), N.stream()),
+            "merge_finalise")
+    return keep_idx, keep_sc, count
+
+
+def gather_rows(src2d: torch.Tensor, idx: torch.Tensor, count_dev: Optional[torch.Tensor], max_rows: int) -> torch.Tensor:
+    row_bytes = src2d.size(1) * src2d.element_size()
+    dst = _empty((max_rows, src2d.size(1)), src2d.dtype, src2d.device)
+    N.check(N.lib().aspa_gather_rows(N.ptr(src2d), N.ptr(idx), N.ptr(count_dev), int(max_rows), int(row_bytes),
+                                     N.ptr(dst), N.stream()), "gather_rows")
+    return dst

@@ -1,0 +1,431 @@
+"""Kernel-level parity tests: every C-ABI entry point against the CPU oracle on seeded inputs.
+All of them need a CUDA device."""
+import math
+
+import pytest
+import torch
+
+from oracle import aspa_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    return torch.device("cuda:0")
+
+
+def _cfg(**kw):
+    base = dict(d_model=64, n_head=4, attn_h_total=4, attn_gates=8, attn_proto_enable=True)
+    base.update(kw)
+    return O.derive_config(**base)
+
+
+# ---------------------------------------------------------------------------------------------- router
+@pytest.mark.parametrize("dtype,G,C,n", [(torch.float32, 8, 64, 200), (torch.float32, 32, 96, 333),
+                                         (torch.bfloat16, 16, 128, 1000), (torch.bfloat16, 32, 1024, 4096)])
+def test_router_matches_oracle(dev, dtype, G, C, n):
+    from proteus_flux_attention_b200 import ops
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(1, n, C, generator=g)
+    x[0, ::37] *= 4.0
+    x = x.to(dtype)
+    w = (torch.randn(G, C, generator=g) * 0.1).to(dtype)
+    protos = torch.randn(G, C, generator=g)
+    protos[:4] += x[0, :4].float() * 2.0  # make some prototype similarities exceed the blend threshold
+    conf = torch.rand(G, generator=g)
+    usage = torch.rand(G, generator=g)
+    s = _cfg(d_model=C, attn_gates=G, attn_h_total=4, attn_proto_threshold=0.05, attn_proto_usage_boost=0.1)
+    gate_o, sim_o, bs_o = O.route_tokens(s, x, w, protos, conf, usage)
+    imp_o = O.token_importance(gate_o, sim_o, bs_o)
+    ub = torch.softmax(-(usage + 1e-6), dim=0)
+    gate, imp, sim, bs, stats = ops.router_fwd(
+        x[0].to(dev), w.to(dev), ops.normalize_rows(protos.to(dev)), (conf + 1e-6).to(dev), ub.to(dev),
+        temp=s.proto_temp, threshold=s.proto_threshold, span=max(1e-6, 1.0 - s.proto_threshold), blend=s.proto_blend,
+        usage_boost=s.proto_usage_boost)
+    assert torch.allclose(sim.cpu(), sim_o[0], atol=2e-6)
+    assert torch.allclose(bs.cpu(), bs_o[0], atol=1e-5)
+    d_gate = (gate.cpu() - gate_o[0]).abs()
+    d_imp = (imp.cpu() - imp_o[0]).abs()
+    if dtype == torch.float32:
+        assert d_gate.max() < 2e-6 and d_imp.max() < 2e-6
+    else:
+        # bf16 activations: the reference rounds logits and probabilities to bf16, so an fp32 accumulation-order
+        # difference can flip a rounding; such flips are one bf16 ulp and must be rare
+        assert d_gate.max() < 1.0 / 64
+        assert (d_gate > 1e-5).float().mean() < 2e-3
+        assert (d_imp > 1e-5).float().mean() < 5e-3
+    assert abs(float(stats[0]) - float(sim_o.sum())) < 1e-2 * max(1.0, abs(float(sim_o.sum())))
+    assert int(round(float(stats[2]))) == int((bs.cpu() > 0).sum())
+
+
+def test_router_without_prototypes(dev):
+    from proteus_flux_attention_b200 import ops
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(1, 130, 64, generator=g)
+    w = torch.randn(8, 64, generator=g) * 0.2
+    s = _cfg(attn_proto_enable=False)
+    gate_o, _, _ = O.route_tokens(s, x, w, None, None, None)
+    gate, imp, sim, bs, stats = ops.router_fwd(x[0].to(dev), w.to(dev), None, None, None, temp=0.2, threshold=0.25,
+                                               span=0.75, blend=0.6, usage_boost=0.0)
+    assert sim is None and bs is None and stats is None
+    assert torch.allclose(gate.cpu(), gate_o[0], atol=2e-6)
+    assert torch.allclose(imp.cpu(), gate_o[0].amax(-1), atol=2e-6)
+
+
+# ---------------------------------------------------------------------------------------------- selection
+@pytest.mark.parametrize("T,ratio,thr,guard,kmin", [(257, 0.25, 0.0, 1, 0), (4096, 0.05, 0.0, 4, 102),
+                                                    (1000, 0.5, 0.7, 2, 0), (64, 0.999, 0.0, 1, 0), (1, 0.3, 0.0, 1, 0),
+                                                    (70000, 0.2, 0.0, 4, 0)])
+def test_token_select_exact(dev, T, ratio, thr, guard, kmin):
+    from proteus_flux_attention_b200 import ops
+    from proteus_flux_attention_b200.aspa import _py_round_f32
+    g = torch.Generator().manual_seed(T)
+    imp = torch.rand(3, T, generator=g)
+    imp[1] = (imp[1] * 8).round() / 8  # heavy ties: lowest index must win
+    imp[2, : T // 2] = 0.5
+    s = _cfg(attn_token_sparse=True, attn_token_keep_ratio=0.5, attn_token_keep_guard=guard, attn_token_keep_min=kmin,
+             attn_token_keep_threshold=thr)
+    want = O.select_active_tokens(s, imp, ratio)
+    g_ = min(max(0, s.token_keep_guard), T)
+    min_keep = max(min(max(0, s.token_keep_min), T), g_)
+    need = max(1, min(max(_py_round_f32(ratio * T), min_keep) if min_keep > 0 else _py_round_f32(ratio * T), T))
+    if ratio >= 0.999 and thr <= 0:
+        pytest.skip("the all-ones case is decided on the host")
+    mask, kept = ops.token_select(imp.to(dev), need, thr, g_)
+    assert torch.equal(mask.cpu().bool(), want)
+    assert kept.cpu().tolist() == want.sum(dim=1).tolist()
+
+
+@pytest.mark.parametrize("G,H,k", [(8, 4, 2), (16, 16, 4), (32, 16, 2), (12, 12, 12), (64, 64, 3)])
+def test_head_select_and_pack_exact(dev, G, H, k):
+    from proteus_flux_attention_b200 import ops
+    B, T = 2, 300
+    g = torch.Generator().manual_seed(G * 100 + H)
+    gate = torch.softmax(torch.randn(B, T, G, generator=g), dim=-1)
+    gate[0, :50] = 1.0 / G  # exact ties across every head
+    tmask = torch.rand(B, T, generator=g) > 0.4
+    g2h = O.gate_to_head(G, H)
+    hp = gate @ torch.nn.functional.one_hot(g2h, H).float()
+    _, hidx = O.head_topk(hp, k)
+    hm = torch.zeros(B, T, H, dtype=torch.bool).scatter_(2, hidx, True) & tmask.unsqueeze(-1)
+    flat = hm.permute(0, 2, 1).reshape(B * H, T)
+    packed = O.pack_active_rows(flat)
+    bits, top_idx, top_score, stats = ops.head_select(gate.view(-1, G).to(dev), g2h.to(torch.int32).to(dev), H, k_host=k,
+                                                      k_dev=None, kmax=k, token_mask=tmask.view(-1).to(torch.uint8).to(dev))
+    # ties between heads summed from several gates can differ in the last bit from the CPU matmul; compare sets
+    got = torch.zeros(B * T, H, dtype=torch.bool)
+    b = bits.cpu()
+    for h in range(H):
+        got[:, h] = ((b >> h) & 1).bool()
+    same = (got.view(B, T, H) == hm).all(-1)
+    assert same.float().mean() > 0.999
+    if G == H:
+        assert bool(same.all())
+        assert torch.equal(top_idx.cpu().view(B, T, k).long(), hidx)
+    offs, tok = ops.pack_rows(bits, B, T, H, B * T * k)
+    if bool(same.all()):
+        assert torch.equal(offs.cpu(), packed[2])
+        assert torch.equal(tok.cpu()[: packed[1].numel()].long(), packed[1])
+    ent = -(gate.clamp_min(1e-9).log() * gate).sum(-1).sum()
+    assert abs(float(stats[1]) - float(ent)) < 1e-3 * float(ent)
+
+
+def test_head_budget_matches_oracle(dev):
+    from proteus_flux_attention_b200 import ops
+    g = torch.Generator().manual_seed(5)
+    for G, H, top_p, dense_k, hmin, lin_k, alpha in [(8, 4, 0.7, 4, 1, 2, 0.3), (16, 16, 0.9, 12, 2, 2, 0.5),
+                                                     (24, 12, 0.5, 8, 2, 2, 0.0), (16, 8, 0.95, 8, 2, 3, 1.0)]:
+        gate = torch.softmax(torch.randn(3, 777, G, generator=g) * 2, dim=-1)
+        g2h = O.gate_to_head(G, H)
+        hp = gate @ torch.nn.functional.one_hot(g2h, H).float()
+        nucleus = O.nucleus_head_count(hp, top_p, dense_k)
+        adaptive = max(hmin, min(dense_k, nucleus))
+        lin = max(1, min(adaptive, lin_k))
+        topk = min(adaptive, max(1, int(round((1.0 - alpha) * adaptive + alpha * lin))))
+        k = ops.head_budget(gate.view(-1, G).to(dev), g2h.to(torch.int32).to(dev), H, top_p=top_p, dense_k=dense_k,
+                            h_min=hmin, linear_head_k=lin_k, alpha=alpha).cpu().tolist()
+        assert k == [topk, adaptive]
+
+
+def test_pack_mask_matches_oracle(dev):
+    from proteus_flux_attention_b200.sparse_attn import _pack_active_rows
+    g = torch.Generator().manual_seed(9)
+    for heads, T in [(5, 37), (67, 300), (128, 513)]:
+        m = torch.rand(heads, T, generator=g) > 0.6
+        m[0] = False
+        want = O.pack_active_rows(m)
+        got = _pack_active_rows(m.to(dev))
+        assert torch.equal(got[0].cpu(), want[0]) and torch.equal(got[1].cpu(), want[1])
+        assert torch.equal(got[2].cpu(), want[2]) and got[3] == want[3]
+    assert _pack_active_rows(torch.zeros(3, 8, dtype=torch.bool, device=dev)) is None
+
+
+# ---------------------------------------------------------------------------------------------- rope / quant
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rope_relayout_matches_oracle(dev, dtype):
+    from proteus_flux_attention_b200 import ops
+    B, T, H, D = 2, 700, 4, 64
+    s = _cfg(d_model=H * D, attn_h_total=H)
+    g = torch.Generator().manual_seed(3)
+    qkv = torch.randn(B, T, 3 * H * D, generator=g).to(dtype)
+    q, k, v = (t.view(B, T, H, D) for t in qkv.chunk(3, dim=2))
+    qo, ko = O.apply_rope(s, q, k)
+    inv = 1.0 / (s.rope_base ** (torch.arange(0, D, 2, dtype=torch.float32) / D))
+    cos, sin = ops.rope_table(inv.to(dev), T, D, dtype)
+    qg, kg, vg, amax = ops.rope_relayout(qkv.to(dev), H, D, cos, sin, want_amax=True)
+    tol = dict(atol=0, rtol=0) if dtype == torch.bfloat16 else dict(atol=1e-6, rtol=1e-6)
+    want_q = qo.permute(0, 2, 1, 3).reshape(B * H, T, D)
+    want_k = ko.permute(0, 2, 1, 3).reshape(B * H, T, D)
+    want_v = v.permute(0, 2, 1, 3).reshape(B * H, T, D)
+    if dtype == torch.bfloat16:
+        # cosf/sinf on the device and the host may differ in the last fp32 bit before the bf16 rounding
+        assert (qg.cpu() != want_q).float().mean() < 1e-3 and (kg.cpu() != want_k).float().mean() < 1e-3
+        assert torch.allclose(qg.cpu().float(), want_q.float(), atol=2e-2, rtol=1e-2)
+    else:
+        assert torch.allclose(qg.cpu(), want_q, **tol) and torch.allclose(kg.cpu(), want_k, **tol)
+    assert torch.equal(vg.cpu(), want_v)
+    assert torch.equal(amax.cpu()[0], qg.float().abs().amax(dim=(1, 2)).cpu())
+    assert torch.equal(amax.cpu()[2], want_v.float().abs().amax(dim=(1, 2)))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_quantize_int8_exact(dev, dtype):
+    from proteus_flux_attention_b200 import ops
+    g = torch.Generator().manual_seed(4)
+    x = (torch.randn(6, 50, 16, generator=g) * 3).to(dtype)
+    x[5] = 0
+    qo, so = O.quantize_per_head_int8(x)
+    xg = x.to(dev)
+    amax = ops.head_amax(xg)
+    qg, sg = ops.quantize_int8(xg, amax)
+    assert torch.equal(sg.cpu(), so)
+    assert torch.equal(qg.cpu(), qo)
+
+
+# ---------------------------------------------------------------------------------------------- candidates
+def test_build_candidates_matches_golden(dev, golden_dir):
+    from proteus_flux_attention_b200 import build_packed_shortlist_candidates
+    for c in torch.load(golden_dir / "candidates.pt", weights_only=False):
+        kw = dict(c["kw"])
+        ps = kw.pop("proto_scores")
+        cand, ln = build_packed_shortlist_candidates(c["rows"].to(dev), c["bids"].to(dev) if c["bids"] is not None else None,
+                                                     c["seq_len"], proto_scores=ps.to(dev) if ps is not None else None, **kw)
+        assert torch.equal(cand.cpu(), c["cand"])
+        assert torch.equal(ln.cpu(), c["len"])
+
+
+def test_build_candidates_empty_and_overflow(dev):
+    from proteus_flux_attention_b200 import build_shortlist_candidates
+    rows = torch.empty(0, dtype=torch.long, device=dev)
+    c, l = build_shortlist_candidates(rows, 16, max_candidates=4, linear_window=4, anchor_stride=2, use_local=True,
+                                      use_anchors=True)
+    assert c.shape == (0, 0) and l.numel() == 0
+    # overflow: the L smallest ids survive, so the row itself is dropped (reference semantics)
+    rows = torch.tensor([40], device=dev)
+    c, l = build_shortlist_candidates(rows, 64, max_candidates=8, linear_window=8, anchor_stride=4, use_local=True,
+                                      use_anchors=True)
+    want, wl = O.build_candidates(torch.tensor([40]), None, 64, max_candidates=8, linear_window=8, anchor_stride=4,
+                                  use_local=True, use_anchors=True)
+    assert torch.equal(c.cpu(), want) and torch.equal(l.cpu(), wl)
+    assert 40 not in c.cpu()[0, : int(l)].tolist()
+
+
+# ---------------------------------------------------------------------------------------------- attention
+def test_attention_matches_golden(dev, golden_dir):
+    from proteus_flux_attention_b200 import aspa_sparse_attention
+    for c in torch.load(golden_dir / "attention.pt", weights_only=False):
+        q, k, v = (c[n].to(dev) for n in "qkv")
+        if c["kind"].startswith("dense"):
+            y = aspa_sparse_attention(q, k, v, active_mask=c["active"].unsqueeze(-1).float().to(dev) if c["active"] is not None else None,
+                                      causal_mask=c["causal"].to(dev) if c["causal"] is not None else None)
+        elif c["kind"] == "shortlist":
+            y = aspa_sparse_attention(q, k, v, active_mask=c["active"].unsqueeze(-1).to(dev),
+                                      shortlist_candidates=c["cand"].to(dev), shortlist_lengths=c["len"].to(dev))
+        else:
+            y = aspa_sparse_attention(c["qi"].to(dev), c["ki"].to(dev), c["vi"].to(dev), active_mask=c["active"].unsqueeze(-1).to(dev),
+                                      prepacked=tuple(t.to(dev) if isinstance(t, torch.Tensor) else t for t in c["packed"]),
+                                      shortlist_candidates=c["cand"].to(dev), shortlist_lengths=c["len"].to(dev),
+                                      q_scale=c["qs"].to(dev), k_scale=c["ks"].to(dev), v_scale=c["vs"].to(dev),
+                                      out_dtype=torch.float32)
+        assert torch.allclose(y.cpu(), c["y"], atol=1e-5, rtol=1e-4), c["kind"]
+
+
+def test_attention_validation_errors(dev):
+    from proteus_flux_attention_b200 import aspa_sparse_attention
+    q = torch.randn(2, 4, 8, device=dev)
+    with pytest.raises(ValueError, match="rank-3"):
+        aspa_sparse_attention(q[0], q[0], q[0])
+    with pytest.raises(ValueError, match="matching shapes"):
+        aspa_sparse_attention(q, q[:, :3], q)
+    with pytest.raises(ValueError, match="dropout_p"):
+        aspa_sparse_attention(q, q, q, dropout_p=1.0)
+    with pytest.raises(ValueError, match="causal_mask must have shape"):
+        aspa_sparse_attention(q, q, q, causal_mask=torch.zeros(3, 3, device=dev))
+    with pytest.raises(ValueError, match="active_mask must have shape"):
+        aspa_sparse_attention(q, q, q, active_mask=torch.ones(2, 5, device=dev))
+    with pytest.raises(ValueError, match="provided together"):
+        aspa_sparse_attention(q, q, q, shortlist_candidates=torch.zeros(8, 2, dtype=torch.long, device=dev))
+    with pytest.raises(ValueError, match="requires q_scale"):
+        aspa_sparse_attention(q.to(torch.int8), q.to(torch.int8), q.to(torch.int8))
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        aspa_sparse_attention(q.cpu(), q.cpu(), q.cpu())
+    z = aspa_sparse_attention(q, q, q, active_mask=torch.zeros(2, 4, device=dev))
+    assert z.shape == q.shape and float(z.abs().sum()) == 0.0
+
+
+def _planned_vs_table(dev, dtype, heads, T, D, L, window, stride, local_cap, anchor_cap, proto_cap, H, seed, quant=False):
+    """The on-the-fly plan must give what the explicit reference table gives."""
+    from proteus_flux_attention_b200 import ops
+    from proteus_flux_attention_b200.sparse_attn import attention_packed
+    g = torch.Generator().manual_seed(seed)
+    q, k, v = (torch.randn(heads, T, D, generator=g).to(dtype) for _ in range(3))
+    active = torch.rand(heads, T, generator=g) > 0.7
+    active[:, 0] = True
+    packed = O.pack_active_rows(active)
+    B = heads // H
+    proto = torch.rand(B, T, generator=g) if proto_cap > 0 else None
+    if proto is not None:
+        proto[:, ::5] = 0.5  # ties in the prototype scores
+    bids = packed[0] // H
+    cand, lens = O.build_candidates(packed[1], bids if proto is not None else None, T, max_candidates=L,
+                                    linear_window=window, anchor_stride=stride, use_local=local_cap > 0,
+                                    use_anchors=anchor_cap > 0, proto_scores=proto, local_cap=local_cap,
+                                    anchor_cap=anchor_cap, proto_cap=proto_cap)
+    scales = None
+    qd, kd, vd = q, k, v
+    if quant:
+        (qd, sq), (kd, sk), (vd, sv) = (O.quantize_per_head_int8(t) for t in (q, k, v))
+        want = O.sparse_attention(qd, kd, vd, packed=packed, candidates=cand, lengths=lens, q_scale=sq, k_scale=sk,
+                                  v_scale=sv, out_dtype=torch.float32)
+        scales = (sq.to(dev), sk.to(dev), sv.to(dev))
+    else:
+        want = O.sparse_attention(q.float(), k.float(), v.float(), packed=packed, candidates=cand, lengths=lens)
+    win = min(window, L, local_cap) if local_cap > 0 else 0
+    slots = min(anchor_cap, L, max(1, T)) if (anchor_cap > 0 and stride > 0) else 0
+    pcap = min(L, proto_cap, T) if proto_cap > 0 else 0
+    assert max(win, 1) + slots + pcap <= L
+    lists = limits = None
+    if pcap > 0:
+        lists, limits = ops.proto_plan(proto.to(dev), pcap)
+    plan = ops.make_plan(win, slots, stride, pcap, lists, limits)
+    out = attention_packed(qd.to(dev), kd.to(dev), vd.to(dev), row_offsets=packed[2].to(dev),
+                           token_idx=packed[1].to(torch.int32).to(dev), max_rows=packed[3],
+                           total_rows=packed[1].numel(), H=H, scales=scales, plan=plan, out_dtype=torch.float32)
+    tol = dict(atol=2e-2, rtol=1e-2) if dtype == torch.bfloat16 or quant else dict(atol=1e-5, rtol=1e-4)
+    got = out.cpu()
+    assert torch.allclose(got, want, **tol), float((got - want).abs().max())
+    if dtype == torch.bfloat16 or quant:  # tensor-core path: mean error must sit far below the tolerance
+        assert float((got - want).abs().mean()) < 2e-3
+    return got
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("case", [
+    dict(T=300, L=48, window=20, stride=7, local_cap=20, anchor_cap=12, proto_cap=0),
+    dict(T=300, L=64, window=24, stride=5, local_cap=24, anchor_cap=16, proto_cap=10),
+    dict(T=513, L=96, window=64, stride=32, local_cap=60, anchor_cap=20, proto_cap=16),
+    dict(T=200, L=40, window=0, stride=3, local_cap=0, anchor_cap=20, proto_cap=12),
+    dict(T=129, L=512, window=512, stride=256, local_cap=362, anchor_cap=150, proto_cap=0),
+    dict(T=64, L=8, window=7, stride=0, local_cap=7, anchor_cap=0, proto_cap=0),
+])
+def test_planned_attention_equals_reference_table(dev, dtype, case):
+    _planned_vs_table(dev, dtype, heads=8, D=64, H=4, seed=11, **case)
+
+
+def test_planned_attention_int8(dev):
+    _planned_vs_table(dev, torch.bfloat16, heads=4, T=400, D=64, L=64, window=30, stride=9, local_cap=30, anchor_cap=20,
+                      proto_cap=10, H=4, seed=13, quant=True)
+
+
+@pytest.mark.parametrize("D", [5, 16, 128])
+def test_planned_attention_other_head_dims(dev, D):
+    _planned_vs_table(dev, torch.float32, heads=4, T=150, D=D, L=32, window=12, stride=6, local_cap=12, anchor_cap=10,
+                      proto_cap=6, H=2, seed=17)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_dense_causal_attention(dev, dtype):
+    from proteus_flux_attention_b200 import aspa_sparse_attention
+    g = torch.Generator().manual_seed(21)
+    q, k, v = (torch.randn(6, 333, 64, generator=g).to(dtype) for _ in range(3))
+    want = torch.nn.functional.scaled_dot_product_attention(q.float()[None], k.float()[None], v.float()[None], is_causal=True)[0]
+    got = aspa_sparse_attention(q.to(dev), k.to(dev), v.to(dev)).cpu().float()
+    tol = dict(atol=2e-2, rtol=1e-2) if dtype == torch.bfloat16 else dict(atol=1e-5, rtol=1e-4)
+    assert torch.allclose(got, want, **tol)
+
+
+def test_attention_is_deterministic(dev):
+    a = _planned_vs_table(dev, torch.bfloat16, heads=8, T=700, D=64, L=96, window=64, stride=16, local_cap=60,
+                          anchor_cap=20, proto_cap=16, H=4, seed=5)
+    b = _planned_vs_table(dev, torch.bfloat16, heads=8, T=700, D=64, L=96, window=64, stride=16, local_cap=60,
+                          anchor_cap=20, proto_cap=16, H=4, seed=5)
+    assert torch.equal(a, b)
+
+
+# ---------------------------------------------------------------------------------------------- EMA / chunk ops
+@pytest.mark.parametrize("dtype,G", [(torch.float32, 8), (torch.bfloat16, 16), (torch.bfloat16, 40)])
+def test_proto_ema_matches_oracle(dev, dtype, G):
+    from proteus_flux_attention_b200 import ops
+    C, n = 96, 1500
+    g = torch.Generator().manual_seed(8)
+    x = torch.randn(1, n, C, generator=g).to(dtype)
+    gate = torch.softmax(torch.randn(1, n, G, generator=g), dim=-1)
+    gate[..., 3] = 0.0  # a gate that never fires stays untouched
+    protos, usage, conf = torch.randn(G, C, generator=g), torch.rand(G, generator=g), torch.rand(G, generator=g)
+    s = _cfg(d_model=C, attn_gates=G, attn_h_total=4)
+    po, uo, co = protos.clone(), usage.clone(), conf.clone()
+    n_upd = O.update_prototypes(s, x, gate, po, uo, co)
+    pg, ug, cg = protos.to(dev), usage.to(dev), conf.to(dev)
+    upd = ops.proto_ema_update(x[0].to(dev), gate[0].to(dev).contiguous(), s.proto_decay, pg, ug, cg)
+    assert int(upd.cpu()) == n_upd
+    assert torch.allclose(pg.cpu(), po, atol=1e-5, rtol=1e-4)
+    assert torch.allclose(ug.cpu(), uo, atol=1e-3, rtol=1e-5)
+    assert torch.allclose(cg.cpu(), co, atol=1e-6)
+    assert torch.equal(pg.cpu()[3], protos[3] * 1.0) or torch.allclose(pg.cpu()[3], protos[3])
+
+
+def test_chunk_select_and_merge_match_golden(dev, golden_dir):
+    from proteus_flux_attention_b200 import ops
+    gd = torch.load(golden_dir / "chunk_select.pt", weights_only=False)
+    for c in gd["select"]:
+        budget = c["budget"]
+        sc = torch.zeros(budget, device=dev)
+        ix = torch.full((budget,), -1, dtype=torch.int64, device=dev)
+        ct = torch.zeros(1, dtype=torch.int32, device=dev)
+        ops.chunk_select(c["scores"].to(dev), c["mask"].to(torch.uint8).to(dev), budget, c["top_p"], 1000, sc, ix, ct)
+        n = int(ct.cpu())
+        assert n == c["idx"].numel()
+        assert torch.equal(ix.cpu()[:n], c["idx"])
+        assert torch.equal(sc.cpu()[:n], c["vals"])
+    for c in gd["finalise"]:
+        ki, ks, kc = ops.merge_finalise(c["scores"].to(dev), c["indices"].to(dev), int(c["indices"].max()) + 5, c["max_tokens"])
+        n = int(kc.cpu())
+        assert n == c["keep_idx"].numel()
+        assert torch.equal(ki.cpu()[:n], c["keep_idx"])
+        assert torch.equal(ks.cpu()[:n], c["keep_sc"])
+
+
+def test_chunk_select_edge_cases(dev):
+    from proteus_flux_attention_b200 import ops
+    T, budget = 5000, 64
+    imp = torch.full((T,), 0.25, device=dev)  # all tied: the lowest indices win
+    sc = torch.zeros(budget, device=dev)
+    ix = torch.full((budget,), -1, dtype=torch.int64, device=dev)
+    ct = torch.zeros(1, dtype=torch.int32, device=dev)
+    ops.chunk_select(imp, None, budget, 0.9, 7, sc, ix, ct)
+    assert int(ct.cpu()) == budget and ix.cpu().tolist() == list(range(7, 7 + budget))
+    ops.chunk_select(imp, torch.zeros(T, dtype=torch.uint8, device=dev), budget, 0.9, 0, sc, ix, ct)
+    assert int(ct.cpu()) == 0  # everything masked: nothing promoted
+    want = O.select_top_tokens(imp.cpu(), None, 0, budget=budget, top_p=0.001)
+    ops.chunk_select(imp, None, budget, 0.001, 0, sc, ix, ct)
+    assert int(ct.cpu()) == want[1].numel() == 1
+
+
+def test_gather_rows(dev):
+    from proteus_flux_attention_b200 import ops
+    src = torch.randn(100, 64, device=dev).to(torch.bfloat16)
+    idx = torch.tensor([3, 99, 0, 50], device=dev)
+    assert torch.equal(ops.gather_rows(src, idx, None, 4), src[idx])
