@@ -1,0 +1,366 @@
+"""Benchmark of the ASPA hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl b200|reference]
+
+Workloads (synthetic, seeded; shapes of the reference's headline configurations):
+  chunked_1m     1,048,576 tokens, d_model 1024, 16 heads, chunk 65,536, 2,048 promoted per chunk, final pass over
+                 the merged 32,768-token shortlist, bf16.  Chunks are sharded over the N ranks (strong scaling).
+  shortlist_256k one INT8 shortlist layer, 262,144 tokens, L = 4096 (local + anchors + prototype picks), bf16.
+  sparse_16k     one sparse layer, batch 4 x 16,384 tokens, top-4 of 16 heads, keep 0.2, RoPE, bf16.
+A step is one pass of the hot path over one batch.  `value` is measured with inputs resident in HBM; `e2e` goes
+through the public API with host buffers (host->device copies of the inputs and device->host reads of the results
+inside the timed region).  One JSON line is printed by rank 0.
+
+`--impl reference` times the CPU oracle (a restatement of the reference's own PyTorch CPU path) on a bounded sample
+of the same workload with all host threads.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+try:
+    METRIC = json.loads((ROOT / "BASELINE.json").read_text())["metric"]
+except Exception:
+    METRIC = "ASPA fwd tokens/sec (256K shortlist, 1M chunked @1/2/4/8 GPU); % HBM/TC roof"
+SEQ_1M, CHUNK, BUDGET, BUFFER, D_MODEL, HEADS = 1 << 20, 65536, 2048, 32768, 1024, 16
+
+
+# ----------------------------------------------------------------------------------------------- helpers
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.rows, self.stop, self.index = [], threading.Event(), index
+        self.thread = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        while not self.stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
+                parts = [p.strip() for p in out.strip().split(",")]
+                if len(parts) >= 7:
+                    self.rows.append(parts)
+            except Exception:
+                pass
+            self.stop.wait(0.2)
+
+    def __enter__(self):
+        self.thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self.stop.set()
+        self.thread.join(timeout=10)
+
+    def summary(self):
+        if not self.rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        mhz = [float(r[0]) for r in self.rows if r[0].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[3 + i].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": float(self.rows[0][1]),
+                "reasons": reasons, "samples": len(self.rows)}
+
+
+def peak_hbm():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def xavier_state(layer, dtype, seed):
+    """Seeded Xavier-uniform weights for the layer's four matrices; identical on every rank."""
+    g = torch.Generator().manual_seed(seed)
+    sd = {k: v.clone() for k, v in layer.state_dict().items()}
+    for k in ("qkv.weight", "proj.weight", "head_router.linear.weight", "routing_prototypes"):
+        w = sd[k].float()
+        bound = (6.0 / (w.size(0) + w.size(1))) ** 0.5
+        w = (torch.rand(w.shape, generator=g) * 2 - 1) * bound
+        sd[k] = w.to(dtype if k != "routing_prototypes" else torch.float32)
+    return sd
+
+
+def chunk_data(c: int, device, dtype):
+    """Chunk c of the synthetic 1M sequence: N(0,1), seeded by the chunk index (independent of the rank count)."""
+    g = torch.Generator(device=device).manual_seed(1000 + c)
+    return torch.randn(CHUNK, D_MODEL, generator=g, device=device, dtype=torch.float32).to(dtype)
+
+
+# ----------------------------------------------------------------------------------------------- workloads
+class ChunkedWorkload:
+    name = "chunked_1m"
+
+    def __init__(self, device, world, rank, group):
+        import proteus_flux_attention_b200 as P
+        from proteus_flux_attention_b200 import distributed as D
+        from proteus_flux_attention_b200.chunked_shortlist import _build_model_config
+        self.P, self.device, self.world, self.rank = P, device, world, rank
+        self.tokens = SEQ_1M
+        cfg = P.ChunkedShortlistConfig(seq_len=SEQ_1M, d_model=D_MODEL, chunk_len=CHUNK, buffer_tokens=BUFFER,
+                                       per_chunk_budget=BUDGET, device=device, heads=HEADS, freeze_prototypes=True,
+                                       warmup=False, collect_summaries=False, pass1_full_forward=True)
+        self.runner = P.ChunkedShortlistRunner(cfg, process_group=group, cache_layers=True)
+        mk = lambda n, r: P.AdaptiveSparseAttention(_build_model_config(n, D_MODEL, heads=HEADS, sparse_ratio=r,  # noqa: E731
+                                                                       shortlist_alpha=1.0, router_top_p=0.9))
+        self.chunk_state = xavier_state(mk(CHUNK, 0.05), torch.bfloat16, 0)
+        self.final_state = xavier_state(mk(BUFFER, 0.5), torch.bfloat16, 1)
+        lo, hi = D.partition_chunks(SEQ_1M // CHUNK, world, rank)
+        self.shard = torch.stack([chunk_data(c, device, torch.bfloat16) for c in range(lo, hi)]).view(1, -1, D_MODEL)
+        self.host_shard = None
+        self.config = {"workload": self.name, "seq_len": SEQ_1M, "d_model": D_MODEL, "heads": HEADS, "chunk_len": CHUNK,
+                       "per_chunk_budget": BUDGET, "buffer_tokens": BUFFER, "pass1": "full layer forward per chunk",
+                       "prototypes": "frozen during pass 1", "sharding": f"chunks over {world} rank(s)",
+                       "l2": "inputs (2 GiB) larger than L2"}
+
+    def step(self):
+        return self.runner.run(self.shard, chunk_state=self.chunk_state, final_state=self.final_state,
+                               sequence_is_local_shard=True)
+
+    def step_e2e(self):
+        if self.host_shard is None:
+            self.host_shard = self.shard.cpu().pin_memory()
+        res = self.runner.run(self.host_shard, chunk_state=self.chunk_state, final_state=self.final_state,
+                              sequence_is_local_shard=True)
+        out = res.final_output.cpu()
+        return self.host_shard.numel() * 2, out.numel() * 2 + res.keep_indices.numel() * 12
+
+
+class LayerWorkload:
+    def __init__(self, name, device):
+        import proteus_flux_attention_b200 as P
+        self.name, self.device = name, device
+        if name == "sparse_16k":
+            self.B, self.T = 4, 16384
+            cfg = dict(d_model=1024, n_head=16, attn_h_total=16, attn_gates=16, attn_h_active=4, attn_h_active_min=4,
+                       attn_h_active_max=4, attn_linear_head_k=4, attn_token_sparse=True, attn_token_keep_ratio=0.2,
+                       attn_mode="auto", attn_small_seq_dense=0, attn_router_top_p=0.0, attn_use_rope=True,
+                       attn_rope_base=10000.0, n_ctx=16384, attn_track_latency=False, attn_proto_enable=True)
+        else:
+            self.B, self.T = 1, 262144
+            cfg = dict(d_model=1024, n_head=16, attn_h_total=16, attn_mode="linear", attn_quantize_int8=True,
+                       attn_linear_L=4096, attn_linear_L_base=4096, attn_linear_L_max=4096, attn_linear_window=4096,
+                       attn_linear_anchor_stride=128, attn_linear_policy="local+anchors+proto", attn_h_active=2,
+                       attn_h_active_min=2, attn_h_active_max=2, attn_token_sparse=True, attn_token_keep_ratio=0.2,
+                       n_ctx=262144, attn_track_latency=False, attn_proto_enable=True)
+        self.tokens = self.B * self.T
+        layer = P.AdaptiveSparseProtoAttention(P.ModelConfig(**cfg))
+        self.state = xavier_state(layer, torch.bfloat16, 0)
+        self.layer = layer.to(torch.bfloat16)
+        self.layer.load_state_dict(self.state)
+        self.layer = self.layer.to(device).eval()
+        g = torch.Generator(device=device).manual_seed(0)
+        x = torch.randn(self.B, self.T, 1024, generator=g, device=device)
+        if name == "shortlist_256k":
+            pos = torch.randperm(self.T, generator=torch.Generator().manual_seed(1))[:64].to(device)
+            x[:, pos] *= 4.0
+        self.x = x.to(torch.bfloat16)
+        self.host_x = None
+        self.config = {"workload": name, "batch": self.B, "seq_len": self.T, "d_model": 1024, "heads": 16,
+                       "l2": "activations (>= 128 MiB per tensor) larger than L2"}
+
+    def _reset(self):
+        # every forward moves the prototype EMA; restore it so each step does identical work
+        for k in ("routing_prototypes", "routing_usage_ema", "routing_confidence"):
+            getattr(self.layer, k).copy_(self.state[k])
+
+    def step(self):
+        self._reset()
+        return self.layer(self.x)
+
+    def step_e2e(self):
+        if self.host_x is None:
+            self.host_x = self.x.cpu().pin_memory()
+        self._reset()
+        y = self.layer(self.host_x.to(self.device, non_blocking=True)).cpu()
+        return self.host_x.numel() * 2, y.numel() * 2
+
+
+# ----------------------------------------------------------------------------------------------- CPU oracle timing
+def cpu_oracle_sample(workload: str):
+    """Time the CPU oracle on a bounded sample of the workload; returns (tokens_per_s, cores, description)."""
+    from oracle import aspa_oracle as O
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+
+    def xav(shape, g):
+        bound = (6.0 / (shape[0] + shape[1])) ** 0.5
+        return (torch.rand(shape, generator=g) * 2 - 1) * bound
+
+    def weights(G, g):
+        return {"qkv.weight": xav((3 * D_MODEL, D_MODEL), g).bfloat16(), "proj.weight": xav((D_MODEL, D_MODEL), g).bfloat16(),
+                "head_router.linear.weight": xav((G, D_MODEL), g).bfloat16(), "routing_prototypes": xav((G, D_MODEL), g)}
+
+    g = torch.Generator().manual_seed(0)
+    if workload == "chunked_1m":
+        n_chunks, chunk = 2, 32768
+        T = n_chunks * chunk
+        seq = torch.randn(1, T, D_MODEL, generator=g).bfloat16()
+        cw, fw = weights(2 * HEADS, g), weights(2 * HEADS, g)
+        t0 = time.perf_counter()
+        O.chunked_run(seq, chunk_len=chunk, buffer_tokens=T // 32, per_chunk_budget=chunk // 32, heads=HEADS,
+                      chunk_weights=cw, final_weights=fw, freeze_prototypes=True)
+        dt = time.perf_counter() - t0
+        return T / dt, cores, (f"same pipeline at 1/16 scale: {n_chunks} chunks of {chunk} tokens, {chunk // 32} promoted per "
+                               f"chunk, final pass over {T // 32} tokens, d_model {D_MODEL}, {HEADS} heads, bf16")
+    if workload == "sparse_16k":
+        cfg = dict(d_model=1024, n_head=16, attn_h_total=16, attn_gates=16, attn_h_active=4, attn_h_active_min=4,
+                   attn_h_active_max=4, attn_linear_head_k=4, attn_token_sparse=True, attn_token_keep_ratio=0.2,
+                   attn_router_top_p=0.0, n_ctx=16384, attn_proto_enable=True, attn_small_seq_dense=0)
+        x = torch.randn(1, 16384, D_MODEL, generator=g).bfloat16()
+        lay = O.OracleLayer(weights(16, g), **cfg)
+        t0 = time.perf_counter()
+        lay.forward(x)
+        dt = time.perf_counter() - t0
+        return 16384 / dt, cores, "one of the four batch rows (1 x 16384 tokens) of the same layer, bf16"
+    cfg = dict(d_model=1024, n_head=16, attn_h_total=16, attn_mode="linear", attn_quantize_int8=True, attn_linear_L=4096,
+               attn_linear_L_base=4096, attn_linear_L_max=4096, attn_linear_window=4096, attn_linear_anchor_stride=128,
+               attn_linear_policy="local+anchors+proto", attn_h_active=2, attn_h_active_min=2, attn_h_active_max=2,
+               attn_token_sparse=True, attn_token_keep_ratio=0.2, n_ctx=262144, attn_proto_enable=True)
+    T = 8192
+    x = torch.randn(1, T, D_MODEL, generator=g).bfloat16()
+    lay = O.OracleLayer(weights(32, g), **cfg)
+    t0 = time.perf_counter()
+    lay.forward(x)
+    dt = time.perf_counter() - t0
+    return T / dt, cores, f"the same INT8 shortlist layer on the first {T} tokens"
+
+
+# ----------------------------------------------------------------------------------------------- main
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="chunked_1m", choices=["chunked_1m", "shortlist_256k", "sparse_16k"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        vals = []
+        for _ in range(max(1, args.warmup // 3)):
+            cpu_oracle_sample(args.workload)
+        for _ in range(args.steps):
+            v, cores, desc = cpu_oracle_sample(args.workload)
+            vals.append(v)
+        v = statistics.mean(vals)
+        print(json.dumps({"impl": "reference", "metric": METRIC, "value": v, "unit": "tokens/s", "n_gpus": args.gpus,
+                          "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "scaling": "strong",
+                          "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": {"workload": args.workload},
+                          "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": desc},
+                          "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        return
+
+    import torch.distributed as dist
+    from proteus_flux_attention_b200 import _native, ops
+    _native.lib()  # no fallback: fail here if the CUDA library is missing
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    group = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+        group = dist.group.WORLD
+    if args.workload == "chunked_1m":
+        wl = ChunkedWorkload(device, world, rank, group)
+    else:
+        if world > 1:
+            raise SystemExit("layer workloads do not shard: run them with --gpus 1 (replicas only)")
+        wl = LayerWorkload(args.workload, device)
+
+    def sync():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(3, args.warmup)):
+        wl.step()
+    sync()
+    with ClockSampler(local_rank) as clocks:
+        launches0 = ops.LAUNCHES
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        sync()
+        e0.record()
+        for _ in range(args.steps):
+            wl.step()
+        e1.record()
+        sync()
+        ms = e0.elapsed_time(e1)
+        launches = ops.LAUNCHES - launches0
+    t = torch.tensor([ms], device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    ms_per_step = ms / args.steps
+    value = wl.tokens / (ms_per_step / 1e3)
+
+    # per-kernel timing over the same steps (separate pass: events between kernels perturb overlap slightly)
+    ops.start_timing()
+    for _ in range(args.steps):
+        wl.step()
+    kt = ops.stop_timing()
+    top = max(kt.items(), key=lambda kv: kv[1][1]) if kt else None
+    peak, peak_kind = peak_hbm()
+    roofline = None
+    if top is not None:
+        name, (n, tot_ms, nbytes) = top
+        achieved = (nbytes / n) / (tot_ms / n * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "kernel": name, "achieved": achieved, "peak": peak, "unit": "GB/s",
+                    "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "traffic": None,
+                    "launch_ms": tot_ms / n, "algorithmic_bytes_per_launch": nbytes / n,
+                    "kernels_ms_per_step": {k: round(v[1] / args.steps, 4) for k, v in sorted(kt.items(), key=lambda kv: -kv[1][1])}}
+
+    e2e = None
+    if not args.no_e2e:
+        for _ in range(2):
+            wl.step_e2e()
+        sync()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            h2d, d2h = wl.step_e2e()
+        sync()
+        dt = torch.tensor([time.perf_counter() - t0], device=device)
+        if world > 1:
+            dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+        e2e = {"value": wl.tokens / (float(dt.item()) / args.steps), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
+               "d2h_bytes_per_step": int(d2h)}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        v, cores, desc = cpu_oracle_sample(args.workload)
+        cpu = {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": desc}
+    if rank == 0:
+        print(json.dumps({"metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+                          "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True,
+                          "scaling": "strong" if args.workload == "chunked_1m" else "replicas", "vs_baseline": None,
+                          "dtype": "bf16", "data": "synthetic", "config": wl.config, "clocks": clocks.summary(),
+                          "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline, "cpu_baseline": cpu}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

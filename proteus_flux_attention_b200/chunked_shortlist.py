@@ -214,15 +214,22 @@ class _ChunkFeeder:
 
 class ChunkedShortlistRunner:
     def __init__(self, config: ChunkedShortlistConfig, *, logger: Optional[logging.Logger] = None,
-                 process_group: Any = None) -> None:
+                 process_group: Any = None, cache_layers: bool = False) -> None:
+        """``cache_layers`` keeps the two layers between calls of ``run`` (the reference builds fresh ones
+        every call): their ``state_dict`` arguments are then read on first use only, and prototype state
+        carries over from call to call unless ``freeze_prototypes`` is set."""
         self.config = config
         self.config.validate()
         self.logger = logger or LOGGER
         self.group = process_group
+        self._layer_cache: Optional[Dict[Tuple, AdaptiveSparseAttention]] = {} if cache_layers else None
 
     def _make_layer(self, seq_len: int, ratio: float, dtype: torch.dtype, state: Optional[Dict[str, torch.Tensor]],
                     frozen: bool) -> AdaptiveSparseAttention:
         cfg = self.config
+        key = (seq_len, ratio, dtype, frozen)
+        if self._layer_cache is not None and key in self._layer_cache:
+            return self._layer_cache[key]
         mc = _build_model_config(seq_len, cfg.d_model, heads=cfg.heads, sparse_ratio=ratio,
                                  shortlist_alpha=cfg.shortlist_alpha, router_top_p=cfg.nucleus_top_p)
         if frozen:
@@ -233,6 +240,8 @@ class ChunkedShortlistRunner:
         layer = layer.to(device=cfg.device, dtype=dtype).eval()
         layer.use_sdpa = False
         layer.set_shortlist_alpha(float(cfg.shortlist_alpha))
+        if self._layer_cache is not None:
+            self._layer_cache[key] = layer
         return layer
 
     @staticmethod

@@ -10,6 +10,49 @@ import torch
 
 from . import _native as N
 
+# ---- optional instrumentation (used by bench.py): launch counter and per-op CUDA-event timing ----------
+LAUNCHES = 0                      # kernels of libaspa_b200.so launched through this module
+_TIMING: Optional[dict] = None    # name -> list of (start_event, end_event, algorithmic_bytes)
+
+
+def start_timing() -> None:
+    global _TIMING
+    _TIMING = {}
+
+
+def stop_timing() -> dict:
+    """Returns name -> (launches, total_ms, algorithmic_bytes); synchronises the device."""
+    global _TIMING
+    rec, _TIMING = _TIMING or {}, None
+    torch.cuda.synchronize()
+    return {k: (len(v), sum(a.elapsed_time(b) for a, b, _ in v), sum(n for _, _, n in v)) for k, v in rec.items()}
+
+
+class _timed:
+    """Counts launches; when timing is on, brackets the op with CUDA events on the current stream."""
+
+    def __init__(self, name: str, launches: int, nbytes: int = 0):
+        self.name, self.launches, self.nbytes = name, launches, nbytes
+
+    def __enter__(self):
+        global LAUNCHES
+        LAUNCHES += self.launches
+        if _TIMING is not None:
+            self.e0 = torch.cuda.Event(enable_timing=True)
+            self.e0.record()
+        return self
+
+    def __exit__(self, *exc):
+        if _TIMING is not None and exc[0] is None:
+            e1 = torch.cuda.Event(enable_timing=True)
+            e1.record()
+            _TIMING.setdefault(self.name, []).append((self.e0, e1, self.nbytes))
+        return False
+
+
+def _nb(*tensors) -> int:
+    return sum(t.numel() * t.element_size() for t in tensors if t is not None)
+
 
 def _empty(shape, dtype, device):
     return torch.empty(shape, dtype=dtype, device=device)
@@ -18,14 +61,16 @@ def _empty(shape, dtype, device):
 def normalize_rows(p: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
     p = p.to(torch.float32).contiguous()
     out = torch.empty_like(p)
-    N.check(N.lib().aspa_normalize_rows(N.ptr(p), p.size(0), p.size(1), eps, N.ptr(out), N.stream()), "normalize_rows")
+    with _timed('normalize_rows', 1, 0):
+        N.check(N.lib().aspa_normalize_rows(N.ptr(p), p.size(0), p.size(1), eps, N.ptr(out), N.stream()), "normalize_rows")
     return out
 
 
 def reduce_partials(partials: torch.Tensor, n_series: int) -> torch.Tensor:
     n_blocks = partials.numel() // n_series
     out = _empty((n_series,), torch.float32, partials.device)
-    N.check(N.lib().aspa_reduce_partials(N.ptr(partials), n_series, n_blocks, N.ptr(out), N.stream()), "reduce_partials")
+    with _timed('reduce_partials', 1, 0):
+        N.check(N.lib().aspa_reduce_partials(N.ptr(partials), n_series, n_blocks, N.ptr(out), N.stream()), "reduce_partials")
     return out
 
 
@@ -43,10 +88,11 @@ def router_fwd(x2d: torch.Tensor, w_router: torch.Tensor, proto_hat: Optional[to
     bs = _empty((n,), torch.float32, dev) if has_proto else None
     ntile = (n + 63) // 64
     partials = _empty((3 * ntile,), torch.float32, dev) if (want_stats and has_proto) else None
-    N.check(N.lib().aspa_router_fwd(
-        N.ptr(x2d), N.dtype_code(x2d.dtype), n, Cdim, N.ptr(w_router), G, N.ptr(proto_hat), N.ptr(conf_eps),
-        N.ptr(usage_bias), temp, threshold, span, blend, usage_boost, N.ptr(gate), N.ptr(imp), N.ptr(sim), N.ptr(bs),
-        N.ptr(partials), N.stream()), "router_fwd")
+    with _timed('router', 1, _nb(x2d, w_router, proto_hat, gate, imp, sim, bs)):
+        N.check(N.lib().aspa_router_fwd(
+            N.ptr(x2d), N.dtype_code(x2d.dtype), n, Cdim, N.ptr(w_router), G, N.ptr(proto_hat), N.ptr(conf_eps),
+            N.ptr(usage_bias), temp, threshold, span, blend, usage_boost, N.ptr(gate), N.ptr(imp), N.ptr(sim), N.ptr(bs),
+            N.ptr(partials), N.stream()), "router_fwd")
     stats = reduce_partials(partials, 3) if partials is not None else None
     return gate, imp, sim, bs, stats
 
@@ -55,8 +101,9 @@ def token_select(importance: torch.Tensor, need: int, threshold: float, guard: i
     B, T = importance.shape
     mask = _empty((B, T), torch.uint8, importance.device)
     kept = _empty((B,), torch.int32, importance.device)
-    N.check(N.lib().aspa_token_select(N.ptr(importance), B, T, int(need), float(threshold), int(guard), N.ptr(mask),
-                                      N.ptr(kept), N.stream()), "token_select")
+    with _timed('token_select', 1, _nb(importance, mask)):
+        N.check(N.lib().aspa_token_select(N.ptr(importance), B, T, int(need), float(threshold), int(guard), N.ptr(mask),
+                                          N.ptr(kept), N.stream()), "token_select")
     return mask, kept
 
 
@@ -65,9 +112,10 @@ def head_budget(gate: torch.Tensor, g2h: torch.Tensor, H: int, *, top_p: float, 
     n, G = gate.shape
     scratch = _empty((H * ((n + 1023) // 1024),), torch.float32, gate.device)
     k_out = _empty((2,), torch.int32, gate.device)
-    N.check(N.lib().aspa_head_budget(N.ptr(gate), n, G, N.ptr(g2h), H, float(top_p), int(dense_k), int(h_min),
-                                     int(linear_head_k), float(alpha), N.ptr(scratch), N.ptr(k_out), N.stream()),
-            "head_budget")
+    with _timed('head_budget', 2, _nb(gate)):
+        N.check(N.lib().aspa_head_budget(N.ptr(gate), n, G, N.ptr(g2h), H, float(top_p), int(dense_k), int(h_min),
+                                         int(linear_head_k), float(alpha), N.ptr(scratch), N.ptr(k_out), N.stream()),
+                "head_budget")
     return k_out
 
 
@@ -80,9 +128,10 @@ def head_select(gate: torch.Tensor, g2h: torch.Tensor, H: int, *, k_host: int, k
     top_score = _empty((n, kmax), torch.float32, dev)
     nblk = (n + 255) // 256
     partials = _empty((2 * nblk,), torch.float32, dev) if want_stats else None
-    N.check(N.lib().aspa_head_select(N.ptr(gate), n, G, N.ptr(g2h), H, int(k_host), N.ptr(k_dev), int(kmax),
-                                     N.ptr(token_mask), N.ptr(bits), N.ptr(top_idx), N.ptr(top_score),
-                                     N.ptr(partials), N.stream()), "head_select")
+    with _timed('head_select', 1, _nb(gate, bits, top_idx, top_score)):
+        N.check(N.lib().aspa_head_select(N.ptr(gate), n, G, N.ptr(g2h), H, int(k_host), N.ptr(k_dev), int(kmax),
+                                         N.ptr(token_mask), N.ptr(bits), N.ptr(top_idx), N.ptr(top_score),
+                                         N.ptr(partials), N.stream()), "head_select")
     stats = reduce_partials(partials, 2) if partials is not None else None
     return bits, top_idx, top_score, stats
 
@@ -92,8 +141,9 @@ def pack_rows(head_bits: torch.Tensor, B: int, T: int, H: int, capacity: int):
     scratch = _empty((int(N.lib().aspa_pack_rows_scratch(B, H, T)),), torch.int32, dev)
     offs = _empty((B * H + 1,), torch.int32, dev)
     tok = _empty((max(1, capacity),), torch.int32, dev)
-    N.check(N.lib().aspa_pack_rows(N.ptr(head_bits), B, T, H, N.ptr(scratch), N.ptr(offs), N.ptr(tok), capacity,
-                                   N.stream()), "pack_rows")
+    with _timed('pack_rows', 3, 2 * _nb(head_bits)):
+        N.check(N.lib().aspa_pack_rows(N.ptr(head_bits), B, T, H, N.ptr(scratch), N.ptr(offs), N.ptr(tok), capacity,
+                                       N.stream()), "pack_rows")
     return offs, tok
 
 
@@ -103,8 +153,9 @@ def pack_mask(mask_u8: torch.Tensor):
     scratch = _empty((heads * ((T + 255) // 256) + 1,), torch.int32, dev)
     offs = _empty((heads + 1,), torch.int32, dev)
     tok = _empty((heads * T,), torch.int32, dev)
-    N.check(N.lib().aspa_pack_mask(N.ptr(mask_u8), heads, T, N.ptr(scratch), N.ptr(offs), N.ptr(tok), heads * T,
-                                   N.stream()), "pack_mask")
+    with _timed('pack_mask', 3, 2 * _nb(mask_u8)):
+        N.check(N.lib().aspa_pack_mask(N.ptr(mask_u8), heads, T, N.ptr(scratch), N.ptr(offs), N.ptr(tok), heads * T,
+                                       N.stream()), "pack_mask")
     return offs, tok
 
 
@@ -112,8 +163,9 @@ def rope_table(inv_freq: torch.Tensor, T: int, D: int, dtype: torch.dtype):
     dev = inv_freq.device
     cos = _empty((T, D // 2), torch.float32, dev)
     sin = _empty((T, D // 2), torch.float32, dev)
-    N.check(N.lib().aspa_rope_table(N.ptr(inv_freq), T, D, N.dtype_code(dtype), N.ptr(cos), N.ptr(sin), N.stream()),
-            "rope_table")
+    with _timed('rope_table', 1, _nb(cos, sin)):
+        N.check(N.lib().aspa_rope_table(N.ptr(inv_freq), T, D, N.dtype_code(dtype), N.ptr(cos), N.ptr(sin), N.stream()),
+                "rope_table")
     return cos, sin
 
 
@@ -125,16 +177,18 @@ def rope_relayout(qkv: torch.Tensor, H: int, D: int, cos: Optional[torch.Tensor]
     k = torch.empty_like(q)
     v = torch.empty_like(q)
     amax = torch.zeros((3, B * H), dtype=torch.float32, device=dev) if want_amax else None
-    N.check(N.lib().aspa_rope_relayout(N.ptr(qkv), N.dtype_code(qkv.dtype), B, T, H, D, N.ptr(cos), N.ptr(sin),
-                                       N.ptr(q), N.ptr(k), N.ptr(v), N.ptr(amax), N.stream()), "rope_relayout")
+    with _timed('rope_relayout', 1, _nb(qkv, q, k, v)):
+        N.check(N.lib().aspa_rope_relayout(N.ptr(qkv), N.dtype_code(qkv.dtype), B, T, H, D, N.ptr(cos), N.ptr(sin),
+                                           N.ptr(q), N.ptr(k), N.ptr(v), N.ptr(amax), N.stream()), "rope_relayout")
     return q, k, v, amax
 
 
 def head_amax(x: torch.Tensor) -> torch.Tensor:
     heads = x.size(0)
     amax = _empty((heads,), torch.float32, x.device)
-    N.check(N.lib().aspa_head_amax(N.ptr(x), N.dtype_code(x.dtype), heads, x.numel() // heads, N.ptr(amax),
-                                   N.stream()), "head_amax")
+    with _timed('head_amax', 1, _nb(x)):
+        N.check(N.lib().aspa_head_amax(N.ptr(x), N.dtype_code(x.dtype), heads, x.numel() // heads, N.ptr(amax),
+                                       N.stream()), "head_amax")
     return amax
 
 
@@ -142,8 +196,9 @@ def quantize_int8(x: torch.Tensor, amax: torch.Tensor):
     heads = x.size(0)
     out = _empty(x.shape, torch.int8, x.device)
     scales = _empty((heads,), torch.float32, x.device)
-    N.check(N.lib().aspa_quantize_int8(N.ptr(x), N.dtype_code(x.dtype), heads, x.numel() // heads, N.ptr(amax),
-                                       N.ptr(out), N.ptr(scales), N.stream()), "quantize_int8")
+    with _timed('quantize_int8', 1, _nb(x, out)):
+        N.check(N.lib().aspa_quantize_int8(N.ptr(x), N.dtype_code(x.dtype), heads, x.numel() // heads, N.ptr(amax),
+                                           N.ptr(out), N.ptr(scales), N.stream()), "quantize_int8")
     return out, scales
 
 
@@ -158,8 +213,9 @@ def proto_plan(scores: torch.Tensor, cap: int):
     lists = _empty((B, nblk, cap + PROTO_BLOCK), torch.int32, dev)
     limits = _empty((B, T), torch.int32, dev)
     scratch = _empty((max(16, int(N.lib().aspa_proto_plan_scratch(B, T, cap))),), torch.uint8, dev)
-    N.check(N.lib().aspa_proto_plan(N.ptr(scores), B, T, int(cap), N.ptr(scratch), N.ptr(lists), N.ptr(limits),
-                                    N.stream()), "proto_plan")
+    with _timed('proto_plan', 1, _nb(scores, lists, limits)):
+        N.check(N.lib().aspa_proto_plan(N.ptr(scores), B, T, int(cap), N.ptr(scratch), N.ptr(lists), N.ptr(limits),
+                                        N.stream()), "proto_plan")
     return lists, limits
 
 
@@ -187,10 +243,11 @@ def build_candidates(rows: torch.Tensor, row_batch: Optional[torch.Tensor], seq_
     def cap(v):
         return -1 if v is None else max(0, int(v))
 
-    N.check(N.lib().aspa_build_candidates(
-        N.ptr(rows), N.ptr(row_batch), n, int(seq_len), int(L), int(linear_window), int(anchor_stride),
-        int(bool(use_local)), int(bool(use_anchors)), N.ptr(proto_scores), cap(local_cap), cap(anchor_cap),
-        cap(proto_cap), N.ptr(cand), N.ptr(lens), N.stream()), "build_candidates")
+    with _timed('build_candidates', 1, _nb(cand, lens)):
+        N.check(N.lib().aspa_build_candidates(
+            N.ptr(rows), N.ptr(row_batch), n, int(seq_len), int(L), int(linear_window), int(anchor_stride),
+            int(bool(use_local)), int(bool(use_anchors)), N.ptr(proto_scores), cap(local_cap), cap(anchor_cap),
+            cap(proto_cap), N.ptr(cand), N.ptr(lens), N.stream()), "build_candidates")
     return cand, lens
 
 
@@ -207,11 +264,17 @@ def gather_attn(q, k, v, *, scales: Optional[Tuple[torch.Tensor, torch.Tensor, t
         ws = _empty((nbytes,), torch.uint8, q.device)
     qs, ks, vs = scales if scales is not None else (None, None, None)
     L = cand.size(1) if cand is not None else 0
-    N.check(N.lib().aspa_gather_attn_fwd(
-        N.ptr(q), N.ptr(k), N.ptr(v), N.dtype_code(q.dtype), N.ptr(qs), N.ptr(ks), N.ptr(vs), heads, T, D, int(H),
-        N.ptr(row_offsets), N.ptr(token_idx), int(max_rows), int(total_rows), N.ptr(cand), N.ptr(cand_len), int(L),
-        C.byref(plan) if plan is not None else None, N.ptr(add_mask), N.ptr(out), N.dtype_code(out.dtype),
-        int(out_layout), N.ptr(ws), N.stream()), "gather_attn_fwd")
+    e = q.element_size()
+    two_pass = plan is not None and cand is None and (plan.anchor_slots > 0 or plan.proto_cap > 0) and D == 64 \
+        and q.dtype in (torch.bfloat16, torch.int8)
+    # algorithmic bytes: each active row's q once, every key and value row once, each active output row once
+    nbytes = int(total_rows) * D * (e + out.element_size()) + 2 * heads * T * D * e
+    with _timed("attention", 2 if two_pass else 1, nbytes):
+        N.check(N.lib().aspa_gather_attn_fwd(
+            N.ptr(q), N.ptr(k), N.ptr(v), N.dtype_code(q.dtype), N.ptr(qs), N.ptr(ks), N.ptr(vs), heads, T, D, int(H),
+            N.ptr(row_offsets), N.ptr(token_idx), int(max_rows), int(total_rows), N.ptr(cand), N.ptr(cand_len), int(L),
+            C.byref(plan) if plan is not None else None, N.ptr(add_mask), N.ptr(out), N.dtype_code(out.dtype),
+            int(out_layout), N.ptr(ws), N.stream()), "gather_attn_fwd")
     return out
 
 
@@ -222,17 +285,19 @@ def proto_ema_update(x2d: torch.Tensor, gate: torch.Tensor, decay: float, protos
     nbytes = int(N.lib().aspa_proto_ema_scratch(n, Cdim, G))
     scratch = _empty((nbytes,), torch.uint8, x2d.device)
     updated = _empty((1,), torch.int32, x2d.device)
-    N.check(N.lib().aspa_proto_ema_update(N.ptr(x2d), N.dtype_code(x2d.dtype), n, Cdim, N.ptr(gate), G, float(decay),
-                                          N.ptr(protos), N.ptr(usage), N.ptr(conf), N.ptr(scratch), N.ptr(updated),
-                                          N.stream()), "proto_ema_update")
+    with _timed('proto_ema', 2, _nb(x2d, gate, protos)):
+        N.check(N.lib().aspa_proto_ema_update(N.ptr(x2d), N.dtype_code(x2d.dtype), n, Cdim, N.ptr(gate), G, float(decay),
+                                              N.ptr(protos), N.ptr(usage), N.ptr(conf), N.ptr(scratch), N.ptr(updated),
+                                              N.stream()), "proto_ema_update")
     return updated
 
 
 def chunk_select(importance: torch.Tensor, token_mask: Optional[torch.Tensor], budget: int, top_p: float, offset: int,
                  out_scores: torch.Tensor, out_idx: torch.Tensor, out_count: torch.Tensor) -> None:
     T = importance.numel()
-    N.check(N.lib().aspa_chunk_select(N.ptr(importance), N.ptr(token_mask), T, int(budget), float(top_p), int(offset),
-                                      N.ptr(out_scores), N.ptr(out_idx), N.ptr(out_count), N.stream()), "chunk_select")
+    with _timed('chunk_select', 1, _nb(importance)):
+        N.check(N.lib().aspa_chunk_select(N.ptr(importance), N.ptr(token_mask), T, int(budget), float(top_p), int(offset),
+                                          N.ptr(out_scores), N.ptr(out_idx), N.ptr(out_count), N.stream()), "chunk_select")
 
 
 def merge_finalise(scores: torch.Tensor, indices: torch.Tensor, seq_len: int, max_tokens: int):
@@ -241,15 +306,17 @@ def merge_finalise(scores: torch.Tensor, indices: torch.Tensor, seq_len: int, ma
     keep_idx = _empty((max_tokens,), torch.int64, dev)
     keep_sc = _empty((max_tokens,), torch.float32, dev)
     count = _empty((1,), torch.int32, dev)
-    N.check(N.lib().aspa_merge_finalise(N.ptr(scores), N.ptr(indices), scores.numel(), int(seq_len), int(max_tokens),
-                                        N.ptr(table), N.ptr(keep_idx), N.ptr(keep_sc), N.ptr(count), N.stream()),
-            "merge_finalise")
+    with _timed('merge_finalise', 2, _nb(scores, indices)):
+        N.check(N.lib().aspa_merge_finalise(N.ptr(scores), N.ptr(indices), scores.numel(), int(seq_len), int(max_tokens),
+                                            N.ptr(table), N.ptr(keep_idx), N.ptr(keep_sc), N.ptr(count), N.stream()),
+                "merge_finalise")
     return keep_idx, keep_sc, count
 
 
 def gather_rows(src2d: torch.Tensor, idx: torch.Tensor, count_dev: Optional[torch.Tensor], max_rows: int) -> torch.Tensor:
     row_bytes = src2d.size(1) * src2d.element_size()
     dst = _empty((max_rows, src2d.size(1)), src2d.dtype, src2d.device)
-    N.check(N.lib().aspa_gather_rows(N.ptr(src2d), N.ptr(idx), N.ptr(count_dev), int(max_rows), int(row_bytes),
-                                     N.ptr(dst), N.stream()), "gather_rows")
+    with _timed('gather_rows', 1, 2 * _nb(dst)):
+        N.check(N.lib().aspa_gather_rows(N.ptr(src2d), N.ptr(idx), N.ptr(count_dev), int(max_rows), int(row_bytes),
+                                         N.ptr(dst), N.stream()), "gather_rows")
     return dst
