@@ -107,6 +107,25 @@ int64_t aspa_pack_rows_scratch(int B, int H, int T);
 int aspa_pack_rows(const uint64_t* head_bits, int B, int T, int H, int32_t* seg_scratch,
                    int32_t* row_offsets, int32_t* token_idx, int64_t capacity, void* stream);
 
+/* aspa_pack_rows for callers that cannot provide scratch memory.  It has no counterpart in the
+ * reference: it exists for hosts that must not allocate at call time — a serving loop whose device
+ * arena was sized once at start-up and which bans allocator calls on the request path (they may
+ * synchronise the device or fragment the arena), or a foreign-language binding with no CUDA allocator
+ * that only forwards the input and output buffers it was given.  The segment-count scratch lives in a
+ * fixed array inside the library: aspa_pack_rows_static_capacity() int32 entries (1 MiB) on every GPU
+ * that loads the library, until the process exits.  Same inputs, outputs and results as aspa_pack_rows.
+ *   - B*H*ceil(T/256) + 1 must not exceed the capacity; larger problems are rejected with ASPA_ERR_ARG
+ *     and a message (use aspa_pack_rows then);
+ *   - no cudaMalloc, cudaFree or other allocating call is made; the first call on each device looks up
+ *     the array's device address (cudaGetSymbolAddress with that device current) — make that first
+ *     call before any stream capture;
+ *   - all calls share the one array, which keeps whatever the previous call left in it (nothing in it
+ *     needs to start at zero); two calls that overlap on the GPU (different streams, or different
+ *     threads on one device) race on it, so serialise them. */
+int64_t aspa_pack_rows_static_capacity(void);
+int aspa_pack_rows_static(const uint64_t* head_bits, int B, int T, int H, int32_t* row_offsets,
+                          int32_t* token_idx, int64_t capacity, void* stream);
+
 /* Pack a (heads, T) uint8 activity mask (the functional API's active_mask). */
 int aspa_pack_mask(const uint8_t* mask, int heads, int T, int32_t* seg_scratch, int32_t* row_offsets,
                    int32_t* token_idx, int64_t capacity, void* stream);

@@ -39,6 +39,8 @@ SIGNATURES = {
     "aspa_head_select": (_i, [_p, _l, _i, _p, _i, _i, _p, _i, _p, _p, _p, _p, _p, _p]),
     "aspa_pack_rows_scratch": (_l, [_i, _i, _i]),
     "aspa_pack_rows": (_i, [_p, _i, _i, _i, _p, _p, _p, _l, _p]),
+    "aspa_pack_rows_static_capacity": (_l, []),
+    "aspa_pack_rows_static": (_i, [_p, _i, _i, _i, _p, _p, _l, _p]),
     "aspa_pack_mask": (_i, [_p, _i, _i, _p, _p, _p, _l, _p]),
     "aspa_rope_table": (_i, [_p, _i, _i, _i, _p, _p, _p]),
     "aspa_rope_relayout": (_i, [_p, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p]),

@@ -1,4 +1,6 @@
 // Token keep (radix select), head budget, per-token head top-k and row packing.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace aspa {
@@ -411,4 +413,67 @@ extern "C" int aspa_pack_mask(const uint8_t* mask, int heads, int T, int32_t* se
     if (heads % d == 0) hp = d;
   return pack_impl<false>(mask, heads / hp, T, hp, seg_scratch, row_offsets, token_idx, capacity,
                           (cudaStream_t)stream);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Row packing for callers that must not allocate.
+//
+// Some hosts of this library cannot hand it scratch memory at call time: a serving loop that sized
+// its device arena once at start-up and forbids allocator calls on the request path (an allocation
+// may synchronise the device or fragment the arena), or a foreign-language binding that has no CUDA
+// allocator of its own and only passes through the input and output buffers it was given.  For them
+// the segment-count scratch of the packer lives in a fixed device array inside the library: 1 MiB
+// per GPU that loads the library, held until the process exits.
+//
+// The array's name is only a host-side handle here, not a device address.  The address is looked up
+// once per device with cudaGetSymbolAddress (that device being current) and cached.
+// ---------------------------------------------------------------------------------------------
+namespace aspa {
+constexpr int64_t PACK_STATIC_INTS = 262144;  // 1 MiB of int32
+static __device__ __align__(256) int32_t g_pack_static_scratch[PACK_STATIC_INTS];
+
+constexpr int PACK_STATIC_MAX_DEVICES = 64;
+static int32_t* g_pack_static_ptr[PACK_STATIC_MAX_DEVICES] = {nullptr};
+static std::mutex g_pack_static_mutex;
+
+// Device address of the static scratch on the current device; nullptr (with the error set) on failure.
+static int32_t* pack_static_scratch_for_current_device() {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= PACK_STATIC_MAX_DEVICES) {
+    set_error("aspa_pack_rows_static: cannot identify the current device (%s)",
+              e != cudaSuccess ? cudaGetErrorString(e) : "device index out of range");
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(g_pack_static_mutex);
+  if (g_pack_static_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_pack_static_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      set_error("aspa_pack_rows_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      return nullptr;
+    }
+    g_pack_static_ptr[dev] = static_cast<int32_t*>(p);
+  }
+  return g_pack_static_ptr[dev];
+}
+}  // namespace aspa
+
+extern "C" int64_t aspa_pack_rows_static_capacity(void) { return aspa::PACK_STATIC_INTS; }
+
+extern "C" int aspa_pack_rows_static(const uint64_t* head_bits, int B, int T, int H, int32_t* row_offsets,
+                                     int32_t* token_idx, int64_t capacity, void* stream) {
+  ASPA_CHECK_ARG(head_bits && row_offsets && token_idx, "null pointer");
+  ASPA_CHECK_ARG(B > 0 && T > 0 && H > 0 && H <= 64, "bad sizes (H <= 64)");
+  const int64_t need = aspa_pack_rows_scratch(B, H, T);
+  if (need > PACK_STATIC_INTS) {
+    set_error("aspa_pack_rows_static: B*H*ceil(T/256)+1 = %lld scratch entries exceed the built-in %lld; "
+              "use aspa_pack_rows with caller-provided scratch",
+              (long long)need, (long long)PACK_STATIC_INTS);
+    return ASPA_ERR_ARG;
+  }
+  int32_t* scratch = pack_static_scratch_for_current_device();
+  if (scratch == nullptr) return ASPA_ERR_CUDA;
+  // Nothing in the scratch has to start at zero: the count pass writes every entry the scan reads.
+  return pack_impl<true>(head_bits, B, T, H, scratch, row_offsets, token_idx, capacity, (cudaStream_t)stream);
 }
