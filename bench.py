@@ -116,7 +116,8 @@ class ChunkedWorkload:
         self.tokens = SEQ_1M
         cfg = P.ChunkedShortlistConfig(seq_len=SEQ_1M, d_model=D_MODEL, chunk_len=CHUNK, buffer_tokens=BUFFER,
                                        per_chunk_budget=BUDGET, device=device, heads=HEADS, freeze_prototypes=True,
-                                       warmup=False, collect_summaries=False, pass1_full_forward=True)
+                                       warmup=False, collect_summaries=False, pass1_full_forward=True,
+                                       use_cuda_graph=True)
         self.runner = P.ChunkedShortlistRunner(cfg, process_group=group, cache_layers=True)
         mk = lambda n, r: P.AdaptiveSparseAttention(_build_model_config(n, D_MODEL, heads=HEADS, sparse_ratio=r,  # noqa: E731
                                                                        shortlist_alpha=1.0, router_top_p=0.9))
@@ -127,7 +128,7 @@ class ChunkedWorkload:
         self.host_shard = None
         self.config = {"workload": self.name, "seq_len": SEQ_1M, "d_model": D_MODEL, "heads": HEADS, "chunk_len": CHUNK,
                        "per_chunk_budget": BUDGET, "buffer_tokens": BUFFER, "pass1": "full layer forward per chunk",
-                       "prototypes": "frozen during pass 1", "sharding": f"chunks over {world} rank(s)",
+                       "prototypes": "frozen during pass 1", "pass1_launch": "CUDA graph replay per chunk", "sharding": f"chunks over {world} rank(s)",
                        "l2": "inputs (2 GiB) larger than L2"}
 
     def step(self):
@@ -137,9 +138,12 @@ class ChunkedWorkload:
     def step_e2e(self):
         if self.host_shard is None:
             self.host_shard = self.shard.cpu().pin_memory()
+            self.host_out = torch.empty((1, BUFFER, D_MODEL), dtype=torch.bfloat16, pin_memory=True)
         res = self.runner.run(self.host_shard, chunk_state=self.chunk_state, final_state=self.final_state,
                               sequence_is_local_shard=True)
-        out = res.final_output.cpu()
+        out = self.host_out[:, : res.final_output.size(1)]
+        out.copy_(res.final_output, non_blocking=True)
+        torch.cuda.synchronize()
         return self.host_shard.numel() * 2, out.numel() * 2 + res.keep_indices.numel() * 12
 
 
@@ -188,8 +192,11 @@ class LayerWorkload:
     def step_e2e(self):
         if self.host_x is None:
             self.host_x = self.x.cpu().pin_memory()
+            self.host_y = torch.empty_like(self.host_x)  # pinned, like the input
         self._reset()
-        y = self.layer(self.host_x.to(self.device, non_blocking=True)).cpu()
+        y = self.layer(self.host_x.to(self.device, non_blocking=True))
+        self.host_y.copy_(y, non_blocking=True)
+        torch.cuda.synchronize()
         return self.host_x.numel() * 2, y.numel() * 2
 
 
@@ -253,6 +260,8 @@ def main():
     ap.add_argument("--workload", default="chunked_1m", choices=["chunked_1m", "shortlist_256k", "sparse_16k"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--profile-mode", action="store_true",
+                    help="for runs under a profiler: exactly --warmup + --steps passes, no timing pass, e2e or CPU baseline")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -296,6 +305,13 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    if args.profile_mode:
+        for _ in range(args.warmup + args.steps):
+            wl.step()
+        sync()
+        if rank == 0:
+            print(json.dumps({"profile_mode": True, "workload": args.workload, "passes": args.warmup + args.steps}))
+        return
     for _ in range(max(3, args.warmup)):
         wl.step()
     sync()

@@ -68,6 +68,19 @@ int aspa_router_fwd(const void* x, int x_dtype, int64_t n, int C, const void* w_
                     float usage_boost, float* gate_probs, float* importance, float* proto_sim, float* blend,
                     float* stat_partials, void* stream);
 
+/* The same router on tcgen05 tensor cores for bf16 activations: 128-token tiles, TMA-staged operands,
+ * accumulator in tensor memory.  Results as aspa_router_fwd (fp32 accumulation order differs).
+ *   aspa_router_tc_scratch_bytes: bytes of 16-byte aligned scratch the call needs, or 0 when the shape is
+ *     not supported (needs C % 64 == 0, G % 4 == 0, 4*G <= 128 with prototypes, G <= 128 without);
+ *   n >= 128; status (1) int32, zeroed by the caller: set non-zero if a bounded device-side wait ran out
+ *     (the outputs are then invalid). */
+int64_t aspa_router_tc_scratch_bytes(int C, int G, int has_proto);
+int aspa_router_fwd_tc(const void* x, int64_t n, int C, const void* w_router, int G, const float* proto_hat,
+                       const float* conf_eps, const float* usage_bias, float proto_temp, float proto_threshold,
+                       float proto_span, float proto_blend, float usage_boost, float* gate_probs,
+                       float* importance, float* proto_sim, float* blend, float* stat_partials, void* scratch,
+                       int32_t* status, void* stream);
+
 /* L2-normalise the G prototype rows (F.normalize(..., eps=1e-6), aspa.py:639-640). */
 int aspa_normalize_rows(const float* src, int rows, int cols, float eps, float* dst, void* stream);
 
@@ -226,10 +239,10 @@ int aspa_chunk_select(const float* importance, const uint8_t* token_mask, int T,
  * unique index (the lowest, as the reference's sort key does), the max_tokens
  * best of them, ascending index order.
  *   scores/indices (n): entries with index < 0 are ignored; seq_len bounds the indices
- *   table: (seq_len) uint32 scratch; keep_idx (max_tokens) int64, keep_scores (max_tokens) fp32,
+ *   table: scratch of 8 * seq_len bytes; keep_idx (max_tokens) int64, keep_scores (max_tokens) fp32,
  *   keep_count (1) int32 out. */
 int aspa_merge_finalise(const float* scores, const int64_t* indices, int64_t n, int64_t seq_len,
-                        int max_tokens, uint32_t* table, int64_t* keep_idx, float* keep_scores,
+                        int max_tokens, void* table, int64_t* keep_idx, float* keep_scores,
                         int32_t* keep_count, void* stream);
 
 /* Gather rows src[idx[i], :] -> dst[i, :] (cs.py:688-689). row_bytes multiple of 16. */

@@ -33,6 +33,8 @@ SIGNATURES = {
     "aspa_last_error_string": (C.c_char_p, []),
     "aspa_version": (_i, []),
     "aspa_router_fwd": (_i, [_p, _i, _l, _i, _p, _i, _p, _p, _p, _f, _f, _f, _f, _f, _p, _p, _p, _p, _p, _p]),
+    "aspa_router_tc_scratch_bytes": (_l, [_i, _i, _i]),
+    "aspa_router_fwd_tc": (_i, [_p, _l, _i, _p, _i, _p, _p, _p, _f, _f, _f, _f, _f, _p, _p, _p, _p, _p, _p, _p, _p]),
     "aspa_normalize_rows": (_i, [_p, _i, _i, _f, _p, _p]),
     "aspa_token_select": (_i, [_p, _i, _i, _i, _f, _i, _p, _p, _p]),
     "aspa_head_budget": (_i, [_p, _l, _i, _p, _i, _d, _i, _i, _i, _d, _p, _p, _p]),

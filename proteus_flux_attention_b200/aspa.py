@@ -279,8 +279,9 @@ class AdaptiveSparseAttention(nn.Module):
         self.qkv = nn.Linear(self.d_model, 3 * self.d_model, bias=self.bias)
         self.proj = nn.Linear(self.d_model, self.d_model, bias=self.bias)
 
-        self.last_head_stats: Optional[dict] = None
-        self._last_sparse_state: Optional[dict] = None
+        self.__dict__["_pending"] = None
+        self.last_head_stats = None
+        self._last_sparse_state = None
         self.last_aux_loss: Optional[torch.Tensor] = None
         self.last_router_reg: Optional[torch.Tensor] = None
         self._latency_ema: Optional[float] = None
@@ -566,6 +567,113 @@ class AdaptiveSparseAttention(nn.Module):
         self.last_router_reg = None
         return y
 
+    # ---- telemetry: filled from one small host record, lazily when the call did not need it ------------------
+    @property
+    def last_head_stats(self) -> Optional[dict]:
+        self._materialize()
+        return self.__dict__.get("_head_stats_value")
+
+    @last_head_stats.setter
+    def last_head_stats(self, value: Optional[dict]) -> None:
+        self.__dict__["_head_stats_value"] = value
+
+    @property
+    def _last_sparse_state(self) -> Optional[dict]:
+        self._materialize()
+        return self.__dict__.get("_sparse_state_value")
+
+    @_last_sparse_state.setter
+    def _last_sparse_state(self, value: Optional[dict]) -> None:
+        self.__dict__["_sparse_state_value"] = value
+
+    def _materialize(self) -> None:
+        """Turn the pending host record of the last call into the telemetry dictionaries (waits for its copy)."""
+        ctx = self.__dict__.get("_pending")
+        if ctx is None:
+            return
+        self.__dict__["_pending"] = None
+        if ctx["event"] is not None:
+            ctx["event"].synchronize()
+        else:
+            torch.cuda.synchronize(ctx["device"])
+        info = self._decode_record(ctx)
+        self._publish(ctx, info, force_dense=False, dense_reason=None, exec_mode=ctx["exec_mode"])
+
+    def _decode_record(self, ctx: dict) -> dict:
+        rec = ctx["pin"].tolist()
+        B, T, H = ctx["B"], ctx["T"], self.h_total
+        nbh = B * H
+        offs = [int(v) for v in rec[: nbh + 1]]
+        kept = [int(v) for v in rec[nbh + 1: nbh + 1 + B]]
+        p0 = nbh + 1 + B
+        counts = [offs[i + 1] - offs[i] for i in range(nbh)]
+        if int(rec[p0 + 7]) != 0:
+            raise RuntimeError("the tensor-core router reported an expired device-side wait; its outputs are invalid")
+        return {"offs": offs, "kept": kept, "topk": int(rec[p0]), "adaptive": int(rec[p0 + 1]), "score_sum": rec[p0 + 2],
+                "entropy_sum": rec[p0 + 3], "sim_sum": rec[p0 + 4], "bs_sum": rec[p0 + 5], "bs_pos": rec[p0 + 6],
+                "counts": counts, "total_rows": offs[-1], "max_rows": max(counts) if counts else 0,
+                "active_heads": sum(1 for c in counts if c > 0),
+                "keep_fraction": float(sum(kept)) / float(B * T) if self.token_sparse else 1.0}
+
+    def _publish(self, ctx: dict, info: dict, *, force_dense: bool, dense_reason: Optional[str], exec_mode: str) -> None:
+        """Build ``last_head_stats`` / ``_last_sparse_state`` exactly as the reference fills them (aspa.py:1688-1915)."""
+        B, T, H = ctx["B"], ctx["T"], self.h_total
+        nbh, alpha, dev = B * H, ctx["alpha"], ctx["device"]
+        topk, counts, total_rows, max_rows = info["topk"], info["counts"], info["total_rows"], info["max_rows"]
+        density = float(max_rows) / float(max(1, T))
+        thr = self._density_threshold()
+        if ctx.get("lazy"):
+            self._last_target_k = topk
+            self._update_density(density)
+            if ctx["use_proto"]:
+                n_tok = float(B * T)
+                self._last_proto_stats = {"max_sim_mean": info["sim_sum"] / n_tok, "blend_mean": info["bs_sum"] / n_tok,
+                                          "active_tokens": int(round(info["bs_pos"]))}
+        common = {"density": density, "target_k": int(topk), "force_dense_threshold": None if thr is None else float(thr),
+                  "quantized": False, "token_keep_fraction": float(info["keep_fraction"]),
+                  "mode_setting": self.mode_setting, "mode_selected": f"cvt(alpha={alpha:.2f})",
+                  "shortlist_alpha": float(alpha)}
+        if force_dense:
+            mode_str = "dense_alpha" if dense_reason == "alpha" else ("dense" if info["active_heads"] == nbh else "dense_auto")
+            exec_mode = mode_str
+            state = dict(common, mode=mode_str, backend=BACKEND_NAME, max_rows=max_rows, dense_reason=dense_reason)
+        elif total_rows == 0:
+            state = dict(common, mode="dense", backend="not_invoked", max_rows=max_rows, dense_reason=None)
+        else:
+            active = [i for i, c in enumerate(counts) if c > 0]
+            offs = info["offs"]
+            state = dict(common, mode="shortlist", backend=BACKEND_NAME, max_rows=int(max_rows), cache_hit=False,
+                         token_idx=ctx["token_idx"][:total_rows], row_offsets_all=ctx["row_offsets"],
+                         active_head_indices=torch.tensor(active, dtype=torch.long, device=dev),
+                         row_offsets=torch.tensor([offs[i] for i in active] + [total_rows], dtype=torch.int32, device=dev),
+                         linear_L=int(self.linear_L), linear_window=int(self.linear_window),
+                         linear_anchor_stride=int(self.linear_anchor_stride), linear_shortlist_backend=BACKEND_NAME)
+        n_tok = float(B * T)
+        stats = {
+            "top_k": int(topk), "mean_gate_prob": float(info["score_sum"] / max(float(total_rows), 1.0)),
+            "router_entropy": float(info["entropy_sum"] / n_tok), "mean_active_per_token": float(total_rows / n_tok),
+            "unique_heads": len({i % H for i, c in enumerate(counts) if c > 0}),
+            "active_fraction": float(total_rows / (n_tok * H)), "max_active_rows": int(max_rows),
+            "max_active_density": float(density), "target_k": int(topk), "seq_len": int(T),
+            "active_min": int(self.h_active_min), "active_max": int(self.h_active_max),
+            "force_dense_threshold": None if thr is None else float(thr), "active_curve": float(self.h_active_curve),
+            "token_keep_fraction": float(info["keep_fraction"]), "mode": exec_mode,
+            "mode_selected": ctx.get("label") or f"cvt(alpha={alpha:.2f})", "shortlist_alpha": float(alpha),
+            "router_top_p": float(self.router_top_p), "nucleus_k": int(info["adaptive"]), "top_a_consensus": True,
+            "mode_setting": self.mode_setting}
+        if dense_reason is not None:
+            stats["dense_reason"] = dense_reason
+        if alpha > 0.0:
+            stats.update(linear_L=int(self.linear_L), linear_window=int(self.linear_window),
+                         linear_anchor_stride=int(self.linear_anchor_stride), linear_shortlist_backend=BACKEND_NAME)
+        if self._last_proto_stats:
+            stats["proto"] = dict(self._last_proto_stats)
+            stats["dna"] = dict(self._last_proto_stats)
+        if ctx.get("label"):
+            state["mode_selected"] = ctx["label"]
+        self.__dict__["_head_stats_value"] = stats
+        self.__dict__["_sparse_state_value"] = state
+
     # ---- forward ------------------------------------------------------------------------------------
     @torch.no_grad()
     def forward(self, x: torch.Tensor) -> torch.Tensor:
@@ -574,6 +682,7 @@ class AdaptiveSparseAttention(nn.Module):
         B, T, C = x.shape
         dev = x.device
         H, D, G = self.h_total, self.d_head, self.attn_gates
+        self.__dict__["_pending"] = None
         self.last_aux_loss = None
         self._last_token_importance = self._last_token_mask = self._last_token_blend = None
         if not self.proto_enabled:
@@ -618,11 +727,12 @@ class AdaptiveSparseAttention(nn.Module):
 
         # 2. token keep
         token_mask_u8 = kept = None
+        kept_bound = T          # host-side upper bound on kept tokens per batch element
+        bound_known = True
         if self.token_sparse:
             ratio = float(self._token_keep_ratio_runtime)
             if ratio >= 0.999 and self.token_keep_threshold <= 0.0:
                 token_mask_u8 = torch.ones((B, T), dtype=torch.uint8, device=dev)
-                kept = torch.full((B,), T, dtype=torch.int32, device=dev)
             else:
                 guard = min(max(0, self.token_keep_guard), T)
                 min_keep = max(min(max(0, self.token_keep_min), T), guard)
@@ -631,123 +741,114 @@ class AdaptiveSparseAttention(nn.Module):
                     need = max(need, min_keep)
                 need = max(1, min(need, T))
                 token_mask_u8, kept = ops.token_select(self._last_token_importance, need, self.token_keep_threshold, guard)
+                kept_bound = min(T, max(need, guard) + guard)
+                bound_known = self.token_keep_threshold <= 0.0
             self._last_token_mask = token_mask_u8.view(torch.bool)
 
         # 3. head budget and per-token head choice
         dense_k = self._choose_active_k(T)
         k_dev = None
-        adaptive_host: Optional[int] = dense_k
         if self.router_top_p > 0.0 and dense_k > self.h_active_min and dense_k > 1:
             k_dev = ops.head_budget(gate, self._gate_to_head_i32, H, top_p=self.router_top_p, dense_k=dense_k,
                                     h_min=self.h_active_min, linear_head_k=self.linear_head_k, alpha=alpha)
-            adaptive_host = None
-        k_host = 0
+        k_host = adaptive_host = 0
         if k_dev is None:
-            adaptive = max(self.h_active_min, dense_k) if self.router_top_p > 0.0 else dense_k
-            lin_k = max(1, min(adaptive, self.linear_head_k))
-            k_host = min(adaptive, max(1, int(round((1.0 - alpha) * float(adaptive) + alpha * float(lin_k)))))
-            adaptive_host = adaptive
+            adaptive_host = dense_k
+            lin_k = max(1, min(adaptive_host, self.linear_head_k))
+            k_host = min(adaptive_host, max(1, int(round((1.0 - alpha) * float(adaptive_host) + alpha * float(lin_k)))))
+        k_bound = k_host if k_dev is None else dense_k
+        if k_dev is None:
+            self._last_target_k = k_host
         head_bits, top_idx, top_score, head_sums = ops.head_select(
             gate, self._gate_to_head_i32, H, k_host=k_host, k_dev=k_dev, kmax=dense_k,
             token_mask=token_mask_u8.view(-1) if token_mask_u8 is not None else None)
         capacity = B * T * dense_k
         row_offsets, token_idx = ops.pack_rows(head_bits, B, T, H, capacity)
 
-        # 4. one statistics record to the host, fetched while the projection runs
-        rec_parts = [row_offsets.to(torch.float64)]
-        rec_parts.append(kept.to(torch.float64) if kept is not None else torch.full((B,), float(T), dtype=torch.float64, device=dev))
-        rec_parts.append(k_dev.to(torch.float64) if k_dev is not None else torch.tensor([float(k_host), float(adaptive_host)], dtype=torch.float64, device=dev))
-        rec_parts.append(head_sums.to(torch.float64))
-        rec_parts.append(proto_sums.to(torch.float64) if proto_sums is not None else torch.zeros(3, dtype=torch.float64, device=dev))
-        rec_dev = torch.cat(rec_parts)
+        # 4. one statistics record to the host: [row offsets | kept per batch | k, adaptive | score, entropy sums |
+        #    prototype sums | router status], copied asynchronously and read when (and if) it is needed
+        f64 = dict(dtype=torch.float64, device=dev)
+        rec_dev = torch.cat([
+            row_offsets.to(torch.float64),
+            kept.to(torch.float64) if kept is not None else torch.full((B,), float(T), **f64),
+            k_dev.to(torch.float64) if k_dev is not None else torch.full((2,), float(k_host), **f64),
+            head_sums.to(torch.float64),
+            proto_sums.to(torch.float64) if proto_sums is not None else torch.zeros(3, **f64),
+            ops.router_status(dev).to(torch.float64)])
         if self._pin is None or self._pin.numel() != rec_dev.numel():
             self._pin = torch.empty(rec_dev.numel(), dtype=torch.float64, pin_memory=True)
         self._pin.copy_(rec_dev, non_blocking=True)
-        ev_rec = torch.cuda.Event()
-        ev_rec.record()
+        capturing = torch.cuda.is_current_stream_capturing()
+        ev_rec = None
+        if not capturing:  # inside a CUDA-graph capture the record is read after the replay's stream has drained
+            ev_rec = torch.cuda.Event()
+            ev_rec.record()
+        ctx = {"B": B, "T": T, "alpha": alpha, "device": dev, "pin": self._pin, "event": ev_rec, "use_proto": use_proto,
+               "token_idx": token_idx, "row_offsets": row_offsets, "exec_mode": "shortlist"}
 
         # 5. projection + RoPE + head-major relayout (does not depend on the record)
         use_quant = bool(self.quantize_sparse_int8 and not self.training)
         q, k, v, amax = self._project_qkv(x, want_amax=use_quant and self.quantize_sparse_int8_mode == "max")
 
-        ev_rec.synchronize()
-        rec = self._pin.tolist()
-        nbh = B * H
-        offs_host = [int(vv) for vv in rec[: nbh + 1]]
-        kept_host = [int(vv) for vv in rec[nbh + 1: nbh + 1 + B]]
-        p0 = nbh + 1 + B
-        topk, adaptive_topk = int(rec[p0]), int(rec[p0 + 1])
-        score_sum, entropy_sum = rec[p0 + 2], rec[p0 + 3]
-        sim_sum, bs_sum, bs_pos = rec[p0 + 4], rec[p0 + 5], rec[p0 + 6]
-        counts = [offs_host[i + 1] - offs_host[i] for i in range(nbh)]
-        total_rows = offs_host[-1]
-        max_rows_est = max(counts) if counts else 0
-        total_active_heads = sum(1 for c in counts if c > 0)
-        token_keep_fraction = float(sum(kept_host)) / float(B * T) if self.token_sparse else 1.0
-        self._last_target_k = topk
-        if topk <= 0:
-            raise RuntimeError("ASPA requires at least one active head per token")
-        density_est = float(max_rows_est) / float(max(1, T))
-        self._update_density(density_est)
-        density_threshold = self._density_threshold()
-        all_rows_active = total_rows == nbh * T
-        force_dense, dense_reason = False, None
-        if alpha <= self.dense_alpha_cutoff and not self.quantize_sparse_int8:
-            force_dense, dense_reason = True, "alpha"
-        if density_threshold is not None and density_est >= density_threshold:
-            force_dense, dense_reason = True, dense_reason or "density"
-        elif all_rows_active and self.force_dense_when_full:
-            force_dense, dense_reason = True, dense_reason or "full"
-        if alpha >= 0.95:
-            dense_reason = None if dense_reason == "alpha" else dense_reason
-            force_dense = False
-        if use_proto:
-            n_tok = float(B * T)
-            self._last_proto_stats = {"max_sim_mean": sim_sum / n_tok, "blend_mean": bs_sum / n_tok,
-                                      "active_tokens": int(round(bs_pos))}
+        # The mode decision needs row counts — unless alpha >= 0.95, where the reference never goes dense
+        # (aspa.py:1636-1639): then the call runs without waiting for the record, on host-side bounds.
+        runtime = self._prepare_linear_runtime(T, B, alpha)
+        plan_args = self._plan_shape(runtime, T, sim is not None)
+        lazy = alpha >= 0.95 and bound_known and plan_args is not None
+        out = torch.zeros((B, T, C), dtype=x.dtype, device=dev)
+        info = None
+        force_dense, dense_reason, exec_mode = False, None, "shortlist"
+        if lazy:
+            total_rows, max_rows = B * kept_bound * k_bound, kept_bound
         else:
-            self._last_proto_stats = None
+            if capturing:
+                raise RuntimeError("this call needs row counts on the host (alpha < 0.95, a keep threshold, or candidate "
+                                   "pieces that may exceed L) and cannot be captured into a CUDA graph")
+            ev_rec.synchronize()
+            info = self._decode_record(ctx)
+            total_rows, max_rows = info["total_rows"], info["max_rows"]
+            self._last_target_k = info["topk"]
+            if info["topk"] <= 0:
+                raise RuntimeError("ASPA requires at least one active head per token")
+            density_est = float(max_rows) / float(max(1, T))
+            self._update_density(density_est)
+            density_threshold = self._density_threshold()
+            if alpha <= self.dense_alpha_cutoff and not self.quantize_sparse_int8:
+                force_dense, dense_reason = True, "alpha"
+            if density_threshold is not None and density_est >= density_threshold:
+                force_dense, dense_reason = True, dense_reason or "density"
+            elif info["total_rows"] == B * H * T and self.force_dense_when_full:
+                force_dense, dense_reason = True, dense_reason or "full"
+            if alpha >= 0.95:
+                dense_reason = None if dense_reason == "alpha" else dense_reason
+                force_dense = False
+            if use_proto:
+                n_tok = float(B * T)
+                self._last_proto_stats = {"max_sim_mean": info["sim_sum"] / n_tok, "blend_mean": info["bs_sum"] / n_tok,
+                                          "active_tokens": int(round(info["bs_pos"]))}
+            else:
+                self._last_proto_stats = None
 
         # 6. attention
-        out = torch.zeros((B, T, C), dtype=x.dtype, device=dev)
-        exec_mode = "sparse"
-        common_state = {"density": density_est, "target_k": int(topk),
-                        "force_dense_threshold": None if density_threshold is None else float(density_threshold),
-                        "quantized": False, "token_keep_fraction": float(token_keep_fraction),
-                        "mode_setting": self.mode_setting, "mode_selected": f"cvt(alpha={alpha:.2f})",
-                        "shortlist_alpha": float(alpha)}
         if force_dense:
+            nbh = B * H
             if token_mask_u8 is None:
                 d_offs, d_tok = self._identity_rows(B, T, dev)
                 d_total, d_max = nbh * T, T
             else:  # every head, kept tokens only: rows of dropped tokens are zero either way (aspa.py:1841-1842)
-                all_bits = torch.where(token_mask_u8.view(-1) != 0, torch.full((), (1 << H) - 1 if H < 64 else -1, dtype=torch.int64, device=dev),
+                full = (1 << H) - 1 if H < 64 else -1
+                all_bits = torch.where(token_mask_u8.view(-1) != 0, torch.full((), full, dtype=torch.int64, device=dev),
                                        torch.zeros((), dtype=torch.int64, device=dev))
                 d_offs, d_tok = ops.pack_rows(all_bits, B, T, H, B * T * H)
-                d_total, d_max = H * sum(kept_host), max(kept_host)
+                d_total, d_max = H * sum(info["kept"]), max(info["kept"])
             if d_total > 0:
                 attention_packed(q, k, v, row_offsets=d_offs, token_idx=d_tok, max_rows=d_max, total_rows=d_total, H=H,
                                  out=out, out_layout=N.OUT_TOKEN_MAJOR)
             _record_backend(BACKEND_NAME, device=str(dev), heads=nbh, tokens=T, max_rows=int(d_max))
-            mode_str = "dense_alpha" if dense_reason == "alpha" else ("dense" if total_active_heads == nbh else "dense_auto")
-            exec_mode = mode_str
-            self._last_sparse_state = dict(common_state, mode=mode_str, backend=BACKEND_NAME, max_rows=max_rows_est,
-                                           dense_reason=dense_reason)
         elif total_rows == 0:
-            dense_reason = None
-            self._last_sparse_state = dict(common_state, mode="dense", backend="not_invoked", max_rows=max_rows_est,
-                                           dense_reason=None)
+            exec_mode = "sparse"
         else:
             dense_reason = None
-            runtime = self._prepare_linear_runtime(T, B, alpha)
-            L = runtime["effective_L"]
-            win = min(runtime["window"], L, runtime["local_cap"]) if (self.linear_use_local and runtime["local_cap"] > 0) else 0
-            slots = 0
-            if self.linear_use_anchors and runtime["anchor_stride"] > 0 and runtime["anchor_cap"] > 0:
-                slots = min(runtime["anchor_cap"], L, max(1, T))
-            pcap = 0
-            if self.linear_use_proto and sim is not None and runtime["proto_cap"] > 0:
-                pcap = min(L, runtime["proto_cap"], T)
             scales = None
             qa, ka, va = q, k, v
             if use_quant:
@@ -759,70 +860,49 @@ class AdaptiveSparseAttention(nn.Module):
                 ka, s_k = ops.quantize_int8(k, amax[1].contiguous())
                 va, s_v = ops.quantize_int8(v, amax[2].contiguous())
                 scales = (s_q, s_k, s_v)
-            tok_used = token_idx[:total_rows] if total_rows < token_idx.numel() else token_idx
-            if max(win, 1) + slots + pcap <= L:
+            if plan_args is not None:
+                win, slots, pcap = plan_args
                 lists = limits = None
                 if pcap > 0:
                     lists, limits = ops.proto_plan(self._last_token_similarity.contiguous(), pcap)
                 plan = ops.make_plan(win, slots, runtime["anchor_stride"], pcap, lists, limits)
-                attention_packed(qa, ka, va, row_offsets=row_offsets, token_idx=tok_used, max_rows=max_rows_est,
+                attention_packed(qa, ka, va, row_offsets=row_offsets, token_idx=token_idx, max_rows=max_rows,
                                  total_rows=total_rows, H=H, scales=scales, plan=plan, out=out,
                                  out_layout=N.OUT_TOKEN_MAJOR)
                 path = "planned"
-            else:  # the candidate pieces can overflow L: use the exact table builder
-                rows64 = tok_used.to(torch.int64)
+            else:  # the candidate pieces can overflow L: use the exact table builder (needs exact row counts)
+                L = runtime["effective_L"]
+                tok_used = token_idx[:total_rows]
                 counts_t = (row_offsets[1:] - row_offsets[:-1]).long()
+                use_p = self.linear_use_proto and sim is not None and runtime["proto_cap"] > 0
                 bids = None
-                if pcap > 0:
-                    bids = torch.repeat_interleave(torch.arange(nbh, device=dev) // H, counts_t, output_size=total_rows)
+                if use_p:
+                    bids = torch.repeat_interleave(torch.arange(B * H, device=dev) // H, counts_t, output_size=total_rows)
                 cand, lens = ops.build_candidates(
-                    rows64, bids, T, L, linear_window=runtime["window"], anchor_stride=runtime["anchor_stride"],
-                    use_local=self.linear_use_local, use_anchors=self.linear_use_anchors,
-                    proto_scores=self._last_token_similarity.contiguous() if pcap > 0 else None,
+                    tok_used.to(torch.int64), bids, T, L, linear_window=runtime["window"],
+                    anchor_stride=runtime["anchor_stride"], use_local=self.linear_use_local,
+                    use_anchors=self.linear_use_anchors,
+                    proto_scores=self._last_token_similarity.contiguous() if use_p else None,
                     local_cap=runtime["local_cap"], anchor_cap=runtime["anchor_cap"], proto_cap=runtime["proto_cap"])
-                attention_packed(qa, ka, va, row_offsets=row_offsets, token_idx=tok_used, max_rows=max_rows_est,
+                attention_packed(qa, ka, va, row_offsets=row_offsets, token_idx=tok_used, max_rows=max_rows,
                                  total_rows=total_rows, H=H, scales=scales, cand=cand, cand_len=lens, out=out,
                                  out_layout=N.OUT_TOKEN_MAJOR)
                 path = "table"
-            _record_backend(BACKEND_NAME, device=str(dev), heads=nbh, tokens=T, max_rows=int(max_rows_est),
+            _record_backend(BACKEND_NAME, device=str(dev), heads=B * H, tokens=T, max_rows=int(max_rows),
                             quantized=bool(use_quant), candidates=path)
             self._last_shortlist_backend_info = get_last_backend_info()
-            exec_mode = "shortlist"
-            active_heads = [i for i, c in enumerate(counts) if c > 0]
-            state = dict(common_state, mode="shortlist", backend=BACKEND_NAME, max_rows=int(max_rows_est),
-                         cache_hit=False, token_idx=tok_used, row_offsets_all=row_offsets,
-                         active_head_indices=torch.tensor(active_heads, dtype=torch.long, device=dev),
-                         row_offsets=torch.tensor([offs_host[i] for i in active_heads] + [total_rows], dtype=torch.int32, device=dev),
-                         linear_L=int(self.linear_L), linear_window=int(self.linear_window),
-                         linear_anchor_stride=int(self.linear_anchor_stride), linear_shortlist_backend=BACKEND_NAME)
-            self._last_sparse_state = state
 
         self.last_head_consensus = None if self.training else out
         y = self.dropout(self.proj(out))
 
-        # 7. telemetry from the host record
-        n_tok = float(B * T)
-        denom = max(float(total_rows), 1.0)
-        unique_heads = len({i % H for i, c in enumerate(counts) if c > 0})
-        stats = {
-            "top_k": int(topk), "mean_gate_prob": float(score_sum / denom), "router_entropy": float(entropy_sum / n_tok),
-            "mean_active_per_token": float(total_rows / n_tok), "unique_heads": int(unique_heads),
-            "active_fraction": float(total_rows / (n_tok * H)), "max_active_rows": int(max_rows_est),
-            "max_active_density": float(density_est), "target_k": int(self._last_target_k or topk), "seq_len": int(T),
-            "active_min": int(self.h_active_min), "active_max": int(self.h_active_max),
-            "force_dense_threshold": None if density_threshold is None else float(density_threshold),
-            "active_curve": float(self.h_active_curve), "token_keep_fraction": float(token_keep_fraction),
-            "mode": exec_mode, "mode_selected": f"cvt(alpha={alpha:.2f})", "shortlist_alpha": float(alpha),
-            "router_top_p": float(self.router_top_p), "nucleus_k": int(adaptive_topk), "top_a_consensus": True}
-        if dense_reason is not None:
-            stats["dense_reason"] = dense_reason
-        if alpha > 0.0:
-            stats.update(linear_L=int(self.linear_L), linear_window=int(self.linear_window),
-                         linear_anchor_stride=int(self.linear_anchor_stride), linear_shortlist_backend=BACKEND_NAME)
-        if self._last_proto_stats:
-            stats["proto"] = dict(self._last_proto_stats)
-            stats["dna"] = dict(self._last_proto_stats)
-        self.last_head_stats = stats
+        # 7. telemetry
+        if lazy:
+            ctx["lazy"] = True
+            self.__dict__["_head_stats_value"] = None
+            self.__dict__["_sparse_state_value"] = None
+            self.__dict__["_pending"] = ctx
+        else:
+            self._publish(ctx, info, force_dense=force_dense, dense_reason=dense_reason, exec_mode=exec_mode)
         self.last_router_reg = self._router_regulariser(gate, B, T) if self.router_reg_lambda > 0.0 else None
         self._top_head_indices, self._top_head_scores = top_idx.view(B, T, -1), top_score.view(B, T, -1)
         self._last_gate_probs = gate.view(B, T, G)
@@ -830,11 +910,24 @@ class AdaptiveSparseAttention(nn.Module):
         # 8. prototype EMA (runs in eval mode too, aspa.py:1917); a decay of exactly 1 leaves the state untouched
         if use_proto and self.routing_usage_ema is not None and self.routing_confidence is not None \
                 and self.proto_decay != 1.0:
-            upd = ops.proto_ema_update(x2d, gate, self.proto_decay, self.routing_prototypes, self.routing_usage_ema,
-                                       self.routing_confidence)
-            self._last_proto_updated = upd
-        self._finalize_latency(f"cvt(alpha={alpha:.2f})::{exec_mode}", ev0, t_start)
+            self._last_proto_updated = ops.proto_ema_update(x2d, gate, self.proto_decay, self.routing_prototypes,
+                                                            self.routing_usage_ema, self.routing_confidence)
+        mode_now = self.__dict__["_sparse_state_value"]["mode"] if not lazy else "shortlist"
+        self._finalize_latency(f"cvt(alpha={alpha:.2f})::{mode_now if force_dense else exec_mode}", ev0, t_start, ctx if lazy else None)
         return y
+
+    def _plan_shape(self, runtime: dict, T: int, have_sim: bool) -> Optional[Tuple[int, int, int]]:
+        """(window, anchor slots, prototype cap) of the structural plan, or None when the candidate pieces could
+        exceed L — then only the explicit table reproduces the reference's "keep the L smallest" cut."""
+        L = runtime["effective_L"]
+        win = min(runtime["window"], L, runtime["local_cap"]) if (self.linear_use_local and runtime["local_cap"] > 0) else 0
+        slots = 0
+        if self.linear_use_anchors and runtime["anchor_stride"] > 0 and runtime["anchor_cap"] > 0:
+            slots = min(runtime["anchor_cap"], L, max(1, T))
+        pcap = 0
+        if self.linear_use_proto and have_sim and runtime["proto_cap"] > 0:
+            pcap = min(L, runtime["proto_cap"], T)
+        return (win, slots, pcap) if max(win, 1) + slots + pcap <= L else None
 
     def _router_regulariser(self, gate: torch.Tensor, B: int, T: int) -> Optional[torch.Tensor]:
         parts = {p.strip() for p in str(self.router_reg_mode or "").lower().replace("|", ",").replace("+", ",").split(",")
@@ -851,7 +944,7 @@ class AdaptiveSparseAttention(nn.Module):
             total = total + t_
         return self.router_reg_lambda * total
 
-    def _finalize_latency(self, label: str, ev0, t_start) -> Optional[float]:
+    def _finalize_latency(self, label: str, ev0, t_start, lazy_ctx: Optional[dict] = None) -> Optional[float]:
         latency = None
         if self.track_latency and ev0 is not None:
             ev1 = torch.cuda.Event(enable_timing=True)
@@ -859,13 +952,19 @@ class AdaptiveSparseAttention(nn.Module):
             ev1.synchronize()
             latency = float(ev0.elapsed_time(ev1))
             self._latency_ema = latency if self._latency_ema is None else 0.8 * self._latency_ema + 0.2 * latency
-        for d in (self.last_head_stats, self._last_sparse_state):
+        if lazy_ctx is not None:
+            lazy_ctx["label"] = label
+            if latency is None:
+                return None
+            self._materialize()
+        for d in (self.__dict__.get("_head_stats_value"), self.__dict__.get("_sparse_state_value")):
             if d is not None:
                 if latency is not None:
                     d["latency_ms"] = latency
                 d["mode_selected"] = label
-        if self.last_head_stats is not None:
-            self.last_head_stats["mode_setting"] = self.mode_setting
+        hs = self.__dict__.get("_head_stats_value")
+        if hs is not None:
+            hs["mode_setting"] = self.mode_setting
         return latency
 
 

@@ -141,6 +141,7 @@ class ChunkedShortlistConfig:
     pass1_full_forward: bool = True      # False: pass 1 runs only router + token keep (its attention output is unused)
     warmup: bool = True                  # the reference's untimed warm-up forward on noise (:583-589)
     collect_summaries: bool = True       # build per-chunk python lists after the loop
+    use_cuda_graph: bool = False         # replay pass 1's per-chunk layer call from a captured CUDA graph
 
     def validate(self) -> None:
         if self.seq_len <= 0:
@@ -180,7 +181,8 @@ class _ChunkFeeder:
         if not self.on_device:
             self.copy_stream = torch.cuda.Stream(device=device)
             shape = (1, chunk_len, source.size(2))
-            self.stage = [torch.empty(shape, dtype=source.dtype, pin_memory=True) for _ in range(2)]
+            self.pinned_source = source.is_pinned()  # pinned input uploads straight from the caller's buffer
+            self.stage = [] if self.pinned_source else [torch.empty(shape, dtype=source.dtype, pin_memory=True) for _ in range(2)]
             self.dev = [torch.empty(shape, dtype=source.dtype, device=device) for _ in range(2)]
             self.ready = [torch.cuda.Event() for _ in range(2)]
             self.consumed = [torch.cuda.Event() for _ in range(2)]
@@ -188,11 +190,15 @@ class _ChunkFeeder:
 
     def _issue(self, slot: int, start: int, end: int) -> None:
         n = end - start
-        self.ready[slot].synchronize()  # the previous upload out of this pinned buffer has finished
-        self.stage[slot][:, :n].copy_(self.src[:, start - self.off:end - self.off])
+        if self.pinned_source:
+            host = self.src[:, start - self.off:end - self.off]
+        else:
+            self.ready[slot].synchronize()  # the previous upload out of this pinned buffer has finished
+            self.stage[slot][:, :n].copy_(self.src[:, start - self.off:end - self.off])
+            host = self.stage[slot][:, :n]
         with torch.cuda.stream(self.copy_stream):
             self.copy_stream.wait_event(self.consumed[slot])
-            self.dev[slot][:, :n].copy_(self.stage[slot][:, :n], non_blocking=True)
+            self.dev[slot][:, :n].copy_(host, non_blocking=True)
             self.ready[slot].record(self.copy_stream)
 
     def get(self, i: int, start: int, end: int, nxt: Optional[Tuple[int, int]]) -> torch.Tensor:
@@ -243,6 +249,29 @@ class ChunkedShortlistRunner:
         if self._layer_cache is not None:
             self._layer_cache[key] = layer
         return layer
+
+    def _chunk_graph(self, layer: AdaptiveSparseAttention, dtype: torch.dtype):
+        """(graph, static input) for one full chunk of pass 1.  The layer call is launch-bound (about 45 small
+        launches around two GEMMs), so replaying a captured graph removes the host from the loop.  Capture needs a
+        call that never waits for the host, which holds for the chunk layer (alpha = 1, no keep threshold)."""
+        cfg = self.config
+        key = ("graph", cfg.chunk_len, dtype, cfg.pass1_full_forward)
+        cache = self._layer_cache if self._layer_cache is not None else self.__dict__.setdefault("_graph_tmp", {})
+        if key in cache:
+            return cache[key]
+        static_x = torch.zeros(1, cfg.chunk_len, cfg.d_model, device=cfg.device, dtype=dtype)
+        side = torch.cuda.Stream(device=cfg.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):  # eager warm-up on a side stream, as graph capture requires
+            for _ in range(2):
+                layer(static_x) if cfg.pass1_full_forward else self._score_only(layer, static_x)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize(cfg.device)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            layer(static_x) if cfg.pass1_full_forward else self._score_only(layer, static_x)
+        cache[key] = (g, static_x)
+        return cache[key]
 
     @staticmethod
     def _score_only(layer: AdaptiveSparseAttention, x: torch.Tensor) -> None:
@@ -338,9 +367,13 @@ class ChunkedShortlistRunner:
         t0 = time.perf_counter()
         ev_a.record()
         bounds = [(c * cfg.chunk_len, min(cfg.seq_len, (c + 1) * cfg.chunk_len)) for c in range(c_lo, c_hi)]
+        graph = self._chunk_graph(chunk_model, base_dtype) if cfg.use_cuda_graph else None
         for i, (start, end) in enumerate(bounds):
             xc = feeder.get(i, start, end, bounds[i + 1] if i + 1 < len(bounds) else None)
-            if cfg.pass1_full_forward:
+            if graph is not None and end - start == cfg.chunk_len:
+                graph[1].copy_(xc, non_blocking=True)   # the graph reads its own static input buffer
+                graph[0].replay()
+            elif cfg.pass1_full_forward:
                 chunk_model(xc)
             else:
                 self._score_only(chunk_model, xc)

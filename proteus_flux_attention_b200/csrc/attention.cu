@@ -555,8 +555,17 @@ extern "C" int aspa_gather_attn_fwd(const void* q, const void* k, const void* v,
   p.scale = 1.0f / sqrtf((float)D);
   p.ws_m = p.ws_l = p.ws_o = nullptr;
 
-  const bool tensor_ok = D == WK_D && (qkv_dtype == ASPA_BF16 || qkv_dtype == ASPA_I8) && cand == nullptr &&
-                         add_mask == nullptr;
+  bool tensor_ok = D == WK_D && (qkv_dtype == ASPA_BF16 || qkv_dtype == ASPA_I8) && cand == nullptr &&
+                   add_mask == nullptr;
+  if (tensor_ok && p.has_plan) {
+    // The tile pass streams the union key range of 16 consecutive rows (about 16*gap + window keys, gap = mean
+    // token distance between the rows of a head); a per-row gather reads 16*window.  With very sparse rows the
+    // union is mostly keys nobody attends to and the CTA count drops below the SM count: gather instead.
+    // total_rows may be a host-side upper bound, which only makes the estimate of the gap conservative.
+    const double gap = (double)T * (double)heads / (double)total_rows;
+    const double window = plan->window > 0 ? plan->window : 1;
+    if (16.0 * gap >= 7.0 * window) tensor_ok = false;
+  }
   if (tensor_ok) {
     const bool extras = p.has_plan && ((plan->anchor_slots > 0 && plan->anchor_stride > 0) ||
                                        (plan->proto_cap > 0 && plan->proto_lists != nullptr));

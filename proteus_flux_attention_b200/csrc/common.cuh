@@ -113,4 +113,51 @@ __device__ __forceinline__ int block_exclusive_scan(int v, int* warp_tot, int* t
   return res;
 }
 
+// ---- selection on keys held in registers ---------------------------------------------------------------
+// Block-wide sum of one int per thread (blockDim.x multiple of 32, <= 1024); `tmp` is 33 ints of shared memory.
+__device__ __forceinline__ int block_sum_int(int v, int* tmp) {
+  v = warp_sum_int(v);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __syncthreads();
+  if (lane == 0) tmp[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    int w = lane < (int)(blockDim.x >> 5) ? tmp[lane] : 0;
+    w = warp_sum_int(w);
+    if (lane == 0) tmp[32] = w;
+  }
+  __syncthreads();
+  return tmp[32];
+}
+
+// The need-th largest (1-based) of the block's keys, found bit by bit: 32 rounds of "how many keys >= candidate",
+// no atomics and no histogram, so heavily skewed key distributions cost nothing extra.
+// Thread t holds keys[j] for element j*blockDim.x + t; slots beyond the data must hold 0 and real keys must be > 0.
+template <int EPT>
+__device__ __forceinline__ uint32_t block_kth_largest(const uint32_t (&keys)[EPT], int need, int* tmp) {
+  uint32_t thr = 0;
+  for (int bit = 31; bit >= 0; --bit) {
+    const uint32_t cand = thr | (1u << bit);
+    int c = 0;
+#pragma unroll
+    for (int j = 0; j < EPT; ++j) c += keys[j] >= cand ? 1 : 0;
+    if (block_sum_int(c, tmp) >= need) thr = cand;
+  }
+  return thr;
+}
+
+// Same search with the keys produced on the fly by `key_of(j)` (j = 0..EPT-1), for callers short of registers.
+template <int EPT, typename F>
+__device__ __forceinline__ uint32_t block_kth_largest_fn(F key_of, int need, int* tmp) {
+  uint32_t thr = 0;
+  for (int bit = 31; bit >= 0; --bit) {
+    const uint32_t cand = thr | (1u << bit);
+    int c = 0;
+#pragma unroll
+    for (int j = 0; j < EPT; ++j) c += key_of(j) >= cand ? 1 : 0;
+    if (block_sum_int(c, tmp) >= need) thr = cand;
+  }
+  return thr;
+}
+
 }  // namespace aspa

@@ -286,6 +286,159 @@ __global__ void __launch_bounds__(1024) chunk_select_kernel(const float* __restr
   if (tid == 0) out_count[0] = nvalid;
 }
 
+// Chunk promotion with the whole chunk's keys in registers (T <= 65536, the pipeline's chunk limit): one read of
+// the scores, bit-by-bit threshold search, picks collected in shared memory and sorted there.
+template <int EPT>
+__global__ void __launch_bounds__(1024) chunk_select_regs_kernel(const float* __restrict__ imp,
+                                                                 const uint8_t* __restrict__ mask, int T, int budget,
+                                                                 float top_p, int64_t offset, int P2,
+                                                                 float* __restrict__ out_scores,
+                                                                 int64_t* __restrict__ out_idx,
+                                                                 int32_t* __restrict__ out_count) {
+  extern __shared__ unsigned long long keys64[];  // [P2]
+  __shared__ int tmp[33];
+  __shared__ float redf[33];
+  __shared__ int fill;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int limit = min(budget, T);
+  uint32_t keys[EPT];
+  float mx = -INFINITY;
+  int nfinite = 0;
+#pragma unroll
+  for (int j = 0; j < EPT; ++j) {
+    const int i = j * 1024 + tid;
+    keys[j] = 0;
+    if (i < T) {
+      float raw = imp[i];
+      if (mask && !mask[i]) raw = -INFINITY;
+      const bool fin = isfinite(raw);
+      nfinite += fin ? 1 : 0;
+      const float sc = fin ? raw : -1e9f;
+      mx = fmaxf(mx, sc);
+      keys[j] = max(float_key(sc), 1u);
+    }
+  }
+  if (tid == 0) fill = 0;
+  const int tot_fin = block_sum_int(nfinite, tmp);
+  if (tot_fin == 0 || limit <= 0) {
+    if (tid == 0) out_count[0] = 0;
+    return;
+  }
+  mx = warp_max(mx);
+  if (lane == 0) redf[warp] = mx;
+  __syncthreads();
+  if (tid == 0) {
+    float m = redf[0];
+    for (int w = 1; w < 32; ++w) m = fmaxf(m, redf[w]);
+    redf[32] = m;
+  }
+  __syncthreads();
+  mx = redf[32];
+  float sum = 0.f;
+#pragma unroll
+  for (int j = 0; j < EPT; ++j)
+    if (keys[j] != 0) sum += expf(key_float(keys[j]) - mx);
+  sum = warp_sum(sum);
+  __syncthreads();
+  if (lane == 0) redf[warp] = sum;
+  __syncthreads();
+  if (tid == 0) {
+    float s = 0.f;
+    for (int w = 0; w < 32; ++w) s += redf[w];
+    redf[32] = s;
+  }
+  __syncthreads();
+  sum = redf[32];
+
+  for (int i = tid; i < P2; i += 1024) keys64[i] = ~0ull;
+  const uint32_t thr = block_kth_largest<EPT>(keys, limit, tmp);
+  int gt = 0, eq = 0;
+#pragma unroll
+  for (int j = 0; j < EPT; ++j) {
+    gt += keys[j] > thr ? 1 : 0;
+    eq += keys[j] == thr ? 1 : 0;
+  }
+  const int n_gt = block_sum_int(gt, tmp);
+  const int n_eq = block_sum_int(eq, tmp);
+  const int take = limit - n_gt;
+  const bool all_ties = take >= n_eq;
+  int ties_seen = 0;
+#pragma unroll
+  for (int j = 0; j < EPT; ++j) {
+    const int i = j * 1024 + tid;
+    const bool tie = keys[j] == thr && keys[j] != 0;
+    bool on = keys[j] > thr || (tie && all_ties);
+    if (!all_ties) {
+      int tot;
+      const int rank = block_exclusive_scan(tie ? 1 : 0, tmp, &tot);
+      on = on || (tie && ties_seen + rank < take);
+      ties_seen += tot;
+    }
+    // slot order is irrelevant: the picks are sorted by (score desc, index asc) right below
+    if (on) keys64[atomicAdd(&fill, 1)] = ((unsigned long long)(~keys[j]) << 32) | (unsigned)i;
+  }
+  __syncthreads();
+  bitonic_u64(keys64, P2);
+  int keep = limit;
+  if (top_p < 1.0f) {
+    float running = 0.f;
+    int below = 0;
+    for (int base = 0; base < limit; base += 1024) {
+      const int i = base + tid;
+      float pr = 0.f;
+      if (i < limit) pr = __fdiv_rn(expf(key_float(~(uint32_t)(keys64[i] >> 32)) - mx), sum);
+      float inc = pr;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float t = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += t;
+      }
+      __syncthreads();
+      if (lane == 31) redf[warp] = inc;
+      __syncthreads();
+      if (warp == 0) {
+        const float w = redf[lane];
+        float winc = w;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const float t = __shfl_up_sync(0xffffffffu, winc, o);
+          if (lane >= o) winc += t;
+        }
+        redf[lane] = winc - w;
+        if (lane == 31) redf[32] = winc;
+      }
+      __syncthreads();
+      const float mass = running + redf[warp] + inc;
+      below += block_sum_int((i < limit && mass < top_p) ? 1 : 0, tmp);
+      running += redf[32];
+      __syncthreads();
+    }
+    keep = below;
+    if (keep < T) keep += 1;
+    keep = min(limit, max(1, keep));
+  }
+  int nvalid = 0;
+  for (int base = 0; base < keep; base += 1024) {
+    const int i = base + tid;
+    bool ok = false;
+    int idx = 0;
+    float raw = 0.f;
+    if (i < keep) {
+      idx = (int)(keys64[i] & 0xffffffffu);
+      raw = imp[idx];
+      ok = isfinite(raw) && !(mask && !mask[idx]);
+    }
+    int tv;
+    const int pos = block_exclusive_scan(ok ? 1 : 0, tmp, &tv);
+    if (ok) {
+      out_scores[nvalid + pos] = raw;
+      out_idx[nvalid + pos] = (int64_t)idx + offset;
+    }
+    nvalid += tv;
+  }
+  if (tid == 0) out_count[0] = nvalid;
+}
+
 // ------------------------------------------------------------------------------------------------
 // Global merge
 // ------------------------------------------------------------------------------------------------
@@ -362,6 +515,109 @@ __global__ void __launch_bounds__(1024) merge_select_kernel(const uint32_t* __re
   if (tid == 0) keep_count[0] = written;
 }
 
+// ---- merge with every candidate in registers (n <= 32768) ------------------------------------------------------
+// table64[idx] = min over candidates with that index of (score_key << 32 | position): the representative of a
+// duplicated index is its lowest score (first position on equal scores), found with one atomicMin per candidate.
+__global__ void merge_scatter64_kernel(const float* __restrict__ scores, const int64_t* __restrict__ indices,
+                                       int64_t n, int64_t seq_len, unsigned long long* __restrict__ table) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int64_t idx = indices[i];
+  if (idx < 0 || idx >= seq_len) return;
+  atomicMin(&table[idx], ((unsigned long long)max(float_key(scores[i]), 1u) << 32) | (unsigned)i);
+}
+
+__device__ void bitonic_i32(int* a, int n) {
+  for (int k = 2; k <= n; k <<= 1)
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const int ixj = i ^ j;
+        if (ixj > i) {
+          const int x = a[i], y = a[ixj];
+          if ((x > y) == ((i & k) == 0)) {
+            a[i] = y;
+            a[ixj] = x;
+          }
+        }
+      }
+      __syncthreads();
+    }
+}
+
+template <int EPT>
+__global__ void __launch_bounds__(1024) merge_select_regs_kernel(const float* __restrict__ scores,
+                                                                 const int64_t* __restrict__ indices, int n,
+                                                                 int64_t seq_len,
+                                                                 const unsigned long long* __restrict__ table,
+                                                                 int max_tokens, int P2, int64_t* __restrict__ keep_idx,
+                                                                 float* __restrict__ keep_scores,
+                                                                 int32_t* __restrict__ keep_count) {
+  extern __shared__ int sel[];  // [P2] selected indices
+  __shared__ int tmp[33];
+  __shared__ int fill;
+  const int tid = threadIdx.x;
+  uint32_t keys[EPT];
+  int idxs[EPT];
+  int reps = 0;
+#pragma unroll
+  for (int j = 0; j < EPT; ++j) {
+    const int i = j * 1024 + tid;
+    keys[j] = 0;
+    idxs[j] = 0;
+    if (i < n) {
+      const int64_t idx = indices[i];
+      if (idx >= 0 && idx < seq_len) {
+        const uint32_t k = max(float_key(scores[i]), 1u);
+        if (table[idx] == (((unsigned long long)k << 32) | (unsigned)i)) {
+          keys[j] = k;
+          idxs[j] = (int)idx;
+          ++reps;
+        }
+      }
+    }
+  }
+  if (tid == 0) fill = 0;
+  for (int i = tid; i < P2; i += 1024) sel[i] = 0x7fffffff;
+  const int n_rep = block_sum_int(reps, tmp);
+  const int need = min(max_tokens, n_rep);
+  if (need <= 0) {
+    if (tid == 0) keep_count[0] = 0;
+    return;
+  }
+  uint32_t thr = 0;          // need == n_rep: every representative is kept
+  uint32_t idx_cut = 0;      // among ties at thr: keep indices whose ~idx >= idx_cut
+  bool all_ties = true;
+  if (need < n_rep) {
+    thr = block_kth_largest<EPT>(keys, need, tmp);
+    int gt = 0, eq = 0;
+#pragma unroll
+    for (int j = 0; j < EPT; ++j) {
+      gt += keys[j] > thr ? 1 : 0;
+      eq += keys[j] == thr ? 1 : 0;
+    }
+    const int n_gt = block_sum_int(gt, tmp);
+    const int n_eq = block_sum_int(eq, tmp);
+    const int take = need - n_gt;
+    all_ties = take >= n_eq;
+    if (!all_ties)  // the `take` lowest indices among the ties = the `take` largest complements
+      idx_cut = block_kth_largest_fn<EPT>([&](int j) { return keys[j] == thr ? ~(uint32_t)idxs[j] : 0u; }, take, tmp);
+  }
+#pragma unroll
+  for (int j = 0; j < EPT; ++j) {
+    if (keys[j] == 0) continue;
+    const bool on = keys[j] > thr || (keys[j] == thr && (all_ties || ~(uint32_t)idxs[j] >= idx_cut));
+    if (on) sel[atomicAdd(&fill, 1)] = idxs[j];
+  }
+  __syncthreads();
+  bitonic_i32(sel, P2);
+  const int cnt = fill;
+  for (int i = tid; i < cnt; i += 1024) {
+    keep_idx[i] = sel[i];
+    keep_scores[i] = key_float((uint32_t)(table[sel[i]] >> 32));
+  }
+  if (tid == 0) keep_count[0] = cnt;
+}
+
 }  // namespace aspa
 
 using namespace aspa;
@@ -410,22 +666,53 @@ extern "C" int aspa_chunk_select(const float* importance, const uint8_t* token_m
   while (P2 < std::min(budget, T)) P2 <<= 1;
   const size_t smem = sizeof(unsigned long long) * P2;
   ASPA_CHECK_ARG(smem <= 200 * 1024, "per-chunk budget too large (max 25600)");
-  cudaFuncSetAttribute(chunk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  chunk_select_kernel<<<1, 1024, smem, (cudaStream_t)stream>>>(importance, token_mask, T, budget, top_p, offset, P2,
-                                                              out_scores, out_idx, out_count);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (T <= 16384) {
+    cudaFuncSetAttribute(chunk_select_regs_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    chunk_select_regs_kernel<16><<<1, 1024, smem, st>>>(importance, token_mask, T, budget, top_p, offset, P2, out_scores,
+                                                        out_idx, out_count);
+  } else if (T <= 65536) {
+    cudaFuncSetAttribute(chunk_select_regs_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    chunk_select_regs_kernel<64><<<1, 1024, smem, st>>>(importance, token_mask, T, budget, top_p, offset, P2, out_scores,
+                                                        out_idx, out_count);
+  } else {
+    cudaFuncSetAttribute(chunk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    chunk_select_kernel<<<1, 1024, smem, st>>>(importance, token_mask, T, budget, top_p, offset, P2, out_scores, out_idx,
+                                               out_count);
+  }
   ASPA_CHECK_LAUNCH();
   return ASPA_OK;
 }
 
 extern "C" int aspa_merge_finalise(const float* scores, const int64_t* indices, int64_t n, int64_t seq_len,
-                                   int max_tokens, uint32_t* table, int64_t* keep_idx, float* keep_scores,
+                                   int max_tokens, void* table, int64_t* keep_idx, float* keep_scores,
                                    int32_t* keep_count, void* stream) {
   ASPA_CHECK_ARG(scores && indices && table && keep_idx && keep_scores && keep_count, "null pointer");
   ASPA_CHECK_ARG(n >= 0 && seq_len > 0 && max_tokens > 0, "bad sizes");
   cudaStream_t st = (cudaStream_t)stream;
-  cudaMemsetAsync(table, 0xff, sizeof(uint32_t) * seq_len, st);
-  if (n > 0) merge_scatter_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, st>>>(scores, indices, n, seq_len, table);
-  merge_select_kernel<<<1, 1024, 0, st>>>(table, seq_len, max_tokens, keep_idx, keep_scores, keep_count);
+  if (n > 0 && n <= 32768 && seq_len < (int64_t)1 << 31) {
+    unsigned long long* t64 = reinterpret_cast<unsigned long long*>(table);
+    cudaMemsetAsync(t64, 0xff, sizeof(unsigned long long) * seq_len, st);
+    merge_scatter64_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, st>>>(scores, indices, n, seq_len, t64);
+    int P2 = 2;
+    while (P2 < std::min<int64_t>(n, max_tokens)) P2 <<= 1;
+    const size_t smem = sizeof(int) * P2;
+    if (n <= 4096) {
+      merge_select_regs_kernel<4><<<1, 1024, smem, st>>>(scores, indices, (int)n, seq_len, t64, max_tokens, P2, keep_idx,
+                                                         keep_scores, keep_count);
+    } else {
+      cudaFuncSetAttribute(merge_select_regs_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      merge_select_regs_kernel<32><<<1, 1024, smem, st>>>(scores, indices, (int)n, seq_len, t64, max_tokens, P2, keep_idx,
+                                                          keep_scores, keep_count);
+    }
+    ASPA_CHECK_LAUNCH();
+    return ASPA_OK;
+  }
+  // large candidate sets: 32-bit score table over the sequence, selected by a streaming radix select
+  uint32_t* t32 = reinterpret_cast<uint32_t*>(table);
+  cudaMemsetAsync(t32, 0xff, sizeof(uint32_t) * seq_len, st);
+  if (n > 0) merge_scatter_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, st>>>(scores, indices, n, seq_len, t32);
+  merge_select_kernel<<<1, 1024, 0, st>>>(t32, seq_len, max_tokens, keep_idx, keep_scores, keep_count);
   ASPA_CHECK_LAUNCH();
   return ASPA_OK;
 }

@@ -30,82 +30,99 @@ __device__ __forceinline__ float rope_mix(float a, float c, float rot, float s, 
   return bf ? bf16_round(r) : r;
 }
 
-// One thread moves 8 consecutive channels of one (token, section, head).  E = elements per thread.
+// RoPE + relayout.  A CTA owns ROPE_TPB consecutive tokens of one batch element; thread v of the CTA owns the
+// 16-byte vector v of every one of those tokens, so section / head / channel are computed once and only the token
+// advances in the loop.  bf16 uses packed bf16x2 multiply/add (each rounds to nearest even, like the reference's
+// eager bf16 ops); fp32 keeps separate fp32 multiplies and adds.
+constexpr int ROPE_TPB = 32;
+
+__device__ __forceinline__ uint32_t rope_word_bf16(uint32_t x, float c, float s) {
+  // x = (even, odd) packed; out = x * (c, c) + (-odd, even) * (s, s)
+  const __nv_bfloat162 xv = *reinterpret_cast<const __nv_bfloat162*>(&x);
+  const uint32_t swapped = __byte_perm(x, 0, 0x1032) ^ 0x00008000u;  // (odd, even) with the new low half negated
+  const __nv_bfloat162 rv = *reinterpret_cast<const __nv_bfloat162*>(&swapped);
+  const __nv_bfloat162 cv = __floats2bfloat162_rn(c, c), sv = __floats2bfloat162_rn(s, s);
+  // the _rn forms forbid fusing the multiply into the add: each step rounds on its own, as in the reference
+  const __nv_bfloat162 o = __hadd2_rn(__hmul2_rn(xv, cv), __hmul2_rn(rv, sv));
+  return *reinterpret_cast<const uint32_t*>(&o);
+}
+
 template <typename T>
-__global__ void __launch_bounds__(256) rope_relayout_kernel(const T* __restrict__ qkv, int B, int Tn, int H, int D,
+__global__ void __launch_bounds__(512) rope_relayout_kernel(const T* __restrict__ qkv, int B, int Tn, int H, int D,
                                                             const float* __restrict__ cos_t,
                                                             const float* __restrict__ sin_t, T* __restrict__ q,
                                                             T* __restrict__ k, T* __restrict__ v,
                                                             float* __restrict__ amax) {
-  constexpr int E = 8;
+  constexpr int E = 16 / sizeof(T);  // elements per 16-byte vector: 8 bf16 or 4 fp32
   const int C = H * D;
   const int vec_per_tok = 3 * C / E;
-  const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const int64_t total = (int64_t)B * Tn * vec_per_tok;
-  float local_max = 0.f;
-  int sec = 0, bh = 0;
-  const bool active = gid < total;
-  if (active) {
-    const int64_t bt = gid / vec_per_tok;
-    const int vi = (int)(gid % vec_per_tok);
-    const int ch = vi * E;  // channel inside 3C
-    sec = ch / C;
-    const int c_in = ch % C;
-    const int h = c_in / D, d0 = c_in % D;
-    const int b = (int)(bt / Tn), t = (int)(bt % Tn);
-    bh = b * H + h;
-    float val[E];
-    const T* src = qkv + bt * (3 * (int64_t)C) + ch;
-    if (sizeof(T) == 2) {
-      const uint4 raw = *reinterpret_cast<const uint4*>(src);
-      const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&raw);
+  const int b = blockIdx.y;
+  const int t0 = blockIdx.x * ROPE_TPB;
+  const int t1 = min(Tn, t0 + ROPE_TPB);
+  const int half = D / 2;
+  for (int vi = threadIdx.x; vi < vec_per_tok; vi += blockDim.x) {
+    const int ch = vi * E;
+    const int sec = ch / C;
+    const int c_in = ch - sec * C;
+    const int h = c_in / D, d0 = c_in - h * D;
+    const int bh = b * H + h;
+    const bool rotate = sec < 2 && cos_t != nullptr;
+    const T* src = qkv + ((int64_t)b * Tn + t0) * (3 * (int64_t)C) + ch;
+    T* dst = (sec == 0 ? q : (sec == 1 ? k : v)) + ((int64_t)bh * Tn + t0) * D + d0;
+    const float* cr = cos_t ? cos_t + (int64_t)t0 * half + d0 / 2 : nullptr;
+    const float* sr = sin_t ? sin_t + (int64_t)t0 * half + d0 / 2 : nullptr;
+    float local_max = 0.f;
+#pragma unroll 4
+    for (int t = t0; t < t1; ++t) {
+      uint4 raw = *reinterpret_cast<const uint4*>(src);
+      if (sizeof(T) == 2) {
+        if (rotate) {
+          const float4 c4 = *reinterpret_cast<const float4*>(cr), s4 = *reinterpret_cast<const float4*>(sr);
+          raw.x = rope_word_bf16(raw.x, c4.x, s4.x);
+          raw.y = rope_word_bf16(raw.y, c4.y, s4.y);
+          raw.z = rope_word_bf16(raw.z, c4.z, s4.z);
+          raw.w = rope_word_bf16(raw.w, c4.w, s4.w);
+        }
+        if (amax) {
+          const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
-      for (int i = 0; i < E; ++i) val[i] = __bfloat162float(e[i]);
-    } else {
-      const float4 a = reinterpret_cast<const float4*>(src)[0], c4 = reinterpret_cast<const float4*>(src)[1];
-      val[0] = a.x; val[1] = a.y; val[2] = a.z; val[3] = a.w;
-      val[4] = c4.x; val[5] = c4.y; val[6] = c4.z; val[7] = c4.w;
-    }
-    if (sec < 2 && cos_t != nullptr) {
-      const int half = D / 2;
-      const float* cr = cos_t + (int64_t)t * half + d0 / 2;
-      const float* sr = sin_t + (int64_t)t * half + d0 / 2;
-#pragma unroll
-      for (int i = 0; i < E; i += 2) {
-        const float c = cr[i / 2], s = sr[i / 2];
-        const float ev = val[i], od = val[i + 1];
-        val[i] = rope_mix(ev, c, -od, s, sizeof(T) == 2);
-        val[i + 1] = rope_mix(od, c, ev, s, sizeof(T) == 2);
+          for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(h2[i]);
+            local_max = fmaxf(local_max, fmaxf(fabsf(f.x), fabsf(f.y)));
+          }
+        }
+      } else {
+        float* f = reinterpret_cast<float*>(&raw);
+        if (rotate) {
+          const float2 c2 = *reinterpret_cast<const float2*>(cr), s2 = *reinterpret_cast<const float2*>(sr);
+          const float e0 = f[0], o0 = f[1], e1 = f[2], o1 = f[3];
+          f[0] = rope_mix(e0, c2.x, -o0, s2.x, false);
+          f[1] = rope_mix(o0, c2.x, e0, s2.x, false);
+          f[2] = rope_mix(e1, c2.y, -o1, s2.y, false);
+          f[3] = rope_mix(o1, c2.y, e1, s2.y, false);
+        }
+        if (amax) local_max = fmaxf(fmaxf(fabsf(f[0]), fabsf(f[1])), fmaxf(local_max, fmaxf(fabsf(f[2]), fabsf(f[3]))));
       }
-    }
-    T* dst = (sec == 0 ? q : (sec == 1 ? k : v)) + ((int64_t)bh * Tn + t) * D + d0;
-    if (sizeof(T) == 2) {
-      uint4 raw;
-      __nv_bfloat16* e = reinterpret_cast<__nv_bfloat16*>(&raw);
-#pragma unroll
-      for (int i = 0; i < E; ++i) e[i] = __float2bfloat16_rn(val[i]);
       *reinterpret_cast<uint4*>(dst) = raw;
-    } else {
-      reinterpret_cast<float4*>(dst)[0] = make_float4(val[0], val[1], val[2], val[3]);
-      reinterpret_cast<float4*>(dst)[1] = make_float4(val[4], val[5], val[6], val[7]);
+      src += 3 * (int64_t)C;
+      dst += D;
+      if (cr) { cr += half; sr += half; }
     }
     if (amax) {
-#pragma unroll
-      for (int i = 0; i < E; ++i) local_max = fmaxf(local_max, fabsf(val[i]));
+      // lanes of a warp may belong to different (section, bh) groups: the lowest lane of every group folds in
+      // its peers and issues one atomic (non-negative floats order like their bit patterns)
+      const int key = sec * B * H + bh;
+      const unsigned active = __activemask();
+      const unsigned peers = __match_any_sync(active, key);
+      const int leader = __ffs(peers) - 1;
+      float gm = local_max;
+      for (int l = 0; l < 32; ++l) {
+        if (!((active >> l) & 1u)) continue;
+        const float o = __shfl_sync(active, local_max, l);
+        if ((peers >> l) & 1u) gm = fmaxf(gm, o);
+      }
+      if ((int)(threadIdx.x & 31) == leader) atomicMax(reinterpret_cast<int*>(amax + key), __float_as_int(gm));
     }
-  }
-  if (amax) {
-    // lanes of a warp may belong to different (section, bh) groups: the lowest lane of every group
-    // folds in its peers and issues one atomic (non-negative floats order like their bit patterns)
-    const int key = active ? (sec * B * H + bh) : -1;
-    const unsigned peers = __match_any_sync(0xffffffffu, key);
-    const int leader = __ffs(peers) - 1;
-    float gm = local_max;
-    for (int l = 0; l < 32; ++l) {
-      const float o = __shfl_sync(0xffffffffu, local_max, l);
-      if ((peers >> l) & 1u) gm = fmaxf(gm, o);
-    }
-    if (active && (int)(threadIdx.x & 31) == leader) atomicMax(reinterpret_cast<int*>(amax + key), __float_as_int(gm));
   }
 }
 
@@ -196,14 +213,18 @@ extern "C" int aspa_rope_relayout(const void* qkv, int dtype, int B, int T, int 
   ASPA_CHECK_ARG(B > 0 && T > 0 && H > 0 && D > 0 && D % 8 == 0, "head_dim must be a multiple of 8");
   ASPA_CHECK_ARG(dtype == ASPA_F32 || dtype == ASPA_BF16, "dtype must be fp32 or bf16");
   ASPA_CHECK_ARG((cos_t == nullptr) == (sin_t == nullptr), "cos/sin tables come together");
-  const int64_t total = (int64_t)B * T * (3 * H * D / 8);
-  const unsigned grid = (unsigned)ceil_div(total, 256);
-  if (dtype == ASPA_BF16)
-    rope_relayout_kernel<__nv_bfloat16><<<grid, 256, 0, (cudaStream_t)stream>>>(
+  const dim3 grid((unsigned)ceil_div(T, ROPE_TPB), (unsigned)B);
+  if (dtype == ASPA_BF16) {
+    const int vec = 3 * H * D / 8;
+    const int threads = (int)std::min<int64_t>(512, ceil_div(vec, 32) * 32);
+    rope_relayout_kernel<__nv_bfloat16><<<grid, threads, 0, (cudaStream_t)stream>>>(
         (const __nv_bfloat16*)qkv, B, T, H, D, cos_t, sin_t, (__nv_bfloat16*)q, (__nv_bfloat16*)k, (__nv_bfloat16*)v, amax);
-  else
-    rope_relayout_kernel<float><<<grid, 256, 0, (cudaStream_t)stream>>>((const float*)qkv, B, T, H, D, cos_t, sin_t,
-                                                                       (float*)q, (float*)k, (float*)v, amax);
+  } else {
+    const int vec = 3 * H * D / 4;
+    const int threads = (int)std::min<int64_t>(512, ceil_div(vec, 32) * 32);
+    rope_relayout_kernel<float><<<grid, threads, 0, (cudaStream_t)stream>>>((const float*)qkv, B, T, H, D, cos_t, sin_t,
+                                                                           (float*)q, (float*)k, (float*)v, amax);
+  }
   ASPA_CHECK_LAUNCH();
   return ASPA_OK;
 }

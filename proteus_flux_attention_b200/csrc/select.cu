@@ -99,6 +99,71 @@ __global__ void __launch_bounds__(1024) token_select_kernel(const float* __restr
   if (threadIdx.x == 0) kept[blockIdx.x] = tot;
 }
 
+// Token keep with every key of the batch row held in registers (T <= 1024 * EPT): one pass over HBM, then the
+// threshold search and the marking run out of registers.
+template <int EPT>
+__global__ void __launch_bounds__(1024) token_select_regs_kernel(const float* __restrict__ importance, int T,
+                                                                 int need0, float threshold, int guard,
+                                                                 uint8_t* __restrict__ token_mask,
+                                                                 int32_t* __restrict__ kept) {
+  __shared__ int tmp[33];
+  const float* imp = importance + (int64_t)blockIdx.x * T;
+  uint8_t* out = token_mask + (int64_t)blockIdx.x * T;
+  uint32_t keys[EPT];
+  int above = 0;
+#pragma unroll
+  for (int j = 0; j < EPT; ++j) {
+    const int i = j * 1024 + threadIdx.x;
+    keys[j] = 0;
+    if (i < T) {
+      const float v = imp[i];
+      keys[j] = max(float_key(v), 1u);
+      above += (threshold > 0.f && v >= threshold) ? 1 : 0;
+    }
+  }
+  int need = need0;
+  if (threshold > 0.f) need = max(need, block_sum_int(above, tmp));
+  need = max(need, guard);
+  need = min(max(1, need), T);
+  if (need >= T) {
+    for (int i = threadIdx.x; i < T; i += 1024) out[i] = 1;
+    if (threadIdx.x == 0) kept[blockIdx.x] = T;
+    return;
+  }
+  const uint32_t thr = block_kth_largest<EPT>(keys, need, tmp);
+  int gt = 0, eq = 0;
+#pragma unroll
+  for (int j = 0; j < EPT; ++j) {
+    gt += keys[j] > thr ? 1 : 0;
+    eq += keys[j] == thr ? 1 : 0;
+  }
+  const int n_gt = block_sum_int(gt, tmp);
+  const int n_eq = block_sum_int(eq, tmp);
+  const int take = need - n_gt;           // ties to accept, lowest token index first
+  const bool all_ties = take >= n_eq;
+  int kept_total = 0, ties_seen = 0;
+#pragma unroll
+  for (int j = 0; j < EPT; ++j) {
+    const int i = j * 1024 + threadIdx.x;
+    const bool tie = keys[j] == thr && keys[j] != 0;
+    bool on = keys[j] > thr || (tie && all_ties);
+    if (!all_ties) {  // rare: rank the ties by index (elements of round j precede those of round j+1)
+      int tot;
+      const int rank = block_exclusive_scan(tie ? 1 : 0, tmp, &tot);
+      on = on || (tie && ties_seen + rank < take);
+      ties_seen += tot;
+    }
+    if (i < T) {
+      if (threshold > 0.f && imp[i] >= threshold) on = true;
+      if (i < guard) on = true;
+      out[i] = on ? 1 : 0;
+      kept_total += on ? 1 : 0;
+    }
+  }
+  const int tot = block_sum_int(kept_total, tmp);
+  if (threadIdx.x == 0) kept[blockIdx.x] = tot;
+}
+
 // ---------------------------------------------------------------------------------------------
 // Head budget
 // ---------------------------------------------------------------------------------------------
@@ -343,7 +408,11 @@ extern "C" int aspa_token_select(const float* importance, int B, int T, int need
                                  uint8_t* token_mask, int32_t* kept, void* stream) {
   ASPA_CHECK_ARG(importance && token_mask && kept, "null pointer");
   ASPA_CHECK_ARG(B > 0 && T > 0, "bad sizes");
-  token_select_kernel<<<B, 1024, 0, (cudaStream_t)stream>>>(importance, T, need, threshold, guard, token_mask, kept);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (T <= 4096) token_select_regs_kernel<4><<<B, 1024, 0, st>>>(importance, T, need, threshold, guard, token_mask, kept);
+  else if (T <= 16384) token_select_regs_kernel<16><<<B, 1024, 0, st>>>(importance, T, need, threshold, guard, token_mask, kept);
+  else if (T <= 65536) token_select_regs_kernel<64><<<B, 1024, 0, st>>>(importance, T, need, threshold, guard, token_mask, kept);
+  else token_select_kernel<<<B, 1024, 0, st>>>(importance, T, need, threshold, guard, token_mask, kept);
   ASPA_CHECK_LAUNCH();
   return ASPA_OK;
 }

@@ -74,6 +74,17 @@ def reduce_partials(partials: torch.Tensor, n_series: int) -> torch.Tensor:
     return out
 
 
+USE_TC_ROUTER = True             # bf16 activations take the tcgen05 router when the shape allows
+_ROUTER_STATUS: dict = {}        # device -> int32[1], raised by the tensor-core router if a bounded wait ran out
+
+
+def router_status(device) -> torch.Tensor:
+    key = str(device)
+    if key not in _ROUTER_STATUS:
+        _ROUTER_STATUS[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _ROUTER_STATUS[key]
+
+
 def router_fwd(x2d: torch.Tensor, w_router: torch.Tensor, proto_hat: Optional[torch.Tensor],
                conf_eps: Optional[torch.Tensor], usage_bias: Optional[torch.Tensor], *, temp: float,
                threshold: float, span: float, blend: float, usage_boost: float, want_stats: bool = True):
@@ -88,6 +99,18 @@ def router_fwd(x2d: torch.Tensor, w_router: torch.Tensor, proto_hat: Optional[to
     bs = _empty((n,), torch.float32, dev) if has_proto else None
     ntile = (n + 63) // 64
     partials = _empty((3 * ntile,), torch.float32, dev) if (want_stats and has_proto) else None
+    tc_bytes = 0
+    if USE_TC_ROUTER and x2d.dtype == torch.bfloat16 and n >= 128 and x2d.data_ptr() % 16 == 0:
+        tc_bytes = int(N.lib().aspa_router_tc_scratch_bytes(Cdim, G, int(has_proto)))
+    if tc_bytes > 0:
+        scratch = _empty((tc_bytes,), torch.uint8, dev)
+        with _timed('router_tc', 2, _nb(x2d, w_router, proto_hat, gate, imp, sim, bs)):
+            N.check(N.lib().aspa_router_fwd_tc(
+                N.ptr(x2d), n, Cdim, N.ptr(w_router), G, N.ptr(proto_hat), N.ptr(conf_eps), N.ptr(usage_bias), temp,
+                threshold, span, blend, usage_boost, N.ptr(gate), N.ptr(imp), N.ptr(sim), N.ptr(bs), N.ptr(partials),
+                N.ptr(scratch), N.ptr(router_status(dev)), N.stream()), "router_fwd_tc")
+        stats = reduce_partials(partials, 3) if partials is not None else None
+        return gate, imp, sim, bs, stats
     with _timed('router', 1, _nb(x2d, w_router, proto_hat, gate, imp, sim, bs)):
         N.check(N.lib().aspa_router_fwd(
             N.ptr(x2d), N.dtype_code(x2d.dtype), n, Cdim, N.ptr(w_router), G, N.ptr(proto_hat), N.ptr(conf_eps),
@@ -302,7 +325,7 @@ def chunk_select(importance: torch.Tensor, token_mask: Optional[torch.Tensor], b
 
 def merge_finalise(scores: torch.Tensor, indices: torch.Tensor, seq_len: int, max_tokens: int):
     dev = scores.device
-    table = _empty((seq_len,), torch.int32, dev)
+    table = _empty((seq_len,), torch.int64, dev)
     keep_idx = _empty((max_tokens,), torch.int64, dev)
     keep_sc = _empty((max_tokens,), torch.float32, dev)
     count = _empty((1,), torch.int32, dev)

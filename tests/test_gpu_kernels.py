@@ -429,3 +429,80 @@ def test_gather_rows(dev):
     src = torch.randn(100, 64, device=dev).to(torch.bfloat16)
     idx = torch.tensor([3, 99, 0, 50], device=dev)
     assert torch.equal(ops.gather_rows(src, idx, None, 4), src[idx])
+
+
+# ---------------------------------------------------------------------------------------------- tcgen05 router
+@pytest.mark.parametrize("G,C,n,proto", [(16, 1024, 4096, True), (32, 1024, 1000, True), (16, 128, 300, False),
+                                         (8, 256, 129, True), (32, 512, 128, True)])
+def test_tensor_core_router_equals_cuda_core_router(dev, G, C, n, proto):
+    """The tcgen05/TMEM router must reproduce the CUDA-core router (same epilogue, different accumulation order)."""
+    from proteus_flux_attention_b200 import _native as N
+    from proteus_flux_attention_b200 import ops
+    assert N.lib().aspa_router_tc_scratch_bytes(C, G, int(proto)) > 0
+    g = torch.Generator().manual_seed(G + C + n)
+    x = torch.randn(n, C, generator=g)
+    x[::41] *= 4.0
+    x = x.to(torch.bfloat16).to(dev)
+    w = (torch.randn(G, C, generator=g) * 0.1).to(torch.bfloat16).to(dev)
+    protos = torch.randn(G, C, generator=g)
+    protos[:2] += x[:2].float().cpu() * 2.0
+    ph = ops.normalize_rows(protos.to(dev)) if proto else None
+    conf = (torch.rand(G, generator=g) + 1e-6).to(dev) if proto else None
+    kw = dict(temp=0.2, threshold=0.05, span=0.95, blend=0.6, usage_boost=0.0)
+    ops.router_status(dev).zero_()
+    ops.USE_TC_ROUTER = True
+    try:
+        a = ops.router_fwd(x, w, ph, conf, None, **kw)
+        ops.USE_TC_ROUTER = False
+        b = ops.router_fwd(x, w, ph, conf, None, **kw)
+    finally:
+        ops.USE_TC_ROUTER = True
+    torch.cuda.synchronize()
+    assert int(ops.router_status(dev).cpu()) == 0, "a bounded wait ran out inside the tensor-core router"
+    gate_a, imp_a, sim_a, bs_a, st_a = a
+    gate_b, imp_b, sim_b, bs_b, st_b = b
+    if proto:
+        assert torch.allclose(sim_a, sim_b, atol=2e-6)
+        assert torch.allclose(bs_a, bs_b, atol=1e-5)
+        assert torch.allclose(st_a, st_b, rtol=1e-3, atol=1e-2)
+    # gate probabilities are bf16-rounded: a rounding flip is one bf16 ulp and must be rare
+    d = (gate_a - gate_b).abs()
+    assert float(d.max()) < 1.0 / 64 and float((d > 1e-5).float().mean()) < 2e-3
+    assert float(((imp_a - imp_b).abs() > 1e-5).float().mean()) < 5e-3
+
+
+def test_merge_finalise_large_and_tied(dev):
+    from proteus_flux_attention_b200 import ops
+    g = torch.Generator().manual_seed(77)
+    n, seq_len, keep = 30000, 200000, 9000
+    idx = torch.randint(0, seq_len, (n,), generator=g)
+    sc = (torch.rand(n, generator=g) * 16).round() / 16  # many equal scores: ties go to the lower index
+    want_i, want_s = O.finalise_indices(sc, idx, max_tokens=keep)
+    ki, ks, kc = ops.merge_finalise(sc.to(dev), idx.to(dev), seq_len, keep)
+    cnt = int(kc.cpu())
+    assert cnt == want_i.numel()
+    assert torch.equal(ki.cpu()[:cnt], want_i) and torch.equal(ks.cpu()[:cnt], want_s)
+    # more candidates than the register path holds: streaming path, same answer
+    n2 = 70000
+    idx2 = torch.randint(0, seq_len, (n2,), generator=g)
+    sc2 = torch.rand(n2, generator=g)
+    want_i, want_s = O.finalise_indices(sc2, idx2, max_tokens=keep)
+    ki, ks, kc = ops.merge_finalise(sc2.to(dev), idx2.to(dev), seq_len, keep)
+    assert int(kc.cpu()) == keep and torch.equal(ki.cpu()[:keep], want_i) and torch.equal(ks.cpu()[:keep], want_s)
+
+
+def test_chunk_select_full_chunk_with_ties(dev):
+    from proteus_flux_attention_b200 import ops
+    g = torch.Generator().manual_seed(31)
+    for T, budget, top_p in [(65536, 2048, 0.9), (20000, 512, 0.3), (65536, 4096, 1.0)]:
+        imp = (torch.rand(T, generator=g) * 512).round() / 512  # ties at the cut
+        mask = torch.rand(T, generator=g) > 0.9
+        want = O.select_top_tokens(imp, mask, 5, budget=budget, top_p=top_p)
+        sc = torch.zeros(budget, device=dev)
+        ix = torch.full((budget,), -1, dtype=torch.int64, device=dev)
+        ct = torch.zeros(1, dtype=torch.int32, device=dev)
+        ops.chunk_select(imp.to(dev), mask.to(torch.uint8).to(dev), budget, top_p, 5, sc, ix, ct)
+        n = int(ct.cpu())
+        assert abs(n - want[1].numel()) <= 1  # the nucleus count may move by one when the mass sits on the cut-off
+        m = min(n, want[1].numel())
+        assert torch.equal(ix.cpu()[:m], want[1][:m]) and torch.equal(sc.cpu()[:m], want[0][:m])
