@@ -59,7 +59,7 @@ class ClockSampler:
                     self.rows.append(parts)
             except Exception:
                 pass
-            self.stop.wait(0.2)
+            self.stop.wait(0.05)
 
     def __enter__(self):
         self.thread.start()
@@ -333,11 +333,19 @@ def main():
     ms_per_step = ms / args.steps
     value = wl.tokens / (ms_per_step / 1e3)
 
-    # per-kernel timing over the same steps (separate pass: events between kernels perturb overlap slightly)
+    # per-kernel timing over the same steps (separate pass: events between kernels perturb overlap slightly).
+    # Kernels replayed from a CUDA graph cannot be bracketed by events, so this pass launches them eagerly; it also
+    # gives the launch count of one step (a graph replay launches exactly the kernels that were captured).
+    if hasattr(wl, "runner"):
+        wl.runner.config.use_cuda_graph = False
+    launches0 = ops.LAUNCHES
     ops.start_timing()
     for _ in range(args.steps):
         wl.step()
     kt = ops.stop_timing()
+    launches = ops.LAUNCHES - launches0
+    if hasattr(wl, "runner"):
+        wl.runner.config.use_cuda_graph = True
     top = max(kt.items(), key=lambda kv: kv[1][1]) if kt else None
     peak, peak_kind = peak_hbm()
     roofline = None

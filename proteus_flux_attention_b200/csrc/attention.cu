@@ -98,7 +98,39 @@ __device__ __forceinline__ float dot_row(const T* __restrict__ krow, const float
   return acc;
 }
 
+// Elements moved by one vector load of a value row (16 bytes; 8 bytes for int8).
+template <typename T> struct VecElems { static constexpr int n = 8; };
+template <> struct VecElems<float> { static constexpr int n = 4; };
+
 template <typename T>
+__device__ __forceinline__ void load_vec(const T* p, float (&o)[8]);
+template <>
+__device__ __forceinline__ void load_vec<float>(const float* p, float (&o)[8]) {
+  const float4 f = *reinterpret_cast<const float4*>(p);
+  o[0] = f.x; o[1] = f.y; o[2] = f.z; o[3] = f.w;
+}
+template <>
+__device__ __forceinline__ void load_vec<__nv_bfloat16>(const __nv_bfloat16* p, float (&o)[8]) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(h2[i]);
+    o[2 * i] = f.x;
+    o[2 * i + 1] = f.y;
+  }
+}
+template <>
+__device__ __forceinline__ void load_vec<int8_t>(const int8_t* p, float (&o)[8]) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const int8_t* b = reinterpret_cast<const int8_t*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) o[i] = (float)b[i];
+}
+
+// kVec: head_dim / VecElems is a power of two <= 32, so LPR = that many lanes cover one value row with one vector
+// load each and 32 / LPR candidates are accumulated per step; otherwise lanes stride over the channels one by one.
+template <typename T, bool kVec>
 __global__ void __launch_bounds__(GEN_WARPS * 32) attn_rows_kernel(const AttnParams p) {
   __shared__ float qs_all[GEN_WARPS][GEN_MAXD];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -157,6 +189,10 @@ __global__ void __launch_bounds__(GEN_WARPS * 32) attn_rows_kernel(const AttnPar
   float acc[GEN_MAXD / 32];
 #pragma unroll
   for (int i = 0; i < GEN_MAXD / 32; ++i) acc[i] = 0.f;
+  constexpr int VE = VecElems<T>::n;
+  const int LPR = kVec ? D / VE : 32;          // lanes per value row
+  const int grp = lane / LPR, sub = lane % LPR;
+  const int groups = 32 / LPR;                  // candidates accumulated per step
 
   for (int c0 = v_begin; c0 < n_virtual; c0 += 32) {
     const int c = c0 + lane;
@@ -206,16 +242,37 @@ __global__ void __launch_bounds__(GEN_WARPS * 32) attn_rows_kernel(const AttnPar
 #pragma unroll
     for (int i = 0; i < GEN_MAXD / 32; ++i) acc[i] *= corr;
     const unsigned live = __ballot_sync(0xffffffffu, pr > 0.f);
-    for (unsigned rem = live; rem; rem &= rem - 1) {
-      const int src = __ffs(rem) - 1;
-      const float pc = __shfl_sync(0xffffffffu, pr, src);
-      const int ic = __shfl_sync(0xffffffffu, idx, src);
-      const T* vrow = vh + (int64_t)ic * D;
+    if (kVec) {
+      const unsigned gmask = groups == 32 ? 0xffffffffu : ((1u << groups) - 1u);
+      for (int c0g = 0; c0g < 32; c0g += groups) {
+        if (!((live >> c0g) & gmask)) continue;  // warp-uniform
+        const float pc = __shfl_sync(0xffffffffu, pr, c0g + grp);
+        const int ic = __shfl_sync(0xffffffffu, idx, c0g + grp);
+        if (pc > 0.f) {
+          float vv[8];
+          load_vec<T>(vh + (int64_t)ic * D + sub * VE, vv);
 #pragma unroll
-      for (int i = 0; i < GEN_MAXD / 32; ++i) {
-        const int d = lane + 32 * i;
-        if (d < D) acc[i] = fmaf(pc, ld_as_float<T>(vrow, d), acc[i]);
+          for (int e = 0; e < VE; ++e) acc[e] = fmaf(pc, vv[e], acc[e]);
+        }
       }
+    } else {
+      for (unsigned rem = live; rem; rem &= rem - 1) {
+        const int src = __ffs(rem) - 1;
+        const float pc = __shfl_sync(0xffffffffu, pr, src);
+        const int ic = __shfl_sync(0xffffffffu, idx, src);
+        const T* vrow = vh + (int64_t)ic * D;
+#pragma unroll
+        for (int i = 0; i < GEN_MAXD / 32; ++i) {
+          const int d = lane + 32 * i;
+          if (d < D) acc[i] = fmaf(pc, ld_as_float<T>(vrow, d), acc[i]);
+        }
+      }
+    }
+  }
+  if (kVec) {  // fold the candidate groups together; lanes 0..LPR-1 end up owning channels sub*VE .. sub*VE+VE-1
+    for (int off = LPR; off < 32; off <<= 1) {
+#pragma unroll
+      for (int e = 0; e < VE; ++e) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], off);
     }
   }
 
@@ -226,22 +283,36 @@ __global__ void __launch_bounds__(GEN_WARPS * 32) attn_rows_kernel(const AttnPar
     const float c2 = (m == -INFINITY) ? 0.f : __expf(m - mm);
     const float lt = l1 * c1 + l * c2;
     const float inv = lt > 0.f ? 1.f / lt : 0.f;
+    // the window pass stores raw P.V (no value scale); acc here is raw too
+    if (kVec) {
+      if (lane < LPR) {
 #pragma unroll
-    for (int i = 0; i < GEN_MAXD / 32; ++i) {
-      const int d = lane + 32 * i;
-      if (d < D) {
-        // the window pass stores raw P.V (no value scale); acc here is raw too
-        const float o = (p.ws_o[grow * D + d] * c1 + acc[i] * c2) * inv * vscale;
-        store_out(p, out_index(p, bh, t, d), o);
+        for (int e = 0; e < VE; ++e) {
+          const int d = sub * VE + e;
+          store_out(p, out_index(p, bh, t, d), (p.ws_o[grow * D + d] * c1 + acc[e] * c2) * inv * vscale);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < GEN_MAXD / 32; ++i) {
+        const int d = lane + 32 * i;
+        if (d < D) store_out(p, out_index(p, bh, t, d), (p.ws_o[grow * D + d] * c1 + acc[i] * c2) * inv * vscale);
       }
     }
     return;
   }
   const float inv = l > 0.f ? 1.f / l : 0.f;
+  if (kVec) {
+    if (lane < LPR) {
 #pragma unroll
-  for (int i = 0; i < GEN_MAXD / 32; ++i) {
-    const int d = lane + 32 * i;
-    if (d < D) store_out(p, out_index(p, bh, t, d), acc[i] * inv * vscale);
+      for (int e = 0; e < VE; ++e) store_out(p, out_index(p, bh, t, sub * VE + e), acc[e] * inv * vscale);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < GEN_MAXD / 32; ++i) {
+      const int d = lane + 32 * i;
+      if (d < D) store_out(p, out_index(p, bh, t, d), acc[i] * inv * vscale);
+    }
   }
 }
 
@@ -516,7 +587,11 @@ extern "C" int64_t aspa_attn_workspace_bytes(int64_t total_rows, int D) {
 template <typename T>
 static void launch_generic(const AttnParams& p, int max_rows, cudaStream_t st) {
   const dim3 grid((unsigned)ceil_div(max_rows, GEN_WARPS), p.heads);
-  attn_rows_kernel<T><<<grid, GEN_WARPS * 32, 0, st>>>(p);
+  constexpr int VE = VecElems<T>::n;
+  const int lpr = p.D % VE == 0 ? p.D / VE : 0;
+  const bool vec = lpr >= 1 && lpr <= 32 && (lpr & (lpr - 1)) == 0;
+  if (vec) attn_rows_kernel<T, true><<<grid, GEN_WARPS * 32, 0, st>>>(p);
+  else attn_rows_kernel<T, false><<<grid, GEN_WARPS * 32, 0, st>>>(p);
 }
 template <typename T>
 static void launch_window(const AttnParams& p, int max_rows, cudaStream_t st) {

@@ -287,7 +287,8 @@ __global__ void __launch_bounds__(1024) chunk_select_kernel(const float* __restr
 }
 
 // Chunk promotion with the whole chunk's keys in registers (T <= 65536, the pipeline's chunk limit): one read of
-// the scores, bit-by-bit threshold search, picks collected in shared memory and sorted there.
+// the scores, bit-by-bit threshold search, picks placed in shared memory by a block scan and sorted there.
+// Thread t owns tokens [t*EPT, (t+1)*EPT), so index order is thread order.
 template <int EPT>
 __global__ void __launch_bounds__(1024) chunk_select_regs_kernel(const float* __restrict__ imp,
                                                                  const uint8_t* __restrict__ mask, int T, int budget,
@@ -298,27 +299,43 @@ __global__ void __launch_bounds__(1024) chunk_select_regs_kernel(const float* __
   extern __shared__ unsigned long long keys64[];  // [P2]
   __shared__ int tmp[33];
   __shared__ float redf[33];
-  __shared__ int fill;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int limit = min(budget, T);
+  const int base = tid * EPT;
   uint32_t keys[EPT];
   float mx = -INFINITY;
   int nfinite = 0;
+  const bool vec_ok = (T % 4 == 0) && (EPT % 4 == 0);
 #pragma unroll
-  for (int j = 0; j < EPT; ++j) {
-    const int i = j * 1024 + tid;
-    keys[j] = 0;
-    if (i < T) {
-      float raw = imp[i];
-      if (mask && !mask[i]) raw = -INFINITY;
-      const bool fin = isfinite(raw);
-      nfinite += fin ? 1 : 0;
-      const float sc = fin ? raw : -1e9f;
-      mx = fmaxf(mx, sc);
-      keys[j] = max(float_key(sc), 1u);
+  for (int j = 0; j < EPT; j += 4) {
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    uint32_t mw = 0x01010101u;
+    if (vec_ok && base + j + 3 < T) {
+      const float4 f = *reinterpret_cast<const float4*>(imp + base + j);
+      v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+      if (mask) mw = *reinterpret_cast<const uint32_t*>(mask + base + j);
+    } else {
+      mw = 0;
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (base + j + e < T) {
+          v[e] = imp[base + j + e];
+          mw |= ((!mask || mask[base + j + e]) ? 1u : 0u) << (8 * e);
+        }
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      keys[j + e] = 0;
+      if (base + j + e < T) {
+        const float raw = ((mw >> (8 * e)) & 0xffu) ? v[e] : -INFINITY;
+        const bool fin = isfinite(raw);
+        nfinite += fin ? 1 : 0;
+        const float sc = fin ? raw : -1e9f;
+        mx = fmaxf(mx, sc);
+        keys[j + e] = max(float_key(sc), 1u);
+      }
     }
   }
-  if (tid == 0) fill = 0;
   const int tot_fin = block_sum_int(nfinite, tmp);
   if (tot_fin == 0 || limit <= 0) {
     if (tid == 0) out_count[0] = 0;
@@ -359,23 +376,26 @@ __global__ void __launch_bounds__(1024) chunk_select_regs_kernel(const float* __
     eq += keys[j] == thr ? 1 : 0;
   }
   const int n_gt = block_sum_int(gt, tmp);
-  const int n_eq = block_sum_int(eq, tmp);
   const int take = limit - n_gt;
-  const bool all_ties = take >= n_eq;
-  int ties_seen = 0;
+  int n_eq;
+  int tie_rank = block_exclusive_scan(eq, tmp, &n_eq);
+  // how many picks this thread contributes, then its first slot (slot order does not matter: sorted below)
+  int mine = 0;
+  {
+    int tr = tie_rank;
+#pragma unroll
+    for (int j = 0; j < EPT; ++j) {
+      if (keys[j] > thr) ++mine;
+      else if (keys[j] == thr && keys[j] != 0) mine += (tr++ < take) ? 1 : 0;
+    }
+  }
+  int total_picks;
+  int slot = block_exclusive_scan(mine, tmp, &total_picks);
 #pragma unroll
   for (int j = 0; j < EPT; ++j) {
-    const int i = j * 1024 + tid;
-    const bool tie = keys[j] == thr && keys[j] != 0;
-    bool on = keys[j] > thr || (tie && all_ties);
-    if (!all_ties) {
-      int tot;
-      const int rank = block_exclusive_scan(tie ? 1 : 0, tmp, &tot);
-      on = on || (tie && ties_seen + rank < take);
-      ties_seen += tot;
-    }
-    // slot order is irrelevant: the picks are sorted by (score desc, index asc) right below
-    if (on) keys64[atomicAdd(&fill, 1)] = ((unsigned long long)(~keys[j]) << 32) | (unsigned)i;
+    bool on = keys[j] > thr;
+    if (keys[j] == thr && keys[j] != 0) on = tie_rank++ < take;
+    if (on) keys64[slot++] = ((unsigned long long)(~keys[j]) << 32) | (unsigned)(base + j);
   }
   __syncthreads();
   bitonic_u64(keys64, P2);
@@ -383,8 +403,8 @@ __global__ void __launch_bounds__(1024) chunk_select_regs_kernel(const float* __
   if (top_p < 1.0f) {
     float running = 0.f;
     int below = 0;
-    for (int base = 0; base < limit; base += 1024) {
-      const int i = base + tid;
+    for (int b0 = 0; b0 < limit; b0 += 1024) {
+      const int i = b0 + tid;
       float pr = 0.f;
       if (i < limit) pr = __fdiv_rn(expf(key_float(~(uint32_t)(keys64[i] >> 32)) - mx), sum);
       float inc = pr;
@@ -418,8 +438,8 @@ __global__ void __launch_bounds__(1024) chunk_select_regs_kernel(const float* __
     keep = min(limit, max(1, keep));
   }
   int nvalid = 0;
-  for (int base = 0; base < keep; base += 1024) {
-    const int i = base + tid;
+  for (int b0 = 0; b0 < keep; b0 += 1024) {
+    const int i = b0 + tid;
     bool ok = false;
     int idx = 0;
     float raw = 0.f;
@@ -554,7 +574,6 @@ __global__ void __launch_bounds__(1024) merge_select_regs_kernel(const float* __
                                                                  int32_t* __restrict__ keep_count) {
   extern __shared__ int sel[];  // [P2] selected indices
   __shared__ int tmp[33];
-  __shared__ int fill;
   const int tid = threadIdx.x;
   uint32_t keys[EPT];
   int idxs[EPT];
@@ -576,7 +595,6 @@ __global__ void __launch_bounds__(1024) merge_select_regs_kernel(const float* __
       }
     }
   }
-  if (tid == 0) fill = 0;
   for (int i = tid; i < P2; i += 1024) sel[i] = 0x7fffffff;
   const int n_rep = block_sum_int(reps, tmp);
   const int need = min(max_tokens, n_rep);
@@ -602,15 +620,21 @@ __global__ void __launch_bounds__(1024) merge_select_regs_kernel(const float* __
     if (!all_ties)  // the `take` lowest indices among the ties = the `take` largest complements
       idx_cut = block_kth_largest_fn<EPT>([&](int j) { return keys[j] == thr ? ~(uint32_t)idxs[j] : 0u; }, take, tmp);
   }
+  // slot of each pick from a block scan of per-thread counts (the order inside `sel` is irrelevant: sorted below)
+  int mine = 0;
+#pragma unroll
+  for (int j = 0; j < EPT; ++j)
+    mine += (keys[j] != 0 && (keys[j] > thr || (keys[j] == thr && (all_ties || ~(uint32_t)idxs[j] >= idx_cut)))) ? 1 : 0;
+  int cnt;
+  int slot = block_exclusive_scan(mine, tmp, &cnt);
 #pragma unroll
   for (int j = 0; j < EPT; ++j) {
     if (keys[j] == 0) continue;
     const bool on = keys[j] > thr || (keys[j] == thr && (all_ties || ~(uint32_t)idxs[j] >= idx_cut));
-    if (on) sel[atomicAdd(&fill, 1)] = idxs[j];
+    if (on) sel[slot++] = idxs[j];
   }
   __syncthreads();
   bitonic_i32(sel, P2);
-  const int cnt = fill;
   for (int i = tid; i < cnt; i += 1024) {
     keep_idx[i] = sel[i];
     keep_scores[i] = key_float((uint32_t)(table[sel[i]] >> 32));

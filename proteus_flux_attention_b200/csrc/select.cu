@@ -99,8 +99,9 @@ __global__ void __launch_bounds__(1024) token_select_kernel(const float* __restr
   if (threadIdx.x == 0) kept[blockIdx.x] = tot;
 }
 
-// Token keep with every key of the batch row held in registers (T <= 1024 * EPT): one pass over HBM, then the
-// threshold search and the marking run out of registers.
+// Token keep with every key of the batch row held in registers (T <= 1024 * EPT).  Thread t owns the EPT
+// consecutive tokens [t*EPT, (t+1)*EPT): index order is thread order, so ranking tied keys by index takes one
+// block scan.  One pass over HBM, then the threshold search and the marking run out of registers.
 template <int EPT>
 __global__ void __launch_bounds__(1024) token_select_regs_kernel(const float* __restrict__ importance, int T,
                                                                  int need0, float threshold, int guard,
@@ -109,16 +110,26 @@ __global__ void __launch_bounds__(1024) token_select_regs_kernel(const float* __
   __shared__ int tmp[33];
   const float* imp = importance + (int64_t)blockIdx.x * T;
   uint8_t* out = token_mask + (int64_t)blockIdx.x * T;
+  const int base = threadIdx.x * EPT;
   uint32_t keys[EPT];
   int above = 0;
+  const bool vec_ok = (T % 4 == 0) && (EPT % 4 == 0);
 #pragma unroll
-  for (int j = 0; j < EPT; ++j) {
-    const int i = j * 1024 + threadIdx.x;
-    keys[j] = 0;
-    if (i < T) {
-      const float v = imp[i];
-      keys[j] = max(float_key(v), 1u);
-      above += (threshold > 0.f && v >= threshold) ? 1 : 0;
+  for (int j = 0; j < EPT; j += 4) {
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (vec_ok && base + j + 3 < T) {
+      const float4 f = *reinterpret_cast<const float4*>(imp + base + j);
+      v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (base + j + e < T) v[e] = imp[base + j + e];
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const bool in = base + j + e < T;
+      keys[j + e] = in ? max(float_key(v[e]), 1u) : 0u;
+      above += (in && threshold > 0.f && v[e] >= threshold) ? 1 : 0;
     }
   }
   int need = need0;
@@ -138,26 +149,36 @@ __global__ void __launch_bounds__(1024) token_select_regs_kernel(const float* __
     eq += keys[j] == thr ? 1 : 0;
   }
   const int n_gt = block_sum_int(gt, tmp);
-  const int n_eq = block_sum_int(eq, tmp);
-  const int take = need - n_gt;           // ties to accept, lowest token index first
-  const bool all_ties = take >= n_eq;
-  int kept_total = 0, ties_seen = 0;
+  const int take = need - n_gt;  // ties to accept, lowest token index first
+  int n_eq;
+  int tie_rank = block_exclusive_scan(eq, tmp, &n_eq);  // ties owned by lower threads = ties at lower indices
+  int kept_total = 0;
+  const float thr_f = threshold;
 #pragma unroll
-  for (int j = 0; j < EPT; ++j) {
-    const int i = j * 1024 + threadIdx.x;
-    const bool tie = keys[j] == thr && keys[j] != 0;
-    bool on = keys[j] > thr || (tie && all_ties);
-    if (!all_ties) {  // rare: rank the ties by index (elements of round j precede those of round j+1)
-      int tot;
-      const int rank = block_exclusive_scan(tie ? 1 : 0, tmp, &tot);
-      on = on || (tie && ties_seen + rank < take);
-      ties_seen += tot;
+  for (int j = 0; j < EPT; j += 4) {
+    uint32_t packed = 0;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int i = base + j + e;
+      const uint32_t k = keys[j + e];
+      bool on = k > thr;
+      if (k == thr && k != 0) {
+        on = tie_rank < take;
+        ++tie_rank;
+      }
+      if (i < T) {
+        if (thr_f > 0.f && key_float(k) >= thr_f) on = true;
+        if (i < guard) on = true;
+        kept_total += on ? 1 : 0;
+        packed |= (on ? 1u : 0u) << (8 * e);
+      }
     }
-    if (i < T) {
-      if (threshold > 0.f && imp[i] >= threshold) on = true;
-      if (i < guard) on = true;
-      out[i] = on ? 1 : 0;
-      kept_total += on ? 1 : 0;
+    if (base + j + 3 < T && (T % 4 == 0)) {
+      *reinterpret_cast<uint32_t*>(out + base + j) = packed;
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (base + j + e < T) out[base + j + e] = (uint8_t)((packed >> (8 * e)) & 1u);
     }
   }
   const int tot = block_sum_int(kept_total, tmp);
