@@ -152,9 +152,12 @@ int aspa_rope_table(const float* inv_freq, int T, int D, int dtype, float* cos_t
  * Replaces _apply_rope_embedding (aspa.py:606-618) and the permutes (aspa.py:1644-1656).
  *   qkv (B, T, 3*H*D) of dtype; q,k,v (B*H, T, D) same dtype out
  *   cos_t/sin_t NULL = no rotation; amax (3, B*H) fp32 in/out or NULL: running max |.| of q,k,v
- *   per bh (caller zeroes it), feeding the INT8 quantiser. */
+ *   per bh (caller zeroes it), feeding the INT8 quantiser.
+ *   q_keep (B, T) uint8 or NULL: when given, the query rows of tokens with q_keep == 0 are skipped (their q is
+ *   left unwritten); only tokens that survive the token keep ever act as queries (aspa.py:1594-1598). */
 int aspa_rope_relayout(const void* qkv, int dtype, int B, int T, int H, int D, const float* cos_t,
-                       const float* sin_t, void* q, void* k, void* v, float* amax, void* stream);
+                       const float* sin_t, void* q, void* k, void* v, float* amax, const uint8_t* q_keep,
+                       void* stream);
 
 /* max |x| per head of a (heads, T*D) tensor (aspa.py:1328). amax is overwritten. */
 int aspa_head_amax(const void* x, int dtype, int heads, int64_t per_head, float* amax, void* stream);

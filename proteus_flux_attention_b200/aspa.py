@@ -522,13 +522,15 @@ class AdaptiveSparseAttention(nn.Module):
             self._identity_pack = {key: hit}
         return hit
 
-    def _project_qkv(self, x: torch.Tensor, want_amax: bool = False):
+    def _project_qkv(self, x: torch.Tensor, want_amax: bool = False, q_keep: Optional[torch.Tensor] = None):
         B, T, _ = x.shape
         qkv = self.qkv(x)
         cos = sin = None
         if self.use_rope:
             cos, sin = self._rope_factors(T, x.device, x.dtype)
-        return ops.rope_relayout(qkv.contiguous(), self.h_total, self.d_head, cos, sin, want_amax)
+        return ops.rope_relayout(qkv.contiguous(), self.h_total, self.d_head, cos, sin, want_amax,
+                                 None if want_amax else q_keep,
+                                 q_fraction=float(self._token_keep_ratio_runtime or 1.0))
 
     def _check_input(self, x: torch.Tensor) -> None:
         if not x.is_cuda:
@@ -788,7 +790,9 @@ class AdaptiveSparseAttention(nn.Module):
 
         # 5. projection + RoPE + head-major relayout (does not depend on the record)
         use_quant = bool(self.quantize_sparse_int8 and not self.training)
-        q, k, v, amax = self._project_qkv(x, want_amax=use_quant and self.quantize_sparse_int8_mode == "max")
+        # queries of dropped tokens are never used (every path below computes rows of kept tokens only)
+        q, k, v, amax = self._project_qkv(x, want_amax=use_quant and self.quantize_sparse_int8_mode == "max",
+                                          q_keep=None if use_quant else token_mask_u8)
 
         # The mode decision needs row counts — unless alpha >= 0.95, where the reference never goes dense
         # (aspa.py:1636-1639): then the call runs without waiting for the record, on host-side bounds.

@@ -130,19 +130,35 @@ __device__ __forceinline__ int block_sum_int(int v, int* tmp) {
   return tmp[32];
 }
 
+// Block-wide sum with ONE barrier: hardware warp reduction, one shared slot per warp, every warp re-reduces the
+// slots.  `buf` holds 64 ints; `parity` (a register of the caller, uniform across the block) alternates between
+// its two halves so that a slot is never overwritten before every warp has read it.
+__device__ __forceinline__ int block_sum_1bar(int v, int* buf, int& parity) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  v = __reduce_add_sync(0xffffffffu, v);
+  int* b = buf + (parity ? 32 : 0);
+  parity ^= 1;
+  if (lane == 0) b[warp] = v;
+  __syncthreads();
+  return __reduce_add_sync(0xffffffffu, lane < nwarp ? b[lane] : 0);
+}
+
 // The need-th largest (1-based) of the block's keys, found bit by bit: 32 rounds of "how many keys >= candidate",
 // no atomics and no histogram, so heavily skewed key distributions cost nothing extra.
-// Thread t holds keys[j] for element j*blockDim.x + t; slots beyond the data must hold 0 and real keys must be > 0.
+// Thread t holds EPT keys; unused slots must hold 0 and real keys must be > 0.  `tmp` holds 64 ints.
 template <int EPT>
 __device__ __forceinline__ uint32_t block_kth_largest(const uint32_t (&keys)[EPT], int need, int* tmp) {
   uint32_t thr = 0;
+  int parity = 0;
+  __syncthreads();
   for (int bit = 31; bit >= 0; --bit) {
     const uint32_t cand = thr | (1u << bit);
     int c = 0;
 #pragma unroll
     for (int j = 0; j < EPT; ++j) c += keys[j] >= cand ? 1 : 0;
-    if (block_sum_int(c, tmp) >= need) thr = cand;
+    if (block_sum_1bar(c, tmp, parity) >= need) thr = cand;
   }
+  __syncthreads();
   return thr;
 }
 
@@ -150,13 +166,16 @@ __device__ __forceinline__ uint32_t block_kth_largest(const uint32_t (&keys)[EPT
 template <int EPT, typename F>
 __device__ __forceinline__ uint32_t block_kth_largest_fn(F key_of, int need, int* tmp) {
   uint32_t thr = 0;
+  int parity = 0;
+  __syncthreads();
   for (int bit = 31; bit >= 0; --bit) {
     const uint32_t cand = thr | (1u << bit);
     int c = 0;
 #pragma unroll
     for (int j = 0; j < EPT; ++j) c += key_of(j) >= cand ? 1 : 0;
-    if (block_sum_int(c, tmp) >= need) thr = cand;
+    if (block_sum_1bar(c, tmp, parity) >= need) thr = cand;
   }
+  __syncthreads();
   return thr;
 }
 

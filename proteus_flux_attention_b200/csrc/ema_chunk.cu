@@ -297,7 +297,7 @@ __global__ void __launch_bounds__(1024) chunk_select_regs_kernel(const float* __
                                                                  int64_t* __restrict__ out_idx,
                                                                  int32_t* __restrict__ out_count) {
   extern __shared__ unsigned long long keys64[];  // [P2]
-  __shared__ int tmp[33];
+  __shared__ int tmp[64];
   __shared__ float redf[33];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int limit = min(budget, T);
@@ -573,7 +573,7 @@ __global__ void __launch_bounds__(1024) merge_select_regs_kernel(const float* __
                                                                  float* __restrict__ keep_scores,
                                                                  int32_t* __restrict__ keep_count) {
   extern __shared__ int sel[];  // [P2] selected indices
-  __shared__ int tmp[33];
+  __shared__ int tmp[64];
   const int tid = threadIdx.x;
   uint32_t keys[EPT];
   int idxs[EPT];

@@ -52,7 +52,8 @@ __global__ void __launch_bounds__(512) rope_relayout_kernel(const T* __restrict_
                                                             const float* __restrict__ cos_t,
                                                             const float* __restrict__ sin_t, T* __restrict__ q,
                                                             T* __restrict__ k, T* __restrict__ v,
-                                                            float* __restrict__ amax) {
+                                                            float* __restrict__ amax,
+                                                            const uint8_t* __restrict__ q_keep) {
   constexpr int E = 16 / sizeof(T);  // elements per 16-byte vector: 8 bf16 or 4 fp32
   const int C = H * D;
   const int vec_per_tok = 3 * C / E;
@@ -72,8 +73,15 @@ __global__ void __launch_bounds__(512) rope_relayout_kernel(const T* __restrict_
     const float* cr = cos_t ? cos_t + (int64_t)t0 * half + d0 / 2 : nullptr;
     const float* sr = sin_t ? sin_t + (int64_t)t0 * half + d0 / 2 : nullptr;
     float local_max = 0.f;
+    const uint8_t* keep = (sec == 0 && q_keep != nullptr) ? q_keep + (int64_t)b * Tn : nullptr;
 #pragma unroll 4
     for (int t = t0; t < t1; ++t) {
+      if (keep != nullptr && !keep[t]) {  // queries of dropped tokens are never read: neither load nor store them
+        src += 3 * (int64_t)C;
+        dst += D;
+        if (cr) { cr += half; sr += half; }
+        continue;
+      }
       uint4 raw = *reinterpret_cast<const uint4*>(src);
       if (sizeof(T) == 2) {
         if (rotate) {
@@ -208,22 +216,24 @@ extern "C" int aspa_rope_table(const float* inv_freq, int T, int D, int dtype, f
 }
 
 extern "C" int aspa_rope_relayout(const void* qkv, int dtype, int B, int T, int H, int D, const float* cos_t,
-                                  const float* sin_t, void* q, void* k, void* v, float* amax, void* stream) {
+                                  const float* sin_t, void* q, void* k, void* v, float* amax,
+                                  const uint8_t* q_keep, void* stream) {
   ASPA_CHECK_ARG(qkv && q && k && v, "null pointer");
   ASPA_CHECK_ARG(B > 0 && T > 0 && H > 0 && D > 0 && D % 8 == 0, "head_dim must be a multiple of 8");
   ASPA_CHECK_ARG(dtype == ASPA_F32 || dtype == ASPA_BF16, "dtype must be fp32 or bf16");
   ASPA_CHECK_ARG((cos_t == nullptr) == (sin_t == nullptr), "cos/sin tables come together");
+  ASPA_CHECK_ARG(!(amax && q_keep), "per-head amax needs every query: do not combine it with q_keep");
   const dim3 grid((unsigned)ceil_div(T, ROPE_TPB), (unsigned)B);
   if (dtype == ASPA_BF16) {
     const int vec = 3 * H * D / 8;
     const int threads = (int)std::min<int64_t>(512, ceil_div(vec, 32) * 32);
     rope_relayout_kernel<__nv_bfloat16><<<grid, threads, 0, (cudaStream_t)stream>>>(
-        (const __nv_bfloat16*)qkv, B, T, H, D, cos_t, sin_t, (__nv_bfloat16*)q, (__nv_bfloat16*)k, (__nv_bfloat16*)v, amax);
+        (const __nv_bfloat16*)qkv, B, T, H, D, cos_t, sin_t, (__nv_bfloat16*)q, (__nv_bfloat16*)k, (__nv_bfloat16*)v, amax, q_keep);
   } else {
     const int vec = 3 * H * D / 4;
     const int threads = (int)std::min<int64_t>(512, ceil_div(vec, 32) * 32);
     rope_relayout_kernel<float><<<grid, threads, 0, (cudaStream_t)stream>>>((const float*)qkv, B, T, H, D, cos_t, sin_t,
-                                                                           (float*)q, (float*)k, (float*)v, amax);
+                                                                           (float*)q, (float*)k, (float*)v, amax, q_keep);
   }
   ASPA_CHECK_LAUNCH();
   return ASPA_OK;

@@ -107,7 +107,7 @@ __global__ void __launch_bounds__(1024) token_select_regs_kernel(const float* __
                                                                  int need0, float threshold, int guard,
                                                                  uint8_t* __restrict__ token_mask,
                                                                  int32_t* __restrict__ kept) {
-  __shared__ int tmp[33];
+  __shared__ int tmp[64];
   const float* imp = importance + (int64_t)blockIdx.x * T;
   uint8_t* out = token_mask + (int64_t)blockIdx.x * T;
   const int base = threadIdx.x * EPT;
@@ -376,7 +376,7 @@ __global__ void __launch_bounds__(PK_SEG) pack_count_kernel(const void* __restri
 __global__ void __launch_bounds__(1024) pack_scan_kernel(int32_t* __restrict__ seg_counts, int64_t n_entries,
                                                          int nseg, int32_t* __restrict__ row_offsets, int n_heads) {
   // single CTA, in-place exclusive scan; row_offsets[bh] = scanned value at (bh, seg 0)
-  __shared__ int tmp[33];
+  __shared__ int tmp[64];
   int running = 0;
   for (int64_t base = 0; base < n_entries; base += blockDim.x) {
     const int64_t i = base + threadIdx.x;

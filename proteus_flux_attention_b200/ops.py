@@ -193,16 +193,17 @@ def rope_table(inv_freq: torch.Tensor, T: int, D: int, dtype: torch.dtype):
 
 
 def rope_relayout(qkv: torch.Tensor, H: int, D: int, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
-                  want_amax: bool = False):
+                  want_amax: bool = False, q_keep: Optional[torch.Tensor] = None, q_fraction: float = 1.0):
     B, T, _ = qkv.shape
     dev = qkv.device
     q = _empty((B * H, T, D), qkv.dtype, dev)
     k = torch.empty_like(q)
     v = torch.empty_like(q)
     amax = torch.zeros((3, B * H), dtype=torch.float32, device=dev) if want_amax else None
-    with _timed('rope_relayout', 1, _nb(qkv, q, k, v)):
+    frac = (2.0 + (q_fraction if q_keep is not None else 1.0)) / 3.0  # share of the buffers that is actually moved
+    with _timed('rope_relayout', 1, int(frac * _nb(qkv, q, k, v))):
         N.check(N.lib().aspa_rope_relayout(N.ptr(qkv), N.dtype_code(qkv.dtype), B, T, H, D, N.ptr(cos), N.ptr(sin),
-                                           N.ptr(q), N.ptr(k), N.ptr(v), N.ptr(amax), N.stream()), "rope_relayout")
+                                           N.ptr(q), N.ptr(k), N.ptr(v), N.ptr(amax), N.ptr(q_keep), N.stream()), "rope_relayout")
     return q, k, v, amax
 
 

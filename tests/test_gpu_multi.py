@@ -1,0 +1,77 @@
+"""Two-GPU test of the sharded chunked pipeline: ranks own disjoint chunk ranges, exchange promotion
+records and kept rows with NCCL all-gather, and must reproduce the single-GPU result bit for bit.
+Skipped when fewer than two CUDA devices are visible.  NVLS is switched off for the child processes."""
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _states():
+    import proteus_flux_attention_b200 as P
+    from proteus_flux_attention_b200.chunked_shortlist import _build_model_config
+    torch.manual_seed(5)
+    a = P.AdaptiveSparseAttention(_build_model_config(2048, 256, heads=4, sparse_ratio=0.05, shortlist_alpha=1.0, router_top_p=0.9))
+    b = P.AdaptiveSparseAttention(_build_model_config(320, 256, heads=4, sparse_ratio=0.5, shortlist_alpha=1.0, router_top_p=0.9))
+    return ({k: v.to(torch.bfloat16) if v.dtype == torch.float32 and "routing" not in k else v for k, v in a.state_dict().items()},
+            {k: v.to(torch.bfloat16) if v.dtype == torch.float32 and "routing" not in k else v for k, v in b.state_dict().items()})
+
+
+def _cfg(dev):
+    import proteus_flux_attention_b200 as P
+    return P.ChunkedShortlistConfig(seq_len=5 * 2048, d_model=256, chunk_len=2048, buffer_tokens=320, per_chunk_budget=64,
+                                    device=dev, heads=4, freeze_prototypes=True, warmup=False)
+
+
+def _worker(rank, world, port, q):
+    import torch.distributed as dist
+    import proteus_flux_attention_b200 as P
+    from proteus_flux_attention_b200 import distributed as D
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        cs, fs = _states()
+        seq = torch.randn(1, 5 * 2048, 256, generator=torch.Generator().manual_seed(9)).to(torch.bfloat16)
+        lo, hi = D.partition_chunks(5, world, rank)
+        shard = seq[:, lo * 2048: hi * 2048].to(dev)
+        res = P.ChunkedShortlistRunner(_cfg(dev), process_group=dist.group.WORLD).run(
+            shard, chunk_state=cs, final_state=fs, sequence_is_local_shard=True)
+        q.put((rank, res.keep_indices.clone(), res.final_output.float().cpu(), res.reduced_sequence.float().cpu()))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gpu_sharding_equals_single_gpu():
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs two CUDA devices")
+    import torch.multiprocessing as mp
+    import proteus_flux_attention_b200 as P
+    dev = torch.device("cuda:0")
+    cs, fs = _states()
+    seq = torch.randn(1, 5 * 2048, 256, generator=torch.Generator().manual_seed(9)).to(torch.bfloat16)
+    want = P.ChunkedShortlistRunner(_cfg(dev)).run(seq.to(dev), chunk_state=cs, final_state=fs)
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    for rank, keep, out, red in results:
+        assert torch.equal(keep, want.keep_indices)
+        assert torch.equal(red, want.reduced_sequence.float().cpu())
+        assert torch.equal(out, want.final_output.float().cpu())
