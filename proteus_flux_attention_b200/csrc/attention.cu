@@ -366,11 +366,25 @@ __device__ __forceinline__ uint4 load_chunk<int8_t>(const int8_t* row, int chunk
   return o;
 }
 
-template <typename T>
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
+  // 16-byte asynchronous copy; src_bytes == 0 fills the destination with zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+constexpr int WK_TILE_BYTES = WK_KEYS * 128;  // one 64-key K or V tile in shared memory
+
+// STAGES == 1: tiles are staged through registers (needed for int8, which is widened to bf16 on the way).
+// STAGES >= 2: bf16 tiles arrive by cp.async into a ring of STAGES buffers, one barrier per tile.
+template <typename T, int STAGES>
 __global__ void __launch_bounds__(128) attn_window_kernel(const AttnParams p) {
-  __shared__ __align__(1024) unsigned char q_s[WK_ROWS * 128];
-  __shared__ __align__(1024) unsigned char k_s[WK_KEYS * 128];
-  __shared__ __align__(1024) unsigned char v_s[WK_KEYS * 128];
+  extern __shared__ __align__(1024) unsigned char wk_smem[];
+  unsigned char* q_s = wk_smem;                                   // [64 rows][128 B]
+  unsigned char* kv_s = wk_smem + WK_ROWS * 128;                  // STAGES x (K tile | V tile)
+  unsigned char* k_s = kv_s;
+  unsigned char* v_s = kv_s + WK_TILE_BYTES;
   __shared__ int ts[WK_ROWS];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -432,11 +446,12 @@ __global__ void __launch_bounds__(128) attn_window_kernel(const AttnParams p) {
     for (int e = 0; e < 4; ++e) o[j][e] = 0.f;
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
-  // register prefetch of the first tile
-  uint4 kreg[4], vreg[4];
+  // register prefetch of the first tile (STAGES == 1) / asynchronous ring (STAGES >= 2)
+  uint4 kreg[STAGES == 1 ? 4 : 1], vreg[STAGES == 1 ? 4 : 1];
   auto fetch = [&](int kt) {
+    if (STAGES != 1) return;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < (STAGES == 1 ? 4 : 1); ++i) {
       const int c = tid + 128 * i;
       const int row = c >> 3, ch = c & 7;
       const int key = kt * WK_KEYS + row;
@@ -449,19 +464,48 @@ __global__ void __launch_bounds__(128) attn_window_kernel(const AttnParams p) {
       }
     }
   };
-  fetch(kt_begin);
+  auto issue = [&](int kt) {  // cp.async tile kt into its ring slot; always commits a group (possibly empty)
+    if (kt <= kt_end) {
+      unsigned char* ks_ = kv_s + ((kt - kt_begin) % STAGES) * 2 * WK_TILE_BYTES;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int c = tid + 128 * i;
+        const int row = c >> 3, ch = c & 7;
+        const int key = kt * WK_KEYS + row;
+        const int64_t off = (int64_t)min(key, Tn - 1) * WK_D + ch * 8;
+        const int nbytes = key < Tn ? 16 : 0;
+        cp_async16(smem_u32(ks_ + swz(row, ch)), kh + off, nbytes);
+        cp_async16(smem_u32(ks_ + WK_TILE_BYTES + swz(row, ch)), vh + off, nbytes);
+      }
+    }
+    cp_async_commit();
+  };
+  if (STAGES == 1) {
+    fetch(kt_begin);
+  } else {
+#pragma unroll
+    for (int s_ = 0; s_ < STAGES - 1; ++s_) issue(kt_begin + s_);
+  }
 
   for (int kt = kt_begin; kt <= kt_end; ++kt) {
-    __syncthreads();  // previous tile fully consumed
+    if (STAGES == 1) {
+      __syncthreads();  // previous tile fully consumed
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int c = tid + 128 * i;
-      const int row = c >> 3, ch = c & 7;
-      *reinterpret_cast<uint4*>(k_s + swz(row, ch)) = kreg[i];
-      *reinterpret_cast<uint4*>(v_s + swz(row, ch)) = vreg[i];
+      for (int i = 0; i < (STAGES == 1 ? 4 : 1); ++i) {
+        const int c = tid + 128 * i;
+        const int row = c >> 3, ch = c & 7;
+        *reinterpret_cast<uint4*>(k_s + swz(row, ch)) = kreg[i];
+        *reinterpret_cast<uint4*>(v_s + swz(row, ch)) = vreg[i];
+      }
+      __syncthreads();
+      if (kt < kt_end) fetch(kt + 1);
+    } else {
+      cp_async_wait<(STAGES >= 2 ? STAGES - 2 : 0)>();  // this thread's copies of tile kt have landed
+      __syncthreads();                 // ... everybody's have, and tile kt-1 is no longer being read
+      issue(kt + STAGES - 1);          // refill the slot tile kt-1 occupied
+      k_s = kv_s + ((kt - kt_begin) % STAGES) * 2 * WK_TILE_BYTES;
+      v_s = k_s + WK_TILE_BYTES;
     }
-    __syncthreads();
-    if (kt < kt_end) fetch(kt + 1);
 
     const int kb = kt * WK_KEYS;
     if (w_first < 0 || kb > w_last || kb + WK_KEYS - 1 < w_lo) continue;  // tile outside this warp's rows
@@ -593,10 +637,16 @@ static void launch_generic(const AttnParams& p, int max_rows, cudaStream_t st) {
   if (vec) attn_rows_kernel<T, true><<<grid, GEN_WARPS * 32, 0, st>>>(p);
   else attn_rows_kernel<T, false><<<grid, GEN_WARPS * 32, 0, st>>>(p);
 }
-template <typename T>
+template <typename T, int STAGES>
 static void launch_window(const AttnParams& p, int max_rows, cudaStream_t st) {
   const dim3 grid((unsigned)ceil_div(max_rows, WK_ROWS), p.heads);
-  attn_window_kernel<T><<<grid, 128, 0, st>>>(p);
+  const int smem = WK_ROWS * 128 + STAGES * 2 * WK_TILE_BYTES;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaFuncSetAttribute(attn_window_kernel<T, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    attr_set = true;
+  }
+  attn_window_kernel<T, STAGES><<<grid, 128, smem, st>>>(p);
 }
 
 extern "C" int aspa_gather_attn_fwd(const void* q, const void* k, const void* v, int qkv_dtype, const float* q_scale,
@@ -652,7 +702,7 @@ extern "C" int aspa_gather_attn_fwd(const void* q, const void* k, const void* v,
       p.ws_o = w + 2 * total_rows;
       p.write_partial = 1;
     }
-    if (qkv_dtype == ASPA_BF16) launch_window<__nv_bfloat16>(p, max_rows, st); else launch_window<int8_t>(p, max_rows, st);
+    if (qkv_dtype == ASPA_BF16) launch_window<__nv_bfloat16, 3>(p, max_rows, st); else launch_window<int8_t, 1>(p, max_rows, st);
     ASPA_CHECK_LAUNCH();
     if (extras) {
       p.write_partial = 0;
