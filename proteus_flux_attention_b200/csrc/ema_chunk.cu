@@ -1,5 +1,6 @@
 // Prototype EMA update, chunk promotion (nucleus + top-budget) and the global merge of the chunked
 // shortlist pipeline.
+#include "cluster.cuh"
 #include "common.cuh"
 
 namespace aspa {
@@ -286,28 +287,29 @@ __global__ void __launch_bounds__(1024) chunk_select_kernel(const float* __restr
   if (tid == 0) out_count[0] = nvalid;
 }
 
-// Chunk promotion with the whole chunk's keys in registers (T <= 65536, the pipeline's chunk limit): one read of
-// the scores, bit-by-bit threshold search, picks placed in shared memory by a block scan and sorted there.
-// Thread t owns tokens [t*EPT, (t+1)*EPT), so index order is thread order.
-template <int EPT>
-__global__ void __launch_bounds__(1024) chunk_select_regs_kernel(const float* __restrict__ imp,
-                                                                 const uint8_t* __restrict__ mask, int T, int budget,
-                                                                 float top_p, int64_t offset, int P2,
-                                                                 float* __restrict__ out_scores,
-                                                                 int64_t* __restrict__ out_idx,
-                                                                 int32_t* __restrict__ out_count) {
-  extern __shared__ unsigned long long keys64[];  // [P2]
-  __shared__ int tmp[64];
+// Chunk promotion with the chunk's keys spread over a cluster (8 keys per thread, 8192 tokens per CTA, up to 8
+// CTAs).  Every CTA places its picks straight into the sort buffer of CTA 0 through distributed shared memory;
+// CTA 0 then sorts them, applies the nucleus cut and writes the result.
+__global__ void __launch_bounds__(CL_THREADS) chunk_select_cluster_kernel(const float* __restrict__ imp,
+                                                                          const uint8_t* __restrict__ mask, int T,
+                                                                          int budget, float top_p, int64_t offset,
+                                                                          int P2, float* __restrict__ out_scores,
+                                                                          int64_t* __restrict__ out_idx,
+                                                                          int32_t* __restrict__ out_count) {
+  extern __shared__ unsigned long long keys64[];  // [P2], used in CTA 0
+  __shared__ ClusterScratch cs;
   __shared__ float redf[33];
+  cg::cluster_group cluster = cg::this_cluster();
+  const int rank = (int)cluster.block_rank();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int limit = min(budget, T);
-  const int base = tid * EPT;
-  uint32_t keys[EPT];
-  float mx = -INFINITY;
-  int nfinite = 0;
-  const bool vec_ok = (T % 4 == 0) && (EPT % 4 == 0);
+  const int base = rank * CL_KEYS_PER_CTA + tid * CL_EPT;
+  int parity = 0;
+  uint32_t keys[CL_EPT];
+  uint32_t stat[2] = {0u, 0u};  // finite scores, largest key
+  const bool vec_ok = (T % 4 == 0);
 #pragma unroll
-  for (int j = 0; j < EPT; j += 4) {
+  for (int j = 0; j < CL_EPT; j += 4) {
     float v[4] = {0.f, 0.f, 0.f, 0.f};
     uint32_t mw = 0x01010101u;
     if (vec_ok && base + j + 3 < T) {
@@ -329,81 +331,74 @@ __global__ void __launch_bounds__(1024) chunk_select_regs_kernel(const float* __
       if (base + j + e < T) {
         const float raw = ((mw >> (8 * e)) & 0xffu) ? v[e] : -INFINITY;
         const bool fin = isfinite(raw);
-        nfinite += fin ? 1 : 0;
-        const float sc = fin ? raw : -1e9f;
-        mx = fmaxf(mx, sc);
-        keys[j + e] = max(float_key(sc), 1u);
+        stat[0] += fin ? 1u : 0u;
+        keys[j + e] = max(float_key(fin ? raw : -1e9f), 1u);
+        stat[1] = max(stat[1], keys[j + e]);
       }
     }
   }
-  const int tot_fin = block_sum_int(nfinite, tmp);
-  if (tot_fin == 0 || limit <= 0) {
-    if (tid == 0) out_count[0] = 0;
+  if (rank == 0)
+    for (int i = tid; i < P2; i += CL_THREADS) keys64[i] = ~0ull;
+  {
+    uint32_t fin[1] = {stat[0]}, top[1] = {stat[1]};
+    cluster_reduce<1, OpAdd>(fin, cs, parity);
+    cluster_reduce<1, OpMax>(top, cs, parity);
+    stat[0] = fin[0];
+    stat[1] = top[0];
+  }
+  if (stat[0] == 0u || limit <= 0) {  // uniform over the cluster
+    if (rank == 0 && tid == 0) out_count[0] = 0;
     return;
   }
-  mx = warp_max(mx);
-  if (lane == 0) redf[warp] = mx;
-  __syncthreads();
-  if (tid == 0) {
-    float m = redf[0];
-    for (int w = 1; w < 32; ++w) m = fmaxf(m, redf[w]);
-    redf[32] = m;
-  }
-  __syncthreads();
-  mx = redf[32];
+  const float mx = key_float(stat[1]);
   float sum = 0.f;
 #pragma unroll
-  for (int j = 0; j < EPT; ++j)
+  for (int j = 0; j < CL_EPT; ++j)
     if (keys[j] != 0) sum += expf(key_float(keys[j]) - mx);
-  sum = warp_sum(sum);
-  __syncthreads();
-  if (lane == 0) redf[warp] = sum;
-  __syncthreads();
-  if (tid == 0) {
-    float s = 0.f;
-    for (int w = 0; w < 32; ++w) s += redf[w];
-    redf[32] = s;
-  }
-  __syncthreads();
-  sum = redf[32];
+  sum = cluster_sum_float(sum, cs, parity);
 
-  for (int i = tid; i < P2; i += 1024) keys64[i] = ~0ull;
-  const uint32_t thr = block_kth_largest<EPT>(keys, limit, tmp);
-  int gt = 0, eq = 0;
+  const uint32_t thr = cluster_kth_largest<CL_EPT>(keys, limit, cs, parity);
+  uint32_t ge[2] = {0u, 0u}, lower[2];
 #pragma unroll
-  for (int j = 0; j < EPT; ++j) {
-    gt += keys[j] > thr ? 1 : 0;
-    eq += keys[j] == thr ? 1 : 0;
+  for (int j = 0; j < CL_EPT; ++j) {
+    ge[0] += keys[j] > thr ? 1u : 0u;
+    ge[1] += (keys[j] == thr && keys[j] != 0) ? 1u : 0u;
   }
-  const int n_gt = block_sum_int(gt, tmp);
-  const int take = limit - n_gt;
+  const int my_eq = (int)ge[1];
+  cluster_reduce<2, OpAdd>(ge, cs, parity, lower);
+  const int take = limit - (int)ge[0];
   int n_eq;
-  int tie_rank = block_exclusive_scan(eq, tmp, &n_eq);
-  // how many picks this thread contributes, then its first slot (slot order does not matter: sorted below)
-  int mine = 0;
+  int tie_rank = (int)lower[1] + block_exclusive_scan(my_eq, cs.scan_tmp, &n_eq);
+  // picks of this thread, then their first slot in CTA 0's buffer (slot order is irrelevant: sorted below)
+  uint32_t mine[1] = {0u}, mine_lower[1];
   {
     int tr = tie_rank;
 #pragma unroll
-    for (int j = 0; j < EPT; ++j) {
-      if (keys[j] > thr) ++mine;
-      else if (keys[j] == thr && keys[j] != 0) mine += (tr++ < take) ? 1 : 0;
+    for (int j = 0; j < CL_EPT; ++j) {
+      if (keys[j] > thr) ++mine[0];
+      else if (keys[j] == thr && keys[j] != 0) mine[0] += (tr++ < take) ? 1u : 0u;
     }
   }
-  int total_picks;
-  int slot = block_exclusive_scan(mine, tmp, &total_picks);
+  int cta_picks;
+  const int in_cta = block_exclusive_scan((int)mine[0], cs.scan_tmp, &cta_picks);
+  mine[0] = (tid == 0) ? (uint32_t)cta_picks : 0u;
+  cluster_reduce<1, OpAdd>(mine, cs, parity, mine_lower);
+  int slot = (int)mine_lower[0] + in_cta;
+  unsigned long long* dst = cluster.map_shared_rank(keys64, 0);
 #pragma unroll
-  for (int j = 0; j < EPT; ++j) {
+  for (int j = 0; j < CL_EPT; ++j) {
     bool on = keys[j] > thr;
     if (keys[j] == thr && keys[j] != 0) on = tie_rank++ < take;
-    if (on) keys64[slot++] = ((unsigned long long)(~keys[j]) << 32) | (unsigned)(base + j);
+    if (on && slot < P2) dst[slot++] = ((unsigned long long)(~keys[j]) << 32) | (unsigned)(base + j);
   }
-  __syncthreads();
+  cluster.sync();
+  if (rank != 0) return;
   bitonic_u64(keys64, P2);
   int keep = limit;
   if (top_p < 1.0f) {
     float running = 0.f;
     int below = 0;
-    for (int b0 = 0; b0 < limit; b0 += 1024) {
+    for (int b0 = 0; b0 < limit; b0 += CL_THREADS) {
       const int i = b0 + tid;
       float pr = 0.f;
       if (i < limit) pr = __fdiv_rn(expf(key_float(~(uint32_t)(keys64[i] >> 32)) - mx), sum);
@@ -429,7 +424,9 @@ __global__ void __launch_bounds__(1024) chunk_select_regs_kernel(const float* __
       }
       __syncthreads();
       const float mass = running + redf[warp] + inc;
-      below += block_sum_int((i < limit && mass < top_p) ? 1 : 0, tmp);
+      int nb;
+      block_exclusive_scan((i < limit && mass < top_p) ? 1 : 0, cs.scan_tmp, &nb);
+      below += nb;
       running += redf[32];
       __syncthreads();
     }
@@ -438,7 +435,7 @@ __global__ void __launch_bounds__(1024) chunk_select_regs_kernel(const float* __
     keep = min(limit, max(1, keep));
   }
   int nvalid = 0;
-  for (int b0 = 0; b0 < keep; b0 += 1024) {
+  for (int b0 = 0; b0 < keep; b0 += CL_THREADS) {
     const int i = b0 + tid;
     bool ok = false;
     int idx = 0;
@@ -449,7 +446,7 @@ __global__ void __launch_bounds__(1024) chunk_select_regs_kernel(const float* __
       ok = isfinite(raw) && !(mask && !mask[idx]);
     }
     int tv;
-    const int pos = block_exclusive_scan(ok ? 1 : 0, tmp, &tv);
+    const int pos = block_exclusive_scan(ok ? 1 : 0, cs.scan_tmp, &tv);
     if (ok) {
       out_scores[nvalid + pos] = raw;
       out_idx[nvalid + pos] = (int64_t)idx + offset;
@@ -564,23 +561,28 @@ __device__ void bitonic_i32(int* a, int n) {
     }
 }
 
-template <int EPT>
-__global__ void __launch_bounds__(1024) merge_select_regs_kernel(const float* __restrict__ scores,
-                                                                 const int64_t* __restrict__ indices, int n,
-                                                                 int64_t seq_len,
-                                                                 const unsigned long long* __restrict__ table,
-                                                                 int max_tokens, int P2, int64_t* __restrict__ keep_idx,
-                                                                 float* __restrict__ keep_scores,
-                                                                 int32_t* __restrict__ keep_count) {
-  extern __shared__ int sel[];  // [P2] selected indices
-  __shared__ int tmp[64];
+// Selection over the representatives with the candidates spread over a cluster (8 per thread, 8192 per CTA, up to
+// 8 CTAs).  The picks land in the sort buffer of CTA 0 through distributed shared memory; CTA 0 sorts them by index.
+__global__ void __launch_bounds__(CL_THREADS) merge_select_cluster_kernel(const float* __restrict__ scores,
+                                                                          const int64_t* __restrict__ indices, int n,
+                                                                          int64_t seq_len,
+                                                                          const unsigned long long* __restrict__ table,
+                                                                          int max_tokens, int P2,
+                                                                          int64_t* __restrict__ keep_idx,
+                                                                          float* __restrict__ keep_scores,
+                                                                          int32_t* __restrict__ keep_count) {
+  extern __shared__ int sel[];  // [P2] selected indices, used in CTA 0
+  __shared__ ClusterScratch cs;
+  cg::cluster_group cluster = cg::this_cluster();
+  const int rank = (int)cluster.block_rank();
   const int tid = threadIdx.x;
-  uint32_t keys[EPT];
-  int idxs[EPT];
-  int reps = 0;
+  int parity = 0;
+  uint32_t keys[CL_EPT];
+  int idxs[CL_EPT];
+  uint32_t reps[1] = {0u};
 #pragma unroll
-  for (int j = 0; j < EPT; ++j) {
-    const int i = j * 1024 + tid;
+  for (int j = 0; j < CL_EPT; ++j) {
+    const int i = rank * CL_KEYS_PER_CTA + j * CL_THREADS + tid;
     keys[j] = 0;
     idxs[j] = 0;
     if (i < n) {
@@ -590,52 +592,58 @@ __global__ void __launch_bounds__(1024) merge_select_regs_kernel(const float* __
         if (table[idx] == (((unsigned long long)k << 32) | (unsigned)i)) {
           keys[j] = k;
           idxs[j] = (int)idx;
-          ++reps;
+          ++reps[0];
         }
       }
     }
   }
-  for (int i = tid; i < P2; i += 1024) sel[i] = 0x7fffffff;
-  const int n_rep = block_sum_int(reps, tmp);
+  if (rank == 0)
+    for (int i = tid; i < P2; i += CL_THREADS) sel[i] = 0x7fffffff;
+  cluster_reduce<1, OpAdd>(reps, cs, parity);
+  const int n_rep = (int)reps[0];
   const int need = min(max_tokens, n_rep);
-  if (need <= 0) {
-    if (tid == 0) keep_count[0] = 0;
+  if (need <= 0) {  // uniform over the cluster
+    if (rank == 0 && tid == 0) keep_count[0] = 0;
     return;
   }
-  uint32_t thr = 0;          // need == n_rep: every representative is kept
-  uint32_t idx_cut = 0;      // among ties at thr: keep indices whose ~idx >= idx_cut
+  uint32_t thr = 0;      // need == n_rep: every representative is kept
+  uint32_t idx_cut = 0;  // among ties at thr: keep indices whose complement >= idx_cut
   bool all_ties = true;
   if (need < n_rep) {
-    thr = block_kth_largest<EPT>(keys, need, tmp);
-    int gt = 0, eq = 0;
+    thr = cluster_kth_largest<CL_EPT>(keys, need, cs, parity);
+    uint32_t ge[2] = {0u, 0u};
 #pragma unroll
-    for (int j = 0; j < EPT; ++j) {
-      gt += keys[j] > thr ? 1 : 0;
-      eq += keys[j] == thr ? 1 : 0;
+    for (int j = 0; j < CL_EPT; ++j) {
+      ge[0] += keys[j] > thr ? 1u : 0u;
+      ge[1] += keys[j] == thr ? 1u : 0u;
     }
-    const int n_gt = block_sum_int(gt, tmp);
-    const int n_eq = block_sum_int(eq, tmp);
-    const int take = need - n_gt;
-    all_ties = take >= n_eq;
+    cluster_reduce<2, OpAdd>(ge, cs, parity);
+    const int take = need - (int)ge[0];
+    all_ties = take >= (int)ge[1];
     if (!all_ties)  // the `take` lowest indices among the ties = the `take` largest complements
-      idx_cut = block_kth_largest_fn<EPT>([&](int j) { return keys[j] == thr ? ~(uint32_t)idxs[j] : 0u; }, take, tmp);
+      idx_cut = cluster_kth_largest_fn<CL_EPT>([&](int j) { return keys[j] == thr ? ~(uint32_t)idxs[j] : 0u; }, take, cs,
+                                               parity);
   }
-  // slot of each pick from a block scan of per-thread counts (the order inside `sel` is irrelevant: sorted below)
+  auto picked = [&](int j) {
+    return keys[j] != 0 && (keys[j] > thr || (keys[j] == thr && (all_ties || ~(uint32_t)idxs[j] >= idx_cut)));
+  };
   int mine = 0;
 #pragma unroll
-  for (int j = 0; j < EPT; ++j)
-    mine += (keys[j] != 0 && (keys[j] > thr || (keys[j] == thr && (all_ties || ~(uint32_t)idxs[j] >= idx_cut)))) ? 1 : 0;
-  int cnt;
-  int slot = block_exclusive_scan(mine, tmp, &cnt);
+  for (int j = 0; j < CL_EPT; ++j) mine += picked(j) ? 1 : 0;
+  int cta_picks;
+  const int in_cta = block_exclusive_scan(mine, cs.scan_tmp, &cta_picks);
+  uint32_t tot[1] = {tid == 0 ? (uint32_t)cta_picks : 0u}, lower[1];
+  cluster_reduce<1, OpAdd>(tot, cs, parity, lower);
+  int slot = (int)lower[0] + in_cta;
+  int* dst = cluster.map_shared_rank(sel, 0);
 #pragma unroll
-  for (int j = 0; j < EPT; ++j) {
-    if (keys[j] == 0) continue;
-    const bool on = keys[j] > thr || (keys[j] == thr && (all_ties || ~(uint32_t)idxs[j] >= idx_cut));
-    if (on) sel[slot++] = idxs[j];
-  }
-  __syncthreads();
+  for (int j = 0; j < CL_EPT; ++j)
+    if (picked(j) && slot < P2) dst[slot++] = idxs[j];
+  cluster.sync();
+  if (rank != 0) return;
+  const int cnt = min((int)tot[0], P2);
   bitonic_i32(sel, P2);
-  for (int i = tid; i < cnt; i += 1024) {
+  for (int i = tid; i < cnt; i += CL_THREADS) {
     keep_idx[i] = sel[i];
     keep_scores[i] = key_float((uint32_t)(table[sel[i]] >> 32));
   }
@@ -691,14 +699,16 @@ extern "C" int aspa_chunk_select(const float* importance, const uint8_t* token_m
   const size_t smem = sizeof(unsigned long long) * P2;
   ASPA_CHECK_ARG(smem <= 200 * 1024, "per-chunk budget too large (max 25600)");
   cudaStream_t st = (cudaStream_t)stream;
-  if (T <= 16384) {
-    cudaFuncSetAttribute(chunk_select_regs_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    chunk_select_regs_kernel<16><<<1, 1024, smem, st>>>(importance, token_mask, T, budget, top_p, offset, P2, out_scores,
-                                                        out_idx, out_count);
-  } else if (T <= 65536) {
-    cudaFuncSetAttribute(chunk_select_regs_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    chunk_select_regs_kernel<64><<<1, 1024, smem, st>>>(importance, token_mask, T, budget, top_p, offset, P2, out_scores,
-                                                        out_idx, out_count);
+  if (T <= CL_MAX * CL_KEYS_PER_CTA) {
+    int csize = 1;
+    while (csize * CL_KEYS_PER_CTA < T) csize <<= 1;
+    cudaFuncSetAttribute(chunk_select_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const cudaError_t e = launch_clusters(chunk_select_cluster_kernel, 1, csize, smem, st, importance, token_mask, T, budget,
+                                          top_p, offset, P2, out_scores, out_idx, out_count);
+    if (e != cudaSuccess) {
+      set_error("aspa_chunk_select: cluster launch failed: %s", cudaGetErrorString(e));
+      return ASPA_ERR_CUDA;
+    }
   } else {
     cudaFuncSetAttribute(chunk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     chunk_select_kernel<<<1, 1024, smem, st>>>(importance, token_mask, T, budget, top_p, offset, P2, out_scores, out_idx,
@@ -714,20 +724,21 @@ extern "C" int aspa_merge_finalise(const float* scores, const int64_t* indices, 
   ASPA_CHECK_ARG(scores && indices && table && keep_idx && keep_scores && keep_count, "null pointer");
   ASPA_CHECK_ARG(n >= 0 && seq_len > 0 && max_tokens > 0, "bad sizes");
   cudaStream_t st = (cudaStream_t)stream;
-  if (n > 0 && n <= 32768 && seq_len < (int64_t)1 << 31) {
+  if (n > 0 && n <= CL_MAX * CL_KEYS_PER_CTA && seq_len < (int64_t)1 << 31) {
     unsigned long long* t64 = reinterpret_cast<unsigned long long*>(table);
     cudaMemsetAsync(t64, 0xff, sizeof(unsigned long long) * seq_len, st);
     merge_scatter64_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, st>>>(scores, indices, n, seq_len, t64);
     int P2 = 2;
     while (P2 < std::min<int64_t>(n, max_tokens)) P2 <<= 1;
     const size_t smem = sizeof(int) * P2;
-    if (n <= 4096) {
-      merge_select_regs_kernel<4><<<1, 1024, smem, st>>>(scores, indices, (int)n, seq_len, t64, max_tokens, P2, keep_idx,
-                                                         keep_scores, keep_count);
-    } else {
-      cudaFuncSetAttribute(merge_select_regs_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      merge_select_regs_kernel<32><<<1, 1024, smem, st>>>(scores, indices, (int)n, seq_len, t64, max_tokens, P2, keep_idx,
-                                                          keep_scores, keep_count);
+    int csize = 1;
+    while ((int64_t)csize * CL_KEYS_PER_CTA < n) csize <<= 1;
+    cudaFuncSetAttribute(merge_select_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const cudaError_t e = launch_clusters(merge_select_cluster_kernel, 1, csize, smem, st, scores, indices, (int)n, seq_len,
+                                          (const unsigned long long*)t64, max_tokens, P2, keep_idx, keep_scores, keep_count);
+    if (e != cudaSuccess) {
+      set_error("aspa_merge_finalise: cluster launch failed: %s", cudaGetErrorString(e));
+      return ASPA_ERR_CUDA;
     }
     ASPA_CHECK_LAUNCH();
     return ASPA_OK;

@@ -1,6 +1,7 @@
 // Token keep (radix select), head budget, per-token head top-k and row packing.
 #include <mutex>
 
+#include "cluster.cuh"
 #include "common.cuh"
 
 namespace aspa {
@@ -183,6 +184,102 @@ __global__ void __launch_bounds__(1024) token_select_regs_kernel(const float* __
   }
   const int tot = block_sum_int(kept_total, tmp);
   if (threadIdx.x == 0) kept[blockIdx.x] = tot;
+}
+
+// Token keep with the row's keys spread over a cluster of CTAs (8 keys per thread, 8192 tokens per CTA, up to
+// 8 CTAs): CTA r of the cluster owns tokens [r*8192, (r+1)*8192) and thread t of it the 8 consecutive tokens from
+// r*8192 + t*8, so index order is (rank, thread, slot) order and tied keys rank by one scan.  grid = rows * csize.
+__global__ void __launch_bounds__(CL_THREADS) token_select_cluster_kernel(const float* __restrict__ importance, int T,
+                                                                          int need0, float threshold, int guard,
+                                                                          uint8_t* __restrict__ token_mask,
+                                                                          int32_t* __restrict__ kept) {
+  __shared__ ClusterScratch cs;
+  cg::cluster_group cluster = cg::this_cluster();
+  const int rank = (int)cluster.block_rank(), csize = (int)cluster.num_blocks();
+  const int row = blockIdx.x / csize;
+  const float* imp = importance + (int64_t)row * T;
+  uint8_t* out = token_mask + (int64_t)row * T;
+  const int base = rank * CL_KEYS_PER_CTA + threadIdx.x * CL_EPT;
+  int parity = 0;
+  uint32_t keys[CL_EPT];
+  uint32_t above = 0;
+  const bool vec_ok = (T % 4 == 0);
+#pragma unroll
+  for (int j = 0; j < CL_EPT; j += 4) {
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (vec_ok && base + j + 3 < T) {
+      const float4 f = *reinterpret_cast<const float4*>(imp + base + j);
+      v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (base + j + e < T) v[e] = imp[base + j + e];
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const bool in = base + j + e < T;
+      keys[j + e] = in ? max(float_key(v[e]), 1u) : 0u;
+      above += (in && threshold > 0.f && v[e] >= threshold) ? 1u : 0u;
+    }
+  }
+  int need = need0;
+  if (threshold > 0.f) {
+    uint32_t a[1] = {above};
+    cluster_reduce<1, OpAdd>(a, cs, parity);
+    need = max(need, (int)a[0]);
+  }
+  need = max(need, guard);
+  need = min(max(1, need), T);
+  if (need >= T) {  // uniform over the cluster
+#pragma unroll
+    for (int j = 0; j < CL_EPT; ++j)
+      if (base + j < T) out[base + j] = 1;
+    if (rank == 0 && threadIdx.x == 0) kept[row] = T;
+    return;
+  }
+  const uint32_t thr = cluster_kth_largest<CL_EPT>(keys, need, cs, parity);
+  uint32_t ge[2] = {0u, 0u}, lower[2];
+#pragma unroll
+  for (int j = 0; j < CL_EPT; ++j) {
+    ge[0] += keys[j] > thr ? 1u : 0u;
+    ge[1] += keys[j] == thr ? 1u : 0u;
+  }
+  const int my_eq = (int)ge[1];
+  cluster_reduce<2, OpAdd>(ge, cs, parity, lower);
+  const int take = need - (int)ge[0];  // ties to accept, lowest token index first
+  int n_eq;
+  int tie_rank = (int)lower[1] + block_exclusive_scan(my_eq, cs.scan_tmp, &n_eq);
+  uint32_t kept_total = 0;
+#pragma unroll
+  for (int j = 0; j < CL_EPT; j += 4) {
+    uint32_t packed = 0;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int i = base + j + e;
+      const uint32_t k = keys[j + e];
+      bool on = k > thr;
+      if (k == thr && k != 0) {
+        on = tie_rank < take;
+        ++tie_rank;
+      }
+      if (i < T) {
+        if (threshold > 0.f && key_float(k) >= threshold) on = true;
+        if (i < guard) on = true;
+        kept_total += on ? 1u : 0u;
+        packed |= (on ? 1u : 0u) << (8 * e);
+      }
+    }
+    if (vec_ok && base + j + 3 < T) {
+      *reinterpret_cast<uint32_t*>(out + base + j) = packed;
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (base + j + e < T) out[base + j + e] = (uint8_t)((packed >> (8 * e)) & 1u);
+    }
+  }
+  uint32_t kt[1] = {kept_total};
+  cluster_reduce<1, OpAdd>(kt, cs, parity);
+  if (rank == 0 && threadIdx.x == 0) kept[row] = (int)kt[0];
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -430,10 +527,20 @@ extern "C" int aspa_token_select(const float* importance, int B, int T, int need
   ASPA_CHECK_ARG(importance && token_mask && kept, "null pointer");
   ASPA_CHECK_ARG(B > 0 && T > 0, "bad sizes");
   cudaStream_t st = (cudaStream_t)stream;
-  if (T <= 4096) token_select_regs_kernel<4><<<B, 1024, 0, st>>>(importance, T, need, threshold, guard, token_mask, kept);
-  else if (T <= 16384) token_select_regs_kernel<16><<<B, 1024, 0, st>>>(importance, T, need, threshold, guard, token_mask, kept);
-  else if (T <= 65536) token_select_regs_kernel<64><<<B, 1024, 0, st>>>(importance, T, need, threshold, guard, token_mask, kept);
-  else token_select_kernel<<<B, 1024, 0, st>>>(importance, T, need, threshold, guard, token_mask, kept);
+  if (T <= 4096) {
+    token_select_regs_kernel<4><<<B, 1024, 0, st>>>(importance, T, need, threshold, guard, token_mask, kept);
+  } else if (T <= CL_MAX * CL_KEYS_PER_CTA) {
+    int csize = 1;
+    while (csize * CL_KEYS_PER_CTA < T) csize <<= 1;  // 1, 2, 4 or 8 CTAs; surplus slots hold no keys
+    const cudaError_t e = launch_clusters(token_select_cluster_kernel, B, csize, 0, st, importance, T, need, threshold,
+                                          guard, token_mask, kept);
+    if (e != cudaSuccess) {
+      set_error("aspa_token_select: cluster launch failed: %s", cudaGetErrorString(e));
+      return ASPA_ERR_CUDA;
+    }
+  } else {
+    token_select_kernel<<<B, 1024, 0, st>>>(importance, T, need, threshold, guard, token_mask, kept);
+  }
   ASPA_CHECK_LAUNCH();
   return ASPA_OK;
 }

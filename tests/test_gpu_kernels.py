@@ -78,7 +78,9 @@ def test_router_without_prototypes(dev):
 # ---------------------------------------------------------------------------------------------- selection
 @pytest.mark.parametrize("T,ratio,thr,guard,kmin", [(257, 0.25, 0.0, 1, 0), (4096, 0.05, 0.0, 4, 102),
                                                     (1000, 0.5, 0.7, 2, 0), (64, 0.999, 0.0, 1, 0), (1, 0.3, 0.0, 1, 0),
-                                                    (70000, 0.2, 0.0, 4, 0)])
+                                                    (70000, 0.2, 0.0, 4, 0), (16384, 0.1, 0.0, 4, 0),
+                                                    (65536, 0.05, 0.0, 4, 0), (20001, 0.33, 0.0, 3, 0),
+                                                    (9000, 0.2, 0.7, 2, 0), (40000, 0.01, 0.0, 1, 600)])
 def test_token_select_exact(dev, T, ratio, thr, guard, kmin):
     from proteus_flux_attention_b200 import ops
     from proteus_flux_attention_b200.aspa import _py_round_f32
@@ -482,6 +484,15 @@ def test_merge_finalise_large_and_tied(dev):
     cnt = int(kc.cpu())
     assert cnt == want_i.numel()
     assert torch.equal(ki.cpu()[:cnt], want_i) and torch.equal(ks.cpu()[:cnt], want_s)
+    # every cluster size of the register path
+    for n1 in (5000, 12000, 50000, 65536):
+        idx1 = torch.randint(0, seq_len, (n1,), generator=g)
+        sc1 = (torch.rand(n1, generator=g) * 64).round() / 64
+        want_i, want_s = O.finalise_indices(sc1, idx1, max_tokens=keep)
+        ki, ks, kc = ops.merge_finalise(sc1.to(dev), idx1.to(dev), seq_len, keep)
+        cnt = int(kc.cpu())
+        assert cnt == want_i.numel()
+        assert torch.equal(ki.cpu()[:cnt], want_i) and torch.equal(ks.cpu()[:cnt], want_s)
     # more candidates than the register path holds: streaming path, same answer
     n2 = 70000
     idx2 = torch.randint(0, seq_len, (n2,), generator=g)
@@ -494,7 +505,8 @@ def test_merge_finalise_large_and_tied(dev):
 def test_chunk_select_full_chunk_with_ties(dev):
     from proteus_flux_attention_b200 import ops
     g = torch.Generator().manual_seed(31)
-    for T, budget, top_p in [(65536, 2048, 0.9), (20000, 512, 0.3), (65536, 4096, 1.0)]:
+    for T, budget, top_p in [(65536, 2048, 0.9), (20000, 512, 0.3), (65536, 4096, 1.0), (8192, 100, 0.95),
+                             (33333, 3000, 0.99), (5000, 5000, 1.0)]:
         imp = (torch.rand(T, generator=g) * 512).round() / 512  # ties at the cut
         mask = torch.rand(T, generator=g) > 0.9
         want = O.select_top_tokens(imp, mask, 5, budget=budget, top_p=top_p)
