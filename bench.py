@@ -40,43 +40,68 @@ SEQ_1M, CHUNK, BUDGET, BUFFER, D_MODEL, HEADS = 1 << 20, 65536, 2048, 32768, 102
 
 # ----------------------------------------------------------------------------------------------- helpers
 class ClockSampler:
-    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
-    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+    """SM clock and throttle reasons from one `nvidia-smi -lms` process that runs beside the benchmark (a sampling
+    thread in this process would compete for the interpreter lock with the timed loop).  Start it early - the tool
+    needs a moment before its first line - and mark the timed region with begin()/end(); only samples whose
+    timestamps fall inside that window are summarised."""
+    Q = ("timestamp,clocks.sm,clocks.max.sm,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index: int):
-        self.rows, self.stop, self.index = [], threading.Event(), index
-        self.thread = threading.Thread(target=self._run, daemon=True)
+    def __init__(self, index: int, period_ms: int = 10):
+        import datetime
+        self.dt = datetime
+        self.t0 = self.t1 = None
+        try:
+            gpu = "GPU-" + str(torch.cuda.get_device_properties(index).uuid)
+        except Exception:
+            gpu = str(index)
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", gpu, f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", str(period_ms)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
 
-    def _run(self):
-        while not self.stop.is_set():
-            try:
-                out = subprocess.run(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
-                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
-                parts = [p.strip() for p in out.strip().split(",")]
-                if len(parts) >= 7:
-                    self.rows.append(parts)
-            except Exception:
-                pass
-            self.stop.wait(0.05)
+    def begin(self):
+        self.t0 = self.dt.datetime.now()
 
-    def __enter__(self):
-        self.thread.start()
-        return self
-
-    def __exit__(self, *a):
-        self.stop.set()
-        self.thread.join(timeout=10)
+    def end(self):
+        self.t1 = self.dt.datetime.now()
 
     def summary(self):
-        if not self.rows:
+        if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
-        mhz = [float(r[0]) for r in self.rows if r[0].replace(".", "").isdigit()]
+        time.sleep(0.05)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=10)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        rows, near = [], []
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 8:
+                continue
+            try:
+                ts = self.dt.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f")
+            except ValueError:
+                continue
+            near.append((ts, parts[1:]))
+            if self.t0 is not None and self.t1 is not None and self.t0 <= ts <= self.t1:
+                rows.append(parts[1:])
+        window = "timed region"
+        if not rows and near and self.t0 is not None:  # region shorter than the sampling period: the closest samples
+            near.sort(key=lambda r: abs((r[0] - self.t0).total_seconds()))
+            rows = [r[1] for r in near[:3]]
+            window = "nearest to the timed region"
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        mhz = [float(r[0]) for r in rows if r[0].replace(".", "").isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(r[3 + i].lower().startswith("active") for r in self.rows)]
-        return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": float(self.rows[0][1]),
-                "reasons": reasons, "samples": len(self.rows)}
+        reasons = [n for i, n in enumerate(names) if any(r[3 + i].lower().startswith("active") for r in rows)]
+        return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": float(rows[0][1]),
+                "reasons": reasons, "samples": len(rows), "window": window}
 
 
 def peak_hbm():
@@ -132,8 +157,11 @@ class ChunkedWorkload:
                        "l2": "inputs (2 GiB) larger than L2"}
 
     def step(self):
-        return self.runner.run(self.shard, chunk_state=self.chunk_state, final_state=self.final_state,
-                               sequence_is_local_shard=True)
+        res = self.runner.run(self.shard, chunk_state=self.chunk_state, final_state=self.final_state,
+                              sequence_is_local_shard=True)
+        self.phases_ms = {"pass1_exchange_merge": round(res.metrics.chunk_time_ms, 3),
+                          "gather_pass2": round(res.metrics.final_time_ms, 3)}
+        return res
 
     def step_e2e(self):
         if self.host_shard is None:
@@ -312,20 +340,25 @@ def main():
         if rank == 0:
             print(json.dumps({"profile_mode": True, "workload": args.workload, "passes": args.warmup + args.steps}))
         return
+    clocks = ClockSampler(local_rank)
     for _ in range(max(3, args.warmup)):
         wl.step()
     sync()
-    with ClockSampler(local_rank) as clocks:
-        launches0 = ops.LAUNCHES
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        sync()
-        e0.record()
-        for _ in range(args.steps):
-            wl.step()
-        e1.record()
-        sync()
-        ms = e0.elapsed_time(e1)
-        launches = ops.LAUNCHES - launches0
+    launches0 = ops.LAUNCHES
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync()
+    clocks.begin()
+    e0.record()
+    for _ in range(args.steps):
+        wl.step()
+    e1.record()
+    sync()
+    clocks.end()
+    ms = e0.elapsed_time(e1)
+    launches = ops.LAUNCHES - launches0
+    clock_summary = clocks.summary()
+    if hasattr(wl, "phases_ms"):  # device time of the two halves of the last timed step, on this rank
+        wl.config["phases_ms_last_step"] = wl.phases_ms
     t = torch.tensor([ms], device=device)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -380,7 +413,7 @@ def main():
         print(json.dumps({"metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
                           "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True,
                           "scaling": "strong" if args.workload == "chunked_1m" else "replicas", "vs_baseline": None,
-                          "dtype": "bf16", "data": "synthetic", "config": wl.config, "clocks": clocks.summary(),
+                          "dtype": "bf16", "data": "synthetic", "config": wl.config, "clocks": clock_summary,
                           "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline, "cpu_baseline": cpu}))
     if world > 1:
         dist.destroy_process_group()

@@ -159,6 +159,17 @@ int aspa_rope_relayout(const void* qkv, int dtype, int B, int T, int H, int D, c
                        const float* sin_t, void* q, void* k, void* v, float* amax, const uint8_t* q_keep,
                        void* stream);
 
+/* The same work for a projection that was split in two so that queries are only computed for kept tokens
+ * (no reference counterpart: the reference projects q for every token, aspa.py:1641):
+ *   aspa_rope_relayout_kv: kv (B, T, 2*H*D) -> k (rotated), v, both (B*H, T, D);
+ *   aspa_rope_rows_q: q_rows (max_rows, H*D), row i belonging to token kept_idx[i] (flat b*T + t; rows with
+ *   i >= *count_dev or an index outside [0, B*T) are skipped) -> rotated into q (B*H, T, D). */
+int aspa_rope_relayout_kv(const void* kv, int dtype, int B, int T, int H, int D, const float* cos_t,
+                          const float* sin_t, void* k, void* v, void* stream);
+int aspa_rope_rows_q(const void* q_rows, int dtype, const int64_t* kept_idx, const int32_t* count_dev,
+                     int64_t max_rows, int B, int T, int H, int D, const float* cos_t, const float* sin_t, void* q,
+                     void* stream);
+
 /* max |x| per head of a (heads, T*D) tensor (aspa.py:1328). amax is overwritten. */
 int aspa_head_amax(const void* x, int dtype, int heads, int64_t per_head, float* amax, void* stream);
 
@@ -222,6 +233,17 @@ int aspa_gather_attn_fwd(const void* q, const void* k, const void* v, int qkv_dt
                          const aspa_shortlist_plan* plan, const float* add_mask, void* out, int out_dtype,
                          int out_layout, void* workspace, void* stream);
 
+/* Same call with the token-major output rows redirected: row b*T + t of `out` becomes row
+ * out_row_map[b*T + t] (the compact slot of a kept token, from aspa_compact_mask), so that the output
+ * projection runs over kept tokens only.  No reference counterpart: the reference projects every row,
+ * dropped tokens included (aspa.py:1854).  out_row_map NULL = aspa_gather_attn_fwd. */
+int aspa_gather_attn_fwd_mapped(const void* q, const void* k, const void* v, int qkv_dtype, const float* q_scale,
+                                const float* k_scale, const float* v_scale, int heads, int T, int D, int H,
+                                const int32_t* row_offsets, const int32_t* token_idx, int max_rows,
+                                int64_t total_rows, const int64_t* cand, const int64_t* cand_len, int L,
+                                const aspa_shortlist_plan* plan, const float* add_mask, void* out, int out_dtype,
+                                int out_layout, const int32_t* out_row_map, void* workspace, void* stream);
+
 /* Prototype EMA (aspa.py:692-718): counts = sum_t probs; mean = probs^T x / counts;
  * prototypes, usage and confidence updated in place for gates with counts > 1e-6.
  *   scratch: aspa_proto_ema_scratch() bytes. Returns via updated (1) int32 the number of gates touched. */
@@ -243,14 +265,32 @@ int aspa_chunk_select(const float* importance, const uint8_t* token_mask, int T,
  * best of them, ascending index order.
  *   scores/indices (n): entries with index < 0 are ignored; seq_len bounds the indices
  *   table: scratch of 8 * seq_len bytes; keep_idx (max_tokens) int64, keep_scores (max_tokens) fp32,
- *   keep_count (1) int32 out. */
+ *   keep_count (1) int32 out.  keep_pos (max_tokens) int64 or NULL: position in scores/indices of the
+ *   entry that represents each kept index (lets the caller fetch rows it stored per candidate instead of going
+ *   back to the sequence); only available for n <= ASPA_MERGE_POS_MAX. */
+#define ASPA_MERGE_POS_MAX 65536
 int aspa_merge_finalise(const float* scores, const int64_t* indices, int64_t n, int64_t seq_len,
-                        int max_tokens, void* table, int64_t* keep_idx, float* keep_scores,
+                        int max_tokens, void* table, int64_t* keep_idx, float* keep_scores, int64_t* keep_pos,
                         int32_t* keep_count, void* stream);
 
 /* Gather rows src[idx[i], :] -> dst[i, :] (cs.py:688-689). row_bytes multiple of 16. */
 int aspa_gather_rows(const void* src, const int64_t* idx, const int32_t* count_dev, int64_t max_rows,
                      int64_t row_bytes, void* dst, void* stream);
+
+/* Ordered compaction of a byte mask (n): kept_idx (capacity) int64 gets the indices i with mask[i] != 0 in
+ * ascending order, padded with n; slot_of (n) int32 gets the position of every kept index in kept_idx (entries of
+ * dropped indices are left unwritten); count (1) int32 the number kept.  Indices beyond `capacity` are dropped
+ * (count still reports all of them).  scratch: aspa_compact_mask_scratch(n) bytes.  No reference counterpart
+ * (the reference uses boolean indexing, aspa.py:1715-1721). */
+int64_t aspa_compact_mask_scratch(int64_t n);
+int aspa_compact_mask(const uint8_t* mask, int64_t n, int64_t capacity, int64_t* kept_idx, int32_t* slot_of,
+                      int32_t* count, void* scratch, void* stream);
+
+/* dst (n, row_bytes): row i = src[slot_of[i]] where mask[i] != 0, else `fill` (one row of row_bytes, NULL =
+ * zeros).  Rebuilds a full-length result from rows computed for kept tokens only; with fill = the projection
+ * bias it equals projecting an all-zero row (aspa.py:1854).  row_bytes multiple of 16. */
+int aspa_scatter_rows_fill(const void* src, const int32_t* slot_of, const uint8_t* mask, const void* fill, int64_t n,
+                           int64_t row_bytes, void* dst, void* stream);
 
 /* Deterministic sum of per-block partials: out[j] = sum_i partials[j * n_blocks + i]. */
 int aspa_reduce_partials(const float* partials, int n_series, int64_t n_blocks, float* out, void* stream);

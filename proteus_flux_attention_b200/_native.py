@@ -57,7 +57,14 @@ SIGNATURES = {
     "aspa_proto_ema_scratch": (_l, [_l, _i, _i]),
     "aspa_proto_ema_update": (_i, [_p, _i, _l, _i, _p, _i, _d, _p, _p, _p, _p, _p, _p]),
     "aspa_chunk_select": (_i, [_p, _p, _i, _i, _f, _l, _p, _p, _p, _p]),
-    "aspa_merge_finalise": (_i, [_p, _p, _l, _l, _i, _p, _p, _p, _p, _p]),
+    "aspa_merge_finalise": (_i, [_p, _p, _l, _l, _i, _p, _p, _p, _p, _p, _p]),
+    "aspa_gather_attn_fwd_mapped": (_i, [_p, _p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _p, _p, _i, _l, _p, _p, _i,
+                                         C.POINTER(ShortlistPlan), _p, _p, _i, _i, _p, _p, _p]),
+    "aspa_rope_relayout_kv": (_i, [_p, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p]),
+    "aspa_rope_rows_q": (_i, [_p, _i, _p, _p, _l, _i, _i, _i, _i, _p, _p, _p, _p]),
+    "aspa_compact_mask_scratch": (_l, [_l]),
+    "aspa_compact_mask": (_i, [_p, _l, _l, _p, _p, _p, _p, _p]),
+    "aspa_scatter_rows_fill": (_i, [_p, _p, _p, _p, _l, _l, _p, _p]),
     "aspa_gather_rows": (_i, [_p, _p, _p, _l, _l, _p, _p]),
     "aspa_reduce_partials": (_i, [_p, _i, _l, _p, _p]),
 }

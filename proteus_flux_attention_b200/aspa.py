@@ -323,6 +323,8 @@ class AdaptiveSparseAttention(nn.Module):
         self._last_shortlist_backend_info: Optional[Dict[str, object]] = None
         self._last_batch_size: Optional[int] = None
         self.last_head_consensus: Optional[torch.Tensor] = None
+        # project queries / outputs for kept tokens only when at most 3/4 of the tokens can survive the token keep
+        self.compact_projection = True
         self._identity_pack: Dict[Tuple[int, int, str], Tuple[torch.Tensor, torch.Tensor]] = {}
         self._pin: Optional[torch.Tensor] = None
 
@@ -531,6 +533,38 @@ class AdaptiveSparseAttention(nn.Module):
         return ops.rope_relayout(qkv.contiguous(), self.h_total, self.d_head, cos, sin, want_amax,
                                  None if want_amax else q_keep,
                                  q_fraction=float(self._token_keep_ratio_runtime or 1.0))
+
+    def _project_compact(self, x: torch.Tensor, compact: dict):
+        """k, v for every token and q for the kept tokens only; the q rows of dropped tokens stay unwritten."""
+        B, T, C = x.shape
+        H, D = self.h_total, self.d_head
+        w, b = self.qkv.weight, self.qkv.bias
+        x_rows = ops.gather_rows(x.view(B * T, C), compact["idx"], compact["count"], compact["slots"],
+                                 out=torch.zeros((compact["slots"], C), dtype=x.dtype, device=x.device))
+        q_rows = F.linear(x_rows, w[:C], None if b is None else b[:C])
+        kv = F.linear(x, w[C:], None if b is None else b[C:])
+        cos = sin = None
+        if self.use_rope:
+            cos, sin = self._rope_factors(T, x.device, x.dtype)
+        k, v = ops.rope_relayout_kv(kv, H, D, cos, sin)
+        q = ops.rope_rows_q(q_rows, compact["idx"], compact["count"], B, T, H, D, cos, sin)
+        return q, k, v
+
+    @property
+    def last_head_consensus(self) -> Optional[torch.Tensor]:
+        """(B, T, C) attention output before the projection (eval mode only, aspa.py:1849); rebuilt on first use
+        when the call kept it as rows of kept tokens."""
+        pending = self.__dict__.get("_consensus_pending")
+        if pending is not None:
+            rows, slot_of, mask, (B, T, C) = pending
+            self.__dict__["_consensus_value"] = ops.scatter_rows_fill(rows, slot_of, mask, None, B * T).view(B, T, C)
+            self.__dict__["_consensus_pending"] = None
+        return self.__dict__.get("_consensus_value")
+
+    @last_head_consensus.setter
+    def last_head_consensus(self, value: Optional[torch.Tensor]) -> None:
+        self.__dict__["_consensus_pending"] = None
+        self.__dict__["_consensus_value"] = value
 
     def _check_input(self, x: torch.Tensor) -> None:
         if not x.is_cuda:
@@ -790,16 +824,35 @@ class AdaptiveSparseAttention(nn.Module):
 
         # 5. projection + RoPE + head-major relayout (does not depend on the record)
         use_quant = bool(self.quantize_sparse_int8 and not self.training)
-        # queries of dropped tokens are never used (every path below computes rows of kept tokens only)
-        q, k, v, amax = self._project_qkv(x, want_amax=use_quant and self.quantize_sparse_int8_mode == "max",
-                                          q_keep=None if use_quant else token_mask_u8)
+        # Queries and outputs only exist for kept tokens (every path below computes rows of kept tokens only, and
+        # the rows of dropped tokens reach the output projection as zeros): with a known bound on the kept count
+        # the query projection, the attention output and the output projection run on the kept rows alone.
+        # INT8 scales are taken over the queries of every token (aspa.py:1328), so that mode projects them all.
+        compact = None
+        if (self.compact_projection and token_mask_u8 is not None and kept is not None and bound_known
+                and not use_quant and 4 * kept_bound <= 3 * T and not self.training):
+            n_slots = B * kept_bound
+            kept_idx, slot_of, kept_cnt = ops.compact_mask(token_mask_u8.view(-1), n_slots)
+            compact = {"idx": kept_idx, "slot_of": slot_of, "count": kept_cnt, "slots": n_slots,
+                       "mask": token_mask_u8.view(-1)}
+            q, k, v = self._project_compact(x, compact)
+            amax = None
+        else:
+            # queries of dropped tokens are never used: skip their relayout
+            q, k, v, amax = self._project_qkv(x, want_amax=use_quant and self.quantize_sparse_int8_mode == "max",
+                                              q_keep=None if use_quant else token_mask_u8)
 
         # The mode decision needs row counts — unless alpha >= 0.95, where the reference never goes dense
         # (aspa.py:1636-1639): then the call runs without waiting for the record, on host-side bounds.
         runtime = self._prepare_linear_runtime(T, B, alpha)
         plan_args = self._plan_shape(runtime, T, sim is not None)
         lazy = alpha >= 0.95 and bound_known and plan_args is not None
-        out = torch.zeros((B, T, C), dtype=x.dtype, device=dev)
+        if compact is not None:
+            out = torch.zeros((compact["slots"], C), dtype=x.dtype, device=dev)
+            row_map = compact["slot_of"]
+        else:
+            out = torch.zeros((B, T, C), dtype=x.dtype, device=dev)
+            row_map = None
         info = None
         force_dense, dense_reason, exec_mode = False, None, "shortlist"
         if lazy:
@@ -847,7 +900,7 @@ class AdaptiveSparseAttention(nn.Module):
                 d_total, d_max = H * sum(info["kept"]), max(info["kept"])
             if d_total > 0:
                 attention_packed(q, k, v, row_offsets=d_offs, token_idx=d_tok, max_rows=d_max, total_rows=d_total, H=H,
-                                 out=out, out_layout=N.OUT_TOKEN_MAJOR)
+                                 out=out, out_layout=N.OUT_TOKEN_MAJOR, out_row_map=row_map)
             _record_backend(BACKEND_NAME, device=str(dev), heads=nbh, tokens=T, max_rows=int(d_max))
         elif total_rows == 0:
             exec_mode = "sparse"
@@ -872,7 +925,7 @@ class AdaptiveSparseAttention(nn.Module):
                 plan = ops.make_plan(win, slots, runtime["anchor_stride"], pcap, lists, limits)
                 attention_packed(qa, ka, va, row_offsets=row_offsets, token_idx=token_idx, max_rows=max_rows,
                                  total_rows=total_rows, H=H, scales=scales, plan=plan, out=out,
-                                 out_layout=N.OUT_TOKEN_MAJOR)
+                                 out_layout=N.OUT_TOKEN_MAJOR, out_row_map=row_map)
                 path = "planned"
             else:  # the candidate pieces can overflow L: use the exact table builder (needs exact row counts)
                 L = runtime["effective_L"]
@@ -890,14 +943,21 @@ class AdaptiveSparseAttention(nn.Module):
                     local_cap=runtime["local_cap"], anchor_cap=runtime["anchor_cap"], proto_cap=runtime["proto_cap"])
                 attention_packed(qa, ka, va, row_offsets=row_offsets, token_idx=tok_used, max_rows=max_rows,
                                  total_rows=total_rows, H=H, scales=scales, cand=cand, cand_len=lens, out=out,
-                                 out_layout=N.OUT_TOKEN_MAJOR)
+                                 out_layout=N.OUT_TOKEN_MAJOR, out_row_map=row_map)
                 path = "table"
             _record_backend(BACKEND_NAME, device=str(dev), heads=B * H, tokens=T, max_rows=int(max_rows),
                             quantized=bool(use_quant), candidates=path)
             self._last_shortlist_backend_info = get_last_backend_info()
 
-        self.last_head_consensus = None if self.training else out
-        y = self.dropout(self.proj(out))
+        if compact is not None:
+            # rows of dropped tokens are zero before the projection, so they leave it as the bias (aspa.py:1854)
+            y_rows = self.proj(out)
+            y = ops.scatter_rows_fill(y_rows, compact["slot_of"], compact["mask"], self.proj.bias, B * T).view(B, T, C)
+            self.__dict__["_consensus_value"] = None
+            self.__dict__["_consensus_pending"] = (out, compact["slot_of"], compact["mask"], (B, T, C))
+        else:
+            self.last_head_consensus = None if self.training else out
+            y = self.dropout(self.proj(out))
 
         # 7. telemetry
         if lazy:

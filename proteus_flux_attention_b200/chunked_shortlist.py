@@ -360,6 +360,11 @@ class ChunkedShortlistRunner:
         rec_idx = torch.full((max(n_local, 1), budget), -1, dtype=torch.int64, device=device)
         rec_count = torch.zeros((max(n_local, 1),), dtype=torch.int32, device=device)
         feeder = _ChunkFeeder(source, source_off, device, cfg.chunk_len)
+        # Host-resident input: the rows of every promoted token are set aside while their chunk is on the device,
+        # so that the reduced sequence is assembled from device memory instead of a second trip to the host.
+        pool = None
+        if not source.is_cuda and n_chunks * budget <= ops.MERGE_POS_MAX:
+            pool = torch.empty((max(n_local, 1) * budget, cfg.d_model), dtype=base_dtype, device=device)
 
         ev_a = torch.cuda.Event(enable_timing=True)
         ev_b = torch.cuda.Event(enable_timing=True)
@@ -377,23 +382,34 @@ class ChunkedShortlistRunner:
                 chunk_model(xc)
             else:
                 self._score_only(chunk_model, xc)
-            feeder.done(i)
             mask = chunk_model._last_token_mask
             ops.chunk_select(chunk_model._last_token_importance.view(-1),
                              mask.view(torch.uint8).view(-1) if mask is not None else None, budget,
                              cfg.nucleus_top_p, start, rec_scores[i], rec_idx[i], rec_count[i:i + 1])
+            if pool is not None:
+                ops.gather_rows(xc[0], (rec_idx[i] - start).clamp_(min=0), rec_count[i:i + 1], budget,
+                                out=pool[i * budget:(i + 1) * budget])
+            feeder.done(i)
 
         # exchange: every rank ends up with the records of all chunks, in chunk order
         all_scores, all_idx, all_count = dist_utils.all_gather_records(self.group, rec_scores, rec_idx, rec_count,
                                                                       n_chunks, world)
-        keep_idx, keep_sc, keep_count = ops.merge_finalise(all_scores.view(-1), all_idx.view(-1), cfg.seq_len,
-                                                           cfg.buffer_tokens)
+        keep_pos = None
+        if pool is not None:
+            keep_idx, keep_sc, keep_count, keep_pos = ops.merge_finalise(all_scores.view(-1), all_idx.view(-1), cfg.seq_len,
+                                                                         cfg.buffer_tokens, want_pos=True)
+        else:
+            keep_idx, keep_sc, keep_count = ops.merge_finalise(all_scores.view(-1), all_idx.view(-1), cfg.seq_len,
+                                                               cfg.buffer_tokens)
         ev_b.record()
         k_host = int(keep_count.item())
         if k_host == 0:
             raise RuntimeError("Chunked pipeline selected zero tokens; adjust per_chunk_budget or sparse ratios.")
         keep_idx, keep_sc = keep_idx[:k_host], keep_sc[:k_host]
-        reduced = self._gather_reduced(source, source_off, keep_idx, k_host, device, world, rank, c_lo, c_hi)
+        if pool is not None:
+            reduced = self._gather_pooled(pool, keep_pos[:k_host], k_host, budget, world, c_lo, c_hi)
+        else:
+            reduced = self._gather_reduced(source, source_off, keep_idx, k_host, device, world, rank, c_lo, c_hi)
         chunk_time_ms = None
         final_output = final_stats = backend_info = None
         final_time_ms = peak_mb = None
@@ -439,6 +455,18 @@ class ChunkedShortlistRunner:
         return ChunkedShortlistResult(keep_indices=keep_idx.to("cpu"), keep_scores=keep_sc.to("cpu"),
                                       reduced_sequence=reduced, metrics=metrics, chunks=summaries,
                                       final_output=final_output, final_stats=final_stats, backend_info=backend_info)
+
+    def _gather_pooled(self, pool: torch.Tensor, keep_pos: torch.Tensor, k: int, budget: int, world: int, c_lo: int,
+                       c_hi: int) -> torch.Tensor:
+        """(1, k, C) rows of the kept tokens from the per-chunk pools of promoted rows.  ``keep_pos`` holds, for every
+        kept index, its position in the chunk-major list of all promotions (chunk * budget + rank within the chunk)."""
+        if world == 1:
+            return ops.gather_rows(pool, keep_pos, None, k).unsqueeze(0)
+        lo, hi = c_lo * budget, c_hi * budget
+        local = keep_pos[(keep_pos >= lo) & (keep_pos < hi)] - lo
+        rows = ops.gather_rows(pool, local.contiguous(), None, int(local.numel())) if local.numel() else \
+            pool.new_zeros((0, pool.size(1)))
+        return dist_utils.all_gather_rows(self.group, rows, k, world).unsqueeze(0)
 
     def _gather_reduced(self, source: torch.Tensor, source_off: int, keep_idx: torch.Tensor, k: int,
                         device: torch.device, world: int, rank: int, c_lo: int, c_hi: int) -> torch.Tensor:

@@ -33,6 +33,7 @@ struct AttnParams {
   const float* add_mask;
   void* out;
   int out_dtype, out_layout;
+  const int32_t* out_row_map;  // token-major only: (B*T) row -> compact row, or NULL
   float scale;
   float* ws_m;  // [total_rows] running max (natural-log domain, already scaled)
   float* ws_l;  // [total_rows] running denominator
@@ -41,10 +42,13 @@ struct AttnParams {
   int write_partial;  // window pass: write ws_* instead of the final output
 };
 
-__device__ __forceinline__ int64_t out_index(const AttnParams& p, int bh, int t, int d) {
-  if (p.out_layout == ASPA_OUT_HEAD_MAJOR) return ((int64_t)bh * p.T + t) * p.D + d;
+// Element offset of out[bh, t, 0].  With a row map the token-major row b*T + t is replaced by its compact slot.
+__device__ __forceinline__ int64_t out_row_base(const AttnParams& p, int bh, int t) {
+  if (p.out_layout == ASPA_OUT_HEAD_MAJOR) return ((int64_t)bh * p.T + t) * p.D;
   const int b = bh / p.H, h = bh % p.H;
-  return (((int64_t)b * p.T + t) * p.H + h) * p.D + d;
+  int64_t row = (int64_t)b * p.T + t;
+  if (p.out_row_map) row = p.out_row_map[row];
+  return (row * p.H + h) * p.D;
 }
 
 __device__ __forceinline__ void store_out(const AttnParams& p, int64_t idx, float v) {
@@ -284,34 +288,36 @@ __global__ void __launch_bounds__(GEN_WARPS * 32) attn_rows_kernel(const AttnPar
     const float lt = l1 * c1 + l * c2;
     const float inv = lt > 0.f ? 1.f / lt : 0.f;
     // the window pass stores raw P.V (no value scale); acc here is raw too
+    const int64_t ob = out_row_base(p, bh, t);
     if (kVec) {
       if (lane < LPR) {
 #pragma unroll
         for (int e = 0; e < VE; ++e) {
           const int d = sub * VE + e;
-          store_out(p, out_index(p, bh, t, d), (p.ws_o[grow * D + d] * c1 + acc[e] * c2) * inv * vscale);
+          store_out(p, ob + d, (p.ws_o[grow * D + d] * c1 + acc[e] * c2) * inv * vscale);
         }
       }
     } else {
 #pragma unroll
       for (int i = 0; i < GEN_MAXD / 32; ++i) {
         const int d = lane + 32 * i;
-        if (d < D) store_out(p, out_index(p, bh, t, d), (p.ws_o[grow * D + d] * c1 + acc[i] * c2) * inv * vscale);
+        if (d < D) store_out(p, ob + d, (p.ws_o[grow * D + d] * c1 + acc[i] * c2) * inv * vscale);
       }
     }
     return;
   }
   const float inv = l > 0.f ? 1.f / l : 0.f;
+  const int64_t ob = out_row_base(p, bh, t);
   if (kVec) {
     if (lane < LPR) {
 #pragma unroll
-      for (int e = 0; e < VE; ++e) store_out(p, out_index(p, bh, t, sub * VE + e), acc[e] * inv * vscale);
+      for (int e = 0; e < VE; ++e) store_out(p, ob + sub * VE + e, acc[e] * inv * vscale);
     }
   } else {
 #pragma unroll
     for (int i = 0; i < GEN_MAXD / 32; ++i) {
       const int d = lane + 32 * i;
-      if (d < D) store_out(p, out_index(p, bh, t, d), acc[i] * inv * vscale);
+      if (d < D) store_out(p, ob + d, acc[i] * inv * vscale);
     }
   }
 }
@@ -606,10 +612,11 @@ __global__ void __launch_bounds__(128) attn_window_kernel(const AttnParams p) {
     } else {
       float inv = ll > 0.f ? 1.f / ll : 0.f;
       if (sizeof(T) == 1) inv *= p.v_scale[bh];
+      const int64_t ob = out_row_base(p, bh, tt);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const int d = 8 * j + qd * 2;
-        const int64_t oi = out_index(p, bh, tt, d);
+        const int64_t oi = ob + d;
         const float a = o[j][2 * half] * inv, b = o[j][2 * half + 1] * inv;
         if (p.out_dtype == ASPA_BF16)
           *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(p.out) + oi) = __floats2bfloat162_rn(a, b);
@@ -655,12 +662,25 @@ extern "C" int aspa_gather_attn_fwd(const void* q, const void* k, const void* v,
                                     int64_t total_rows, const int64_t* cand, const int64_t* cand_len, int L,
                                     const aspa_shortlist_plan* plan, const float* add_mask, void* out, int out_dtype,
                                     int out_layout, void* workspace, void* stream) {
+  return aspa_gather_attn_fwd_mapped(q, k, v, qkv_dtype, q_scale, k_scale, v_scale, heads, T, D, H, row_offsets, token_idx,
+                                     max_rows, total_rows, cand, cand_len, L, plan, add_mask, out, out_dtype, out_layout,
+                                     nullptr, workspace, stream);
+}
+
+extern "C" int aspa_gather_attn_fwd_mapped(const void* q, const void* k, const void* v, int qkv_dtype,
+                                           const float* q_scale, const float* k_scale, const float* v_scale, int heads,
+                                           int T, int D, int H, const int32_t* row_offsets, const int32_t* token_idx,
+                                           int max_rows, int64_t total_rows, const int64_t* cand,
+                                           const int64_t* cand_len, int L, const aspa_shortlist_plan* plan,
+                                           const float* add_mask, void* out, int out_dtype, int out_layout,
+                                           const int32_t* out_row_map, void* workspace, void* stream) {
   ASPA_CHECK_ARG(q && k && v && row_offsets && token_idx && out, "null pointer");
   ASPA_CHECK_ARG(heads > 0 && T > 0 && D > 0 && D <= GEN_MAXD, "head_dim must be in [1, 256]");
   ASPA_CHECK_ARG(qkv_dtype == ASPA_F32 || qkv_dtype == ASPA_BF16 || qkv_dtype == ASPA_I8, "bad qkv dtype");
   ASPA_CHECK_ARG(out_dtype == ASPA_F32 || out_dtype == ASPA_BF16, "bad out dtype");
   ASPA_CHECK_ARG(out_layout == ASPA_OUT_HEAD_MAJOR || (out_layout == ASPA_OUT_TOKEN_MAJOR && H > 0 && heads % H == 0),
                  "token-major output needs H dividing heads");
+  ASPA_CHECK_ARG(out_row_map == nullptr || out_layout == ASPA_OUT_TOKEN_MAJOR, "a row map needs the token-major layout");
   if (qkv_dtype == ASPA_I8) ASPA_CHECK_ARG(q_scale && k_scale && v_scale, "int8 inputs need q/k/v scales");
   ASPA_CHECK_ARG((cand == nullptr) == (cand_len == nullptr), "candidates and lengths come together");
   if (cand) ASPA_CHECK_ARG(L > 0, "candidate width must be positive");
@@ -676,7 +696,7 @@ extern "C" int aspa_gather_attn_fwd(const void* q, const void* k, const void* v,
   p.has_plan = (plan != nullptr && cand == nullptr) ? 1 : 0;
   if (p.has_plan) p.plan = *plan;
   p.add_mask = add_mask;
-  p.out = out; p.out_dtype = out_dtype; p.out_layout = out_layout;
+  p.out = out; p.out_dtype = out_dtype; p.out_layout = out_layout; p.out_row_map = out_row_map;
   p.scale = 1.0f / sqrtf((float)D);
   p.ws_m = p.ws_l = p.ws_o = nullptr;
 

@@ -570,6 +570,7 @@ __global__ void __launch_bounds__(CL_THREADS) merge_select_cluster_kernel(const 
                                                                           int max_tokens, int P2,
                                                                           int64_t* __restrict__ keep_idx,
                                                                           float* __restrict__ keep_scores,
+                                                                          int64_t* __restrict__ keep_pos,
                                                                           int32_t* __restrict__ keep_count) {
   extern __shared__ int sel[];  // [P2] selected indices, used in CTA 0
   __shared__ ClusterScratch cs;
@@ -644,8 +645,10 @@ __global__ void __launch_bounds__(CL_THREADS) merge_select_cluster_kernel(const 
   const int cnt = min((int)tot[0], P2);
   bitonic_i32(sel, P2);
   for (int i = tid; i < cnt; i += CL_THREADS) {
+    const unsigned long long e = table[sel[i]];
     keep_idx[i] = sel[i];
-    keep_scores[i] = key_float((uint32_t)(table[sel[i]] >> 32));
+    keep_scores[i] = key_float((uint32_t)(e >> 32));
+    if (keep_pos) keep_pos[i] = (int64_t)(e & 0xffffffffull);
   }
   if (tid == 0) keep_count[0] = cnt;
 }
@@ -653,6 +656,7 @@ __global__ void __launch_bounds__(CL_THREADS) merge_select_cluster_kernel(const 
 }  // namespace aspa
 
 using namespace aspa;
+static_assert(ASPA_MERGE_POS_MAX == CL_MAX * CL_KEYS_PER_CTA, "header constant out of step with the cluster kernels");
 
 extern "C" int64_t aspa_proto_ema_scratch(int64_t n, int C, int G) {
   const int64_t nchunk = ceil_div(n, EMA_TOK);
@@ -720,9 +724,11 @@ extern "C" int aspa_chunk_select(const float* importance, const uint8_t* token_m
 
 extern "C" int aspa_merge_finalise(const float* scores, const int64_t* indices, int64_t n, int64_t seq_len,
                                    int max_tokens, void* table, int64_t* keep_idx, float* keep_scores,
-                                   int32_t* keep_count, void* stream) {
+                                   int64_t* keep_pos, int32_t* keep_count, void* stream) {
   ASPA_CHECK_ARG(scores && indices && table && keep_idx && keep_scores && keep_count, "null pointer");
   ASPA_CHECK_ARG(n >= 0 && seq_len > 0 && max_tokens > 0, "bad sizes");
+  ASPA_CHECK_ARG(keep_pos == nullptr || (n > 0 && n <= ASPA_MERGE_POS_MAX && seq_len < (int64_t)1 << 31),
+                 "candidate positions are only tracked for n <= ASPA_MERGE_POS_MAX");
   cudaStream_t st = (cudaStream_t)stream;
   if (n > 0 && n <= CL_MAX * CL_KEYS_PER_CTA && seq_len < (int64_t)1 << 31) {
     unsigned long long* t64 = reinterpret_cast<unsigned long long*>(table);
@@ -735,7 +741,7 @@ extern "C" int aspa_merge_finalise(const float* scores, const int64_t* indices, 
     while ((int64_t)csize * CL_KEYS_PER_CTA < n) csize <<= 1;
     cudaFuncSetAttribute(merge_select_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     const cudaError_t e = launch_clusters(merge_select_cluster_kernel, 1, csize, smem, st, scores, indices, (int)n, seq_len,
-                                          (const unsigned long long*)t64, max_tokens, P2, keep_idx, keep_scores, keep_count);
+                                          (const unsigned long long*)t64, max_tokens, P2, keep_idx, keep_scores, keep_pos, keep_count);
     if (e != cudaSuccess) {
       set_error("aspa_merge_finalise: cluster launch failed: %s", cudaGetErrorString(e));
       return ASPA_ERR_CUDA;

@@ -53,22 +53,23 @@ __global__ void __launch_bounds__(512) rope_relayout_kernel(const T* __restrict_
                                                             const float* __restrict__ sin_t, T* __restrict__ q,
                                                             T* __restrict__ k, T* __restrict__ v,
                                                             float* __restrict__ amax,
-                                                            const uint8_t* __restrict__ q_keep) {
+                                                            const uint8_t* __restrict__ q_keep, int nsec, int sec0) {
+  // the source holds `nsec` sections per token, the first of them being section `sec0` of (q, k, v)
   constexpr int E = 16 / sizeof(T);  // elements per 16-byte vector: 8 bf16 or 4 fp32
   const int C = H * D;
-  const int vec_per_tok = 3 * C / E;
+  const int vec_per_tok = nsec * C / E;
   const int b = blockIdx.y;
   const int t0 = blockIdx.x * ROPE_TPB;
   const int t1 = min(Tn, t0 + ROPE_TPB);
   const int half = D / 2;
   for (int vi = threadIdx.x; vi < vec_per_tok; vi += blockDim.x) {
     const int ch = vi * E;
-    const int sec = ch / C;
-    const int c_in = ch - sec * C;
+    const int sec = sec0 + ch / C;
+    const int c_in = ch % C;
     const int h = c_in / D, d0 = c_in - h * D;
     const int bh = b * H + h;
     const bool rotate = sec < 2 && cos_t != nullptr;
-    const T* src = qkv + ((int64_t)b * Tn + t0) * (3 * (int64_t)C) + ch;
+    const T* src = qkv + ((int64_t)b * Tn + t0) * (nsec * (int64_t)C) + ch;
     T* dst = (sec == 0 ? q : (sec == 1 ? k : v)) + ((int64_t)bh * Tn + t0) * D + d0;
     const float* cr = cos_t ? cos_t + (int64_t)t0 * half + d0 / 2 : nullptr;
     const float* sr = sin_t ? sin_t + (int64_t)t0 * half + d0 / 2 : nullptr;
@@ -77,7 +78,7 @@ __global__ void __launch_bounds__(512) rope_relayout_kernel(const T* __restrict_
 #pragma unroll 4
     for (int t = t0; t < t1; ++t) {
       if (keep != nullptr && !keep[t]) {  // queries of dropped tokens are never read: neither load nor store them
-        src += 3 * (int64_t)C;
+        src += nsec * (int64_t)C;
         dst += D;
         if (cr) { cr += half; sr += half; }
         continue;
@@ -112,7 +113,7 @@ __global__ void __launch_bounds__(512) rope_relayout_kernel(const T* __restrict_
         if (amax) local_max = fmaxf(fmaxf(fabsf(f[0]), fabsf(f[1])), fmaxf(local_max, fmaxf(fabsf(f[2]), fabsf(f[3]))));
       }
       *reinterpret_cast<uint4*>(dst) = raw;
-      src += 3 * (int64_t)C;
+      src += nsec * (int64_t)C;
       dst += D;
       if (cr) { cr += half; sr += half; }
     }
@@ -189,6 +190,67 @@ __global__ void __launch_bounds__(256) quantize_int8_kernel(const T* __restrict_
   }
 }
 
+// RoPE of compact query rows: row i of q_rows (H*D wide) belongs to token kept_idx[i]; it is rotated at that
+// token's position and stored head-major.  One thread per 16-byte vector.
+template <typename T>
+__global__ void __launch_bounds__(256) rope_rows_q_kernel(const T* __restrict__ q_rows,
+                                                          const int64_t* __restrict__ kept_idx,
+                                                          const int32_t* __restrict__ count_dev, int64_t max_rows,
+                                                          int64_t n_tok, int Tn, int H, int D,
+                                                          const float* __restrict__ cos_t,
+                                                          const float* __restrict__ sin_t, T* __restrict__ q) {
+  constexpr int E = 16 / sizeof(T);
+  const int C = H * D, half = D / 2;
+  const int vec_per_row = C / E;
+  const int64_t rows = count_dev ? min((int64_t)count_dev[0], max_rows) : max_rows;
+  const int64_t total = rows * vec_per_row;
+  for (int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; g < total; g += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = g / vec_per_row;
+    const int ch = (int)(g % vec_per_row) * E;
+    const int64_t tok = kept_idx[r];
+    if (tok < 0 || tok >= n_tok) continue;
+    const int b = (int)(tok / Tn), t = (int)(tok % Tn);
+    const int h = ch / D, d0 = ch % D;
+    uint4 raw = *reinterpret_cast<const uint4*>(q_rows + r * C + ch);
+    if (cos_t != nullptr) {
+      const float* cr = cos_t + (int64_t)t * half + d0 / 2;
+      const float* sr = sin_t + (int64_t)t * half + d0 / 2;
+      if (sizeof(T) == 2) {
+        const float4 c4 = *reinterpret_cast<const float4*>(cr), s4 = *reinterpret_cast<const float4*>(sr);
+        raw.x = rope_word_bf16(raw.x, c4.x, s4.x);
+        raw.y = rope_word_bf16(raw.y, c4.y, s4.y);
+        raw.z = rope_word_bf16(raw.z, c4.z, s4.z);
+        raw.w = rope_word_bf16(raw.w, c4.w, s4.w);
+      } else {
+        float* f = reinterpret_cast<float*>(&raw);
+        const float2 c2 = *reinterpret_cast<const float2*>(cr), s2 = *reinterpret_cast<const float2*>(sr);
+        const float e0 = f[0], o0 = f[1], e1 = f[2], o1 = f[3];
+        f[0] = rope_mix(e0, c2.x, -o0, s2.x, false);
+        f[1] = rope_mix(o0, c2.x, e0, s2.x, false);
+        f[2] = rope_mix(e1, c2.y, -o1, s2.y, false);
+        f[3] = rope_mix(o1, c2.y, e1, s2.y, false);
+      }
+    }
+    *reinterpret_cast<uint4*>(q + (((int64_t)b * H + h) * Tn + t) * D + d0) = raw;
+  }
+}
+
+// dst row i = src[slot_of[i]] for kept rows, `fill` (or zeros) for the others.
+__global__ void __launch_bounds__(256) scatter_rows_fill_kernel(const uint4* __restrict__ src,
+                                                                const int32_t* __restrict__ slot_of,
+                                                                const uint8_t* __restrict__ mask,
+                                                                const uint4* __restrict__ fill, int64_t n,
+                                                                int64_t vec_per_row, uint4* __restrict__ dst) {
+  const int64_t total = n * vec_per_row;
+  for (int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; g < total; g += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = g / vec_per_row, c = g % vec_per_row;
+    uint4 val = make_uint4(0u, 0u, 0u, 0u);
+    if (mask[r]) val = src[(int64_t)slot_of[r] * vec_per_row + c];
+    else if (fill) val = fill[c];
+    dst[g] = val;
+  }
+}
+
 __global__ void __launch_bounds__(256) gather_rows_kernel(const uint4* __restrict__ src,
                                                           const int64_t* __restrict__ idx,
                                                           const int32_t* __restrict__ count_dev, int64_t max_rows,
@@ -228,12 +290,12 @@ extern "C" int aspa_rope_relayout(const void* qkv, int dtype, int B, int T, int 
     const int vec = 3 * H * D / 8;
     const int threads = (int)std::min<int64_t>(512, ceil_div(vec, 32) * 32);
     rope_relayout_kernel<__nv_bfloat16><<<grid, threads, 0, (cudaStream_t)stream>>>(
-        (const __nv_bfloat16*)qkv, B, T, H, D, cos_t, sin_t, (__nv_bfloat16*)q, (__nv_bfloat16*)k, (__nv_bfloat16*)v, amax, q_keep);
+        (const __nv_bfloat16*)qkv, B, T, H, D, cos_t, sin_t, (__nv_bfloat16*)q, (__nv_bfloat16*)k, (__nv_bfloat16*)v, amax, q_keep, 3, 0);
   } else {
     const int vec = 3 * H * D / 4;
     const int threads = (int)std::min<int64_t>(512, ceil_div(vec, 32) * 32);
     rope_relayout_kernel<float><<<grid, threads, 0, (cudaStream_t)stream>>>((const float*)qkv, B, T, H, D, cos_t, sin_t,
-                                                                           (float*)q, (float*)k, (float*)v, amax, q_keep);
+                                                                           (float*)q, (float*)k, (float*)v, amax, q_keep, 3, 0);
   }
   ASPA_CHECK_LAUNCH();
   return ASPA_OK;
@@ -274,6 +336,62 @@ extern "C" int aspa_gather_rows(const void* src, const int64_t* idx, const int32
   const int64_t total = max_rows * (row_bytes / 16);
   gather_rows_kernel<<<(unsigned)std::min<int64_t>(ceil_div(total, 256), 148 * 16), 256, 0, (cudaStream_t)stream>>>(
       (const uint4*)src, idx, count_dev, max_rows, row_bytes / 16, (uint4*)dst);
+  ASPA_CHECK_LAUNCH();
+  return ASPA_OK;
+}
+
+extern "C" int aspa_rope_relayout_kv(const void* kv, int dtype, int B, int T, int H, int D, const float* cos_t,
+                                     const float* sin_t, void* k, void* v, void* stream) {
+  ASPA_CHECK_ARG(kv && k && v, "null pointer");
+  ASPA_CHECK_ARG(B > 0 && T > 0 && H > 0 && D > 0 && D % 2 == 0, "bad sizes");
+  ASPA_CHECK_ARG(dtype == ASPA_F32 || dtype == ASPA_BF16, "dtype must be fp32 or bf16");
+  ASPA_CHECK_ARG(D % (dtype == ASPA_BF16 ? 8 : 4) == 0, "head_dim must fill 16-byte vectors");
+  ASPA_CHECK_ARG((cos_t == nullptr) == (sin_t == nullptr), "cos/sin tables come together");
+  const dim3 grid((unsigned)ceil_div(T, ROPE_TPB), (unsigned)B);
+  if (dtype == ASPA_BF16) {
+    const int vec = 2 * H * D / 8;
+    const int threads = (int)std::min<int64_t>(512, ceil_div(vec, 32) * 32);
+    rope_relayout_kernel<__nv_bfloat16><<<grid, threads, 0, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)kv, B, T, H, D, cos_t, sin_t, nullptr, (__nv_bfloat16*)k, (__nv_bfloat16*)v, nullptr, nullptr, 2, 1);
+  } else {
+    const int vec = 2 * H * D / 4;
+    const int threads = (int)std::min<int64_t>(512, ceil_div(vec, 32) * 32);
+    rope_relayout_kernel<float><<<grid, threads, 0, (cudaStream_t)stream>>>((const float*)kv, B, T, H, D, cos_t, sin_t, nullptr,
+                                                                           (float*)k, (float*)v, nullptr, nullptr, 2, 1);
+  }
+  ASPA_CHECK_LAUNCH();
+  return ASPA_OK;
+}
+
+extern "C" int aspa_rope_rows_q(const void* q_rows, int dtype, const int64_t* kept_idx, const int32_t* count_dev,
+                                int64_t max_rows, int B, int T, int H, int D, const float* cos_t, const float* sin_t,
+                                void* q, void* stream) {
+  ASPA_CHECK_ARG(q_rows && kept_idx && q, "null pointer");
+  ASPA_CHECK_ARG(B > 0 && T > 0 && H > 0 && D > 0 && D % 2 == 0 && max_rows >= 0, "bad sizes");
+  ASPA_CHECK_ARG(dtype == ASPA_F32 || dtype == ASPA_BF16, "dtype must be fp32 or bf16");
+  ASPA_CHECK_ARG(D % (dtype == ASPA_BF16 ? 8 : 4) == 0, "head_dim must fill 16-byte vectors");
+  ASPA_CHECK_ARG((cos_t == nullptr) == (sin_t == nullptr), "cos/sin tables come together");
+  if (max_rows == 0) return ASPA_OK;
+  const int64_t total = max_rows * (H * D / (dtype == ASPA_BF16 ? 8 : 4));
+  const unsigned blocks = (unsigned)std::min<int64_t>(ceil_div(total, 256), 148 * 16);
+  if (dtype == ASPA_BF16)
+    rope_rows_q_kernel<__nv_bfloat16><<<blocks, 256, 0, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)q_rows, kept_idx, count_dev, max_rows, (int64_t)B * T, T, H, D, cos_t, sin_t, (__nv_bfloat16*)q);
+  else
+    rope_rows_q_kernel<float><<<blocks, 256, 0, (cudaStream_t)stream>>>((const float*)q_rows, kept_idx, count_dev, max_rows,
+                                                                        (int64_t)B * T, T, H, D, cos_t, sin_t, (float*)q);
+  ASPA_CHECK_LAUNCH();
+  return ASPA_OK;
+}
+
+extern "C" int aspa_scatter_rows_fill(const void* src, const int32_t* slot_of, const uint8_t* mask, const void* fill,
+                                      int64_t n, int64_t row_bytes, void* dst, void* stream) {
+  ASPA_CHECK_ARG(src && slot_of && mask && dst, "null pointer");
+  ASPA_CHECK_ARG(n >= 0 && row_bytes > 0 && row_bytes % 16 == 0, "row_bytes must be a multiple of 16");
+  if (n == 0) return ASPA_OK;
+  const int64_t total = n * (row_bytes / 16);
+  scatter_rows_fill_kernel<<<(unsigned)std::min<int64_t>(ceil_div(total, 256), 148 * 32), 256, 0, (cudaStream_t)stream>>>(
+      (const uint4*)src, slot_of, mask, (const uint4*)fill, n, row_bytes / 16, (uint4*)dst);
   ASPA_CHECK_LAUNCH();
   return ASPA_OK;
 }

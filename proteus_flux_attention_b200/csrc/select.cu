@@ -1,4 +1,5 @@
 // Token keep (radix select), head budget, per-token head top-k and row packing.
+#include <algorithm>
 #include <mutex>
 
 #include "cluster.cuh"
@@ -518,6 +519,68 @@ __global__ void __launch_bounds__(PK_SEG) pack_fill_kernel(const void* __restric
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Ordered compaction of a byte mask
+// ---------------------------------------------------------------------------------------------
+constexpr int CM_THREADS = 256;
+constexpr int CM_PER_THREAD = 8;
+constexpr int CM_BLOCK = CM_THREADS * CM_PER_THREAD;  // indices per CTA
+
+__global__ void __launch_bounds__(CM_THREADS) compact_count_kernel(const uint8_t* __restrict__ mask, int64_t n,
+                                                                   int32_t* __restrict__ block_counts) {
+  __shared__ int tmp[33];
+  const int64_t base = (int64_t)blockIdx.x * CM_BLOCK + threadIdx.x * CM_PER_THREAD;
+  int c = 0;
+#pragma unroll
+  for (int j = 0; j < CM_PER_THREAD; ++j)
+    if (base + j < n) c += mask[base + j] ? 1 : 0;
+  const int tot = block_sum_int(c, tmp);
+  if (threadIdx.x == 0) block_counts[blockIdx.x] = tot;
+}
+
+__global__ void __launch_bounds__(CM_THREADS) compact_fill_kernel(const uint8_t* __restrict__ mask, int64_t n,
+                                                                  int64_t capacity,
+                                                                  const int32_t* __restrict__ block_counts,
+                                                                  int64_t* __restrict__ kept_idx,
+                                                                  int32_t* __restrict__ slot_of,
+                                                                  int32_t* __restrict__ count) {
+  __shared__ int tmp[33];
+  __shared__ int64_t sh_prefix, sh_total;
+  // this CTA's first slot and the grand total, summed in a fixed order from the per-CTA counts
+  int64_t before = 0, all = 0;
+  for (int i = threadIdx.x; i < (int)gridDim.x; i += CM_THREADS) {
+    const int c = block_counts[i];
+    all += c;
+    if (i < (int)blockIdx.x) before += c;
+  }
+  if (threadIdx.x == 0) sh_prefix = 0, sh_total = 0;
+  __syncthreads();
+  atomicAdd(reinterpret_cast<unsigned long long*>(&sh_prefix), (unsigned long long)before);
+  atomicAdd(reinterpret_cast<unsigned long long*>(&sh_total), (unsigned long long)all);
+  __syncthreads();
+  const int64_t prefix = sh_prefix, total = sh_total;
+  const int64_t base = (int64_t)blockIdx.x * CM_BLOCK + threadIdx.x * CM_PER_THREAD;
+  uint32_t bits = 0;
+  int c = 0;
+#pragma unroll
+  for (int j = 0; j < CM_PER_THREAD; ++j)
+    if (base + j < n && mask[base + j]) bits |= 1u << j, ++c;
+  int blk_total;
+  int64_t slot = prefix + block_exclusive_scan(c, tmp, &blk_total);
+#pragma unroll
+  for (int j = 0; j < CM_PER_THREAD; ++j)
+    if ((bits >> j) & 1u) {
+      if (slot < capacity) kept_idx[slot] = base + j;
+      slot_of[base + j] = (int32_t)min(slot, (int64_t)0x7fffffff);
+      ++slot;
+    }
+  // padding of the tail, spread over the grid
+  for (int64_t i = total + (int64_t)blockIdx.x * CM_THREADS + threadIdx.x; i < capacity;
+       i += (int64_t)gridDim.x * CM_THREADS)
+    kept_idx[i] = n;
+  if (blockIdx.x == 0 && threadIdx.x == 0) count[0] = (int32_t)min(total, (int64_t)0x7fffffff);
+}
+
 }  // namespace aspa
 
 using namespace aspa;
@@ -673,4 +736,20 @@ extern "C" int aspa_pack_rows_static(const uint64_t* head_bits, int B, int T, in
   if (scratch == nullptr) return ASPA_ERR_CUDA;
   // Nothing in the scratch has to start at zero: the count pass writes every entry the scan reads.
   return pack_impl<true>(head_bits, B, T, H, scratch, row_offsets, token_idx, capacity, (cudaStream_t)stream);
+}
+
+extern "C" int64_t aspa_compact_mask_scratch(int64_t n) { return (int64_t)sizeof(int32_t) * std::max<int64_t>(1, ceil_div(n, CM_BLOCK)); }
+
+extern "C" int aspa_compact_mask(const uint8_t* mask, int64_t n, int64_t capacity, int64_t* kept_idx, int32_t* slot_of,
+                                 int32_t* count, void* scratch, void* stream) {
+  ASPA_CHECK_ARG(mask && kept_idx && slot_of && count && scratch, "null pointer");
+  ASPA_CHECK_ARG(n > 0 && n < ((int64_t)1 << 31) && capacity >= 0, "bad sizes");
+  cudaStream_t st = (cudaStream_t)stream;
+  const unsigned nblk = (unsigned)ceil_div(n, CM_BLOCK);
+  int32_t* counts = reinterpret_cast<int32_t*>(scratch);
+  compact_count_kernel<<<nblk, CM_THREADS, 0, st>>>(mask, n, counts);
+  ASPA_CHECK_LAUNCH();
+  compact_fill_kernel<<<nblk, CM_THREADS, 0, st>>>(mask, n, capacity, counts, kept_idx, slot_of, count);
+  ASPA_CHECK_LAUNCH();
+  return ASPA_OK;
 }

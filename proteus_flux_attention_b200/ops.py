@@ -279,8 +279,9 @@ def gather_attn(q, k, v, *, scales: Optional[Tuple[torch.Tensor, torch.Tensor, t
                 row_offsets: torch.Tensor, token_idx: torch.Tensor, max_rows: int, total_rows: int,
                 cand: Optional[torch.Tensor] = None, cand_len: Optional[torch.Tensor] = None,
                 plan: Optional[N.ShortlistPlan] = None, add_mask: Optional[torch.Tensor] = None,
-                out: torch.Tensor, out_layout: int):
-    """Launch the attention kernels; `out` must be zero-filled by the caller."""
+                out: torch.Tensor, out_layout: int, out_row_map: Optional[torch.Tensor] = None):
+    """Launch the attention kernels; `out` must be zero-filled by the caller.  ``out_row_map`` (B*T int32)
+    redirects token-major output rows to compact slots."""
     heads, T, D = q.shape
     ws = None
     nbytes = int(N.lib().aspa_attn_workspace_bytes(int(total_rows), D))
@@ -294,11 +295,11 @@ def gather_attn(q, k, v, *, scales: Optional[Tuple[torch.Tensor, torch.Tensor, t
     # algorithmic bytes: each active row's q once, every key and value row once, each active output row once
     nbytes = int(total_rows) * D * (e + out.element_size()) + 2 * heads * T * D * e
     with _timed("attention", 2 if two_pass else 1, nbytes):
-        N.check(N.lib().aspa_gather_attn_fwd(
+        N.check(N.lib().aspa_gather_attn_fwd_mapped(
             N.ptr(q), N.ptr(k), N.ptr(v), N.dtype_code(q.dtype), N.ptr(qs), N.ptr(ks), N.ptr(vs), heads, T, D, int(H),
             N.ptr(row_offsets), N.ptr(token_idx), int(max_rows), int(total_rows), N.ptr(cand), N.ptr(cand_len), int(L),
             C.byref(plan) if plan is not None else None, N.ptr(add_mask), N.ptr(out), N.dtype_code(out.dtype),
-            int(out_layout), N.ptr(ws), N.stream()), "gather_attn_fwd")
+            int(out_layout), N.ptr(out_row_map), N.ptr(ws), N.stream()), "gather_attn_fwd")
     return out
 
 
@@ -324,23 +325,79 @@ def chunk_select(importance: torch.Tensor, token_mask: Optional[torch.Tensor], b
                                           N.ptr(out_scores), N.ptr(out_idx), N.ptr(out_count), N.stream()), "chunk_select")
 
 
-def merge_finalise(scores: torch.Tensor, indices: torch.Tensor, seq_len: int, max_tokens: int):
+MERGE_POS_MAX = 65536  # ASPA_MERGE_POS_MAX of the C header
+
+
+def merge_finalise(scores: torch.Tensor, indices: torch.Tensor, seq_len: int, max_tokens: int, want_pos: bool = False):
+    """Returns (keep_idx, keep_scores, count) and, with ``want_pos``, the candidate position of every kept index."""
     dev = scores.device
     table = _empty((seq_len,), torch.int64, dev)
     keep_idx = _empty((max_tokens,), torch.int64, dev)
     keep_sc = _empty((max_tokens,), torch.float32, dev)
+    keep_pos = _empty((max_tokens,), torch.int64, dev) if want_pos else None
     count = _empty((1,), torch.int32, dev)
     with _timed('merge_finalise', 2, _nb(scores, indices)):
         N.check(N.lib().aspa_merge_finalise(N.ptr(scores), N.ptr(indices), scores.numel(), int(seq_len), int(max_tokens),
-                                            N.ptr(table), N.ptr(keep_idx), N.ptr(keep_sc), N.ptr(count), N.stream()),
-                "merge_finalise")
+                                            N.ptr(table), N.ptr(keep_idx), N.ptr(keep_sc), N.ptr(keep_pos), N.ptr(count),
+                                            N.stream()), "merge_finalise")
+    if want_pos:
+        return keep_idx, keep_sc, count, keep_pos
     return keep_idx, keep_sc, count
 
 
-def gather_rows(src2d: torch.Tensor, idx: torch.Tensor, count_dev: Optional[torch.Tensor], max_rows: int) -> torch.Tensor:
+def gather_rows(src2d: torch.Tensor, idx: torch.Tensor, count_dev: Optional[torch.Tensor], max_rows: int,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """dst[i] = src2d[idx[i]] for i < count (all max_rows when count_dev is None); other rows are left as they are."""
     row_bytes = src2d.size(1) * src2d.element_size()
-    dst = _empty((max_rows, src2d.size(1)), src2d.dtype, src2d.device)
+    dst = out if out is not None else _empty((max_rows, src2d.size(1)), src2d.dtype, src2d.device)
     with _timed('gather_rows', 1, 2 * _nb(dst)):
         N.check(N.lib().aspa_gather_rows(N.ptr(src2d), N.ptr(idx), N.ptr(count_dev), int(max_rows), int(row_bytes),
                                          N.ptr(dst), N.stream()), "gather_rows")
+    return dst
+
+
+def rope_relayout_kv(kv: torch.Tensor, H: int, D: int, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor]):
+    """kv (B, T, 2*H*D) -> rotated k and v, both (B*H, T, D)."""
+    B, T, _ = kv.shape
+    k = _empty((B * H, T, D), kv.dtype, kv.device)
+    v = torch.empty_like(k)
+    with _timed('rope_relayout', 1, _nb(kv, k, v)):
+        N.check(N.lib().aspa_rope_relayout_kv(N.ptr(kv), N.dtype_code(kv.dtype), B, T, H, D, N.ptr(cos), N.ptr(sin),
+                                              N.ptr(k), N.ptr(v), N.stream()), "rope_relayout_kv")
+    return k, v
+
+
+def rope_rows_q(q_rows: torch.Tensor, kept_idx: torch.Tensor, count_dev: Optional[torch.Tensor], B: int, T: int, H: int,
+                D: int, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor]) -> torch.Tensor:
+    """Compact query rows -> (B*H, T, D) with only the kept tokens' rows written."""
+    q = _empty((B * H, T, D), q_rows.dtype, q_rows.device)
+    with _timed('rope_rows_q', 1, 2 * _nb(q_rows)):
+        N.check(N.lib().aspa_rope_rows_q(N.ptr(q_rows), N.dtype_code(q_rows.dtype), N.ptr(kept_idx), N.ptr(count_dev),
+                                         q_rows.size(0), B, T, H, D, N.ptr(cos), N.ptr(sin), N.ptr(q), N.stream()),
+                "rope_rows_q")
+    return q
+
+
+def compact_mask(mask_u8: torch.Tensor, capacity: int):
+    """Ordered indices of the non-zero mask bytes: (kept_idx int64 (capacity) padded with n, slot_of int32 (n), count)."""
+    n = mask_u8.numel()
+    dev = mask_u8.device
+    kept_idx = _empty((capacity,), torch.int64, dev)
+    slot_of = _empty((n,), torch.int32, dev)
+    count = _empty((1,), torch.int32, dev)
+    scratch = _empty((int(N.lib().aspa_compact_mask_scratch(n)),), torch.uint8, dev)
+    with _timed('compact_mask', 2, 2 * n + 4 * n + 8 * capacity):
+        N.check(N.lib().aspa_compact_mask(N.ptr(mask_u8), n, int(capacity), N.ptr(kept_idx), N.ptr(slot_of), N.ptr(count),
+                                          N.ptr(scratch), N.stream()), "compact_mask")
+    return kept_idx, slot_of, count
+
+
+def scatter_rows_fill(src2d: torch.Tensor, slot_of: torch.Tensor, mask_u8: torch.Tensor, fill: Optional[torch.Tensor],
+                      n: int) -> torch.Tensor:
+    """(n, C): row i = src2d[slot_of[i]] where mask_u8[i] != 0, else ``fill`` (a (C,) row; None = zeros)."""
+    Cdim = src2d.size(1)
+    dst = _empty((n, Cdim), src2d.dtype, src2d.device)
+    with _timed('scatter_rows_fill', 1, _nb(dst)):
+        N.check(N.lib().aspa_scatter_rows_fill(N.ptr(src2d), N.ptr(slot_of), N.ptr(mask_u8), N.ptr(fill), n,
+                                               Cdim * src2d.element_size(), N.ptr(dst), N.stream()), "scatter_rows_fill")
     return dst

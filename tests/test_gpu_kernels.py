@@ -518,3 +518,74 @@ def test_chunk_select_full_chunk_with_ties(dev):
         assert abs(n - want[1].numel()) <= 1  # the nucleus count may move by one when the mass sits on the cut-off
         m = min(n, want[1].numel())
         assert torch.equal(ix.cpu()[:m], want[1][:m]) and torch.equal(sc.cpu()[:m], want[0][:m])
+
+
+# ---------------------------------------------------------------------------------------------- kept-row compaction
+@pytest.mark.parametrize("n,frac,cap_extra", [(1, 1.0, 0), (2048, 0.5, 7), (2049, 0.05, 0), (70001, 0.3, 100), (300000, 0.01, 1)])
+def test_compact_mask_exact(dev, n, frac, cap_extra):
+    from proteus_flux_attention_b200 import ops
+    g = torch.Generator().manual_seed(n)
+    mask = (torch.rand(n, generator=g) < frac).to(torch.uint8)
+    want = mask.nonzero().view(-1)
+    cap = want.numel() + cap_extra
+    idx, slot_of, cnt = ops.compact_mask(mask.to(dev), cap)
+    assert int(cnt.cpu()) == want.numel()
+    assert torch.equal(idx.cpu()[: want.numel()], want)
+    assert bool((idx.cpu()[want.numel():] == n).all())
+    assert torch.equal(slot_of.cpu()[want].long(), torch.arange(want.numel()))
+    # a capacity below the count drops the tail and still reports the full count
+    if want.numel() > 3:
+        idx2, _, cnt2 = ops.compact_mask(mask.to(dev), want.numel() - 3)
+        assert int(cnt2.cpu()) == want.numel() and torch.equal(idx2.cpu(), want[:-3])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_split_projection_relayout_equals_fused(dev, dtype):
+    from proteus_flux_attention_b200 import ops
+    B, T, H, D = 2, 300, 4, 16
+    C = H * D
+    g = torch.Generator().manual_seed(5)
+    qkv = torch.randn(B, T, 3 * C, generator=g).to(dtype).to(dev)
+    inv = (1.0 / (10000.0 ** (torch.arange(0, D, 2).float() / D))).to(dev)
+    cos, sin = ops.rope_table(inv, T, D, dtype)
+    q0, k0, v0, _ = ops.rope_relayout(qkv, H, D, cos, sin)
+    k1, v1 = ops.rope_relayout_kv(qkv[..., C:].contiguous(), H, D, cos, sin)
+    assert torch.equal(k0, k1) and torch.equal(v0, v1)
+    mask = (torch.rand(B * T, generator=g) < 0.3).to(torch.uint8).to(dev)
+    idx, slot_of, cnt = ops.compact_mask(mask, B * T)
+    rows = ops.gather_rows(qkv.view(B * T, 3 * C)[:, :C].contiguous(), idx, cnt, B * T)
+    q1 = ops.rope_rows_q(rows, idx, cnt, B, T, H, D, cos, sin)
+    keep = mask.view(B, 1, T).bool().expand(B, H, T).reshape(B * H, T)
+    assert torch.equal(q0[keep], q1[keep])
+    # without rotation: a pure relayout
+    k2, v2 = ops.rope_relayout_kv(qkv[..., C:].contiguous(), H, D, None, None)
+    assert torch.equal(v2, v0) and torch.equal(k2.view(B, H, T, D).permute(0, 2, 1, 3).reshape(B, T, C), qkv[..., C:2 * C])
+
+
+def test_scatter_rows_fill(dev):
+    from proteus_flux_attention_b200 import ops
+    g = torch.Generator().manual_seed(9)
+    n, C = 1000, 64
+    mask = (torch.rand(n, generator=g) < 0.4).to(torch.uint8).to(dev)
+    idx, slot_of, cnt = ops.compact_mask(mask, n)
+    k = int(cnt.cpu())
+    rows = torch.randn(n, C, generator=g).bfloat16().to(dev)
+    fill = torch.randn(C, generator=g).bfloat16().to(dev)
+    for f in (fill, None):
+        got = ops.scatter_rows_fill(rows, slot_of, mask, f, n)
+        want = (f if f is not None else torch.zeros(C, dtype=torch.bfloat16, device=dev)).expand(n, C).clone()
+        want[idx[:k]] = rows[:k]
+        assert torch.equal(got, want)
+
+
+def test_merge_finalise_reports_candidate_positions(dev):
+    from proteus_flux_attention_b200 import ops
+    g = torch.Generator().manual_seed(13)
+    n, seq_len, keep = 20000, 100000, 6000
+    idx = torch.randint(0, seq_len, (n,), generator=g)
+    idx[::7] = -1  # unused slots
+    sc = torch.rand(n, generator=g)
+    ki, ks, kc, kp = ops.merge_finalise(sc.to(dev), idx.to(dev), seq_len, keep, want_pos=True)
+    cnt = int(kc.cpu())
+    ki, ks, kp = ki.cpu()[:cnt], ks.cpu()[:cnt], kp.cpu()[:cnt]
+    assert torch.equal(idx[kp], ki) and torch.equal(sc[kp], ks)

@@ -329,3 +329,32 @@ def test_chunked_scoring_only_equals_full_forward(dev):
                         final_weights=fs)
     assert torch.equal(a.keep_indices, ora["keep_indices"])
     assert torch.allclose(a.final_output.cpu(), ora["final_output"], atol=1e-5, rtol=1e-4)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_projection_on_kept_rows_equals_full_projection(dev, dtype):
+    """Projecting q / the output for kept tokens only must give what projecting every token gives."""
+    import proteus_flux_attention_b200 as P
+    cfg = dict(d_model=128, n_head=8, attn_h_total=8, attn_gates=8, attn_h_active=2, attn_h_active_min=2, attn_h_active_max=2,
+               attn_token_sparse=True, attn_token_keep_ratio=0.3, attn_mode="auto", attn_small_seq_dense=0,
+               attn_router_top_p=0.0, attn_use_rope=True, n_ctx=1024, attn_proto_enable=True, bias=True)
+    torch.manual_seed(3)
+    layer = P.AdaptiveSparseProtoAttention(P.ModelConfig(**cfg)).to(dtype).to(dev).eval()
+    with torch.no_grad():
+        layer.proj.bias.normal_()
+        layer.qkv.bias.normal_()
+    state = {k: v.clone() for k, v in layer.state_dict().items()}
+    x = torch.randn(2, 700, 128, device=dev).to(dtype)
+    outs, cons = [], []
+    for flag in (True, False):
+        layer.load_state_dict(state)
+        layer.compact_projection = flag
+        outs.append(layer(x).float())
+        cons.append(layer.last_head_consensus.float())
+    tol = 1e-4 if dtype == torch.float32 else 3e-2
+    assert float((outs[0] - outs[1]).abs().max()) <= tol
+    assert float((cons[0] - cons[1]).abs().max()) <= tol
+    kept = layer._last_token_mask
+    assert 0 < int(kept.sum()) < kept.numel()
+    # rows of dropped tokens are exactly the projection bias
+    assert torch.equal(outs[0][~kept], layer.proj.bias.float().expand_as(outs[0])[~kept])
