@@ -48,7 +48,7 @@ class ClockSampler:
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index: int, period_ms: int = 10):
+    def __init__(self, index: int, period_ms: int = 200):
         import datetime
         self.dt = datetime
         self.t0 = self.t1 = None

@@ -273,7 +273,8 @@ int aspa_merge_finalise(const float* scores, const int64_t* indices, int64_t n, 
                         int max_tokens, void* table, int64_t* keep_idx, float* keep_scores, int64_t* keep_pos,
                         int32_t* keep_count, void* stream);
 
-/* Gather rows src[idx[i], :] -> dst[i, :] (cs.py:688-689). row_bytes multiple of 16. */
+/* Gather rows src[idx[i], :] -> dst[i, :] (cs.py:688-689); a negative index gives a row of zeros; rows
+ * i >= *count_dev (when count_dev is given) are left untouched.  row_bytes multiple of 16. */
 int aspa_gather_rows(const void* src, const int64_t* idx, const int32_t* count_dev, int64_t max_rows,
                      int64_t row_bytes, void* dst, void* stream);
 

@@ -462,11 +462,11 @@ class ChunkedShortlistRunner:
         kept index, its position in the chunk-major list of all promotions (chunk * budget + rank within the chunk)."""
         if world == 1:
             return ops.gather_rows(pool, keep_pos, None, k).unsqueeze(0)
+        # every rank fills the rows it holds and leaves zeros elsewhere; the sum over ranks is the full sequence
         lo, hi = c_lo * budget, c_hi * budget
-        local = keep_pos[(keep_pos >= lo) & (keep_pos < hi)] - lo
-        rows = ops.gather_rows(pool, local.contiguous(), None, int(local.numel())) if local.numel() else \
-            pool.new_zeros((0, pool.size(1)))
-        return dist_utils.all_gather_rows(self.group, rows, k, world).unsqueeze(0)
+        local = torch.where((keep_pos >= lo) & (keep_pos < hi), keep_pos - lo, torch.full_like(keep_pos, -1))
+        rows = ops.gather_rows(pool, local, None, k)
+        return dist_utils.sum_disjoint_rows(self.group, rows, world).unsqueeze(0)
 
     def _gather_reduced(self, source: torch.Tensor, source_off: int, keep_idx: torch.Tensor, k: int,
                         device: torch.device, world: int, rank: int, c_lo: int, c_hi: int) -> torch.Tensor:
@@ -477,16 +477,18 @@ class ChunkedShortlistRunner:
             if source.is_cuda:
                 return ops.gather_rows(source[0], keep_idx, None, k).unsqueeze(0)
             return source[:, keep_idx.cpu()].to(device, non_blocking=True)
-        # sharded input: every rank contributes the kept rows that fall inside its own chunks
+        # sharded input: every rank fills the kept rows that fall inside its own chunks and leaves zeros elsewhere;
+        # the sum over ranks is the full reduced sequence
         lo, hi = c_lo * cfg.chunk_len, min(cfg.seq_len, c_hi * cfg.chunk_len)
-        mine = (keep_idx >= lo) & (keep_idx < hi)
-        local_idx = (keep_idx[mine] - source_off)
+        local_idx = torch.where((keep_idx >= lo) & (keep_idx < hi), keep_idx - source_off, torch.full_like(keep_idx, -1))
         if source.is_cuda:
-            rows = ops.gather_rows(source[0], local_idx.contiguous(), None, int(local_idx.numel())) if local_idx.numel() else \
-                source.new_zeros((0, cfg.d_model))
+            rows = ops.gather_rows(source[0], local_idx, None, k)
         else:
-            rows = source[0, local_idx.cpu()].to(device)
-        return dist_utils.all_gather_rows(self.group, rows, k, world).unsqueeze(0)
+            li = local_idx.cpu()
+            rows = torch.zeros((k, cfg.d_model), dtype=source.dtype)
+            rows[li >= 0] = source[0, li[li >= 0]]
+            rows = rows.to(device)
+        return dist_utils.sum_disjoint_rows(self.group, rows, world).unsqueeze(0)
 
 
 __all__ = ["ChunkedShortlistConfig", "ChunkedShortlistMetrics", "ChunkedShortlistResult", "ChunkedShortlistRunner",

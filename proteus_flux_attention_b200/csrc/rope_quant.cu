@@ -259,7 +259,8 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const uint4* __restric
   const int64_t total = rows * vec_per_row;
   for (int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; g < total; g += (int64_t)gridDim.x * blockDim.x) {
     const int64_t r = g / vec_per_row, c = g % vec_per_row;
-    dst[g] = src[idx[r] * vec_per_row + c];
+    const int64_t i = idx[r];
+    dst[g] = i >= 0 ? src[i * vec_per_row + c] : make_uint4(0u, 0u, 0u, 0u);
   }
 }
 

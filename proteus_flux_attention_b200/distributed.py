@@ -58,13 +58,38 @@ def all_gather_records(group: Any, scores: torch.Tensor, idx: torch.Tensor, coun
         recv = torch.empty((world * s.shape[0],) + tuple(s.shape[1:]), dtype=s.dtype, device=s.device)
         dist.all_gather_into_tensor(recv, s.contiguous(), group=group)
         outs.append(recv)
-    keep = []
-    for r in range(world):
-        rlo, rhi = partition_chunks(n_chunks, world, r)
-        keep.extend(r * cap + j for j in range(rhi - rlo))
-    sel = torch.tensor(keep, dtype=torch.long, device=scores.device)
+    if cap * world == n_chunks:  # every rank owns `cap` chunks: the concatenation is already in chunk order
+        return outs[0].view(n_chunks, budget), outs[1].view(n_chunks, budget), outs[2].view(n_chunks)
+    sel = _padding_free_rows(n_chunks, world, cap, scores.device)
     return (outs[0].view(world * cap, budget)[sel].contiguous(), outs[1].view(world * cap, budget)[sel].contiguous(),
             outs[2].view(world * cap)[sel].contiguous())
+
+
+_SEL_CACHE: dict = {}
+
+
+def _padding_free_rows(n_chunks: int, world: int, cap: int, device: torch.device) -> torch.Tensor:
+    """Rows of the (world * cap) gathered layout that hold real chunks; built once per shape (an upload from the
+    host stalls the stream)."""
+    key = (n_chunks, world, cap, str(device))
+    sel = _SEL_CACHE.get(key)
+    if sel is None:
+        keep = []
+        for r in range(world):
+            rlo, rhi = partition_chunks(n_chunks, world, r)
+            keep.extend(r * cap + j for j in range(rhi - rlo))
+        sel = torch.tensor(keep, dtype=torch.long, device=device)
+        _SEL_CACHE[key] = sel
+    return sel
+
+
+def sum_disjoint_rows(group: Any, rows: torch.Tensor, world: int) -> torch.Tensor:
+    """All-reduce (sum) of per-rank (k, C) row blocks in which every row is non-zero on at most one rank: each rank
+    fills the kept rows it owns and leaves the others zero, so the sum is the complete reduced sequence, exactly
+    (x + 0 is exact in every float format).  Fixed shapes, no host synchronisation."""
+    if world > 1:
+        dist.all_reduce(rows, op=dist.ReduceOp.SUM, group=group)
+    return rows
 
 
 def all_gather_rows(group: Any, rows: torch.Tensor, total: int, world: int) -> torch.Tensor:

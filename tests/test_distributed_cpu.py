@@ -62,6 +62,11 @@ def _worker(rank, world, port, n_chunks, chunk_len, budget, buffer_tokens, seed,
         shard = seq[0, lo * chunk_len: hi * chunk_len]
         rows = shard[keep_idx[mine] - lo * chunk_len]
         reduced = D.all_gather_rows(None, rows, keep_idx.numel(), world)
+        # the exchange the runner uses: every rank fills its own rows, zeros elsewhere, then a sum over ranks
+        filled = torch.zeros(keep_idx.numel(), seq.size(2))
+        filled[mine] = rows
+        summed = D.sum_disjoint_rows(None, filled, world)
+        assert torch.equal(summed, reduced)
         out_q.put((rank, a_ct.tolist(), keep_idx.tolist(), reduced.clone()))
     finally:
         dist.destroy_process_group()

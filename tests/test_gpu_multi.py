@@ -1,5 +1,5 @@
 """Two-GPU test of the sharded chunked pipeline: ranks own disjoint chunk ranges, exchange promotion
-records and kept rows with NCCL all-gather, and must reproduce the single-GPU result bit for bit.
+records with NCCL all-gather and kept rows with an all-reduce of disjoint rows, and must reproduce the single-GPU result bit for bit.
 Skipped when fewer than two CUDA devices are visible.  NVLS is switched off for the child processes."""
 import os
 import socket
@@ -44,10 +44,12 @@ def _worker(rank, world, port, q):
         cs, fs = _states()
         seq = torch.randn(1, 5 * 2048, 256, generator=torch.Generator().manual_seed(9)).to(torch.bfloat16)
         lo, hi = D.partition_chunks(5, world, rank)
-        shard = seq[:, lo * 2048: hi * 2048].to(dev)
-        res = P.ChunkedShortlistRunner(_cfg(dev), process_group=dist.group.WORLD).run(
-            shard, chunk_state=cs, final_state=fs, sequence_is_local_shard=True)
-        q.put((rank, res.keep_indices.clone(), res.final_output.float().cpu(), res.reduced_sequence.float().cpu()))
+        shard = seq[:, lo * 2048: hi * 2048].contiguous()
+        for where, src in (("hbm", shard.to(dev)), ("host", shard.pin_memory())):  # resident shard, streamed shard
+            res = P.ChunkedShortlistRunner(_cfg(dev), process_group=dist.group.WORLD).run(
+                src, chunk_state=cs, final_state=fs, sequence_is_local_shard=True)
+            q.put((rank, where, res.keep_indices.clone(), res.final_output.float().cpu(),
+                   res.reduced_sequence.float().cpu()))
     finally:
         dist.destroy_process_group()
 
@@ -67,11 +69,12 @@ def test_two_gpu_sharding_equals_single_gpu():
     procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
     for p in procs:
         p.start()
-    results = [q.get(timeout=300) for _ in procs]
+    results = [q.get(timeout=300) for _ in range(2 * len(procs))]
     for p in procs:
         p.join(timeout=120)
         assert p.exitcode == 0
-    for rank, keep, out, red in results:
+    assert sorted((r[0], r[1]) for r in results) == [(0, "hbm"), (0, "host"), (1, "hbm"), (1, "host")]
+    for rank, where, keep, out, red in results:
         assert torch.equal(keep, want.keep_indices)
         assert torch.equal(red, want.reduced_sequence.float().cpu())
         assert torch.equal(out, want.final_output.float().cpu())
