@@ -113,6 +113,9 @@ class SwitchRouter(nn.Module):
 
 
 # ---- config parsing helpers ------------------------------------------------------------------
+_SIDE_STREAMS: Dict[str, "torch.cuda.Stream"] = {}  # one second stream per device, shared by all layers
+
+
 def _num(config, name, default, kind=float):
     """``kind(getattr(config, name, default) or default)`` — zero and None select the default."""
     return kind(getattr(config, name, default) or default)
@@ -534,21 +537,49 @@ class AdaptiveSparseAttention(nn.Module):
                                  None if want_amax else q_keep,
                                  q_fraction=float(self._token_keep_ratio_runtime or 1.0))
 
-    def _project_compact(self, x: torch.Tensor, compact: dict):
-        """k, v for every token and q for the kept tokens only; the q rows of dropped tokens stay unwritten."""
+    def _fork_kv_projection(self, x: torch.Tensor) -> dict:
+        """K/V projection + RoPE/relayout of every token on a second stream.  Nothing in it depends on the routing
+        chain (router, token keep, head choice, packing), whose kernels are small or latency-bound and leave most of
+        the GPU idle; the two run side by side and meet before the attention.  The outputs are allocated on the
+        calling stream, so the allocator's stream bookkeeping stays with the caller."""
+        B, T, C = x.shape
+        H, D = self.h_total, self.d_head
+        dev = x.device
+        w, b = self.qkv.weight, self.qkv.bias
+        kv = torch.empty((B * T, 2 * C), dtype=x.dtype, device=dev)
+        k = torch.empty((B * H, T, D), dtype=x.dtype, device=dev)
+        v = torch.empty_like(k)
+        cos = sin = None
+        if self.use_rope:
+            cos, sin = self._rope_factors(T, dev, x.dtype)
+        main = torch.cuda.current_stream()
+        side = _SIDE_STREAMS.get(str(dev))
+        if side is None:
+            side = _SIDE_STREAMS[str(dev)] = torch.cuda.Stream(device=dev)
+        ready, done = torch.cuda.Event(), torch.cuda.Event()
+        ready.record(main)
+        side.wait_event(ready)
+        with torch.cuda.stream(side):
+            if b is None:
+                torch.mm(x.view(B * T, C), w[C:].t(), out=kv)
+            else:
+                torch.addmm(b[C:], x.view(B * T, C), w[C:].t(), out=kv)
+            ops.rope_relayout_kv(kv.view(B, T, 2 * C), H, D, cos, sin, out=(k, v))
+            done.record(side)
+        return {"k": k, "v": v, "kv": kv, "done": done}
+
+    def _project_compact_q(self, x: torch.Tensor, compact: dict) -> torch.Tensor:
+        """q for the kept tokens only; the q rows of dropped tokens stay unwritten."""
         B, T, C = x.shape
         H, D = self.h_total, self.d_head
         w, b = self.qkv.weight, self.qkv.bias
         x_rows = ops.gather_rows(x.view(B * T, C), compact["idx"], compact["count"], compact["slots"],
                                  out=torch.zeros((compact["slots"], C), dtype=x.dtype, device=x.device))
         q_rows = F.linear(x_rows, w[:C], None if b is None else b[:C])
-        kv = F.linear(x, w[C:], None if b is None else b[C:])
         cos = sin = None
         if self.use_rope:
             cos, sin = self._rope_factors(T, x.device, x.dtype)
-        k, v = ops.rope_relayout_kv(kv, H, D, cos, sin)
-        q = ops.rope_rows_q(q_rows, compact["idx"], compact["count"], B, T, H, D, cos, sin)
-        return q, k, v
+        return ops.rope_rows_q(q_rows, compact["idx"], compact["count"], B, T, H, D, cos, sin)
 
     @property
     def last_head_consensus(self) -> Optional[torch.Tensor]:
@@ -743,6 +774,34 @@ class AdaptiveSparseAttention(nn.Module):
         else:
             self._token_keep_ratio_runtime = None
 
+        # host-side arithmetic of the token keep (aspa.py:806-829): how many tokens can survive is known before any
+        # kernel runs, which lets the K/V projection start on a second stream beside the routing chain
+        keep_all = need = guard = 0
+        kept_bound = T          # upper bound on kept tokens per batch element
+        bound_known = True
+        if self.token_sparse:
+            ratio = float(self._token_keep_ratio_runtime)
+            keep_all = ratio >= 0.999 and self.token_keep_threshold <= 0.0
+            if not keep_all:
+                guard = min(max(0, self.token_keep_guard), T)
+                min_keep = max(min(max(0, self.token_keep_min), T), guard)
+                need = _py_round_f32(ratio * T)
+                if min_keep > 0:
+                    need = max(need, min_keep)
+                need = max(1, min(need, T))
+                kept_bound = min(T, max(need, guard) + guard)
+                bound_known = self.token_keep_threshold <= 0.0
+        use_quant = bool(self.quantize_sparse_int8 and not self.training)
+        # Queries and outputs only exist for kept tokens (every path below computes rows of kept tokens only, and
+        # the rows of dropped tokens reach the output projection as zeros): with a known bound on the kept count
+        # the query projection, the attention output and the output projection run on the kept rows alone.
+        # INT8 scales are taken over the queries of every token (aspa.py:1328), so that mode projects them all.
+        will_compact = (self.compact_projection and self.token_sparse and not keep_all and bound_known
+                        and not use_quant and 4 * kept_bound <= 3 * T and not self.training)
+        # started before the router: launched after it, the projection's CTAs starve the cluster launches of the
+        # token keep (measured: 158 us instead of 40 us per call)
+        kv_fork = self._fork_kv_projection(x) if will_compact else None
+
         # 1. router
         x2d = x.view(B * T, C)
         proto_hat = conf_eps = usage_bias = None
@@ -760,25 +819,13 @@ class AdaptiveSparseAttention(nn.Module):
         self._last_token_similarity = sim.view(B, T) if sim is not None else None
         self._last_token_blend = bs.view(B, T) if bs is not None else None
         self._last_token_importance = imp.view(B, T)
-
         # 2. token keep
         token_mask_u8 = kept = None
-        kept_bound = T          # host-side upper bound on kept tokens per batch element
-        bound_known = True
         if self.token_sparse:
-            ratio = float(self._token_keep_ratio_runtime)
-            if ratio >= 0.999 and self.token_keep_threshold <= 0.0:
+            if keep_all:
                 token_mask_u8 = torch.ones((B, T), dtype=torch.uint8, device=dev)
             else:
-                guard = min(max(0, self.token_keep_guard), T)
-                min_keep = max(min(max(0, self.token_keep_min), T), guard)
-                need = _py_round_f32(ratio * T)
-                if min_keep > 0:
-                    need = max(need, min_keep)
-                need = max(1, min(need, T))
                 token_mask_u8, kept = ops.token_select(self._last_token_importance, need, self.token_keep_threshold, guard)
-                kept_bound = min(T, max(need, guard) + guard)
-                bound_known = self.token_keep_threshold <= 0.0
             self._last_token_mask = token_mask_u8.view(torch.bool)
 
         # 3. head budget and per-token head choice
@@ -823,19 +870,15 @@ class AdaptiveSparseAttention(nn.Module):
                "token_idx": token_idx, "row_offsets": row_offsets, "exec_mode": "shortlist"}
 
         # 5. projection + RoPE + head-major relayout (does not depend on the record)
-        use_quant = bool(self.quantize_sparse_int8 and not self.training)
-        # Queries and outputs only exist for kept tokens (every path below computes rows of kept tokens only, and
-        # the rows of dropped tokens reach the output projection as zeros): with a known bound on the kept count
-        # the query projection, the attention output and the output projection run on the kept rows alone.
-        # INT8 scales are taken over the queries of every token (aspa.py:1328), so that mode projects them all.
         compact = None
-        if (self.compact_projection and token_mask_u8 is not None and kept is not None and bound_known
-                and not use_quant and 4 * kept_bound <= 3 * T and not self.training):
+        if will_compact:
             n_slots = B * kept_bound
             kept_idx, slot_of, kept_cnt = ops.compact_mask(token_mask_u8.view(-1), n_slots)
             compact = {"idx": kept_idx, "slot_of": slot_of, "count": kept_cnt, "slots": n_slots,
                        "mask": token_mask_u8.view(-1)}
-            q, k, v = self._project_compact(x, compact)
+            q = self._project_compact_q(x, compact)
+            k, v = kv_fork["k"], kv_fork["v"]
+            torch.cuda.current_stream().wait_event(kv_fork["done"])
             amax = None
         else:
             # queries of dropped tokens are never used: skip their relayout

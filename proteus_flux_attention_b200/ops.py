@@ -356,11 +356,15 @@ def gather_rows(src2d: torch.Tensor, idx: torch.Tensor, count_dev: Optional[torc
     return dst
 
 
-def rope_relayout_kv(kv: torch.Tensor, H: int, D: int, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor]):
+def rope_relayout_kv(kv: torch.Tensor, H: int, D: int, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
+                     out: Optional[Tuple[torch.Tensor, torch.Tensor]] = None):
     """kv (B, T, 2*H*D) -> rotated k and v, both (B*H, T, D)."""
     B, T, _ = kv.shape
-    k = _empty((B * H, T, D), kv.dtype, kv.device)
-    v = torch.empty_like(k)
+    if out is not None:
+        k, v = out
+    else:
+        k = _empty((B * H, T, D), kv.dtype, kv.device)
+        v = torch.empty_like(k)
     with _timed('rope_relayout', 1, _nb(kv, k, v)):
         N.check(N.lib().aspa_rope_relayout_kv(N.ptr(kv), N.dtype_code(kv.dtype), B, T, H, D, N.ptr(cos), N.ptr(sin),
                                               N.ptr(k), N.ptr(v), N.stream()), "rope_relayout_kv")
