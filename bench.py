@@ -39,26 +39,55 @@ SEQ_1M, CHUNK, BUDGET, BUFFER, D_MODEL, HEADS = 1 << 20, 65536, 2048, 32768, 102
 
 
 # ----------------------------------------------------------------------------------------------- helpers
+_NVML_CHILD = r"""
+import sys, time, datetime
+import pynvml as nv
+nv.nvmlInit()
+target, period = sys.argv[1], float(sys.argv[2])
+try:
+    h = nv.nvmlDeviceGetHandleByUUID(target.encode() if target.startswith("GPU-") else target)
+except Exception:
+    h = nv.nvmlDeviceGetHandleByIndex(int(target) if target.isdigit() else 0)
+mx = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+get = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or nv.nvmlDeviceGetCurrentClocksThrottleReasons
+while True:
+    sm = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
+    r = int(get(h))
+    f = lambda bit: "Active" if r & bit else "Not Active"
+    # NVML reason bits: 0x8 hw slowdown, 0x40 hw thermal slowdown, 0x20 sw thermal slowdown, 0x4 sw power cap
+    print(datetime.datetime.now().strftime("%Y/%m/%d %H:%M:%S.%f"), sm, mx, hex(r), f(0x8), f(0x40), f(0x20), f(0x4),
+          sep=", ", flush=True)
+    time.sleep(period)
+"""
+
+
 class ClockSampler:
-    """SM clock and throttle reasons from one `nvidia-smi -lms` process that runs beside the benchmark (a sampling
-    thread in this process would compete for the interpreter lock with the timed loop).  Start it early - the tool
-    needs a moment before its first line - and mark the timed region with begin()/end(); only samples whose
-    timestamps fall inside that window are summarised."""
+    """SM clock and throttle reasons, sampled by a separate process while the benchmark runs (a sampling thread in
+    this process competes for the interpreter lock with the timed loop).  `nvml`: a small python child polling NVML;
+    `smi`: one `nvidia-smi -lms` process.  Start it early - either needs a moment before its first line - and mark
+    the timed region with begin()/end(); only samples whose timestamps fall inside that window are summarised."""
     Q = ("timestamp,clocks.sm,clocks.max.sm,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index: int, period_ms: int = 200):
+    def __init__(self, index: int, kind: str = "nvml", period_ms: int = 20):
         import datetime
         self.dt = datetime
         self.t0 = self.t1 = None
+        self.kind = kind
+        self.proc = None
         try:
             gpu = "GPU-" + str(torch.cuda.get_device_properties(index).uuid)
         except Exception:
             gpu = str(index)
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", gpu, f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", str(period_ms)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            if kind == "nvml":
+                self.proc = subprocess.Popen([sys.executable, "-c", _NVML_CHILD, gpu, str(period_ms / 1e3)],
+                                             stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            elif kind == "smi":
+                self.proc = subprocess.Popen(["nvidia-smi", "-i", gpu, f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                              "-lms", str(period_ms)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL,
+                                             text=True)
         except Exception:
             self.proc = None
 
@@ -101,7 +130,7 @@ class ClockSampler:
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         reasons = [n for i, n in enumerate(names) if any(r[3 + i].lower().startswith("active") for r in rows)]
         return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": float(rows[0][1]),
-                "reasons": reasons, "samples": len(rows), "window": window}
+                "reasons": reasons, "samples": len(rows), "window": window, "sampler": self.kind}
 
 
 def peak_hbm():
@@ -288,6 +317,9 @@ def main():
     ap.add_argument("--workload", default="chunked_1m", choices=["chunked_1m", "shortlist_256k", "sparse_16k"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--clock-sampler", default="nvml", choices=["nvml", "smi", "none"],
+                    help="how SM clocks / throttle reasons are sampled during the timed region")
+    ap.add_argument("--clock-period-ms", type=int, default=20)
     ap.add_argument("--profile-mode", action="store_true",
                     help="for runs under a profiler: exactly --warmup + --steps passes, no timing pass, e2e or CPU baseline")
     args = ap.parse_args()
@@ -340,7 +372,7 @@ def main():
         if rank == 0:
             print(json.dumps({"profile_mode": True, "workload": args.workload, "passes": args.warmup + args.steps}))
         return
-    clocks = ClockSampler(local_rank)
+    clocks = ClockSampler(local_rank, args.clock_sampler, args.clock_period_ms)
     for _ in range(max(3, args.warmup)):
         wl.step()
     sync()

@@ -91,6 +91,16 @@ int aspa_normalize_rows(const float* src, int rows, int cols, float eps, float* 
 int aspa_token_select(const float* importance, int B, int T, int need, float threshold, int guard,
                       uint8_t* token_mask, int32_t* kept, void* stream);
 
+/* Token keep plus the ordered list of kept tokens in one launch (no reference counterpart: the reference indexes
+ * with the boolean mask, aspa.py:1715-1721).  Batch row b owns slots [b*slots_per_row, (b+1)*slots_per_row):
+ *   kept_idx (B*slots_per_row) int64: flat index b*T + t of the kept tokens of row b, ascending, padded with -1;
+ *   slot_of (B*T) int32: slot of every kept token (entries of dropped tokens are left unwritten).
+ * Kept tokens beyond slots_per_row are dropped from kept_idx (kept[] still counts them).  T <= ASPA_TOKEN_COMPACT_MAX_T. */
+#define ASPA_TOKEN_COMPACT_MAX_T 65536
+int aspa_token_select_compact(const float* importance, int B, int T, int need, float threshold, int guard,
+                              uint8_t* token_mask, int32_t* kept, int64_t* kept_idx, int32_t* slot_of,
+                              int slots_per_row, void* stream);
+
 /* Column sums of gate_probs mapped to heads, then the nucleus head count and the
  * blended per-token head budget, all on the device.
  * Replaces _nucleus_head_count (aspa.py:749-780) and the budget blend (aspa.py:1575-1586).
@@ -119,6 +129,14 @@ int aspa_head_select(const float* gate_probs, int64_t n, int G, const int32_t* g
 int64_t aspa_pack_rows_scratch(int B, int H, int T);
 int aspa_pack_rows(const uint64_t* head_bits, int B, int T, int H, int32_t* seg_scratch,
                    int32_t* row_offsets, int32_t* token_idx, int64_t capacity, void* stream);
+
+/* aspa_head_select followed by aspa_pack_rows in fewer launches: when T is a multiple of 256 the head choice
+ * counts the rows of every (head, 256-token segment) itself, which is the first phase of the packing.
+ * gate_probs (B*T, G); the other arguments as in the two separate calls. */
+int aspa_head_select_pack(const float* gate_probs, int B, int T, int G, const int32_t* gate_to_head, int H, int k_host,
+                          const int32_t* k_dev, int kmax, const uint8_t* token_mask, uint64_t* head_bits,
+                          int32_t* top_idx, float* top_score, float* stat_partials, int32_t* seg_scratch,
+                          int32_t* row_offsets, int32_t* token_idx, int64_t capacity, void* stream);
 
 /* aspa_pack_rows for callers that cannot provide scratch memory.  It has no counterpart in the
  * reference: it exists for hosts that must not allocate at call time — a serving loop whose device
@@ -166,6 +184,10 @@ int aspa_rope_relayout(const void* qkv, int dtype, int B, int T, int H, int D, c
  *   i >= *count_dev or an index outside [0, B*T) are skipped) -> rotated into q (B*H, T, D). */
 int aspa_rope_relayout_kv(const void* kv, int dtype, int B, int T, int H, int D, const float* cos_t,
                           const float* sin_t, void* k, void* v, void* stream);
+/* RoPE in place on rows that stay where the projection wrote them: x points at the first row, rows are H*D wide
+ * and `row_stride` elements apart, row r belongs to position r % T. */
+int aspa_rope_inplace(void* x, int dtype, int64_t n_rows, int T, int64_t row_stride, int H, int D, const float* cos_t,
+                      const float* sin_t, void* stream);
 int aspa_rope_rows_q(const void* q_rows, int dtype, const int64_t* kept_idx, const int32_t* count_dev,
                      int64_t max_rows, int B, int T, int H, int D, const float* cos_t, const float* sin_t, void* q,
                      void* stream);
@@ -233,16 +255,27 @@ int aspa_gather_attn_fwd(const void* q, const void* k, const void* v, int qkv_dt
                          const aspa_shortlist_plan* plan, const float* add_mask, void* out, int out_dtype,
                          int out_layout, void* workspace, void* stream);
 
-/* Same call with the token-major output rows redirected: row b*T + t of `out` becomes row
- * out_row_map[b*T + t] (the compact slot of a kept token, from aspa_compact_mask), so that the output
- * projection runs over kept tokens only.  No reference counterpart: the reference projects every row,
- * dropped tokens included (aspa.py:1854).  out_row_map NULL = aspa_gather_attn_fwd. */
-int aspa_gather_attn_fwd_mapped(const void* q, const void* k, const void* v, int qkv_dtype, const float* q_scale,
-                                const float* k_scale, const float* v_scale, int heads, int T, int D, int H,
-                                const int32_t* row_offsets, const int32_t* token_idx, int max_rows,
-                                int64_t total_rows, const int64_t* cand, const int64_t* cand_len, int L,
-                                const aspa_shortlist_plan* plan, const float* add_mask, void* out, int out_dtype,
-                                int out_layout, const int32_t* out_row_map, void* workspace, void* stream);
+/* Element strides of k and v: row of (batch b, head h, token t) starts at b*batch + h*head + t*token.
+ * Head-major (heads, T, D) is {H*T*D, T*D, D}; the k half of a fused (B, T, 2, H, D) projection is
+ * {T*2*H*D, D, 2*H*D}.  Every row start must stay 16-byte aligned. */
+typedef struct aspa_kv_layout {
+  int64_t k_batch, k_head, k_token;
+  int64_t v_batch, v_head, v_token;
+} aspa_kv_layout;
+
+/* aspa_gather_attn_fwd with two extras (no reference counterpart for either):
+ *   out_row_map (B*T) int32 or NULL: row b*T + t of the token-major `out` becomes row out_row_map[b*T + t]
+ *   (the compact slot of a kept token, from aspa_compact_mask), so that the output projection runs over kept
+ *   tokens only — the reference projects every row, dropped tokens included (aspa.py:1854);
+ *   kv_layout or NULL: k and v read where the projection left them instead of from head-major copies (the
+ *   reference permutes them, aspa.py:1644-1656).  Needs H > 0. */
+int aspa_gather_attn_fwd_ex(const void* q, const void* k, const void* v, int qkv_dtype, const float* q_scale,
+                            const float* k_scale, const float* v_scale, int heads, int T, int D, int H,
+                            const int32_t* row_offsets, const int32_t* token_idx, int max_rows,
+                            int64_t total_rows, const int64_t* cand, const int64_t* cand_len, int L,
+                            const aspa_shortlist_plan* plan, const float* add_mask, void* out, int out_dtype,
+                            int out_layout, const int32_t* out_row_map, const aspa_kv_layout* kv_layout,
+                            void* workspace, void* stream);
 
 /* Prototype EMA (aspa.py:692-718): counts = sum_t probs; mean = probs^T x / counts;
  * prototypes, usage and confidence updated in place for gates with counts > 1e-6.
@@ -292,6 +325,18 @@ int aspa_compact_mask(const uint8_t* mask, int64_t n, int64_t capacity, int64_t*
  * bias it equals projecting an all-zero row (aspa.py:1854).  row_bytes multiple of 16. */
 int aspa_scatter_rows_fill(const void* src, const int32_t* slot_of, const uint8_t* mask, const void* fill, int64_t n,
                            int64_t row_bytes, void* dst, void* stream);
+
+/* One fp64 record of a layer call for a single device-to-host copy (the reference reads these values with
+ * some twenty .item() calls, aspa.py:1560-1640, 1856-1916):
+ *   [row_offsets (n_offsets) | kept (n_kept) | k, adaptive k | selected-score sum, entropy sum |
+ *    prototype similarity sum, blend sum, blended-token count | router status]
+ * kept NULL -> kept_fill; k_dev NULL -> k_fill (both entries); head_partials (2 * head_blocks) and
+ * proto_partials (3 * proto_blocks, may be NULL -> zeros) are the per-block partial sums written by
+ * aspa_head_select and the router; status (1) int32 or NULL.  record: n_offsets + n_kept + 8 doubles. */
+int aspa_stats_record(const int32_t* row_offsets, int n_offsets, const int32_t* kept, int n_kept, double kept_fill,
+                      const int32_t* k_dev, double k_fill, const float* head_partials, int64_t head_blocks,
+                      const float* proto_partials, int64_t proto_blocks, const int32_t* status, double* record,
+                      void* stream);
 
 /* Deterministic sum of per-block partials: out[j] = sum_i partials[j * n_blocks + i]. */
 int aspa_reduce_partials(const float* partials, int n_series, int64_t n_blocks, float* out, void* stream);

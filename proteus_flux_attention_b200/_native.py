@@ -28,6 +28,12 @@ class ShortlistPlan(C.Structure):
                 ("proto_lists", C.c_void_p), ("proto_limit", C.c_void_p)]
 
 
+class KVLayout(C.Structure):
+    """Mirror of ``aspa_kv_layout``: element strides (batch, head, token) of k and of v."""
+    _fields_ = [("k_batch", C.c_int64), ("k_head", C.c_int64), ("k_token", C.c_int64),
+                ("v_batch", C.c_int64), ("v_head", C.c_int64), ("v_token", C.c_int64)]
+
+
 # name -> (restype, argtypes); must list every symbol of include/aspa_b200.h
 SIGNATURES = {
     "aspa_last_error_string": (C.c_char_p, []),
@@ -58,8 +64,9 @@ SIGNATURES = {
     "aspa_proto_ema_update": (_i, [_p, _i, _l, _i, _p, _i, _d, _p, _p, _p, _p, _p, _p]),
     "aspa_chunk_select": (_i, [_p, _p, _i, _i, _f, _l, _p, _p, _p, _p]),
     "aspa_merge_finalise": (_i, [_p, _p, _l, _l, _i, _p, _p, _p, _p, _p, _p]),
-    "aspa_gather_attn_fwd_mapped": (_i, [_p, _p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _p, _p, _i, _l, _p, _p, _i,
-                                         C.POINTER(ShortlistPlan), _p, _p, _i, _i, _p, _p, _p]),
+    "aspa_gather_attn_fwd_ex": (_i, [_p, _p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _p, _p, _i, _l, _p, _p, _i,
+                                     C.POINTER(ShortlistPlan), _p, _p, _i, _i, _p, C.POINTER(KVLayout), _p, _p]),
+    "aspa_rope_inplace": (_i, [_p, _i, _l, _i, _l, _i, _i, _p, _p, _p]),
     "aspa_rope_relayout_kv": (_i, [_p, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p]),
     "aspa_rope_rows_q": (_i, [_p, _i, _p, _p, _l, _i, _i, _i, _i, _p, _p, _p, _p]),
     "aspa_compact_mask_scratch": (_l, [_l]),
@@ -67,6 +74,9 @@ SIGNATURES = {
     "aspa_scatter_rows_fill": (_i, [_p, _p, _p, _p, _l, _l, _p, _p]),
     "aspa_gather_rows": (_i, [_p, _p, _p, _l, _l, _p, _p]),
     "aspa_reduce_partials": (_i, [_p, _i, _l, _p, _p]),
+    "aspa_stats_record": (_i, [_p, _i, _p, _i, _d, _p, _d, _p, _l, _p, _l, _p, _p, _p]),
+    "aspa_token_select_compact": (_i, [_p, _i, _i, _i, _f, _i, _p, _p, _p, _p, _i, _p]),
+    "aspa_head_select_pack": (_i, [_p, _i, _i, _i, _p, _i, _i, _p, _i, _p, _p, _p, _p, _p, _p, _p, _p, _l, _p]),
 }
 
 

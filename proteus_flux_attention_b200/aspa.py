@@ -113,6 +113,7 @@ class SwitchRouter(nn.Module):
 
 
 # ---- config parsing helpers ------------------------------------------------------------------
+KV_GEMM_SM_TARGET = 0  # > 0: the forked K/V projection is sized for this many SMs and starts after the router
 _SIDE_STREAMS: Dict[str, "torch.cuda.Stream"] = {}  # one second stream per device, shared by all layers
 
 
@@ -537,18 +538,17 @@ class AdaptiveSparseAttention(nn.Module):
                                  None if want_amax else q_keep,
                                  q_fraction=float(self._token_keep_ratio_runtime or 1.0))
 
-    def _fork_kv_projection(self, x: torch.Tensor) -> dict:
+    def _fork_kv_projection(self, x: torch.Tensor, sm_target: int = 0) -> dict:
         """K/V projection + RoPE/relayout of every token on a second stream.  Nothing in it depends on the routing
         chain (router, token keep, head choice, packing), whose kernels are small or latency-bound and leave most of
         the GPU idle; the two run side by side and meet before the attention.  The outputs are allocated on the
-        calling stream, so the allocator's stream bookkeeping stays with the caller."""
+        calling stream, so the allocator's stream bookkeeping stays with the caller.  No head-major copies are made:
+        the attention kernels read keys and values out of the (B*T, 2, H, D) projection through element strides."""
         B, T, C = x.shape
         H, D = self.h_total, self.d_head
         dev = x.device
         w, b = self.qkv.weight, self.qkv.bias
         kv = torch.empty((B * T, 2 * C), dtype=x.dtype, device=dev)
-        k = torch.empty((B * H, T, D), dtype=x.dtype, device=dev)
-        v = torch.empty_like(k)
         cos = sin = None
         if self.use_rope:
             cos, sin = self._rope_factors(T, dev, x.dtype)
@@ -560,21 +560,30 @@ class AdaptiveSparseAttention(nn.Module):
         ready.record(main)
         side.wait_event(ready)
         with torch.cuda.stream(side):
+            limited = sm_target > 0 and ops.blas_sm_target(sm_target)
             if b is None:
                 torch.mm(x.view(B * T, C), w[C:].t(), out=kv)
             else:
                 torch.addmm(b[C:], x.view(B * T, C), w[C:].t(), out=kv)
-            ops.rope_relayout_kv(kv.view(B, T, 2 * C), H, D, cos, sin, out=(k, v))
+            if limited:
+                ops.blas_sm_target(0)
+            if cos is not None:  # keys are rotated where the projection left them; values are used as they are
+                ops.rope_inplace(kv.view(-1), B * T, T, 2 * C, H, D, cos, sin)
             done.record(side)
-        return {"k": k, "v": v, "kv": kv, "done": done}
+        flat = kv.view(-1)
+        layout = N.KVLayout(k_batch=T * 2 * C, k_head=D, k_token=2 * C, v_batch=T * 2 * C, v_head=D, v_token=2 * C)
+        return {"k": flat, "v": flat[C:], "kv": kv, "layout": layout, "done": done}
 
     def _project_compact_q(self, x: torch.Tensor, compact: dict) -> torch.Tensor:
         """q for the kept tokens only; the q rows of dropped tokens stay unwritten."""
         B, T, C = x.shape
         H, D = self.h_total, self.d_head
         w, b = self.qkv.weight, self.qkv.bias
-        x_rows = ops.gather_rows(x.view(B * T, C), compact["idx"], compact["count"], compact["slots"],
-                                 out=torch.zeros((compact["slots"], C), dtype=x.dtype, device=x.device))
+        if compact["count"] is None:   # -1 padded list: the gather writes zeros into the unused slots itself
+            x_rows = ops.gather_rows(x.view(B * T, C), compact["idx"], None, compact["slots"])
+        else:
+            x_rows = ops.gather_rows(x.view(B * T, C), compact["idx"], compact["count"], compact["slots"],
+                                     out=torch.zeros((compact["slots"], C), dtype=x.dtype, device=x.device))
         q_rows = F.linear(x_rows, w[:C], None if b is None else b[:C])
         cos = sin = None
         if self.use_rope:
@@ -798,9 +807,9 @@ class AdaptiveSparseAttention(nn.Module):
         # INT8 scales are taken over the queries of every token (aspa.py:1328), so that mode projects them all.
         will_compact = (self.compact_projection and self.token_sparse and not keep_all and bound_known
                         and not use_quant and 4 * kept_bound <= 3 * T and not self.training)
-        # started before the router: launched after it, the projection's CTAs starve the cluster launches of the
-        # token keep (measured: 158 us instead of 40 us per call)
-        kv_fork = self._fork_kv_projection(x) if will_compact else None
+        # Started before the router unless the GEMM can be told to leave some SMs alone: launched after the router
+        # with all SMs, its CTAs starve the cluster launches of the token keep (158 us instead of 40 us per call).
+        kv_fork = self._fork_kv_projection(x) if will_compact and KV_GEMM_SM_TARGET <= 0 else None
 
         # 1. router
         x2d = x.view(B * T, C)
@@ -815,15 +824,24 @@ class AdaptiveSparseAttention(nn.Module):
         gate, imp, sim, bs, proto_sums = ops.router_fwd(
             x2d, self.head_router.linear.weight.contiguous(), proto_hat, conf_eps, usage_bias, temp=self.proto_temp,
             threshold=self.proto_threshold, span=max(1e-6, 1.0 - self.proto_threshold), blend=self.proto_blend,
-            usage_boost=self.proto_usage_boost)
+            usage_boost=self.proto_usage_boost, raw_stats=True)
         self._last_token_similarity = sim.view(B, T) if sim is not None else None
         self._last_token_blend = bs.view(B, T) if bs is not None else None
         self._last_token_importance = imp.view(B, T)
+        if will_compact and kv_fork is None:
+            kv_fork = self._fork_kv_projection(x, sm_target=KV_GEMM_SM_TARGET)
+
         # 2. token keep
-        token_mask_u8 = kept = None
+        token_mask_u8 = kept = compact = None
         if self.token_sparse:
             if keep_all:
                 token_mask_u8 = torch.ones((B, T), dtype=torch.uint8, device=dev)
+            elif will_compact and T <= ops.TOKEN_COMPACT_MAX_T:
+                # the keep also emits the ordered list of kept tokens (row b owns slots [b*kept_bound, ...), -1 padded)
+                token_mask_u8, kept, kept_idx, slot_of = ops.token_select_compact(
+                    self._last_token_importance, need, self.token_keep_threshold, guard, kept_bound)
+                compact = {"idx": kept_idx, "slot_of": slot_of, "count": None, "slots": B * kept_bound,
+                           "mask": token_mask_u8.view(-1)}
             else:
                 token_mask_u8, kept = ops.token_select(self._last_token_importance, need, self.token_keep_threshold, guard)
             self._last_token_mask = token_mask_u8.view(torch.bool)
@@ -842,22 +860,15 @@ class AdaptiveSparseAttention(nn.Module):
         k_bound = k_host if k_dev is None else dense_k
         if k_dev is None:
             self._last_target_k = k_host
-        head_bits, top_idx, top_score, head_sums = ops.head_select(
-            gate, self._gate_to_head_i32, H, k_host=k_host, k_dev=k_dev, kmax=dense_k,
-            token_mask=token_mask_u8.view(-1) if token_mask_u8 is not None else None)
         capacity = B * T * dense_k
-        row_offsets, token_idx = ops.pack_rows(head_bits, B, T, H, capacity)
+        head_bits, top_idx, top_score, head_partials, row_offsets, token_idx = ops.head_select_pack(
+            gate, self._gate_to_head_i32, B, T, H, k_host=k_host, k_dev=k_dev, kmax=dense_k,
+            token_mask=token_mask_u8.view(-1) if token_mask_u8 is not None else None, capacity=capacity)
 
         # 4. one statistics record to the host: [row offsets | kept per batch | k, adaptive | score, entropy sums |
-        #    prototype sums | router status], copied asynchronously and read when (and if) it is needed
-        f64 = dict(dtype=torch.float64, device=dev)
-        rec_dev = torch.cat([
-            row_offsets.to(torch.float64),
-            kept.to(torch.float64) if kept is not None else torch.full((B,), float(T), **f64),
-            k_dev.to(torch.float64) if k_dev is not None else torch.full((2,), float(k_host), **f64),
-            head_sums.to(torch.float64),
-            proto_sums.to(torch.float64) if proto_sums is not None else torch.zeros(3, **f64),
-            ops.router_status(dev).to(torch.float64)])
+        #    prototype sums | router status], built by one kernel, copied asynchronously and read when (and if) needed
+        rec_dev = ops.stats_record(row_offsets, kept, B, float(T), k_dev, float(k_host), head_partials, proto_sums,
+                                   ops.router_status(dev))
         if self._pin is None or self._pin.numel() != rec_dev.numel():
             self._pin = torch.empty(rec_dev.numel(), dtype=torch.float64, pin_memory=True)
         self._pin.copy_(rec_dev, non_blocking=True)
@@ -870,14 +881,15 @@ class AdaptiveSparseAttention(nn.Module):
                "token_idx": token_idx, "row_offsets": row_offsets, "exec_mode": "shortlist"}
 
         # 5. projection + RoPE + head-major relayout (does not depend on the record)
-        compact = None
+        kv_layout = None
         if will_compact:
-            n_slots = B * kept_bound
-            kept_idx, slot_of, kept_cnt = ops.compact_mask(token_mask_u8.view(-1), n_slots)
-            compact = {"idx": kept_idx, "slot_of": slot_of, "count": kept_cnt, "slots": n_slots,
-                       "mask": token_mask_u8.view(-1)}
+            if compact is None:  # rows too long for the fused keep: compact the mask separately
+                n_slots = B * kept_bound
+                kept_idx, slot_of, kept_cnt = ops.compact_mask(token_mask_u8.view(-1), n_slots)
+                compact = {"idx": kept_idx, "slot_of": slot_of, "count": kept_cnt, "slots": n_slots,
+                           "mask": token_mask_u8.view(-1)}
             q = self._project_compact_q(x, compact)
-            k, v = kv_fork["k"], kv_fork["v"]
+            k, v, kv_layout = kv_fork["k"], kv_fork["v"], kv_fork["layout"]
             torch.cuda.current_stream().wait_event(kv_fork["done"])
             amax = None
         else:
@@ -943,7 +955,7 @@ class AdaptiveSparseAttention(nn.Module):
                 d_total, d_max = H * sum(info["kept"]), max(info["kept"])
             if d_total > 0:
                 attention_packed(q, k, v, row_offsets=d_offs, token_idx=d_tok, max_rows=d_max, total_rows=d_total, H=H,
-                                 out=out, out_layout=N.OUT_TOKEN_MAJOR, out_row_map=row_map)
+                                 out=out, out_layout=N.OUT_TOKEN_MAJOR, out_row_map=row_map, kv_layout=kv_layout)
             _record_backend(BACKEND_NAME, device=str(dev), heads=nbh, tokens=T, max_rows=int(d_max))
         elif total_rows == 0:
             exec_mode = "sparse"
@@ -968,7 +980,7 @@ class AdaptiveSparseAttention(nn.Module):
                 plan = ops.make_plan(win, slots, runtime["anchor_stride"], pcap, lists, limits)
                 attention_packed(qa, ka, va, row_offsets=row_offsets, token_idx=token_idx, max_rows=max_rows,
                                  total_rows=total_rows, H=H, scales=scales, plan=plan, out=out,
-                                 out_layout=N.OUT_TOKEN_MAJOR, out_row_map=row_map)
+                                 out_layout=N.OUT_TOKEN_MAJOR, out_row_map=row_map, kv_layout=kv_layout)
                 path = "planned"
             else:  # the candidate pieces can overflow L: use the exact table builder (needs exact row counts)
                 L = runtime["effective_L"]
@@ -986,7 +998,7 @@ class AdaptiveSparseAttention(nn.Module):
                     local_cap=runtime["local_cap"], anchor_cap=runtime["anchor_cap"], proto_cap=runtime["proto_cap"])
                 attention_packed(qa, ka, va, row_offsets=row_offsets, token_idx=tok_used, max_rows=max_rows,
                                  total_rows=total_rows, H=H, scales=scales, cand=cand, cand_len=lens, out=out,
-                                 out_layout=N.OUT_TOKEN_MAJOR, out_row_map=row_map)
+                                 out_layout=N.OUT_TOKEN_MAJOR, out_row_map=row_map, kv_layout=kv_layout)
                 path = "table"
             _record_backend(BACKEND_NAME, device=str(dev), heads=B * H, tokens=T, max_rows=int(max_rows),
                             quantized=bool(use_quant), candidates=path)

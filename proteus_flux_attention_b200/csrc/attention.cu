@@ -34,6 +34,7 @@ struct AttnParams {
   void* out;
   int out_dtype, out_layout;
   const int32_t* out_row_map;  // token-major only: (B*T) row -> compact row, or NULL
+  aspa_kv_layout kv;           // element strides of k and v (batch, head, token)
   float scale;
   float* ws_m;  // [total_rows] running max (natural-log domain, already scaled)
   float* ws_l;  // [total_rows] running denominator
@@ -147,8 +148,9 @@ __global__ void __launch_bounds__(GEN_WARPS * 32) attn_rows_kernel(const AttnPar
   const int t = p.token_idx[grow];
   const int D = p.D, Tn = p.T;
   const T* qh = reinterpret_cast<const T*>(p.q) + (int64_t)bh * Tn * D;
-  const T* kh = reinterpret_cast<const T*>(p.k) + (int64_t)bh * Tn * D;
-  const T* vh = reinterpret_cast<const T*>(p.v) + (int64_t)bh * Tn * D;
+  const T* kh = reinterpret_cast<const T*>(p.k) + (bh / p.H) * p.kv.k_batch + (bh % p.H) * p.kv.k_head;
+  const T* vh = reinterpret_cast<const T*>(p.v) + (bh / p.H) * p.kv.v_batch + (bh % p.H) * p.kv.v_head;
+  const int64_t k_ts = p.kv.k_token, v_ts = p.kv.v_token;
   float* qs = qs_all[warp];
   for (int d = lane; d < D; d += 32) qs[d] = ld_as_float<T>(qh, (int64_t)t * D + d);
   __syncwarp();
@@ -234,7 +236,7 @@ __global__ void __launch_bounds__(GEN_WARPS * 32) attn_rows_kernel(const AttnPar
     }
     float s = -INFINITY;
     if (idx >= 0) {
-      s = dot_row<T>(kh + (int64_t)idx * D, qs, D) * sc;
+      s = dot_row<T>(kh + (int64_t)idx * k_ts, qs, D) * sc;
       if (p.add_mask) s += p.add_mask[(int64_t)t * Tn + idx];
     }
     const float m_new = fmaxf(m, warp_max(s));
@@ -254,7 +256,7 @@ __global__ void __launch_bounds__(GEN_WARPS * 32) attn_rows_kernel(const AttnPar
         const int ic = __shfl_sync(0xffffffffu, idx, c0g + grp);
         if (pc > 0.f) {
           float vv[8];
-          load_vec<T>(vh + (int64_t)ic * D + sub * VE, vv);
+          load_vec<T>(vh + (int64_t)ic * v_ts + sub * VE, vv);
 #pragma unroll
           for (int e = 0; e < VE; ++e) acc[e] = fmaf(pc, vv[e], acc[e]);
         }
@@ -264,7 +266,7 @@ __global__ void __launch_bounds__(GEN_WARPS * 32) attn_rows_kernel(const AttnPar
         const int src = __ffs(rem) - 1;
         const float pc = __shfl_sync(0xffffffffu, pr, src);
         const int ic = __shfl_sync(0xffffffffu, idx, src);
-        const T* vrow = vh + (int64_t)ic * D;
+        const T* vrow = vh + (int64_t)ic * v_ts;
 #pragma unroll
         for (int i = 0; i < GEN_MAXD / 32; ++i) {
           const int d = lane + 32 * i;
@@ -403,8 +405,9 @@ __global__ void __launch_bounds__(128) attn_window_kernel(const AttnParams p) {
   const int Tn = p.T;
   const int window = p.has_plan ? (p.plan.window > 0 ? p.plan.window : 1) : (Tn + 1);  // no plan = causal
   const T* qh = reinterpret_cast<const T*>(p.q) + (int64_t)bh * Tn * WK_D;
-  const T* kh = reinterpret_cast<const T*>(p.k) + (int64_t)bh * Tn * WK_D;
-  const T* vh = reinterpret_cast<const T*>(p.v) + (int64_t)bh * Tn * WK_D;
+  const T* kh = reinterpret_cast<const T*>(p.k) + (bh / p.H) * p.kv.k_batch + (bh % p.H) * p.kv.k_head;
+  const T* vh = reinterpret_cast<const T*>(p.v) + (bh / p.H) * p.kv.v_batch + (bh % p.H) * p.kv.v_head;
+  const int64_t k_ts = p.kv.k_token, v_ts = p.kv.v_token;
 
   if (tid < WK_ROWS) ts[tid] = tid < nrows ? p.token_idx[start + r0 + tid] : -1;
   __syncthreads();
@@ -462,8 +465,8 @@ __global__ void __launch_bounds__(128) attn_window_kernel(const AttnParams p) {
       const int row = c >> 3, ch = c & 7;
       const int key = kt * WK_KEYS + row;
       if (key < Tn) {
-        kreg[i] = load_chunk<T>(kh + (int64_t)key * WK_D, ch);
-        vreg[i] = load_chunk<T>(vh + (int64_t)key * WK_D, ch);
+        kreg[i] = load_chunk<T>(kh + (int64_t)key * k_ts, ch);
+        vreg[i] = load_chunk<T>(vh + (int64_t)key * v_ts, ch);
       } else {
         kreg[i] = make_uint4(0, 0, 0, 0);
         vreg[i] = make_uint4(0, 0, 0, 0);
@@ -478,10 +481,10 @@ __global__ void __launch_bounds__(128) attn_window_kernel(const AttnParams p) {
         const int c = tid + 128 * i;
         const int row = c >> 3, ch = c & 7;
         const int key = kt * WK_KEYS + row;
-        const int64_t off = (int64_t)min(key, Tn - 1) * WK_D + ch * 8;
+        const int64_t kc = min(key, Tn - 1);
         const int nbytes = key < Tn ? 16 : 0;
-        cp_async16(smem_u32(ks_ + swz(row, ch)), kh + off, nbytes);
-        cp_async16(smem_u32(ks_ + WK_TILE_BYTES + swz(row, ch)), vh + off, nbytes);
+        cp_async16(smem_u32(ks_ + swz(row, ch)), kh + kc * k_ts + ch * 8, nbytes);
+        cp_async16(smem_u32(ks_ + WK_TILE_BYTES + swz(row, ch)), vh + kc * v_ts + ch * 8, nbytes);
       }
     }
     cp_async_commit();
@@ -662,18 +665,19 @@ extern "C" int aspa_gather_attn_fwd(const void* q, const void* k, const void* v,
                                     int64_t total_rows, const int64_t* cand, const int64_t* cand_len, int L,
                                     const aspa_shortlist_plan* plan, const float* add_mask, void* out, int out_dtype,
                                     int out_layout, void* workspace, void* stream) {
-  return aspa_gather_attn_fwd_mapped(q, k, v, qkv_dtype, q_scale, k_scale, v_scale, heads, T, D, H, row_offsets, token_idx,
-                                     max_rows, total_rows, cand, cand_len, L, plan, add_mask, out, out_dtype, out_layout,
-                                     nullptr, workspace, stream);
+  return aspa_gather_attn_fwd_ex(q, k, v, qkv_dtype, q_scale, k_scale, v_scale, heads, T, D, H, row_offsets, token_idx,
+                                 max_rows, total_rows, cand, cand_len, L, plan, add_mask, out, out_dtype, out_layout,
+                                 nullptr, nullptr, workspace, stream);
 }
 
-extern "C" int aspa_gather_attn_fwd_mapped(const void* q, const void* k, const void* v, int qkv_dtype,
-                                           const float* q_scale, const float* k_scale, const float* v_scale, int heads,
-                                           int T, int D, int H, const int32_t* row_offsets, const int32_t* token_idx,
-                                           int max_rows, int64_t total_rows, const int64_t* cand,
-                                           const int64_t* cand_len, int L, const aspa_shortlist_plan* plan,
-                                           const float* add_mask, void* out, int out_dtype, int out_layout,
-                                           const int32_t* out_row_map, void* workspace, void* stream) {
+extern "C" int aspa_gather_attn_fwd_ex(const void* q, const void* k, const void* v, int qkv_dtype,
+                                       const float* q_scale, const float* k_scale, const float* v_scale, int heads,
+                                       int T, int D, int H, const int32_t* row_offsets, const int32_t* token_idx,
+                                       int max_rows, int64_t total_rows, const int64_t* cand,
+                                       const int64_t* cand_len, int L, const aspa_shortlist_plan* plan,
+                                       const float* add_mask, void* out, int out_dtype, int out_layout,
+                                       const int32_t* out_row_map, const aspa_kv_layout* kv_layout, void* workspace,
+                                       void* stream) {
   ASPA_CHECK_ARG(q && k && v && row_offsets && token_idx && out, "null pointer");
   ASPA_CHECK_ARG(heads > 0 && T > 0 && D > 0 && D <= GEN_MAXD, "head_dim must be in [1, 256]");
   ASPA_CHECK_ARG(qkv_dtype == ASPA_F32 || qkv_dtype == ASPA_BF16 || qkv_dtype == ASPA_I8, "bad qkv dtype");
@@ -697,6 +701,18 @@ extern "C" int aspa_gather_attn_fwd_mapped(const void* q, const void* k, const v
   if (p.has_plan) p.plan = *plan;
   p.add_mask = add_mask;
   p.out = out; p.out_dtype = out_dtype; p.out_layout = out_layout; p.out_row_map = out_row_map;
+  if (kv_layout) {
+    ASPA_CHECK_ARG(H > 0 && heads % H == 0, "a k/v layout needs H dividing heads");
+    const int64_t a = 16 / (qkv_dtype == ASPA_F32 ? 4 : (qkv_dtype == ASPA_BF16 ? 2 : 1));  // elements per 16 bytes
+    ASPA_CHECK_ARG(kv_layout->k_token % a == 0 && kv_layout->v_token % a == 0 && kv_layout->k_head % a == 0 &&
+                       kv_layout->v_head % a == 0 && kv_layout->k_batch % a == 0 && kv_layout->v_batch % a == 0,
+                   "k/v strides must keep rows 16-byte aligned");
+    p.kv = *kv_layout;
+  } else {  // head-major (heads, T, D)
+    p.kv.k_token = p.kv.v_token = D;
+    p.kv.k_head = p.kv.v_head = (int64_t)T * D;
+    p.kv.k_batch = p.kv.v_batch = (int64_t)p.H * T * D;
+  }
   p.scale = 1.0f / sqrtf((float)D);
   p.ws_m = p.ws_l = p.ws_o = nullptr;
 

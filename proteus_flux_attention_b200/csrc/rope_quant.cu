@@ -235,6 +235,45 @@ __global__ void __launch_bounds__(256) rope_rows_q_kernel(const T* __restrict__ 
   }
 }
 
+// RoPE in place: row r (H*D wide, rows `row_stride` elements apart) is rotated at position r % Tn.
+// One thread per 16-byte vector, consecutive threads on consecutive vectors of a row.
+template <typename T>
+__global__ void __launch_bounds__(256) rope_inplace_kernel(T* __restrict__ x, int64_t n_rows, int Tn,
+                                                           int64_t row_stride, int H, int D,
+                                                           const float* __restrict__ cos_t,
+                                                           const float* __restrict__ sin_t) {
+  constexpr int E = 16 / sizeof(T);
+  const int C = H * D, half = D / 2;
+  const int vec_per_row = C / E;
+  const int64_t total = n_rows * vec_per_row;
+  for (int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; g < total; g += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = g / vec_per_row;
+    const int ch = (int)(g % vec_per_row) * E;
+    const int t = (int)(r % Tn);
+    const int d0 = ch % D;
+    T* ptr = x + r * row_stride + ch;
+    uint4 raw = *reinterpret_cast<const uint4*>(ptr);
+    const float* cr = cos_t + (int64_t)t * half + d0 / 2;
+    const float* sr = sin_t + (int64_t)t * half + d0 / 2;
+    if (sizeof(T) == 2) {
+      const float4 c4 = *reinterpret_cast<const float4*>(cr), s4 = *reinterpret_cast<const float4*>(sr);
+      raw.x = rope_word_bf16(raw.x, c4.x, s4.x);
+      raw.y = rope_word_bf16(raw.y, c4.y, s4.y);
+      raw.z = rope_word_bf16(raw.z, c4.z, s4.z);
+      raw.w = rope_word_bf16(raw.w, c4.w, s4.w);
+    } else {
+      float* f = reinterpret_cast<float*>(&raw);
+      const float2 c2 = *reinterpret_cast<const float2*>(cr), s2 = *reinterpret_cast<const float2*>(sr);
+      const float e0 = f[0], o0 = f[1], e1 = f[2], o1 = f[3];
+      f[0] = rope_mix(e0, c2.x, -o0, s2.x, false);
+      f[1] = rope_mix(o0, c2.x, e0, s2.x, false);
+      f[2] = rope_mix(e1, c2.y, -o1, s2.y, false);
+      f[3] = rope_mix(o1, c2.y, e1, s2.y, false);
+    }
+    *reinterpret_cast<uint4*>(ptr) = raw;
+  }
+}
+
 // dst row i = src[slot_of[i]] for kept rows, `fill` (or zeros) for the others.
 __global__ void __launch_bounds__(256) scatter_rows_fill_kernel(const uint4* __restrict__ src,
                                                                 const int32_t* __restrict__ slot_of,
@@ -393,6 +432,25 @@ extern "C" int aspa_scatter_rows_fill(const void* src, const int32_t* slot_of, c
   const int64_t total = n * (row_bytes / 16);
   scatter_rows_fill_kernel<<<(unsigned)std::min<int64_t>(ceil_div(total, 256), 148 * 32), 256, 0, (cudaStream_t)stream>>>(
       (const uint4*)src, slot_of, mask, (const uint4*)fill, n, row_bytes / 16, (uint4*)dst);
+  ASPA_CHECK_LAUNCH();
+  return ASPA_OK;
+}
+
+extern "C" int aspa_rope_inplace(void* x, int dtype, int64_t n_rows, int T, int64_t row_stride, int H, int D,
+                                 const float* cos_t, const float* sin_t, void* stream) {
+  ASPA_CHECK_ARG(x && cos_t && sin_t, "null pointer");
+  ASPA_CHECK_ARG(n_rows >= 0 && T > 0 && H > 0 && D > 0 && D % 2 == 0 && row_stride >= (int64_t)H * D, "bad sizes");
+  ASPA_CHECK_ARG(dtype == ASPA_F32 || dtype == ASPA_BF16, "dtype must be fp32 or bf16");
+  const int E = dtype == ASPA_BF16 ? 8 : 4;
+  ASPA_CHECK_ARG(D % E == 0 && row_stride % E == 0, "rows must start on 16-byte boundaries");
+  if (n_rows == 0) return ASPA_OK;
+  const int64_t total = n_rows * (H * D / E);
+  const unsigned blocks = (unsigned)std::min<int64_t>(ceil_div(total, 256), 148 * 32);
+  if (dtype == ASPA_BF16)
+    rope_inplace_kernel<__nv_bfloat16><<<blocks, 256, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)x, n_rows, T, row_stride, H, D,
+                                                                                 cos_t, sin_t);
+  else
+    rope_inplace_kernel<float><<<blocks, 256, 0, (cudaStream_t)stream>>>((float*)x, n_rows, T, row_stride, H, D, cos_t, sin_t);
   ASPA_CHECK_LAUNCH();
   return ASPA_OK;
 }

@@ -152,6 +152,38 @@ __global__ void reduce_partials_kernel(const float* __restrict__ partials, int64
   if (threadIdx.x == 0) out[blockIdx.x] = acc;
 }
 
+// Everything the host may want to know about one layer call, gathered into one fp64 record by a single CTA:
+// [row offsets | kept per batch row | k, adaptive k | selected-score sum, entropy sum | prototype sums (3) | status].
+// Series sums use the order of reduce_partials_kernel (one warp per series, lane-strided, then a shuffle tree).
+__global__ void __launch_bounds__(256) stats_record_kernel(const int32_t* __restrict__ row_offsets, int n_offsets,
+                                                           const int32_t* __restrict__ kept, int n_kept,
+                                                           double kept_fill, const int32_t* __restrict__ k_dev,
+                                                           double k_fill, const float* __restrict__ head_partials,
+                                                           int64_t head_blocks,
+                                                           const float* __restrict__ proto_partials,
+                                                           int64_t proto_blocks, const int32_t* __restrict__ status,
+                                                           double* __restrict__ rec) {
+  for (int i = threadIdx.x; i < n_offsets; i += blockDim.x) rec[i] = (double)row_offsets[i];
+  double* r = rec + n_offsets;
+  for (int i = threadIdx.x; i < n_kept; i += blockDim.x) r[i] = kept ? (double)kept[i] : kept_fill;
+  r += n_kept;
+  if (threadIdx.x < 2) r[threadIdx.x] = k_dev ? (double)k_dev[threadIdx.x] : k_fill;
+  r += 2;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (warp < 5) {
+    const bool head = warp < 2;
+    const float* p = head ? head_partials : proto_partials;
+    const int64_t nb = head ? head_blocks : proto_blocks;
+    const int series = head ? warp : warp - 2;
+    float acc = 0.f;
+    if (p != nullptr)
+      for (int64_t i = lane; i < nb; i += 32) acc += p[(int64_t)series * nb + i];
+    acc = warp_sum(acc);
+    if (lane == 0) r[warp] = (double)acc;
+  }
+  if (threadIdx.x == 0) r[5] = status ? (double)status[0] : 0.0;
+}
+
 }  // namespace aspa
 
 using namespace aspa;
@@ -202,6 +234,19 @@ extern "C" int aspa_normalize_rows(const float* src, int rows, int cols, float e
 extern "C" int aspa_reduce_partials(const float* partials, int n_series, int64_t n_blocks, float* out, void* stream) {
   ASPA_CHECK_ARG(partials && out && n_series > 0 && n_blocks >= 0, "bad arguments");
   reduce_partials_kernel<<<n_series, 32, 0, (cudaStream_t)stream>>>(partials, n_blocks, out);
+  ASPA_CHECK_LAUNCH();
+  return ASPA_OK;
+}
+
+extern "C" int aspa_stats_record(const int32_t* row_offsets, int n_offsets, const int32_t* kept, int n_kept,
+                                 double kept_fill, const int32_t* k_dev, double k_fill, const float* head_partials,
+                                 int64_t head_blocks, const float* proto_partials, int64_t proto_blocks,
+                                 const int32_t* status, double* record, void* stream) {
+  ASPA_CHECK_ARG(row_offsets && record && n_offsets > 0 && n_kept >= 0 && head_blocks >= 0 && proto_blocks >= 0,
+                 "bad arguments");
+  stats_record_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(row_offsets, n_offsets, kept, n_kept, kept_fill, k_dev, k_fill,
+                                                           head_partials, head_blocks, proto_partials, proto_blocks, status,
+                                                           record);
   ASPA_CHECK_LAUNCH();
   return ASPA_OK;
 }

@@ -193,7 +193,10 @@ __global__ void __launch_bounds__(1024) token_select_regs_kernel(const float* __
 __global__ void __launch_bounds__(CL_THREADS) token_select_cluster_kernel(const float* __restrict__ importance, int T,
                                                                           int need0, float threshold, int guard,
                                                                           uint8_t* __restrict__ token_mask,
-                                                                          int32_t* __restrict__ kept) {
+                                                                          int32_t* __restrict__ kept,
+                                                                          int64_t* __restrict__ kept_idx,
+                                                                          int32_t* __restrict__ slot_of,
+                                                                          int slots_per_row) {
   __shared__ ClusterScratch cs;
   cg::cluster_group cluster = cg::this_cluster();
   const int rank = (int)cluster.block_rank(), csize = (int)cluster.num_blocks();
@@ -234,7 +237,16 @@ __global__ void __launch_bounds__(CL_THREADS) token_select_cluster_kernel(const 
   if (need >= T) {  // uniform over the cluster
 #pragma unroll
     for (int j = 0; j < CL_EPT; ++j)
-      if (base + j < T) out[base + j] = 1;
+      if (base + j < T) {
+        out[base + j] = 1;
+        if (kept_idx != nullptr) {
+          if (base + j < slots_per_row) kept_idx[(int64_t)row * slots_per_row + base + j] = (int64_t)row * T + base + j;
+          slot_of[(int64_t)row * T + base + j] = row * slots_per_row + base + j;
+        }
+      }
+    if (kept_idx != nullptr)
+      for (int i = T + rank * CL_THREADS + threadIdx.x; i < slots_per_row; i += csize * CL_THREADS)
+        kept_idx[(int64_t)row * slots_per_row + i] = -1;
     if (rank == 0 && threadIdx.x == 0) kept[row] = T;
     return;
   }
@@ -250,7 +262,7 @@ __global__ void __launch_bounds__(CL_THREADS) token_select_cluster_kernel(const 
   const int take = need - (int)ge[0];  // ties to accept, lowest token index first
   int n_eq;
   int tie_rank = (int)lower[1] + block_exclusive_scan(my_eq, cs.scan_tmp, &n_eq);
-  uint32_t kept_total = 0;
+  uint32_t kept_total = 0, on_bits = 0;
 #pragma unroll
   for (int j = 0; j < CL_EPT; j += 4) {
     uint32_t packed = 0;
@@ -268,6 +280,7 @@ __global__ void __launch_bounds__(CL_THREADS) token_select_cluster_kernel(const 
         if (i < guard) on = true;
         kept_total += on ? 1u : 0u;
         packed |= (on ? 1u : 0u) << (8 * e);
+        on_bits |= (on ? 1u : 0u) << (j + e);
       }
     }
     if (vec_ok && base + j + 3 < T) {
@@ -278,9 +291,26 @@ __global__ void __launch_bounds__(CL_THREADS) token_select_cluster_kernel(const 
         if (base + j + e < T) out[base + j + e] = (uint8_t)((packed >> (8 * e)) & 1u);
     }
   }
-  uint32_t kt[1] = {kept_total};
-  cluster_reduce<1, OpAdd>(kt, cs, parity);
+  int cta_total = 0;
+  int slot = 0;
+  if (kept_idx != nullptr) slot = block_exclusive_scan((int)kept_total, cs.scan_tmp, &cta_total);
+  uint32_t kt[1] = {kept_total}, kt_lower[1];
+  cluster_reduce<1, OpAdd>(kt, cs, parity, kt_lower);
   if (rank == 0 && threadIdx.x == 0) kept[row] = (int)kt[0];
+  if (kept_idx != nullptr) {
+    // ordered compaction of the kept tokens of this row: slots [row * slots_per_row, ...), padded with -1
+    slot += (int)kt_lower[0];
+    const int64_t s0 = (int64_t)row * slots_per_row;
+#pragma unroll
+    for (int j = 0; j < CL_EPT; ++j)
+      if ((on_bits >> j) & 1u) {
+        if (slot < slots_per_row) kept_idx[s0 + slot] = (int64_t)row * T + base + j;
+        slot_of[(int64_t)row * T + base + j] = (int)min(s0 + slot, (int64_t)0x7fffffff);
+        ++slot;
+      }
+    for (int i = (int)kt[0] + rank * CL_THREADS + threadIdx.x; i < slots_per_row; i += csize * CL_THREADS)
+      kept_idx[s0 + i] = -1;
+  }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -369,6 +399,10 @@ __global__ void head_budget_kernel(const float* __restrict__ partials, int64_t n
 // ---------------------------------------------------------------------------------------------
 // Per-token head top-k
 // ---------------------------------------------------------------------------------------------
+// One thread per token, head scores in registers (HT = compile-time bound on H, statically indexed).  When
+// `seg_counts` is given (T a multiple of 256, so a CTA is exactly one packing segment) the CTA also counts the rows
+// of every head in its segment, which is the first phase of the row packing.
+template <int HT>
 __global__ void __launch_bounds__(256) head_select_kernel(const float* __restrict__ gate_probs, int64_t n, int G,
                                                           const int32_t* __restrict__ gate_to_head, int H,
                                                           int k_host, const int32_t* __restrict__ k_dev, int kmax,
@@ -376,33 +410,62 @@ __global__ void __launch_bounds__(256) head_select_kernel(const float* __restric
                                                           uint64_t* __restrict__ head_bits,
                                                           int32_t* __restrict__ top_idx,
                                                           float* __restrict__ top_score,
-                                                          float* __restrict__ stat_partials) {
+                                                          float* __restrict__ stat_partials, int T, int nseg,
+                                                          int32_t* __restrict__ seg_counts) {
   __shared__ int g2h[128];
   __shared__ float red[2][8];
-  for (int i = threadIdx.x; i < G; i += blockDim.x) g2h[i] = gate_to_head[i];
+  __shared__ int cnt[64];
+  __shared__ int not_identity;
+  if (threadIdx.x == 0) not_identity = (G != H) ? 1 : 0;
+  for (int i = threadIdx.x; i < 64; i += blockDim.x) cnt[i] = 0;
   __syncthreads();
+  for (int i = threadIdx.x; i < G; i += blockDim.x) {
+    const int h = gate_to_head[i];
+    g2h[i] = h;
+    if (h != i) not_identity = 1;
+  }
+  __syncthreads();
+  const bool identity = not_identity == 0;  // gate g feeds head g: no scatter needed
   const int k = min(k_dev ? k_dev[0] : k_host, kmax);
   const int64_t tok = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   float score_sum = 0.f, ent = 0.f;
+  uint64_t bits = 0;
   if (tok < n) {
-    float hp[64];
-#pragma unroll 8
-    for (int h = 0; h < 64; ++h) hp[h] = 0.f;
+    float hp[HT];
+#pragma unroll
+    for (int h = 0; h < HT; ++h) hp[h] = 0.f;
     const float* gp = gate_probs + tok * G;
-    for (int g = 0; g < G; ++g) {
-      const float p = gp[g];
-      ent -= logf(fmaxf(p, 1e-9f)) * p;
-      const int h = g2h[g];
-      // dynamic register indexing would spill; H <= 64 keeps this small enough for local memory
-      hp[h] += p;
+    if (identity) {
+#pragma unroll
+      for (int h = 0; h < HT; h += 4) {
+        if (h + 3 < G && (G % 4) == 0) {
+          const float4 p4 = *reinterpret_cast<const float4*>(gp + h);
+          hp[h] = p4.x; hp[h + 1] = p4.y; hp[h + 2] = p4.z; hp[h + 3] = p4.w;
+        } else {
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            if (h + e < G) hp[h + e] = gp[h + e];
+        }
+      }
+#pragma unroll
+      for (int h = 0; h < HT; ++h)
+        if (h < G) ent -= logf(fmaxf(hp[h], 1e-9f)) * hp[h];
+    } else {
+      for (int g = 0; g < G; ++g) {
+        const float p = gp[g];
+        ent -= logf(fmaxf(p, 1e-9f)) * p;
+        const int h = g2h[g];
+#pragma unroll
+        for (int hh = 0; hh < HT; ++hh) hp[hh] += hh == h ? p : 0.f;  // static register indexing
+      }
     }
-    uint64_t bits = 0;
     for (int j = 0; j < kmax; ++j) {
       int best = -1;
       float bv = -INFINITY;
       if (j < k) {
-        for (int h = 0; h < H; ++h)
-          if (!((bits >> h) & 1ull) && hp[h] > bv) {
+#pragma unroll
+        for (int h = 0; h < HT; ++h)
+          if (h < H && !((bits >> h) & 1ull) && hp[h] > bv) {
             bv = hp[h];
             best = h;
           }
@@ -417,6 +480,12 @@ __global__ void __launch_bounds__(256) head_select_kernel(const float* __restric
     if (token_mask && !token_mask[tok]) bits = 0;
     head_bits[tok] = bits;
   }
+  if (seg_counts) {
+    for (int h = 0; h < H; ++h) {
+      const unsigned bal = __ballot_sync(0xffffffffu, (bits >> h) & 1ull);
+      if ((threadIdx.x & 31) == 0 && bal) atomicAdd(&cnt[h], __popc(bal));
+    }
+  }
   if (stat_partials) {
     score_sum = warp_sum(score_sum);
     ent = warp_sum(ent);
@@ -424,17 +493,38 @@ __global__ void __launch_bounds__(256) head_select_kernel(const float* __restric
       red[0][threadIdx.x >> 5] = score_sum;
       red[1][threadIdx.x >> 5] = ent;
     }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      float a = 0.f, b = 0.f;
-      for (int w = 0; w < 8; ++w) {
-        a += red[0][w];
-        b += red[1][w];
-      }
-      stat_partials[blockIdx.x] = a;
-      stat_partials[gridDim.x + blockIdx.x] = b;
-    }
   }
+  __syncthreads();
+  if (stat_partials && threadIdx.x == 0) {
+    float a = 0.f, b = 0.f;
+    for (int w = 0; w < 8; ++w) {
+      a += red[0][w];
+      b += red[1][w];
+    }
+    stat_partials[blockIdx.x] = a;
+    stat_partials[gridDim.x + blockIdx.x] = b;
+  }
+  if (seg_counts) {
+    const int64_t t0 = (int64_t)blockIdx.x * 256;
+    const int b = (int)(t0 / T), seg = (int)((t0 % T) / 256);
+    for (int h = threadIdx.x; h < H; h += blockDim.x) seg_counts[((int64_t)b * H + h) * nseg + seg] = cnt[h];
+  }
+}
+
+static void launch_head_select(const float* gate_probs, int64_t n, int G, const int32_t* gate_to_head, int H, int k_host,
+                               const int32_t* k_dev, int kmax, const uint8_t* token_mask, uint64_t* head_bits,
+                               int32_t* top_idx, float* top_score, float* stat_partials, int T, int nseg,
+                               int32_t* seg_counts, cudaStream_t st) {
+  const unsigned grid = (unsigned)ceil_div(n, 256);
+  if (H <= 16)
+    head_select_kernel<16><<<grid, 256, 0, st>>>(gate_probs, n, G, gate_to_head, H, k_host, k_dev, kmax, token_mask,
+                                                 head_bits, top_idx, top_score, stat_partials, T, nseg, seg_counts);
+  else if (H <= 32)
+    head_select_kernel<32><<<grid, 256, 0, st>>>(gate_probs, n, G, gate_to_head, H, k_host, k_dev, kmax, token_mask,
+                                                 head_bits, top_idx, top_score, stat_partials, T, nseg, seg_counts);
+  else
+    head_select_kernel<64><<<grid, 256, 0, st>>>(gate_probs, n, G, gate_to_head, H, k_host, k_dev, kmax, token_mask,
+                                                 head_bits, top_idx, top_score, stat_partials, T, nseg, seg_counts);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -584,6 +674,7 @@ __global__ void __launch_bounds__(CM_THREADS) compact_fill_kernel(const uint8_t*
 }  // namespace aspa
 
 using namespace aspa;
+static_assert(ASPA_TOKEN_COMPACT_MAX_T == CL_MAX * CL_KEYS_PER_CTA, "header constant out of step with the cluster kernels");
 
 extern "C" int aspa_token_select(const float* importance, int B, int T, int need, float threshold, int guard,
                                  uint8_t* token_mask, int32_t* kept, void* stream) {
@@ -596,13 +687,33 @@ extern "C" int aspa_token_select(const float* importance, int B, int T, int need
     int csize = 1;
     while (csize * CL_KEYS_PER_CTA < T) csize <<= 1;  // 1, 2, 4 or 8 CTAs; surplus slots hold no keys
     const cudaError_t e = launch_clusters(token_select_cluster_kernel, B, csize, 0, st, importance, T, need, threshold,
-                                          guard, token_mask, kept);
+                                          guard, token_mask, kept, (int64_t*)nullptr, (int32_t*)nullptr, 0);
     if (e != cudaSuccess) {
       set_error("aspa_token_select: cluster launch failed: %s", cudaGetErrorString(e));
       return ASPA_ERR_CUDA;
     }
   } else {
     token_select_kernel<<<B, 1024, 0, st>>>(importance, T, need, threshold, guard, token_mask, kept);
+  }
+  ASPA_CHECK_LAUNCH();
+  return ASPA_OK;
+}
+
+extern "C" int aspa_token_select_compact(const float* importance, int B, int T, int need, float threshold, int guard,
+                                         uint8_t* token_mask, int32_t* kept, int64_t* kept_idx, int32_t* slot_of,
+                                         int slots_per_row, void* stream) {
+  ASPA_CHECK_ARG(importance && token_mask && kept && kept_idx && slot_of, "null pointer");
+  ASPA_CHECK_ARG(B > 0 && T > 0 && slots_per_row > 0, "bad sizes");
+  ASPA_CHECK_ARG(T <= ASPA_TOKEN_COMPACT_MAX_T, "rows longer than ASPA_TOKEN_COMPACT_MAX_T: use aspa_token_select + aspa_compact_mask");
+  ASPA_CHECK_ARG((int64_t)B * std::max(T, slots_per_row) < ((int64_t)1 << 31), "slot numbers must fit 31 bits");
+  cudaStream_t st = (cudaStream_t)stream;
+  int csize = 1;
+  while (csize * CL_KEYS_PER_CTA < T) csize <<= 1;
+  const cudaError_t e = launch_clusters(token_select_cluster_kernel, B, csize, 0, st, importance, T, need, threshold, guard,
+                                        token_mask, kept, kept_idx, slot_of, slots_per_row);
+  if (e != cudaSuccess) {
+    set_error("aspa_token_select_compact: cluster launch failed: %s", cudaGetErrorString(e));
+    return ASPA_ERR_CUDA;
   }
   ASPA_CHECK_LAUNCH();
   return ASPA_OK;
@@ -628,9 +739,30 @@ extern "C" int aspa_head_select(const float* gate_probs, int64_t n, int G, const
                                 void* stream) {
   ASPA_CHECK_ARG(gate_probs && gate_to_head && head_bits, "null pointer");
   ASPA_CHECK_ARG(n > 0 && G > 0 && G <= 128 && H > 0 && H <= 64 && kmax > 0 && kmax <= H, "bad sizes");
-  head_select_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, (cudaStream_t)stream>>>(
-      gate_probs, n, G, gate_to_head, H, k_host, k_dev, kmax, token_mask, head_bits, top_idx, top_score,
-      stat_partials);
+  launch_head_select(gate_probs, n, G, gate_to_head, H, k_host, k_dev, kmax, token_mask, head_bits, top_idx, top_score,
+                     stat_partials, 0, 0, nullptr, (cudaStream_t)stream);
+  ASPA_CHECK_LAUNCH();
+  return ASPA_OK;
+}
+
+extern "C" int aspa_head_select_pack(const float* gate_probs, int B, int T, int G, const int32_t* gate_to_head, int H,
+                                     int k_host, const int32_t* k_dev, int kmax, const uint8_t* token_mask,
+                                     uint64_t* head_bits, int32_t* top_idx, float* top_score, float* stat_partials,
+                                     int32_t* seg_scratch, int32_t* row_offsets, int32_t* token_idx, int64_t capacity,
+                                     void* stream) {
+  ASPA_CHECK_ARG(gate_probs && gate_to_head && head_bits && seg_scratch && row_offsets && token_idx, "null pointer");
+  ASPA_CHECK_ARG(B > 0 && T > 0 && G > 0 && G <= 128 && H > 0 && H <= 64 && kmax > 0 && kmax <= H, "bad sizes");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t n = (int64_t)B * T;
+  const int nseg = (int)ceil_div(T, PK_SEG);
+  const bool fused = T % PK_SEG == 0;  // a 256-token CTA of the head choice is then exactly one packing segment
+  launch_head_select(gate_probs, n, G, gate_to_head, H, k_host, k_dev, kmax, token_mask, head_bits, top_idx, top_score,
+                     stat_partials, T, nseg, fused ? seg_scratch : nullptr, st);
+  ASPA_CHECK_LAUNCH();
+  const dim3 grid(nseg, B);
+  if (!fused) pack_count_kernel<true><<<grid, PK_SEG, 0, st>>>(head_bits, T, H, nseg, seg_scratch);
+  pack_scan_kernel<<<1, 1024, 0, st>>>(seg_scratch, (int64_t)B * H * nseg, nseg, row_offsets, B * H);
+  pack_fill_kernel<true><<<grid, PK_SEG, 0, st>>>(head_bits, T, H, nseg, seg_scratch, token_idx, capacity);
   ASPA_CHECK_LAUNCH();
   return ASPA_OK;
 }

@@ -87,8 +87,10 @@ def router_status(device) -> torch.Tensor:
 
 def router_fwd(x2d: torch.Tensor, w_router: torch.Tensor, proto_hat: Optional[torch.Tensor],
                conf_eps: Optional[torch.Tensor], usage_bias: Optional[torch.Tensor], *, temp: float,
-               threshold: float, span: float, blend: float, usage_boost: float, want_stats: bool = True):
-    """x2d (n, C) fp32/bf16 -> gate (n, G) fp32, importance (n), sim (n)|None, blend (n)|None, stats (3,)|None."""
+               threshold: float, span: float, blend: float, usage_boost: float, want_stats: bool = True,
+               raw_stats: bool = False):
+    """x2d (n, C) fp32/bf16 -> gate (n, G) fp32, importance (n), sim (n)|None, blend (n)|None, stats (3,)|None.
+    With ``raw_stats`` the last item is the (3 * blocks) tensor of per-block partial sums instead of their sums."""
     n, Cdim = x2d.shape
     G = w_router.size(0)
     dev = x2d.device
@@ -109,14 +111,14 @@ def router_fwd(x2d: torch.Tensor, w_router: torch.Tensor, proto_hat: Optional[to
                 N.ptr(x2d), n, Cdim, N.ptr(w_router), G, N.ptr(proto_hat), N.ptr(conf_eps), N.ptr(usage_bias), temp,
                 threshold, span, blend, usage_boost, N.ptr(gate), N.ptr(imp), N.ptr(sim), N.ptr(bs), N.ptr(partials),
                 N.ptr(scratch), N.ptr(router_status(dev)), N.stream()), "router_fwd_tc")
-        stats = reduce_partials(partials, 3) if partials is not None else None
+        stats = (partials if raw_stats else reduce_partials(partials, 3)) if partials is not None else None
         return gate, imp, sim, bs, stats
     with _timed('router', 1, _nb(x2d, w_router, proto_hat, gate, imp, sim, bs)):
         N.check(N.lib().aspa_router_fwd(
             N.ptr(x2d), N.dtype_code(x2d.dtype), n, Cdim, N.ptr(w_router), G, N.ptr(proto_hat), N.ptr(conf_eps),
             N.ptr(usage_bias), temp, threshold, span, blend, usage_boost, N.ptr(gate), N.ptr(imp), N.ptr(sim), N.ptr(bs),
             N.ptr(partials), N.stream()), "router_fwd")
-    stats = reduce_partials(partials, 3) if partials is not None else None
+    stats = (partials if raw_stats else reduce_partials(partials, 3)) if partials is not None else None
     return gate, imp, sim, bs, stats
 
 
@@ -279,9 +281,11 @@ def gather_attn(q, k, v, *, scales: Optional[Tuple[torch.Tensor, torch.Tensor, t
                 row_offsets: torch.Tensor, token_idx: torch.Tensor, max_rows: int, total_rows: int,
                 cand: Optional[torch.Tensor] = None, cand_len: Optional[torch.Tensor] = None,
                 plan: Optional[N.ShortlistPlan] = None, add_mask: Optional[torch.Tensor] = None,
-                out: torch.Tensor, out_layout: int, out_row_map: Optional[torch.Tensor] = None):
+                out: torch.Tensor, out_layout: int, out_row_map: Optional[torch.Tensor] = None,
+                kv_layout: Optional[N.KVLayout] = None):
     """Launch the attention kernels; `out` must be zero-filled by the caller.  ``out_row_map`` (B*T int32)
-    redirects token-major output rows to compact slots."""
+    redirects token-major output rows to compact slots.  With ``kv_layout`` k and v are any tensors holding the
+    rows at those element strides (q stays (heads, T, D))."""
     heads, T, D = q.shape
     ws = None
     nbytes = int(N.lib().aspa_attn_workspace_bytes(int(total_rows), D))
@@ -295,11 +299,12 @@ def gather_attn(q, k, v, *, scales: Optional[Tuple[torch.Tensor, torch.Tensor, t
     # algorithmic bytes: each active row's q once, every key and value row once, each active output row once
     nbytes = int(total_rows) * D * (e + out.element_size()) + 2 * heads * T * D * e
     with _timed("attention", 2 if two_pass else 1, nbytes):
-        N.check(N.lib().aspa_gather_attn_fwd_mapped(
+        N.check(N.lib().aspa_gather_attn_fwd_ex(
             N.ptr(q), N.ptr(k), N.ptr(v), N.dtype_code(q.dtype), N.ptr(qs), N.ptr(ks), N.ptr(vs), heads, T, D, int(H),
             N.ptr(row_offsets), N.ptr(token_idx), int(max_rows), int(total_rows), N.ptr(cand), N.ptr(cand_len), int(L),
             C.byref(plan) if plan is not None else None, N.ptr(add_mask), N.ptr(out), N.dtype_code(out.dtype),
-            int(out_layout), N.ptr(out_row_map), N.ptr(ws), N.stream()), "gather_attn_fwd")
+            int(out_layout), N.ptr(out_row_map), C.byref(kv_layout) if kv_layout is not None else None, N.ptr(ws),
+            N.stream()), "gather_attn_fwd")
     return out
 
 
@@ -405,3 +410,84 @@ def scatter_rows_fill(src2d: torch.Tensor, slot_of: torch.Tensor, mask_u8: torch
         N.check(N.lib().aspa_scatter_rows_fill(N.ptr(src2d), N.ptr(slot_of), N.ptr(mask_u8), N.ptr(fill), n,
                                                Cdim * src2d.element_size(), N.ptr(dst), N.stream()), "scatter_rows_fill")
     return dst
+
+
+def rope_inplace(x_rows: torch.Tensor, n_rows: int, T: int, row_stride: int, H: int, D: int, cos: torch.Tensor,
+                 sin: torch.Tensor) -> None:
+    """Rotate, in place, ``n_rows`` rows of H*D elements that start at ``x_rows`` and lie ``row_stride`` elements apart."""
+    e = x_rows.element_size()
+    with _timed('rope_inplace', 1, 2 * n_rows * H * D * e):
+        N.check(N.lib().aspa_rope_inplace(N.ptr(x_rows), N.dtype_code(x_rows.dtype), int(n_rows), int(T), int(row_stride),
+                                          H, D, N.ptr(cos), N.ptr(sin), N.stream()), "rope_inplace")
+
+
+_CUBLAS = None
+
+
+def blas_sm_target(count: int) -> bool:
+    """``cublasSetSmCountTarget`` on the cuBLAS handle torch uses for the current device and stream: GEMMs issued
+    through it afterwards size their grids for ``count`` multiprocessors (0 = all of them).  Lets a large projection
+    leave a few SMs to small kernels that run beside it on another stream.  False when the library cannot be reached."""
+    global _CUBLAS
+    try:
+        if _CUBLAS is None:
+            path = next((l.split()[-1] for l in open("/proc/self/maps") if "libcublas.so" in l), "libcublas.so.12")
+            _CUBLAS = C.CDLL(path)
+            _CUBLAS.cublasSetSmCountTarget.restype = C.c_int
+            _CUBLAS.cublasSetSmCountTarget.argtypes = [C.c_void_p, C.c_int]
+        return _CUBLAS.cublasSetSmCountTarget(C.c_void_p(torch.cuda.current_blas_handle()), int(count)) == 0
+    except Exception:
+        return False
+
+
+TOKEN_COMPACT_MAX_T = 65536  # ASPA_TOKEN_COMPACT_MAX_T of the C header
+
+
+def token_select_compact(importance: torch.Tensor, need: int, threshold: float, guard: int, slots_per_row: int):
+    """Token keep plus the ordered kept-token list in one launch: (mask, kept, kept_idx padded with -1, slot_of)."""
+    B, T = importance.shape
+    dev = importance.device
+    mask = _empty((B, T), torch.uint8, dev)
+    kept = _empty((B,), torch.int32, dev)
+    kept_idx = _empty((B * slots_per_row,), torch.int64, dev)
+    slot_of = _empty((B * T,), torch.int32, dev)
+    with _timed('token_select', 1, _nb(importance, mask, kept_idx, slot_of)):
+        N.check(N.lib().aspa_token_select_compact(N.ptr(importance), B, T, int(need), float(threshold), int(guard),
+                                                  N.ptr(mask), N.ptr(kept), N.ptr(kept_idx), N.ptr(slot_of),
+                                                  int(slots_per_row), N.stream()), "token_select_compact")
+    return mask, kept, kept_idx, slot_of
+
+
+def head_select_pack(gate: torch.Tensor, g2h: torch.Tensor, B: int, T: int, H: int, *, k_host: int,
+                     k_dev: Optional[torch.Tensor], kmax: int, token_mask: Optional[torch.Tensor], capacity: int):
+    """Per-token head choice and row packing.  Returns (bits, top_idx, top_score, stat partials (2 * blocks),
+    row_offsets, token_idx)."""
+    n, G = gate.shape
+    dev = gate.device
+    bits = _empty((n,), torch.int64, dev)
+    top_idx = _empty((n, kmax), torch.int32, dev)
+    top_score = _empty((n, kmax), torch.float32, dev)
+    partials = _empty((2 * ((n + 255) // 256),), torch.float32, dev)
+    scratch = _empty((int(N.lib().aspa_pack_rows_scratch(B, H, T)),), torch.int32, dev)
+    offs = _empty((B * H + 1,), torch.int32, dev)
+    tok = _empty((max(1, capacity),), torch.int32, dev)
+    with _timed('head_select_pack', 3 if T % 256 == 0 else 4, _nb(gate, bits, top_idx, top_score) + 2 * _nb(bits)):
+        N.check(N.lib().aspa_head_select_pack(N.ptr(gate), B, T, G, N.ptr(g2h), H, int(k_host), N.ptr(k_dev), int(kmax),
+                                              N.ptr(token_mask), N.ptr(bits), N.ptr(top_idx), N.ptr(top_score),
+                                              N.ptr(partials), N.ptr(scratch), N.ptr(offs), N.ptr(tok), int(capacity),
+                                              N.stream()), "head_select_pack")
+    return bits, top_idx, top_score, partials, offs, tok
+
+
+def stats_record(row_offsets: torch.Tensor, kept: Optional[torch.Tensor], n_kept: int, kept_fill: float,
+                 k_dev: Optional[torch.Tensor], k_fill: float, head_partials: torch.Tensor,
+                 proto_partials: Optional[torch.Tensor], status: Optional[torch.Tensor]) -> torch.Tensor:
+    """fp64 record [row offsets | kept | k, adaptive k | score, entropy sums | 3 prototype sums | status]."""
+    rec = _empty((row_offsets.numel() + n_kept + 8,), torch.float64, row_offsets.device)
+    with _timed('stats_record', 1, 0):
+        N.check(N.lib().aspa_stats_record(
+            N.ptr(row_offsets), row_offsets.numel(), N.ptr(kept), int(n_kept), float(kept_fill), N.ptr(k_dev), float(k_fill),
+            N.ptr(head_partials), head_partials.numel() // 2, N.ptr(proto_partials),
+            proto_partials.numel() // 3 if proto_partials is not None else 0, N.ptr(status), N.ptr(rec), N.stream()),
+            "stats_record")
+    return rec

@@ -589,3 +589,86 @@ def test_merge_finalise_reports_candidate_positions(dev):
     cnt = int(kc.cpu())
     ki, ks, kp = ki.cpu()[:cnt], ks.cpu()[:cnt], kp.cpu()[:cnt]
     assert torch.equal(idx[kp], ki) and torch.equal(sc[kp], ks)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_reads_strided_kv_and_rope_in_place(dev, dtype):
+    """Keys/values left token-major inside a fused (B, T, 2, H, D) projection give the same attention as head-major
+    copies; the in-place rotation of the key half equals the relayout kernel's rotation."""
+    from proteus_flux_attention_b200 import ops, _native as N
+    B, T, H, D = 2, 520, 4, 64
+    C = H * D
+    g = torch.Generator().manual_seed(21)
+    kv = torch.randn(B, T, 2 * C, generator=g).to(dtype).to(dev)
+    q = torch.randn(B * H, T, D, generator=g).to(dtype).to(dev)
+    inv = (1.0 / (10000.0 ** (torch.arange(0, D, 2).float() / D))).to(dev)
+    cos, sin = ops.rope_table(inv, T, D, dtype)
+    k_ref, v_ref = ops.rope_relayout_kv(kv, H, D, cos, sin)
+    kv2 = kv.clone()
+    ops.rope_inplace(kv2.view(-1), B * T, T, 2 * C, H, D, cos, sin)
+    assert torch.equal(kv2.view(B, T, 2, H, D)[:, :, 0].permute(0, 2, 1, 3).reshape(B * H, T, D), k_ref)
+    assert torch.equal(kv2[..., C:], kv[..., C:])
+    # packed rows: every third token of every head, a window plan (tensor-core path for bf16) and causal (generic path)
+    tok = torch.arange(0, T, 3, dtype=torch.int32, device=dev)
+    offs = (torch.arange(B * H + 1, device=dev) * tok.numel()).to(torch.int32)
+    toks = tok.repeat(B * H)
+    layout = N.KVLayout(k_batch=T * 2 * C, k_head=D, k_token=2 * C, v_batch=T * 2 * C, v_head=D, v_token=2 * C)
+    flat = kv2.view(-1)
+    for plan in (ops.make_plan(48, 0, 0, 0, None, None), ops.make_plan(16, 4, 32, 0, None, None), None):
+        outs = []
+        for kk, vv, lay in ((k_ref, v_ref, None), (flat, flat[C:], layout)):
+            out = torch.zeros(B, T, C, dtype=dtype, device=dev)
+            ops.gather_attn(q, kk, vv, scales=None, H=H, row_offsets=offs, token_idx=toks, max_rows=tok.numel(),
+                            total_rows=toks.numel(), plan=plan, out=out, out_layout=N.OUT_TOKEN_MAJOR, kv_layout=lay)
+            outs.append(out)
+        assert torch.equal(outs[0], outs[1])
+
+
+@pytest.mark.parametrize("B,T,need,thr,guard", [(3, 300, 40, 0.0, 2), (2, 4096, 200, 0.0, 4), (2, 9000, 3000, 0.6, 1),
+                                                (1, 65536, 3277, 0.0, 4), (4, 16384, 16384, 0.0, 0), (2, 20001, 5, 0.0, 9)])
+def test_token_select_compact_equals_select_then_compact(dev, B, T, need, thr, guard):
+    from proteus_flux_attention_b200 import ops
+    g = torch.Generator().manual_seed(T + need)
+    imp = torch.rand(B, T, generator=g)
+    imp[0] = (imp[0] * 16).round() / 16  # ties
+    imp = imp.to(dev)
+    mask0, kept0 = ops.token_select(imp, need, thr, guard)
+    slots = min(T, int(kept0.max().cpu()) + 3)
+    mask1, kept1, idx1, slot1 = ops.token_select_compact(imp, need, thr, guard, slots)
+    assert torch.equal(mask0, mask1) and torch.equal(kept0, kept1)
+    idx1, slot1 = idx1.cpu().view(B, slots), slot1.cpu().view(B, T)
+    for b in range(B):
+        want = mask0[b].cpu().nonzero().view(-1)
+        k = want.numel()
+        assert torch.equal(idx1[b, :k], want + b * T) and bool((idx1[b, k:] == -1).all())
+        assert torch.equal(slot1[b, want].long(), torch.arange(k) + b * slots)
+
+
+@pytest.mark.parametrize("B,T,G,H,k", [(2, 512, 16, 16, 4), (1, 300, 8, 4, 2), (2, 1024, 32, 16, 16), (1, 256, 64, 64, 3),
+                                       (3, 777, 12, 12, 5)])
+def test_head_select_pack_equals_separate_calls(dev, B, T, G, H, k):
+    from proteus_flux_attention_b200 import ops
+    g = torch.Generator().manual_seed(B * T + G)
+    gate = torch.softmax(torch.randn(B * T, G, generator=g), dim=-1).to(dev)
+    g2h = (torch.arange(G) % H).to(torch.int32).to(dev)
+    tmask = (torch.rand(B * T, generator=g) < 0.4).to(torch.uint8).to(dev)
+    bits0, ti0, ts0, sums0 = ops.head_select(gate, g2h, H, k_host=k, k_dev=None, kmax=k, token_mask=tmask)
+    offs0, tok0 = ops.pack_rows(bits0, B, T, H, B * T * k)
+    bits1, ti1, ts1, part1, offs1, tok1 = ops.head_select_pack(gate, g2h, B, T, H, k_host=k, k_dev=None, kmax=k,
+                                                               token_mask=tmask, capacity=B * T * k)
+    assert torch.equal(bits0, bits1) and torch.equal(ti0, ti1) and torch.equal(ts0, ts1)
+    assert torch.equal(offs0, offs1)
+    n = int(offs0[-1].cpu())
+    assert torch.equal(tok0[:n], tok1[:n])
+    assert torch.equal(ops.reduce_partials(part1, 2), sums0)
+    # the record kernel reproduces the concatenation of the separate pieces
+    kept = torch.tensor([5, 7, 9][:B], dtype=torch.int32, device=dev)
+    status = torch.tensor([3], dtype=torch.int32, device=dev)
+    proto_part = torch.rand(3 * 11, generator=g).to(dev)
+    rec = ops.stats_record(offs1, kept, B, 0.0, None, 4.0, part1, proto_part, status).cpu()
+    want = torch.cat([offs1.double().cpu(), kept.double().cpu(), torch.tensor([4.0, 4.0], dtype=torch.float64),
+                      sums0.double().cpu(), ops.reduce_partials(proto_part, 3).double().cpu(),
+                      torch.tensor([3.0], dtype=torch.float64)])
+    assert torch.equal(rec, want)
+    rec2 = ops.stats_record(offs1, None, B, float(T), kept[:2] if B >= 2 else None, 1.0, part1, None, None).cpu()
+    assert bool((rec2[offs1.numel():offs1.numel() + B] == float(T)).all()) and bool((rec2[-4:] == 0).all())
