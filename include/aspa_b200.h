@@ -68,8 +68,9 @@ int aspa_router_fwd(const void* x, int x_dtype, int64_t n, int C, const void* w_
                     float usage_boost, float* gate_probs, float* importance, float* proto_sim, float* blend,
                     float* stat_partials, void* stream);
 
-/* The same router on tcgen05 tensor cores for bf16 activations: 128-token tiles, TMA-staged operands,
- * accumulator in tensor memory.  Results as aspa_router_fwd (fp32 accumulation order differs).
+/* The same router on tcgen05 tensor cores for bf16 activations: persistent CTAs, 128-token tiles, TMA-staged
+ * operands, double-buffered accumulator in tensor memory.  Results as aspa_router_fwd (fp32 accumulation order
+ * differs).  stat_partials here holds 3 * ceil(n/32) entries (one partial per 32 tokens).
  *   aspa_router_tc_scratch_bytes: bytes of 16-byte aligned scratch the call needs, or 0 when the shape is
  *     not supported (needs C % 64 == 0, G % 4 == 0, 4*G <= 128 with prototypes, G <= 128 without);
  *   n >= 128; status (1) int32, zeroed by the caller: set non-zero if a bounded device-side wait ran out

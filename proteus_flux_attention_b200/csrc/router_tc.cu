@@ -1,19 +1,30 @@
 // Router on the 5th-generation tensor cores (bf16 activations).
 //
-// One CTA owns a tile of 128 tokens.  The skinny product  [128 tokens x C] . [C x N]  with
+// The skinny product  [tokens x C] . [C x N]  with
 //   N = G router columns + 3*G prototype columns (the fp32 normalised prototypes split into three bf16 terms
 //       hi + mid + lo, so that the sum of the three products carries fp32 precision)
-// runs as tcgen05.mma (M=128, N, K=16, bf16 x bf16 -> fp32) with the accumulator in tensor memory.
-//   warp 4      : TMA producer — 128x64 activation tiles and Nx64 weight tiles, 128-byte swizzle, 3-stage ring
-//   warp 5      : allocates tensor memory, issues the MMAs, commits them to the "stage free" and "accumulator
-//                 ready" mbarriers, frees tensor memory at the end
-//   warps 0..3  : while the ring runs, sum x^2 of their own token row straight from the staged tiles (the L2 norm
-//                 the cosine needs); afterwards read the accumulator with tcgen05.ld and run the per-token epilogue
-//                 (softmaxes, prototype blend, importance) shared with the CUDA-core kernel.
+// runs as tcgen05.mma (M=128, N, K=16, bf16 x bf16 -> fp32) with the accumulators in tensor memory.
+//
+// Persistent kernel, one CTA per SM, tiles of 128 tokens handed out round-robin.  The activation stream never waits
+// for an epilogue: the accumulator is double-buffered in tensor memory and every role has its own warps.
+//   warps 0..3   : norm warps — while the ring runs, sum x^2 of their own token row straight from the staged tiles
+//                  (the L2 norm the cosine needs) and hand the 128 norms of a tile over through shared memory
+//   warps 4..7   : epilogue group 0 (tiles 0, 2, 4, ... of this CTA, accumulator buffer 0)
+//   warps 8..11  : epilogue group 1 (tiles 1, 3, 5, ..., accumulator buffer 1)
+//                  read the accumulator with tcgen05.ld and run the per-token epilogue (softmaxes, prototype blend,
+//                  importance) shared with the CUDA-core kernel, in registers when G is 16 or 32
+//   warp 12      : TMA producer — 128x64 activation tiles and Nx64 weight tiles, 128-byte swizzle, ring of up to
+//                  8 stages (as many as shared memory holds)
+//   warp 13      : allocates tensor memory, issues the MMAs, commits them to the "stage free" and "accumulator
+//                  ready" mbarriers, frees tensor memory at the end
+// (Tried and dropped, both slower: taking the norms from the tensor cores as the diagonal of x.x^T, which costs more
+// shared-memory bandwidth than the norm warps; prefetching the next tile into L2 with cp.async.bulk.prefetch.)
 // x is read from HBM exactly once; the weight tiles (<= 256 KB in total) stay in L2.
-// Every mbarrier wait is bounded: on expiry the kernel raises a status word, skips its remaining work, still
-// frees tensor memory and returns.
+// Every mbarrier wait is bounded: on expiry the kernel raises a status word, every role leaves its loop, tensor
+// memory is still freed and the kernel returns.
 #include <cuda.h>
+
+#include <algorithm>
 
 #include "common.cuh"
 #include "router_epilogue.cuh"
@@ -22,12 +33,48 @@ namespace aspa {
 
 constexpr int TC_BM = 128;
 constexpr int TC_BK = 64;       // bf16 per k-block = one 128-byte swizzle row
-constexpr int TC_STAGES = 3;
+constexpr int TC_MAX_STAGES = 8;
 constexpr int TC_A_BYTES = TC_BM * TC_BK * 2;   // 16 KB
-constexpr int TC_B_BYTES_MAX = 128 * TC_BK * 2; // 16 KB
-constexpr int TC_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES_MAX;
-constexpr int TC_SMEM_BYTES = TC_STAGES * TC_STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int TC_THREADS = 14 * 32;
+constexpr int TC_SMEM_LIMIT = 225 * 1024;
 constexpr uint32_t TC_SPIN_LIMIT = 1u << 22;
+
+// Shared-memory plan of one CTA (all offsets from the 1024-byte aligned base).
+struct TcPlan {
+  int stages;        // ring depth
+  int stage_bytes;   // 16 KB of activations (+ N * 128 bytes of weights when they stream through the ring)
+  int w_resident;    // 1: the whole weight operand (num_k tiles of N x 64) sits in shared memory, loaded once
+  int w_off;         // resident weights
+  int scratch_off;   // 2 groups x 128 rows x (2G+1) floats for the shared-memory epilogue (G other than 16, 32)
+  int norm_off;      // 2 x 128 floats: row norms of the tile in flight for each accumulator buffer
+  int bar_off;       // mbarriers, tensor-memory slot, abort flag (256 B), then copies of conf_eps and usage_bias (2 x 256 B)
+  int total;         // bytes to request (includes 1024 of alignment slack)
+};
+
+static inline bool tc_reg_epilogue(int N, int G, bool has_proto) {
+  // the register epilogue expects the column layout [G | G | G | G] (N == 4G, no padding) or just [G]
+  return (G == 16 || G == 32) && (!has_proto || N == 4 * G);
+}
+
+// The TMA unit turns a box into one request per 128-byte row and, measured, issues about one row every 6 cycles:
+// 192 rows per k-block (128 of activations, 64 of weights) cap the stream near 14 B/clk per SM, a third of what HBM
+// can deliver.  Keeping the weights resident leaves the whole request rate to the activations.
+static inline TcPlan tc_plan(int N, int G, int C, bool has_proto) {
+  TcPlan p;
+  const int scratch = tc_reg_epilogue(N, G, has_proto) ? 0 : 2 * TC_BM * (2 * G + 1) * 4;
+  const int w_bytes = N * C * 2;
+  const int fixed = scratch + 2 * TC_BM * 4 + 1024 + 1024;
+  p.w_resident = (TC_SMEM_LIMIT - fixed - w_bytes) / TC_A_BYTES >= 4 ? 1 : 0;
+  p.stage_bytes = p.w_resident ? TC_A_BYTES : TC_A_BYTES + N * TC_BK * 2;
+  p.stages = (TC_SMEM_LIMIT - fixed - (p.w_resident ? w_bytes : 0)) / p.stage_bytes;
+  if (p.stages > TC_MAX_STAGES) p.stages = TC_MAX_STAGES;
+  p.w_off = p.stages * p.stage_bytes;
+  p.scratch_off = p.w_off + (p.w_resident ? w_bytes : 0);
+  p.norm_off = p.scratch_off + scratch;
+  p.bar_off = (p.norm_off + 2 * TC_BM * 4 + 15) & ~15;
+  p.total = p.bar_off + 1024 + 1024;
+  return p;
+}
 
 __device__ __forceinline__ uint32_t s_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -89,34 +136,58 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-__global__ void __launch_bounds__(192, 2)
-router_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w, int64_t n,
+__device__ __forceinline__ bool aborted(const int* flag) { return *reinterpret_cast<const volatile int*>(flag) != 0; }
+
+// GT = number of gates when it is 16 or 32 (epilogue in registers), 0 = any other count (epilogue through shared memory)
+template <int GT>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+router_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
+                 const __nv_bfloat16* __restrict__ x, int64_t n,
                  int C, int G, int N, int has_proto, const float* __restrict__ conf_eps,
                  const float* __restrict__ usage_bias, float proto_temp, float proto_threshold, float proto_span,
                  float proto_blend, float usage_boost, float* __restrict__ gate_probs,
                  float* __restrict__ importance, float* __restrict__ proto_sim, float* __restrict__ blend,
-                 float* __restrict__ stat_partials, int* __restrict__ status) {
+                 float* __restrict__ stat_partials, int* __restrict__ status, const TcPlan plan) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + TC_STAGES * TC_STAGE_BYTES);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * TC_STAGES + 1);
+  const int S = plan.stages;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + plan.bar_off);
+  // barrier order: full[S], empty[S], acc_full[2], acc_empty[2], nrm_full[2], nrm_empty[2], wbar
+  const uint32_t full0 = s_addr(bars), empty0 = s_addr(bars + S), acc_full0 = s_addr(bars + 2 * S),
+                 acc_empty0 = s_addr(bars + 2 * S + 2), nrm_full0 = s_addr(bars + 2 * S + 4),
+                 nrm_empty0 = s_addr(bars + 2 * S + 6), wbar = s_addr(bars + 2 * S + 8);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 9);
   int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
-  const uint32_t full0 = s_addr(bars), empty0 = s_addr(bars + TC_STAGES), accbar = s_addr(bars + 2 * TC_STAGES);
+  float* norm_s = reinterpret_cast<float*>(smem + plan.norm_off);
+  float* conf_s = reinterpret_cast<float*>(smem + plan.bar_off + 256);
+  float* ub_s = conf_s + 64;
+  if (threadIdx.x < 64) {
+    conf_s[threadIdx.x] = (conf_eps != nullptr && (int)threadIdx.x < G) ? conf_eps[threadIdx.x] : 0.f;
+    ub_s[threadIdx.x] = (usage_bias != nullptr && (int)threadIdx.x < G) ? usage_bias[threadIdx.x] : 0.f;
+  }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile = blockIdx.x;
   const int num_k = C / TC_BK;
-  const uint32_t tmem_cols = N <= 32 ? 32 : (N <= 64 ? 64 : 128);
+  const int64_t ntiles = (n + TC_BM - 1) / TC_BM;
+  const uint32_t buf_cols = (uint32_t)N;   // one accumulator buffer
+  uint32_t tmem_cols = 32;
+  while (tmem_cols < 2 * buf_cols) tmem_cols <<= 1;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < TC_STAGES; ++s) {
+    for (int s = 0; s < S; ++s) {
       mbar_init(full0 + 8 * s, 1);       // the producer's expect_tx arrival; TMA completes the bytes
       mbar_init(empty0 + 8 * s, 1 + 4);  // one MMA commit + one arrival per norm warp
     }
-    mbar_init(accbar, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full0 + 8 * b, 1);          // MMA commit
+      mbar_init(acc_empty0 + 8 * b, TC_BM);     // every thread of the epilogue group that owns the buffer
+      mbar_init(nrm_full0 + 8 * b, TC_BM);      // every norm thread
+      mbar_init(nrm_empty0 + 8 * b, TC_BM);     // every thread of the epilogue group
+    }
+    mbar_init(wbar, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 5) {  // whole warp: allocate tensor memory, publish its base address in shared memory
+  if (warp == 13) {  // whole warp: allocate tensor memory, publish its base address in shared memory
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s_addr(tmem_slot)), "r"(tmem_cols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -125,122 +196,197 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
 
-  float nsq = 0.f;
-  if (warp == 4) {
+  if (warp == 12) {
+    // ---- TMA producer ------------------------------------------------------------------------------------
     if (lane == 0) {
-      for (int kb = 0; kb < num_k; ++kb) {
-        const int s = kb % TC_STAGES;
-        const uint32_t ph = (kb / TC_STAGES) & 1;
-        if (!mbar_wait(empty0 + 8 * s, ph ^ 1)) { atomicExch(abort_flag, 1); atomicExch(status, 1); break; }
-        const uint32_t a_dst = s_addr(smem + s * TC_STAGE_BYTES), b_dst = a_dst + TC_A_BYTES;
-        mbar_expect_tx(full0 + 8 * s, TC_A_BYTES + N * TC_BK * 2);
-        tma_load_2d(a_dst, &tmap_x, kb * TC_BK, tile * TC_BM, full0 + 8 * s);
-        tma_load_2d(b_dst, &tmap_w, kb * TC_BK, 0, full0 + 8 * s);
+      uint32_t it = 0;
+      bool ok = true;
+      const uint32_t w_tile = (uint32_t)N * TC_BK * 2;
+      if (plan.w_resident) {  // the whole weight operand, once: num_k tiles of N x 64 on one barrier
+        mbar_expect_tx(wbar, w_tile * (uint32_t)num_k);
+        for (int kb = 0; kb < num_k; ++kb) tma_load_2d(s_addr(smem + plan.w_off) + kb * w_tile, &tmap_w, kb * TC_BK, 0, wbar);
       }
+      for (int64_t tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+        for (int kb = 0; kb < num_k; ++kb, ++it) {
+          const int s = (int)(it % (uint32_t)S);
+          const uint32_t ph = (it / (uint32_t)S) & 1u;
+          if (aborted(abort_flag)) { ok = false; break; }
+          if (!mbar_wait(empty0 + 8 * s, ph ^ 1u)) { atomicExch(abort_flag, 1); atomicExch(status, 1); ok = false; break; }
+          const uint32_t a_dst = s_addr(smem + s * plan.stage_bytes), b_dst = a_dst + TC_A_BYTES;
+          mbar_expect_tx(full0 + 8 * s, TC_A_BYTES + (plan.w_resident ? 0u : w_tile));
+          tma_load_2d(a_dst, &tmap_x, kb * TC_BK, (int)(tile * TC_BM), full0 + 8 * s);
+          if (!plan.w_resident) tma_load_2d(b_dst, &tmap_w, kb * TC_BK, 0, full0 + 8 * s);
+        }
+      }
+      if (plan.w_resident) mbar_wait(wbar, 0);  // the weight copies, too, must have landed before shared memory goes away
+      // Shared memory must outlive every copy this thread started.  On the normal path the consumers have already
+      // waited for all of them; after an abort they may have left early, so wait here (bounded) for the last
+      // copy issued into each stage.
+      const uint32_t first = it > (uint32_t)S ? it - (uint32_t)S : 0u;
+      for (uint32_t j = first; j < it; ++j) mbar_wait(full0 + 8 * (j % (uint32_t)S), (j / (uint32_t)S) & 1u);
     }
-  } else if (warp == 5) {
+  } else if (warp == 13) {
+    // ---- MMA issuer --------------------------------------------------------------------------------------
     if (lane == 0) {
       // instruction descriptor: D fp32, A/B bf16, both K-major, N/8 at bit 17, M/16 at bit 24
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+      uint32_t it = 0, t = 0;
       bool ok = true;
-      for (int kb = 0; kb < num_k && ok; ++kb) {
-        const int s = kb % TC_STAGES;
-        const uint32_t ph = (kb / TC_STAGES) & 1;
-        if (!mbar_wait(full0 + 8 * s, ph)) { atomicExch(abort_flag, 1); atomicExch(status, 2); ok = false; break; }
+      if (plan.w_resident && !mbar_wait(wbar, 0)) { atomicExch(abort_flag, 1); atomicExch(status, 8); ok = false; }
+      for (int64_t tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++t) {
+        const uint32_t buf = t & 1u, aph = (t >> 1) & 1u;
+        if (aborted(abort_flag)) break;
+        if (!mbar_wait(acc_empty0 + 8 * buf, aph ^ 1u)) { atomicExch(abort_flag, 1); atomicExch(status, 5); break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a_addr = s_addr(smem + s * TC_STAGE_BYTES), b_addr = a_addr + TC_A_BYTES;
+        const uint32_t d_tmem = tmem_base + buf * buf_cols;
+        for (int kb = 0; kb < num_k; ++kb, ++it) {
+          const int s = (int)(it % (uint32_t)S);
+          const uint32_t ph = (it / (uint32_t)S) & 1u;
+          if (aborted(abort_flag)) { ok = false; break; }
+          if (!mbar_wait(full0 + 8 * s, ph)) { atomicExch(abort_flag, 1); atomicExch(status, 2); ok = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a_addr = s_addr(smem + s * plan.stage_bytes);
+          const uint32_t b_addr = plan.w_resident ? s_addr(smem + plan.w_off) + (uint32_t)kb * (uint32_t)N * TC_BK * 2
+                                                  : a_addr + TC_A_BYTES;
 #pragma unroll
-        for (int k = 0; k < TC_BK / 16; ++k) {
-          umma_bf16(tmem_base, umma_desc_k_sw128(a_addr + k * 32), umma_desc_k_sw128(b_addr + k * 32), idesc,
-                    (kb > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < TC_BK / 16; ++k) {
+            umma_bf16(d_tmem, umma_desc_k_sw128(a_addr + k * 32), umma_desc_k_sw128(b_addr + k * 32), idesc,
+                      (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(empty0 + 8 * s);  // arrives once the MMAs above have finished reading this stage
         }
-        umma_commit(empty0 + 8 * s);  // arrives once the MMAs above have finished reading this stage
+        if (ok) umma_commit(acc_full0 + 8 * buf);  // arrives once every MMA of the tile has landed in tensor memory
       }
-      umma_commit(accbar);            // arrives once every MMA has landed in tensor memory
+    }
+  } else if (warp < 4) {
+    // ---- norm warps: thread r owns token row r of every tile ------------------------------------------------
+    const int r = threadIdx.x;
+    uint32_t it = 0, t = 0;
+    bool ok = true;
+    for (int64_t tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++t) {
+      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+      for (int kb = 0; kb < num_k; ++kb, ++it) {
+        const int s = (int)(it % (uint32_t)S);
+        const uint32_t ph = (it / (uint32_t)S) & 1u;
+        if (aborted(abort_flag)) { ok = false; break; }
+        if (!mbar_wait(full0 + 8 * s, ph)) { atomicExch(abort_flag, 1); atomicExch(status, 3); ok = false; break; }
+        if (has_proto) {
+          const unsigned char* row = smem + s * plan.stage_bytes + r * 128;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            // the swizzle only permutes 16-byte chunks inside a row; rotate the start so lanes hit different banks
+            const uint4 raw = *reinterpret_cast<const uint4*>(row + (((j + r) & 7) << 4));
+            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+            const float2 f0 = __bfloat1622float2(h2[0]), f1 = __bfloat1622float2(h2[1]);
+            const float2 f2 = __bfloat1622float2(h2[2]), f3 = __bfloat1622float2(h2[3]);
+            a0 = fmaf(f0.x, f0.x, a0); a1 = fmaf(f0.y, f0.y, a1);
+            a2 = fmaf(f1.x, f1.x, a2); a3 = fmaf(f1.y, f1.y, a3);
+            a0 = fmaf(f2.x, f2.x, a0); a1 = fmaf(f2.y, f2.y, a1);
+            a2 = fmaf(f3.x, f3.x, a2); a3 = fmaf(f3.y, f3.y, a3);
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty0 + 8 * s);
+      }
+      if (!ok) break;
+      const uint32_t buf = t & 1u, nph = (t >> 1) & 1u;
+      if (!mbar_wait(nrm_empty0 + 8 * buf, nph ^ 1u)) { atomicExch(abort_flag, 1); atomicExch(status, 6); break; }
+      norm_s[buf * TC_BM + r] = (a0 + a1) + (a2 + a3);
+      mbar_arrive(nrm_full0 + 8 * buf);  // release: the store above is visible to whoever observes the phase flip
     }
   } else {
-    // norm warps: thread r owns token row r of the tile
-    const int r = threadIdx.x;
-    bool ok = true;
-    for (int kb = 0; kb < num_k && ok; ++kb) {
-      const int s = kb % TC_STAGES;
-      const uint32_t ph = (kb / TC_STAGES) & 1;
-      if (!mbar_wait(full0 + 8 * s, ph)) { atomicExch(abort_flag, 1); atomicExch(status, 3); ok = false; break; }
-      const unsigned char* row = smem + s * TC_STAGE_BYTES + r * 128;
+    // ---- epilogue groups ---------------------------------------------------------------------------------
+    const int grp = (warp - 4) >> 2;          // accumulator buffer of this group
+    const int r = threadIdx.x - 128 - grp * TC_BM;   // row of the tile = lane of tensor memory
+    const int quarter = warp & 3;             // a warp may only touch tensor-memory lanes [32*(warp%4), +32)
+    const int stride = 2 * G + 1;
+    float* row = reinterpret_cast<float*>(smem + plan.scratch_off) + (grp * TC_BM + r) * stride;
+    const int64_t nb = (n + 31) / 32;         // statistics: one partial per 32 tokens
+    uint32_t t = 0;
+    for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++t) {
+      if ((int)(t & 1u) != grp) continue;
+      const uint32_t ph = (t >> 1) & 1u;
+      if (aborted(abort_flag)) break;
+      if (!mbar_wait(acc_full0 + 8 * grp, ph)) { atomicExch(abort_flag, 1); atomicExch(status, 4); break; }
+      if (!mbar_wait(nrm_full0 + 8 * grp, ph)) { atomicExch(abort_flag, 1); atomicExch(status, 7); break; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)grp * buf_cols;
+      const int64_t tok = tile * TC_BM + r;
+      float st_sim = 0.f, st_bs = 0.f;
+      if (GT > 0) {
+        constexpr int GR = GT > 0 ? GT : 16;
+        float lg[GR], pd[GR];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        // the swizzle only permutes 16-byte chunks inside a row; rotate the start so lanes hit different banks
-        const uint4 raw = *reinterpret_cast<const uint4*>(row + (((j + r) & 7) << 4));
-        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        for (int c0 = 0; c0 < GR; c0 += 16) {
+          float v[16];
+          tmem_ld16(t_row + (uint32_t)c0, v);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float2 f = __bfloat1622float2(h2[i]);
-          nsq = fmaf(f.x, f.x, nsq);
-          nsq = fmaf(f.y, f.y, nsq);
+          for (int i = 0; i < 16; ++i) lg[c0 + i] = v[i];
+        }
+#pragma unroll
+        for (int g = 0; g < GR; ++g) pd[g] = 0.f;
+        if (has_proto) {
+#pragma unroll
+          for (int part = 0; part < 3; ++part) {   // hi, then + mid, then + lo
+#pragma unroll
+            for (int c0 = 0; c0 < GR; c0 += 16) {
+              float v[16];
+              tmem_ld16(t_row + (uint32_t)((1 + part) * GR + c0), v);
+#pragma unroll
+              for (int i = 0; i < 16; ++i) pd[c0 + i] = part == 0 ? v[i] : pd[c0 + i] + v[i];
+            }
+          }
+        }
+        const float nsq = norm_s[grp * TC_BM + r];
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        mbar_arrive(acc_empty0 + 8 * grp);   // the MMA warp may overwrite this accumulator buffer
+        mbar_arrive(nrm_empty0 + 8 * grp);   // the norm warps may overwrite this norm buffer
+        if (tok < n) {
+          float imp;
+          router_epilogue_regs<GR>(lg, pd, true, has_proto != 0, nsq, conf_eps ? conf_s : nullptr,
+                                   usage_bias ? ub_s : nullptr, proto_temp, proto_threshold, proto_span, proto_blend,
+                                   usage_boost, gate_probs + tok * G, &imp, proto_sim ? proto_sim + tok : nullptr,
+                                   blend ? blend + tok : nullptr, &st_sim, &st_bs);
+          importance[tok] = imp;
+        }
+      } else {
+        for (int c0 = 0; c0 < N; c0 += 16) {
+          float v[16];
+          tmem_ld16(t_row + (uint32_t)c0, v);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int c = c0 + i;
+            if (c < 2 * G) row[c] = v[i];                            // router logits, then the hi prototype term
+            else if (c < 4 * G) row[G + (c - 2 * G) % G] += v[i];    // mid and lo terms fold into the same slot
+          }
+        }
+        const float nsq = norm_s[grp * TC_BM + r];
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        mbar_arrive(acc_empty0 + 8 * grp);
+        mbar_arrive(nrm_empty0 + 8 * grp);
+        if (tok < n) {
+          float imp;
+          router_epilogue(row, 1, G, true, has_proto != 0, nsq, conf_eps ? conf_s : nullptr, usage_bias ? ub_s : nullptr,
+                          proto_temp, proto_threshold, proto_span, proto_blend, usage_boost, gate_probs + tok * G, &imp,
+                          proto_sim ? proto_sim + tok : nullptr, blend ? blend + tok : nullptr, &st_sim, &st_bs);
+          importance[tok] = imp;
         }
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(empty0 + 8 * s);
+      if (stat_partials) {  // fixed order inside the warp: shuffle tree
+        const float a = warp_sum(st_sim), b = warp_sum(st_bs), c = warp_sum(st_bs > 0.f ? 1.f : 0.f);
+        const int64_t blk = tile * (TC_BM / 32) + quarter;
+        if (lane == 0 && blk < nb) {
+          stat_partials[blk] = a;
+          stat_partials[nb + blk] = b;
+          stat_partials[2 * nb + blk] = c;
+        }
+      }
     }
   }
 
-  // ---- epilogue -----------------------------------------------------------------------------------------
-  float st_sim = 0.f, st_bs = 0.f;
-  float* es = reinterpret_cast<float*>(smem);  // reuses the ring: every load and MMA has completed by now
-  const int stride = 2 * G + 1;
-  if (warp < 4) {
-    const int r = threadIdx.x;
-    bool ok = *reinterpret_cast<volatile int*>(abort_flag) == 0;
-    if (ok && !mbar_wait(accbar, 0)) { atomicExch(abort_flag, 1); atomicExch(status, 4); ok = false; }
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (ok) {
-      float* row = es + r * stride;
-      for (int c0 = 0; c0 < N; c0 += 16) {
-        float v[16];
-        tmem_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const int c = c0 + i;
-          if (c < G) row[c] = v[i];
-          else if (c < 2 * G) row[c] = v[i];          // hi term
-          else if (c < 4 * G) row[G + (c - 2 * G) % G] += v[i];  // mid and lo terms fold into the same slot
-        }
-      }
-      const int64_t tok = (int64_t)tile * TC_BM + r;
-      if (tok < n) {
-        float imp;
-        router_epilogue(row, 1, G, true, has_proto != 0, nsq, conf_eps, usage_bias, proto_temp, proto_threshold,
-                        proto_span, proto_blend, usage_boost, gate_probs + tok * G, &imp,
-                        proto_sim ? proto_sim + tok : nullptr, blend ? blend + tok : nullptr, &st_sim, &st_bs);
-        importance[tok] = imp;
-      }
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (stat_partials) {  // same layout as the CUDA-core kernel: one entry per 64 tokens
-    float* sbuf = es + TC_BM * stride;
-    if (warp < 4) {
-      sbuf[threadIdx.x] = st_sim;
-      sbuf[TC_BM + threadIdx.x] = st_bs;
-    }
-    __syncthreads();
-    if (threadIdx.x < 2) {
-      const int64_t nb = (n + 63) / 64, blk = (int64_t)tile * 2 + threadIdx.x;
-      if (blk < nb) {
-        float a = 0.f, b = 0.f, c = 0.f;
-        for (int i = 0; i < 64; ++i) {
-          a += sbuf[threadIdx.x * 64 + i];
-          b += sbuf[TC_BM + threadIdx.x * 64 + i];
-          c += sbuf[TC_BM + threadIdx.x * 64 + i] > 0.f ? 1.f : 0.f;
-        }
-        stat_partials[blk] = a;
-        stat_partials[nb + blk] = b;
-        stat_partials[2 * nb + blk] = c;
-      }
-    }
-  }
-  if (warp == 5) {
+  if (warp == 13) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
   }
@@ -333,14 +479,25 @@ extern "C" int aspa_router_fwd_tc(const void* x, int64_t n, int C, const void* w
     set_error("aspa_router_fwd_tc: cuTensorMapEncodeTiled failed");
     return ASPA_ERR_CUDA;
   }
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaFuncSetAttribute(router_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES);
-    attr_set = true;
+  const TcPlan plan = tc_plan(N, G, C, has_proto);
+  if (plan.stages < 2) {
+    set_error("aspa_router_fwd_tc: shared memory holds fewer than two ring stages for this shape");
+    return ASPA_ERR_UNSUPPORTED;
   }
-  router_tc_kernel<<<(unsigned)ceil_div(n, TC_BM), 192, TC_SMEM_BYTES, st>>>(
-      mx, mw, n, C, G, N, has_proto ? 1 : 0, conf_eps, usage_bias, proto_temp, proto_threshold, proto_span,
-      proto_blend, usage_boost, gate_probs, importance, proto_sim, blend, stat_partials, status);
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int64_t ntiles = ceil_div(n, TC_BM);
+  const unsigned grid = (unsigned)std::min<int64_t>(ntiles, sms > 0 ? sms : 148);
+  auto launch = [&](auto kernel) {
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, plan.total);
+    kernel<<<grid, TC_THREADS, plan.total, st>>>(mx, mw, (const __nv_bfloat16*)x, n, C, G, N, has_proto ? 1 : 0, conf_eps, usage_bias, proto_temp,
+                                                 proto_threshold, proto_span, proto_blend, usage_boost, gate_probs,
+                                                 importance, proto_sim, blend, stat_partials, status, plan);
+  };
+  if (tc_reg_epilogue(N, G, has_proto) && G == 16) launch(router_tc_kernel<16>);
+  else if (tc_reg_epilogue(N, G, has_proto)) launch(router_tc_kernel<32>);
+  else launch(router_tc_kernel<0>);
   ASPA_CHECK_LAUNCH();
   return ASPA_OK;
 }

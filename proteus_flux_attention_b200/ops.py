@@ -99,11 +99,11 @@ def router_fwd(x2d: torch.Tensor, w_router: torch.Tensor, proto_hat: Optional[to
     has_proto = proto_hat is not None
     sim = _empty((n,), torch.float32, dev) if has_proto else None
     bs = _empty((n,), torch.float32, dev) if has_proto else None
-    ntile = (n + 63) // 64
-    partials = _empty((3 * ntile,), torch.float32, dev) if (want_stats and has_proto) else None
     tc_bytes = 0
     if USE_TC_ROUTER and x2d.dtype == torch.bfloat16 and n >= 128 and x2d.data_ptr() % 16 == 0:
         tc_bytes = int(N.lib().aspa_router_tc_scratch_bytes(Cdim, G, int(has_proto)))
+    ntile = (n + 31) // 32 if tc_bytes > 0 else (n + 63) // 64  # statistics partials: per 32 / per 64 tokens
+    partials = _empty((3 * ntile,), torch.float32, dev) if (want_stats and has_proto) else None
     if tc_bytes > 0:
         scratch = _empty((tc_bytes,), torch.uint8, dev)
         with _timed('router_tc', 2, _nb(x2d, w_router, proto_hat, gate, imp, sim, bs)):
