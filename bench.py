@@ -257,6 +257,41 @@ class LayerWorkload:
         return self.host_x.numel() * 2, y.numel() * 2
 
 
+class RouterWorkload:
+    """The router alone on 65536 tokens x 1024 channels (bf16, 16 gates with prototypes): the shape of one chunk of the
+    chunked pipeline.  For profiling the tcgen05 kernel in isolation (--profile-mode)."""
+    name = "router_64k"
+
+    def __init__(self, device):
+        from proteus_flux_attention_b200 import ops
+        self.ops, self.device = ops, device
+        self.tokens = 65536
+        g = torch.Generator(device=device).manual_seed(0)
+        self.x = torch.randn(self.tokens, D_MODEL, generator=g, device=device).to(torch.bfloat16)
+        self.w = (torch.randn(16, D_MODEL, generator=g, device=device) * 0.03).to(torch.bfloat16)
+        self.p = torch.nn.functional.normalize(torch.randn(16, D_MODEL, generator=g, device=device), dim=-1)
+        self.conf = torch.full((16,), 1e-6, device=device)
+        self.ub = torch.full((16,), 1.0 / 16, device=device)
+        self.host_x = None
+        self.config = {"workload": self.name, "tokens": self.tokens, "d_model": D_MODEL, "gates": 16,
+                       "l2": "activations (134 MB) larger than L2"}
+
+    def step(self):
+        return self.ops.router_fwd(self.x, self.w, self.p, self.conf, self.ub, temp=0.3, threshold=0.2, span=0.8, blend=0.5,
+                                   usage_boost=0.1, raw_stats=True)
+
+    def step_e2e(self):
+        if self.host_x is None:
+            self.host_x = self.x.cpu().pin_memory()
+            self.host_imp = torch.empty(self.tokens, dtype=torch.float32, pin_memory=True)
+        x = self.host_x.to(self.device, non_blocking=True)
+        out = self.ops.router_fwd(x, self.w, self.p, self.conf, self.ub, temp=0.3, threshold=0.2, span=0.8, blend=0.5,
+                                  usage_boost=0.1, raw_stats=True)
+        self.host_imp.copy_(out[1], non_blocking=True)
+        torch.cuda.synchronize()
+        return self.host_x.numel() * 2, self.host_imp.numel() * 4
+
+
 # ----------------------------------------------------------------------------------------------- CPU oracle timing
 def cpu_oracle_sample(workload: str):
     """Time the CPU oracle on a bounded sample of the workload; returns (tokens_per_s, cores, description)."""
@@ -314,7 +349,7 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="chunked_1m", choices=["chunked_1m", "shortlist_256k", "sparse_16k"])
+    ap.add_argument("--workload", default="chunked_1m", choices=["chunked_1m", "shortlist_256k", "sparse_16k", "router_64k"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--clock-sampler", default="nvml", choices=["nvml", "smi", "none"],
@@ -358,7 +393,7 @@ def main():
     else:
         if world > 1:
             raise SystemExit("layer workloads do not shard: run them with --gpus 1 (replicas only)")
-        wl = LayerWorkload(args.workload, device)
+        wl = RouterWorkload(device) if args.workload == "router_64k" else LayerWorkload(args.workload, device)
 
     def sync():
         if world > 1:
@@ -438,7 +473,7 @@ def main():
                "d2h_bytes_per_step": int(d2h)}
 
     cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and args.workload != "router_64k":
         v, cores, desc = cpu_oracle_sample(args.workload)
         cpu = {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": desc}
     if rank == 0:
