@@ -298,11 +298,13 @@ int aspa_chunk_select(const float* importance, const uint8_t* token_mask, int T,
  * unique index (the lowest, as the reference's sort key does), the max_tokens
  * best of them, ascending index order.
  *   scores/indices (n): entries with index < 0 are ignored; seq_len bounds the indices
- *   table: scratch of 8 * seq_len bytes; keep_idx (max_tokens) int64, keep_scores (max_tokens) fp32,
+ *   table: scratch of aspa_merge_finalise_scratch(seq_len) bytes, 16-byte aligned; keep_idx (max_tokens) int64,
+ *   padded with seq_len beyond keep_count when n <= ASPA_MERGE_POS_MAX; keep_scores (max_tokens) fp32,
  *   keep_count (1) int32 out.  keep_pos (max_tokens) int64 or NULL: position in scores/indices of the
  *   entry that represents each kept index (lets the caller fetch rows it stored per candidate instead of going
  *   back to the sequence); only available for n <= ASPA_MERGE_POS_MAX. */
 #define ASPA_MERGE_POS_MAX 65536
+int64_t aspa_merge_finalise_scratch(int64_t seq_len);
 int aspa_merge_finalise(const float* scores, const int64_t* indices, int64_t n, int64_t seq_len,
                         int max_tokens, void* table, int64_t* keep_idx, float* keep_scores, int64_t* keep_pos,
                         int32_t* keep_count, void* stream);
@@ -314,7 +316,7 @@ int aspa_gather_rows(const void* src, const int64_t* idx, const int32_t* count_d
 
 /* Ordered compaction of a byte mask (n): kept_idx (capacity) int64 gets the indices i with mask[i] != 0 in
  * ascending order, padded with n; slot_of (n) int32 gets the position of every kept index in kept_idx (entries of
- * dropped indices are left unwritten); count (1) int32 the number kept.  Indices beyond `capacity` are dropped
+ * dropped indices are left unwritten; slot_of may be NULL); count (1) int32 the number kept.  Indices beyond `capacity` are dropped
  * (count still reports all of them).  scratch: aspa_compact_mask_scratch(n) bytes.  No reference counterpart
  * (the reference uses boolean indexing, aspa.py:1715-1721). */
 int64_t aspa_compact_mask_scratch(int64_t n);

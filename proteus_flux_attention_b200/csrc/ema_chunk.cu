@@ -562,17 +562,14 @@ __device__ void bitonic_i32(int* a, int n) {
 }
 
 // Selection over the representatives with the candidates spread over a cluster (8 per thread, 8192 per CTA, up to
-// 8 CTAs).  The picks land in the sort buffer of CTA 0 through distributed shared memory; CTA 0 sorts them by index.
+// 8 CTAs).  Every pick raises the byte of its sequence index in `picked`; an ordered compaction of that mask then
+// yields the kept indices in ascending order (no sort).
 __global__ void __launch_bounds__(CL_THREADS) merge_select_cluster_kernel(const float* __restrict__ scores,
                                                                           const int64_t* __restrict__ indices, int n,
                                                                           int64_t seq_len,
                                                                           const unsigned long long* __restrict__ table,
-                                                                          int max_tokens, int P2,
-                                                                          int64_t* __restrict__ keep_idx,
-                                                                          float* __restrict__ keep_scores,
-                                                                          int64_t* __restrict__ keep_pos,
-                                                                          int32_t* __restrict__ keep_count) {
-  extern __shared__ int sel[];  // [P2] selected indices, used in CTA 0
+                                                                          int max_tokens,
+                                                                          uint8_t* __restrict__ picked) {
   __shared__ ClusterScratch cs;
   cg::cluster_group cluster = cg::this_cluster();
   const int rank = (int)cluster.block_rank();
@@ -598,15 +595,10 @@ __global__ void __launch_bounds__(CL_THREADS) merge_select_cluster_kernel(const 
       }
     }
   }
-  if (rank == 0)
-    for (int i = tid; i < P2; i += CL_THREADS) sel[i] = 0x7fffffff;
   cluster_reduce<1, OpAdd>(reps, cs, parity);
   const int n_rep = (int)reps[0];
   const int need = min(max_tokens, n_rep);
-  if (need <= 0) {  // uniform over the cluster
-    if (rank == 0 && tid == 0) keep_count[0] = 0;
-    return;
-  }
+  if (need <= 0) return;  // uniform over the cluster
   uint32_t thr = 0;      // need == n_rep: every representative is kept
   uint32_t idx_cut = 0;  // among ties at thr: keep indices whose complement >= idx_cut
   bool all_ties = true;
@@ -625,32 +617,21 @@ __global__ void __launch_bounds__(CL_THREADS) merge_select_cluster_kernel(const 
       idx_cut = cluster_kth_largest_fn<CL_EPT>([&](int j) { return keys[j] == thr ? ~(uint32_t)idxs[j] : 0u; }, take, cs,
                                                parity);
   }
-  auto picked = [&](int j) {
-    return keys[j] != 0 && (keys[j] > thr || (keys[j] == thr && (all_ties || ~(uint32_t)idxs[j] >= idx_cut)));
-  };
-  int mine = 0;
-#pragma unroll
-  for (int j = 0; j < CL_EPT; ++j) mine += picked(j) ? 1 : 0;
-  int cta_picks;
-  const int in_cta = block_exclusive_scan(mine, cs.scan_tmp, &cta_picks);
-  uint32_t tot[1] = {tid == 0 ? (uint32_t)cta_picks : 0u}, lower[1];
-  cluster_reduce<1, OpAdd>(tot, cs, parity, lower);
-  int slot = (int)lower[0] + in_cta;
-  int* dst = cluster.map_shared_rank(sel, 0);
 #pragma unroll
   for (int j = 0; j < CL_EPT; ++j)
-    if (picked(j) && slot < P2) dst[slot++] = idxs[j];
-  cluster.sync();
-  if (rank != 0) return;
-  const int cnt = min((int)tot[0], P2);
-  bitonic_i32(sel, P2);
-  for (int i = tid; i < cnt; i += CL_THREADS) {
-    const unsigned long long e = table[sel[i]];
-    keep_idx[i] = sel[i];
-    keep_scores[i] = key_float((uint32_t)(e >> 32));
-    if (keep_pos) keep_pos[i] = (int64_t)(e & 0xffffffffull);
-  }
-  if (tid == 0) keep_count[0] = cnt;
+    if (keys[j] != 0 && (keys[j] > thr || (keys[j] == thr && (all_ties || ~(uint32_t)idxs[j] >= idx_cut))))
+      picked[idxs[j]] = 1;
+}
+
+// keep_scores / keep_pos of the kept indices from the table entry of each (score key << 32 | candidate position).
+__global__ void merge_emit_kernel(const int64_t* __restrict__ keep_idx, const int32_t* __restrict__ keep_count,
+                                  int max_tokens, const unsigned long long* __restrict__ table,
+                                  float* __restrict__ keep_scores, int64_t* __restrict__ keep_pos) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= min(keep_count[0], max_tokens)) return;
+  const unsigned long long e = table[keep_idx[i]];
+  keep_scores[i] = key_float((uint32_t)(e >> 32));
+  if (keep_pos) keep_pos[i] = (int64_t)(e & 0xffffffffull);
 }
 
 }  // namespace aspa
@@ -722,6 +703,10 @@ extern "C" int aspa_chunk_select(const float* importance, const uint8_t* token_m
   return ASPA_OK;
 }
 
+extern "C" int64_t aspa_merge_finalise_scratch(int64_t seq_len) {
+  return 8 * seq_len + ((seq_len + 15) / 16) * 16 + aspa_compact_mask_scratch(seq_len);
+}
+
 extern "C" int aspa_merge_finalise(const float* scores, const int64_t* indices, int64_t n, int64_t seq_len,
                                    int max_tokens, void* table, int64_t* keep_idx, float* keep_scores,
                                    int64_t* keep_pos, int32_t* keep_count, void* stream) {
@@ -731,21 +716,26 @@ extern "C" int aspa_merge_finalise(const float* scores, const int64_t* indices, 
                  "candidate positions are only tracked for n <= ASPA_MERGE_POS_MAX");
   cudaStream_t st = (cudaStream_t)stream;
   if (n > 0 && n <= CL_MAX * CL_KEYS_PER_CTA && seq_len < (int64_t)1 << 31) {
+    // scratch: [64-bit table (seq_len) | picked bytes (seq_len, rounded up to 16) | compaction block counts]
     unsigned long long* t64 = reinterpret_cast<unsigned long long*>(table);
+    uint8_t* picked = reinterpret_cast<uint8_t*>(t64 + seq_len);
+    void* cscratch = picked + ((seq_len + 15) / 16) * 16;
     cudaMemsetAsync(t64, 0xff, sizeof(unsigned long long) * seq_len, st);
+    cudaMemsetAsync(picked, 0, (size_t)seq_len, st);
     merge_scatter64_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, st>>>(scores, indices, n, seq_len, t64);
-    int P2 = 2;
-    while (P2 < std::min<int64_t>(n, max_tokens)) P2 <<= 1;
-    const size_t smem = sizeof(int) * P2;
     int csize = 1;
     while ((int64_t)csize * CL_KEYS_PER_CTA < n) csize <<= 1;
-    cudaFuncSetAttribute(merge_select_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    const cudaError_t e = launch_clusters(merge_select_cluster_kernel, 1, csize, smem, st, scores, indices, (int)n, seq_len,
-                                          (const unsigned long long*)t64, max_tokens, P2, keep_idx, keep_scores, keep_pos, keep_count);
+    const cudaError_t e = launch_clusters(merge_select_cluster_kernel, 1, csize, 0, st, scores, indices, (int)n, seq_len,
+                                          (const unsigned long long*)t64, max_tokens, picked);
     if (e != cudaSuccess) {
       set_error("aspa_merge_finalise: cluster launch failed: %s", cudaGetErrorString(e));
       return ASPA_ERR_CUDA;
     }
+    ASPA_CHECK_LAUNCH();
+    const int rc = aspa_compact_mask(picked, seq_len, max_tokens, keep_idx, nullptr, keep_count, cscratch, stream);
+    if (rc != ASPA_OK) return rc;
+    merge_emit_kernel<<<(unsigned)ceil_div(max_tokens, 256), 256, 0, st>>>(keep_idx, keep_count, max_tokens, t64, keep_scores,
+                                                                            keep_pos);
     ASPA_CHECK_LAUNCH();
     return ASPA_OK;
   }

@@ -661,7 +661,7 @@ __global__ void __launch_bounds__(CM_THREADS) compact_fill_kernel(const uint8_t*
   for (int j = 0; j < CM_PER_THREAD; ++j)
     if ((bits >> j) & 1u) {
       if (slot < capacity) kept_idx[slot] = base + j;
-      slot_of[base + j] = (int32_t)min(slot, (int64_t)0x7fffffff);
+      if (slot_of) slot_of[base + j] = (int32_t)min(slot, (int64_t)0x7fffffff);
       ++slot;
     }
   // padding of the tail, spread over the grid
@@ -874,7 +874,7 @@ extern "C" int64_t aspa_compact_mask_scratch(int64_t n) { return (int64_t)sizeof
 
 extern "C" int aspa_compact_mask(const uint8_t* mask, int64_t n, int64_t capacity, int64_t* kept_idx, int32_t* slot_of,
                                  int32_t* count, void* scratch, void* stream) {
-  ASPA_CHECK_ARG(mask && kept_idx && slot_of && count && scratch, "null pointer");
+  ASPA_CHECK_ARG(mask && kept_idx && count && scratch, "null pointer");
   ASPA_CHECK_ARG(n > 0 && n < ((int64_t)1 << 31) && capacity >= 0, "bad sizes");
   cudaStream_t st = (cudaStream_t)stream;
   const unsigned nblk = (unsigned)ceil_div(n, CM_BLOCK);

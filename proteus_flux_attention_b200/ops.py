@@ -336,7 +336,7 @@ MERGE_POS_MAX = 65536  # ASPA_MERGE_POS_MAX of the C header
 def merge_finalise(scores: torch.Tensor, indices: torch.Tensor, seq_len: int, max_tokens: int, want_pos: bool = False):
     """Returns (keep_idx, keep_scores, count) and, with ``want_pos``, the candidate position of every kept index."""
     dev = scores.device
-    table = _empty((seq_len,), torch.int64, dev)
+    table = _empty((int(N.lib().aspa_merge_finalise_scratch(int(seq_len))),), torch.uint8, dev)
     keep_idx = _empty((max_tokens,), torch.int64, dev)
     keep_sc = _empty((max_tokens,), torch.float32, dev)
     keep_pos = _empty((max_tokens,), torch.int64, dev) if want_pos else None
