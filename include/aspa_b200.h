@@ -294,6 +294,14 @@ int aspa_proto_ema_update(const void* x, int x_dtype, int64_t n, int C, const fl
 int aspa_chunk_select(const float* importance, const uint8_t* token_mask, int T, int budget, float top_p,
                       int64_t offset, float* out_scores, int64_t* out_idx, int32_t* out_count, void* stream);
 
+/* The same promotion with the record slot read from device memory: the results go to rec_scores / rec_idx
+ * (n_slots, budget) and rec_count (n_slots) at slot *slot_dev, and slot_offsets[*slot_dev] is added to the
+ * indices.  One captured launch (a CUDA-graph node) can thus serve every chunk of a pass; the caller only rewrites
+ * *slot_dev between replays.  T <= 65536. */
+int aspa_chunk_select_slot(const float* importance, const uint8_t* token_mask, int T, int budget, float top_p,
+                           const int32_t* slot_dev, const int64_t* slot_offsets, float* rec_scores, int64_t* rec_idx,
+                           int32_t* rec_count, void* stream);
+
 /* Merge of all chunks' promotions (cs.py:211-254): one representative score per
  * unique index (the lowest, as the reference's sort key does), the max_tokens
  * best of them, ascending index order.

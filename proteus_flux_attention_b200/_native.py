@@ -63,6 +63,7 @@ SIGNATURES = {
     "aspa_proto_ema_scratch": (_l, [_l, _i, _i]),
     "aspa_proto_ema_update": (_i, [_p, _i, _l, _i, _p, _i, _d, _p, _p, _p, _p, _p, _p]),
     "aspa_chunk_select": (_i, [_p, _p, _i, _i, _f, _l, _p, _p, _p, _p]),
+    "aspa_chunk_select_slot": (_i, [_p, _p, _i, _i, _f, _p, _p, _p, _p, _p, _p]),
     "aspa_merge_finalise_scratch": (_l, [_l]),
     "aspa_merge_finalise": (_i, [_p, _p, _l, _l, _i, _p, _p, _p, _p, _p, _p]),
     "aspa_gather_attn_fwd_ex": (_i, [_p, _p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _p, _p, _i, _l, _p, _p, _i,

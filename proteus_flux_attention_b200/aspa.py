@@ -329,6 +329,8 @@ class AdaptiveSparseAttention(nn.Module):
         self.last_head_consensus: Optional[torch.Tensor] = None
         # project queries / outputs for kept tokens only when at most 3/4 of the tokens can survive the token keep
         self.compact_projection = True
+        # optional callable(layer), invoked as soon as token importance and the token mask of a call are launched
+        self.after_token_keep = None
         self._identity_pack: Dict[Tuple[int, int, str], Tuple[torch.Tensor, torch.Tensor]] = {}
         self._pin: Optional[torch.Tensor] = None
 
@@ -845,6 +847,8 @@ class AdaptiveSparseAttention(nn.Module):
             else:
                 token_mask_u8, kept = ops.token_select(self._last_token_importance, need, self.token_keep_threshold, guard)
             self._last_token_mask = token_mask_u8.view(torch.bool)
+        if self.after_token_keep is not None:  # importance and mask are final: work that only needs them can fork here
+            self.after_token_keep(self)
 
         # 3. head budget and per-token head choice
         dense_k = self._choose_active_k(T)

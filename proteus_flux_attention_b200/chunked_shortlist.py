@@ -218,6 +218,44 @@ class _ChunkFeeder:
             self.consumed[i % 2].record(torch.cuda.current_stream())
 
 
+class _Pass1Records:
+    """Fixed-size promotion records of the chunks this rank owns, filled by ``aspa_chunk_select_slot``: the chunk's
+    slot number lives in device memory, so the same launch - eager or a node of a captured graph - serves every chunk.
+    The promotion only needs token importance and the token mask, which are final early in the layer call; it runs on
+    its own stream beside the rest of that call (it occupies 8 SMs)."""
+
+    def __init__(self, n_slots: int, budget: int, device: torch.device, top_p: float):
+        self.n_slots, self.budget, self.top_p = n_slots, budget, top_p
+        self.scores = torch.zeros((n_slots, budget), dtype=torch.float32, device=device)
+        self.idx = torch.full((n_slots, budget), -1, dtype=torch.int64, device=device)
+        self.count = torch.zeros((n_slots,), dtype=torch.int32, device=device)
+        self.slot = torch.zeros((1,), dtype=torch.int32, device=device)
+        self.offsets = torch.zeros((n_slots,), dtype=torch.int64, device=device)
+        self.stream = torch.cuda.Stream(device=device)
+
+    def reset(self, first_chunk: int, chunk_len: int) -> None:
+        self.scores.zero_()
+        self.idx.fill_(-1)
+        self.count.zero_()
+        torch.arange(first_chunk, first_chunk + self.n_slots, out=self.offsets)
+        self.offsets.mul_(chunk_len)
+
+    def hook(self, layer: AdaptiveSparseAttention) -> None:
+        """Called by the layer right after its token keep: fork the promotion of this chunk."""
+        main = torch.cuda.current_stream()
+        ready = torch.cuda.Event()
+        ready.record(main)
+        self.stream.wait_event(ready)
+        mask = layer._last_token_mask
+        with torch.cuda.stream(self.stream):
+            ops.chunk_select_slot(layer._last_token_importance.view(-1),
+                                  mask.view(torch.uint8).view(-1) if mask is not None else None, self.budget, self.top_p,
+                                  self.slot, self.offsets, self.scores, self.idx, self.count)
+
+    def join(self) -> None:
+        torch.cuda.current_stream().wait_stream(self.stream)
+
+
 class ChunkedShortlistRunner:
     def __init__(self, config: ChunkedShortlistConfig, *, logger: Optional[logging.Logger] = None,
                  process_group: Any = None, cache_layers: bool = False) -> None:
@@ -250,12 +288,30 @@ class ChunkedShortlistRunner:
             self._layer_cache[key] = layer
         return layer
 
-    def _chunk_graph(self, layer: AdaptiveSparseAttention, dtype: torch.dtype):
+    def _records(self, n_slots: int) -> _Pass1Records:
+        cfg = self.config
+        key = ("records", n_slots, cfg.per_chunk_budget, float(cfg.nucleus_top_p))
+        cache = self._layer_cache if self._layer_cache is not None else self.__dict__.setdefault("_graph_tmp", {})
+        if key not in cache:
+            cache[key] = _Pass1Records(n_slots, cfg.per_chunk_budget, torch.device(cfg.device), float(cfg.nucleus_top_p))
+        return cache[key]
+
+    def _chunk_step(self, layer: AdaptiveSparseAttention, x: torch.Tensor, records: _Pass1Records) -> None:
+        """Layer call (or scoring only) of one chunk with the promotion forked off inside it, joined at the end."""
+        layer.after_token_keep = records.hook
+        try:
+            layer(x) if self.config.pass1_full_forward else self._score_only(layer, x)
+        finally:
+            layer.after_token_keep = None
+        records.join()
+
+    def _chunk_graph(self, layer: AdaptiveSparseAttention, dtype: torch.dtype, records: _Pass1Records):
         """(graph, static input) for one full chunk of pass 1.  The layer call is launch-bound (about 45 small
         launches around two GEMMs), so replaying a captured graph removes the host from the loop.  Capture needs a
-        call that never waits for the host, which holds for the chunk layer (alpha = 1, no keep threshold)."""
+        call that never waits for the host, which holds for the chunk layer (alpha = 1, no keep threshold).  The
+        promotion of the chunk is part of the graph; it finds its record slot in device memory."""
         cfg = self.config
-        key = ("graph", cfg.chunk_len, dtype, cfg.pass1_full_forward)
+        key = ("graph", cfg.chunk_len, dtype, cfg.pass1_full_forward, id(records))
         cache = self._layer_cache if self._layer_cache is not None else self.__dict__.setdefault("_graph_tmp", {})
         if key in cache:
             return cache[key]
@@ -264,12 +320,12 @@ class ChunkedShortlistRunner:
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):  # eager warm-up on a side stream, as graph capture requires
             for _ in range(2):
-                layer(static_x) if cfg.pass1_full_forward else self._score_only(layer, static_x)
+                self._chunk_step(layer, static_x, records)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize(cfg.device)
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
-            layer(static_x) if cfg.pass1_full_forward else self._score_only(layer, static_x)
+            self._chunk_step(layer, static_x, records)
         cache[key] = (g, static_x)
         return cache[key]
 
@@ -298,6 +354,8 @@ class ChunkedShortlistRunner:
         else:
             mask, _ = ops.token_select(layer._last_token_importance, need, layer.token_keep_threshold, guard)
         layer._last_token_mask = mask.view(torch.bool)
+        if layer.after_token_keep is not None:
+            layer.after_token_keep(layer)
         if layer.proto_decay != 1.0:
             ops.proto_ema_update(x2d, gate, layer.proto_decay, layer.routing_prototypes, layer.routing_usage_ema,
                                  layer.routing_confidence)
@@ -356,9 +414,8 @@ class ChunkedShortlistRunner:
 
         n_local = c_hi - c_lo
         budget = cfg.per_chunk_budget
-        rec_scores = torch.zeros((max(n_local, 1), budget), dtype=torch.float32, device=device)
-        rec_idx = torch.full((max(n_local, 1), budget), -1, dtype=torch.int64, device=device)
-        rec_count = torch.zeros((max(n_local, 1),), dtype=torch.int32, device=device)
+        records = self._records(max(n_local, 1))
+        rec_scores, rec_idx, rec_count = records.scores, records.idx, records.count
         feeder = _ChunkFeeder(source, source_off, device, cfg.chunk_len)
         # Host-resident input: the rows of every promoted token are set aside while their chunk is on the device,
         # so that the reduced sequence is assembled from device memory instead of a second trip to the host.
@@ -372,20 +429,16 @@ class ChunkedShortlistRunner:
         t0 = time.perf_counter()
         ev_a.record()
         bounds = [(c * cfg.chunk_len, min(cfg.seq_len, (c + 1) * cfg.chunk_len)) for c in range(c_lo, c_hi)]
-        graph = self._chunk_graph(chunk_model, base_dtype) if cfg.use_cuda_graph else None
+        graph = self._chunk_graph(chunk_model, base_dtype, records) if cfg.use_cuda_graph else None
+        records.reset(c_lo, cfg.chunk_len)  # after a possible capture, whose warm-up calls wrote into slot 0
         for i, (start, end) in enumerate(bounds):
             xc = feeder.get(i, start, end, bounds[i + 1] if i + 1 < len(bounds) else None)
+            records.slot.fill_(i)
             if graph is not None and end - start == cfg.chunk_len:
                 graph[1].copy_(xc, non_blocking=True)   # the graph reads its own static input buffer
                 graph[0].replay()
-            elif cfg.pass1_full_forward:
-                chunk_model(xc)
             else:
-                self._score_only(chunk_model, xc)
-            mask = chunk_model._last_token_mask
-            ops.chunk_select(chunk_model._last_token_importance.view(-1),
-                             mask.view(torch.uint8).view(-1) if mask is not None else None, budget,
-                             cfg.nucleus_top_p, start, rec_scores[i], rec_idx[i], rec_count[i:i + 1])
+                self._chunk_step(chunk_model, xc, records)
             if pool is not None:
                 ops.gather_rows(xc[0], (rec_idx[i] - start).clamp_(min=0), rec_count[i:i + 1], budget,
                                 out=pool[i * budget:(i + 1) * budget])

@@ -295,8 +295,17 @@ __global__ void __launch_bounds__(CL_THREADS) chunk_select_cluster_kernel(const 
                                                                           int budget, float top_p, int64_t offset,
                                                                           int P2, float* __restrict__ out_scores,
                                                                           int64_t* __restrict__ out_idx,
-                                                                          int32_t* __restrict__ out_count) {
+                                                                          int32_t* __restrict__ out_count,
+                                                                          const int32_t* __restrict__ slot_dev,
+                                                                          const int64_t* __restrict__ slot_offsets) {
   extern __shared__ unsigned long long keys64[];  // [P2], used in CTA 0
+  if (slot_dev != nullptr) {  // record slot and index offset come from device memory (the launch may be a graph node)
+    const int slot = slot_dev[0];
+    offset = slot_offsets[slot];
+    out_scores += (int64_t)slot * budget;
+    out_idx += (int64_t)slot * budget;
+    out_count += slot;
+  }
   __shared__ ClusterScratch cs;
   __shared__ float redf[33];
   cg::cluster_group cluster = cg::this_cluster();
@@ -689,7 +698,8 @@ extern "C" int aspa_chunk_select(const float* importance, const uint8_t* token_m
     while (csize * CL_KEYS_PER_CTA < T) csize <<= 1;
     cudaFuncSetAttribute(chunk_select_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     const cudaError_t e = launch_clusters(chunk_select_cluster_kernel, 1, csize, smem, st, importance, token_mask, T, budget,
-                                          top_p, offset, P2, out_scores, out_idx, out_count);
+                                          top_p, offset, P2, out_scores, out_idx, out_count, (const int32_t*)nullptr,
+                                          (const int64_t*)nullptr);
     if (e != cudaSuccess) {
       set_error("aspa_chunk_select: cluster launch failed: %s", cudaGetErrorString(e));
       return ASPA_ERR_CUDA;
@@ -698,6 +708,30 @@ extern "C" int aspa_chunk_select(const float* importance, const uint8_t* token_m
     cudaFuncSetAttribute(chunk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     chunk_select_kernel<<<1, 1024, smem, st>>>(importance, token_mask, T, budget, top_p, offset, P2, out_scores, out_idx,
                                                out_count);
+  }
+  ASPA_CHECK_LAUNCH();
+  return ASPA_OK;
+}
+
+extern "C" int aspa_chunk_select_slot(const float* importance, const uint8_t* token_mask, int T, int budget, float top_p,
+                                      const int32_t* slot_dev, const int64_t* slot_offsets, float* rec_scores,
+                                      int64_t* rec_idx, int32_t* rec_count, void* stream) {
+  ASPA_CHECK_ARG(importance && slot_dev && slot_offsets && rec_scores && rec_idx && rec_count, "null pointer");
+  ASPA_CHECK_ARG(T > 0 && budget > 0, "bad sizes");
+  ASPA_CHECK_ARG(T <= CL_MAX * CL_KEYS_PER_CTA, "chunks longer than 65536 tokens: use aspa_chunk_select");
+  int P2 = 2;
+  while (P2 < std::min(budget, T)) P2 <<= 1;
+  const size_t smem = sizeof(unsigned long long) * P2;
+  ASPA_CHECK_ARG(smem <= 200 * 1024, "per-chunk budget too large (max 25600)");
+  cudaStream_t st = (cudaStream_t)stream;
+  int csize = 1;
+  while (csize * CL_KEYS_PER_CTA < T) csize <<= 1;
+  cudaFuncSetAttribute(chunk_select_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  const cudaError_t e = launch_clusters(chunk_select_cluster_kernel, 1, csize, smem, st, importance, token_mask, T, budget,
+                                        top_p, (int64_t)0, P2, rec_scores, rec_idx, rec_count, slot_dev, slot_offsets);
+  if (e != cudaSuccess) {
+    set_error("aspa_chunk_select_slot: cluster launch failed: %s", cudaGetErrorString(e));
+    return ASPA_ERR_CUDA;
   }
   ASPA_CHECK_LAUNCH();
   return ASPA_OK;

@@ -491,3 +491,14 @@ def stats_record(row_offsets: torch.Tensor, kept: Optional[torch.Tensor], n_kept
             proto_partials.numel() // 3 if proto_partials is not None else 0, N.ptr(status), N.ptr(rec), N.stream()),
             "stats_record")
     return rec
+
+
+def chunk_select_slot(importance: torch.Tensor, token_mask: Optional[torch.Tensor], budget: int, top_p: float,
+                      slot_dev: torch.Tensor, slot_offsets: torch.Tensor, rec_scores: torch.Tensor, rec_idx: torch.Tensor,
+                      rec_count: torch.Tensor) -> None:
+    """Chunk promotion into record slot ``slot_dev[0]`` (int32 on the device); ``slot_offsets`` (n_slots) int64."""
+    T = importance.numel()
+    with _timed('chunk_select', 1, _nb(importance)):
+        N.check(N.lib().aspa_chunk_select_slot(N.ptr(importance), N.ptr(token_mask), T, int(budget), float(top_p),
+                                               N.ptr(slot_dev), N.ptr(slot_offsets), N.ptr(rec_scores), N.ptr(rec_idx),
+                                               N.ptr(rec_count), N.stream()), "chunk_select_slot")
