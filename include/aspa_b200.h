@@ -269,14 +269,20 @@ typedef struct aspa_kv_layout {
  *   (the compact slot of a kept token, from aspa_compact_mask), so that the output projection runs over kept
  *   tokens only — the reference projects every row, dropped tokens included (aspa.py:1854);
  *   kv_layout or NULL: k and v read where the projection left them instead of from head-major copies (the
- *   reference permutes them, aspa.py:1644-1656).  Needs H > 0. */
+ *   reference permutes them, aspa.py:1644-1656).  Needs H > 0;
+ *   regroup_ws or NULL: scratch of aspa_attn_regroup_bytes() bytes.  With it, and enough rows per (head,
+ *   token % anchor_stride) group, the strided anchor keys t - j*stride of a plan run as a third tile pass over the
+ *   rows regrouped by residue class (the anchors of one class are a window over K[rho + stride*i]); without it they
+ *   are gathered row by row. */
 int aspa_gather_attn_fwd_ex(const void* q, const void* k, const void* v, int qkv_dtype, const float* q_scale,
                             const float* k_scale, const float* v_scale, int heads, int T, int D, int H,
                             const int32_t* row_offsets, const int32_t* token_idx, int max_rows,
                             int64_t total_rows, const int64_t* cand, const int64_t* cand_len, int L,
                             const aspa_shortlist_plan* plan, const float* add_mask, void* out, int out_dtype,
                             int out_layout, const int32_t* out_row_map, const aspa_kv_layout* kv_layout,
-                            void* workspace, void* stream);
+                            void* workspace, void* regroup_ws, void* stream);
+/* Bytes of regroup_ws for the call above (0 when the plan has no anchors). */
+int64_t aspa_attn_regroup_bytes(int64_t total_rows, int heads, int anchor_stride);
 
 /* Prototype EMA (aspa.py:692-718): counts = sum_t probs; mean = probs^T x / counts;
  * prototypes, usage and confidence updated in place for gates with counts > 1e-6.

@@ -67,7 +67,8 @@ SIGNATURES = {
     "aspa_merge_finalise_scratch": (_l, [_l]),
     "aspa_merge_finalise": (_i, [_p, _p, _l, _l, _i, _p, _p, _p, _p, _p, _p]),
     "aspa_gather_attn_fwd_ex": (_i, [_p, _p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _p, _p, _i, _l, _p, _p, _i,
-                                     C.POINTER(ShortlistPlan), _p, _p, _i, _i, _p, C.POINTER(KVLayout), _p, _p]),
+                                     C.POINTER(ShortlistPlan), _p, _p, _i, _i, _p, C.POINTER(KVLayout), _p, _p, _p]),
+    "aspa_attn_regroup_bytes": (_l, [_l, _i, _i]),
     "aspa_rope_inplace": (_i, [_p, _i, _l, _i, _l, _i, _i, _p, _p, _p]),
     "aspa_rope_relayout_kv": (_i, [_p, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p]),
     "aspa_rope_rows_q": (_i, [_p, _i, _p, _p, _l, _i, _i, _i, _i, _p, _p, _p, _p]),

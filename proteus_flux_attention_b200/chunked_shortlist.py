@@ -171,22 +171,31 @@ class ChunkedShortlistConfig:
 
 
 class _ChunkFeeder:
-    """Hands out (1, len, C) device views of the chunks this rank owns."""
+    """Hands out (1, len, C) device views of the chunks this rank owns.
 
-    def __init__(self, source: torch.Tensor, local_start: int, device: torch.device, chunk_len: int):
+    A sequence that is resident in HBM is handed out as views of itself.  A host sequence is uploaded chunk by chunk
+    on a copy stream, one chunk ahead of the compute stream, into two device buffers.  With ``targets`` (the static
+    inputs of two captured graphs) every chunk, resident or not, is copied into ``targets[i % 2]`` on that copy stream,
+    so the copy of chunk i+1 overlaps the layer call of chunk i."""
+
+    def __init__(self, source: torch.Tensor, local_start: int, device: torch.device, chunk_len: int,
+                 targets: Optional[List[torch.Tensor]] = None):
         self.src = source
         self.off = local_start  # global index of source[:, 0]
         self.device = device
         self.on_device = source.is_cuda
-        if not self.on_device:
+        self.copying = targets is not None or not self.on_device
+        if self.copying:
             self.copy_stream = torch.cuda.Stream(device=device)
             shape = (1, chunk_len, source.size(2))
-            self.pinned_source = source.is_pinned()  # pinned input uploads straight from the caller's buffer
+            self.pinned_source = self.on_device or source.is_pinned()  # uploads straight from the caller's buffer
             self.stage = [] if self.pinned_source else [torch.empty(shape, dtype=source.dtype, pin_memory=True) for _ in range(2)]
-            self.dev = [torch.empty(shape, dtype=source.dtype, device=device) for _ in range(2)]
+            self.dev = targets if targets is not None else [torch.empty(shape, dtype=source.dtype, device=device) for _ in range(2)]
             self.ready = [torch.cuda.Event() for _ in range(2)]
             self.consumed = [torch.cuda.Event() for _ in range(2)]
             self.prefetched: Dict[int, int] = {}
+            if self.on_device:  # the source must be complete before the copy stream reads it
+                self.copy_stream.wait_stream(torch.cuda.current_stream())
 
     def _issue(self, slot: int, start: int, end: int) -> None:
         n = end - start
@@ -202,7 +211,7 @@ class _ChunkFeeder:
             self.ready[slot].record(self.copy_stream)
 
     def get(self, i: int, start: int, end: int, nxt: Optional[Tuple[int, int]]) -> torch.Tensor:
-        if self.on_device:
+        if not self.copying:
             return self.src[:, start - self.off:end - self.off]
         slot = i % 2
         if self.prefetched.pop(i, None) is None:
@@ -214,7 +223,7 @@ class _ChunkFeeder:
         return self.dev[slot][:, :end - start]
 
     def done(self, i: int) -> None:
-        if not self.on_device:
+        if self.copying:
             self.consumed[i % 2].record(torch.cuda.current_stream())
 
 
@@ -306,7 +315,7 @@ class ChunkedShortlistRunner:
         records.join()
 
     def _chunk_graph(self, layer: AdaptiveSparseAttention, dtype: torch.dtype, records: _Pass1Records):
-        """(graph, static input) for one full chunk of pass 1.  The layer call is launch-bound (about 45 small
+        """(graphs, static inputs) for one full chunk of pass 1.  The layer call is launch-bound (about 45 small
         launches around two GEMMs), so replaying a captured graph removes the host from the loop.  Capture needs a
         call that never waits for the host, which holds for the chunk layer (alpha = 1, no keep threshold).  The
         promotion of the chunk is part of the graph; it finds its record slot in device memory."""
@@ -315,18 +324,23 @@ class ChunkedShortlistRunner:
         cache = self._layer_cache if self._layer_cache is not None else self.__dict__.setdefault("_graph_tmp", {})
         if key in cache:
             return cache[key]
-        static_x = torch.zeros(1, cfg.chunk_len, cfg.d_model, device=cfg.device, dtype=dtype)
+        statics = [torch.zeros(1, cfg.chunk_len, cfg.d_model, device=cfg.device, dtype=dtype) for _ in range(2)]
         side = torch.cuda.Stream(device=cfg.device)
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):  # eager warm-up on a side stream, as graph capture requires
             for _ in range(2):
-                self._chunk_step(layer, static_x, records)
+                self._chunk_step(layer, statics[0], records)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize(cfg.device)
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
-            self._chunk_step(layer, static_x, records)
-        cache[key] = (g, static_x)
+        # two graphs, one per input buffer (the copy of the next chunk overlaps the replay of this one); they are
+        # replayed one after the other on one stream, so they can share the memory of their intermediates
+        graphs = []
+        for k in range(2):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, pool=graphs[0].pool() if graphs else None):
+                self._chunk_step(layer, statics[k], records)
+            graphs.append(g)
+        cache[key] = (graphs, statics)
         return cache[key]
 
     @staticmethod
@@ -416,7 +430,6 @@ class ChunkedShortlistRunner:
         budget = cfg.per_chunk_budget
         records = self._records(max(n_local, 1))
         rec_scores, rec_idx, rec_count = records.scores, records.idx, records.count
-        feeder = _ChunkFeeder(source, source_off, device, cfg.chunk_len)
         # Host-resident input: the rows of every promoted token are set aside while their chunk is on the device,
         # so that the reduced sequence is assembled from device memory instead of a second trip to the host.
         pool = None
@@ -430,13 +443,13 @@ class ChunkedShortlistRunner:
         ev_a.record()
         bounds = [(c * cfg.chunk_len, min(cfg.seq_len, (c + 1) * cfg.chunk_len)) for c in range(c_lo, c_hi)]
         graph = self._chunk_graph(chunk_model, base_dtype, records) if cfg.use_cuda_graph else None
+        feeder = _ChunkFeeder(source, source_off, device, cfg.chunk_len, targets=graph[1] if graph is not None else None)
         records.reset(c_lo, cfg.chunk_len)  # after a possible capture, whose warm-up calls wrote into slot 0
         for i, (start, end) in enumerate(bounds):
             xc = feeder.get(i, start, end, bounds[i + 1] if i + 1 < len(bounds) else None)
             records.slot.fill_(i)
             if graph is not None and end - start == cfg.chunk_len:
-                graph[1].copy_(xc, non_blocking=True)   # the graph reads its own static input buffer
-                graph[0].replay()
+                graph[0][i % 2].replay()   # xc is the static input of that graph
             else:
                 self._chunk_step(chunk_model, xc, records)
             if pool is not None:

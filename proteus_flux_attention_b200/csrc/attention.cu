@@ -15,6 +15,8 @@
 
 namespace aspa {
 
+constexpr int ANCHOR_NO_KEYS = -(1 << 30);  // a row of the anchor pass that has no anchor key
+
 struct AttnParams {
   const void* q;
   const void* k;
@@ -40,6 +42,14 @@ struct AttnParams {
   float* ws_l;  // [total_rows] running denominator
   float* ws_o;  // [total_rows][D] unnormalised output
   int extras_only;  // second pass: skip the local window, merge with ws_*
+  int anchors_done; // extras pass: the strided anchor keys were already folded into ws_* by the tile pass
+  int read_partial; // tile pass: start from the state in ws_* instead of an empty one
+  // anchor tile pass: rows regrouped by (head, token % stride); keys are the strided view K[rho + stride * i]
+  int an_stride;            // 0 = ordinary window pass
+  int an_window, an_jmin;   // strided keys i in (it - jmin - an_window, it - jmin]
+  const int32_t* an_offsets;  // (heads * stride + 1) first row of every (head, residue) group
+  const int32_t* an_tok;      // per regrouped row: token / stride - jmin, or ANCHOR_NO_KEYS
+  const int32_t* an_row;      // per regrouped row: its position in the head-grouped packing (workspace row)
   int write_partial;  // window pass: write ws_* instead of the final output
 };
 
@@ -164,7 +174,7 @@ __global__ void __launch_bounds__(GEN_WARPS * 32) attn_rows_kernel(const AttnPar
   // virtual candidate space
   const bool explicit_c = p.cand != nullptr;
   const bool planned = !explicit_c && p.has_plan;
-  int n_loc = 0, loc_start = 0, n_anchor = 0, n_proto = 0, n_virtual = 0, v_begin = 0;
+  int n_loc = 0, loc_start = 0, n_anchor = 0, n_anchor_true = 0, n_proto = 0, n_virtual = 0, v_begin = 0;
   const int32_t* plist = nullptr;
   int astride = 1, j0 = 0;
   bool anchor_clamps = false;
@@ -178,6 +188,8 @@ __global__ void __launch_bounds__(GEN_WARPS * 32) attn_rows_kernel(const AttnPar
     n_anchor = p.plan.anchor_stride > 0 ? p.plan.anchor_slots : 0;
     j0 = t / astride + 1;  // first anchor slot that clamps to key 0
     anchor_clamps = n_anchor > 0 && (t - (long long)n_anchor * astride) < 0;
+    n_anchor_true = n_anchor;
+    if (p.anchors_done && n_anchor > 0) n_anchor = 1;  // only the slot that clamps to key 0 is left to this pass
     if (p.plan.proto_cap > 0 && p.plan.proto_lists != nullptr) {
       const int b = bh / p.H;
       const int nblk = (Tn + p.plan.proto_block - 1) / p.plan.proto_block;
@@ -211,20 +223,23 @@ __global__ void __launch_bounds__(GEN_WARPS * 32) attn_rows_kernel(const AttnPar
         if (c < n_loc) {
           idx = loc_start + c;
         } else if (c < n_loc + n_anchor) {
-          const int j = c - n_loc + 1;
-          const long long a = (long long)t - (long long)j * astride;
-          if (a >= 0) {
-            if (a < loc_start) idx = (int)a;
-          } else if (j == j0 && (t % astride) != 0 && loc_start > 0) {
-            idx = 0;
+          // after the anchor tile pass the one slot left here is the slot that clamps to key 0, if the row has it
+          const int j = p.anchors_done ? j0 : c - n_loc + 1;
+          if (j <= n_anchor_true) {
+            const long long a = (long long)t - (long long)j * astride;
+            if (a >= 0) {
+              if (a < loc_start) idx = (int)a;
+            } else if (j == j0 && (t % astride) != 0 && loc_start > 0) {
+              idx = 0;
+            }
           }
         } else {
           const int u = plist[c - n_loc - n_anchor];
           if (u >= 0 && u < loc_start) {
             bool is_anchor = false;
-            if (n_anchor > 0) {
+            if (n_anchor_true > 0) {
               const int dlt = t - u;
-              if (dlt % astride == 0 && dlt / astride >= 1 && dlt / astride <= n_anchor) is_anchor = true;
+              if (dlt % astride == 0 && dlt / astride >= 1 && dlt / astride <= n_anchor_true) is_anchor = true;
               if (u == 0 && anchor_clamps) is_anchor = true;
             }
             if (!is_anchor) idx = u;
@@ -396,31 +411,59 @@ __global__ void __launch_bounds__(128) attn_window_kernel(const AttnParams p) {
   __shared__ int ts[WK_ROWS];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int bh = blockIdx.y;
-  const int start = p.row_offsets[bh];
-  const int cnt = p.row_offsets[bh + 1] - start;
-  const int r0 = blockIdx.x * WK_ROWS;
-  if (r0 >= cnt) return;
+  // Ordinary pass: blockIdx.y is a (batch, head) pair, keys are the tokens, a row t sees keys (t - window, t].
+  // Anchor pass: blockIdx.y is a (head, residue rho) group, keys are the strided view K[rho + stride * i], and a
+  // row of token t = stride * it + rho sees strided keys (it - jmin - an_window, it - jmin]; ts[] then holds
+  // it - jmin (possibly negative: a row without anchor keys, which still has to carry its partial state along).
+  const bool anchor = p.an_stride > 0;
+  const int astr = anchor ? p.an_stride : 1;
+  const int bh = anchor ? blockIdx.y / astr : blockIdx.y;
+  const int rho = anchor ? blockIdx.y % astr : 0;
+  const int32_t* offs = anchor ? p.an_offsets : p.row_offsets;
+  const int start = offs[blockIdx.y];
+  const int cnt = offs[blockIdx.y + 1] - start;
+  // a CTA takes 64-row tiles of its group in turn (the grid's x extent need not cover the largest group)
+  for (int r0 = blockIdx.x * WK_ROWS; r0 < cnt; r0 += gridDim.x * WK_ROWS) {
   const int nrows = min(WK_ROWS, cnt - r0);
-  const int Tn = p.T;
-  const int window = p.has_plan ? (p.plan.window > 0 ? p.plan.window : 1) : (Tn + 1);  // no plan = causal
-  const T* qh = reinterpret_cast<const T*>(p.q) + (int64_t)bh * Tn * WK_D;
-  const T* kh = reinterpret_cast<const T*>(p.k) + (bh / p.H) * p.kv.k_batch + (bh % p.H) * p.kv.k_head;
-  const T* vh = reinterpret_cast<const T*>(p.v) + (bh / p.H) * p.kv.v_batch + (bh % p.H) * p.kv.v_head;
-  const int64_t k_ts = p.kv.k_token, v_ts = p.kv.v_token;
+  const int Tn = anchor ? (p.T - rho + astr - 1) / astr : p.T;   // number of keys in this pass's key space
+  const int window = anchor ? p.an_window : (p.has_plan ? (p.plan.window > 0 ? p.plan.window : 1) : (Tn + 1));
+  const T* qh = reinterpret_cast<const T*>(p.q) + (int64_t)bh * p.T * WK_D;
+  const int64_t k_ts = p.kv.k_token * astr, v_ts = p.kv.v_token * astr;
+  const T* kh = reinterpret_cast<const T*>(p.k) + (bh / p.H) * p.kv.k_batch + (bh % p.H) * p.kv.k_head + rho * p.kv.k_token;
+  const T* vh = reinterpret_cast<const T*>(p.v) + (bh / p.H) * p.kv.v_batch + (bh % p.H) * p.kv.v_head + rho * p.kv.v_token;
+  constexpr int ABSENT = -2147483647;
+  __shared__ int grow_s[WK_ROWS];   // workspace / packing row of every tile row
 
-  if (tid < WK_ROWS) ts[tid] = tid < nrows ? p.token_idx[start + r0 + tid] : -1;
+  if (tid < WK_ROWS) {
+    int tv = ABSENT, gr = 0;
+    if (tid < nrows) {
+      if (anchor) {
+        tv = p.an_tok[start + r0 + tid];
+        if (tv == ANCHOR_NO_KEYS) tv = -1;   // present, sees nothing
+        gr = p.an_row[start + r0 + tid];
+      } else {
+        tv = p.token_idx[start + r0 + tid];
+        gr = start + r0 + tid;
+      }
+    }
+    ts[tid] = tv;
+    grow_s[tid] = gr;
+  }
   __syncthreads();
   // Q rows (gathered) -> swizzled shared tile
   for (int c = tid; c < WK_ROWS * 8; c += 128) {
     const int row = c >> 3, ch = c & 7;
     uint4 val = make_uint4(0, 0, 0, 0);
-    if (ts[row] >= 0) val = load_chunk<T>(qh + (int64_t)ts[row] * WK_D, ch);
+    if (ts[row] != ABSENT) {
+      const int64_t tq = anchor ? (int64_t)p.token_idx[grow_s[row]] : (int64_t)ts[row];
+      val = load_chunk<T>(qh + tq * WK_D, ch);
+    }
     *reinterpret_cast<uint4*>(q_s + swz(row, ch)) = val;
   }
+  // rows ascend inside a group; rows without keys (negative) come first
   const int t_first = ts[0], t_last = ts[nrows - 1];
   const int lo = max(0, t_first - window + 1);
-  const int kt_begin = lo / WK_KEYS, kt_end = t_last / WK_KEYS;  // inclusive
+  const int kt_begin = lo / WK_KEYS, kt_end = t_last < 0 ? -1 : t_last / WK_KEYS;  // inclusive
 
   // this warp's rows
   const int wr0 = warp * 16;
@@ -435,6 +478,7 @@ __global__ void __launch_bounds__(128) attn_window_kernel(const AttnParams p) {
     }
   }
   const int w_lo = w_first < 0 ? 0 : max(0, w_first - window + 1);
+  const bool has0 = tg0 != ABSENT, has1 = tg1 != ABSENT;
 
   float sc_log2 = p.scale * 1.4426950408889634f;
   if (sizeof(T) == 1) sc_log2 *= p.q_scale[bh] * p.k_scale[bh];
@@ -454,6 +498,33 @@ __global__ void __launch_bounds__(128) attn_window_kernel(const AttnParams p) {
 #pragma unroll
     for (int e = 0; e < 4; ++e) o[j][e] = 0.f;
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  if (p.read_partial) {
+    // continue from the state an earlier pass left in the workspace (natural-log maximum, denominator, raw P.V);
+    // the denominator is kept per quad here and summed over the quad at the end, so only lane qd == 0 takes it
+    const float inv_ln2 = 1.4426950408889634f;
+    if (has0) {
+      const int64_t gr = grow_s[wr0 + g];
+      const float mw = p.ws_m[gr];
+      m0 = (mw == -INFINITY) ? -INFINITY : mw * inv_ln2;
+      l0 = qd == 0 ? p.ws_l[gr] : 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float2 pr = *reinterpret_cast<const float2*>(p.ws_o + gr * WK_D + 8 * j + qd * 2);
+        o[j][0] = pr.x; o[j][1] = pr.y;
+      }
+    }
+    if (has1) {
+      const int64_t gr = grow_s[wr0 + g + 8];
+      const float mw = p.ws_m[gr];
+      m1 = (mw == -INFINITY) ? -INFINITY : mw * inv_ln2;
+      l1 = qd == 0 ? p.ws_l[gr] : 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float2 pr = *reinterpret_cast<const float2*>(p.ws_o + gr * WK_D + 8 * j + qd * 2);
+        o[j][2] = pr.x; o[j][3] = pr.y;
+      }
+    }
+  }
 
   // register prefetch of the first tile (STAGES == 1) / asynchronous ring (STAGES >= 2)
   uint4 kreg[STAGES == 1 ? 4 : 1], vreg[STAGES == 1 ? 4 : 1];
@@ -490,7 +561,7 @@ __global__ void __launch_bounds__(128) attn_window_kernel(const AttnParams p) {
     cp_async_commit();
   };
   if (STAGES == 1) {
-    fetch(kt_begin);
+    if (kt_begin <= kt_end) fetch(kt_begin);
   } else {
 #pragma unroll
     for (int s_ = 0; s_ < STAGES - 1; ++s_) issue(kt_begin + s_);
@@ -599,8 +670,8 @@ __global__ void __launch_bounds__(128) attn_window_kernel(const AttnParams p) {
 #pragma unroll
   for (int half = 0; half < 2; ++half) {
     const int tt = half ? tg1 : tg0;
-    if (tt < 0) continue;
-    const int64_t grow = (int64_t)start + r0 + wr0 + g + 8 * half;
+    if (tt == ABSENT) continue;
+    const int64_t grow = grow_s[wr0 + g + 8 * half];
     const float mm = half ? m1 : m0, ll = half ? l1 : l0;
     if (p.write_partial) {
       if (qd == 0) {
@@ -628,11 +699,66 @@ __global__ void __launch_bounds__(128) attn_window_kernel(const AttnParams p) {
       }
     }
   }
+  cp_async_wait<0>();
+  __syncthreads();  // shared tiles and row tables are reused by the next 64-row tile
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Regrouping of the packed rows by (head, token % stride) for the anchor tile pass
+// ------------------------------------------------------------------------------------------------
+// One warp per (head, residue): walks the head's rows (token-ascending) and keeps those of its residue, in order.
+// pass 0 counts, pass 1 fills; the counts are scanned in between.
+__global__ void __launch_bounds__(256) anchor_regroup_kernel(const int32_t* __restrict__ row_offsets,
+                                                             const int32_t* __restrict__ token_idx, int heads,
+                                                             int stride, int window, int jmin, int fill,
+                                                             int32_t* __restrict__ grp_offsets,
+                                                             int32_t* __restrict__ grp_tok,
+                                                             int32_t* __restrict__ grp_row) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (warp >= heads * stride) return;
+  const int bh = warp / stride, rho = warp % stride;
+  const int start = row_offsets[bh], cnt = row_offsets[bh + 1] - start;
+  int n = 0;
+  const int base = fill ? grp_offsets[warp] : 0;
+  for (int r0 = 0; r0 < cnt; r0 += 32) {
+    const int r = r0 + lane;
+    const int t = r < cnt ? token_idx[start + r] : -1;
+    const bool mine = t >= 0 && (t % stride) == rho;
+    const unsigned bal = __ballot_sync(0xffffffffu, mine);
+    if (fill && mine) {
+      const int pos = base + n + __popc(bal & ((1u << lane) - 1u));
+      // rows whose local window already reaches key 0 have no anchor key at all
+      grp_tok[pos] = (t + 1 >= window) ? t / stride - jmin : ANCHOR_NO_KEYS;
+      grp_row[pos] = start + r;
+    }
+    n += __popc(bal);
+  }
+  if (!fill && lane == 0) grp_offsets[warp] = n;
+}
+
+__global__ void __launch_bounds__(1024) anchor_scan_kernel(int32_t* __restrict__ grp_offsets, int n_groups) {
+  __shared__ int tmp[64];
+  int running = 0;
+  for (int base = 0; base < n_groups; base += 1024) {
+    const int i = base + threadIdx.x;
+    const int v = i < n_groups ? grp_offsets[i] : 0;
+    int tot;
+    const int ex = block_exclusive_scan(v, tmp, &tot);
+    if (i < n_groups) grp_offsets[i] = running + ex;
+    running += tot;
+  }
+  if (threadIdx.x == 0) grp_offsets[n_groups] = running;
 }
 
 }  // namespace aspa
 
 using namespace aspa;
+
+extern "C" int64_t aspa_attn_regroup_bytes(int64_t total_rows, int heads, int anchor_stride) {
+  if (anchor_stride <= 0) return 0;
+  return (int64_t)sizeof(int32_t) * ((int64_t)heads * anchor_stride + 1 + 2 * total_rows);
+}
 
 extern "C" int64_t aspa_attn_workspace_bytes(int64_t total_rows, int D) {
   return (int64_t)sizeof(float) * total_rows * (D + 2);
@@ -648,8 +774,8 @@ static void launch_generic(const AttnParams& p, int max_rows, cudaStream_t st) {
   else attn_rows_kernel<T, false><<<grid, GEN_WARPS * 32, 0, st>>>(p);
 }
 template <typename T, int STAGES>
-static void launch_window(const AttnParams& p, int max_rows, cudaStream_t st) {
-  const dim3 grid((unsigned)ceil_div(max_rows, WK_ROWS), p.heads);
+static void launch_window(const AttnParams& p, int max_rows, cudaStream_t st, int groups = 0) {
+  const dim3 grid((unsigned)ceil_div(max_rows, WK_ROWS), groups > 0 ? groups : p.heads);
   const int smem = WK_ROWS * 128 + STAGES * 2 * WK_TILE_BYTES;
   static bool attr_set = false;
   if (!attr_set) {
@@ -667,7 +793,7 @@ extern "C" int aspa_gather_attn_fwd(const void* q, const void* k, const void* v,
                                     int out_layout, void* workspace, void* stream) {
   return aspa_gather_attn_fwd_ex(q, k, v, qkv_dtype, q_scale, k_scale, v_scale, heads, T, D, H, row_offsets, token_idx,
                                  max_rows, total_rows, cand, cand_len, L, plan, add_mask, out, out_dtype, out_layout,
-                                 nullptr, nullptr, workspace, stream);
+                                 nullptr, nullptr, workspace, nullptr, stream);
 }
 
 extern "C" int aspa_gather_attn_fwd_ex(const void* q, const void* k, const void* v, int qkv_dtype,
@@ -677,7 +803,7 @@ extern "C" int aspa_gather_attn_fwd_ex(const void* q, const void* k, const void*
                                        const int64_t* cand_len, int L, const aspa_shortlist_plan* plan,
                                        const float* add_mask, void* out, int out_dtype, int out_layout,
                                        const int32_t* out_row_map, const aspa_kv_layout* kv_layout, void* workspace,
-                                       void* stream) {
+                                       void* regroup_ws, void* stream) {
   ASPA_CHECK_ARG(q && k && v && row_offsets && token_idx && out, "null pointer");
   ASPA_CHECK_ARG(heads > 0 && T > 0 && D > 0 && D <= GEN_MAXD, "head_dim must be in [1, 256]");
   ASPA_CHECK_ARG(qkv_dtype == ASPA_F32 || qkv_dtype == ASPA_BF16 || qkv_dtype == ASPA_I8, "bad qkv dtype");
@@ -715,6 +841,7 @@ extern "C" int aspa_gather_attn_fwd_ex(const void* q, const void* k, const void*
   }
   p.scale = 1.0f / sqrtf((float)D);
   p.ws_m = p.ws_l = p.ws_o = nullptr;
+  p.an_stride = 0;
 
   bool tensor_ok = D == WK_D && (qkv_dtype == ASPA_BF16 || qkv_dtype == ASPA_I8) && cand == nullptr &&
                    add_mask == nullptr;
@@ -740,6 +867,41 @@ extern "C" int aspa_gather_attn_fwd_ex(const void* q, const void* k, const void*
     }
     if (qkv_dtype == ASPA_BF16) launch_window<__nv_bfloat16, 3>(p, max_rows, st); else launch_window<int8_t, 1>(p, max_rows, st);
     ASPA_CHECK_LAUNCH();
+    // Anchors t - j*stride of the rows of one residue class t % stride are a window over the strided key sequence of
+    // that class: with enough rows per (head, residue) group they go through the tile kernel too, regrouped.
+    const int n_loc_full = (extras && plan->window > 0) ? plan->window : 1;
+    const int a_stride = extras ? plan->anchor_stride : 0;
+    const int jmin = (n_loc_full - 1) / std::max(1, a_stride) + 1;   // first anchor slot outside the window
+    const int an_window = extras ? plan->anchor_slots - jmin + 1 : 0;
+    const bool anchor_tiles = extras && regroup_ws != nullptr && a_stride > 0 && a_stride <= 1024 && an_window >= 64 &&
+                              total_rows >= (int64_t)8 * heads * a_stride;
+    if (anchor_tiles) {
+      const int R = plan->anchor_stride, n_groups = heads * R;
+      int32_t* goffs = reinterpret_cast<int32_t*>(regroup_ws);
+      int32_t* gtok = goffs + n_groups + 1;
+      int32_t* grow_ = gtok + total_rows;
+      const unsigned blocks = (unsigned)ceil_div((int64_t)n_groups * 32, 256);
+      anchor_regroup_kernel<<<blocks, 256, 0, st>>>(row_offsets, token_idx, heads, R, n_loc_full, jmin, 0, goffs, gtok, grow_);
+      anchor_scan_kernel<<<1, 1024, 0, st>>>(goffs, n_groups);
+      anchor_regroup_kernel<<<blocks, 256, 0, st>>>(row_offsets, token_idx, heads, R, n_loc_full, jmin, 1, goffs, gtok, grow_);
+      ASPA_CHECK_LAUNCH();
+      AttnParams pa = p;
+      pa.an_stride = R;
+      pa.an_window = an_window;
+      pa.an_jmin = jmin;
+      pa.an_offsets = goffs;
+      pa.an_tok = gtok;
+      pa.an_row = grow_;
+      pa.read_partial = 1;
+      pa.write_partial = 1;
+      // rows per group are about total_rows / n_groups: two 64-row tiles per CTA column cover the usual group in
+      // one step, and the kernel's tile loop takes care of larger groups
+      const int rows_bound = (int)std::min<int64_t>(max_rows, std::max<int64_t>(WK_ROWS, 2 * total_rows / n_groups));
+      if (qkv_dtype == ASPA_BF16) launch_window<__nv_bfloat16, 3>(pa, rows_bound, st, n_groups);
+      else launch_window<int8_t, 1>(pa, rows_bound, st, n_groups);
+      ASPA_CHECK_LAUNCH();
+      p.anchors_done = 1;
+    }
     if (extras) {
       p.write_partial = 0;
       p.extras_only = 1;

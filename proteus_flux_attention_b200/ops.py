@@ -74,6 +74,7 @@ def reduce_partials(partials: torch.Tensor, n_series: int) -> torch.Tensor:
     return out
 
 
+USE_ANCHOR_TILES = True          # strided anchor keys of a plan go through the tile kernel when groups are large enough
 USE_TC_ROUTER = True             # bf16 activations take the tcgen05 router when the shape allows
 _ROUTER_STATUS: dict = {}        # device -> int32[1], raised by the tensor-core router if a bounded wait ran out
 
@@ -291,6 +292,11 @@ def gather_attn(q, k, v, *, scales: Optional[Tuple[torch.Tensor, torch.Tensor, t
     nbytes = int(N.lib().aspa_attn_workspace_bytes(int(total_rows), D))
     if plan is not None and cand is None and nbytes > 0:
         ws = _empty((nbytes,), torch.uint8, q.device)
+    regroup = None
+    if ws is not None and plan.anchor_slots > 0 and plan.anchor_stride > 0 and USE_ANCHOR_TILES:
+        rb = int(N.lib().aspa_attn_regroup_bytes(int(total_rows), heads, int(plan.anchor_stride)))
+        if rb > 0:
+            regroup = _empty((rb,), torch.uint8, q.device)
     qs, ks, vs = scales if scales is not None else (None, None, None)
     L = cand.size(1) if cand is not None else 0
     e = q.element_size()
@@ -304,7 +310,7 @@ def gather_attn(q, k, v, *, scales: Optional[Tuple[torch.Tensor, torch.Tensor, t
             N.ptr(row_offsets), N.ptr(token_idx), int(max_rows), int(total_rows), N.ptr(cand), N.ptr(cand_len), int(L),
             C.byref(plan) if plan is not None else None, N.ptr(add_mask), N.ptr(out), N.dtype_code(out.dtype),
             int(out_layout), N.ptr(out_row_map), C.byref(kv_layout) if kv_layout is not None else None, N.ptr(ws),
-            N.stream()), "gather_attn_fwd")
+            N.ptr(regroup), N.stream()), "gather_attn_fwd")
     return out
 
 

@@ -672,3 +672,23 @@ def test_head_select_pack_equals_separate_calls(dev, B, T, G, H, k):
     assert torch.equal(rec, want)
     rec2 = ops.stats_record(offs1, None, B, float(T), kept[:2] if B >= 2 else None, 1.0, part1, None, None).cpu()
     assert bool((rec2[offs1.numel():offs1.numel() + B] == float(T)).all()) and bool((rec2[-4:] == 0).all())
+
+
+@pytest.mark.parametrize("case", [
+    dict(T=3000, L=400, window=40, stride=8, local_cap=40, anchor_cap=200, proto_cap=20),
+    dict(T=2500, L=300, window=33, stride=16, local_cap=33, anchor_cap=140, proto_cap=0),
+    dict(T=2048, L=256, window=0, stride=4, local_cap=0, anchor_cap=120, proto_cap=8),
+])
+@pytest.mark.parametrize("quant", [False, True])
+def test_anchor_keys_through_the_tile_kernel(dev, case, quant):
+    """Plans with many anchor slots and enough rows per (head, token % stride) group run the anchors as a third tile
+    pass over regrouped rows; the result must still be what the explicit reference table gives, and what the
+    row-by-row gather of the same anchors gives."""
+    from proteus_flux_attention_b200 import ops
+    a = _planned_vs_table(dev, torch.bfloat16, heads=4, D=64, H=2, seed=17, quant=quant, **case)
+    ops.USE_ANCHOR_TILES = False
+    try:
+        b = _planned_vs_table(dev, torch.bfloat16, heads=4, D=64, H=2, seed=17, quant=quant, **case)
+    finally:
+        ops.USE_ANCHOR_TILES = True
+    assert float((a - b).abs().max()) < 2e-2 and float((a - b).abs().mean()) < 1e-3
