@@ -1,5 +1,7 @@
 // Shortlist planning: block-wise prefix top-k of prototype scores, and the explicit (N, L) candidate
 // table for callers of the functional API.
+#include <utility>
+
 #include "common.cuh"
 
 namespace aspa {
@@ -162,6 +164,106 @@ __global__ void __launch_bounds__(256) proto_plan_kernel(const float* __restrict
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Hierarchical plan (prototype cap <= PLAN_FAST_CAP): the prefix top-k of a block is assembled from
+//   A. the sorted top-cap list of every 1024-token super-block (its own tokens only),
+//   B. an inclusive scan of those lists with "top-cap of the union" as the (associative) operator,
+//   C. per block: top-cap of [scanned list of the super-blocks before mine] U [tokens of my super-block before me],
+// so a block looks at about cap + 1024 scores instead of its whole prefix.  Same lists, same limits as
+// proto_plan_kernel (the order (score desc, index asc) is total, so every top-cap set is unique).
+// ------------------------------------------------------------------------------------------------
+constexpr int PLAN_SB = 1024;          // tokens per super-block (8 blocks)
+constexpr int PLAN_FAST_CAP = 960;     // 2 * cap and cap + PLAN_SB must fit a 2048-entry sort
+
+__device__ __forceinline__ unsigned long long plan_key(float score, int idx) {
+  return ((unsigned long long)(~float_key(score)) << 32) | (unsigned)idx;
+}
+
+// A: grid (nsb, B).  lists_out[(b*nsb + s) * cap + i]: sorted keys of super-block s, ~0 padded.
+__global__ void __launch_bounds__(256) plan_superblock_kernel(const float* __restrict__ proto_scores, int T, int cap,
+                                                              unsigned long long* __restrict__ lists_out) {
+  __shared__ unsigned long long keys[PLAN_SB];
+  const int s = blockIdx.x, b = blockIdx.y, nsb = gridDim.x;
+  const float* sc = proto_scores + (int64_t)b * T;
+  const int t0 = s * PLAN_SB;
+  for (int i = threadIdx.x; i < PLAN_SB; i += blockDim.x) keys[i] = t0 + i < T ? plan_key(sc[t0 + i], t0 + i) : ~0ull;
+  __syncthreads();
+  bitonic_sort_u64(keys, PLAN_SB);
+  unsigned long long* out = lists_out + ((int64_t)b * nsb + s) * cap;
+  for (int i = threadIdx.x; i < cap; i += blockDim.x) out[i] = i < PLAN_SB ? keys[i] : ~0ull;
+}
+
+// B: one Hillis-Steele level.  out[s] = top-cap(in[s] U in[s - d]) for s >= d, else in[s].  grid (nsb, B).
+__global__ void __launch_bounds__(256) plan_scan_level_kernel(const unsigned long long* __restrict__ in, int cap, int d,
+                                                              unsigned long long* __restrict__ out) {
+  __shared__ unsigned long long keys[2048];
+  const int s = blockIdx.x, b = blockIdx.y, nsb = gridDim.x;
+  const unsigned long long* a = in + ((int64_t)b * nsb + s) * cap;
+  unsigned long long* o = out + ((int64_t)b * nsb + s) * cap;
+  if (s < d) {
+    for (int i = threadIdx.x; i < cap; i += blockDim.x) o[i] = a[i];
+    return;
+  }
+  const unsigned long long* c = in + ((int64_t)b * nsb + s - d) * cap;
+  int P2 = 2;
+  while (P2 < 2 * cap) P2 <<= 1;
+  for (int i = threadIdx.x; i < P2; i += blockDim.x) keys[i] = i < cap ? a[i] : (i < 2 * cap ? c[i - cap] : ~0ull);
+  __syncthreads();
+  bitonic_sort_u64(keys, P2);
+  for (int i = threadIdx.x; i < cap; i += blockDim.x) o[i] = keys[i];
+}
+
+// C: grid (nblk, B).  `scanned` holds the inclusive scan of the super-block lists.
+__global__ void __launch_bounds__(256) plan_block_kernel(const float* __restrict__ proto_scores, int T, int cap,
+                                                         const unsigned long long* __restrict__ scanned, int nsb,
+                                                         int list_stride, int32_t* __restrict__ lists,
+                                                         int32_t* __restrict__ limits) {
+  __shared__ unsigned long long keys[2048];
+  const int blk = blockIdx.x, b = blockIdx.y, nblk = gridDim.x;
+  const float* sc = proto_scores + (int64_t)b * T;
+  const int t0 = blk * PLAN_BLOCK;
+  const int nb = min(PLAN_BLOCK, T - t0);
+  const int s = t0 / PLAN_SB, sb0 = s * PLAN_SB;
+  // candidates of the prefix [0, t0): everything kept from earlier super-blocks + my super-block up to t0
+  const unsigned long long* prev = s > 0 ? scanned + ((int64_t)b * nsb + s - 1) * cap : nullptr;
+  const int n_prev = prev ? cap : 0, n_mine = t0 - sb0;
+  int P2 = 2;
+  while (P2 < n_prev + n_mine) P2 <<= 1;
+  for (int i = threadIdx.x; i < P2; i += blockDim.x) {
+    unsigned long long k = ~0ull;
+    if (i < n_prev) k = prev[i];
+    else if (i < n_prev + n_mine) k = plan_key(sc[sb0 + i - n_prev], sb0 + i - n_prev);
+    keys[i] = k;
+  }
+  __syncthreads();
+  if (n_prev + n_mine > 1) bitonic_sort_u64(keys, P2);
+  // keep min(cap, t0) of them (pads sort last; real keys are fewer than that only when t0 < cap), add my tokens
+  const int nprefix = min(cap, t0);
+  __syncthreads();
+  int Q2 = 1;
+  while (Q2 < cap + PLAN_BLOCK) Q2 <<= 1;
+  for (int i = threadIdx.x; i < Q2; i += blockDim.x) {
+    if (i >= nprefix) keys[i] = (i - nprefix) < nb ? plan_key(sc[t0 + i - nprefix], t0 + i - nprefix) : ~0ull;
+  }
+  __syncthreads();
+  const int total = nprefix + nb;
+  bitonic_sort_u64(keys, Q2);
+  int32_t* out = lists + ((int64_t)b * nblk + blk) * list_stride;
+  for (int i = threadIdx.x; i < list_stride; i += blockDim.x)
+    out[i] = i < total ? (int32_t)(keys[i] & 0xffffffffu) : -1;
+  if ((int)threadIdx.x < nb) {
+    const int t = t0 + threadIdx.x;
+    const int want = min(t + 1, cap);
+    int have = 0, pos = 0;
+    while (pos < total && have < want) {
+      const int idx = (int)(keys[pos] & 0xffffffffu);
+      if (idx <= t) ++have;
+      ++pos;
+    }
+    limits[(int64_t)b * T + t] = pos;
+  }
+}
+
 // Explicit candidate table: one CTA per row.
 __global__ void __launch_bounds__(256) build_candidates_kernel(
     const int64_t* __restrict__ rows, const int64_t* __restrict__ row_batch, int seq_len, int L, int w_local,
@@ -232,23 +334,39 @@ __global__ void __launch_bounds__(256) build_candidates_kernel(
 using namespace aspa;
 
 extern "C" int64_t aspa_proto_plan_scratch(int B, int T, int proto_cap) {
-  (void)B; (void)T; (void)proto_cap;
-  return 16;  // this implementation keeps everything in shared memory
+  if (proto_cap <= 0 || proto_cap > PLAN_FAST_CAP || T <= 2 * PLAN_SB) return 16;  // the one-kernel plan needs none
+  const int64_t nsb = ceil_div(T, PLAN_SB);
+  return 2 * (int64_t)B * nsb * proto_cap * (int64_t)sizeof(unsigned long long);   // two scan buffers
 }
 
 extern "C" int aspa_proto_plan(const float* proto_scores, int B, int T, int proto_cap, void* scratch,
                                int32_t* proto_lists, int32_t* proto_limit, void* stream) {
-  (void)scratch;
   ASPA_CHECK_ARG(proto_scores && proto_lists && proto_limit, "null pointer");
   ASPA_CHECK_ARG(B > 0 && T > 0 && proto_cap > 0, "bad sizes");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (proto_cap <= PLAN_FAST_CAP && T > 2 * PLAN_SB) {
+    ASPA_CHECK_ARG(scratch != nullptr, "scratch of aspa_proto_plan_scratch() bytes required");
+    const int nsb = (int)ceil_div(T, PLAN_SB), nblk = (int)ceil_div(T, PLAN_BLOCK);
+    unsigned long long* buf0 = reinterpret_cast<unsigned long long*>(scratch);
+    unsigned long long* buf1 = buf0 + (int64_t)B * nsb * proto_cap;
+    plan_superblock_kernel<<<dim3(nsb, B), 256, 0, st>>>(proto_scores, T, proto_cap, buf0);
+    unsigned long long *in = buf0, *out = buf1;
+    for (int d = 1; d < nsb; d <<= 1) {
+      plan_scan_level_kernel<<<dim3(nsb, B), 256, 0, st>>>(in, proto_cap, d, out);
+      std::swap(in, out);
+    }
+    plan_block_kernel<<<dim3(nblk, B), 256, 0, st>>>(proto_scores, T, proto_cap, in, nsb, proto_cap + PLAN_BLOCK,
+                                                     proto_lists, proto_limit);
+    ASPA_CHECK_LAUNCH();
+    return ASPA_OK;
+  }
   int P2 = 1;
   while (P2 < proto_cap + PLAN_BLOCK) P2 <<= 1;
   const size_t smem = sizeof(unsigned long long) * P2;
   ASPA_CHECK_ARG(smem <= 200 * 1024, "proto_cap too large for the planning kernel (max ~ 25000)");
   cudaFuncSetAttribute(proto_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   const dim3 grid((unsigned)ceil_div(T, PLAN_BLOCK), B);
-  proto_plan_kernel<<<grid, 256, smem, (cudaStream_t)stream>>>(proto_scores, T, proto_cap, proto_cap + PLAN_BLOCK,
-                                                               proto_lists, proto_limit);
+  proto_plan_kernel<<<grid, 256, smem, st>>>(proto_scores, T, proto_cap, proto_cap + PLAN_BLOCK, proto_lists, proto_limit);
   ASPA_CHECK_LAUNCH();
   return ASPA_OK;
 }

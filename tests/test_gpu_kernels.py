@@ -692,3 +692,31 @@ def test_anchor_keys_through_the_tile_kernel(dev, case, quant):
     finally:
         ops.USE_ANCHOR_TILES = True
     assert float((a - b).abs().max()) < 2e-2 and float((a - b).abs().mean()) < 1e-3
+
+
+@pytest.mark.parametrize("T,cap", [(5000, 10), (9000, 409), (4100, 960), (3000, 40), (2049, 200)])
+def test_proto_plan_hierarchical_matches_definition(dev, T, cap):
+    """Block lists = (top-cap of the prefix before the block) U (the block's tokens), sorted by (score desc, index asc);
+    limits[t] = leading entries needed for min(t+1, cap) picks with index <= t.  Long rows take the hierarchical
+    kernels; the definition is evaluated directly here."""
+    from proteus_flux_attention_b200 import ops
+    g = torch.Generator().manual_seed(T + cap)
+    sc = torch.rand(2, T, generator=g)
+    sc[:, ::3] = (sc[:, ::3] * 8).round() / 8   # plenty of ties
+    lists, limits = ops.proto_plan(sc.to(dev), cap)
+    lists, limits = lists.cpu(), limits.cpu()
+    for b in range(2):
+        order_key = lambda idx: sorted(idx, key=lambda i: (-float(sc[b, i]), i))  # noqa: E731
+        for blk in range((T + 127) // 128):
+            t0 = blk * 128
+            nb = min(128, T - t0)
+            prefix = order_key(range(t0))[: min(cap, t0)]
+            want = order_key(prefix + list(range(t0, t0 + nb)))
+            got = lists[b, blk].tolist()
+            assert got[: len(want)] == want and all(v == -1 for v in got[len(want):])
+            for t in (t0, t0 + nb // 2, t0 + nb - 1):
+                need, have, pos = min(t + 1, cap), 0, 0
+                while pos < len(want) and have < need:
+                    have += 1 if want[pos] <= t else 0
+                    pos += 1
+                assert int(limits[b, t]) == pos
