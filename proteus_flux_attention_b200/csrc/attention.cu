@@ -12,6 +12,7 @@
 //                         groups keep the masked-out fraction small).  INT8 inputs are widened to bf16 while
 //                         staging (|v| <= 127 is exact in bf16, dot products of 64 such terms are exact in fp32).
 #include "common.cuh"
+#include "mma.cuh"
 
 namespace aspa {
 
@@ -346,29 +347,8 @@ constexpr int WK_ROWS = 64;   // packed rows per CTA
 constexpr int WK_KEYS = 64;   // keys per tile
 constexpr int WK_D = 64;
 
-__device__ __forceinline__ uint32_t smem_u32(const void* ptr) { return (uint32_t)__cvta_generic_to_shared(ptr); }
-
 // 64x64 bf16 tile, rows of 128 B = 8 chunks of 16 B; chunk c of row r lives at chunk (c ^ (r & 7)).
 __device__ __forceinline__ int swz(int row, int chunk) { return row * 128 + ((chunk ^ (row & 7)) << 4); }
-
-__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
-}
-__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<uint32_t*>(&h);
-}
 
 // 8 consecutive elements of a row -> one 16-byte bf16 chunk
 template <typename T>
@@ -388,14 +368,6 @@ __device__ __forceinline__ uint4 load_chunk<int8_t>(const int8_t* row, int chunk
   o.w = pack_bf16((float)b[6], (float)b[7]);
   return o;
 }
-
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
-  // 16-byte asynchronous copy; src_bytes == 0 fills the destination with zeros
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 constexpr int WK_TILE_BYTES = WK_KEYS * 128;  // one 64-key K or V tile in shared memory
 

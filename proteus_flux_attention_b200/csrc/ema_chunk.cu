@@ -2,6 +2,7 @@
 // shortlist pipeline.
 #include "cluster.cuh"
 #include "common.cuh"
+#include "mma.cuh"
 
 namespace aspa {
 
@@ -54,6 +55,142 @@ __global__ void __launch_bounds__(EMA_CH) ema_partial_kernel(const T* __restrict
     for (int g = 0; g < GT; ++g)
       if (g < G) part_c[(int64_t)chunk * G + g] = cnt[g];
   }
+}
+
+// The same partial sums on the tensor cores (bf16 activations): W[g][c] = sum_t probs[t][g] * x[t][c] is a GEMM with
+// M = gates, N = channels, K = tokens.  The fp32 probabilities are split into three bf16 terms (hi + mid + lo), so
+// every product is exact and the fp32 accumulation carries full precision; x is used as it is.
+// CTA = 8 warps: a chunk of ETC_TOK tokens x 256 channels (32 per warp); token steps of 32 arrive by cp.async in a
+// 3-stage ring; B fragments come from ldmatrix.trans on the staged (token-major) tile.
+constexpr int ETC_TOK = 2048;    // tokens per CTA
+constexpr int ETC_STEP = 32;     // tokens per pipeline stage
+constexpr int ETC_CH = 256;      // channels per CTA
+constexpr int ETC_STAGES = 3;
+constexpr int ETC_X_BYTES = ETC_STEP * ETC_CH * 2;   // 16 KB
+
+template <int MT>  // MT = ceil(G / 16) m-tiles of 16 gates
+__global__ void __launch_bounds__(256) ema_partial_tc_kernel(const __nv_bfloat16* __restrict__ x, int64_t n, int C,
+                                                             const float* __restrict__ gate_probs, int G,
+                                                             float* __restrict__ part_w, float* __restrict__ part_c) {
+  extern __shared__ __align__(128) unsigned char etc_smem[];
+  unsigned char* xs = etc_smem;                                              // ETC_STAGES x [32 tokens][512 B], swizzled
+  float* ps = reinterpret_cast<float*>(etc_smem + ETC_STAGES * ETC_X_BYTES);  // ETC_STAGES x [32 tokens][MT*16]
+  constexpr int GP = MT * 16;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int chunk = blockIdx.x, c0 = blockIdx.y * ETC_CH;
+  const int64_t t_begin = (int64_t)chunk * ETC_TOK;
+  const int64_t t_end = min(n, t_begin + ETC_TOK);
+  const int nsteps = (int)((t_end - t_begin + ETC_STEP - 1) / ETC_STEP);
+
+  auto issue = [&](int step) {
+    if (step < nsteps) {
+      const int slot = step % ETC_STAGES;
+      const int64_t tb = t_begin + (int64_t)step * ETC_STEP;
+      unsigned char* xd = xs + slot * ETC_X_BYTES;
+      // 32 tokens x 32 chunks of 16 B; chunk c of token r lives at chunk (c ^ (r & 7)) of its 512-byte row
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int idx = tid + 256 * i;
+        const int r = idx >> 5, ch = idx & 31;
+        const int64_t t = tb + r;
+        const bool ok = t < t_end && c0 + ch * 8 < C;
+        const __nv_bfloat16* src = x + (ok ? t : t_begin) * C + (ok ? c0 + ch * 8 : 0);
+        cp_async16(smem_u32(xd + r * 512 + ((ch ^ (r & 7)) << 4)), src, ok ? 16 : 0);
+      }
+      float* pd = ps + slot * ETC_STEP * GP;
+      for (int idx = tid; idx < ETC_STEP * GP / 4; idx += 256) {   // 16-byte pieces of the probability rows
+        const int r = idx / (GP / 4), g4 = (idx % (GP / 4)) * 4;
+        const int64_t t = tb + r;
+        const bool ok = t < t_end && g4 + 3 < G && (G % 4) == 0;
+        if (ok || (t < t_end && g4 < G)) {
+          if (ok) {
+            cp_async16(smem_u32(pd + r * GP + g4), gate_probs + t * G + g4, 16);
+          } else {   // ragged gate count: plain loads
+            for (int e = 0; e < 4; ++e) pd[r * GP + g4 + e] = g4 + e < G ? gate_probs[t * G + g4 + e] : 0.f;
+          }
+        } else {
+          *reinterpret_cast<float4*>(pd + r * GP + g4) = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      }
+    }
+    cp_async_commit();
+  };
+
+  float acc[MT][4][4];
+#pragma unroll
+  for (int m = 0; m < MT; ++m)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[m][j][e] = 0.f;
+  float cnt = 0.f;   // thread g < G of the first channel group sums the probabilities of gate g, in token order
+
+#pragma unroll
+  for (int s_ = 0; s_ < ETC_STAGES - 1; ++s_) issue(s_);
+  const int gq = lane >> 2, q = lane & 3;
+  for (int step = 0; step < nsteps; ++step) {
+    cp_async_wait<ETC_STAGES - 2>();
+    __syncthreads();
+    issue(step + ETC_STAGES - 1);
+    const unsigned char* xd = xs + (step % ETC_STAGES) * ETC_X_BYTES;
+    const float* pd = ps + (step % ETC_STAGES) * ETC_STEP * GP;
+    if (blockIdx.y == 0 && tid < G) {
+      for (int r = 0; r < ETC_STEP; ++r) cnt += pd[r * GP + tid];
+    }
+#pragma unroll
+    for (int k16 = 0; k16 < ETC_STEP / 16; ++k16) {
+      // B fragments: this warp's 32 channels = chunks 4*warp .. 4*warp+3, two n-tiles per ldmatrix
+      uint32_t bf[4][2];
+#pragma unroll
+      for (int jp = 0; jp < 2; ++jp) {
+        const int r = k16 * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);
+        const int ch = warp * 4 + jp * 2 + (lane >> 4);
+        ldmatrix_x4_trans(smem_u32(xd + r * 512 + ((ch ^ (r & 7)) << 4)), bf[2 * jp][0], bf[2 * jp][1], bf[2 * jp + 1][0],
+                          bf[2 * jp + 1][1]);
+      }
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+        // A = probs^T: A[gate][token]; fragment rows gq, gq+8, token pairs 2q, 2q+1 and +8
+        float pv[8];
+        const int g0 = m * 16 + gq, tk = k16 * 16 + 2 * q;
+        pv[0] = pd[(tk) * GP + g0];          pv[1] = pd[(tk + 1) * GP + g0];
+        pv[2] = pd[(tk) * GP + g0 + 8];      pv[3] = pd[(tk + 1) * GP + g0 + 8];
+        pv[4] = pd[(tk + 8) * GP + g0];      pv[5] = pd[(tk + 9) * GP + g0];
+        pv[6] = pd[(tk + 8) * GP + g0 + 8];  pv[7] = pd[(tk + 9) * GP + g0 + 8];
+        float res[8];
+#pragma unroll
+        for (int term = 0; term < 3; ++term) {
+          uint32_t af[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float v0 = term == 0 ? pv[2 * i] : res[2 * i], v1 = term == 0 ? pv[2 * i + 1] : res[2 * i + 1];
+            const float h0 = bf16_round(v0), h1 = bf16_round(v1);
+            res[2 * i] = v0 - h0;       // exact: what this term does not represent
+            res[2 * i + 1] = v1 - h1;
+            af[i] = pack_bf16(h0, h1);
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) mma_bf16(acc[m][j], af, bf[j][0], bf[j][1]);
+        }
+      }
+    }
+  }
+  cp_async_wait<0>();
+  // partial sums: part_w[(chunk*G + g)*C + c]
+#pragma unroll
+  for (int m = 0; m < MT; ++m)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int c = c0 + warp * 32 + j * 8 + 2 * q;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int g = m * 16 + gq + 8 * half;
+        if (g < G && c < C)
+          *reinterpret_cast<float2*>(part_w + ((int64_t)chunk * G + g) * C + c) =
+              make_float2(acc[m][j][2 * half], acc[m][j][2 * half + 1]);
+      }
+    }
+  if (blockIdx.y == 0 && tid < G) part_c[(int64_t)chunk * G + tid] = cnt;
 }
 
 __global__ void __launch_bounds__(256) ema_apply_kernel(const float* __restrict__ part_w,
@@ -670,12 +807,30 @@ extern "C" int aspa_proto_ema_update(const void* x, int x_dtype, int64_t n, int 
   ASPA_CHECK_ARG(n > 0 && C > 0 && G > 0 && G <= 64, "bad sizes (G <= 64)");
   ASPA_CHECK_ARG(x_dtype == ASPA_F32 || x_dtype == ASPA_BF16, "x must be fp32 or bf16");
   cudaStream_t st = (cudaStream_t)stream;
-  const int64_t nchunk = ceil_div(n, EMA_TOK);
+  // bf16 activations with 8-element aligned rows go through the tensor cores (larger token chunks, fewer partials)
+  const bool tc = x_dtype == ASPA_BF16 && C % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+                  (reinterpret_cast<uintptr_t>(gate_probs) & 15) == 0;
+  const int64_t nchunk = ceil_div(n, tc ? ETC_TOK : EMA_TOK);
   float* pw = reinterpret_cast<float*>(scratch);
   float* pc = pw + nchunk * G * C;
   if (updated) cudaMemsetAsync(updated, 0, sizeof(int32_t), st);
-  if (x_dtype == ASPA_F32) ema_launch<float>((const float*)x, n, C, gate_probs, G, pw, pc, st);
-  else ema_launch<__nv_bfloat16>((const __nv_bfloat16*)x, n, C, gate_probs, G, pw, pc, st);
+  if (tc) {
+    const int MT = (int)ceil_div(G, 16);
+    const dim3 grid((unsigned)nchunk, (unsigned)ceil_div(C, ETC_CH));
+    const size_t smem = ETC_STAGES * (ETC_X_BYTES + ETC_STEP * MT * 16 * sizeof(float));
+    auto launch = [&](auto kernel) {
+      cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      kernel<<<grid, 256, smem, st>>>((const __nv_bfloat16*)x, n, C, gate_probs, G, pw, pc);
+    };
+    if (MT == 1) launch(ema_partial_tc_kernel<1>);
+    else if (MT == 2) launch(ema_partial_tc_kernel<2>);
+    else if (MT == 3) launch(ema_partial_tc_kernel<3>);
+    else launch(ema_partial_tc_kernel<4>);
+  } else if (x_dtype == ASPA_F32) {
+    ema_launch<float>((const float*)x, n, C, gate_probs, G, pw, pc, st);
+  } else {
+    ema_launch<__nv_bfloat16>((const __nv_bfloat16*)x, n, C, gate_probs, G, pw, pc, st);
+  }
   ASPA_CHECK_LAUNCH();
   ema_apply_kernel<<<dim3((unsigned)ceil_div(C, 256), G), 256, 0, st>>>(pw, pc, nchunk, C, G, (float)decay, (float)(1.0 - decay), prototypes, usage,
                                                                        confidence, updated);
