@@ -252,6 +252,7 @@ __global__ void __launch_bounds__(GEN_WARPS * 32) attn_rows_kernel(const AttnPar
     }
     float s = -INFINITY;
     if (idx >= 0) {
+      // one key row per lane (sharing a row between lanes and reducing with shuffles was measured 20-40 % slower)
       s = dot_row<T>(kh + (int64_t)idx * k_ts, qs, D) * sc;
       if (p.add_mask) s += p.add_mask[(int64_t)t * Tn + idx];
     }

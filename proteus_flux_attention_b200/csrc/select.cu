@@ -190,6 +190,7 @@ __global__ void __launch_bounds__(1024) token_select_regs_kernel(const float* __
 // Token keep with the row's keys spread over a cluster of CTAs (8 keys per thread, 8192 tokens per CTA, up to
 // 8 CTAs): CTA r of the cluster owns tokens [r*8192, (r+1)*8192) and thread t of it the 8 consecutive tokens from
 // r*8192 + t*8, so index order is (rank, thread, slot) order and tied keys rank by one scan.  grid = rows * csize.
+template <int EPT>
 __global__ void __launch_bounds__(CL_THREADS) token_select_cluster_kernel(const float* __restrict__ importance, int T,
                                                                           int need0, float threshold, int guard,
                                                                           uint8_t* __restrict__ token_mask,
@@ -203,13 +204,13 @@ __global__ void __launch_bounds__(CL_THREADS) token_select_cluster_kernel(const 
   const int row = blockIdx.x / csize;
   const float* imp = importance + (int64_t)row * T;
   uint8_t* out = token_mask + (int64_t)row * T;
-  const int base = rank * CL_KEYS_PER_CTA + threadIdx.x * CL_EPT;
+  const int base = rank * (EPT * CL_THREADS) + threadIdx.x * EPT;
   int parity = 0;
-  uint32_t keys[CL_EPT];
+  uint32_t keys[EPT];
   uint32_t above = 0;
   const bool vec_ok = (T % 4 == 0);
 #pragma unroll
-  for (int j = 0; j < CL_EPT; j += 4) {
+  for (int j = 0; j < EPT; j += 4) {
     float v[4] = {0.f, 0.f, 0.f, 0.f};
     if (vec_ok && base + j + 3 < T) {
       const float4 f = *reinterpret_cast<const float4*>(imp + base + j);
@@ -236,7 +237,7 @@ __global__ void __launch_bounds__(CL_THREADS) token_select_cluster_kernel(const 
   need = min(max(1, need), T);
   if (need >= T) {  // uniform over the cluster
 #pragma unroll
-    for (int j = 0; j < CL_EPT; ++j)
+    for (int j = 0; j < EPT; ++j)
       if (base + j < T) {
         out[base + j] = 1;
         if (kept_idx != nullptr) {
@@ -250,10 +251,10 @@ __global__ void __launch_bounds__(CL_THREADS) token_select_cluster_kernel(const 
     if (rank == 0 && threadIdx.x == 0) kept[row] = T;
     return;
   }
-  const uint32_t thr = cluster_kth_largest<CL_EPT>(keys, need, cs, parity);
+  const uint32_t thr = cluster_kth_largest<EPT>(keys, need, cs, parity);
   uint32_t ge[2] = {0u, 0u}, lower[2];
 #pragma unroll
-  for (int j = 0; j < CL_EPT; ++j) {
+  for (int j = 0; j < EPT; ++j) {
     ge[0] += keys[j] > thr ? 1u : 0u;
     ge[1] += keys[j] == thr ? 1u : 0u;
   }
@@ -264,7 +265,7 @@ __global__ void __launch_bounds__(CL_THREADS) token_select_cluster_kernel(const 
   int tie_rank = (int)lower[1] + block_exclusive_scan(my_eq, cs.scan_tmp, &n_eq);
   uint32_t kept_total = 0, on_bits = 0;
 #pragma unroll
-  for (int j = 0; j < CL_EPT; j += 4) {
+  for (int j = 0; j < EPT; j += 4) {
     uint32_t packed = 0;
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
@@ -302,7 +303,7 @@ __global__ void __launch_bounds__(CL_THREADS) token_select_cluster_kernel(const 
     slot += (int)kt_lower[0];
     const int64_t s0 = (int64_t)row * slots_per_row;
 #pragma unroll
-    for (int j = 0; j < CL_EPT; ++j)
+    for (int j = 0; j < EPT; ++j)
       if ((on_bits >> j) & 1u) {
         if (slot < slots_per_row) kept_idx[s0 + slot] = (int64_t)row * T + base + j;
         slot_of[(int64_t)row * T + base + j] = (int)min(s0 + slot, (int64_t)0x7fffffff);
@@ -686,7 +687,14 @@ extern "C" int aspa_token_select(const float* importance, int B, int T, int need
   } else if (T <= CL_MAX * CL_KEYS_PER_CTA) {
     int csize = 1;
     while (csize * CL_KEYS_PER_CTA < T) csize <<= 1;  // 1, 2, 4 or 8 CTAs; surplus slots hold no keys
-    const cudaError_t e = launch_clusters(token_select_cluster_kernel, B, csize, 0, st, importance, T, need, threshold,
+    const cudaError_t e = launch_clusters(token_select_cluster_kernel<CL_EPT>, B, csize, 0, st, importance, T, need, threshold,
+                                          guard, token_mask, kept, (int64_t*)nullptr, (int32_t*)nullptr, 0);
+    if (e != cudaSuccess) {
+      set_error("aspa_token_select: cluster launch failed: %s", cudaGetErrorString(e));
+      return ASPA_ERR_CUDA;
+    }
+  } else if (T <= CL_MAX * 32 * CL_THREADS) {  // up to 262144 tokens: 32 keys per thread over 8 CTAs
+    const cudaError_t e = launch_clusters(token_select_cluster_kernel<32>, B, CL_MAX, 0, st, importance, T, need, threshold,
                                           guard, token_mask, kept, (int64_t*)nullptr, (int32_t*)nullptr, 0);
     if (e != cudaSuccess) {
       set_error("aspa_token_select: cluster launch failed: %s", cudaGetErrorString(e));
@@ -709,7 +717,7 @@ extern "C" int aspa_token_select_compact(const float* importance, int B, int T, 
   cudaStream_t st = (cudaStream_t)stream;
   int csize = 1;
   while (csize * CL_KEYS_PER_CTA < T) csize <<= 1;
-  const cudaError_t e = launch_clusters(token_select_cluster_kernel, B, csize, 0, st, importance, T, need, threshold, guard,
+  const cudaError_t e = launch_clusters(token_select_cluster_kernel<CL_EPT>, B, csize, 0, st, importance, T, need, threshold, guard,
                                         token_mask, kept, kept_idx, slot_of, slots_per_row);
   if (e != cudaSuccess) {
     set_error("aspa_token_select_compact: cluster launch failed: %s", cudaGetErrorString(e));

@@ -80,7 +80,8 @@ def test_router_without_prototypes(dev):
                                                     (1000, 0.5, 0.7, 2, 0), (64, 0.999, 0.0, 1, 0), (1, 0.3, 0.0, 1, 0),
                                                     (70000, 0.2, 0.0, 4, 0), (16384, 0.1, 0.0, 4, 0),
                                                     (65536, 0.05, 0.0, 4, 0), (20001, 0.33, 0.0, 3, 0),
-                                                    (9000, 0.2, 0.7, 2, 0), (40000, 0.01, 0.0, 1, 600)])
+                                                    (9000, 0.2, 0.7, 2, 0), (40000, 0.01, 0.0, 1, 600), (200000, 0.2, 0.0, 4, 0),
+                                                    (262144, 0.05, 0.0, 4, 0), (300000, 0.1, 0.0, 2, 0)])
 def test_token_select_exact(dev, T, ratio, thr, guard, kmin):
     from proteus_flux_attention_b200 import ops
     from proteus_flux_attention_b200.aspa import _py_round_f32
