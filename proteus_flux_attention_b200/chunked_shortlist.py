@@ -164,6 +164,9 @@ class ChunkedShortlistConfig:
             raise ValueError("final_sparse_ratio must be positive.")
         if not (0.0 <= self.shortlist_alpha <= 1.0):
             raise ValueError("shortlist_alpha must be within [0, 1].")
+        if self.use_cuda_graph and not self.freeze_prototypes:
+            raise ValueError("use_cuda_graph needs freeze_prototypes=True (capture runs the layer extra times, which "
+                             "would move the prototype state)")
         if self.storage not in {"cpu", "disk", "auto", "device"}:
             raise ValueError("storage must be 'cpu', 'disk', 'auto' or 'device'.")
         if self.ram_limit_bytes is not None and self.ram_limit_bytes <= 0:
@@ -343,6 +346,34 @@ class ChunkedShortlistRunner:
         cache[key] = (graphs, statics)
         return cache[key]
 
+    def _final_replay(self, layer: AdaptiveSparseAttention, reduced: torch.Tensor) -> torch.Tensor:
+        """Pass 2 from a captured graph (one per reduced length): about sixty launches whose host cost would otherwise
+        exceed their device time.  The telemetry record of the call is re-armed after every replay."""
+        key = ("final_graph", reduced.size(1), reduced.dtype)
+        cache = self._layer_cache if self._layer_cache is not None else self.__dict__.setdefault("_graph_tmp", {})
+        if key not in cache:
+            static_in = torch.empty_like(reduced)
+            static_in.copy_(reduced)
+            side = torch.cuda.Stream(device=reduced.device)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for _ in range(2):
+                    layer(static_in)
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize(reduced.device)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                static_out = layer(static_in)
+            cache[key] = (g, static_in, static_out, layer.__dict__.get("_pending"))
+        g, static_in, static_out, ctx = cache[key]
+        static_in.copy_(reduced, non_blocking=True)
+        g.replay()
+        if ctx is not None:  # the replay refreshed the pinned record: decode it again on the next telemetry access
+            layer.__dict__["_pending"] = dict(ctx)
+            layer.__dict__["_head_stats_value"] = None
+            layer.__dict__["_sparse_state_value"] = None
+        return static_out.detach().clone()
+
     @staticmethod
     def _score_only(layer: AdaptiveSparseAttention, x: torch.Tensor) -> None:
         """Router + token keep + prototype EMA of one chunk, without the attention whose output pass 1 discards."""
@@ -482,7 +513,10 @@ class ChunkedShortlistRunner:
         if cfg.run_final_pass:
             final_model = self._make_layer(k_host, cfg.final_sparse_ratio, base_dtype, final_state, cfg.freeze_prototypes)
             torch.cuda.reset_peak_memory_stats(device)
-            final_output = final_model(reduced).detach()
+            if cfg.use_cuda_graph:
+                final_output = self._final_replay(final_model, reduced)
+            else:
+                final_output = final_model(reduced).detach()
             backend_info = get_last_backend_info()
             final_stats = _sanitize_mapping(dict(final_model.last_head_stats or {}))
             st = {k: v for k, v in (final_model._last_sparse_state or {}).items() if not isinstance(v, torch.Tensor)}

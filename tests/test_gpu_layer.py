@@ -358,3 +358,30 @@ def test_projection_on_kept_rows_equals_full_projection(dev, dtype):
     assert 0 < int(kept.sum()) < kept.numel()
     # rows of dropped tokens are exactly the projection bias
     assert torch.equal(outs[0][~kept], layer.proj.bias.float().expand_as(outs[0])[~kept])
+
+
+def test_chunked_pipeline_graph_replay_equals_eager(dev):
+    """Pass 1 replayed from captured graphs (promotion forked inside, double-buffered inputs) and pass 2 from its own
+    graph must give what the eager pipeline gives, run after run, for resident and host-streamed sequences."""
+    import proteus_flux_attention_b200 as P
+    from proteus_flux_attention_b200.chunked_shortlist import _build_model_config
+    torch.manual_seed(11)
+    mk = lambda n, r: P.AdaptiveSparseAttention(_build_model_config(n, 256, heads=4, sparse_ratio=r, shortlist_alpha=1.0,  # noqa: E731
+                                                                   router_top_p=0.9))
+    cast = lambda sd: {k: v.to(torch.bfloat16) if v.dtype == torch.float32 and "routing" not in k else v for k, v in sd.items()}  # noqa: E731
+    cs, fs = cast(mk(2048, 0.05).state_dict()), cast(mk(512, 0.5).state_dict())
+    seq = torch.randn(1, 5 * 2048 + 300, 256, generator=torch.Generator().manual_seed(4)).to(torch.bfloat16)
+    base = dict(seq_len=seq.size(1), d_model=256, chunk_len=2048, buffer_tokens=512, per_chunk_budget=128, device=dev, heads=4,
+                freeze_prototypes=True, warmup=False)
+    want = P.ChunkedShortlistRunner(P.ChunkedShortlistConfig(**base)).run(seq.to(dev), chunk_state=cs, final_state=fs)
+    runner = P.ChunkedShortlistRunner(P.ChunkedShortlistConfig(**base, use_cuda_graph=True), cache_layers=True)
+    for source in (seq.to(dev), seq.pin_memory(), seq.to(dev)):
+        got = runner.run(source, chunk_state=cs, final_state=fs)
+        assert torch.equal(got.keep_indices, want.keep_indices)
+        assert torch.equal(got.keep_scores, want.keep_scores)
+        assert torch.equal(got.reduced_sequence.cpu(), want.reduced_sequence.cpu())
+        assert torch.equal(got.final_output.cpu(), want.final_output.cpu())
+        assert got.final_stats["sparse_state"]["mode"] == want.final_stats["sparse_state"]["mode"]
+        assert [c.promoted for c in got.chunks] == [c.promoted for c in want.chunks]
+    with pytest.raises(ValueError, match="freeze_prototypes"):
+        P.ChunkedShortlistConfig(**{**base, "freeze_prototypes": False}, use_cuda_graph=True).validate()
