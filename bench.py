@@ -352,6 +352,8 @@ def main():
     ap.add_argument("--workload", default="chunked_1m", choices=["chunked_1m", "shortlist_256k", "sparse_16k", "router_64k"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-other-workloads", action="store_true",
+                    help="skip the shortlist_256k / sparse_16k side measurements of the default run")
     ap.add_argument("--clock-sampler", default="nvml", choices=["nvml", "smi", "none"],
                     help="how SM clocks / throttle reasons are sampled during the timed region")
     ap.add_argument("--clock-period-ms", type=int, default=20)
@@ -471,6 +473,28 @@ def main():
             dist.all_reduce(dt, op=dist.ReduceOp.MAX)
         e2e = {"value": wl.tokens / (float(dt.item()) / args.steps), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
                "d2h_bytes_per_step": int(d2h)}
+
+    # the single-layer workloads of the same metric, measured in the same run (one GPU; they do not shard)
+    others = None
+    if rank == 0 and world == 1 and args.workload == "chunked_1m" and not args.no_other_workloads:
+        others = {}
+        for name, k in (("shortlist_256k", 5), ("sparse_16k", 20)):
+            lw = LayerWorkload(name, device)
+            for _ in range(3):
+                lw.step()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(k):
+                lw.step()
+            b.record()
+            torch.cuda.synchronize()
+            ms_l = a.elapsed_time(b) / k
+            others[name] = {"tokens_per_s": lw.tokens / (ms_l / 1e3), "ms_per_step": ms_l, "steps": k, "warmup": 3,
+                            "config": lw.config}
+            del lw
+            torch.cuda.empty_cache()
+        wl.config["other_workloads"] = others
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline and args.workload != "router_64k":
