@@ -265,7 +265,19 @@ __global__ void __launch_bounds__(GEN_WARPS * 32) attn_rows_kernel(const AttnPar
 #pragma unroll
     for (int i = 0; i < GEN_MAXD / 32; ++i) acc[i] *= corr;
     const unsigned live = __ballot_sync(0xffffffffu, pr > 0.f);
-    if (kVec) {
+    if (kVec && LPR == 8) {
+      // head_dim 64 in bf16 / int8: eight steps of four candidates, written without branches so that the eight value
+      // loads are independent instructions the scheduler can have in flight together (dead candidates: weight 0, row 0)
+#pragma unroll
+      for (int st = 0; st < 8; ++st) {
+        const float pc = __shfl_sync(0xffffffffu, pr, st * 4 + grp);
+        const int ic = max(__shfl_sync(0xffffffffu, idx, st * 4 + grp), 0);
+        float vv[8];
+        load_vec<T>(vh + (int64_t)ic * v_ts + sub * VE, vv);
+#pragma unroll
+        for (int e = 0; e < VE; ++e) acc[e] = fmaf(pc, vv[e], acc[e]);
+      }
+    } else if (kVec) {
       const unsigned gmask = groups == 32 ? 0xffffffffu : ((1u << groups) - 1u);
       for (int c0g = 0; c0g < 32; c0g += groups) {
         if (!((live >> c0g) & gmask)) continue;  // warp-uniform
