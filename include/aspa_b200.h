@@ -193,6 +193,13 @@ int aspa_rope_rows_q(const void* q_rows, int dtype, const int64_t* kept_idx, con
                      int64_t max_rows, int B, int T, int H, int D, const float* cos_t, const float* sin_t, void* q,
                      void* stream);
 
+/* RoPE + head-major split + symmetric per-head INT8 in two passes over the fused bf16 projection (the first pass
+ * only takes the per-head amax of the rotated values): same results as aspa_rope_relayout followed by
+ * aspa_quantize_int8 on q, k and v, without the bf16 head-major intermediates (aspa.py:1312-1363, 1644-1656).
+ *   qkv (B, T, 3*H*D) bf16; q8, k8, v8 (B*H, T, D) int8 out; amax, scales (3, B*H) fp32 out. */
+int aspa_rope_quantize(const void* qkv, int B, int T, int H, int D, const float* cos_t, const float* sin_t,
+                       int8_t* q8, int8_t* k8, int8_t* v8, float* amax, float* scales, void* stream);
+
 /* max |x| per head of a (heads, T*D) tensor (aspa.py:1328). amax is overwritten. */
 int aspa_head_amax(const void* x, int dtype, int heads, int64_t per_head, float* amax, void* stream);
 

@@ -52,6 +52,7 @@ SIGNATURES = {
     "aspa_pack_mask": (_i, [_p, _i, _i, _p, _p, _p, _l, _p]),
     "aspa_rope_table": (_i, [_p, _i, _i, _i, _p, _p, _p]),
     "aspa_rope_relayout": (_i, [_p, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p]),
+    "aspa_rope_quantize": (_i, [_p, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p]),
     "aspa_head_amax": (_i, [_p, _i, _i, _l, _p, _p]),
     "aspa_quantize_int8": (_i, [_p, _i, _i, _l, _p, _p, _p, _p]),
     "aspa_proto_plan_scratch": (_l, [_i, _i, _i]),

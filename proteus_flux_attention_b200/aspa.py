@@ -885,7 +885,7 @@ class AdaptiveSparseAttention(nn.Module):
                "token_idx": token_idx, "row_offsets": row_offsets, "exec_mode": "shortlist"}
 
         # 5. projection + RoPE + head-major relayout (does not depend on the record)
-        kv_layout = None
+        kv_layout = quant_pack = None
         if will_compact:
             if compact is None:  # rows too long for the fused keep: compact the mask separately
                 n_slots = B * kept_bound
@@ -896,6 +896,15 @@ class AdaptiveSparseAttention(nn.Module):
             k, v, kv_layout = kv_fork["k"], kv_fork["v"], kv_fork["layout"]
             torch.cuda.current_stream().wait_event(kv_fork["done"])
             amax = None
+        elif (use_quant and alpha >= 0.95 and x.dtype == torch.bfloat16 and D % 8 == 0
+              and (self.quantize_sparse_int8_mode == "max" or self.quantize_sparse_int8_percentile >= 1.0)):
+            # INT8 shortlist that can never turn dense (alpha >= 0.95): rotate, split and quantise straight from the
+            # fused projection; the bf16 head-major q, k, v are never materialised
+            cos = sin = None
+            if self.use_rope:
+                cos, sin = self._rope_factors(T, dev, x.dtype)
+            quant_pack = ops.rope_quantize(self.qkv(x).contiguous(), H, D, cos, sin)
+            q = k = v = amax = None
         else:
             # queries of dropped tokens are never used: skip their relayout
             q, k, v, amax = self._project_qkv(x, want_amax=use_quant and self.quantize_sparse_int8_mode == "max",
@@ -967,7 +976,10 @@ class AdaptiveSparseAttention(nn.Module):
             dense_reason = None
             scales = None
             qa, ka, va = q, k, v
-            if use_quant:
+            if quant_pack is not None:
+                qa, ka, va, sc3 = quant_pack
+                scales = (sc3[0], sc3[1], sc3[2])
+            elif use_quant:
                 if self.quantize_sparse_int8_mode != "max" and self.quantize_sparse_int8_percentile < 1.0:
                     raise NotImplementedError("INT8 percentile scaling below 1.0 is not built in the sm_100a path")
                 if amax is None:

@@ -47,7 +47,10 @@ __device__ __forceinline__ uint32_t rope_word_bf16(uint32_t x, float c, float s)
   return *reinterpret_cast<const uint32_t*>(&o);
 }
 
-template <typename T>
+// MODE 0: write the rotated / relaid-out values (and optionally their per-head amax); MODE 1: amax only, nothing
+// written; MODE 2: write symmetric per-head INT8 of the rotated values using the amax of an earlier MODE 1 pass
+// (bf16 only: q8/k8/v8 are passed through the q, k, v pointers).
+template <typename T, int MODE>
 __global__ void __launch_bounds__(512) rope_relayout_kernel(const T* __restrict__ qkv, int B, int Tn, int H, int D,
                                                             const float* __restrict__ cos_t,
                                                             const float* __restrict__ sin_t, T* __restrict__ q,
@@ -74,12 +77,19 @@ __global__ void __launch_bounds__(512) rope_relayout_kernel(const T* __restrict_
     const float* cr = cos_t ? cos_t + (int64_t)t0 * half + d0 / 2 : nullptr;
     const float* sr = sin_t ? sin_t + (int64_t)t0 * half + d0 / 2 : nullptr;
     float local_max = 0.f;
+    float qscale = 1.f;
+    int8_t* dst8 = nullptr;
+    if (MODE == 2) {
+      qscale = fmaxf(__fdiv_rn(amax[sec * B * H + bh], 127.0f), 1e-6f);
+      dst8 = reinterpret_cast<int8_t*>(sec == 0 ? q : (sec == 1 ? k : v)) + ((int64_t)bh * Tn + t0) * D + d0;
+    }
     const uint8_t* keep = (sec == 0 && q_keep != nullptr) ? q_keep + (int64_t)b * Tn : nullptr;
 #pragma unroll 4
     for (int t = t0; t < t1; ++t) {
       if (keep != nullptr && !keep[t]) {  // queries of dropped tokens are never read: neither load nor store them
         src += nsec * (int64_t)C;
         dst += D;
+        if (MODE == 2) dst8 += D;
         if (cr) { cr += half; sr += half; }
         continue;
       }
@@ -92,13 +102,24 @@ __global__ void __launch_bounds__(512) rope_relayout_kernel(const T* __restrict_
           raw.z = rope_word_bf16(raw.z, c4.z, s4.z);
           raw.w = rope_word_bf16(raw.w, c4.w, s4.w);
         }
-        if (amax) {
+        if (MODE != 2 && amax) {
           const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const float2 f = __bfloat1622float2(h2[i]);
             local_max = fmaxf(local_max, fmaxf(fabsf(f.x), fabsf(f.y)));
           }
+        }
+        if (MODE == 2) {
+          const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&raw);
+          union { int8_t b8[8]; uint2 u; } pk;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float r = rintf(__fdiv_rn(__bfloat162float(e[i]), qscale));
+            pk.b8[i] = (int8_t)fminf(fmaxf(r, -127.f), 127.f);
+          }
+          *reinterpret_cast<uint2*>(dst8) = pk.u;
+          dst8 += D;
         }
       } else {
         float* f = reinterpret_cast<float*>(&raw);
@@ -112,12 +133,12 @@ __global__ void __launch_bounds__(512) rope_relayout_kernel(const T* __restrict_
         }
         if (amax) local_max = fmaxf(fmaxf(fabsf(f[0]), fabsf(f[1])), fmaxf(local_max, fmaxf(fabsf(f[2]), fabsf(f[3]))));
       }
-      *reinterpret_cast<uint4*>(dst) = raw;
+      if (MODE == 0) *reinterpret_cast<uint4*>(dst) = raw;
       src += nsec * (int64_t)C;
       dst += D;
       if (cr) { cr += half; sr += half; }
     }
-    if (amax) {
+    if (MODE != 2 && amax) {
       // lanes of a warp may belong to different (section, bh) groups: the lowest lane of every group folds in
       // its peers and issues one atomic (non-negative floats order like their bit patterns)
       const int key = sec * B * H + bh;
@@ -303,6 +324,11 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const uint4* __restric
   }
 }
 
+__global__ void scale_from_amax_kernel(const float* __restrict__ amax, int n, float* __restrict__ scales) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) scales[i] = fmaxf(__fdiv_rn(amax[i], 127.0f), 1e-6f);
+}
+
 }  // namespace aspa
 
 using namespace aspa;
@@ -329,12 +355,12 @@ extern "C" int aspa_rope_relayout(const void* qkv, int dtype, int B, int T, int 
   if (dtype == ASPA_BF16) {
     const int vec = 3 * H * D / 8;
     const int threads = (int)std::min<int64_t>(512, ceil_div(vec, 32) * 32);
-    rope_relayout_kernel<__nv_bfloat16><<<grid, threads, 0, (cudaStream_t)stream>>>(
+    rope_relayout_kernel<__nv_bfloat16, 0><<<grid, threads, 0, (cudaStream_t)stream>>>(
         (const __nv_bfloat16*)qkv, B, T, H, D, cos_t, sin_t, (__nv_bfloat16*)q, (__nv_bfloat16*)k, (__nv_bfloat16*)v, amax, q_keep, 3, 0);
   } else {
     const int vec = 3 * H * D / 4;
     const int threads = (int)std::min<int64_t>(512, ceil_div(vec, 32) * 32);
-    rope_relayout_kernel<float><<<grid, threads, 0, (cudaStream_t)stream>>>((const float*)qkv, B, T, H, D, cos_t, sin_t,
+    rope_relayout_kernel<float, 0><<<grid, threads, 0, (cudaStream_t)stream>>>((const float*)qkv, B, T, H, D, cos_t, sin_t,
                                                                            (float*)q, (float*)k, (float*)v, amax, q_keep, 3, 0);
   }
   ASPA_CHECK_LAUNCH();
@@ -391,12 +417,12 @@ extern "C" int aspa_rope_relayout_kv(const void* kv, int dtype, int B, int T, in
   if (dtype == ASPA_BF16) {
     const int vec = 2 * H * D / 8;
     const int threads = (int)std::min<int64_t>(512, ceil_div(vec, 32) * 32);
-    rope_relayout_kernel<__nv_bfloat16><<<grid, threads, 0, (cudaStream_t)stream>>>(
+    rope_relayout_kernel<__nv_bfloat16, 0><<<grid, threads, 0, (cudaStream_t)stream>>>(
         (const __nv_bfloat16*)kv, B, T, H, D, cos_t, sin_t, nullptr, (__nv_bfloat16*)k, (__nv_bfloat16*)v, nullptr, nullptr, 2, 1);
   } else {
     const int vec = 2 * H * D / 4;
     const int threads = (int)std::min<int64_t>(512, ceil_div(vec, 32) * 32);
-    rope_relayout_kernel<float><<<grid, threads, 0, (cudaStream_t)stream>>>((const float*)kv, B, T, H, D, cos_t, sin_t, nullptr,
+    rope_relayout_kernel<float, 0><<<grid, threads, 0, (cudaStream_t)stream>>>((const float*)kv, B, T, H, D, cos_t, sin_t, nullptr,
                                                                            (float*)k, (float*)v, nullptr, nullptr, 2, 1);
   }
   ASPA_CHECK_LAUNCH();
@@ -451,6 +477,30 @@ extern "C" int aspa_rope_inplace(void* x, int dtype, int64_t n_rows, int T, int6
                                                                                  cos_t, sin_t);
   else
     rope_inplace_kernel<float><<<blocks, 256, 0, (cudaStream_t)stream>>>((float*)x, n_rows, T, row_stride, H, D, cos_t, sin_t);
+  ASPA_CHECK_LAUNCH();
+  return ASPA_OK;
+}
+
+extern "C" int aspa_rope_quantize(const void* qkv, int B, int T, int H, int D, const float* cos_t, const float* sin_t,
+                                  int8_t* q8, int8_t* k8, int8_t* v8, float* amax, float* scales, void* stream) {
+  ASPA_CHECK_ARG(qkv && q8 && k8 && v8 && amax && scales, "null pointer");
+  ASPA_CHECK_ARG(B > 0 && T > 0 && H > 0 && D > 0 && D % 8 == 0, "bad sizes (head_dim must be a multiple of 8)");
+  ASPA_CHECK_ARG((cos_t == nullptr) == (sin_t == nullptr), "cos/sin tables come together");
+  cudaStream_t st = (cudaStream_t)stream;
+  const dim3 grid((unsigned)ceil_div(T, ROPE_TPB), (unsigned)B);
+  const int vec = 3 * H * D / 8;
+  const int threads = (int)std::min<int64_t>(512, ceil_div(vec, 32) * 32);
+  cudaMemsetAsync(amax, 0, sizeof(float) * 3 * B * H, st);
+  const __nv_bfloat16* src = (const __nv_bfloat16*)qkv;
+  rope_relayout_kernel<__nv_bfloat16, 1><<<grid, threads, 0, st>>>(src, B, T, H, D, cos_t, sin_t, nullptr, nullptr, nullptr,
+                                                                   amax, nullptr, 3, 0);
+  ASPA_CHECK_LAUNCH();
+  rope_relayout_kernel<__nv_bfloat16, 2><<<grid, threads, 0, st>>>(
+      src, B, T, H, D, cos_t, sin_t, reinterpret_cast<__nv_bfloat16*>(q8), reinterpret_cast<__nv_bfloat16*>(k8),
+      reinterpret_cast<__nv_bfloat16*>(v8), amax, nullptr, 3, 0);
+  ASPA_CHECK_LAUNCH();
+  // scales = max(amax / 127, 1e-6), the formula of the quantiser
+  scale_from_amax_kernel<<<(unsigned)ceil_div(3 * B * H, 256), 256, 0, st>>>(amax, 3 * B * H, scales);
   ASPA_CHECK_LAUNCH();
   return ASPA_OK;
 }

@@ -721,3 +721,17 @@ def test_proto_plan_hierarchical_matches_definition(dev, T, cap):
                     have += 1 if want[pos] <= t else 0
                     pos += 1
                 assert int(limits[b, t]) == pos
+
+
+def test_rope_quantize_equals_relayout_then_quantize(dev):
+    from proteus_flux_attention_b200 import ops
+    B, T, H, D = 2, 333, 4, 64
+    g = torch.Generator().manual_seed(23)
+    qkv = (torch.randn(B, T, 3 * H * D, generator=g) * 3).to(torch.bfloat16).to(dev)
+    inv = (1.0 / (10000.0 ** (torch.arange(0, D, 2).float() / D))).to(dev)
+    for cos, sin in (ops.rope_table(inv, T, D, torch.bfloat16), (None, None)):
+        q, k, v, amax = ops.rope_relayout(qkv, H, D, cos, sin, want_amax=True)
+        want = [ops.quantize_int8(t, amax[i].contiguous()) for i, t in enumerate((q, k, v))]
+        q8, k8, v8, scales = ops.rope_quantize(qkv, H, D, cos, sin)
+        for i, got in enumerate((q8, k8, v8)):
+            assert torch.equal(got, want[i][0]) and torch.equal(scales[i], want[i][1])
