@@ -133,6 +133,14 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(rows), "window": window, "sampler": self.kind}
 
 
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the main kernels of one 65536-token chunk
+# of the chunked_1m workload, from one ncu capture on B200 (summary: profiles/ncu_traffic_chunked_1m_kernels.md).
+NCU_DRAM_BYTES_PER_LAUNCH = {
+    "chunked_1m": {"attention": 238.3e6, "rope_inplace": 226.2e6, "router_tc": 135.8e6, "scatter_rows_fill": 78.0e6,
+                   "token_select": 0.3e6},
+}
+
+
 def peak_hbm():
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
@@ -455,7 +463,8 @@ def main():
         name, (n, tot_ms, nbytes) = top
         achieved = (nbytes / n) / (tot_ms / n * 1e-3) / 1e9
         roofline = {"bound": "hbm", "kernel": name, "achieved": achieved, "peak": peak, "unit": "GB/s",
-                    "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "traffic": None,
+                    "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
+                    "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(args.workload, {}).get(name) if world == 1 else None,
                     "launch_ms": tot_ms / n, "algorithmic_bytes_per_launch": nbytes / n,
                     "kernels_ms_per_step": {k: round(v[1] / args.steps, 4) for k, v in sorted(kt.items(), key=lambda kv: -kv[1][1])}}
 

@@ -460,23 +460,56 @@ __global__ void __launch_bounds__(256) head_select_kernel(const float* __restric
         for (int hh = 0; hh < HT; ++hh) hp[hh] += hh == h ? p : 0.f;  // static register indexing
       }
     }
-    for (int j = 0; j < kmax; ++j) {
-      int best = -1;
-      float bv = -INFINITY;
-      if (j < k) {
+    if (HT <= 32 && (kmax & 3) == 0) {
+      // picks kept in registers (statically indexed) and written as 16-byte vectors: scalar stores of a token's row
+      // would each dirty a separate 32-byte sector
+      int ti[HT];
+      float tsc[HT];
 #pragma unroll
-        for (int h = 0; h < HT; ++h)
-          if (h < H && !((bits >> h) & 1ull) && hp[h] > bv) {
-            bv = hp[h];
-            best = h;
+      for (int j = 0; j < HT; ++j) {
+        int best = -1;
+        float bv = -INFINITY;
+        if (j < k) {
+#pragma unroll
+          for (int h = 0; h < HT; ++h)
+            if (h < H && !((bits >> h) & 1ull) && hp[h] > bv) {
+              bv = hp[h];
+              best = h;
+            }
+          if (best >= 0) {
+            bits |= 1ull << best;
+            score_sum += bv;
           }
-        if (best >= 0) {
-          bits |= 1ull << best;
-          score_sum += bv;
         }
+        ti[j] = best;
+        tsc[j] = best >= 0 ? bv : 0.f;
       }
-      if (top_idx) top_idx[tok * kmax + j] = best;
-      if (top_score) top_score[tok * kmax + j] = best >= 0 ? bv : 0.f;
+#pragma unroll
+      for (int j = 0; j < HT; j += 4)
+        if (j < kmax) {
+          if (top_idx) *reinterpret_cast<int4*>(top_idx + tok * kmax + j) = make_int4(ti[j], ti[j + 1], ti[j + 2], ti[j + 3]);
+          if (top_score)
+            *reinterpret_cast<float4*>(top_score + tok * kmax + j) = make_float4(tsc[j], tsc[j + 1], tsc[j + 2], tsc[j + 3]);
+        }
+    } else {
+      for (int j = 0; j < kmax; ++j) {
+        int best = -1;
+        float bv = -INFINITY;
+        if (j < k) {
+#pragma unroll
+          for (int h = 0; h < HT; ++h)
+            if (h < H && !((bits >> h) & 1ull) && hp[h] > bv) {
+              bv = hp[h];
+              best = h;
+            }
+          if (best >= 0) {
+            bits |= 1ull << best;
+            score_sum += bv;
+          }
+        }
+        if (top_idx) top_idx[tok * kmax + j] = best;
+        if (top_score) top_score[tok * kmax + j] = best >= 0 ? bv : 0.f;
+      }
     }
     if (token_mask && !token_mask[tok]) bits = 0;
     head_bits[tok] = bits;
