@@ -384,8 +384,7 @@ __device__ __forceinline__ uint4 load_chunk<int8_t>(const int8_t* row, int chunk
 
 constexpr int WK_TILE_BYTES = WK_KEYS * 128;  // one 64-key K or V tile in shared memory
 
-// STAGES == 1: tiles are staged through registers (needed for int8, which is widened to bf16 on the way).
-// STAGES >= 2: bf16 tiles arrive by cp.async into a ring of STAGES buffers, one barrier per tile.
+// STAGES >= 2: depth of the cp.async ring (bf16 tiles, or raw int8 tiles that are widened in shared memory).
 template <typename T, int STAGES>
 __global__ void __launch_bounds__(128) attn_window_kernel(const AttnParams p) {
   extern __shared__ __align__(1024) unsigned char wk_smem[];
@@ -511,66 +510,85 @@ __global__ void __launch_bounds__(128) attn_window_kernel(const AttnParams p) {
     }
   }
 
-  // register prefetch of the first tile (STAGES == 1) / asynchronous ring (STAGES >= 2)
-  uint4 kreg[STAGES == 1 ? 4 : 1], vreg[STAGES == 1 ? 4 : 1];
-  auto fetch = [&](int kt) {
-    if (STAGES != 1) return;
-#pragma unroll
-    for (int i = 0; i < (STAGES == 1 ? 4 : 1); ++i) {
-      const int c = tid + 128 * i;
-      const int row = c >> 3, ch = c & 7;
-      const int key = kt * WK_KEYS + row;
-      if (key < Tn) {
-        kreg[i] = load_chunk<T>(kh + (int64_t)key * k_ts, ch);
-        vreg[i] = load_chunk<T>(vh + (int64_t)key * v_ts, ch);
-      } else {
-        kreg[i] = make_uint4(0, 0, 0, 0);
-        vreg[i] = make_uint4(0, 0, 0, 0);
-      }
-    }
-  };
+  // bf16: tiles arrive by cp.async into a ring of STAGES (K | V) buffers, one barrier per tile.
+  // int8: raw 64-byte rows arrive by cp.async into a ring of STAGES raw buffers behind two bf16 (K | V) buffers; the
+  // raw tile kt+1 is widened into the free bf16 buffer while tile kt is being multiplied, again one barrier per tile.
+  constexpr bool kI8 = sizeof(T) == 1;
+  constexpr int RAW_TILE = WK_KEYS * WK_D;   // bytes of one raw int8 tile
+  unsigned char* raw_s = kv_s + 2 * 2 * WK_TILE_BYTES;
   auto issue = [&](int kt) {  // cp.async tile kt into its ring slot; always commits a group (possibly empty)
     if (kt <= kt_end) {
-      unsigned char* ks_ = kv_s + ((kt - kt_begin) % STAGES) * 2 * WK_TILE_BYTES;
+      if (kI8) {
+        unsigned char* rk = raw_s + ((kt - kt_begin) % STAGES) * 2 * RAW_TILE;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int c = tid + 128 * i;
-        const int row = c >> 3, ch = c & 7;
-        const int key = kt * WK_KEYS + row;
-        const int64_t kc = min(key, Tn - 1);
-        const int nbytes = key < Tn ? 16 : 0;
-        cp_async16(smem_u32(ks_ + swz(row, ch)), kh + kc * k_ts + ch * 8, nbytes);
-        cp_async16(smem_u32(ks_ + WK_TILE_BYTES + swz(row, ch)), vh + kc * v_ts + ch * 8, nbytes);
+        for (int i = 0; i < 2; ++i) {
+          const int c = tid + 128 * i;
+          const int row = c >> 2, rc = c & 3;
+          const int key = kt * WK_KEYS + row;
+          const int64_t kc = min(key, Tn - 1);
+          const int nbytes = key < Tn ? 16 : 0;
+          cp_async16(smem_u32(rk + row * 64 + rc * 16), kh + kc * k_ts + rc * 16, nbytes);
+          cp_async16(smem_u32(rk + RAW_TILE + row * 64 + rc * 16), vh + kc * v_ts + rc * 16, nbytes);
+        }
+      } else {
+        unsigned char* ks_ = kv_s + ((kt - kt_begin) % STAGES) * 2 * WK_TILE_BYTES;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int c = tid + 128 * i;
+          const int row = c >> 3, ch = c & 7;
+          const int key = kt * WK_KEYS + row;
+          const int64_t kc = min(key, Tn - 1);
+          const int nbytes = key < Tn ? 16 : 0;
+          cp_async16(smem_u32(ks_ + swz(row, ch)), kh + kc * k_ts + ch * 8, nbytes);
+          cp_async16(smem_u32(ks_ + WK_TILE_BYTES + swz(row, ch)), vh + kc * v_ts + ch * 8, nbytes);
+        }
       }
     }
     cp_async_commit();
   };
-  if (STAGES == 1) {
-    if (kt_begin <= kt_end) fetch(kt_begin);
-  } else {
+  auto widen = [&](int kt) {  // int8 only: raw tile kt -> bf16 buffer (kt - kt_begin) % 2, swizzled
+    if (!kI8 || kt > kt_end) return;
+    const unsigned char* rk = raw_s + ((kt - kt_begin) % STAGES) * 2 * RAW_TILE;
+    unsigned char* dk = kv_s + ((kt - kt_begin) % 2) * 2 * WK_TILE_BYTES;
 #pragma unroll
-    for (int s_ = 0; s_ < STAGES - 1; ++s_) issue(kt_begin + s_);
+    for (int which = 0; which < 2; ++which) {   // K, then V
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int c = tid + 128 * i;
+        const int row = c >> 2, rc = c & 3;
+        const uint4 raw = *reinterpret_cast<const uint4*>(rk + which * RAW_TILE + row * 64 + rc * 16);
+        const int8_t* bq = reinterpret_cast<const int8_t*>(&raw);
+        uint4 lo, hi;
+        lo.x = pack_bf16((float)bq[0], (float)bq[1]);   lo.y = pack_bf16((float)bq[2], (float)bq[3]);
+        lo.z = pack_bf16((float)bq[4], (float)bq[5]);   lo.w = pack_bf16((float)bq[6], (float)bq[7]);
+        hi.x = pack_bf16((float)bq[8], (float)bq[9]);   hi.y = pack_bf16((float)bq[10], (float)bq[11]);
+        hi.z = pack_bf16((float)bq[12], (float)bq[13]); hi.w = pack_bf16((float)bq[14], (float)bq[15]);
+        *reinterpret_cast<uint4*>(dk + which * WK_TILE_BYTES + swz(row, 2 * rc)) = lo;
+        *reinterpret_cast<uint4*>(dk + which * WK_TILE_BYTES + swz(row, 2 * rc + 1)) = hi;
+      }
+    }
+  };
+#pragma unroll
+  for (int s_ = 0; s_ < STAGES - 1; ++s_) issue(kt_begin + s_);
+  if (kI8) {
+    cp_async_wait<(STAGES >= 2 ? STAGES - 2 : 0)>();
+    __syncthreads();
+    widen(kt_begin);
   }
 
+  // copies that may still be in flight at the top of an iteration: the bf16 path needs tile kt, the int8 path tile kt+1
+  constexpr int PEND = kI8 ? (STAGES >= 3 ? STAGES - 3 : 0) : (STAGES >= 2 ? STAGES - 2 : 0);
   for (int kt = kt_begin; kt <= kt_end; ++kt) {
-    if (STAGES == 1) {
-      __syncthreads();  // previous tile fully consumed
-#pragma unroll
-      for (int i = 0; i < (STAGES == 1 ? 4 : 1); ++i) {
-        const int c = tid + 128 * i;
-        const int row = c >> 3, ch = c & 7;
-        *reinterpret_cast<uint4*>(k_s + swz(row, ch)) = kreg[i];
-        *reinterpret_cast<uint4*>(v_s + swz(row, ch)) = vreg[i];
-      }
-      __syncthreads();
-      if (kt < kt_end) fetch(kt + 1);
+    cp_async_wait<PEND>();           // this thread's copies of tile kt (int8: kt+1) have landed
+    __syncthreads();                 // ... everybody's have, and tile kt-1 is no longer being read
+    issue(kt + STAGES - 1);          // refill the slot tile kt-1 occupied
+    if (kI8) {
+      widen(kt + 1);
+      k_s = kv_s + ((kt - kt_begin) % 2) * 2 * WK_TILE_BYTES;
     } else {
-      cp_async_wait<(STAGES >= 2 ? STAGES - 2 : 0)>();  // this thread's copies of tile kt have landed
-      __syncthreads();                 // ... everybody's have, and tile kt-1 is no longer being read
-      issue(kt + STAGES - 1);          // refill the slot tile kt-1 occupied
       k_s = kv_s + ((kt - kt_begin) % STAGES) * 2 * WK_TILE_BYTES;
-      v_s = k_s + WK_TILE_BYTES;
     }
+    v_s = k_s + WK_TILE_BYTES;
 
     const int kb = kt * WK_KEYS;
     if (w_first < 0 || kb > w_last || kb + WK_KEYS - 1 < w_lo) continue;  // tile outside this warp's rows
@@ -761,7 +779,8 @@ static void launch_generic(const AttnParams& p, int max_rows, cudaStream_t st) {
 template <typename T, int STAGES>
 static void launch_window(const AttnParams& p, int max_rows, cudaStream_t st, int groups = 0) {
   const dim3 grid((unsigned)ceil_div(max_rows, WK_ROWS), groups > 0 ? groups : p.heads);
-  const int smem = WK_ROWS * 128 + STAGES * 2 * WK_TILE_BYTES;
+  const int smem = sizeof(T) == 1 ? WK_ROWS * 128 + 2 * 2 * WK_TILE_BYTES + STAGES * 2 * WK_KEYS * WK_D
+                                  : WK_ROWS * 128 + STAGES * 2 * WK_TILE_BYTES;
   static bool attr_set = false;
   if (!attr_set) {
     cudaFuncSetAttribute(attn_window_kernel<T, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -850,7 +869,7 @@ extern "C" int aspa_gather_attn_fwd_ex(const void* q, const void* k, const void*
       p.ws_o = w + 2 * total_rows;
       p.write_partial = 1;
     }
-    if (qkv_dtype == ASPA_BF16) launch_window<__nv_bfloat16, 3>(p, max_rows, st); else launch_window<int8_t, 1>(p, max_rows, st);
+    if (qkv_dtype == ASPA_BF16) launch_window<__nv_bfloat16, 3>(p, max_rows, st); else launch_window<int8_t, 4>(p, max_rows, st);
     ASPA_CHECK_LAUNCH();
     // Anchors t - j*stride of the rows of one residue class t % stride are a window over the strided key sequence of
     // that class: with enough rows per (head, residue) group they go through the tile kernel too, regrouped.
@@ -883,7 +902,7 @@ extern "C" int aspa_gather_attn_fwd_ex(const void* q, const void* k, const void*
       // one step, and the kernel's tile loop takes care of larger groups
       const int rows_bound = (int)std::min<int64_t>(max_rows, std::max<int64_t>(WK_ROWS, 2 * total_rows / n_groups));
       if (qkv_dtype == ASPA_BF16) launch_window<__nv_bfloat16, 3>(pa, rows_bound, st, n_groups);
-      else launch_window<int8_t, 1>(pa, rows_bound, st, n_groups);
+      else launch_window<int8_t, 4>(pa, rows_bound, st, n_groups);
       ASPA_CHECK_LAUNCH();
       p.anchors_done = 1;
     }
