@@ -113,7 +113,6 @@ class SwitchRouter(nn.Module):
 
 
 # ---- config parsing helpers ------------------------------------------------------------------
-KV_GEMM_SM_TARGET = 0  # > 0: the forked K/V projection is sized for this many SMs and starts after the router
 _SIDE_STREAMS: Dict[str, "torch.cuda.Stream"] = {}  # one second stream per device, shared by all layers
 
 
@@ -540,7 +539,7 @@ class AdaptiveSparseAttention(nn.Module):
                                  None if want_amax else q_keep,
                                  q_fraction=float(self._token_keep_ratio_runtime or 1.0))
 
-    def _fork_kv_projection(self, x: torch.Tensor, sm_target: int = 0) -> dict:
+    def _fork_kv_projection(self, x: torch.Tensor) -> dict:
         """K/V projection + RoPE/relayout of every token on a second stream.  Nothing in it depends on the routing
         chain (router, token keep, head choice, packing), whose kernels are small or latency-bound and leave most of
         the GPU idle; the two run side by side and meet before the attention.  The outputs are allocated on the
@@ -562,13 +561,10 @@ class AdaptiveSparseAttention(nn.Module):
         ready.record(main)
         side.wait_event(ready)
         with torch.cuda.stream(side):
-            limited = sm_target > 0 and ops.blas_sm_target(sm_target)
             if b is None:
                 torch.mm(x.view(B * T, C), w[C:].t(), out=kv)
             else:
                 torch.addmm(b[C:], x.view(B * T, C), w[C:].t(), out=kv)
-            if limited:
-                ops.blas_sm_target(0)
             if cos is not None:  # keys are rotated where the projection left them; values are used as they are
                 ops.rope_inplace(kv.view(-1), B * T, T, 2 * C, H, D, cos, sin)
             done.record(side)
@@ -809,9 +805,9 @@ class AdaptiveSparseAttention(nn.Module):
         # INT8 scales are taken over the queries of every token (aspa.py:1328), so that mode projects them all.
         will_compact = (self.compact_projection and self.token_sparse and not keep_all and bound_known
                         and not use_quant and 4 * kept_bound <= 3 * T and not self.training)
-        # Started before the router unless the GEMM can be told to leave some SMs alone: launched after the router
-        # with all SMs, its CTAs starve the cluster launches of the token keep (158 us instead of 40 us per call).
-        kv_fork = self._fork_kv_projection(x) if will_compact and KV_GEMM_SM_TARGET <= 0 else None
+        # Started before the router: launched after it, the projection's CTAs starve the cluster launches of the token
+        # keep (158 us instead of 40 us per call).
+        kv_fork = self._fork_kv_projection(x) if will_compact else None
 
         # 1. router
         x2d = x.view(B * T, C)
@@ -830,9 +826,6 @@ class AdaptiveSparseAttention(nn.Module):
         self._last_token_similarity = sim.view(B, T) if sim is not None else None
         self._last_token_blend = bs.view(B, T) if bs is not None else None
         self._last_token_importance = imp.view(B, T)
-        if will_compact and kv_fork is None:
-            kv_fork = self._fork_kv_projection(x, sm_target=KV_GEMM_SM_TARGET)
-
         # 2. token keep
         token_mask_u8 = kept = compact = None
         if self.token_sparse:

@@ -427,25 +427,6 @@ def rope_inplace(x_rows: torch.Tensor, n_rows: int, T: int, row_stride: int, H: 
                                           H, D, N.ptr(cos), N.ptr(sin), N.stream()), "rope_inplace")
 
 
-_CUBLAS = None
-
-
-def blas_sm_target(count: int) -> bool:
-    """``cublasSetSmCountTarget`` on the cuBLAS handle torch uses for the current device and stream: GEMMs issued
-    through it afterwards size their grids for ``count`` multiprocessors (0 = all of them).  Lets a large projection
-    leave a few SMs to small kernels that run beside it on another stream.  False when the library cannot be reached."""
-    global _CUBLAS
-    try:
-        if _CUBLAS is None:
-            path = next((l.split()[-1] for l in open("/proc/self/maps") if "libcublas.so" in l), "libcublas.so.12")
-            _CUBLAS = C.CDLL(path)
-            _CUBLAS.cublasSetSmCountTarget.restype = C.c_int
-            _CUBLAS.cublasSetSmCountTarget.argtypes = [C.c_void_p, C.c_int]
-        return _CUBLAS.cublasSetSmCountTarget(C.c_void_p(torch.cuda.current_blas_handle()), int(count)) == 0
-    except Exception:
-        return False
-
-
 TOKEN_COMPACT_MAX_T = 65536  # ASPA_TOKEN_COMPACT_MAX_T of the C header
 
 
