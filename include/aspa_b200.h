@@ -189,6 +189,10 @@ int aspa_rope_relayout_kv(const void* kv, int dtype, int B, int T, int H, int D,
  * and `row_stride` elements apart, row r belongs to position r % T. */
 int aspa_rope_inplace(void* x, int dtype, int64_t n_rows, int T, int64_t row_stride, int H, int D, const float* cos_t,
                       const float* sin_t, void* stream);
+/* The same rotation written head-major: heads_out is (n_rows / T * H, T, D), x is left as it was (NULL heads_out:
+ * in place).  Keys of one head at consecutive positions end up contiguous, which is what a window of keys wants. */
+int aspa_rope_rows_to_heads(void* x, int dtype, int64_t n_rows, int T, int64_t row_stride, int H, int D,
+                            const float* cos_t, const float* sin_t, void* heads_out, void* stream);
 int aspa_rope_rows_q(const void* q_rows, int dtype, const int64_t* kept_idx, const int32_t* count_dev,
                      int64_t max_rows, int B, int T, int H, int D, const float* cos_t, const float* sin_t, void* q,
                      void* stream);

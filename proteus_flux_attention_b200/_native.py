@@ -71,6 +71,7 @@ SIGNATURES = {
                                      C.POINTER(ShortlistPlan), _p, _p, _i, _i, _p, C.POINTER(KVLayout), _p, _p, _p]),
     "aspa_attn_regroup_bytes": (_l, [_l, _i, _i]),
     "aspa_rope_inplace": (_i, [_p, _i, _l, _i, _l, _i, _i, _p, _p, _p]),
+    "aspa_rope_rows_to_heads": (_i, [_p, _i, _l, _i, _l, _i, _i, _p, _p, _p, _p]),
     "aspa_rope_relayout_kv": (_i, [_p, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p]),
     "aspa_rope_rows_q": (_i, [_p, _i, _p, _p, _l, _i, _i, _i, _i, _p, _p, _p, _p]),
     "aspa_compact_mask_scratch": (_l, [_l]),

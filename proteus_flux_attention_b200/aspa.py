@@ -113,7 +113,8 @@ class SwitchRouter(nn.Module):
 
 
 # ---- config parsing helpers ------------------------------------------------------------------
-_SIDE_STREAMS: Dict[str, "torch.cuda.Stream"] = {}  # one second stream per device, shared by all layers
+K_HEAD_MAJOR = True   # rotated keys are written head-major (a window of keys becomes one contiguous run)
+_SIDE_STREAMS: Dict[Tuple[str, int], "torch.cuda.Stream"] = {}  # second streams per (device, priority), shared by all layers
 
 
 def _num(config, name, default, kind=float):
@@ -551,12 +552,19 @@ class AdaptiveSparseAttention(nn.Module):
         w, b = self.qkv.weight, self.qkv.bias
         kv = torch.empty((B * T, 2 * C), dtype=x.dtype, device=dev)
         cos = sin = None
+        k_heads = None
         if self.use_rope:
             cos, sin = self._rope_factors(T, dev, x.dtype)
+            if K_HEAD_MAJOR:
+                k_heads = torch.empty((B * H, T, D), dtype=x.dtype, device=dev)
         main = torch.cuda.current_stream()
-        side = _SIDE_STREAMS.get(str(dev))
+        # One priority level below the caller's stream when that one is elevated: the GEMM fills the GPU, and the
+        # short kernels of the calling stream then take SMs as its blocks retire instead of waiting for all of them.
+        # Still above priority 0, where bulk copies run.
+        prio = min(0, int(main.priority) + 1)
+        side = _SIDE_STREAMS.get((str(dev), prio))
         if side is None:
-            side = _SIDE_STREAMS[str(dev)] = torch.cuda.Stream(device=dev)
+            side = _SIDE_STREAMS[(str(dev), prio)] = torch.cuda.Stream(device=dev, priority=prio)
         ready, done = torch.cuda.Event(), torch.cuda.Event()
         ready.record(main)
         side.wait_event(ready)
@@ -566,9 +574,12 @@ class AdaptiveSparseAttention(nn.Module):
             else:
                 torch.addmm(b[C:], x.view(B * T, C), w[C:].t(), out=kv)
             if cos is not None:  # keys are rotated where the projection left them; values are used as they are
-                ops.rope_inplace(kv.view(-1), B * T, T, 2 * C, H, D, cos, sin)
+                ops.rope_inplace(kv.view(-1), B * T, T, 2 * C, H, D, cos, sin, heads_out=k_heads)
             done.record(side)
         flat = kv.view(-1)
+        if k_heads is not None:
+            layout = N.KVLayout(k_batch=H * T * D, k_head=T * D, k_token=D, v_batch=T * 2 * C, v_head=D, v_token=2 * C)
+            return {"k": k_heads.view(-1), "v": flat[C:], "kv": kv, "layout": layout, "done": done}
         layout = N.KVLayout(k_batch=T * 2 * C, k_head=D, k_token=2 * C, v_batch=T * 2 * C, v_head=D, v_token=2 * C)
         return {"k": flat, "v": flat[C:], "kv": kv, "layout": layout, "done": done}
 

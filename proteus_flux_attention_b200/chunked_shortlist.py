@@ -178,8 +178,9 @@ class _ChunkFeeder:
 
     A sequence that is resident in HBM is handed out as views of itself.  A host sequence is uploaded chunk by chunk
     on a copy stream, one chunk ahead of the compute stream, into two device buffers.  With ``targets`` (the static
-    inputs of two captured graphs) every chunk, resident or not, is copied into ``targets[i % 2]`` on that copy stream,
-    so the copy of chunk i+1 overlaps the layer call of chunk i."""
+    inputs of captured graphs, chunk i going to ``targets[i % len(targets)]``) every chunk, resident or not, is copied
+    there on that copy stream, half the ring ahead: with four targets and two chunks in flight the copy of chunk i+2
+    runs while chunks i and i+1 are being worked on."""
 
     def __init__(self, source: torch.Tensor, local_start: int, device: torch.device, chunk_len: int,
                  targets: Optional[List[torch.Tensor]] = None):
@@ -191,12 +192,15 @@ class _ChunkFeeder:
         if self.copying:
             self.copy_stream = torch.cuda.Stream(device=device)
             shape = (1, chunk_len, source.size(2))
-            self.pinned_source = self.on_device or source.is_pinned()  # uploads straight from the caller's buffer
-            self.stage = [] if self.pinned_source else [torch.empty(shape, dtype=source.dtype, pin_memory=True) for _ in range(2)]
             self.dev = targets if targets is not None else [torch.empty(shape, dtype=source.dtype, device=device) for _ in range(2)]
-            self.ready = [torch.cuda.Event() for _ in range(2)]
-            self.consumed = [torch.cuda.Event() for _ in range(2)]
-            self.prefetched: Dict[int, int] = {}
+            self.nbuf = len(self.dev)
+            self.ahead = max(1, self.nbuf // 2)
+            self.pinned_source = self.on_device or source.is_pinned()  # uploads straight from the caller's buffer
+            self.stage = [] if self.pinned_source else [torch.empty(shape, dtype=source.dtype, pin_memory=True)
+                                                        for _ in range(self.nbuf)]
+            self.ready = [torch.cuda.Event() for _ in range(self.nbuf)]
+            self.consumed = [torch.cuda.Event() for _ in range(self.nbuf)]
+            self.issued = 0   # chunks 0 .. issued-1 have their copy on the copy stream
             if self.on_device:  # the source must be complete before the copy stream reads it
                 self.copy_stream.wait_stream(torch.cuda.current_stream())
 
@@ -213,21 +217,23 @@ class _ChunkFeeder:
             self.dev[slot][:, :n].copy_(host, non_blocking=True)
             self.ready[slot].record(self.copy_stream)
 
-    def get(self, i: int, start: int, end: int, nxt: Optional[Tuple[int, int]]) -> torch.Tensor:
+    def get(self, i: int, bounds: Sequence[Tuple[int, int]]) -> torch.Tensor:
+        """Chunk i (``bounds[i]`` = its global start and end) on the device, ordered after its copy on the current
+        stream; starts the copies of the chunks up to ``ahead`` behind it."""
+        start, end = bounds[i]
         if not self.copying:
             return self.src[:, start - self.off:end - self.off]
-        slot = i % 2
-        if self.prefetched.pop(i, None) is None:
-            self._issue(slot, start, end)
-        if nxt is not None:
-            self._issue((i + 1) % 2, nxt[0], nxt[1])
-            self.prefetched[i + 1] = (i + 1) % 2
+        while self.issued < min(len(bounds), i + self.ahead + 1):
+            j = self.issued
+            self._issue(j % self.nbuf, bounds[j][0], bounds[j][1])
+            self.issued += 1
+        slot = i % self.nbuf
         torch.cuda.current_stream().wait_event(self.ready[slot])
         return self.dev[slot][:, :end - start]
 
     def done(self, i: int) -> None:
         if self.copying:
-            self.consumed[i % 2].record(torch.cuda.current_stream())
+            self.consumed[i % self.nbuf].record(torch.cuda.current_stream())
 
 
 class _Pass1Records:
@@ -241,9 +247,11 @@ class _Pass1Records:
         self.scores = torch.zeros((n_slots, budget), dtype=torch.float32, device=device)
         self.idx = torch.full((n_slots, budget), -1, dtype=torch.int64, device=device)
         self.count = torch.zeros((n_slots,), dtype=torch.int32, device=device)
-        self.slot = torch.zeros((1,), dtype=torch.int32, device=device)
+        # two slot numbers: two chunks can be in flight at once, each on its own lane (stream + captured graph)
+        self.slots = [torch.zeros((1,), dtype=torch.int32, device=device) for _ in range(2)]
+        self.slot = self.slots[0]
         self.offsets = torch.zeros((n_slots,), dtype=torch.int64, device=device)
-        self.stream = torch.cuda.Stream(device=device)
+        self.stream = torch.cuda.Stream(device=device, priority=-2)
 
     def reset(self, first_chunk: int, chunk_len: int) -> None:
         self.scores.zero_()
@@ -251,6 +259,9 @@ class _Pass1Records:
         self.count.zero_()
         torch.arange(first_chunk, first_chunk + self.n_slots, out=self.offsets)
         self.offsets.mul_(chunk_len)
+
+    def use_lane(self, lane: int) -> None:
+        self.slot = self.slots[lane]
 
     def hook(self, layer: AdaptiveSparseAttention) -> None:
         """Called by the layer right after its token keep: fork the promotion of this chunk."""
@@ -327,23 +338,34 @@ class ChunkedShortlistRunner:
         cache = self._layer_cache if self._layer_cache is not None else self.__dict__.setdefault("_graph_tmp", {})
         if key in cache:
             return cache[key]
-        statics = [torch.zeros(1, cfg.chunk_len, cfg.d_model, device=cfg.device, dtype=dtype) for _ in range(2)]
-        side = torch.cuda.Stream(device=cfg.device)
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):  # eager warm-up on a side stream, as graph capture requires
-            for _ in range(2):
-                self._chunk_step(layer, statics[0], records)
-        torch.cuda.current_stream().wait_stream(side)
-        torch.cuda.synchronize(cfg.device)
-        # two graphs, one per input buffer (the copy of the next chunk overlaps the replay of this one); they are
-        # replayed one after the other on one stream, so they can share the memory of their intermediates
-        graphs = []
-        for k in range(2):
+        statics = [torch.zeros(1, cfg.chunk_len, cfg.d_model, device=cfg.device, dtype=dtype) for _ in range(4)]
+        # Two lanes, each a stream of priority -2 with its own record slot and memory for the intermediates: chunk i+1
+        # starts on the other lane while chunk i is still running, so its GEMM (compute bound) runs beside the
+        # attention and the row scatter of chunk i (memory and latency bound).  Each lane has two graphs, one per
+        # static input, used in turn (chunk i: lane i % 2, graph and input i % 4), so that the copy of a chunk can run
+        # two chunks ahead; the two graphs of a lane never overlap and share the lane's memory.
+        # Priorities: the layer forks its key/value GEMM onto a stream one level below the caller's, and the copy of
+        # the next chunk runs at priority 0; captured kernel nodes keep the priority of the stream they came from.
+        # So the short selection kernels of the main line take SMs as GEMM blocks retire instead of queueing behind
+        # all of them, and the GEMM in turn is not held up by the copy.
+        lanes = [torch.cuda.Stream(device=cfg.device, priority=-2) for _ in range(2)]
+        graphs: List[Any] = [None] * 4
+        for k in range(4):
+            lane = k % 2
+            records.use_lane(lane)
+            if k < 2:
+                lanes[lane].wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(lanes[lane]):  # eager warm-up on a side stream, as graph capture requires
+                    for _ in range(2):
+                        self._chunk_step(layer, statics[k], records)
+                torch.cuda.current_stream().wait_stream(lanes[lane])
+                torch.cuda.synchronize(cfg.device)
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, pool=graphs[0].pool() if graphs else None):
+            with torch.cuda.graph(g, pool=graphs[lane].pool() if k >= 2 else None, stream=lanes[lane]):
                 self._chunk_step(layer, statics[k], records)
-            graphs.append(g)
-        cache[key] = (graphs, statics)
+            graphs[k] = g
+        records.use_lane(0)
+        cache[key] = (graphs, statics, lanes)
         return cache[key]
 
     def _final_replay(self, layer: AdaptiveSparseAttention, reduced: torch.Tensor) -> torch.Tensor:
@@ -354,7 +376,7 @@ class ChunkedShortlistRunner:
         if key not in cache:
             static_in = torch.empty_like(reduced)
             static_in.copy_(reduced)
-            side = torch.cuda.Stream(device=reduced.device)
+            side = torch.cuda.Stream(device=reduced.device, priority=-2)   # see _chunk_graph
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
                 for _ in range(2):
@@ -362,7 +384,7 @@ class ChunkedShortlistRunner:
             torch.cuda.current_stream().wait_stream(side)
             torch.cuda.synchronize(reduced.device)
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
+            with torch.cuda.graph(g, stream=side):
                 static_out = layer(static_in)
             cache[key] = (g, static_in, static_out, layer.__dict__.get("_pending"))
         g, static_in, static_out, ctx = cache[key]
@@ -476,17 +498,29 @@ class ChunkedShortlistRunner:
         graph = self._chunk_graph(chunk_model, base_dtype, records) if cfg.use_cuda_graph else None
         feeder = _ChunkFeeder(source, source_off, device, cfg.chunk_len, targets=graph[1] if graph is not None else None)
         records.reset(c_lo, cfg.chunk_len)  # after a possible capture, whose warm-up calls wrote into slot 0
+        main = torch.cuda.current_stream()
+        lanes = graph[2] if graph is not None else [main]
+        for lane in lanes:
+            if lane is not main:
+                lane.wait_stream(main)
         for i, (start, end) in enumerate(bounds):
-            xc = feeder.get(i, start, end, bounds[i + 1] if i + 1 < len(bounds) else None)
-            records.slot.fill_(i)
-            if graph is not None and end - start == cfg.chunk_len:
-                graph[0][i % 2].replay()   # xc is the static input of that graph
-            else:
-                self._chunk_step(chunk_model, xc, records)
-            if pool is not None:
-                ops.gather_rows(xc[0], (rec_idx[i] - start).clamp_(min=0), rec_count[i:i + 1], budget,
-                                out=pool[i * budget:(i + 1) * budget])
-            feeder.done(i)
+            k = i % len(lanes)
+            records.use_lane(k)
+            with torch.cuda.stream(lanes[k]):
+                xc = feeder.get(i, bounds)
+                records.slot.fill_(i)
+                if graph is not None and end - start == cfg.chunk_len:
+                    graph[0][i % len(graph[0])].replay()   # xc is the static input of that graph
+                else:
+                    self._chunk_step(chunk_model, xc, records)
+                if pool is not None:
+                    ops.gather_rows(xc[0], (rec_idx[i] - start).clamp_(min=0), rec_count[i:i + 1], budget,
+                                    out=pool[i * budget:(i + 1) * budget])
+                feeder.done(i)
+        records.use_lane(0)
+        for lane in lanes:
+            if lane is not main:
+                main.wait_stream(lane)
 
         # exchange: every rank ends up with the records of all chunks, in chunk order
         all_scores, all_idx, all_count = dist_utils.all_gather_records(self.group, rec_scores, rec_idx, rec_count,

@@ -144,6 +144,86 @@ __device__ __forceinline__ void load_vec<int8_t>(const int8_t* p, float (&o)[8])
   for (int i = 0; i < 8; ++i) o[i] = (float)b[i];
 }
 
+// The candidate list of one packed row as a function of the slot number: an explicit table row, the pieces of a
+// structural plan (window, strided anchors, prototype picks, with the duplicates the reference's dedup removes
+// skipped), or the causal / masked prefix.
+struct RowCands {
+  const int64_t* cand_row;
+  const int32_t* plist;
+  int t, Tn, n_loc, loc_start, n_anchor, n_anchor_true, n_proto, n_virtual, v_begin, astride, j0;
+  bool explicit_c, planned, anchor_clamps, anchors_done;
+
+  __device__ __forceinline__ void init(const AttnParams& p, int bh, int64_t grow, int t_, int start, int cnt) {
+    t = t_; Tn = p.T;
+    explicit_c = p.cand != nullptr;
+    planned = !explicit_c && p.has_plan;
+    n_loc = 0; loc_start = 0; n_anchor = 0; n_anchor_true = 0; n_proto = 0; n_virtual = 0; v_begin = 0;
+    plist = nullptr; cand_row = nullptr;
+    astride = 1; j0 = 0;
+    anchor_clamps = false;
+    anchors_done = p.anchors_done != 0;
+    if (explicit_c) {
+      long long len = p.cand_len[grow];
+      n_virtual = (int)max(1LL, min(len, (long long)p.L));
+      cand_row = p.cand + grow * p.L;
+    } else if (planned) {
+      n_loc = p.plan.window > 0 ? min(t + 1, p.plan.window) : 1;
+      loc_start = t - n_loc + 1;
+      astride = max(1, p.plan.anchor_stride);
+      n_anchor = p.plan.anchor_stride > 0 ? p.plan.anchor_slots : 0;
+      j0 = t / astride + 1;  // first anchor slot that clamps to key 0
+      anchor_clamps = n_anchor > 0 && (t - (long long)n_anchor * astride) < 0;
+      n_anchor_true = n_anchor;
+      if (anchors_done && n_anchor > 0) n_anchor = 1;  // only the slot that clamps to key 0 is left to this pass
+      if (p.plan.proto_cap > 0 && p.plan.proto_lists != nullptr) {
+        const int b = bh / p.H;
+        const int nblk = (Tn + p.plan.proto_block - 1) / p.plan.proto_block;
+        plist = p.plan.proto_lists + ((int64_t)b * nblk + t / p.plan.proto_block) * p.plan.proto_list_stride;
+        n_proto = p.plan.proto_limit[(int64_t)b * Tn + t];
+      }
+      n_virtual = n_loc + n_anchor + n_proto;
+      v_begin = p.extras_only ? n_loc : 0;
+    } else {
+      const int max_tok = p.token_idx[start + cnt - 1];
+      n_virtual = p.add_mask ? max_tok + 1 : t + 1;
+    }
+  }
+
+  // key index of slot c (< n_virtual), or -1 for a slot that holds nothing
+  __device__ __forceinline__ int index_of(int c) const {
+    if (explicit_c) {
+      const long long raw = cand_row[c];
+      return (int)min(max(raw, 0LL), (long long)Tn - 1);
+    }
+    if (!planned) return c;
+    if (c < n_loc) return loc_start + c;
+    if (c < n_loc + n_anchor) {
+      // after the anchor tile pass the one slot left here is the slot that clamps to key 0, if the row has it
+      const int j = anchors_done ? j0 : c - n_loc + 1;
+      if (j <= n_anchor_true) {
+        const long long a = (long long)t - (long long)j * astride;
+        if (a >= 0) {
+          if (a < loc_start) return (int)a;
+        } else if (j == j0 && (t % astride) != 0 && loc_start > 0) {
+          return 0;
+        }
+      }
+      return -1;
+    }
+    const int u = plist[c - n_loc - n_anchor];
+    if (u >= 0 && u < loc_start) {
+      bool is_anchor = false;
+      if (n_anchor_true > 0) {
+        const int dlt = t - u;
+        if (dlt % astride == 0 && dlt / astride >= 1 && dlt / astride <= n_anchor_true) is_anchor = true;
+        if (u == 0 && anchor_clamps) is_anchor = true;
+      }
+      if (!is_anchor) return u;
+    }
+    return -1;
+  }
+};
+
 // kVec: head_dim / VecElems is a power of two <= 32, so LPR = that many lanes cover one value row with one vector
 // load each and 32 / LPR candidates are accumulated per step; otherwise lanes stride over the channels one by one.
 template <typename T, bool kVec>
@@ -172,37 +252,9 @@ __global__ void __launch_bounds__(GEN_WARPS * 32) attn_rows_kernel(const AttnPar
     vscale = p.v_scale[bh];
   }
 
-  // virtual candidate space
-  const bool explicit_c = p.cand != nullptr;
-  const bool planned = !explicit_c && p.has_plan;
-  int n_loc = 0, loc_start = 0, n_anchor = 0, n_anchor_true = 0, n_proto = 0, n_virtual = 0, v_begin = 0;
-  const int32_t* plist = nullptr;
-  int astride = 1, j0 = 0;
-  bool anchor_clamps = false;
-  if (explicit_c) {
-    long long len = p.cand_len[grow];
-    n_virtual = (int)max(1LL, min(len, (long long)p.L));
-  } else if (planned) {
-    n_loc = p.plan.window > 0 ? min(t + 1, p.plan.window) : 1;
-    loc_start = t - n_loc + 1;
-    astride = max(1, p.plan.anchor_stride);
-    n_anchor = p.plan.anchor_stride > 0 ? p.plan.anchor_slots : 0;
-    j0 = t / astride + 1;  // first anchor slot that clamps to key 0
-    anchor_clamps = n_anchor > 0 && (t - (long long)n_anchor * astride) < 0;
-    n_anchor_true = n_anchor;
-    if (p.anchors_done && n_anchor > 0) n_anchor = 1;  // only the slot that clamps to key 0 is left to this pass
-    if (p.plan.proto_cap > 0 && p.plan.proto_lists != nullptr) {
-      const int b = bh / p.H;
-      const int nblk = (Tn + p.plan.proto_block - 1) / p.plan.proto_block;
-      plist = p.plan.proto_lists + ((int64_t)b * nblk + t / p.plan.proto_block) * p.plan.proto_list_stride;
-      n_proto = p.plan.proto_limit[(int64_t)b * Tn + t];
-    }
-    n_virtual = n_loc + n_anchor + n_proto;
-    v_begin = p.extras_only ? n_loc : 0;
-  } else {
-    const int max_tok = p.token_idx[start + cnt - 1];
-    n_virtual = p.add_mask ? max_tok + 1 : t + 1;
-  }
+  RowCands rc;
+  rc.init(p, bh, grow, t, start, cnt);
+  const int n_virtual = rc.n_virtual, v_begin = rc.v_begin;
 
   float m = -INFINITY, l = 0.f;
   float acc[GEN_MAXD / 32];
@@ -215,41 +267,7 @@ __global__ void __launch_bounds__(GEN_WARPS * 32) attn_rows_kernel(const AttnPar
 
   for (int c0 = v_begin; c0 < n_virtual; c0 += 32) {
     const int c = c0 + lane;
-    int idx = -1;
-    if (c < n_virtual) {
-      if (explicit_c) {
-        long long raw = p.cand[grow * p.L + c];
-        idx = (int)min(max(raw, 0LL), (long long)Tn - 1);
-      } else if (planned) {
-        if (c < n_loc) {
-          idx = loc_start + c;
-        } else if (c < n_loc + n_anchor) {
-          // after the anchor tile pass the one slot left here is the slot that clamps to key 0, if the row has it
-          const int j = p.anchors_done ? j0 : c - n_loc + 1;
-          if (j <= n_anchor_true) {
-            const long long a = (long long)t - (long long)j * astride;
-            if (a >= 0) {
-              if (a < loc_start) idx = (int)a;
-            } else if (j == j0 && (t % astride) != 0 && loc_start > 0) {
-              idx = 0;
-            }
-          }
-        } else {
-          const int u = plist[c - n_loc - n_anchor];
-          if (u >= 0 && u < loc_start) {
-            bool is_anchor = false;
-            if (n_anchor_true > 0) {
-              const int dlt = t - u;
-              if (dlt % astride == 0 && dlt / astride >= 1 && dlt / astride <= n_anchor_true) is_anchor = true;
-              if (u == 0 && anchor_clamps) is_anchor = true;
-            }
-            if (!is_anchor) idx = u;
-          }
-        }
-      } else {
-        idx = c;
-      }
-    }
+    const int idx = c < n_virtual ? rc.index_of(c) : -1;
     float s = -INFINITY;
     if (idx >= 0) {
       // one key row per lane (sharing a row between lanes and reducing with shuffles was measured 20-40 % slower)
@@ -350,6 +368,158 @@ __global__ void __launch_bounds__(GEN_WARPS * 32) attn_rows_kernel(const AttnPar
       const int d = lane + 32 * i;
       if (d < D) store_out(p, ob + d, acc[i] * inv * vscale);
     }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// row kernel for head_dim 64 in bf16 or int8
+// ------------------------------------------------------------------------------------------------
+// Same work split as attn_rows_kernel (one warp per row, 32 candidates per step, one key per lane), but the key rows
+// reach the lanes through shared memory: eight lanes copy one row with cp.async (four rows per instruction, whole
+// 128-byte lines), and each lane then reads its own row from a padded tile.  A lane that loads its own row straight
+// from global memory touches 32 different lines per instruction, eight instructions per step; measured, that kept
+// the L1 tag stage near 80 % busy with DRAM at 27 %.  The copy of the next step's keys is started as soon as the
+// scores of this step are in registers, so it overlaps the value accumulation.  q sits in registers as packed
+// bf16 pairs (int8: packed bytes, dp4a — the integer dot is exact either way).
+constexpr int R64_PITCH_PAD = 16;
+
+template <typename T>
+__device__ __forceinline__ void r64_issue_keys(const T* kh, int64_t k_ts, int idx, unsigned char* tile, int grp, int sub) {
+  constexpr int ROWB = 64 * sizeof(T), PITCH = ROWB + R64_PITCH_PAD, CH = ROWB / 8;   // bytes per lane per row
+#pragma unroll
+  for (int st = 0; st < 8; ++st) {
+    const int row = st * 4 + grp;
+    const int ic = max(__shfl_sync(0xffffffffu, idx, row), 0);   // a dead slot copies key 0; its score is masked
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(tile + row * PITCH + sub * CH);
+    const T* src = kh + (int64_t)ic * k_ts + sub * (CH / (int)sizeof(T));
+    if (CH == 16) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+    else asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
+  }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+}
+
+template <typename T>
+__global__ void __launch_bounds__(GEN_WARPS * 32, 4) attn_rows64_kernel(const AttnParams p) {
+  constexpr int ROWB = 64 * sizeof(T), PITCH = ROWB + R64_PITCH_PAD, WARP_BYTES = 32 * PITCH + ROWB;
+  extern __shared__ __align__(16) unsigned char r64_smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bh = blockIdx.y;
+  const int start = p.row_offsets[bh];
+  const int cnt = p.row_offsets[bh + 1] - start;
+  const int r = blockIdx.x * GEN_WARPS + warp;
+  if (r >= cnt) return;
+  const int64_t grow = (int64_t)start + r;
+  const int t = p.token_idx[grow];
+  const int Tn = p.T;
+  const T* qh = reinterpret_cast<const T*>(p.q) + ((int64_t)bh * Tn + t) * 64;
+  const T* kh = reinterpret_cast<const T*>(p.k) + (bh / p.H) * p.kv.k_batch + (bh % p.H) * p.kv.k_head;
+  const T* vh = reinterpret_cast<const T*>(p.v) + (bh / p.H) * p.kv.v_batch + (bh % p.H) * p.kv.v_head;
+  const int64_t k_ts = p.kv.k_token, v_ts = p.kv.v_token;
+  unsigned char* tile = r64_smem + warp * WARP_BYTES;
+  const uint4* qrow = reinterpret_cast<const uint4*>(tile + 32 * PITCH);   // the row's q, read as broadcasts
+  if (lane < ROWB / 16) reinterpret_cast<uint4*>(tile + 32 * PITCH)[lane] = reinterpret_cast<const uint4*>(qh)[lane];
+  __syncwarp();
+  float sc = p.scale;
+  float vscale = 1.f;
+  if (sizeof(T) == 1) {
+    sc *= p.q_scale[bh] * p.k_scale[bh];
+    vscale = p.v_scale[bh];
+  }
+  RowCands rc;
+  rc.init(p, bh, grow, t, start, cnt);
+  const int n_virtual = rc.n_virtual;
+
+  float m = -INFINITY, l = 0.f;
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  const int grp = lane >> 3, sub = lane & 7;
+
+  int idx = rc.v_begin + lane < n_virtual ? rc.index_of(rc.v_begin + lane) : -1;
+  if (rc.v_begin < n_virtual) r64_issue_keys<T>(kh, k_ts, idx, tile, grp, sub);
+  for (int c0 = rc.v_begin; c0 < n_virtual; c0 += 32) {
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncwarp();
+    float s = -INFINITY;
+    {
+      const uint4* krow = reinterpret_cast<const uint4*>(tile + lane * PITCH);
+      if (sizeof(T) == 2) {
+        float a = 0.f;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint4 raw = krow[c], qraw = qrow[c];
+          const uint32_t kw[4] = {raw.x, raw.y, raw.z, raw.w}, qw[4] = {qraw.x, qraw.y, qraw.z, qraw.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {   // bf16 -> fp32 is a 16-bit shift; same product order as dot_row
+            a = fmaf(__uint_as_float(kw[i] << 16), __uint_as_float(qw[i] << 16), a);
+            a = fmaf(__uint_as_float(kw[i] & 0xffff0000u), __uint_as_float(qw[i] & 0xffff0000u), a);
+          }
+        }
+        if (idx >= 0) s = a * sc;
+      } else {
+        int a = 0;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const uint4 raw = krow[c], qraw = qrow[c];
+          a = __dp4a((int)raw.x, (int)qraw.x, a);
+          a = __dp4a((int)raw.y, (int)qraw.y, a);
+          a = __dp4a((int)raw.z, (int)qraw.z, a);
+          a = __dp4a((int)raw.w, (int)qraw.w, a);
+        }
+        if (idx >= 0) s = (float)a * sc;
+      }
+    }
+    __syncwarp();   // every lane has read its row: the tile may take the next step's keys
+    const int idx_cur = idx;
+    if (c0 + 32 < n_virtual) {
+      idx = c0 + 32 + lane < n_virtual ? rc.index_of(c0 + 32 + lane) : -1;
+      r64_issue_keys<T>(kh, k_ts, idx, tile, grp, sub);
+    }
+    const float m_new = fmaxf(m, warp_max(s));
+    if (m_new == -INFINITY) continue;  // nothing valid yet (warp-uniform)
+    const float pr = (s == -INFINITY) ? 0.f : __expf(s - m_new);
+    const float corr = (m == -INFINITY) ? 0.f : __expf(m - m_new);
+    l = l * corr + warp_sum(pr);
+    m = m_new;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] *= corr;
+    // eight steps of four candidates, branch-free: eight independent value loads in flight (dead: weight 0, row 0)
+#pragma unroll
+    for (int st = 0; st < 8; ++st) {
+      const float pc = __shfl_sync(0xffffffffu, pr, st * 4 + grp);
+      const int ic = max(__shfl_sync(0xffffffffu, idx_cur, st * 4 + grp), 0);
+      float vv[8];
+      load_vec<T>(vh + (int64_t)ic * v_ts + sub * 8, vv);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = fmaf(pc, vv[e], acc[e]);
+    }
+  }
+#pragma unroll
+  for (int off = 8; off < 32; off <<= 1) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], off);
+  }
+  const int64_t ob = out_row_base(p, bh, t);
+  if (p.extras_only) {
+    const float m1 = p.ws_m[grow], l1 = p.ws_l[grow];
+    const float mm = fmaxf(m, m1);
+    const float c1 = (m1 == -INFINITY) ? 0.f : __expf(m1 - mm);
+    const float c2 = (m == -INFINITY) ? 0.f : __expf(m - mm);
+    const float lt = l1 * c1 + l * c2;
+    const float inv = lt > 0.f ? 1.f / lt : 0.f;
+    if (lane < 8) {   // the window pass stores raw P.V (no value scale); acc here is raw too
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const int d = sub * 8 + e;
+        store_out(p, ob + d, (p.ws_o[grow * 64 + d] * c1 + acc[e] * c2) * inv * vscale);
+      }
+    }
+    return;
+  }
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+  if (lane < 8) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) store_out(p, ob + sub * 8 + e, acc[e] * inv * vscale);
   }
 }
 
@@ -768,8 +938,21 @@ extern "C" int64_t aspa_attn_workspace_bytes(int64_t total_rows, int D) {
 }
 
 template <typename T>
+static void launch_rows64(const AttnParams& p, dim3 grid, cudaStream_t st) {
+  constexpr int ROWB = 64 * (int)sizeof(T);
+  constexpr int smem = GEN_WARPS * (32 * (ROWB + R64_PITCH_PAD) + ROWB);
+  attn_rows64_kernel<T><<<grid, GEN_WARPS * 32, smem, st>>>(p);
+}
+template <>
+void launch_rows64<float>(const AttnParams&, dim3, cudaStream_t) {}
+
+template <typename T>
 static void launch_generic(const AttnParams& p, int max_rows, cudaStream_t st) {
   const dim3 grid((unsigned)ceil_div(max_rows, GEN_WARPS), p.heads);
+  if (sizeof(T) <= 2 && p.D == 64 && p.add_mask == nullptr) {
+    launch_rows64<T>(p, grid, st);
+    return;
+  }
   constexpr int VE = VecElems<T>::n;
   const int lpr = p.D % VE == 0 ? p.D / VE : 0;
   const bool vec = lpr >= 1 && lpr <= 32 && (lpr & (lpr - 1)) == 0;

@@ -258,11 +258,13 @@ __global__ void __launch_bounds__(256) rope_rows_q_kernel(const T* __restrict__ 
 
 // RoPE in place: row r (H*D wide, rows `row_stride` elements apart) is rotated at position r % Tn.
 // One thread per 16-byte vector, consecutive threads on consecutive vectors of a row.
+// With `heads_out` the rotated rows go there instead, head-major ((r / Tn) * H + h, r % Tn, D): the same bytes moved,
+// and the keys of one head at consecutive positions become one contiguous run.
 template <typename T>
 __global__ void __launch_bounds__(256) rope_inplace_kernel(T* __restrict__ x, int64_t n_rows, int Tn,
                                                            int64_t row_stride, int H, int D,
                                                            const float* __restrict__ cos_t,
-                                                           const float* __restrict__ sin_t) {
+                                                           const float* __restrict__ sin_t, T* __restrict__ heads_out) {
   constexpr int E = 16 / sizeof(T);
   const int C = H * D, half = D / 2;
   const int vec_per_row = C / E;
@@ -291,7 +293,8 @@ __global__ void __launch_bounds__(256) rope_inplace_kernel(T* __restrict__ x, in
       f[2] = rope_mix(e1, c2.y, -o1, s2.y, false);
       f[3] = rope_mix(o1, c2.y, e1, s2.y, false);
     }
-    *reinterpret_cast<uint4*>(ptr) = raw;
+    T* dst = heads_out ? heads_out + (((r / Tn) * H + ch / D) * (int64_t)Tn + t) * D + d0 : ptr;
+    *reinterpret_cast<uint4*>(dst) = raw;
   }
 }
 
@@ -464,7 +467,13 @@ extern "C" int aspa_scatter_rows_fill(const void* src, const int32_t* slot_of, c
 
 extern "C" int aspa_rope_inplace(void* x, int dtype, int64_t n_rows, int T, int64_t row_stride, int H, int D,
                                  const float* cos_t, const float* sin_t, void* stream) {
+  return aspa_rope_rows_to_heads(x, dtype, n_rows, T, row_stride, H, D, cos_t, sin_t, nullptr, stream);
+}
+
+extern "C" int aspa_rope_rows_to_heads(void* x, int dtype, int64_t n_rows, int T, int64_t row_stride, int H, int D,
+                                       const float* cos_t, const float* sin_t, void* heads_out, void* stream) {
   ASPA_CHECK_ARG(x && cos_t && sin_t, "null pointer");
+  ASPA_CHECK_ARG(heads_out == nullptr || n_rows % T == 0, "head-major output needs whole sequences");
   ASPA_CHECK_ARG(n_rows >= 0 && T > 0 && H > 0 && D > 0 && D % 2 == 0 && row_stride >= (int64_t)H * D, "bad sizes");
   ASPA_CHECK_ARG(dtype == ASPA_F32 || dtype == ASPA_BF16, "dtype must be fp32 or bf16");
   const int E = dtype == ASPA_BF16 ? 8 : 4;
@@ -474,9 +483,10 @@ extern "C" int aspa_rope_inplace(void* x, int dtype, int64_t n_rows, int T, int6
   const unsigned blocks = (unsigned)std::min<int64_t>(ceil_div(total, 256), 148 * 32);
   if (dtype == ASPA_BF16)
     rope_inplace_kernel<__nv_bfloat16><<<blocks, 256, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)x, n_rows, T, row_stride, H, D,
-                                                                                 cos_t, sin_t);
+                                                                                 cos_t, sin_t, (__nv_bfloat16*)heads_out);
   else
-    rope_inplace_kernel<float><<<blocks, 256, 0, (cudaStream_t)stream>>>((float*)x, n_rows, T, row_stride, H, D, cos_t, sin_t);
+    rope_inplace_kernel<float><<<blocks, 256, 0, (cudaStream_t)stream>>>((float*)x, n_rows, T, row_stride, H, D, cos_t, sin_t,
+                                                                (float*)heads_out);
   ASPA_CHECK_LAUNCH();
   return ASPA_OK;
 }

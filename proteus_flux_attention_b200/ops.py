@@ -419,12 +419,14 @@ def scatter_rows_fill(src2d: torch.Tensor, slot_of: torch.Tensor, mask_u8: torch
 
 
 def rope_inplace(x_rows: torch.Tensor, n_rows: int, T: int, row_stride: int, H: int, D: int, cos: torch.Tensor,
-                 sin: torch.Tensor) -> None:
-    """Rotate, in place, ``n_rows`` rows of H*D elements that start at ``x_rows`` and lie ``row_stride`` elements apart."""
+                 sin: torch.Tensor, heads_out: Optional[torch.Tensor] = None) -> None:
+    """Rotate ``n_rows`` rows of H*D elements that start at ``x_rows`` and lie ``row_stride`` elements apart: in
+    place, or into ``heads_out`` (n_rows / T * H, T, D) when given."""
     e = x_rows.element_size()
     with _timed('rope_inplace', 1, 2 * n_rows * H * D * e):
-        N.check(N.lib().aspa_rope_inplace(N.ptr(x_rows), N.dtype_code(x_rows.dtype), int(n_rows), int(T), int(row_stride),
-                                          H, D, N.ptr(cos), N.ptr(sin), N.stream()), "rope_inplace")
+        N.check(N.lib().aspa_rope_rows_to_heads(N.ptr(x_rows), N.dtype_code(x_rows.dtype), int(n_rows), int(T),
+                                                int(row_stride), H, D, N.ptr(cos), N.ptr(sin), N.ptr(heads_out),
+                                                N.stream()), "rope_rows_to_heads")
 
 
 TOKEN_COMPACT_MAX_T = 65536  # ASPA_TOKEN_COMPACT_MAX_T of the C header
