@@ -328,29 +328,44 @@ class ChunkedShortlistRunner:
             layer.after_token_keep = None
         records.join()
 
-    def _chunk_graph(self, layer: AdaptiveSparseAttention, dtype: torch.dtype, records: _Pass1Records):
-        """(graphs, static inputs) for one full chunk of pass 1.  The layer call is launch-bound (about 45 small
-        launches around two GEMMs), so replaying a captured graph removes the host from the loop.  Capture needs a
-        call that never waits for the host, which holds for the chunk layer (alpha = 1, no keep threshold).  The
-        promotion of the chunk is part of the graph; it finds its record slot in device memory."""
+    def _chunk_graph(self, layer: AdaptiveSparseAttention, dtype: torch.dtype, records: _Pass1Records,
+                     resident: Optional[List[torch.Tensor]] = None):
+        """(graphs, static inputs, lanes) for the full chunks of pass 1.  The layer call is launch-bound (about 45
+        small launches around two GEMMs), so replaying a captured graph removes the host from the loop.  Capture needs
+        a call that never waits for the host, which holds for the chunk layer (alpha = 1, no keep threshold).  The
+        promotion of the chunk is part of the graph; it finds its record slot in device memory.
+
+        A host sequence goes through a ring of four static inputs (chunk i: input and graph i % 4).  For a sequence
+        that is resident in HBM, ``resident`` lists its chunks and every chunk gets a graph of its own that reads the
+        chunk where it lies (static inputs: None): copying 128 MiB per chunk into a static input costs a sixth of the
+        chunk's memory traffic, and at the lowest priority, beside two chunks in flight, the copy became the slowest
+        stage.  Those graphs are valid for that address only; a sequence at another address is captured afresh."""
         cfg = self.config
-        key = ("graph", cfg.chunk_len, dtype, cfg.pass1_full_forward, id(records))
         cache = self._layer_cache if self._layer_cache is not None else self.__dict__.setdefault("_graph_tmp", {})
-        if key in cache:
-            return cache[key]
-        statics = [torch.zeros(1, cfg.chunk_len, cfg.d_model, device=cfg.device, dtype=dtype) for _ in range(4)]
+        if resident is not None:
+            key = ("graph_resident", cfg.chunk_len, dtype, cfg.pass1_full_forward, id(records))
+            signature = tuple(int(t.data_ptr()) for t in resident)
+            if key in cache and cache[key][3] == signature:
+                return cache[key]
+            cache.pop(key, None)
+            statics = list(resident)
+        else:
+            key = ("graph", cfg.chunk_len, dtype, cfg.pass1_full_forward, id(records))
+            signature = None
+            if key in cache:
+                return cache[key]
+            statics = [torch.zeros(1, cfg.chunk_len, cfg.d_model, device=cfg.device, dtype=dtype) for _ in range(4)]
         # Two lanes, each a stream of priority -2 with its own record slot and memory for the intermediates: chunk i+1
         # starts on the other lane while chunk i is still running, so its GEMM (compute bound) runs beside the
-        # attention and the row scatter of chunk i (memory and latency bound).  Each lane has two graphs, one per
-        # static input, used in turn (chunk i: lane i % 2, graph and input i % 4), so that the copy of a chunk can run
-        # two chunks ahead; the two graphs of a lane never overlap and share the lane's memory.
+        # attention and the row scatter of chunk i (memory and latency bound).  Graph k runs on lane k % 2; the graphs
+        # of a lane never overlap and share the lane's memory.  With the ring the copy of a chunk runs two chunks ahead.
         # Priorities: the layer forks its key/value GEMM onto a stream one level below the caller's, and the copy of
         # the next chunk runs at priority 0; captured kernel nodes keep the priority of the stream they came from.
         # So the short selection kernels of the main line take SMs as GEMM blocks retire instead of queueing behind
         # all of them, and the GEMM in turn is not held up by the copy.
         lanes = [torch.cuda.Stream(device=cfg.device, priority=-2) for _ in range(2)]
-        graphs: List[Any] = [None] * 4
-        for k in range(4):
+        graphs: List[Any] = [None] * len(statics)
+        for k in range(len(statics)):
             lane = k % 2
             records.use_lane(lane)
             if k < 2:
@@ -365,7 +380,7 @@ class ChunkedShortlistRunner:
                 self._chunk_step(layer, statics[k], records)
             graphs[k] = g
         records.use_lane(0)
-        cache[key] = (graphs, statics, lanes)
+        cache[key] = (graphs, statics if resident is None else None, lanes, signature)
         return cache[key]
 
     def _final_replay(self, layer: AdaptiveSparseAttention, reduced: torch.Tensor) -> torch.Tensor:
@@ -495,7 +510,12 @@ class ChunkedShortlistRunner:
         t0 = time.perf_counter()
         ev_a.record()
         bounds = [(c * cfg.chunk_len, min(cfg.seq_len, (c + 1) * cfg.chunk_len)) for c in range(c_lo, c_hi)]
-        graph = self._chunk_graph(chunk_model, base_dtype, records) if cfg.use_cuda_graph else None
+        graph = None
+        if cfg.use_cuda_graph:
+            resident = None
+            if source.is_cuda and source.is_contiguous():
+                resident = [source[:, s - source_off:e - source_off] for s, e in bounds if e - s == cfg.chunk_len]
+            graph = self._chunk_graph(chunk_model, base_dtype, records, resident)
         feeder = _ChunkFeeder(source, source_off, device, cfg.chunk_len, targets=graph[1] if graph is not None else None)
         records.reset(c_lo, cfg.chunk_len)  # after a possible capture, whose warm-up calls wrote into slot 0
         main = torch.cuda.current_stream()
