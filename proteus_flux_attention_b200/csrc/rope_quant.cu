@@ -257,7 +257,6 @@ __global__ void __launch_bounds__(256) rope_rows_q_kernel(const T* __restrict__ 
 }
 
 // RoPE in place: row r (H*D wide, rows `row_stride` elements apart) is rotated at position r % Tn.
-// One thread per 16-byte vector, consecutive threads on consecutive vectors of a row.
 // With `heads_out` the rotated rows go there instead, head-major ((r / Tn) * H + h, r % Tn, D): the same bytes moved,
 // and the keys of one head at consecutive positions become one contiguous run.
 template <typename T>
@@ -265,36 +264,56 @@ __global__ void __launch_bounds__(256) rope_inplace_kernel(T* __restrict__ x, in
                                                            int64_t row_stride, int H, int D,
                                                            const float* __restrict__ cos_t,
                                                            const float* __restrict__ sin_t, T* __restrict__ heads_out) {
+  // One thread per (row, 16-byte vector of a head): it loads its cos/sin factors once and walks over the heads,
+  // HB heads per step so that HB loads are in flight.  Consecutive threads take consecutive vectors of one head
+  // (whole 128-byte lines for head_dim 64 in bf16).
   constexpr int E = 16 / sizeof(T);
-  const int C = H * D, half = D / 2;
-  const int vec_per_row = C / E;
-  const int64_t total = n_rows * vec_per_row;
+  constexpr int HB = 8;
+  const int half = D / 2, vec_per_head = D / E;
+  const int64_t total = n_rows * vec_per_head;
   for (int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; g < total; g += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t r = g / vec_per_row;
-    const int ch = (int)(g % vec_per_row) * E;
+    const int64_t r = g / vec_per_head;
+    const int d0 = (int)(g % vec_per_head) * E;
     const int t = (int)(r % Tn);
-    const int d0 = ch % D;
-    T* ptr = x + r * row_stride + ch;
-    uint4 raw = *reinterpret_cast<const uint4*>(ptr);
     const float* cr = cos_t + (int64_t)t * half + d0 / 2;
     const float* sr = sin_t + (int64_t)t * half + d0 / 2;
+    float c[4], sn[4];
     if (sizeof(T) == 2) {
       const float4 c4 = *reinterpret_cast<const float4*>(cr), s4 = *reinterpret_cast<const float4*>(sr);
-      raw.x = rope_word_bf16(raw.x, c4.x, s4.x);
-      raw.y = rope_word_bf16(raw.y, c4.y, s4.y);
-      raw.z = rope_word_bf16(raw.z, c4.z, s4.z);
-      raw.w = rope_word_bf16(raw.w, c4.w, s4.w);
+      c[0] = c4.x; c[1] = c4.y; c[2] = c4.z; c[3] = c4.w;
+      sn[0] = s4.x; sn[1] = s4.y; sn[2] = s4.z; sn[3] = s4.w;
     } else {
-      float* f = reinterpret_cast<float*>(&raw);
       const float2 c2 = *reinterpret_cast<const float2*>(cr), s2 = *reinterpret_cast<const float2*>(sr);
-      const float e0 = f[0], o0 = f[1], e1 = f[2], o1 = f[3];
-      f[0] = rope_mix(e0, c2.x, -o0, s2.x, false);
-      f[1] = rope_mix(o0, c2.x, e0, s2.x, false);
-      f[2] = rope_mix(e1, c2.y, -o1, s2.y, false);
-      f[3] = rope_mix(o1, c2.y, e1, s2.y, false);
+      c[0] = c2.x; c[1] = c2.y; sn[0] = s2.x; sn[1] = s2.y;
+      c[2] = c[3] = sn[2] = sn[3] = 0.f;
     }
-    T* dst = heads_out ? heads_out + (((r / Tn) * H + ch / D) * (int64_t)Tn + t) * D + d0 : ptr;
-    *reinterpret_cast<uint4*>(dst) = raw;
+    T* src = x + r * row_stride + d0;
+    T* dst = heads_out ? heads_out + ((r / Tn) * H * (int64_t)Tn + t) * D + d0 : src;
+    const int64_t dst_head = heads_out ? (int64_t)Tn * D : (int64_t)D;
+    for (int h0 = 0; h0 < H; h0 += HB) {
+      uint4 raw[HB];
+#pragma unroll
+      for (int i = 0; i < HB; ++i)
+        if (h0 + i < H) raw[i] = *reinterpret_cast<const uint4*>(src + (int64_t)(h0 + i) * D);
+#pragma unroll
+      for (int i = 0; i < HB; ++i) {
+        if (h0 + i >= H) break;
+        if (sizeof(T) == 2) {
+          raw[i].x = rope_word_bf16(raw[i].x, c[0], sn[0]);
+          raw[i].y = rope_word_bf16(raw[i].y, c[1], sn[1]);
+          raw[i].z = rope_word_bf16(raw[i].z, c[2], sn[2]);
+          raw[i].w = rope_word_bf16(raw[i].w, c[3], sn[3]);
+        } else {
+          float* f = reinterpret_cast<float*>(&raw[i]);
+          const float e0 = f[0], o0 = f[1], e1 = f[2], o1 = f[3];
+          f[0] = rope_mix(e0, c[0], -o0, sn[0], false);
+          f[1] = rope_mix(o0, c[0], e0, sn[0], false);
+          f[2] = rope_mix(e1, c[1], -o1, sn[1], false);
+          f[3] = rope_mix(o1, c[1], e1, sn[1], false);
+        }
+        *reinterpret_cast<uint4*>(dst + (int64_t)(h0 + i) * dst_head) = raw[i];
+      }
+    }
   }
 }
 
@@ -479,8 +498,8 @@ extern "C" int aspa_rope_rows_to_heads(void* x, int dtype, int64_t n_rows, int T
   const int E = dtype == ASPA_BF16 ? 8 : 4;
   ASPA_CHECK_ARG(D % E == 0 && row_stride % E == 0, "rows must start on 16-byte boundaries");
   if (n_rows == 0) return ASPA_OK;
-  const int64_t total = n_rows * (H * D / E);
-  const unsigned blocks = (unsigned)std::min<int64_t>(ceil_div(total, 256), 148 * 32);
+  const int64_t total = n_rows * (D / E);
+  const unsigned blocks = (unsigned)std::min<int64_t>(ceil_div(total, 256), 148 * 8);
   if (dtype == ASPA_BF16)
     rope_inplace_kernel<__nv_bfloat16><<<blocks, 256, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)x, n_rows, T, row_stride, H, D,
                                                                                  cos_t, sin_t, (__nv_bfloat16*)heads_out);
