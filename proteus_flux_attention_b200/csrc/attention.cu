@@ -392,7 +392,7 @@ __device__ __forceinline__ void r64_issue_keys(const T* kh, int64_t k_ts, int id
     const int ic = max(__shfl_sync(0xffffffffu, idx, row), 0);   // a dead slot copies key 0; its score is masked
     const unsigned dst = (unsigned)__cvta_generic_to_shared(tile + row * PITCH + sub * CH);
     const T* src = kh + (int64_t)ic * k_ts + sub * (CH / (int)sizeof(T));
-    if (CH == 16) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+    if (CH == 16) asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
     else asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
   }
   asm volatile("cp.async.commit_group;" ::: "memory");
