@@ -36,6 +36,16 @@ __device__ __forceinline__ float rope_mix(float a, float c, float rot, float s, 
 // eager bf16 ops); fp32 keeps separate fp32 multiplies and adds.
 constexpr int ROPE_TPB = 32;
 
+// rintf(v / scale), the quantiser's rounding, without a division per element: for |v / scale| < 256 the product with
+// the rounded reciprocal is within 2^-15 of the correctly rounded quotient, so both round to the same integer unless
+// the product lies that close to a tie; only then (about one element in ten thousand) the exact quotient decides.
+__device__ __forceinline__ float quant_round(float v, float scale, float inv) {
+  const float qp = v * inv;
+  float r = rintf(qp);
+  if (fabsf(qp - r) > 0.499f || !(fabsf(qp) < 256.f)) r = rintf(__fdiv_rn(v, scale));
+  return r;
+}
+
 __device__ __forceinline__ uint32_t rope_word_bf16(uint32_t x, float c, float s) {
   // x = (even, odd) packed; out = x * (c, c) + (-odd, even) * (s, s)
   const __nv_bfloat162 xv = *reinterpret_cast<const __nv_bfloat162*>(&x);
@@ -77,10 +87,11 @@ __global__ void __launch_bounds__(512) rope_relayout_kernel(const T* __restrict_
     const float* cr = cos_t ? cos_t + (int64_t)t0 * half + d0 / 2 : nullptr;
     const float* sr = sin_t ? sin_t + (int64_t)t0 * half + d0 / 2 : nullptr;
     float local_max = 0.f;
-    float qscale = 1.f;
+    float qscale = 1.f, qinv = 1.f;
     int8_t* dst8 = nullptr;
     if (MODE == 2) {
       qscale = fmaxf(__fdiv_rn(amax[sec * B * H + bh], 127.0f), 1e-6f);
+      qinv = __fdiv_rn(1.0f, qscale);
       dst8 = reinterpret_cast<int8_t*>(sec == 0 ? q : (sec == 1 ? k : v)) + ((int64_t)bh * Tn + t0) * D + d0;
     }
     const uint8_t* keep = (sec == 0 && q_keep != nullptr) ? q_keep + (int64_t)b * Tn : nullptr;
@@ -115,7 +126,7 @@ __global__ void __launch_bounds__(512) rope_relayout_kernel(const T* __restrict_
           union { int8_t b8[8]; uint2 u; } pk;
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
-            const float r = rintf(__fdiv_rn(__bfloat162float(e[i]), qscale));
+            const float r = quant_round(__bfloat162float(e[i]), qscale, qinv);
             pk.b8[i] = (int8_t)fminf(fmaxf(r, -127.f), 127.f);
           }
           *reinterpret_cast<uint2*>(dst8) = pk.u;
@@ -180,6 +191,7 @@ __global__ void __launch_bounds__(256) quantize_int8_kernel(const T* __restrict_
                                                             int8_t* __restrict__ out, float* __restrict__ scales) {
   const int head = blockIdx.y;
   const float scale = fmaxf(__fdiv_rn(amax[head], 127.0f), 1e-6f);
+  const float inv = __fdiv_rn(1.0f, scale);
   if (blockIdx.x == 0 && threadIdx.x == 0) scales[head] = scale;
   const T* p = x + (int64_t)head * per_head;
   int8_t* o = out + (int64_t)head * per_head;
@@ -198,7 +210,7 @@ __global__ void __launch_bounds__(256) quantize_int8_kernel(const T* __restrict_
     union { int8_t b[8]; uint2 u; } pk;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const float r = rintf(__fdiv_rn(val[i], scale));
+      const float r = quant_round(val[i], scale, inv);
       pk.b[i] = (int8_t)fminf(fmaxf(r, -127.f), 127.f);
     }
     reinterpret_cast<uint2*>(o)[vi] = pk.u;

@@ -2,6 +2,8 @@
 All of them need a CUDA device."""
 import math
 
+import numpy as np
+
 import pytest
 import torch
 
@@ -204,6 +206,30 @@ def test_quantize_int8_exact(dev, dtype):
     xg = x.to(dev)
     amax = ops.head_amax(xg)
     qg, sg = ops.quantize_int8(xg, amax)
+    assert torch.equal(sg.cpu(), so)
+    assert torch.equal(qg.cpu(), qo)
+
+
+def test_quantize_int8_exact_near_ties(dev):
+    """The kernels round x / scale through a product with the reciprocal and fall back to the exact quotient near a
+    tie: values a few ulps either side of (k + 0.5) * scale must land where the oracle's division puts them."""
+    from proteus_flux_attention_b200 import ops
+    heads, n = 3, 4096
+    g = torch.Generator().manual_seed(9)
+    x = torch.empty(heads, n, 1)
+    for h, amax in enumerate((127.0, 3.3711, 0.0123)):
+        scale = np.float32(amax) / np.float32(127.0)
+        k = torch.randint(-126, 126, (n,), generator=g).float() + 0.5
+        v = (k.numpy().astype(np.float32) * scale).astype(np.float32)
+        steps = torch.randint(-3, 4, (n,), generator=g).numpy()
+        for _ in range(3):   # move up to three ulps towards +/- infinity
+            v = np.where(steps > 0, np.nextafter(v, np.float32(np.inf)), np.where(steps < 0, np.nextafter(v, np.float32(-np.inf)), v))
+            steps = steps - np.sign(steps)
+        x[h, :, 0] = torch.from_numpy(v.astype(np.float32))
+        x[h, 0, 0] = amax
+    qo, so = O.quantize_per_head_int8(x)
+    xg = x.to(dev)
+    qg, sg = ops.quantize_int8(xg, ops.head_amax(xg))
     assert torch.equal(sg.cpu(), so)
     assert torch.equal(qg.cpu(), qo)
 
@@ -609,6 +635,12 @@ def test_attention_reads_strided_kv_and_rope_in_place(dev, dtype):
     ops.rope_inplace(kv2.view(-1), B * T, T, 2 * C, H, D, cos, sin)
     assert torch.equal(kv2.view(B, T, 2, H, D)[:, :, 0].permute(0, 2, 1, 3).reshape(B * H, T, D), k_ref)
     assert torch.equal(kv2[..., C:], kv[..., C:])
+    # the same rotation written head-major, the source left untouched; mixed layouts (keys head-major, values strided)
+    kv3 = kv.clone()
+    k_heads = torch.empty(B * H, T, D, dtype=dtype, device=dev)
+    ops.rope_inplace(kv3.view(-1), B * T, T, 2 * C, H, D, cos, sin, heads_out=k_heads)
+    assert torch.equal(k_heads, k_ref) and torch.equal(kv3, kv)
+    mixed = N.KVLayout(k_batch=H * T * D, k_head=T * D, k_token=D, v_batch=T * 2 * C, v_head=D, v_token=2 * C)
     # packed rows: every third token of every head, a window plan (tensor-core path for bf16) and causal (generic path)
     tok = torch.arange(0, T, 3, dtype=torch.int32, device=dev)
     offs = (torch.arange(B * H + 1, device=dev) * tok.numel()).to(torch.int32)
@@ -617,12 +649,12 @@ def test_attention_reads_strided_kv_and_rope_in_place(dev, dtype):
     flat = kv2.view(-1)
     for plan in (ops.make_plan(48, 0, 0, 0, None, None), ops.make_plan(16, 4, 32, 0, None, None), None):
         outs = []
-        for kk, vv, lay in ((k_ref, v_ref, None), (flat, flat[C:], layout)):
+        for kk, vv, lay in ((k_ref, v_ref, None), (flat, flat[C:], layout), (k_heads.view(-1), flat[C:], mixed)):
             out = torch.zeros(B, T, C, dtype=dtype, device=dev)
             ops.gather_attn(q, kk, vv, scales=None, H=H, row_offsets=offs, token_idx=toks, max_rows=tok.numel(),
                             total_rows=toks.numel(), plan=plan, out=out, out_layout=N.OUT_TOKEN_MAJOR, kv_layout=lay)
             outs.append(out)
-        assert torch.equal(outs[0], outs[1])
+        assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
 
 
 @pytest.mark.parametrize("B,T,need,thr,guard", [(3, 300, 40, 0.0, 2), (2, 4096, 200, 0.0, 4), (2, 9000, 3000, 0.6, 1),
