@@ -95,7 +95,7 @@ __global__ void __launch_bounds__(512) rope_relayout_kernel(const T* __restrict_
       dst8 = reinterpret_cast<int8_t*>(sec == 0 ? q : (sec == 1 ? k : v)) + ((int64_t)bh * Tn + t0) * D + d0;
     }
     const uint8_t* keep = (sec == 0 && q_keep != nullptr) ? q_keep + (int64_t)b * Tn : nullptr;
-#pragma unroll 4
+#pragma unroll 8
     for (int t = t0; t < t1; ++t) {
       if (keep != nullptr && !keep[t]) {  // queries of dropped tokens are never read: neither load nor store them
         src += nsec * (int64_t)C;
