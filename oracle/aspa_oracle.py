@@ -213,6 +213,13 @@ def derive_config(**kwargs: Any) -> SimpleNamespace:
     s.token_keep_guard = guard
     s.token_keep_min = max(kmin, guard if s.token_sparse else kmin)
     s.token_keep_threshold = max(0.0, _f(cfg, "attn_token_keep_threshold", 0.0))
+    # key/value memory bank (aspa.py:389-416)
+    s.memory_enabled = bool(_get(cfg, "attn_memory_enable", False))
+    slots = int(_get(cfg, "attn_memory_slots", 0) or 0)
+    if slots <= 0:
+        s.memory_enabled, slots = False, 1
+    s.memory_slots = slots
+    s.memory_decay = float(max(0.0, min(1.0, float(_get(cfg, "attn_memory_decay", 0.9) or 0.9))))
     return s
 
 
@@ -588,6 +595,74 @@ def build_candidates(rows: torch.Tensor, row_batch_ids: Optional[torch.Tensor], 
 
 
 # ----------------------------------------------------------------------------
+# key/value memory bank (aspa.py:932-1035)
+# ----------------------------------------------------------------------------
+def new_memory_bank(s) -> SimpleNamespace:
+    return SimpleNamespace(keys=torch.zeros(s.h_total, s.memory_slots, s.d_head),
+                           values=torch.zeros(s.h_total, s.memory_slots, s.d_head),
+                           counts=torch.zeros(s.h_total, s.memory_slots),
+                           ptr=torch.zeros(s.h_total, dtype=torch.long))
+
+
+def memory_update(s, mem, active_heads: torch.Tensor, k_comp: torch.Tensor, v_comp: torch.Tensor,
+                  mask_comp: torch.Tensor) -> None:
+    """aspa.py:932-969.  For every active (batch, head) pair in ascending order: the head's whole bank decays, the
+    mean key / value over the pair's active tokens goes into the slot under the ring pointer, the pointer advances.
+    The sums are taken in the dtype of k.  With a decay of 1.0 nothing is written at all (the writes sit inside the
+    ``decay < 1`` branch of the reference)."""
+    if not s.memory_enabled or active_heads.numel() == 0 or mask_comp.numel() == 0:
+        return
+    counts = mask_comp.sum(dim=1)
+    if not bool((counts > 0).any()):
+        return
+    mf = mask_comp.to(k_comp.dtype)
+    sums_k = torch.einsum("ht,htd->hd", mf, k_comp)
+    sums_v = torch.einsum("ht,htd->hd", mf, v_comp)
+    for i, head in enumerate((active_heads % s.h_total).tolist()):
+        c = counts[i].item()
+        if c <= 0 or not s.memory_decay < 1.0:
+            continue
+        mem.keys[head] *= s.memory_decay
+        mem.values[head] *= s.memory_decay
+        mem.counts[head] *= s.memory_decay
+        slot = int(mem.ptr[head])
+        mem.keys[head, slot] = (sums_k[i] / c).to(torch.float32)
+        mem.values[head, slot] = (sums_v[i] / c).to(torch.float32)
+        mem.counts[head, slot] = float(c)
+        mem.ptr[head] = (mem.ptr[head] + 1) % s.memory_slots
+
+
+def memory_candidates(s, mem, active_heads: torch.Tensor, token_idx: torch.Tensor, row_offsets: torch.Tensor,
+                      k_comp: torch.Tensor, v_comp: torch.Tensor, seq_len: int):
+    """aspa.py:971-1035: k, v with ``max_mem`` memory rows appended per active head (the ring read from the pointer
+    on, the first ``count`` rows of it, ``count`` = slots whose count is positive), and per packed row the extra
+    candidate ids ``seq_len + j``.  Returns (k_aug, v_aug, extra, extra_len, max_mem)."""
+    if not s.memory_enabled or active_heads.numel() == 0:
+        return k_comp, v_comp, None, None, 0
+    hid = (active_heads % s.h_total).long()
+    per_head = (mem.counts.index_select(0, hid) > 0).sum(dim=1)
+    max_mem = int(per_head.max()) if per_head.numel() else 0
+    if max_mem <= 0:
+        return k_comp, v_comp, None, None, 0
+    A, D = k_comp.size(0), k_comp.size(2)
+    mk, mv = k_comp.new_zeros(A, max_mem, D), v_comp.new_zeros(A, max_mem, D)
+    valid = torch.zeros(A, max_mem, dtype=torch.bool)
+    for i, head in enumerate(hid.tolist()):
+        c = int(per_head[i])
+        if c <= 0:
+            continue
+        p_ = int(mem.ptr[head])
+        keys = torch.cat([mem.keys[head, p_:], mem.keys[head, :p_]], dim=0).to(k_comp.dtype)
+        vals = torch.cat([mem.values[head, p_:], mem.values[head, :p_]], dim=0).to(v_comp.dtype)
+        mk[i, :c], mv[i, :c], valid[i, :c] = keys[:c], vals[:c], True
+    k_aug, v_aug = torch.cat([k_comp, mk], dim=1), torch.cat([v_comp, mv], dim=1)
+    ids = (torch.arange(max_mem) + seq_len).unsqueeze(0).expand(A, -1)
+    row_head = torch.repeat_interleave(torch.arange(A), (row_offsets[1:] - row_offsets[:-1]).long())
+    extra = torch.where(valid[row_head], ids[row_head].to(token_idx.dtype), token_idx.unsqueeze(1).expand(-1, max_mem))
+    return k_aug, v_aug, extra, valid[row_head].long().sum(dim=1).to(token_idx.dtype), max_mem
+
+
+# ----------------------------------------------------------------------------
 # INT8 per-head quantiser (aspa.py:1312-1363)
 # ----------------------------------------------------------------------------
 
@@ -710,6 +785,7 @@ class OracleLayer:
         self.onehot = F.one_hot(self.g2h, num_classes=s.h_total).to(torch.float32)
         self.state = SimpleNamespace(latency_ema=None, current_alpha=0.0, L_scale=s.linear_L_scale_init,
                                      alpha_override=None, last_target_k=None)
+        self.memory = new_memory_bank(s) if s.memory_enabled else None
         self.trace: Dict[str, Any] = {}
 
     def set_shortlist_alpha(self, v: float) -> None:
@@ -790,12 +866,27 @@ class OracleLayer:
                 rt = effective_linear_params(s, T, B, alpha, st.L_scale, st.last_target_k)
                 tr["runtime"] = rt
                 bids = (packed[0] // s.h_total) if (s.linear_use_proto and sim is not None) else None
+                extra = extra_len = None
+                T_eff = T
+                if self.memory is not None:   # aspa.py:1220-1260, on the heads that have active rows
+                    act = torch.nonzero(counts > 0).flatten()
+                    offs_comp = torch.cat([counts.new_zeros(1), counts[act].cumsum(0)])
+                    memory_update(s, self.memory, act, kf[act], vf[act], flat[act])
+                    k_aug, v_aug, extra, extra_len, mm = memory_candidates(
+                        s, self.memory, act, packed[1], offs_comp, kf[act], vf[act], T)
+                    if mm > 0:
+                        T_eff = T + mm
+                        pad = qf.new_zeros(qf.size(0), mm, qf.size(2))
+                        qf = torch.cat([qf, pad], dim=1)
+                        kf, vf = torch.cat([kf, pad], dim=1), torch.cat([vf, pad.to(vf.dtype)], dim=1)
+                        kf[act], vf[act] = k_aug, v_aug
                 cands, lens = build_candidates(
-                    packed[1], bids, T, max_candidates=rt["effective_L"], linear_window=rt["window"],
+                    packed[1], bids, T_eff, max_candidates=rt["effective_L"], linear_window=rt["window"],
                     anchor_stride=s.linear_anchor_stride, use_local=s.linear_use_local,
                     use_anchors=s.linear_use_anchors,
                     proto_scores=sim if (s.linear_use_proto and sim is not None) else None,
-                    local_cap=rt["local_cap"], anchor_cap=rt["anchor_cap"], proto_cap=rt["proto_cap"])
+                    local_cap=rt["local_cap"], anchor_cap=rt["anchor_cap"], proto_cap=rt["proto_cap"],
+                    extra_candidates=extra, extra_lengths=extra_len)
                 tr["candidates"], tr["lengths"], tr["packed"] = cands, lens, packed
                 if s.quantize_int8:
                     qq, qs_ = quantize_per_head_int8(qf, s.quantize_mode, s.quantize_percentile)
@@ -805,6 +896,7 @@ class OracleLayer:
                                            q_scale=qs_, k_scale=ks_, v_scale=vs_, out_dtype=qf.dtype)
                 else:
                     att = sparse_attention(qf, kf, vf, packed=packed, candidates=cands, lengths=lens)
+                att = att[:, :T].contiguous()
                 tr["mode"] = "shortlist"
         out = att.view(B, s.h_total, T, s.d_head).permute(0, 2, 1, 3)
         if tmask is not None:

@@ -105,6 +105,9 @@ def layer_case(name: str, cfg: dict, *, B: int, T: int, dtype=torch.float32, see
                 "conf_after": mod.routing_confidence.clone(),
                 "linear_L": int(mod.linear_L), "linear_window": int(mod.linear_window),
             }
+            if getattr(mod, "memory_enabled", False):
+                r["memory_after"] = {"keys": mod.memory_keys.clone(), "values": mod.memory_values.clone(),
+                                     "counts": mod.memory_counts.clone(), "ptr": mod.memory_ptr.clone()}
             xs.append(x)
             rec.append(r)
     finally:
@@ -305,11 +308,26 @@ BASE = dict(d_model=64, n_head=4, attn_h_total=4, attn_gates=8, attn_h_active=2,
             attn_linear_anchor_stride=8, attn_use_rope=True)
 
 
+def memory_cases():
+    # the key/value memory bank (aspa.py:932-1035): state after every call, ring of 3 slots wrapping with B = 2
+    layer_case("layer_fp32_memory", dict(BASE, attn_mode="linear", attn_memory_enable=True, attn_memory_slots=3,
+                                         attn_memory_decay=0.75), B=2, T=160, calls=3)
+    layer_case("layer_bf16_int8_memory", dict(BASE, attn_mode="linear", attn_quantize_int8=True, attn_linear_L=40,
+                                              attn_linear_L_max=40, attn_linear_window=40, attn_memory_enable=True,
+                                              attn_memory_slots=2, attn_memory_decay=0.9),
+               B=2, T=192, dtype=torch.bfloat16, calls=3, outliers=8)
+
+
 def main():
+    import sys
+    if "--memory-only" in sys.argv:
+        memory_cases()
+        return
     schedule_case()
     candidate_case()
     attention_case()
     chunk_select_case()
+    memory_cases()
     layer_case("layer_fp32_auto", dict(BASE, attn_linear_switch_ctx=400), B=2, T=192, calls=2)
     layer_case("layer_fp32_proto", dict(BASE, attn_mode="linear", attn_linear_policy="local+anchors+proto",
                                         attn_linear_L=48, attn_linear_L_max=48, attn_linear_window=20,

@@ -79,7 +79,8 @@ def test_chunk_selection_matches_reference(golden_dir):
 
 
 LAYER_CASES = ["layer_fp32_auto", "layer_fp32_proto", "layer_bf16_rope", "layer_bf16_int8",
-               "layer_fp32_dense_fastpath", "layer_fp32_dense_density", "layer_fp32_nucleus"]
+               "layer_fp32_dense_fastpath", "layer_fp32_dense_density", "layer_fp32_nucleus",
+               "layer_fp32_memory", "layer_bf16_int8_memory"]
 
 
 def _tie_only(imp_row, a, b):
@@ -138,6 +139,12 @@ def test_layer_matches_reference(golden_dir, name):
             assert torch.allclose(layer.protos, ref["protos_after"], atol=1e-5, rtol=1e-4)
             assert torch.allclose(layer.usage, ref["usage_after"], atol=1e-3, rtol=1e-4)
             assert torch.allclose(layer.conf, ref["conf_after"], atol=1e-6)
+            if "memory_after" in ref and same_mask and bool(ok_tok.all()):   # the bank after this call (aspa.py:932-969)
+                m, want = layer.memory, ref["memory_after"]
+                mtol = dict(atol=2e-2, rtol=2e-2) if bf16 else dict(atol=1e-5, rtol=1e-4)
+                assert torch.equal(m.ptr, want["ptr"])
+                assert torch.allclose(m.counts, want["counts"], atol=1e-5, rtol=1e-6)
+                assert torch.allclose(m.keys, want["keys"], **mtol) and torch.allclose(m.values, want["values"], **mtol)
         else:
             assert torch.allclose(y.float(), ref["y"].float(), atol=1e-5, rtol=1e-4)
 
