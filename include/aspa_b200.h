@@ -369,6 +369,24 @@ int aspa_stats_record(const int32_t* row_offsets, int n_offsets, const int32_t* 
 /* Deterministic sum of per-block partials: out[j] = sum_i partials[j * n_blocks + i]. */
 int aspa_reduce_partials(const float* partials, int n_series, int64_t n_blocks, float* out, void* stream);
 
+/* Key/value memory bank (reference models/aspa.py:932-969, _update_memory_bank).  mem_keys / mem_values (H, slots, D),
+ * mem_counts (H, slots) fp32 and mem_ptr (H) int64 are the layer's buffers.  For every (batch, head) pair with packed
+ * rows, in batch order per head: the head's bank is multiplied by `decay`, the mean key and mean value over the
+ * pair's rows (k, v of dtype `dtype`, read through kv_layout or head-major (B*H, T, D) when NULL) go into the slot under
+ * the ring pointer with the row count beside them, and the pointer advances.  decay >= 1 writes nothing, as the
+ * reference does.  head_dim <= 256. */
+int aspa_memory_update(const void* k, const void* v, int dtype, const aspa_kv_layout* kv_layout, int B, int H, int T,
+                       int D, const int32_t* row_offsets, const int32_t* token_idx, float decay, float* mem_keys,
+                       float* mem_values, float* mem_counts, int64_t* mem_ptr, int slots, void* stream);
+/* INT8 side of _prepare_memory_candidates (aspa.py:971-1013, 1262-1272): the reference quantises k and v with the
+ * ring appended, so the per-head amax covers the appended rows (the first c rows of the ring read from the pointer on,
+ * c = slots with a positive count, values rounded to `dtype`).  Folds that into amax_k / amax_v (B*H) for the pairs
+ * that have packed rows.  The appended rows never reach the attention: the candidate builder clamps their ids onto
+ * the row's own token (sa.py:570-571). */
+int aspa_memory_fold_amax(const float* mem_keys, const float* mem_values, const float* mem_counts,
+                          const int64_t* mem_ptr, int B, int H, int slots, int D, int dtype,
+                          const int32_t* row_offsets, float* amax_k, float* amax_v, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

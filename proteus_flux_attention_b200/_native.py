@@ -72,6 +72,8 @@ SIGNATURES = {
     "aspa_attn_regroup_bytes": (_l, [_l, _i, _i]),
     "aspa_rope_inplace": (_i, [_p, _i, _l, _i, _l, _i, _i, _p, _p, _p]),
     "aspa_rope_rows_to_heads": (_i, [_p, _i, _l, _i, _l, _i, _i, _p, _p, _p, _p]),
+    "aspa_memory_update": (_i, [_p, _p, _i, _p, _i, _i, _i, _i, _p, _p, _f, _p, _p, _p, _p, _i, _p]),
+    "aspa_memory_fold_amax": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _p, _p, _p]),
     "aspa_rope_relayout_kv": (_i, [_p, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p]),
     "aspa_rope_rows_q": (_i, [_p, _i, _p, _p, _l, _i, _i, _i, _i, _p, _p, _p, _p]),
     "aspa_compact_mask_scratch": (_l, [_l]),

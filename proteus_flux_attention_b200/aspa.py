@@ -9,7 +9,10 @@ follow the reference; the arithmetic runs in libaspa_b200.so.
 
 Differences that are deliberate:
   * forward only (the reference's kernel path has no autograd either); attention
-    dropout and the KV memory bank raise ``NotImplementedError``;
+    dropout raises ``NotImplementedError``;
+  * the key/value memory bank (:932-1035) is kept as state (four buffers, updated by every shortlist call) and
+    enters the INT8 scales of k and v; its rows never reach the attention in the reference either, because the
+    candidate builder clamps the memory ids onto the row's own token (kernels/sparse_attn.py:570-571);
   * one device-to-host read per call (a small statistics record) instead of the
     reference's ~20 ``.item()`` calls; it is issued before the QKV projection and
     waited on after it, so the GPU does not idle;
@@ -239,7 +242,16 @@ class AdaptiveSparseAttention(nn.Module):
             cutoff = 0.25
         self.dense_alpha_cutoff = float(max(0.0, min(0.95, cutoff)))
 
+        # key/value memory bank (aspa.py:389-416): non-persistent fp32 buffers, ring pointer per head
         self.memory_enabled = bool(g("attn_memory_enable", False)) and int(g("attn_memory_slots", 0) or 0) > 0
+        self.memory_slots = int(g("attn_memory_slots", 0) or 0) if self.memory_enabled else 1
+        self.memory_decay = float(max(0.0, min(1.0, float(g("attn_memory_decay", 0.9) or 0.9))))
+        self.register_buffer("memory_keys", torch.zeros(heads, self.memory_slots, self.d_head, dtype=torch.float32),
+                             persistent=False)
+        self.register_buffer("memory_values", torch.zeros(heads, self.memory_slots, self.d_head, dtype=torch.float32),
+                             persistent=False)
+        self.register_buffer("memory_counts", torch.zeros(heads, self.memory_slots, dtype=torch.float32), persistent=False)
+        self.register_buffer("memory_ptr", torch.zeros(heads, dtype=torch.long), persistent=False)
         self.quantize_sparse_int8 = bool(g("attn_quantize_int8", False))
         qmode = str(g("attn_quantize_int8_mode", "max") or "max").lower()
         self.quantize_sparse_int8_mode = qmode if qmode in {"max", "percentile", "ema_percentile"} else "max"
@@ -622,8 +634,6 @@ class AdaptiveSparseAttention(nn.Module):
             raise TypeError("ASPA kernels take float32 or bfloat16 activations")
         if self.qkv.weight.dtype != x.dtype:
             raise TypeError(f"activation dtype {x.dtype} does not match the layer weights ({self.qkv.weight.dtype})")
-        if self.memory_enabled:
-            raise NotImplementedError("the KV memory bank (attn_memory_enable) is not built in the sm_100a path yet")
         if self.training and self.dropout.p > 0.0:
             raise NotImplementedError("attention dropout is not implemented in the sm_100a kernels (forward-only build)")
 
@@ -900,7 +910,7 @@ class AdaptiveSparseAttention(nn.Module):
             k, v, kv_layout = kv_fork["k"], kv_fork["v"], kv_fork["layout"]
             torch.cuda.current_stream().wait_event(kv_fork["done"])
             amax = None
-        elif (use_quant and alpha >= 0.95 and x.dtype == torch.bfloat16 and D % 8 == 0
+        elif (use_quant and alpha >= 0.95 and x.dtype == torch.bfloat16 and D % 8 == 0 and not self.memory_enabled
               and (self.quantize_sparse_int8_mode == "max" or self.quantize_sparse_int8_percentile >= 1.0)):
             # INT8 shortlist that can never turn dense (alpha >= 0.95): rotate, split and quantise straight from the
             # fused projection; the bf16 head-major q, k, v are never materialised
@@ -980,6 +990,9 @@ class AdaptiveSparseAttention(nn.Module):
             dense_reason = None
             scales = None
             qa, ka, va = q, k, v
+            if self.memory_enabled:   # aspa.py:1220-1225: the bank takes this call's mean keys / values first
+                ops.memory_update(k, v, kv_layout, B, H, T, D, row_offsets, token_idx, self.memory_decay,
+                                  self.memory_keys, self.memory_values, self.memory_counts, self.memory_ptr)
             if quant_pack is not None:
                 qa, ka, va, sc3 = quant_pack
                 scales = (sc3[0], sc3[1], sc3[2])
@@ -988,6 +1001,10 @@ class AdaptiveSparseAttention(nn.Module):
                     raise NotImplementedError("INT8 percentile scaling below 1.0 is not built in the sm_100a path")
                 if amax is None:
                     amax = torch.stack([ops.head_amax(t_) for t_ in (q, k, v)])
+                if self.memory_enabled:   # k and v are quantised with the ring appended (aspa.py:1226-1272)
+                    amax = amax.clone()
+                    ops.memory_fold_amax(self.memory_keys, self.memory_values, self.memory_counts, self.memory_ptr, B,
+                                         x.dtype, row_offsets, amax[1], amax[2])
                 qa, s_q = ops.quantize_int8(q, amax[0].contiguous())
                 ka, s_k = ops.quantize_int8(k, amax[1].contiguous())
                 va, s_v = ops.quantize_int8(v, amax[2].contiguous())

@@ -429,6 +429,28 @@ def rope_inplace(x_rows: torch.Tensor, n_rows: int, T: int, row_stride: int, H: 
                                                 N.stream()), "rope_rows_to_heads")
 
 
+def memory_update(k: torch.Tensor, v: torch.Tensor, kv_layout: Optional[N.KVLayout], B: int, H: int, T: int, D: int,
+                  row_offsets: torch.Tensor, token_idx: torch.Tensor, decay: float, mem_keys: torch.Tensor,
+                  mem_values: torch.Tensor, mem_counts: torch.Tensor, mem_ptr: torch.Tensor) -> None:
+    """Push the mean key / value of every (batch, head) pair that has packed rows into the head's ring (in place)."""
+    with _timed('memory_update', 1, 0):
+        N.check(N.lib().aspa_memory_update(
+            N.ptr(k), N.ptr(v), N.dtype_code(k.dtype), C.byref(kv_layout) if kv_layout is not None else None, B, H, T, D,
+            N.ptr(row_offsets), N.ptr(token_idx), float(decay), N.ptr(mem_keys), N.ptr(mem_values), N.ptr(mem_counts),
+            N.ptr(mem_ptr), int(mem_keys.size(1)), N.stream()), "memory_update")
+
+
+def memory_fold_amax(mem_keys: torch.Tensor, mem_values: torch.Tensor, mem_counts: torch.Tensor, mem_ptr: torch.Tensor,
+                     B: int, dtype: torch.dtype, row_offsets: torch.Tensor, amax_k: torch.Tensor,
+                     amax_v: torch.Tensor) -> None:
+    """amax_k, amax_v (B*H) fp32, in place: max with the amax of the ring rows the reference appends to k and v."""
+    H, S, D = mem_keys.shape
+    with _timed('memory_fold_amax', 1, 0):
+        N.check(N.lib().aspa_memory_fold_amax(
+            N.ptr(mem_keys), N.ptr(mem_values), N.ptr(mem_counts), N.ptr(mem_ptr), B, H, S, D, N.dtype_code(dtype),
+            N.ptr(row_offsets), N.ptr(amax_k), N.ptr(amax_v), N.stream()), "memory_fold_amax")
+
+
 TOKEN_COMPACT_MAX_T = 65536  # ASPA_TOKEN_COMPACT_MAX_T of the C header
 
 

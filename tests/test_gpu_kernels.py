@@ -767,3 +767,51 @@ def test_rope_quantize_equals_relayout_then_quantize(dev):
         q8, k8, v8, scales = ops.rope_quantize(qkv, H, D, cos, sin)
         for i, got in enumerate((q8, k8, v8)):
             assert torch.equal(got, want[i][0]) and torch.equal(scales[i], want[i][1])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_memory_bank_update_and_int8_amax(dev, dtype):
+    """aspa_memory_update / aspa_memory_fold_amax against the oracle's restatement of the reference's memory bank:
+    three calls with B = 3 and a ring of 2 slots (wraps inside one call), one head without rows, keys and values read
+    through strides; then the amax the INT8 path takes over k, v with the ring appended."""
+    from proteus_flux_attention_b200 import ops, _native as N
+    from types import SimpleNamespace
+    B, H, T, D, S = 3, 4, 96, 32, 2
+    C = H * D
+    s = SimpleNamespace(memory_enabled=True, memory_slots=S, memory_decay=0.8, h_total=H, d_head=D)
+    mem = O.new_memory_bank(s)
+    mk, mv = torch.zeros(H, S, D, device=dev), torch.zeros(H, S, D, device=dev)
+    mc, mp = torch.zeros(H, S, device=dev), torch.zeros(H, dtype=torch.long, device=dev)
+    g = torch.Generator().manual_seed(31)
+    layout = N.KVLayout(k_batch=T * 2 * C, k_head=D, k_token=2 * C, v_batch=T * 2 * C, v_head=D, v_token=2 * C)
+    for call in range(3):
+        kv = torch.randn(B, T, 2 * C, generator=g).to(dtype)
+        mask = torch.rand(B * H, T, generator=g) < 0.3
+        mask[1] = False                      # a pair without rows
+        if call == 1:
+            mask[H:2 * H] = False            # a whole batch row without rows
+        packed = O.pack_active_rows(mask)
+        k_h = kv[..., :C].view(B, T, H, D).permute(0, 2, 1, 3).reshape(B * H, T, D)
+        v_h = kv[..., C:].view(B, T, H, D).permute(0, 2, 1, 3).reshape(B * H, T, D)
+        act = torch.nonzero(mask.sum(1) > 0).flatten()
+        O.memory_update(s, mem, act, k_h[act], v_h[act], mask[act])
+        flat = kv.to(dev).view(-1)
+        ops.memory_update(flat, flat[C:], layout, B, H, T, D, packed[2].to(dev), packed[1].to(torch.int32).to(dev),
+                          s.memory_decay, mk, mv, mc, mp)
+        tol = dict(atol=1e-2, rtol=1e-2) if dtype == torch.bfloat16 else dict(atol=1e-6, rtol=1e-5)
+        assert torch.equal(mp.cpu(), mem.ptr)
+        assert torch.allclose(mc.cpu(), mem.counts, atol=1e-5)
+        assert torch.allclose(mk.cpu(), mem.keys, **tol) and torch.allclose(mv.cpu(), mem.values, **tol)
+    # INT8 scales: make one memory row larger than anything in k so that it decides the head's amax
+    mem.keys[2, int(mem.ptr[2])] *= 40.0
+    mk.copy_(mem.keys.to(dev)); mv.copy_(mem.values.to(dev)); mc.copy_(mem.counts.to(dev))
+    counts = mask.sum(1)
+    offs_comp = torch.cat([counts.new_zeros(1), counts[act].cumsum(0)])
+    k_aug, v_aug, _, _, mm = O.memory_candidates(s, mem, act, packed[1], offs_comp, k_h[act], v_h[act], T)
+    assert mm > 0
+    amax = torch.stack([k_h.float().abs().amax(dim=(1, 2)), v_h.float().abs().amax(dim=(1, 2))]).to(dev)
+    ops.memory_fold_amax(mk, mv, mc, mp, B, dtype, packed[2].to(dev), amax[0], amax[1])
+    want_k = k_aug.float().abs().amax(dim=(1, 2))
+    want_v = v_aug.float().abs().amax(dim=(1, 2))
+    assert torch.equal(amax[0].cpu()[act], want_k) and torch.equal(amax[1].cpu()[act], want_v)
+    assert float(want_k.max()) > float(k_h.float().abs().max())

@@ -8,7 +8,8 @@ from oracle import aspa_oracle as O
 pytestmark = pytest.mark.gpu
 
 LAYER_CASES = ["layer_fp32_auto", "layer_fp32_proto", "layer_bf16_rope", "layer_bf16_int8",
-               "layer_fp32_dense_fastpath", "layer_fp32_dense_density", "layer_fp32_nucleus"]
+               "layer_fp32_dense_fastpath", "layer_fp32_dense_density", "layer_fp32_nucleus",
+               "layer_fp32_memory", "layer_bf16_int8_memory"]
 
 
 @pytest.fixture(scope="module")
@@ -151,6 +152,15 @@ def test_layer_matches_golden_and_oracle(dev, golden_dir, name):
                 assert abs(mod.last_head_stats[key] - ref["stats"][key]) < 1e-4, key
             assert mod.last_head_stats["unique_heads"] == ref["stats"]["unique_heads"]
             assert mod.last_head_stats["max_active_rows"] == ref["stats"]["max_active_rows"]
+        if "memory_after" in ref:   # the key/value memory bank after this call, against the reference's and the oracle's
+            want = ref["memory_after"]
+            mtol = dict(atol=5e-2, rtol=5e-2) if bf16 else dict(atol=1e-5, rtol=1e-4)
+            assert torch.equal(mod.memory_ptr.cpu(), want["ptr"]) and torch.equal(ora.memory.ptr, want["ptr"])
+            assert mod.memory_keys.dtype == torch.float32
+            assert torch.allclose(mod.memory_counts.cpu(), want["counts"], atol=(3.0 if bf16 else 1e-5))
+            assert torch.allclose(mod.memory_keys.cpu(), want["keys"], **mtol)
+            assert torch.allclose(mod.memory_values.cpu(), want["values"], **mtol)
+            assert float(want["keys"].abs().max()) > 0.05
 
 
 def test_layer_state_dict_roundtrip_and_fp32_buffers(dev):
