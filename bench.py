@@ -464,6 +464,7 @@ def main():
         achieved = (nbytes / n) / (tot_ms / n * 1e-3) / 1e9
         roofline = {"bound": "hbm", "kernel": name, "achieved": achieved, "peak": peak, "unit": "GB/s",
                     "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
+                    "frac_of_nominal_8tbs": achieved / 8000.0,
                     "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(args.workload, {}).get(name) if world == 1 else None,
                     "launch_ms": tot_ms / n, "algorithmic_bytes_per_launch": nbytes / n,
                     "kernels_ms_per_step": {k: round(v[1] / args.steps, 4) for k, v in sorted(kt.items(), key=lambda kv: -kv[1][1])}}
