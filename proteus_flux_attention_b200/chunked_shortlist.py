@@ -173,6 +173,9 @@ class ChunkedShortlistConfig:
             raise ValueError("ram_limit_bytes must be positive when provided.")
 
 
+PASS1_LANES = 2   # chunks of pass 1 in flight at once (streams, record slots, memory pools)
+
+
 class _ChunkFeeder:
     """Hands out (1, len, C) device views of the chunks this rank owns.
 
@@ -248,7 +251,7 @@ class _Pass1Records:
         self.idx = torch.full((n_slots, budget), -1, dtype=torch.int64, device=device)
         self.count = torch.zeros((n_slots,), dtype=torch.int32, device=device)
         # two slot numbers: two chunks can be in flight at once, each on its own lane (stream + captured graph)
-        self.slots = [torch.zeros((1,), dtype=torch.int32, device=device) for _ in range(2)]
+        self.slots = [torch.zeros((1,), dtype=torch.int32, device=device) for _ in range(PASS1_LANES)]
         self.slot = self.slots[0]
         self.offsets = torch.zeros((n_slots,), dtype=torch.int64, device=device)
         self.stream = torch.cuda.Stream(device=device, priority=-2)
@@ -354,21 +357,21 @@ class ChunkedShortlistRunner:
             signature = None
             if key in cache:
                 return cache[key]
-            statics = [torch.zeros(1, cfg.chunk_len, cfg.d_model, device=cfg.device, dtype=dtype) for _ in range(4)]
+            statics = [torch.zeros(1, cfg.chunk_len, cfg.d_model, device=cfg.device, dtype=dtype) for _ in range(2 * PASS1_LANES)]
         # Two lanes, each a stream of priority -2 with its own record slot and memory for the intermediates: chunk i+1
         # starts on the other lane while chunk i is still running, so its GEMM (compute bound) runs beside the
-        # attention and the row scatter of chunk i (memory and latency bound).  Graph k runs on lane k % 2; the graphs
+        # attention and the row scatter of chunk i (memory and latency bound).  Graph k runs on lane k % PASS1_LANES; the graphs
         # of a lane never overlap and share the lane's memory.  With the ring the copy of a chunk runs two chunks ahead.
         # Priorities: the layer forks its key/value GEMM onto a stream one level below the caller's, and the copy of
         # the next chunk runs at priority 0; captured kernel nodes keep the priority of the stream they came from.
         # So the short selection kernels of the main line take SMs as GEMM blocks retire instead of queueing behind
         # all of them, and the GEMM in turn is not held up by the copy.
-        lanes = [torch.cuda.Stream(device=cfg.device, priority=-2) for _ in range(2)]
+        lanes = [torch.cuda.Stream(device=cfg.device, priority=-2) for _ in range(PASS1_LANES)]
         graphs: List[Any] = [None] * len(statics)
         for k in range(len(statics)):
-            lane = k % 2
+            lane = k % PASS1_LANES
             records.use_lane(lane)
-            if k < 2:
+            if k < PASS1_LANES:
                 lanes[lane].wait_stream(torch.cuda.current_stream())
                 with torch.cuda.stream(lanes[lane]):  # eager warm-up on a side stream, as graph capture requires
                     for _ in range(2):
@@ -376,7 +379,7 @@ class ChunkedShortlistRunner:
                 torch.cuda.current_stream().wait_stream(lanes[lane])
                 torch.cuda.synchronize(cfg.device)
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, pool=graphs[lane].pool() if k >= 2 else None, stream=lanes[lane]):
+            with torch.cuda.graph(g, pool=graphs[lane].pool() if k >= PASS1_LANES else None, stream=lanes[lane]):
                 self._chunk_step(layer, statics[k], records)
             graphs[k] = g
         records.use_lane(0)
