@@ -556,25 +556,58 @@ class ChunkedShortlistRunner:
             keep_idx, keep_sc, keep_count = ops.merge_finalise(all_scores.view(-1), all_idx.view(-1), cfg.seq_len,
                                                                cfg.buffer_tokens)
         ev_b.record()
-        k_host = int(keep_count.item())
+
+        def second_half(k_host: int):
+            """Gather the kept rows and run pass 2 for a kept count of ``k_host``."""
+            kidx, ksc = keep_idx[:k_host], keep_sc[:k_host]
+            if pool is not None:
+                red = self._gather_pooled(pool, keep_pos[:k_host], k_host, budget, world, c_lo, c_hi)
+            else:
+                red = self._gather_reduced(source, source_off, kidx, k_host, device, world, rank, c_lo, c_hi)
+            out = info = stats = None
+            if cfg.run_final_pass:
+                final_model = self._make_layer(k_host, cfg.final_sparse_ratio, base_dtype, final_state, cfg.freeze_prototypes)
+                torch.cuda.reset_peak_memory_stats(device)
+                if cfg.use_cuda_graph:
+                    out = self._final_replay(final_model, red)
+                else:
+                    out = final_model(red).detach()
+                info = get_last_backend_info()
+                stats = (final_model,)
+            return kidx, ksc, red, out, info, stats
+
+        # The kept count is a device value.  Waiting for it here leaves the GPU idle for a host round trip (about
+        # 0.1 ms before pass 2 can even be enqueued).  With graphs on, pass 2 is enqueued for the count that holds
+        # whenever the chunks promote at least `buffer_tokens` tokens in all, min(buffer, chunks * budget), while the
+        # real count travels to a pinned word; it is checked once the stream has drained, and only a run that guessed
+        # wrong (indices beyond the real count are -1 and gather zero rows) repeats the second half.  Every rank sees
+        # the same records, so every rank takes the same branch.
+        speculate = cfg.use_cuda_graph and (pool is not None or source.is_cuda)
+        if speculate:
+            k_guess = min(cfg.buffer_tokens, n_chunks * budget)
+            count_pin = self.__dict__.get("_count_pin")
+            if count_pin is None:
+                count_pin = self.__dict__["_count_pin"] = torch.zeros(1, dtype=torch.int32, pin_memory=True)
+            count_pin.copy_(keep_count, non_blocking=True)
+            counted = torch.cuda.Event()
+            counted.record()
+            result = second_half(k_guess)
+            counted.synchronize()
+            k_host = int(count_pin.item())
+        else:
+            k_host = int(keep_count.item())
+            k_guess = k_host
+            result = None
         if k_host == 0:
             raise RuntimeError("Chunked pipeline selected zero tokens; adjust per_chunk_budget or sparse ratios.")
-        keep_idx, keep_sc = keep_idx[:k_host], keep_sc[:k_host]
-        if pool is not None:
-            reduced = self._gather_pooled(pool, keep_pos[:k_host], k_host, budget, world, c_lo, c_hi)
-        else:
-            reduced = self._gather_reduced(source, source_off, keep_idx, k_host, device, world, rank, c_lo, c_hi)
+        if result is None or k_host != k_guess:
+            result = second_half(k_host)
+        keep_idx, keep_sc, reduced, final_output, backend_info, fm = result
         chunk_time_ms = None
-        final_output = final_stats = backend_info = None
+        final_stats = None
         final_time_ms = peak_mb = None
-        if cfg.run_final_pass:
-            final_model = self._make_layer(k_host, cfg.final_sparse_ratio, base_dtype, final_state, cfg.freeze_prototypes)
-            torch.cuda.reset_peak_memory_stats(device)
-            if cfg.use_cuda_graph:
-                final_output = self._final_replay(final_model, reduced)
-            else:
-                final_output = final_model(reduced).detach()
-            backend_info = get_last_backend_info()
+        if fm is not None:
+            final_model = fm[0]
             final_stats = _sanitize_mapping(dict(final_model.last_head_stats or {}))
             st = {k: v for k, v in (final_model._last_sparse_state or {}).items() if not isinstance(v, torch.Tensor)}
             if st:

@@ -343,9 +343,10 @@ def merge_finalise(scores: torch.Tensor, indices: torch.Tensor, seq_len: int, ma
     """Returns (keep_idx, keep_scores, count) and, with ``want_pos``, the candidate position of every kept index."""
     dev = scores.device
     table = _empty((int(N.lib().aspa_merge_finalise_scratch(int(seq_len))),), torch.uint8, dev)
-    keep_idx = _empty((max_tokens,), torch.int64, dev)
+    # entries beyond the kept count stay -1 (a gather by them reads nothing)
+    keep_idx = torch.full((max_tokens,), -1, dtype=torch.int64, device=dev)
     keep_sc = _empty((max_tokens,), torch.float32, dev)
-    keep_pos = _empty((max_tokens,), torch.int64, dev) if want_pos else None
+    keep_pos = torch.full((max_tokens,), -1, dtype=torch.int64, device=dev) if want_pos else None
     count = _empty((1,), torch.int32, dev)
     with _timed('merge_finalise', 2, _nb(scores, indices)):
         N.check(N.lib().aspa_merge_finalise(N.ptr(scores), N.ptr(indices), scores.numel(), int(seq_len), int(max_tokens),

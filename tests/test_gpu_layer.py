@@ -393,5 +393,16 @@ def test_chunked_pipeline_graph_replay_equals_eager(dev):
         assert torch.equal(got.final_output.cpu(), want.final_output.cpu())
         assert got.final_stats["sparse_state"]["mode"] == want.final_stats["sparse_state"]["mode"]
         assert [c.promoted for c in got.chunks] == [c.promoted for c in want.chunks]
+    # a buffer the promotions cannot fill: the graph path enqueues pass 2 for min(buffer, chunks * budget) kept tokens
+    # before the real count is known, finds fewer (the short last chunk promotes only what it kept) and repeats it
+    wide = dict(base, buffer_tokens=1024)
+    want = P.ChunkedShortlistRunner(P.ChunkedShortlistConfig(**wide)).run(seq.to(dev), chunk_state=cs, final_state=fs)
+    assert want.keep_indices.numel() < 6 * 128
+    runner = P.ChunkedShortlistRunner(P.ChunkedShortlistConfig(**wide, use_cuda_graph=True), cache_layers=True)
+    for source in (seq.to(dev), seq.pin_memory()):
+        got = runner.run(source, chunk_state=cs, final_state=fs)
+        assert torch.equal(got.keep_indices, want.keep_indices)
+        assert torch.equal(got.reduced_sequence.cpu(), want.reduced_sequence.cpu())
+        assert torch.equal(got.final_output.cpu(), want.final_output.cpu())
     with pytest.raises(ValueError, match="freeze_prototypes"):
         P.ChunkedShortlistConfig(**{**base, "freeze_prototypes": False}, use_cuda_graph=True).validate()
