@@ -595,6 +595,31 @@ class AdaptiveSparseAttention(nn.Module):
         layout = N.KVLayout(k_batch=T * 2 * C, k_head=D, k_token=2 * C, v_batch=T * 2 * C, v_head=D, v_token=2 * C)
         return {"k": flat, "v": flat[C:], "kv": kv, "layout": layout, "done": done}
 
+    def _fork_qkv_quantize(self, x: torch.Tensor) -> dict:
+        """Fused QKV projection, RoPE, head-major split and per-head INT8 quantisation of one call on the second
+        stream (see ``_fork_kv_projection``).  The results are used on the calling stream; they are marked as such
+        for the caching allocator."""
+        B, T, C = x.shape
+        H, D = self.h_total, self.d_head
+        dev = x.device
+        cos = sin = None
+        if self.use_rope:
+            cos, sin = self._rope_factors(T, dev, x.dtype)
+        main = torch.cuda.current_stream()
+        prio = min(0, int(main.priority) + 1)
+        side = _SIDE_STREAMS.get((str(dev), prio))
+        if side is None:
+            side = _SIDE_STREAMS[(str(dev), prio)] = torch.cuda.Stream(device=dev, priority=prio)
+        ready, done = torch.cuda.Event(), torch.cuda.Event()
+        ready.record(main)
+        side.wait_event(ready)
+        with torch.cuda.stream(side):
+            pack = ops.rope_quantize(self.qkv(x).contiguous(), H, D, cos, sin)
+            done.record(side)
+        for t_ in pack:
+            t_.record_stream(main)
+        return {"pack": pack, "done": done}
+
     def _project_compact_q(self, x: torch.Tensor, compact: dict) -> torch.Tensor:
         """q for the kept tokens only; the q rows of dropped tokens stay unwritten."""
         B, T, C = x.shape
@@ -829,6 +854,12 @@ class AdaptiveSparseAttention(nn.Module):
         # Started before the router: launched after it, the projection's CTAs starve the cluster launches of the token
         # keep (158 us instead of 40 us per call).
         kv_fork = self._fork_kv_projection(x) if will_compact else None
+        # INT8 shortlist that can never turn dense (alpha >= 0.95): the fused projection and its rotate / split /
+        # quantise passes do not depend on the routing either, so they take the second stream the same way
+        fuse_quant = (use_quant and not will_compact and alpha >= 0.95 and x.dtype == torch.bfloat16 and D % 8 == 0
+                      and not self.memory_enabled
+                      and (self.quantize_sparse_int8_mode == "max" or self.quantize_sparse_int8_percentile >= 1.0))
+        quant_fork = self._fork_qkv_quantize(x) if fuse_quant else None
 
         # 1. router
         x2d = x.view(B * T, C)
@@ -898,6 +929,21 @@ class AdaptiveSparseAttention(nn.Module):
         ctx = {"B": B, "T": T, "alpha": alpha, "device": dev, "pin": self._pin, "event": ev_rec, "use_proto": use_proto,
                "token_idx": token_idx, "row_offsets": row_offsets, "exec_mode": "shortlist"}
 
+        # Work that needs neither q, k, v nor the record goes first: while the projection is still running on the
+        # second stream this stream would otherwise only wait for it.  The prototype EMA (runs in eval mode too,
+        # aspa.py:1917; a decay of exactly 1 leaves the state untouched; the router has read the prototypes already),
+        # the block lists of the prototype picks, the zero fill of the attention output.
+        if use_proto and self.routing_usage_ema is not None and self.routing_confidence is not None \
+                and self.proto_decay != 1.0:
+            self._last_proto_updated = ops.proto_ema_update(x2d, gate, self.proto_decay, self.routing_prototypes,
+                                                            self.routing_usage_ema, self.routing_confidence)
+        runtime = self._prepare_linear_runtime(T, B, alpha)
+        plan_args = self._plan_shape(runtime, T, sim is not None)
+        early_lists = None
+        if plan_args is not None and plan_args[2] > 0:
+            early_lists = ops.proto_plan(self._last_token_similarity.contiguous(), plan_args[2])
+        out_early = None if will_compact else torch.zeros((B, T, C), dtype=x.dtype, device=dev)
+
         # 5. projection + RoPE + head-major relayout (does not depend on the record)
         kv_layout = quant_pack = None
         if will_compact:
@@ -910,14 +956,11 @@ class AdaptiveSparseAttention(nn.Module):
             k, v, kv_layout = kv_fork["k"], kv_fork["v"], kv_fork["layout"]
             torch.cuda.current_stream().wait_event(kv_fork["done"])
             amax = None
-        elif (use_quant and alpha >= 0.95 and x.dtype == torch.bfloat16 and D % 8 == 0 and not self.memory_enabled
-              and (self.quantize_sparse_int8_mode == "max" or self.quantize_sparse_int8_percentile >= 1.0)):
-            # INT8 shortlist that can never turn dense (alpha >= 0.95): rotate, split and quantise straight from the
-            # fused projection; the bf16 head-major q, k, v are never materialised
-            cos = sin = None
-            if self.use_rope:
-                cos, sin = self._rope_factors(T, dev, x.dtype)
-            quant_pack = ops.rope_quantize(self.qkv(x).contiguous(), H, D, cos, sin)
+        elif quant_fork is not None:
+            # rotate, split and quantise straight from the fused projection; the bf16 head-major q, k, v are never
+            # materialised
+            quant_pack = quant_fork["pack"]
+            torch.cuda.current_stream().wait_event(quant_fork["done"])
             q = k = v = amax = None
         else:
             # queries of dropped tokens are never used: skip their relayout
@@ -926,14 +969,12 @@ class AdaptiveSparseAttention(nn.Module):
 
         # The mode decision needs row counts — unless alpha >= 0.95, where the reference never goes dense
         # (aspa.py:1636-1639): then the call runs without waiting for the record, on host-side bounds.
-        runtime = self._prepare_linear_runtime(T, B, alpha)
-        plan_args = self._plan_shape(runtime, T, sim is not None)
         lazy = alpha >= 0.95 and bound_known and plan_args is not None
         if compact is not None:
             out = torch.zeros((compact["slots"], C), dtype=x.dtype, device=dev)
             row_map = compact["slot_of"]
         else:
-            out = torch.zeros((B, T, C), dtype=x.dtype, device=dev)
+            out = out_early
             row_map = None
         info = None
         force_dense, dense_reason, exec_mode = False, None, "shortlist"
@@ -1013,7 +1054,7 @@ class AdaptiveSparseAttention(nn.Module):
                 win, slots, pcap = plan_args
                 lists = limits = None
                 if pcap > 0:
-                    lists, limits = ops.proto_plan(self._last_token_similarity.contiguous(), pcap)
+                    lists, limits = early_lists
                 plan = ops.make_plan(win, slots, runtime["anchor_stride"], pcap, lists, limits)
                 attention_packed(qa, ka, va, row_offsets=row_offsets, token_idx=token_idx, max_rows=max_rows,
                                  total_rows=total_rows, H=H, scales=scales, plan=plan, out=out,
@@ -1063,11 +1104,6 @@ class AdaptiveSparseAttention(nn.Module):
         self._top_head_indices, self._top_head_scores = top_idx.view(B, T, -1), top_score.view(B, T, -1)
         self._last_gate_probs = gate.view(B, T, G)
 
-        # 8. prototype EMA (runs in eval mode too, aspa.py:1917); a decay of exactly 1 leaves the state untouched
-        if use_proto and self.routing_usage_ema is not None and self.routing_confidence is not None \
-                and self.proto_decay != 1.0:
-            self._last_proto_updated = ops.proto_ema_update(x2d, gate, self.proto_decay, self.routing_prototypes,
-                                                            self.routing_usage_ema, self.routing_confidence)
         mode_now = self.__dict__["_sparse_state_value"]["mode"] if not lazy else "shortlist"
         self._finalize_latency(f"cvt(alpha={alpha:.2f})::{mode_now if force_dense else exec_mode}", ev0, t_start, ctx if lazy else None)
         return y
