@@ -292,6 +292,21 @@ int aspa_gather_attn_fwd_ex(const void* q, const void* k, const void* v, int qkv
                             const aspa_shortlist_plan* plan, const float* add_mask, void* out, int out_dtype,
                             int out_layout, const int32_t* out_row_map, const aspa_kv_layout* kv_layout,
                             void* workspace, void* regroup_ws, void* stream);
+/* The same call with the regrouping of its anchor tile pass done ahead of time: aspa_attn_regroup_rows depends on the
+ * packed rows and the plan only, not on q, k, v, so a caller whose projection is still running on another stream can
+ * issue it before waiting for that stream.  It fills regroup_ws and sets *prepared (host int) to 1 when the call below,
+ * given the same arguments, will take the anchor tile pass; regroup_prepared passes that flag on.  No reference
+ * counterpart. */
+int aspa_attn_regroup_rows(int qkv_dtype, int heads, int T, int D, const int32_t* row_offsets, const int32_t* token_idx,
+                           int64_t total_rows, const aspa_shortlist_plan* plan, void* regroup_ws, int32_t* prepared,
+                           void* stream);
+int aspa_gather_attn_fwd_prepared(const void* q, const void* k, const void* v, int qkv_dtype, const float* q_scale,
+                                  const float* k_scale, const float* v_scale, int heads, int T, int D, int H,
+                                  const int32_t* row_offsets, const int32_t* token_idx, int max_rows, int64_t total_rows,
+                                  const int64_t* cand, const int64_t* cand_len, int L, const aspa_shortlist_plan* plan,
+                                  const float* add_mask, void* out, int out_dtype, int out_layout,
+                                  const int32_t* out_row_map, const aspa_kv_layout* kv_layout, void* workspace,
+                                  void* regroup_ws, int regroup_prepared, void* stream);
 /* Bytes of regroup_ws for the call above (0 when the plan has no anchors). */
 int64_t aspa_attn_regroup_bytes(int64_t total_rows, int heads, int anchor_stride);
 

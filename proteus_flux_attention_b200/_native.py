@@ -70,6 +70,10 @@ SIGNATURES = {
     "aspa_gather_attn_fwd_ex": (_i, [_p, _p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _p, _p, _i, _l, _p, _p, _i,
                                      C.POINTER(ShortlistPlan), _p, _p, _i, _i, _p, C.POINTER(KVLayout), _p, _p, _p]),
     "aspa_attn_regroup_bytes": (_l, [_l, _i, _i]),
+    "aspa_gather_attn_fwd_prepared": (_i, [_p, _p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _p, _p, _i, _l, _p, _p, _i,
+                                           C.POINTER(ShortlistPlan), _p, _p, _i, _i, _p, C.POINTER(KVLayout), _p, _p, _i,
+                                           _p]),
+    "aspa_attn_regroup_rows": (_i, [_i, _i, _i, _i, _p, _p, _l, C.POINTER(ShortlistPlan), _p, C.POINTER(C.c_int32), _p]),
     "aspa_rope_inplace": (_i, [_p, _i, _l, _i, _l, _i, _i, _p, _p, _p]),
     "aspa_rope_rows_to_heads": (_i, [_p, _i, _l, _i, _l, _i, _i, _p, _p, _p, _p]),
     "aspa_memory_update": (_i, [_p, _p, _i, _p, _i, _i, _i, _i, _p, _p, _f, _p, _p, _p, _p, _i, _p]),

@@ -943,6 +943,13 @@ class AdaptiveSparseAttention(nn.Module):
         if plan_args is not None and plan_args[2] > 0:
             early_lists = ops.proto_plan(self._last_token_similarity.contiguous(), plan_args[2])
         out_early = None if will_compact else torch.zeros((B, T, C), dtype=x.dtype, device=dev)
+        early_plan = early_regroup = None
+        if plan_args is not None:
+            early_plan = ops.make_plan(plan_args[0], plan_args[1], runtime["anchor_stride"], plan_args[2],
+                                       *(early_lists if early_lists is not None else (None, None)))
+            if alpha >= 0.95 and bound_known:   # row counts are host-side bounds: the anchor regrouping can go now too
+                early_regroup = ops.regroup_rows(early_plan, torch.int8 if use_quant else x.dtype, B * H, T, D,
+                                                 row_offsets, token_idx, B * kept_bound * k_bound)
 
         # 5. projection + RoPE + head-major relayout (does not depend on the record)
         kv_layout = quant_pack = None
@@ -1051,14 +1058,10 @@ class AdaptiveSparseAttention(nn.Module):
                 va, s_v = ops.quantize_int8(v, amax[2].contiguous())
                 scales = (s_q, s_k, s_v)
             if plan_args is not None:
-                win, slots, pcap = plan_args
-                lists = limits = None
-                if pcap > 0:
-                    lists, limits = early_lists
-                plan = ops.make_plan(win, slots, runtime["anchor_stride"], pcap, lists, limits)
                 attention_packed(qa, ka, va, row_offsets=row_offsets, token_idx=token_idx, max_rows=max_rows,
-                                 total_rows=total_rows, H=H, scales=scales, plan=plan, out=out,
-                                 out_layout=N.OUT_TOKEN_MAJOR, out_row_map=row_map, kv_layout=kv_layout)
+                                 total_rows=total_rows, H=H, scales=scales, plan=early_plan, out=out,
+                                 out_layout=N.OUT_TOKEN_MAJOR, out_row_map=row_map, kv_layout=kv_layout,
+                                 regroup=early_regroup if lazy else None)
                 path = "planned"
             else:  # the candidate pieces can overflow L: use the exact table builder (needs exact row counts)
                 L = runtime["effective_L"]

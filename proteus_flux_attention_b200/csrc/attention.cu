@@ -928,6 +928,65 @@ __global__ void __launch_bounds__(1024) anchor_scan_kernel(int32_t* __restrict__
 
 using namespace aspa;
 
+// Does a planned call take the tile (tensor-core) path?  The tile pass streams the union key range of 16 consecutive
+// rows (about 16*gap + window keys, gap = mean token distance between the rows of a head); a per-row gather reads
+// 16*window.  With very sparse rows the union is mostly keys nobody attends to and the CTA count drops below the SM
+// count: gather instead.  total_rows may be a host-side upper bound, which only makes the estimate of the gap
+// conservative.
+static bool tile_path_ok(int qkv_dtype, int D, bool has_cand, bool has_mask, const aspa_shortlist_plan* plan, int heads,
+                         int T, int64_t total_rows) {
+  if (!(D == WK_D && (qkv_dtype == ASPA_BF16 || qkv_dtype == ASPA_I8) && !has_cand && !has_mask)) return false;
+  if (plan != nullptr) {
+    const double gap = (double)T * (double)heads / (double)std::max<int64_t>(total_rows, 1);
+    const double window = plan->window > 0 ? plan->window : 1;
+    if (16.0 * gap >= 7.0 * window) return false;
+  }
+  return true;
+}
+
+// Anchors t - j*stride of the rows of one residue class t % stride are a window over the strided key sequence of that
+// class: with enough rows per (head, residue) group they go through the tile kernel too, regrouped.
+struct AnchorTiles {
+  bool use;
+  int n_loc_full, jmin, an_window;
+};
+static AnchorTiles anchor_tiles_for(const aspa_shortlist_plan* plan, bool has_ws, int heads, int64_t total_rows) {
+  AnchorTiles a = {false, 1, 1, 0};
+  if (plan == nullptr || !(plan->anchor_slots > 0 && plan->anchor_stride > 0)) return a;
+  a.n_loc_full = plan->window > 0 ? plan->window : 1;
+  a.jmin = (a.n_loc_full - 1) / plan->anchor_stride + 1;   // first anchor slot outside the window
+  a.an_window = plan->anchor_slots - a.jmin + 1;
+  a.use = has_ws && plan->anchor_stride <= 1024 && a.an_window >= 64 &&
+          total_rows >= (int64_t)8 * heads * plan->anchor_stride;
+  return a;
+}
+static void launch_regroup(const int32_t* row_offsets, const int32_t* token_idx, int heads, int R, const AnchorTiles& a,
+                           int64_t total_rows, void* regroup_ws, cudaStream_t st) {
+  const int n_groups = heads * R;
+  int32_t* goffs = reinterpret_cast<int32_t*>(regroup_ws);
+  int32_t* gtok = goffs + n_groups + 1;
+  int32_t* grow_ = gtok + total_rows;
+  const unsigned blocks = (unsigned)ceil_div((int64_t)n_groups * 32, 256);
+  anchor_regroup_kernel<<<blocks, 256, 0, st>>>(row_offsets, token_idx, heads, R, a.n_loc_full, a.jmin, 0, goffs, gtok, grow_);
+  anchor_scan_kernel<<<1, 1024, 0, st>>>(goffs, n_groups);
+  anchor_regroup_kernel<<<blocks, 256, 0, st>>>(row_offsets, token_idx, heads, R, a.n_loc_full, a.jmin, 1, goffs, gtok, grow_);
+}
+
+extern "C" int aspa_attn_regroup_rows(int qkv_dtype, int heads, int T, int D, const int32_t* row_offsets,
+                                      const int32_t* token_idx, int64_t total_rows, const aspa_shortlist_plan* plan,
+                                      void* regroup_ws, int32_t* prepared, void* stream) {
+  ASPA_CHECK_ARG(row_offsets && token_idx && plan && prepared, "null pointer");
+  *prepared = 0;
+  if (total_rows <= 0 || regroup_ws == nullptr) return ASPA_OK;
+  if (!tile_path_ok(qkv_dtype, D, false, false, plan, heads, T, total_rows)) return ASPA_OK;
+  const AnchorTiles a = anchor_tiles_for(plan, true, heads, total_rows);
+  if (!a.use) return ASPA_OK;
+  launch_regroup(row_offsets, token_idx, heads, plan->anchor_stride, a, total_rows, regroup_ws, (cudaStream_t)stream);
+  ASPA_CHECK_LAUNCH();
+  *prepared = 1;
+  return ASPA_OK;
+}
+
 extern "C" int64_t aspa_attn_regroup_bytes(int64_t total_rows, int heads, int anchor_stride) {
   if (anchor_stride <= 0) return 0;
   return (int64_t)sizeof(int32_t) * ((int64_t)heads * anchor_stride + 1 + 2 * total_rows);
@@ -991,6 +1050,20 @@ extern "C" int aspa_gather_attn_fwd_ex(const void* q, const void* k, const void*
                                        const float* add_mask, void* out, int out_dtype, int out_layout,
                                        const int32_t* out_row_map, const aspa_kv_layout* kv_layout, void* workspace,
                                        void* regroup_ws, void* stream) {
+  return aspa_gather_attn_fwd_prepared(q, k, v, qkv_dtype, q_scale, k_scale, v_scale, heads, T, D, H, row_offsets,
+                                       token_idx, max_rows, total_rows, cand, cand_len, L, plan, add_mask, out, out_dtype,
+                                       out_layout, out_row_map, kv_layout, workspace, regroup_ws, 0, stream);
+}
+
+extern "C" int aspa_gather_attn_fwd_prepared(const void* q, const void* k, const void* v, int qkv_dtype,
+                                             const float* q_scale, const float* k_scale, const float* v_scale,
+                                             int heads, int T, int D, int H, const int32_t* row_offsets,
+                                             const int32_t* token_idx, int max_rows, int64_t total_rows,
+                                             const int64_t* cand, const int64_t* cand_len, int L,
+                                             const aspa_shortlist_plan* plan, const float* add_mask, void* out,
+                                             int out_dtype, int out_layout, const int32_t* out_row_map,
+                                             const aspa_kv_layout* kv_layout, void* workspace, void* regroup_ws,
+                                             int regroup_prepared, void* stream) {
   ASPA_CHECK_ARG(q && k && v && row_offsets && token_idx && out, "null pointer");
   ASPA_CHECK_ARG(heads > 0 && T > 0 && D > 0 && D <= GEN_MAXD, "head_dim must be in [1, 256]");
   ASPA_CHECK_ARG(qkv_dtype == ASPA_F32 || qkv_dtype == ASPA_BF16 || qkv_dtype == ASPA_I8, "bad qkv dtype");
@@ -1030,17 +1103,8 @@ extern "C" int aspa_gather_attn_fwd_ex(const void* q, const void* k, const void*
   p.ws_m = p.ws_l = p.ws_o = nullptr;
   p.an_stride = 0;
 
-  bool tensor_ok = D == WK_D && (qkv_dtype == ASPA_BF16 || qkv_dtype == ASPA_I8) && cand == nullptr &&
-                   add_mask == nullptr;
-  if (tensor_ok && p.has_plan) {
-    // The tile pass streams the union key range of 16 consecutive rows (about 16*gap + window keys, gap = mean
-    // token distance between the rows of a head); a per-row gather reads 16*window.  With very sparse rows the
-    // union is mostly keys nobody attends to and the CTA count drops below the SM count: gather instead.
-    // total_rows may be a host-side upper bound, which only makes the estimate of the gap conservative.
-    const double gap = (double)T * (double)heads / (double)total_rows;
-    const double window = plan->window > 0 ? plan->window : 1;
-    if (16.0 * gap >= 7.0 * window) tensor_ok = false;
-  }
+  const bool tensor_ok = tile_path_ok(qkv_dtype, D, cand != nullptr, add_mask != nullptr, p.has_plan ? plan : nullptr,
+                                      heads, T, total_rows);
   if (tensor_ok) {
     const bool extras = p.has_plan && ((plan->anchor_slots > 0 && plan->anchor_stride > 0) ||
                                        (plan->proto_cap > 0 && plan->proto_lists != nullptr));
@@ -1054,28 +1118,20 @@ extern "C" int aspa_gather_attn_fwd_ex(const void* q, const void* k, const void*
     }
     if (qkv_dtype == ASPA_BF16) launch_window<__nv_bfloat16, 3>(p, max_rows, st); else launch_window<int8_t, 4>(p, max_rows, st);
     ASPA_CHECK_LAUNCH();
-    // Anchors t - j*stride of the rows of one residue class t % stride are a window over the strided key sequence of
-    // that class: with enough rows per (head, residue) group they go through the tile kernel too, regrouped.
-    const int n_loc_full = (extras && plan->window > 0) ? plan->window : 1;
-    const int a_stride = extras ? plan->anchor_stride : 0;
-    const int jmin = (n_loc_full - 1) / std::max(1, a_stride) + 1;   // first anchor slot outside the window
-    const int an_window = extras ? plan->anchor_slots - jmin + 1 : 0;
-    const bool anchor_tiles = extras && regroup_ws != nullptr && a_stride > 0 && a_stride <= 1024 && an_window >= 64 &&
-                              total_rows >= (int64_t)8 * heads * a_stride;
-    if (anchor_tiles) {
+    const AnchorTiles at = anchor_tiles_for(extras ? plan : nullptr, regroup_ws != nullptr, heads, total_rows);
+    if (at.use) {
       const int R = plan->anchor_stride, n_groups = heads * R;
       int32_t* goffs = reinterpret_cast<int32_t*>(regroup_ws);
       int32_t* gtok = goffs + n_groups + 1;
       int32_t* grow_ = gtok + total_rows;
-      const unsigned blocks = (unsigned)ceil_div((int64_t)n_groups * 32, 256);
-      anchor_regroup_kernel<<<blocks, 256, 0, st>>>(row_offsets, token_idx, heads, R, n_loc_full, jmin, 0, goffs, gtok, grow_);
-      anchor_scan_kernel<<<1, 1024, 0, st>>>(goffs, n_groups);
-      anchor_regroup_kernel<<<blocks, 256, 0, st>>>(row_offsets, token_idx, heads, R, n_loc_full, jmin, 1, goffs, gtok, grow_);
-      ASPA_CHECK_LAUNCH();
+      if (!regroup_prepared) {   // else aspa_attn_regroup_rows has filled regroup_ws for these rows already
+        launch_regroup(row_offsets, token_idx, heads, R, at, total_rows, regroup_ws, st);
+        ASPA_CHECK_LAUNCH();
+      }
       AttnParams pa = p;
       pa.an_stride = R;
-      pa.an_window = an_window;
-      pa.an_jmin = jmin;
+      pa.an_window = at.an_window;
+      pa.an_jmin = at.jmin;
       pa.an_offsets = goffs;
       pa.an_tok = gtok;
       pa.an_row = grow_;

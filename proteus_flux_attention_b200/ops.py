@@ -278,12 +278,31 @@ def build_candidates(rows: torch.Tensor, row_batch: Optional[torch.Tensor], seq_
     return cand, lens
 
 
+def regroup_rows(plan: N.ShortlistPlan, dtype: torch.dtype, heads: int, T: int, D: int, row_offsets: torch.Tensor,
+                 token_idx: torch.Tensor, total_rows: int):
+    """The regrouping of the anchor tile pass of a planned attention call, ahead of the call (it needs the packed rows
+    and the plan, not q, k, v).  Returns (scratch, prepared) for ``gather_attn(regroup=...)``, or None when the plan
+    has no anchors."""
+    if not (plan.anchor_slots > 0 and plan.anchor_stride > 0 and USE_ANCHOR_TILES):
+        return None
+    rb = int(N.lib().aspa_attn_regroup_bytes(int(total_rows), heads, int(plan.anchor_stride)))
+    if rb <= 0:
+        return None
+    ws = _empty((rb,), torch.uint8, row_offsets.device)
+    prepared = C.c_int32(0)
+    with _timed('regroup_rows', 3, 0):
+        N.check(N.lib().aspa_attn_regroup_rows(N.dtype_code(dtype), heads, int(T), int(D), N.ptr(row_offsets),
+                                               N.ptr(token_idx), int(total_rows), C.byref(plan), N.ptr(ws),
+                                               C.byref(prepared), N.stream()), "attn_regroup_rows")
+    return ws, int(prepared.value)
+
+
 def gather_attn(q, k, v, *, scales: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]], H: int,
                 row_offsets: torch.Tensor, token_idx: torch.Tensor, max_rows: int, total_rows: int,
                 cand: Optional[torch.Tensor] = None, cand_len: Optional[torch.Tensor] = None,
                 plan: Optional[N.ShortlistPlan] = None, add_mask: Optional[torch.Tensor] = None,
                 out: torch.Tensor, out_layout: int, out_row_map: Optional[torch.Tensor] = None,
-                kv_layout: Optional[N.KVLayout] = None):
+                kv_layout: Optional[N.KVLayout] = None, regroup=None):
     """Launch the attention kernels; `out` must be zero-filled by the caller.  ``out_row_map`` (B*T int32)
     redirects token-major output rows to compact slots.  With ``kv_layout`` k and v are any tensors holding the
     rows at those element strides (q stays (heads, T, D))."""
@@ -292,8 +311,10 @@ def gather_attn(q, k, v, *, scales: Optional[Tuple[torch.Tensor, torch.Tensor, t
     nbytes = int(N.lib().aspa_attn_workspace_bytes(int(total_rows), D))
     if plan is not None and cand is None and nbytes > 0:
         ws = _empty((nbytes,), torch.uint8, q.device)
-    regroup = None
-    if ws is not None and plan.anchor_slots > 0 and plan.anchor_stride > 0 and USE_ANCHOR_TILES:
+    prepared = 0
+    if regroup is not None:
+        regroup, prepared = regroup
+    elif ws is not None and plan.anchor_slots > 0 and plan.anchor_stride > 0 and USE_ANCHOR_TILES:
         rb = int(N.lib().aspa_attn_regroup_bytes(int(total_rows), heads, int(plan.anchor_stride)))
         if rb > 0:
             regroup = _empty((rb,), torch.uint8, q.device)
@@ -305,12 +326,12 @@ def gather_attn(q, k, v, *, scales: Optional[Tuple[torch.Tensor, torch.Tensor, t
     # algorithmic bytes: each active row's q once, every key and value row once, each active output row once
     nbytes = int(total_rows) * D * (e + out.element_size()) + 2 * heads * T * D * e
     with _timed("attention", 2 if two_pass else 1, nbytes):
-        N.check(N.lib().aspa_gather_attn_fwd_ex(
+        N.check(N.lib().aspa_gather_attn_fwd_prepared(
             N.ptr(q), N.ptr(k), N.ptr(v), N.dtype_code(q.dtype), N.ptr(qs), N.ptr(ks), N.ptr(vs), heads, T, D, int(H),
             N.ptr(row_offsets), N.ptr(token_idx), int(max_rows), int(total_rows), N.ptr(cand), N.ptr(cand_len), int(L),
             C.byref(plan) if plan is not None else None, N.ptr(add_mask), N.ptr(out), N.dtype_code(out.dtype),
             int(out_layout), N.ptr(out_row_map), C.byref(kv_layout) if kv_layout is not None else None, N.ptr(ws),
-            N.ptr(regroup), N.stream()), "gather_attn_fwd")
+            N.ptr(regroup), int(prepared), N.stream()), "gather_attn_fwd")
     return out
 
 

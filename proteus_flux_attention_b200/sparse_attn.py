@@ -113,14 +113,14 @@ def attention_packed(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, row_o
                      scales=None, cand=None, cand_len=None, plan=None, add_mask=None,
                      out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
                      out_layout: int = N.OUT_HEAD_MAJOR, out_row_map: Optional[torch.Tensor] = None,
-                     kv_layout=None) -> torch.Tensor:
+                     kv_layout=None, regroup=None) -> torch.Tensor:
     """Internal entry used by the layer: rows already packed on the device."""
     heads, T, D = q.shape
     if out is None:
         out = torch.zeros((heads, T, D), dtype=out_dtype or q.dtype, device=q.device)
     ops.gather_attn(q, k, v, scales=scales, H=H, row_offsets=row_offsets, token_idx=token_idx, max_rows=max_rows,
                     total_rows=total_rows, cand=cand, cand_len=cand_len, plan=plan, add_mask=add_mask, out=out,
-                    out_layout=out_layout, out_row_map=out_row_map, kv_layout=kv_layout)
+                    out_layout=out_layout, out_row_map=out_row_map, kv_layout=kv_layout, regroup=regroup)
     return out
 
 
