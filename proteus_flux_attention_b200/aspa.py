@@ -597,8 +597,7 @@ class AdaptiveSparseAttention(nn.Module):
 
     def _fork_qkv_quantize(self, x: torch.Tensor) -> dict:
         """Fused QKV projection, RoPE, head-major split and per-head INT8 quantisation of one call on the second
-        stream (see ``_fork_kv_projection``).  The results are used on the calling stream; they are marked as such
-        for the caching allocator."""
+        stream (see ``_fork_kv_projection``).  The results are allocated on the calling stream, where they are used."""
         B, T, C = x.shape
         H, D = self.h_total, self.d_head
         dev = x.device
@@ -613,11 +612,10 @@ class AdaptiveSparseAttention(nn.Module):
         ready, done = torch.cuda.Event(), torch.cuda.Event()
         ready.record(main)
         side.wait_event(ready)
+        pack = ops.rope_quantize_outputs(B, T, H, D, dev)   # on the calling stream, where they are used
         with torch.cuda.stream(side):
-            pack = ops.rope_quantize(self.qkv(x).contiguous(), H, D, cos, sin)
+            ops.rope_quantize(self.qkv(x).contiguous(), H, D, cos, sin, out=pack)
             done.record(side)
-        for t_ in pack:
-            t_.record_stream(main)
         return {"pack": pack, "done": done}
 
     def _project_compact_q(self, x: torch.Tensor, compact: dict) -> torch.Tensor:

@@ -537,14 +537,18 @@ def chunk_select_slot(importance: torch.Tensor, token_mask: Optional[torch.Tenso
                                                N.ptr(rec_count), N.stream()), "chunk_select_slot")
 
 
-def rope_quantize(qkv: torch.Tensor, H: int, D: int, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor]):
+def rope_quantize_outputs(B: int, T: int, H: int, D: int, dev: torch.device):
+    """(q8, k8, v8, scales) for ``rope_quantize(out=...)``, allocated on the current stream."""
+    q8 = _empty((B * H, T, D), torch.int8, dev)
+    return q8, torch.empty_like(q8), torch.empty_like(q8), _empty((3, B * H), torch.float32, dev)
+
+
+def rope_quantize(qkv: torch.Tensor, H: int, D: int, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], out=None):
     """Fused bf16 projection (B, T, 3*H*D) -> rotated, head-major INT8 q, k, v (B*H, T, D) and their per-head scales."""
     B, T, _ = qkv.shape
     dev = qkv.device
-    q8 = _empty((B * H, T, D), torch.int8, dev)
-    k8, v8 = torch.empty_like(q8), torch.empty_like(q8)
+    q8, k8, v8, scales = out if out is not None else rope_quantize_outputs(B, T, H, D, dev)
     amax = _empty((3, B * H), torch.float32, dev)
-    scales = _empty((3, B * H), torch.float32, dev)
     with _timed('rope_quantize', 3, 2 * _nb(qkv) + _nb(q8, k8, v8)):
         N.check(N.lib().aspa_rope_quantize(N.ptr(qkv), B, T, H, D, N.ptr(cos), N.ptr(sin), N.ptr(q8), N.ptr(k8), N.ptr(v8),
                                            N.ptr(amax), N.ptr(scales), N.stream()), "rope_quantize")

@@ -406,3 +406,34 @@ def test_chunked_pipeline_graph_replay_equals_eager(dev):
         assert torch.equal(got.final_output.cpu(), want.final_output.cpu())
     with pytest.raises(ValueError, match="freeze_prototypes"):
         P.ChunkedShortlistConfig(**{**base, "freeze_prototypes": False}, use_cuda_graph=True).validate()
+
+
+def test_captured_layer_call_equals_eager(dev):
+    """A layer call replayed from a captured graph gives what the eager call gives, state updates included (the
+    prototype EMA moves with every replay); a call that must wait for the host refuses to be captured."""
+    import proteus_flux_attention_b200 as P
+    cfg = dict(d_model=256, n_head=4, attn_h_total=4, attn_gates=8, attn_h_active=2, attn_h_active_min=2,
+               attn_h_active_max=2, attn_token_sparse=True, attn_token_keep_ratio=0.3, attn_router_top_p=0.0,
+               attn_mode="linear", attn_linear_L=96, attn_linear_window=64, attn_linear_anchor_stride=16, n_ctx=2048,
+               attn_track_latency=False, attn_proto_enable=True, attn_quantize_int8=True)
+    torch.manual_seed(5)
+    make = lambda c: P.AdaptiveSparseProtoAttention(P.ModelConfig(**c)).to(torch.bfloat16).to(dev).eval()  # noqa: E731
+    a = make(cfg)
+    b = make(cfg)
+    b.load_state_dict(a.state_dict())
+    g = torch.Generator().manual_seed(6)
+    xs = [torch.randn(2, 1536, 256, generator=g).to(torch.bfloat16).to(dev) for _ in range(3)]
+    call = P.CapturedLayerCall(b, xs[0])
+    assert all(torch.equal(v, b.state_dict()[k]) for k, v in a.state_dict().items())   # capture left the state alone
+    for x in xs:
+        want = a(x)
+        got = call(x).clone()
+        assert torch.equal(got, want)
+        assert torch.equal(a.routing_prototypes, b.routing_prototypes)
+        assert a.last_head_stats["top_k"] == b.last_head_stats["top_k"]
+        assert a._last_sparse_state["mode"] == b._last_sparse_state["mode"] == "shortlist"
+    with pytest.raises(ValueError):
+        call(xs[0][:, :100])
+    slow = make(dict(cfg, attn_mode="auto", attn_linear_switch_ctx=4000, attn_quantize_int8=False))   # alpha < 0.95
+    with pytest.raises(RuntimeError, match="cannot be captured"):
+        P.CapturedLayerCall(slow, xs[0])
