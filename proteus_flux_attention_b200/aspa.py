@@ -937,6 +937,17 @@ class AdaptiveSparseAttention(nn.Module):
                                                             self.routing_usage_ema, self.routing_confidence)
         runtime = self._prepare_linear_runtime(T, B, alpha)
         plan_args = self._plan_shape(runtime, T, sim is not None)
+        # Can this call turn dense at all?  Not at alpha >= 0.95 (aspa.py:1636-1639); below that the reference goes
+        # dense on alpha <= cutoff (without INT8), on a row density at or above the threshold, or when every
+        # (head, token) row is active (aspa.py:1625-1635) - and with host-side bounds on the kept tokens and on k
+        # all three can often be ruled out before any kernel has run.  Then the call needs no row counts on the host:
+        # it sizes its grids from the bounds and can be captured into a CUDA graph.
+        thr = self._density_threshold()
+        never_dense = alpha >= 0.95 or (
+            (alpha > self.dense_alpha_cutoff or self.quantize_sparse_int8)
+            and (thr is None or float(kept_bound) / float(max(1, T)) < thr)
+            and (kept_bound < T or k_bound < H or not self.force_dense_when_full))
+        lazy = never_dense and bound_known and plan_args is not None
         early_lists = None
         if plan_args is not None and plan_args[2] > 0:
             early_lists = ops.proto_plan(self._last_token_similarity.contiguous(), plan_args[2])
@@ -945,7 +956,7 @@ class AdaptiveSparseAttention(nn.Module):
         if plan_args is not None:
             early_plan = ops.make_plan(plan_args[0], plan_args[1], runtime["anchor_stride"], plan_args[2],
                                        *(early_lists if early_lists is not None else (None, None)))
-            if alpha >= 0.95 and bound_known:   # row counts are host-side bounds: the anchor regrouping can go now too
+            if lazy:   # row counts are host-side bounds: the anchor regrouping can go now too
                 early_regroup = ops.regroup_rows(early_plan, torch.int8 if use_quant else x.dtype, B * H, T, D,
                                                  row_offsets, token_idx, B * kept_bound * k_bound)
 
@@ -974,7 +985,6 @@ class AdaptiveSparseAttention(nn.Module):
 
         # The mode decision needs row counts — unless alpha >= 0.95, where the reference never goes dense
         # (aspa.py:1636-1639): then the call runs without waiting for the record, on host-side bounds.
-        lazy = alpha >= 0.95 and bound_known and plan_args is not None
         if compact is not None:
             out = torch.zeros((compact["slots"], C), dtype=x.dtype, device=dev)
             row_map = compact["slot_of"]

@@ -434,6 +434,13 @@ def test_captured_layer_call_equals_eager(dev):
         assert a._last_sparse_state["mode"] == b._last_sparse_state["mode"] == "shortlist"
     with pytest.raises(ValueError):
         call(xs[0][:, :100])
-    slow = make(dict(cfg, attn_mode="auto", attn_linear_switch_ctx=4000, attn_quantize_int8=False))   # alpha < 0.95
+    # alpha < 0.95 alone does not stop a capture (a kept-token bound below the density threshold rules dense out) ...
+    auto = make(dict(cfg, attn_mode="auto", attn_linear_switch_ctx=4000, attn_quantize_int8=False))
+    ref_auto = make(dict(cfg, attn_mode="auto", attn_linear_switch_ctx=4000, attn_quantize_int8=False))
+    ref_auto.load_state_dict(auto.state_dict())
+    call_auto = P.CapturedLayerCall(auto, xs[0])
+    assert torch.equal(call_auto(xs[1]), ref_auto(xs[1])) and 0.0 < auto._current_alpha < 0.95
+    # ... a keep threshold does: how many tokens survive is then only known on the device
+    slow = make(dict(cfg, attn_token_keep_threshold=0.5))
     with pytest.raises(RuntimeError, match="cannot be captured"):
         P.CapturedLayerCall(slow, xs[0])
