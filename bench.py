@@ -142,6 +142,24 @@ NCU_DRAM_BYTES_PER_LAUNCH = {
 }
 
 
+def bind_to_gpu_node(index: int):
+    """Pin this process to the CPUs NVML reports as local to GPU `index` (read-only query), so that the pinned host
+    buffers of a rank are first touched on the NUMA node its GPU hangs off.  Returns the CPU count, or None."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(index)
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (os.cpu_count() + 63) // 64)
+        cpus = {64 * w + b for w, word in enumerate(words) for b in range(64) if (int(word) >> b) & 1}
+        cpus &= set(os.sched_getaffinity(0))
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+            return len(cpus)
+    except Exception:
+        pass
+    return None
+
+
 def peak_hbm():
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
@@ -396,6 +414,9 @@ def main():
     ap.add_argument("--clock-sampler", default="nvml", choices=["nvml", "smi", "none"],
                     help="how SM clocks / throttle reasons are sampled during the timed region")
     ap.add_argument("--clock-period-ms", type=int, default=20)
+    ap.add_argument("--bind-numa", action="store_true",
+                    help="multi-GPU runs: pin each rank to the CPUs NVML reports as local to its GPU before the pinned "
+                         "host buffers of the end-to-end measurement are allocated (off by default)")
     ap.add_argument("--profile-mode", action="store_true",
                     help="for runs under a profiler: exactly --warmup + --steps passes, no timing pass, e2e or CPU baseline")
     args = ap.parse_args()
@@ -425,6 +446,7 @@ def main():
     _native.lib()  # no fallback: fail here if the CUDA library is missing
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
+    cpu_affinity = bind_to_gpu_node(local_rank) if (world > 1 and args.bind_numa) else None
     group = None
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
@@ -435,6 +457,8 @@ def main():
         if world > 1:
             raise SystemExit("layer workloads do not shard: run them with --gpus 1 (replicas only)")
         wl = RouterWorkload(device) if args.workload == "router_64k" else LayerWorkload(args.workload, device)
+    if cpu_affinity is not None:
+        wl.config["host_binding"] = f"each rank pinned to the {cpu_affinity} CPUs local to its GPU (NVML affinity)"
 
     def sync():
         if world > 1:
