@@ -137,7 +137,7 @@ class ClockSampler:
 # of the chunked_1m workload, from ncu captures on B200 (summaries: profiles/ncu_traffic_chunked_1m_kernels.md, profiles/ncu_full_attn_rows64_chunked_1m.md,
 # profiles/ncu_full_router_tc_65536x1024.md).
 NCU_DRAM_BYTES_PER_LAUNCH = {
-    "chunked_1m": {"attention": 248.2e6, "rope_inplace": 226.2e6, "router_tc": 138.5e6, "scatter_rows_fill": 78.0e6,
+    "chunked_1m": {"attention": 245.4e6, "rope_inplace": 234.8e6, "router_tc": 134.9e6, "scatter_rows_fill": 78.4e6,
                    "token_select": 0.3e6},
 }
 
