@@ -3,7 +3,7 @@
 Run in the development container, where the reference source tree is
 mounted read-only:
 
-    PROTEUS_REF_SRC=<reference>/src python tests/golden/make_golden.py
+    PROTEUS_REF_SRC=<reference>/src python tests/golden/make_golden.py [--memory-only]
 
 The reference is imported unmodified from PROTEUS_REF_SRC.  Every case stores
 the seeded inputs, the module weights and the outputs the reference produced,
@@ -18,7 +18,9 @@ from pathlib import Path
 
 import torch
 
-REF = os.environ.get("PROTEUS_REF_SRC", "/root/reference/src")
+REF = os.environ.get("PROTEUS_REF_SRC")
+if not REF:
+    raise SystemExit("set PROTEUS_REF_SRC to the src directory of the reference project")
 sys.path.insert(0, REF)
 
 import proteus_attention.kernels.sparse_attn as sa  # noqa: E402
