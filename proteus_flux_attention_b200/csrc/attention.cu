@@ -543,16 +543,23 @@ template <>
 __device__ __forceinline__ uint4 load_chunk<__nv_bfloat16>(const __nv_bfloat16* row, int chunk) {
   return reinterpret_cast<const uint4*>(row)[chunk];
 }
+// Two int8 values (bytes 2*pair and 2*pair+1 of `flipped`, a word whose bytes have had their sign bits flipped) as a
+// bf16 pair, without I2F or F2F: each byte goes into the mantissa of 2^23, 8388736 comes off, and the upper half of
+// the resulting fp32 IS the bf16 (an integer of magnitude <= 128 needs at most 8 significant bits).
+__device__ __forceinline__ uint32_t i8x2_to_bf16x2(uint32_t flipped, int pair) {
+  const float a = __uint_as_float(__byte_perm(flipped, 0x4B000000u, 0x7440u + 2 * pair)) - 8388736.0f;
+  const float b = __uint_as_float(__byte_perm(flipped, 0x4B000000u, 0x7441u + 2 * pair)) - 8388736.0f;
+  return __byte_perm(__float_as_uint(a), __float_as_uint(b), 0x7632u);
+}
+__device__ __forceinline__ uint4 i8x8_to_bf16x8(uint32_t lo, uint32_t hi) {
+  lo ^= 0x80808080u;
+  hi ^= 0x80808080u;
+  return make_uint4(i8x2_to_bf16x2(lo, 0), i8x2_to_bf16x2(lo, 1), i8x2_to_bf16x2(hi, 0), i8x2_to_bf16x2(hi, 1));
+}
 template <>
 __device__ __forceinline__ uint4 load_chunk<int8_t>(const int8_t* row, int chunk) {
   const uint2 raw = reinterpret_cast<const uint2*>(row)[chunk];
-  const int8_t* b = reinterpret_cast<const int8_t*>(&raw);
-  uint4 o;
-  o.x = pack_bf16((float)b[0], (float)b[1]);
-  o.y = pack_bf16((float)b[2], (float)b[3]);
-  o.z = pack_bf16((float)b[4], (float)b[5]);
-  o.w = pack_bf16((float)b[6], (float)b[7]);
-  return o;
+  return i8x8_to_bf16x8(raw.x, raw.y);
 }
 
 constexpr int WK_TILE_BYTES = WK_KEYS * 128;  // one 64-key K or V tile in shared memory
@@ -730,12 +737,7 @@ __global__ void __launch_bounds__(128) attn_window_kernel(const AttnParams p) {
         const int c = tid + 128 * i;
         const int row = c >> 2, rc = c & 3;
         const uint4 raw = *reinterpret_cast<const uint4*>(rk + which * RAW_TILE + row * 64 + rc * 16);
-        const int8_t* bq = reinterpret_cast<const int8_t*>(&raw);
-        uint4 lo, hi;
-        lo.x = pack_bf16((float)bq[0], (float)bq[1]);   lo.y = pack_bf16((float)bq[2], (float)bq[3]);
-        lo.z = pack_bf16((float)bq[4], (float)bq[5]);   lo.w = pack_bf16((float)bq[6], (float)bq[7]);
-        hi.x = pack_bf16((float)bq[8], (float)bq[9]);   hi.y = pack_bf16((float)bq[10], (float)bq[11]);
-        hi.z = pack_bf16((float)bq[12], (float)bq[13]); hi.w = pack_bf16((float)bq[14], (float)bq[15]);
+        const uint4 lo = i8x8_to_bf16x8(raw.x, raw.y), hi = i8x8_to_bf16x8(raw.z, raw.w);
         *reinterpret_cast<uint4*>(dk + which * WK_TILE_BYTES + swz(row, 2 * rc)) = lo;
         *reinterpret_cast<uint4*>(dk + which * WK_TILE_BYTES + swz(row, 2 * rc + 1)) = hi;
       }
