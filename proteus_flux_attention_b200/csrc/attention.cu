@@ -402,7 +402,7 @@ __device__ __forceinline__ void r64_issue_keys(const T* kh, int64_t k_ts, int id
 }
 
 template <typename T>
-__global__ void __launch_bounds__(GEN_WARPS * 32, 4) attn_rows64_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(GEN_WARPS * 32, 3) attn_rows64_kernel(const AttnParams p) {
   constexpr int ROWB = 64 * sizeof(T), PITCH = ROWB + R64_PITCH_PAD, WARP_BYTES = 32 * PITCH + ROWB;
   extern __shared__ __align__(16) unsigned char r64_smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
