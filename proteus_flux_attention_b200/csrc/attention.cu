@@ -447,18 +447,18 @@ __global__ void __launch_bounds__(GEN_WARPS * 32, 3) attn_rows64_kernel(const At
     {
       const uint4* krow = reinterpret_cast<const uint4*>(tile + lane * PITCH);
       if (sizeof(T) == 2) {
-        float a = 0.f;
+        // bf16 -> fp32 is a 16-bit shift; even and odd channels accumulate side by side in one packed fp32 FMA
+        float2 a2 = make_float2(0.f, 0.f);
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
           const uint4 raw = krow[c], qraw = qrow[c];
           const uint32_t kw[4] = {raw.x, raw.y, raw.z, raw.w}, qw[4] = {qraw.x, qraw.y, qraw.z, qraw.w};
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {   // bf16 -> fp32 is a 16-bit shift; same product order as dot_row
-            a = fmaf(__uint_as_float(kw[i] << 16), __uint_as_float(qw[i] << 16), a);
-            a = fmaf(__uint_as_float(kw[i] & 0xffff0000u), __uint_as_float(qw[i] & 0xffff0000u), a);
-          }
+          for (int i = 0; i < 4; ++i)
+            a2 = __ffma2_rn(make_float2(__uint_as_float(kw[i] << 16), __uint_as_float(kw[i] & 0xffff0000u)),
+                            make_float2(__uint_as_float(qw[i] << 16), __uint_as_float(qw[i] & 0xffff0000u)), a2);
         }
-        if (idx >= 0) s = a * sc;
+        if (idx >= 0) s = (a2.x + a2.y) * sc;
       } else {
         int a = 0;
 #pragma unroll
@@ -493,8 +493,13 @@ __global__ void __launch_bounds__(GEN_WARPS * 32, 3) attn_rows64_kernel(const At
       const int ic = max(__shfl_sync(0xffffffffu, idx_cur, st * 4 + grp), 0);
       float vv[8];
       load_vec<T>(vh + (int64_t)ic * v_ts + sub * 8, vv);
+      const float2 pc2 = make_float2(pc, pc);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) acc[e] = fmaf(pc, vv[e], acc[e]);
+      for (int e = 0; e < 8; e += 2) {   // packed fp32 FMA: two channels per instruction, each rounded as before
+        const float2 r2 = __ffma2_rn(pc2, make_float2(vv[e], vv[e + 1]), make_float2(acc[e], acc[e + 1]));
+        acc[e] = r2.x;
+        acc[e + 1] = r2.y;
+      }
     }
   }
 #pragma unroll
