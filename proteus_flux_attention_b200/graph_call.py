@@ -27,7 +27,7 @@ class CapturedLayerCall:
         self.static_in = example.detach().clone()
         stream = torch.cuda.Stream(device=example.device, priority=priority)
         stream.wait_stream(torch.cuda.current_stream())
-        state = {k: v.detach().clone() for k, v in layer.state_dict().items()}
+        state = {n: b.detach().clone() for n, b in layer.named_buffers()}   # EMAs, memory bank: a call moves them
         with torch.no_grad(), torch.cuda.stream(stream):   # eager warm-up on a side stream, as graph capture requires
             for _ in range(2):
                 layer(self.static_in)
@@ -35,7 +35,7 @@ class CapturedLayerCall:
         torch.cuda.synchronize(example.device)
         pending = layer.__dict__.get("_pending")
         if not (isinstance(pending, dict) and pending.get("lazy")):
-            layer.load_state_dict(state)
+            self._restore(state)
             raise RuntimeError("this layer call waits for row counts on the host (alpha < 0.95, a keep threshold, or "
                                "candidate pieces that may exceed L) and cannot be captured into a CUDA graph")
         self.graph = torch.cuda.CUDAGraph()
@@ -43,7 +43,12 @@ class CapturedLayerCall:
             self.static_out = layer(self.static_in)
         self._pending = layer.__dict__.get("_pending")
         torch.cuda.synchronize(example.device)
-        layer.load_state_dict(state)   # the warm-up and capture calls moved the prototype EMA; put the state back
+        self._restore(state)   # the warm-up and capture calls moved the state; put it back, in place
+
+    def _restore(self, state) -> None:
+        with torch.no_grad():
+            for n, b in self.layer.named_buffers():
+                b.copy_(state[n])
 
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
         if x.shape != self.static_in.shape or x.dtype != self.static_in.dtype:
