@@ -403,7 +403,7 @@ def cpu_oracle_sample(workload: str):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="chunked_1m", choices=["chunked_1m", "shortlist_256k", "sparse_16k", "router_64k"])
