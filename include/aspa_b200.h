@@ -82,6 +82,23 @@ int aspa_router_fwd_tc(const void* x, int64_t n, int C, const void* w_router, in
                        float* importance, float* proto_sim, float* blend, float* stat_partials, void* scratch,
                        int32_t* status, void* stream);
 
+/* Read (and with reset != 0 clear) the status word a device-side bounded wait raises.  Synchronises `stream`.
+ * Returns ASPA_OK when the word is zero, else ASPA_ERR_TIMEOUT with aspa_last_error_string() naming the wait that
+ * ran out; the outputs of the call that raised it are invalid.  The reference has no device-side waits; its
+ * counterpart is the RuntimeWarning + fallback around a failed native launch (sa.py:1524-1525), which this
+ * implementation turns into an error because it has no fallback. */
+int aspa_read_status(int32_t* status, int reset, void* stream);
+
+/* aspa_router_fwd_tc with the two knobs a test needs to see a bounded wait run out without faulting the device:
+ * `spin_limit` (>= 1024) replaces the built-in iteration limit of every wait, and the producer skips the copy of the
+ * first k-block of tile `withhold_tile` (-1: none), so the consumers of that stage give up, the kernel frees its
+ * tensor memory and returns with *status != 0.  Fixed prototype parameters (temp 0.3, threshold 0.2, blend 0.5),
+ * no usage bias, no statistics.  No counterpart in the reference. */
+int aspa_router_fwd_tc_probe(const void* x, int64_t n, int C, const void* w_router, int G, const float* proto_hat,
+                             const float* conf_eps, float* gate_probs, float* importance, float* proto_sim,
+                             float* blend, void* scratch, int32_t* status, uint32_t spin_limit, int64_t withhold_tile,
+                             void* stream);
+
 /* L2-normalise the G prototype rows (F.normalize(..., eps=1e-6), aspa.py:639-640). */
 int aspa_normalize_rows(const float* src, int rows, int cols, float eps, float* dst, void* stream);
 

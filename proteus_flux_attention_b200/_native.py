@@ -41,6 +41,8 @@ SIGNATURES = {
     "aspa_router_fwd": (_i, [_p, _i, _l, _i, _p, _i, _p, _p, _p, _f, _f, _f, _f, _f, _p, _p, _p, _p, _p, _p]),
     "aspa_router_tc_scratch_bytes": (_l, [_i, _i, _i]),
     "aspa_router_fwd_tc": (_i, [_p, _l, _i, _p, _i, _p, _p, _p, _f, _f, _f, _f, _f, _p, _p, _p, _p, _p, _p, _p, _p]),
+    "aspa_read_status": (_i, [_p, _i, _p]),
+    "aspa_router_fwd_tc_probe": (_i, [_p, _l, _i, _p, _i, _p, _p, _p, _p, _p, _p, _p, _p, C.c_uint32, _l, _p]),
     "aspa_normalize_rows": (_i, [_p, _i, _i, _f, _p, _p]),
     "aspa_token_select": (_i, [_p, _i, _i, _i, _f, _i, _p, _p, _p]),
     "aspa_head_budget": (_i, [_p, _l, _i, _p, _i, _d, _i, _i, _i, _d, _p, _p, _p]),
@@ -116,7 +118,16 @@ def last_error() -> str:
     return lib().aspa_last_error_string().decode("utf-8", "replace")
 
 
+ERR_TIMEOUT = -4
+
+
+class DeviceWaitTimeout(RuntimeError):
+    """A bounded device-side wait ran out (status ASPA_ERR_TIMEOUT); the outputs of that call are invalid."""
+
+
 def check(rc: int, what: str) -> None:
+    if rc == ERR_TIMEOUT:
+        raise DeviceWaitTimeout(f"{what}: {last_error()}")
     if rc != 0:
         raise RuntimeError(f"{what} failed with status {rc}: {last_error()}")
 

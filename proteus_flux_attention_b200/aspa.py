@@ -175,6 +175,8 @@ class AdaptiveSparseAttention(nn.Module):
         inv_freq = 1.0 / (self.rope_base ** (torch.arange(0, self.d_head, 2, dtype=torch.float32) / max(self.d_head, 1)))
         self.register_buffer("_rope_inv_freq", inv_freq, persistent=False)
         self._rope_cache: Dict[Tuple[str, int, str], Tuple[int, torch.Tensor, torch.Tensor]] = {}
+        self._rope_retired: list = []   # outgrown tables, kept alive for graphs captured with them
+        self._n_ctx_hint = int(g("n_ctx", 0) or 0)
 
         self.dropout = nn.Dropout(config.p_dropout)
         self.use_sdpa = bool(g("use_sdpa", True))
@@ -527,8 +529,15 @@ class AdaptiveSparseAttention(nn.Module):
         key = (device.type, int(device.index) if device.index is not None else -1, str(dtype))
         cached = self._rope_cache.get(key)
         if cached is None or cached[0] < seq_len:
-            cos, sin = ops.rope_table(self._rope_inv_freq.to(device), seq_len, self.d_head, dtype)
-            cached = (seq_len, cos, sin)
+            # A captured CUDA graph holds the raw address of the table it was captured with, so a table that is
+            # outgrown is retired, never freed: it stays alive for as long as the layer does.  The first table
+            # already spans the configured context, which makes growth the exception.
+            if cached is not None:
+                self._rope_retired.append(cached)
+            span = max(seq_len, self._n_ctx_hint) if cached is None else seq_len
+            span = min(span, max(seq_len, 1 << 20))
+            cos, sin = ops.rope_table(self._rope_inv_freq.to(device), span, self.d_head, dtype)
+            cached = (span, cos, sin)
             self._rope_cache[key] = cached
         return cached[1][:seq_len], cached[2][:seq_len]
 
@@ -717,6 +726,21 @@ class AdaptiveSparseAttention(nn.Module):
         info = self._decode_record(ctx)
         self._publish(ctx, info, force_dense=False, dense_reason=None, exec_mode=ctx["exec_mode"])
 
+    def check_previous_call(self) -> None:
+        """A call that runs without waiting for the host (lazy telemetry, graph replay) cannot report an expired
+        device-side wait of its own router; the pinned record it left behind can.  Called at the start of the next
+        call and by ``CapturedLayerCall``: reads one word of pinned memory, never waits; raises ``DeviceWaitTimeout``
+        (after clearing the device word) if the previous call's router gave up, because what that call returned was
+        built on unwritten gate probabilities."""
+        ctx = self.__dict__.get("_pending")
+        if ctx is None or ctx.get("pin") is None or torch.cuda.is_current_stream_capturing():
+            return
+        if ctx["event"] is not None and not ctx["event"].query():
+            return
+        slot = ctx["B"] * self.h_total + 1 + ctx["B"] + 7
+        if slot < ctx["pin"].numel() and int(ctx["pin"][slot]) != 0:
+            ops.check_router_status(ctx["device"])
+
     def _decode_record(self, ctx: dict) -> dict:
         rec = ctx["pin"].tolist()
         B, T, H = ctx["B"], ctx["T"], self.h_total
@@ -726,6 +750,7 @@ class AdaptiveSparseAttention(nn.Module):
         p0 = nbh + 1 + B
         counts = [offs[i + 1] - offs[i] for i in range(nbh)]
         if int(rec[p0 + 7]) != 0:
+            ops.check_router_status(ctx["device"])   # raises DeviceWaitTimeout and clears the device word
             raise RuntimeError("the tensor-core router reported an expired device-side wait; its outputs are invalid")
         return {"offs": offs, "kept": kept, "topk": int(rec[p0]), "adaptive": int(rec[p0 + 1]), "score_sum": rec[p0 + 2],
                 "entropy_sum": rec[p0 + 3], "sim_sum": rec[p0 + 4], "bs_sum": rec[p0 + 5], "bs_pos": rec[p0 + 6],
@@ -800,6 +825,7 @@ class AdaptiveSparseAttention(nn.Module):
         B, T, C = x.shape
         dev = x.device
         H, D, G = self.h_total, self.d_head, self.attn_gates
+        self.check_previous_call()
         self.__dict__["_pending"] = None
         self.last_aux_loss = None
         self._last_token_importance = self._last_token_mask = self._last_token_blend = None

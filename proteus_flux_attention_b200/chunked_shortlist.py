@@ -448,6 +448,24 @@ class ChunkedShortlistRunner:
     def run(self, sequence: Optional[torch.Tensor] = None, *, chunk_state: Optional[Dict[str, torch.Tensor]] = None,
             final_state: Optional[Dict[str, torch.Tensor]] = None, warmup_input: Optional[torch.Tensor] = None,
             sequence_is_local_shard: bool = False) -> ChunkedShortlistResult:
+        """Run both passes (see ``_run``).  Without ``cache_layers`` the layers are built afresh on every call, so
+        whatever was captured against them - graphs, record buffers - lives for this call only: a graph replayed
+        after its layer is gone would read freed weights."""
+        if self._layer_cache is not None:
+            return self._run(sequence, chunk_state=chunk_state, final_state=final_state, warmup_input=warmup_input,
+                             sequence_is_local_shard=sequence_is_local_shard)
+        self.__dict__["_graph_tmp"] = {}
+        try:
+            return self._run(sequence, chunk_state=chunk_state, final_state=final_state, warmup_input=warmup_input,
+                             sequence_is_local_shard=sequence_is_local_shard)
+        finally:
+            if torch.device(self.config.device).type == "cuda":   # nothing of this call is still replaying
+                torch.cuda.synchronize(torch.device(self.config.device))
+            self.__dict__.pop("_graph_tmp", None)
+
+    def _run(self, sequence: Optional[torch.Tensor] = None, *, chunk_state: Optional[Dict[str, torch.Tensor]] = None,
+             final_state: Optional[Dict[str, torch.Tensor]] = None, warmup_input: Optional[torch.Tensor] = None,
+             sequence_is_local_shard: bool = False) -> ChunkedShortlistResult:
         """Run both passes.  ``sequence``: (1, T, C) on the host or the device; ``None`` generates seeded noise as
         the reference does.  ``chunk_state`` / ``final_state`` optionally supply the layers' ``state_dict`` (the
         reference draws fresh random weights inside ``run``; ranks of a sharded run must agree on them).  With
@@ -613,7 +631,13 @@ class ChunkedShortlistRunner:
             if st:
                 final_stats["sparse_state"] = _sanitize_mapping(st)
         ev_c.record()
+        status_pin = self.__dict__.get("_status_pin")
+        if status_pin is None:
+            status_pin = self.__dict__["_status_pin"] = torch.zeros(1, dtype=torch.int32, pin_memory=True)
+        status_pin.copy_(ops.router_status(device), non_blocking=True)
         torch.cuda.synchronize(device)
+        if int(status_pin.item()) != 0:   # a bounded wait ran out in some chunk's router: nothing of this run is valid
+            ops.check_router_status(device)
         t1 = time.perf_counter()
         chunk_time_ms = float(ev_a.elapsed_time(ev_b))
         if cfg.run_final_pass:

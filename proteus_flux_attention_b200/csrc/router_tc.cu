@@ -88,8 +88,8 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 // Bounded wait: returns false when the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (uint32_t it = 0; it < TC_SPIN_LIMIT; ++it) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t limit = TC_SPIN_LIMIT) {
+  for (uint32_t it = 0; it < limit; ++it) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
@@ -147,7 +147,8 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                  const float* __restrict__ usage_bias, float proto_temp, float proto_threshold, float proto_span,
                  float proto_blend, float usage_boost, float* __restrict__ gate_probs,
                  float* __restrict__ importance, float* __restrict__ proto_sim, float* __restrict__ blend,
-                 float* __restrict__ stat_partials, int* __restrict__ status, const TcPlan plan) {
+                 float* __restrict__ stat_partials, int* __restrict__ status, const TcPlan plan,
+                 const uint32_t spin, const int64_t withhold_tile) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int S = plan.stages;
@@ -199,7 +200,7 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
   if (warp == 12) {
     // ---- TMA producer ------------------------------------------------------------------------------------
     if (lane == 0) {
-      uint32_t it = 0;
+      uint32_t it = 0, withheld = 0xffffffffu;
       bool ok = true;
       const uint32_t w_tile = (uint32_t)N * TC_BK * 2;
       if (plan.w_resident) {  // the whole weight operand, once: num_k tiles of N x 64 on one barrier
@@ -211,19 +212,24 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
           const int s = (int)(it % (uint32_t)S);
           const uint32_t ph = (it / (uint32_t)S) & 1u;
           if (aborted(abort_flag)) { ok = false; break; }
-          if (!mbar_wait(empty0 + 8 * s, ph ^ 1u)) { atomicExch(abort_flag, 1); atomicExch(status, 1); ok = false; break; }
+          if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, spin)) { atomicExch(abort_flag, 1); atomicExch(status, 1); ok = false; break; }
           const uint32_t a_dst = s_addr(smem + s * plan.stage_bytes), b_dst = a_dst + TC_A_BYTES;
+          if (tile == withhold_tile && kb == 0) {   // test hook: this stage is never filled, its consumers must give up
+            withheld = it;
+            continue;
+          }
           mbar_expect_tx(full0 + 8 * s, TC_A_BYTES + (plan.w_resident ? 0u : w_tile));
           tma_load_2d(a_dst, &tmap_x, kb * TC_BK, (int)(tile * TC_BM), full0 + 8 * s);
           if (!plan.w_resident) tma_load_2d(b_dst, &tmap_w, kb * TC_BK, 0, full0 + 8 * s);
         }
       }
-      if (plan.w_resident) mbar_wait(wbar, 0);  // the weight copies, too, must have landed before shared memory goes away
+      if (plan.w_resident) mbar_wait(wbar, 0, spin);  // the weight copies, too, must have landed before shared memory goes away
       // Shared memory must outlive every copy this thread started.  On the normal path the consumers have already
       // waited for all of them; after an abort they may have left early, so wait here (bounded) for the last
       // copy issued into each stage.
       const uint32_t first = it > (uint32_t)S ? it - (uint32_t)S : 0u;
-      for (uint32_t j = first; j < it; ++j) mbar_wait(full0 + 8 * (j % (uint32_t)S), (j / (uint32_t)S) & 1u);
+      for (uint32_t j = first; j < it; ++j)
+        if (j != withheld) mbar_wait(full0 + 8 * (j % (uint32_t)S), (j / (uint32_t)S) & 1u, spin);
     }
   } else if (warp == 13) {
     // ---- MMA issuer --------------------------------------------------------------------------------------
@@ -232,18 +238,18 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
       uint32_t it = 0, t = 0;
       bool ok = true;
-      if (plan.w_resident && !mbar_wait(wbar, 0)) { atomicExch(abort_flag, 1); atomicExch(status, 8); ok = false; }
+      if (plan.w_resident && !mbar_wait(wbar, 0, spin)) { atomicExch(abort_flag, 1); atomicExch(status, 8); ok = false; }
       for (int64_t tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++t) {
         const uint32_t buf = t & 1u, aph = (t >> 1) & 1u;
         if (aborted(abort_flag)) break;
-        if (!mbar_wait(acc_empty0 + 8 * buf, aph ^ 1u)) { atomicExch(abort_flag, 1); atomicExch(status, 5); break; }
+        if (!mbar_wait(acc_empty0 + 8 * buf, aph ^ 1u, spin)) { atomicExch(abort_flag, 1); atomicExch(status, 5); break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t d_tmem = tmem_base + buf * buf_cols;
         for (int kb = 0; kb < num_k; ++kb, ++it) {
           const int s = (int)(it % (uint32_t)S);
           const uint32_t ph = (it / (uint32_t)S) & 1u;
           if (aborted(abort_flag)) { ok = false; break; }
-          if (!mbar_wait(full0 + 8 * s, ph)) { atomicExch(abort_flag, 1); atomicExch(status, 2); ok = false; break; }
+          if (!mbar_wait(full0 + 8 * s, ph, spin)) { atomicExch(abort_flag, 1); atomicExch(status, 2); ok = false; break; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t a_addr = s_addr(smem + s * plan.stage_bytes);
           const uint32_t b_addr = plan.w_resident ? s_addr(smem + plan.w_off) + (uint32_t)kb * (uint32_t)N * TC_BK * 2
@@ -269,7 +275,7 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         const int s = (int)(it % (uint32_t)S);
         const uint32_t ph = (it / (uint32_t)S) & 1u;
         if (aborted(abort_flag)) { ok = false; break; }
-        if (!mbar_wait(full0 + 8 * s, ph)) { atomicExch(abort_flag, 1); atomicExch(status, 3); ok = false; break; }
+        if (!mbar_wait(full0 + 8 * s, ph, spin)) { atomicExch(abort_flag, 1); atomicExch(status, 3); ok = false; break; }
         if (has_proto) {
           const unsigned char* row = smem + s * plan.stage_bytes + r * 128;
 #pragma unroll
@@ -290,7 +296,7 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
       }
       if (!ok) break;
       const uint32_t buf = t & 1u, nph = (t >> 1) & 1u;
-      if (!mbar_wait(nrm_empty0 + 8 * buf, nph ^ 1u)) { atomicExch(abort_flag, 1); atomicExch(status, 6); break; }
+      if (!mbar_wait(nrm_empty0 + 8 * buf, nph ^ 1u, spin)) { atomicExch(abort_flag, 1); atomicExch(status, 6); break; }
       norm_s[buf * TC_BM + r] = (a0 + a1) + (a2 + a3);
       mbar_arrive(nrm_full0 + 8 * buf);  // release: the store above is visible to whoever observes the phase flip
     }
@@ -307,8 +313,8 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
       if ((int)(t & 1u) != grp) continue;
       const uint32_t ph = (t >> 1) & 1u;
       if (aborted(abort_flag)) break;
-      if (!mbar_wait(acc_full0 + 8 * grp, ph)) { atomicExch(abort_flag, 1); atomicExch(status, 4); break; }
-      if (!mbar_wait(nrm_full0 + 8 * grp, ph)) { atomicExch(abort_flag, 1); atomicExch(status, 7); break; }
+      if (!mbar_wait(acc_full0 + 8 * grp, ph, spin)) { atomicExch(abort_flag, 1); atomicExch(status, 4); break; }
+      if (!mbar_wait(nrm_full0 + 8 * grp, ph, spin)) { atomicExch(abort_flag, 1); atomicExch(status, 7); break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)grp * buf_cols;
       const int64_t tok = tile * TC_BM + r;
@@ -455,11 +461,29 @@ extern "C" int64_t aspa_router_tc_scratch_bytes(int C, int G, int has_proto) {
   return (int64_t)N * C * 2;
 }
 
-extern "C" int aspa_router_fwd_tc(const void* x, int64_t n, int C, const void* w_router, int G,
-                                  const float* proto_hat, const float* conf_eps, const float* usage_bias,
-                                  float proto_temp, float proto_threshold, float proto_span, float proto_blend,
-                                  float usage_boost, float* gate_probs, float* importance, float* proto_sim,
-                                  float* blend, float* stat_partials, void* scratch, int32_t* status, void* stream) {
+// Per-device launch facts, looked up once per device: SM count, and whether each kernel variant has been given its
+// shared-memory limit on that device (the attribute belongs to the function on ONE device).
+struct TcDeviceInfo {
+  int sms;
+  bool attr[3];
+};
+static TcDeviceInfo* tc_device_info() {
+  static TcDeviceInfo info[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (info[dev].sms == 0) {
+    int sms = 0;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    info[dev].sms = sms > 0 ? sms : 148;
+  }
+  return &info[dev];
+}
+
+static int router_tc_launch(const void* x, int64_t n, int C, const void* w_router, int G, const float* proto_hat,
+                            const float* conf_eps, const float* usage_bias, float proto_temp, float proto_threshold,
+                            float proto_span, float proto_blend, float usage_boost, float* gate_probs,
+                            float* importance, float* proto_sim, float* blend, float* stat_partials, void* scratch,
+                            int32_t* status, uint32_t spin, int64_t withhold_tile, void* stream) {
   ASPA_CHECK_ARG(x && w_router && gate_probs && importance && scratch && status, "null pointer");
   const bool has_proto = proto_hat != nullptr;
   if (aspa_router_tc_scratch_bytes(C, G, has_proto) == 0 || n < TC_BM) {
@@ -474,7 +498,7 @@ extern "C" int aspa_router_fwd_tc(const void* x, int64_t n, int C, const void* w
   router_wcat_kernel<<<(unsigned)ceil_div((int64_t)N * C, 256), 256, 0, st>>>((const __nv_bfloat16*)w_router, proto_hat,
                                                                              G, C, N, wcat);
   ASPA_CHECK_LAUNCH();
-  CUtensorMap mx, mw;
+  CUtensorMap mx, mw;   // host-side encoding of two descriptors (no driver round trip, no device work)
   if (!make_map(&mx, x, (uint64_t)n, (uint64_t)C, TC_BM) || !make_map(&mw, wcat, (uint64_t)N, (uint64_t)C, (uint32_t)N)) {
     set_error("aspa_router_fwd_tc: cuTensorMapEncodeTiled failed");
     return ASPA_ERR_CUDA;
@@ -484,20 +508,63 @@ extern "C" int aspa_router_fwd_tc(const void* x, int64_t n, int C, const void* w
     set_error("aspa_router_fwd_tc: shared memory holds fewer than two ring stages for this shape");
     return ASPA_ERR_UNSUPPORTED;
   }
-  int dev = 0, sms = 0;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  TcDeviceInfo* di = tc_device_info();
+  ASPA_CHECK_ARG(di != nullptr, "cannot identify the current device");
   const int64_t ntiles = ceil_div(n, TC_BM);
-  const unsigned grid = (unsigned)std::min<int64_t>(ntiles, sms > 0 ? sms : 148);
-  auto launch = [&](auto kernel) {
-    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, plan.total);
+  const unsigned grid = (unsigned)std::min<int64_t>(ntiles, di->sms);
+  auto launch = [&](auto kernel, int variant) {
+    if (!di->attr[variant]) {
+      cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_LIMIT + 2048);
+      di->attr[variant] = true;
+    }
     kernel<<<grid, TC_THREADS, plan.total, st>>>(mx, mw, (const __nv_bfloat16*)x, n, C, G, N, has_proto ? 1 : 0, conf_eps, usage_bias, proto_temp,
                                                  proto_threshold, proto_span, proto_blend, usage_boost, gate_probs,
-                                                 importance, proto_sim, blend, stat_partials, status, plan);
+                                                 importance, proto_sim, blend, stat_partials, status, plan, spin,
+                                                 withhold_tile);
   };
-  if (tc_reg_epilogue(N, G, has_proto) && G == 16) launch(router_tc_kernel<16>);
-  else if (tc_reg_epilogue(N, G, has_proto)) launch(router_tc_kernel<32>);
-  else launch(router_tc_kernel<0>);
+  if (tc_reg_epilogue(N, G, has_proto) && G == 16) launch(router_tc_kernel<16>, 0);
+  else if (tc_reg_epilogue(N, G, has_proto)) launch(router_tc_kernel<32>, 1);
+  else launch(router_tc_kernel<0>, 2);
   ASPA_CHECK_LAUNCH();
   return ASPA_OK;
+}
+
+extern "C" int aspa_router_fwd_tc(const void* x, int64_t n, int C, const void* w_router, int G,
+                                  const float* proto_hat, const float* conf_eps, const float* usage_bias,
+                                  float proto_temp, float proto_threshold, float proto_span, float proto_blend,
+                                  float usage_boost, float* gate_probs, float* importance, float* proto_sim,
+                                  float* blend, float* stat_partials, void* scratch, int32_t* status, void* stream) {
+  return router_tc_launch(x, n, C, w_router, G, proto_hat, conf_eps, usage_bias, proto_temp, proto_threshold, proto_span,
+                          proto_blend, usage_boost, gate_probs, importance, proto_sim, blend, stat_partials, scratch,
+                          status, TC_SPIN_LIMIT, -1, stream);
+}
+
+extern "C" int aspa_router_fwd_tc_probe(const void* x, int64_t n, int C, const void* w_router, int G,
+                                        const float* proto_hat, const float* conf_eps, float* gate_probs,
+                                        float* importance, float* proto_sim, float* blend, void* scratch,
+                                        int32_t* status, uint32_t spin_limit, int64_t withhold_tile, void* stream) {
+  ASPA_CHECK_ARG(spin_limit >= 1024, "spin_limit below 1024 would time healthy waits out");
+  return router_tc_launch(x, n, C, w_router, G, proto_hat, conf_eps, nullptr, 0.3f, 0.2f, 0.8f, 0.5f, 0.f, gate_probs,
+                          importance, proto_sim, blend, nullptr, scratch, status, spin_limit, withhold_tile, stream);
+}
+
+extern "C" int aspa_read_status(int32_t* status, int reset, void* stream) {
+  ASPA_CHECK_ARG(status != nullptr, "null pointer");
+  cudaStream_t st = (cudaStream_t)stream;
+  int32_t host = 0;
+  cudaError_t e = cudaMemcpyAsync(&host, status, sizeof(host), cudaMemcpyDeviceToHost, st);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) {
+    set_error("aspa_read_status: %s", cudaGetErrorString(e));
+    return ASPA_ERR_CUDA;
+  }
+  if (host == 0) return ASPA_OK;
+  if (reset) cudaMemsetAsync(status, 0, sizeof(int32_t), st);
+  static const char* const who[] = {"", "the producer's wait for a free ring stage", "the MMA warp's wait for a filled stage",
+                                    "a norm warp's wait for a filled stage", "an epilogue warp's wait for the accumulator",
+                                    "the MMA warp's wait for a free accumulator", "a norm warp's wait for a free norm buffer",
+                                    "an epilogue warp's wait for the row norms", "the MMA warp's wait for the resident weights"};
+  set_error("a bounded device-side wait ran out in the tensor-core router (%s); the outputs of that call are invalid",
+            host >= 1 && host <= 8 ? who[host] : "unknown wait");
+  return ASPA_ERR_TIMEOUT;
 }

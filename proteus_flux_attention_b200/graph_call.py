@@ -53,6 +53,7 @@ class CapturedLayerCall:
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
         if x.shape != self.static_in.shape or x.dtype != self.static_in.dtype:
             raise ValueError(f"captured for {tuple(self.static_in.shape)} {self.static_in.dtype}, got {tuple(x.shape)} {x.dtype}")
+        self.layer.check_previous_call()   # an expired router wait of the previous replay surfaces here
         if x.data_ptr() != self.static_in.data_ptr():
             self.static_in.copy_(x, non_blocking=True)
         self.graph.replay()

@@ -86,6 +86,15 @@ def router_status(device) -> torch.Tensor:
     return _ROUTER_STATUS[key]
 
 
+def check_router_status(device) -> None:
+    """Raise ``DeviceWaitTimeout`` if a bounded wait of the tensor-core router ran out since the last check, and
+    clear the word so that later, healthy calls are not blamed for it.  Waits for the current stream: call it where
+    the host synchronises anyway."""
+    key = str(device)
+    if key in _ROUTER_STATUS:
+        N.check(N.lib().aspa_read_status(N.ptr(_ROUTER_STATUS[key]), 1, N.stream()), "tensor-core router")
+
+
 def router_fwd(x2d: torch.Tensor, w_router: torch.Tensor, proto_hat: Optional[torch.Tensor],
                conf_eps: Optional[torch.Tensor], usage_bias: Optional[torch.Tensor], *, temp: float,
                threshold: float, span: float, blend: float, usage_boost: float, want_stats: bool = True,

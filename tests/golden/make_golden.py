@@ -3,7 +3,7 @@
 Run in the development container, where the reference source tree is
 mounted read-only:
 
-    PROTEUS_REF_SRC=<reference>/src python tests/golden/make_golden.py [--memory-only]
+    PROTEUS_REF_SRC=<reference>/src python tests/golden/make_golden.py [--memory-only | --config1-only]
 
 The reference is imported unmodified from PROTEUS_REF_SRC.  Every case stores
 the seeded inputs, the module weights and the outputs the reference produced,
@@ -320,11 +320,44 @@ def memory_cases():
                B=2, T=192, dtype=torch.bfloat16, calls=3, outliers=8)
 
 
+def config1_case():
+    """BASELINE configuration 1 at full size (1 x 4096 x 512 fp32, 8 heads, 8 gates, top-2, keep 0.25).  Weights and
+    input come from seeds (``seeded.py``), so only what the reference produced is stored: token mask, packed rows,
+    head choice, and the output rows of the kept tokens (the other rows are exactly zero: no projection bias)."""
+    sys.path.insert(0, str(OUT))
+    import seeded
+    cfg = dict(seeded.CONFIG1)
+    mod = AdaptiveSparseProtoAttention(ModelConfig(**cfg)).eval()
+    w = seeded.xavier_state(cfg["d_model"], cfg["attn_gates"], torch.float32, 0)
+    sd = mod.state_dict()
+    sd.update(w)
+    mod.load_state_dict(sd)
+    x = seeded.normal_input(1, 4096, cfg["d_model"], torch.float32, 0)
+    with torch.no_grad():
+        y = mod(x)
+    st = mod._last_sparse_state
+    mask = mod._last_token_mask.clone()
+    kept = mask[0].nonzero().flatten()
+    assert float(y[0][~mask[0]].abs().max()) == 0.0
+    stats = {k: v for k, v in mod.last_head_stats.items() if isinstance(v, (int, float, str, bool)) or v is None}
+    torch.save({"seed": 0, "mode": st["mode"], "token_mask": mask, "token_idx": st["token_idx"].to(torch.int32),
+                "row_offsets": st["row_offsets"].clone(), "active_head_indices": st["active_head_indices"].clone(),
+                "head_idx": mod._top_head_indices[0][kept].to(torch.int8) if hasattr(mod, "_top_head_indices") else None,
+                "importance": mod._last_token_importance.clone(), "y_kept": y[0][kept].clone(),
+                "y_abs_sum": float(y.double().abs().sum()), "stats": stats,
+                "linear_L": int(mod.linear_L), "linear_window": int(mod.linear_window)}, OUT / "layer_cfg1_full.pt")
+    print("layer_cfg1_full", st["mode"], "rows", st["token_idx"].numel(), "kept", int(mask.sum()))
+
+
 def main():
     import sys
     if "--memory-only" in sys.argv:
         memory_cases()
         return
+    if "--config1-only" in sys.argv:
+        config1_case()
+        return
+    config1_case()
     schedule_case()
     candidate_case()
     attention_case()

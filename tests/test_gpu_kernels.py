@@ -815,3 +815,47 @@ def test_memory_bank_update_and_int8_amax(dev, dtype):
     want_v = v_aug.float().abs().amax(dim=(1, 2))
     assert torch.equal(amax[0].cpu()[act], want_k) and torch.equal(amax[1].cpu()[act], want_v)
     assert float(want_k.max()) > float(k_h.float().abs().max())
+
+
+# ---------------------------------------------------------------------------------------------- bounded waits
+def test_router_bounded_wait_runs_out_and_reports_timeout(dev):
+    """A device-side wait that can never succeed must end by itself: the probe entry withholds the copy of one ring
+    stage, the consumers of that stage give up after `spin_limit` polls, the kernel frees its tensor memory and
+    returns, and the host reads ASPA_ERR_TIMEOUT through aspa_read_status.  The context stays usable: the same
+    shape runs clean right afterwards and matches the CUDA-core router."""
+    import ctypes as C
+    from proteus_flux_attention_b200 import _native as N
+    from proteus_flux_attention_b200 import ops
+    n, Cdim, G = 4096, 1024, 16
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(n, Cdim, generator=g).to(torch.bfloat16).to(dev)
+    w = (torch.randn(G, Cdim, generator=g) * 0.05).to(torch.bfloat16).to(dev)
+    ph = ops.normalize_rows(torch.randn(G, Cdim, generator=g).to(dev))
+    conf = torch.full((G,), 1e-6, device=dev)
+    gate = torch.empty(n, G, device=dev)
+    imp, sim, bs = (torch.empty(n, device=dev) for _ in range(3))
+    scratch = torch.empty(N.lib().aspa_router_tc_scratch_bytes(Cdim, G, 1), dtype=torch.uint8, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    stream = N.stream()
+
+    def probe(withhold):
+        return N.lib().aspa_router_fwd_tc_probe(N.ptr(x), n, Cdim, N.ptr(w), G, N.ptr(ph), N.ptr(conf), N.ptr(gate),
+                                                N.ptr(imp), N.ptr(sim), N.ptr(bs), N.ptr(scratch), N.ptr(status),
+                                                C.c_uint32(1 << 14), withhold, stream)
+
+    assert probe(3) == 0, N.last_error()            # the launch itself succeeds; the kernel returns by itself
+    rc = N.lib().aspa_read_status(N.ptr(status), 1, stream)
+    assert rc == N.ERR_TIMEOUT and "bounded device-side wait" in N.last_error()
+    with pytest.raises(N.DeviceWaitTimeout):
+        N.check(rc, "router")
+    assert N.lib().aspa_read_status(N.ptr(status), 1, stream) == 0      # cleared by the read above
+    assert probe(-1) == 0, N.last_error()           # nothing withheld: healthy, with the same short limit
+    assert N.lib().aspa_read_status(N.ptr(status), 1, stream) == 0
+    ops.USE_TC_ROUTER = False
+    try:
+        ref = ops.router_fwd(x, w, ph, conf, None, temp=0.3, threshold=0.2, span=0.8, blend=0.5, usage_boost=0.0)
+    finally:
+        ops.USE_TC_ROUTER = True
+    d = (gate - ref[0]).abs()
+    assert float(d.max()) < 1.0 / 64 and float((d > 1e-5).float().mean()) < 2e-3
+    assert torch.allclose(sim, ref[2], atol=2e-6)

@@ -444,3 +444,55 @@ def test_captured_layer_call_equals_eager(dev):
     slow = make(dict(cfg, attn_token_keep_threshold=0.5))
     with pytest.raises(RuntimeError, match="cannot be captured"):
         P.CapturedLayerCall(slow, xs[0])
+
+
+def test_chunked_graphs_do_not_outlive_their_layers(dev):
+    """Without ``cache_layers`` every ``run`` builds fresh layers; graphs captured in one call must not be replayed
+    by the next, whose layers (and weights) are different objects.  Two graph runs with different weights must each
+    equal the eager run with the same weights."""
+    import proteus_flux_attention_b200 as P
+    from proteus_flux_attention_b200.chunked_shortlist import _build_model_config
+    T, C, chunk = 4 * 2048, 256, 2048
+    seq = torch.randn(1, T, C, generator=torch.Generator().manual_seed(21)).to(torch.bfloat16).to(dev)
+
+    def states(seed):
+        torch.manual_seed(seed)
+        a = P.AdaptiveSparseAttention(_build_model_config(chunk, C, heads=4, sparse_ratio=0.05, shortlist_alpha=1.0, router_top_p=0.9))
+        b = P.AdaptiveSparseAttention(_build_model_config(256, C, heads=4, sparse_ratio=0.5, shortlist_alpha=1.0, router_top_p=0.9))
+        return tuple({k: (v.to(torch.bfloat16) if v.dtype == torch.float32 and "routing" not in k else v)
+                      for k, v in m.state_dict().items()} for m in (a, b))
+
+    def cfg(graph):
+        return P.ChunkedShortlistConfig(seq_len=T, d_model=C, chunk_len=chunk, buffer_tokens=256, per_chunk_budget=64,
+                                        device=dev, heads=4, freeze_prototypes=True, warmup=False, use_cuda_graph=graph)
+
+    graph_runner = P.ChunkedShortlistRunner(cfg(True))            # cache_layers=False
+    for seed in (31, 32):
+        cs, fs = states(seed)
+        got = graph_runner.run(seq, chunk_state=cs, final_state=fs)
+        want = P.ChunkedShortlistRunner(cfg(False)).run(seq, chunk_state=cs, final_state=fs)
+        assert torch.equal(got.keep_indices, want.keep_indices)
+        assert torch.equal(got.final_output, want.final_output)
+    assert "_graph_tmp" not in graph_runner.__dict__
+
+
+def test_rope_table_survives_a_longer_eager_call_between_replays(dev):
+    """A captured call keeps the address of the RoPE table it was captured with; an eager call at a larger length on
+    the same layer must not free or move that table."""
+    import proteus_flux_attention_b200 as P
+    cfg = dict(d_model=128, n_head=4, attn_h_total=4, attn_gates=8, attn_h_active=2, attn_h_active_min=2,
+               attn_h_active_max=2, attn_token_sparse=True, attn_token_keep_ratio=0.3, attn_mode="linear",
+               attn_router_top_p=0.0, attn_linear_L=64, attn_linear_window=48, attn_linear_anchor_stride=16,
+               attn_use_rope=True, n_ctx=512, attn_track_latency=False, attn_proto_enable=True, attn_proto_decay=1.0)
+    torch.manual_seed(2)
+    layer = P.AdaptiveSparseProtoAttention(P.ModelConfig(**cfg)).to(torch.bfloat16).to(dev).eval()
+    x = torch.randn(1, 512, 128, device=dev).to(torch.bfloat16)
+    want = layer(x).clone()
+    call = P.CapturedLayerCall(layer, x)
+    assert torch.equal(call(x), want)
+    big = torch.randn(1, 2048, 128, device=dev).to(torch.bfloat16)
+    layer(big)                                    # grows the table past n_ctx
+    junk = [torch.full((1 << 16,), 7.0, device=dev) for _ in range(64)]   # would land in freed table memory
+    torch.cuda.synchronize()
+    assert torch.equal(call(x), want)
+    del junk

@@ -3,6 +3,7 @@ records with NCCL all-gather and kept rows with an all-reduce of disjoint rows, 
 Skipped when fewer than two CUDA devices are visible.  NVLS is switched off for the child processes."""
 import os
 import socket
+import time
 
 import pytest
 import torch
@@ -33,14 +34,17 @@ def _cfg(dev):
 
 
 def _worker(rank, world, port, q):
+    import traceback
     import torch.distributed as dist
     import proteus_flux_attention_b200 as P
     from proteus_flux_attention_b200 import distributed as D
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
-    torch.cuda.set_device(rank)
-    dev = torch.device("cuda", rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    started = False
     try:
+        torch.cuda.set_device(rank)
+        dev = torch.device("cuda", rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+        started = True
         cs, fs = _states()
         seq = torch.randn(1, 5 * 2048, 256, generator=torch.Generator().manual_seed(9)).to(torch.bfloat16)
         lo, hi = D.partition_chunks(5, world, rank)
@@ -50,13 +54,18 @@ def _worker(rank, world, port, q):
                 src, chunk_state=cs, final_state=fs, sequence_is_local_shard=True)
             q.put((rank, where, res.keep_indices.clone(), res.final_output.float().cpu(),
                    res.reduced_sequence.float().cpu()))
+    except BaseException:   # the parent fails fast on this and tears the peer down
+        q.put(("error", rank, traceback.format_exc()))
+        raise
     finally:
-        dist.destroy_process_group()
+        if started:
+            dist.destroy_process_group()
 
 
 def test_two_gpu_sharding_equals_single_gpu():
     if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
         pytest.skip("needs two CUDA devices")
+    import queue
     import torch.multiprocessing as mp
     import proteus_flux_attention_b200 as P
     dev = torch.device("cuda:0")
@@ -66,13 +75,36 @@ def test_two_gpu_sharding_equals_single_gpu():
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q), daemon=True) for r in range(2)]
     for p in procs:
         p.start()
-    results = [q.get(timeout=300) for _ in range(2 * len(procs))]
-    for p in procs:
-        p.join(timeout=120)
-        assert p.exitcode == 0
+    results = []
+    try:
+        # a worker that dies leaves its peer blocked in a collective: collect with a deadline, fail on the first
+        # reported error or dead child, and never leave a child behind
+        deadline = time.monotonic() + 300
+        while len(results) < 2 * len(procs):
+            assert time.monotonic() < deadline, "workers did not report within 300 s"
+            try:
+                item = q.get(timeout=5)
+            except queue.Empty:
+                dead = [p for p in procs if p.exitcode not in (None, 0)]
+                assert not dead, f"worker exited with code {dead[0].exitcode} before reporting"
+                continue
+            assert item[0] != "error", f"rank {item[1]} failed:\n{item[2]}"
+            results.append(item)
+        for p in procs:
+            p.join(timeout=120)
+            assert p.exitcode == 0
+    finally:
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+        for p in procs:
+            p.join(timeout=10)
+            if p.is_alive():
+                p.kill()
+                p.join(timeout=10)
     assert sorted((r[0], r[1]) for r in results) == [(0, "hbm"), (0, "host"), (1, "hbm"), (1, "host")]
     for rank, where, keep, out, red in results:
         assert torch.equal(keep, want.keep_indices)

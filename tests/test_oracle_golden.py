@@ -158,3 +158,27 @@ def test_chunked_pipeline_matches_reference(golden_dir):
         assert torch.equal(r["keep_indices"], c["keep_indices"])
         assert torch.allclose(r["keep_scores"], c["keep_scores"], atol=1e-6)
         assert torch.allclose(r["final_output"], c["final_output"], atol=1e-5, rtol=1e-4)
+
+
+def test_oracle_matches_reference_at_baseline_config1_full_size(golden_dir):
+    """1 x 4096 x 512 fp32, 8 heads, top-2, keep 0.25 (the reference's own CPU-runnable headline configuration): the
+    oracle reproduces the token mask, the packed rows and the output rows the reference produced.  Weights and input
+    are rebuilt from the seeds the fixture was generated with."""
+    import sys
+    sys.path.insert(0, str(golden_dir))
+    import seeded
+    g = _load(golden_dir, "layer_cfg1_full.pt")
+    cfg = dict(seeded.CONFIG1)
+    w = seeded.xavier_state(cfg["d_model"], cfg["attn_gates"], torch.float32, g["seed"])
+    x = seeded.normal_input(1, 4096, cfg["d_model"], torch.float32, g["seed"])
+    lay = O.OracleLayer(w, **cfg)
+    y = lay.forward(x)
+    tr = lay.trace
+    assert tr["mode"] == g["mode"]
+    assert torch.equal(tr["token_mask"], g["token_mask"])
+    assert torch.equal(tr["packed"][1].to(torch.int32), g["token_idx"])
+    assert torch.equal(tr["packed"][2].to(torch.int32), g["row_offsets"])
+    assert float((tr["importance"] - g["importance"]).abs().max()) < 1e-6
+    kept = g["token_mask"][0].nonzero().flatten()
+    assert torch.allclose(y[0][kept], g["y_kept"], atol=1e-6, rtol=1e-5)
+    assert float(y[0][~g["token_mask"][0]].abs().max()) == 0.0
