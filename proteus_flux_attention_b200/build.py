@@ -15,7 +15,8 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libaspa_b200.so"
-SOURCES = ["router.cu", "router_tc.cu", "select.cu", "rope_quant.cu", "plan.cu", "attention.cu", "ema_chunk.cu", "memory_bank.cu"]
+SOURCES = ["router.cu", "router_tc.cu", "select.cu", "rope_quant.cu", "plan.cu", "attention.cu", "attention_tc.cu", "ema_chunk.cu",
+           "memory_bank.cu"]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC", "--use_fast_math=false"]
 
@@ -29,7 +30,7 @@ def needs_build() -> bool:
     if not LIB.exists():
         return True
     t = LIB.stat().st_mtime
-    deps = [CSRC / s for s in SOURCES] + [CSRC / "common.cuh", CSRC / "router_epilogue.cuh", PKG.parent / "include" / "aspa_b200.h", Path(__file__)]
+    deps = [CSRC / s for s in SOURCES] + sorted(CSRC.glob("*.cuh")) + [PKG.parent / "include" / "aspa_b200.h", Path(__file__)]
     return any(d.stat().st_mtime > t for d in deps)
 
 
