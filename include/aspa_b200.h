@@ -324,6 +324,16 @@ int aspa_gather_attn_fwd_prepared(const void* q, const void* k, const void* v, i
                                   const float* add_mask, void* out, int out_dtype, int out_layout,
                                   const int32_t* out_row_map, const aspa_kv_layout* kv_layout, void* workspace,
                                   void* regroup_ws, int regroup_prepared, void* stream);
+/* Tile kernel of the window passes (head_dim 64, bf16 or int8).  Two kernels replace the Triton kernel's tiled
+ * products (sa.py:597-919): a tcgen05 / tensor-memory kernel on 128-row x 128-key tiles and a warp-MMA kernel on
+ * 16-row groups for rows too sparse to fill 128-row tiles.  aspa_attn_tc_mode selects: 0 never the tcgen05 kernel,
+ * 1 (default) when window >= 32 * mean token gap between the rows of a head, 2 whenever the shape allows; returns the
+ * previous mode (any other argument only queries).  aspa_attn_tc_status reads (reset != 0: and clears) the word a
+ * bounded device-side wait of the tcgen05 kernel raises: ASPA_OK, or ASPA_ERR_TIMEOUT when a wait ran out since
+ * the last reset (outputs of that call are invalid).  Synchronises `stream`. */
+int aspa_attn_tc_mode(int mode);
+int aspa_attn_tc_status(int reset, void* stream);
+
 /* Bytes of regroup_ws for the call above (0 when the plan has no anchors). */
 int64_t aspa_attn_regroup_bytes(int64_t total_rows, int heads, int anchor_stride);
 

@@ -890,15 +890,25 @@ using namespace aspa;
 // 16*window.  With very sparse rows the union is mostly keys nobody attends to and the CTA count drops below the SM
 // count: gather instead.  total_rows may be a host-side upper bound, which only makes the estimate of the gap
 // conservative.
+static int g_attn_tc_mode = 1;   // see tc_tiles_wanted
 static bool tile_path_ok(int qkv_dtype, int D, bool has_cand, bool has_mask, const aspa_shortlist_plan* plan, int heads,
                          int T, int64_t total_rows) {
   if (!(D == WK_D && (qkv_dtype == ASPA_BF16 || qkv_dtype == ASPA_I8) && !has_cand && !has_mask)) return false;
   if (plan != nullptr) {
     const double gap = (double)T * (double)heads / (double)std::max<int64_t>(total_rows, 1);
     const double window = plan->window > 0 ? plan->window : 1;
-    if (16.0 * gap >= 7.0 * window) return false;
+    if (16.0 * gap >= 7.0 * window && g_attn_tc_mode != 2) return false;
   }
   return true;
+}
+
+// Which tile kernel?  The tcgen05 kernel works on 128-row tiles whose union key range is about 128*gap + window keys,
+// of which a row uses `window`: it is taken when at least a fifth of the tile is useful (window >= 32 * gap), the
+// warp-MMA kernel with its 16-row groups otherwise.  Mode 0 = never, 1 = by that rule, 2 = whenever the shape allows.
+static bool tc_tiles_wanted(int window, int heads, int T, int64_t total_rows) {
+  if (g_attn_tc_mode != 1) return g_attn_tc_mode == 2;
+  const double gap = (double)T * (double)heads / (double)std::max<int64_t>(total_rows, 1);
+  return (double)window >= 32.0 * gap;
 }
 
 // Anchors t - j*stride of the rows of one residue class t % stride are a window over the strided key sequence of that
@@ -947,6 +957,12 @@ extern "C" int aspa_attn_regroup_rows(int qkv_dtype, int heads, int T, int D, co
 extern "C" int64_t aspa_attn_regroup_bytes(int64_t total_rows, int heads, int anchor_stride) {
   if (anchor_stride <= 0) return 0;
   return (int64_t)sizeof(int32_t) * ((int64_t)heads * anchor_stride + 1 + 2 * total_rows);
+}
+
+extern "C" int aspa_attn_tc_mode(int mode) {
+  const int old = g_attn_tc_mode;
+  if (mode >= 0 && mode <= 2) g_attn_tc_mode = mode;
+  return old;
 }
 
 extern "C" int64_t aspa_attn_workspace_bytes(int64_t total_rows, int D) {
@@ -1073,7 +1089,10 @@ extern "C" int aspa_gather_attn_fwd_prepared(const void* q, const void* k, const
       p.ws_o = w + 2 * total_rows;
       p.write_partial = 1;
     }
-    if (qkv_dtype == ASPA_BF16) launch_window<__nv_bfloat16, 3>(p, max_rows, st); else launch_window<int8_t, 4>(p, max_rows, st);
+    const int win_keys = p.has_plan ? (plan->window > 0 ? plan->window : 1) : T;
+    if (!(tc_tiles_wanted(win_keys, heads, T, total_rows) && launch_window_tc(p, qkv_dtype, max_rows, 0, st))) {
+      if (qkv_dtype == ASPA_BF16) launch_window<__nv_bfloat16, 3>(p, max_rows, st); else launch_window<int8_t, 4>(p, max_rows, st);
+    }
     ASPA_CHECK_LAUNCH();
     const AnchorTiles at = anchor_tiles_for(extras ? plan : nullptr, regroup_ws != nullptr, heads, total_rows);
     if (at.use) {
@@ -1097,8 +1116,10 @@ extern "C" int aspa_gather_attn_fwd_prepared(const void* q, const void* k, const
       // rows per group are about total_rows / n_groups: two 64-row tiles per CTA column cover the usual group in
       // one step, and the kernel's tile loop takes care of larger groups
       const int rows_bound = (int)std::min<int64_t>(max_rows, std::max<int64_t>(WK_ROWS, 2 * total_rows / n_groups));
-      if (qkv_dtype == ASPA_BF16) launch_window<__nv_bfloat16, 3>(pa, rows_bound, st, n_groups);
-      else launch_window<int8_t, 4>(pa, rows_bound, st, n_groups);
+      if (!(tc_tiles_wanted(at.an_window, heads, T, total_rows) && launch_window_tc(pa, qkv_dtype, rows_bound, n_groups, st))) {
+        if (qkv_dtype == ASPA_BF16) launch_window<__nv_bfloat16, 3>(pa, rows_bound, st, n_groups);
+        else launch_window<int8_t, 4>(pa, rows_bound, st, n_groups);
+      }
       ASPA_CHECK_LAUNCH();
       p.anchors_done = 1;
     }

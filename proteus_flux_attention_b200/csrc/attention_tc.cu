@@ -185,12 +185,19 @@ __global__ void __launch_bounds__(TA_THREADS, 1) attn_window_tc_kernel(const Att
       const int pt = tid - 128;
       bool ok = true;
       if (!kI8) {
-        int issued = 0;
+        int pending = -1;   // ring stage whose copies are committed but not yet published
         for (int i = 0; i < ntiles && ok; ++i) {
           const uint32_t it = g_it + i;
           const int s = (int)(it % S);
+          const uint32_t ph = ((it / S) & 1u) ^ 1u;
           if (aborted(abort_flag)) { ok = false; break; }
-          if (!mbar_wait(kv_empty0 + 8 * s, ((it / S) & 1u) ^ 1u, spin)) {
+          if (pending >= 0 && !mbar_test(kv_empty0 + 8 * s, ph)) {   // no free stage yet: publish what is in flight first
+            cp_async_wait<0>();
+            fence_proxy_async();
+            mbar_arrive(kv_full0 + 8 * pending);
+            pending = -1;
+          }
+          if (!mbar_wait(kv_empty0 + 8 * s, ph, spin)) {
             atomicExch(abort_flag, 1); atomicExch(&g_attn_tc_status, 1); ok = false; break;
           }
           unsigned char* ks = kv_s + s * 2 * TA_TILE;
@@ -205,17 +212,17 @@ __global__ void __launch_bounds__(TA_THREADS, 1) attn_window_tc_kernel(const Att
             cp_async16(smem_u32(ks + TA_TILE + ta_swz(row, ch)), vh + kc * v_ts + ch * 8, nbytes);
           }
           cp_async_commit();
-          ++issued;
-          if (i > 0) {   // tile i-1 has landed once at most one group is still in flight
+          if (pending >= 0) {   // the previous tile has landed once at most one group is still in flight
             cp_async_wait<1>();
             fence_proxy_async();
-            mbar_arrive(kv_full0 + 8 * (int)((it - 1) % S));
+            mbar_arrive(kv_full0 + 8 * pending);
           }
+          pending = s;
         }
         cp_async_wait<0>();   // nothing of this thread is in flight into shared memory past this point
-        if (ok && issued == ntiles && ntiles > 0) {
+        if (ok && pending >= 0) {
           fence_proxy_async();
-          mbar_arrive(kv_full0 + 8 * (int)((g_it + ntiles - 1) % S));
+          mbar_arrive(kv_full0 + 8 * pending);
         }
       } else {
         // int8: the raw rows of the next tile are in registers while this tile is widened and stored
@@ -333,9 +340,9 @@ __global__ void __launch_bounds__(TA_THREADS, 1) attn_window_tc_kernel(const Att
         m = (mw == -INFINITY) ? -INFINITY : mw * 1.4426950408889634f;
         l = p.ws_l[gr];
 #pragma unroll
-        for (int d = 0; d < TA_D; d += 4) {
-          const float4 f = *reinterpret_cast<const float4*>(p.ws_o + gr * TA_D + d);
-          o[d] = f.x; o[d + 1] = f.y; o[d + 2] = f.z; o[d + 3] = f.w;
+        for (int d = 0; d < TA_D; d += 2) {   // the workspace rows start on 8-byte boundaries only
+          const float2 f = *reinterpret_cast<const float2*>(p.ws_o + gr * TA_D + d);
+          o[d] = f.x; o[d + 1] = f.y;
         }
       }
       float c_prev = 1.f;
@@ -360,10 +367,13 @@ __global__ void __launch_bounds__(TA_THREADS, 1) attn_window_tc_kernel(const Att
         const bool active = w_any && kb <= w_last && kb + TA_BN - 1 >= w_lo;   // warp-uniform
         float c_j = 1.f;
         if (aborted(abort_flag)) { ok = false; break; }
+        // Every warp waits for S_j, also one that skips the tile: S_j is issued only after P_{j-2} was signalled by all
+        // 128 threads, so passing this wait is what tells a warp that its next arrival on that barrier belongs to the
+        // phase of tile j and not to the one of tile j-2 (a warp running ahead would be counted twice in one phase).
+        if (!mbar_wait(s_full0 + 8 * b, (it >> 1) & 1u, spin)) {
+          atomicExch(abort_flag, 1); atomicExch(&g_attn_tc_status, 6); ok = false; break;
+        }
         if (active) {
-          if (!mbar_wait(s_full0 + 8 * b, (it >> 1) & 1u, spin)) {
-            atomicExch(abort_flag, 1); atomicExch(&g_attn_tc_status, 6); ok = false; break;
-          }
           tc_fence_after();
           const uint32_t t_s = t_lane + b * TA_BN;
           // valid columns of this row inside the tile: [clo, clo + span]; an empty range is (huge, 0)
@@ -437,8 +447,8 @@ __global__ void __launch_bounds__(TA_THREADS, 1) attn_window_tc_kernel(const Att
           p.ws_m[gr] = (m == -INFINITY) ? -INFINITY : m * 0.6931471805599453f;   // natural-log domain
           p.ws_l[gr] = l;
 #pragma unroll
-          for (int d = 0; d < TA_D; d += 4)
-            *reinterpret_cast<float4*>(p.ws_o + gr * TA_D + d) = make_float4(o[d], o[d + 1], o[d + 2], o[d + 3]);
+          for (int d = 0; d < TA_D; d += 2)
+            *reinterpret_cast<float2*>(p.ws_o + gr * TA_D + d) = make_float2(o[d], o[d + 1]);
         } else {
           float inv = l > 0.f ? 1.f / l : 0.f;
           if (kI8) inv *= p.v_scale[bh];
