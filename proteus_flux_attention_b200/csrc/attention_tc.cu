@@ -3,22 +3,29 @@
 // Same job as attn_window_kernel (attention.cu): a CTA owns consecutive packed rows of one head (or of one
 // (head, token % stride) group in the anchor pass), streams the union key range of those rows through shared memory
 // and keeps a per-row online softmax.  Here the tile is 128 rows x 128 keys and both products run as tcgen05.mma with
-// the accumulators in tensor memory:
-//     S = Q K^T   (M 128, N 128, K 64: four instructions)      -> tensor memory, double buffered
-//     O_j = P V   (M 128, N 64,  K 128: eight instructions)    -> tensor memory, double buffered, one per key tile
-// Roles (nine warps):
-//   warps 0..3  softmax: thread r owns row r = tensor-memory lane r.  Reads S with tcgen05.ld (once for the row
-//               maximum, once for the exponentials: a 128-column row does not fit the register file beside the 64
-//               output accumulators), writes P as 16-bit values into a 128-byte-swizzled shared-memory operand, and
-//               folds the finished O_{j-1} into its fp32 accumulators (o = o * c_{j-1} + O_{j-1}) while the tensor
-//               core is busy with tile j.  A warp whose 32 rows cannot see a key tile skips it altogether.
-//   warps 4..7  producers: K and V tiles into a three-stage ring.  bf16 rows arrive by cp.async into the swizzled
+// accumulators AND the probabilities in tensor memory:
+//     S_j = Q K_j^T  (M 128, N 128, K 64: four instructions, both operands from shared memory)  -> S[j & 1]
+//     O  += P_j V_j  (M 128, N 64, K 128: eight instructions, A = P_j from tensor memory, B = V where it lies
+//                     in shared memory, as the MN-major operand)                                -> O, accumulated
+// Tensor-memory columns: S0 [0,128) S1 [128,256) P0 [256,320) P1 [320,384) O_lo [384,448) O_hi [448,512): the two
+// 64-key halves of a tile keep separate softmax states and separate accumulators, merged when the row tile ends.
+// Roles (twelve warps: with thirteen the register file would allow 128 registers per thread instead of 168):
+//   warps 0..7  softmax.  Warp w owns tensor-memory lanes 32*(w % 4) .. +31 (one row each) and the key columns
+//               64*(w / 4) .. +63 of every tile, so two warps share a row and every scheduler has two softmax warps to
+//               hide the tensor-memory and special-function latencies of each other.  The two halves of a row never
+//               talk during the key loop: each keeps its own base, row sum and accumulator (split-K style).  A thread
+//               reads its 64 scores once, takes their maximum, exponentiates, packs to 16-bit pairs and writes them with
+//               tcgen05.st.  The softmax base moves lazily: only when the maximum outgrows it by 2^8 does the thread
+//               rescale its accumulator row in tensor memory (probabilities stay below 256, sums in fp32), so in
+//               steady state nobody touches O but the tensor core.  A warp whose rows cannot see a 64-key half tile
+//               writes zeros for it and waits for nothing but its turn.
+//   warps 8..10 producers: K and V tiles into a four-stage ring.  bf16 rows arrive by cp.async into the swizzled
 //               layout; int8 rows are loaded one tile ahead into registers and widened to fp16 on the way (0x6400 | byte
 //               is the half 1024 + byte, one subtraction gives the signed value: exact).  Rows may have any
 //               16-byte-aligned stride (the anchor pass reads every stride-th key), which is why this is not a TMA box.
-//   warp 8      allocates tensor memory, issues every tcgen05.mma and tcgen05.commit, frees tensor memory.
+//   warp 11     allocates tensor memory, issues every tcgen05.mma and tcgen05.commit, frees tensor memory.
 // int8 inputs run as fp16 x fp16 (values up to 127 and their 64-term dot products are exact in fp32 accumulation),
-// P is fp16 there; bf16 inputs run as bf16 x bf16 with P in bf16.  V is used where it lies, as the MN-major B operand.
+// P is fp16 there; bf16 inputs run as bf16 x bf16 with P in bf16.
 // Every mbarrier wait is bounded; on expiry the CTA raises g_attn_tc_status, all roles leave, tensor memory is freed.
 #include <cuda_fp16.h>
 
@@ -34,21 +41,29 @@ namespace aspa {
 constexpr int TA_BM = 128;                 // packed rows per tile = tensor-memory lanes
 constexpr int TA_BN = 128;                 // keys per tile
 constexpr int TA_D = 64;
-constexpr int TA_STAGES = 3;
+constexpr int TA_STAGES = 4;
 constexpr int TA_TILE = TA_BN * 128;       // bytes of one K or V tile: 128 rows of 128 bytes
 constexpr int TA_Q_BYTES = TA_BM * 128;
-constexpr int TA_P_BYTES = TA_BM * 256;    // two 64-key blocks of 128 rows x 128 bytes
-constexpr int TA_THREADS = 9 * 32;
-constexpr int TA_TAIL = 2048;              // row tables (2 x 128 ints), mbarriers, tensor-memory slot, abort flag
-constexpr int TA_SMEM = 1024 + TA_Q_BYTES + TA_STAGES * 2 * TA_TILE + 2 * TA_P_BYTES + TA_TAIL;
-constexpr uint32_t TA_TMEM_COLS = 512;     // S0 [0,128) S1 [128,256) O0 [256,320) O1 [320,384)
+constexpr int TA_PROD = 3 * 32;             // producer threads
+constexpr int TA_THREADS = 12 * 32;
+constexpr int TA_TAIL = 4096;              // row tables (2 x 128 ints), half-row exchange (4 x 128 floats), mbarriers, flags
+constexpr int TA_SMEM = 1024 + TA_Q_BYTES + TA_STAGES * 2 * TA_TILE + TA_TAIL;
+constexpr uint32_t TA_TMEM_COLS = 512;
+constexpr uint32_t TA_COL_P = 256, TA_COL_O = 384;
 constexpr int TA_ABSENT = -2147483647;
+constexpr float TA_LAZY = 8.f;             // the softmax base follows the row maximum once it is this far (log2) behind
 
 __device__ int g_attn_tc_status;           // non-zero after a bounded wait ran out in any CTA of any launch
 
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float y;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
   return y;
 }
 
@@ -85,14 +100,17 @@ __global__ void __launch_bounds__(TA_THREADS, 1) attn_window_tc_kernel(const Att
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(ta_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* q_s = smem;
   unsigned char* kv_s = smem + TA_Q_BYTES;
-  unsigned char* p_s = kv_s + S * 2 * TA_TILE;
-  unsigned char* tail = p_s + 2 * TA_P_BYTES;
+  unsigned char* tail = kv_s + S * 2 * TA_TILE;
   int* ts = reinterpret_cast<int*>(tail);            // per tile row: its token (anchor pass: strided position), or ABSENT
   int* grow_s = ts + TA_BM;                          // per tile row: row of the head-grouped packing (workspace row)
-  uint64_t* bars = reinterpret_cast<uint64_t*>(tail + 1024);
+  float* lsum_s = reinterpret_cast<float*>(grow_s + TA_BM);   // [2][128] row sums of the two column halves, exchanged at the end
+  float* msum_s = lsum_s + 2 * TA_BM;                          // [2][128] their softmax bases
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tail + 3072);
+  // kv_full[S], kv_empty[S], s_full[2], p_ready[2], o_final, pair[4], pv_done[2]
   const uint32_t kv_full0 = s_addr(bars), kv_empty0 = s_addr(bars + S), s_full0 = s_addr(bars + 2 * S),
-                 p_ready0 = s_addr(bars + 2 * S + 2), o_full0 = s_addr(bars + 2 * S + 4);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 6);
+                 p_ready0 = s_addr(bars + 2 * S + 2), o_final = s_addr(bars + 2 * S + 4), pair0 = s_addr(bars + 2 * S + 5),
+                 pv_done0 = s_addr(bars + 2 * S + 9);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 11);
   int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -107,18 +125,20 @@ __global__ void __launch_bounds__(TA_THREADS, 1) attn_window_tc_kernel(const Att
 
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
-      mbar_init(kv_full0 + 8 * s, 4 * 32);         // every producer thread
+      mbar_init(kv_full0 + 8 * s, TA_PROD);        // every producer thread
       mbar_init(kv_empty0 + 8 * s, 1);             // one tcgen05.commit
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(s_full0 + 8 * b, 1);
-      mbar_init(p_ready0 + 8 * b, TA_BM);          // every softmax thread
-      mbar_init(o_full0 + 8 * b, 1);
+      mbar_init(p_ready0 + 8 * b, 2 * TA_BM);      // every softmax thread
+      mbar_init(pv_done0 + 8 * b, 1);
     }
+    mbar_init(o_final, 1);
+    for (int q = 0; q < 4; ++q) mbar_init(pair0 + 8 * q, 64);   // the two warps that share a lane quarter
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 8) tmem_alloc(s_addr(tmem_slot), TA_TMEM_COLS);
+  if (warp == 11) tmem_alloc(s_addr(tmem_slot), TA_TMEM_COLS);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -137,6 +157,8 @@ __global__ void __launch_bounds__(TA_THREADS, 1) attn_window_tc_kernel(const Att
   constexpr uint32_t idesc_pv = umma_idesc_f16(kFmt, 0, 1, TA_BM, TA_D);   // V as it lies: MN-major B operand
 
   uint32_t g_it = 0;   // key tiles this CTA has been through (every role counts the same)
+  uint32_t g_rt = 0;   // row tiles with at least one key tile
+  uint32_t pair_uses = 0;   // softmax warps: exchanges done over the barrier two warps of a lane quarter share
   for (int r0 = blockIdx.x * TA_BM; r0 < cnt; r0 += gridDim.x * TA_BM) {
     __syncthreads();                                  // the previous row tile is finished in every role
     if (aborted(abort_flag)) break;
@@ -180,9 +202,9 @@ __global__ void __launch_bounds__(TA_THREADS, 1) attn_window_tc_kernel(const Att
     const int ntiles = t_last < 0 ? 0 : t_last / TA_BN - kt_begin + 1;
     __syncthreads();
 
-    if (warp >= 4 && warp < 8) {
+    if (warp >= 8 && warp < 11) {
       // ---- producers ---------------------------------------------------------------------------------------
-      const int pt = tid - 128;
+      const int pt = tid - 256;
       bool ok = true;
       if (!kI8) {
         int pending = -1;   // ring stage whose copies are committed but not yet published
@@ -202,14 +224,24 @@ __global__ void __launch_bounds__(TA_THREADS, 1) attn_window_tc_kernel(const Att
           }
           unsigned char* ks = kv_s + s * 2 * TA_TILE;
           const int kb = (kt_begin + i) * TA_BN;
+          const bool whole = kb + TA_BN <= Tn;   // every key of the tile exists: no clamping
+          const T* kt_ptr = kh + (int64_t)kb * k_ts;
+          const T* vt_ptr = vh + (int64_t)kb * v_ts;
 #pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            const int id = pt + 128 * c, row = id >> 3, ch = id & 7;
-            const int key = kb + row;
-            const int64_t kc = min(key, Tn - 1);
-            const int nbytes = key < Tn ? 16 : 0;
-            cp_async16(smem_u32(ks + ta_swz(row, ch)), kh + kc * k_ts + ch * 8, nbytes);
-            cp_async16(smem_u32(ks + TA_TILE + ta_swz(row, ch)), vh + kc * v_ts + ch * 8, nbytes);
+          for (int c = 0; c < (TA_BN * 8 + TA_PROD - 1) / TA_PROD; ++c) {
+            const int id = pt + TA_PROD * c, row = id >> 3, ch = id & 7;
+            if (id < TA_BN * 8) {
+              if (whole) {
+                cp_async16(smem_u32(ks + ta_swz(row, ch)), kt_ptr + row * k_ts + ch * 8, 16);
+                cp_async16(smem_u32(ks + TA_TILE + ta_swz(row, ch)), vt_ptr + row * v_ts + ch * 8, 16);
+              } else {
+                const int key = kb + row;
+                const int64_t kc = min(key, Tn - 1);
+                const int nbytes = key < Tn ? 16 : 0;
+                cp_async16(smem_u32(ks + ta_swz(row, ch)), kh + kc * k_ts + ch * 8, nbytes);
+                cp_async16(smem_u32(ks + TA_TILE + ta_swz(row, ch)), vh + kc * v_ts + ch * 8, nbytes);
+              }
+            }
           }
           cp_async_commit();
           if (pending >= 0) {   // the previous tile has landed once at most one group is still in flight
@@ -226,15 +258,16 @@ __global__ void __launch_bounds__(TA_THREADS, 1) attn_window_tc_kernel(const Att
         }
       } else {
         // int8: the raw rows of the next tile are in registers while this tile is widened and stored
-        uint4 nk[4], nv[4];
+        constexpr int NC = (TA_BN * 4 + TA_PROD - 1) / TA_PROD;   // 16-byte raw chunks per thread and tile
+        uint4 nk[NC], nv[NC];
         auto fetch = [&](int i) {
           const int kb = (kt_begin + i) * TA_BN;
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            const int id = pt + 128 * c, row = id >> 2, rc = id & 3;
+          for (int c = 0; c < NC; ++c) {
+            const int id = pt + TA_PROD * c, row = id >> 2, rc = id & 3;
             const int key = kb + row;
             nk[c] = nv[c] = make_uint4(0, 0, 0, 0);
-            if (key < Tn) {
+            if (id < TA_BN * 4 && key < Tn) {
               nk[c] = *reinterpret_cast<const uint4*>(kh + (int64_t)key * k_ts + rc * 16);
               nv[c] = *reinterpret_cast<const uint4*>(vh + (int64_t)key * v_ts + rc * 16);
             }
@@ -244,9 +277,9 @@ __global__ void __launch_bounds__(TA_THREADS, 1) attn_window_tc_kernel(const Att
         for (int i = 0; i < ntiles; ++i) {
           const uint32_t it = g_it + i;
           const int s = (int)(it % S);
-          uint4 ck[4], cv[4];
+          uint4 ck[NC], cv[NC];
 #pragma unroll
-          for (int c = 0; c < 4; ++c) { ck[c] = nk[c]; cv[c] = nv[c]; }
+          for (int c = 0; c < NC; ++c) { ck[c] = nk[c]; cv[c] = nv[c]; }
           if (i + 1 < ntiles) fetch(i + 1);
           if (aborted(abort_flag)) break;
           if (!mbar_wait(kv_empty0 + 8 * s, ((it / S) & 1u) ^ 1u, spin)) {
@@ -254,8 +287,9 @@ __global__ void __launch_bounds__(TA_THREADS, 1) attn_window_tc_kernel(const Att
           }
           unsigned char* ks = kv_s + s * 2 * TA_TILE;
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            const int id = pt + 128 * c, row = id >> 2, rc = id & 3;
+          for (int c = 0; c < NC; ++c) {
+            const int id = pt + TA_PROD * c, row = id >> 2, rc = id & 3;
+            if (id >= TA_BN * 4) continue;
             uint4 a, b;
             i8x4_to_f16x4(ck[c].x, a.x, a.y); i8x4_to_f16x4(ck[c].y, a.z, a.w);
             i8x4_to_f16x4(ck[c].z, b.x, b.y); i8x4_to_f16x4(ck[c].w, b.z, b.w);
@@ -270,7 +304,7 @@ __global__ void __launch_bounds__(TA_THREADS, 1) attn_window_tc_kernel(const Att
           mbar_arrive(kv_full0 + 8 * s);
         }
       }
-    } else if (warp == 8) {
+    } else if (warp == 11) {
       // ---- MMA issuer ----------------------------------------------------------------------------------------
       if (lane == 0 && ntiles > 0) {
         const uint32_t q_addr = s_addr(q_s);
@@ -299,27 +333,30 @@ __global__ void __launch_bounds__(TA_THREADS, 1) attn_window_tc_kernel(const Att
             atomicExch(abort_flag, 1); atomicExch(&g_attn_tc_status, 3); ok = false; break;
           }
           tc_fence_after();
-          const uint32_t p_addr = s_addr(p_s + b * TA_P_BYTES);
+          const uint32_t p_tmem = tmem_base + TA_COL_P + b * (TA_BN / 2);
           const uint32_t v_addr = s_addr(kv_s + s * 2 * TA_TILE + TA_TILE);
-          const uint32_t d_tmem = tmem_base + 2 * TA_BN + b * TA_D;
+          const uint32_t acc0 = (j > 0 || p.read_partial) ? 1u : 0u;
 #pragma unroll
-          for (int k = 0; k < TA_BN / 16; ++k)   // 16 keys per instruction: 32 bytes along a P row, 16 rows of V
-            umma_f16(d_tmem, umma_desc_k_sw128(p_addr + (k >> 2) * (TA_BM * 128) + (k & 3) * 32),
-                     umma_desc_k_sw128(v_addr + k * 16 * 128), idesc_pv, k > 0 ? 1u : 0u);
-          umma_commit(o_full0 + 8 * b);        // O_j complete (and every earlier instruction)
+          for (int hh = 0; hh < 2; ++hh) {       // keys 64*hh .. +63 accumulate into their own O
+            const uint32_t o_tmem = tmem_base + TA_COL_O + hh * TA_D;
+#pragma unroll
+            for (int k = 0; k < 4; ++k)          // 16 keys per instruction: 8 columns of P, 16 rows of V
+              umma_f16_ts(o_tmem, p_tmem + hh * 32 + k * 8, umma_desc_k_sw128(v_addr + (hh * 4 + k) * 16 * 128), idesc_pv,
+                          k > 0 ? 1u : acc0);
+          }
+          umma_commit(pv_done0 + 8 * b);       // O holds the sum up to tile j
           umma_commit(kv_empty0 + 8 * s);      // K_j and V_j have been read: the stage may be refilled
           if (j + 2 < ntiles) issue_qk(j + 2); // S[b] was read by the softmax warps before they signalled P_j
         }
-        if (ok) {   // nothing may still be running when shared or tensor memory is reused
-          const uint32_t last = g_it + ntiles - 1;
-          if (!mbar_wait(o_full0 + 8 * (last & 1u), (last >> 1) & 1u, spin)) {
-            atomicExch(abort_flag, 1); atomicExch(&g_attn_tc_status, 4);
-          }
+        if (ok) {
+          umma_commit(o_final);                // everything issued for this row tile has finished
+          if (!mbar_wait(o_final, g_rt & 1u, spin)) { atomicExch(abort_flag, 1); atomicExch(&g_attn_tc_status, 4); }
         }
       }
     } else {
-      // ---- softmax warps: thread r owns row r ----------------------------------------------------------------------
-      const int r = tid;
+      // ---- softmax warps: lane quarter q4, column half h; thread (q4, lane) owns the half row (r, keys 64h .. 64h+63) ------
+      const int q4 = warp & 3, h = warp >> 2;
+      const int r = q4 * 32 + lane;
       const int tr_raw = ts[r];
       const bool present = tr_raw != TA_ABSENT;
       const int tr = present ? tr_raw : -1;
@@ -328,154 +365,203 @@ __global__ void __launch_bounds__(TA_THREADS, 1) attn_window_tc_kernel(const Att
       const int w_first = __reduce_min_sync(0xffffffffu, tr < 0 ? 0x7fffffff : tr);
       const bool w_any = w_last >= 0;
       const int w_lo = w_any ? max(0, w_first - window + 1) : 0;
-      const uint32_t t_lane = tmem_base + ((uint32_t)(warp * 32) << 16);
+      const uint32_t t_lane = tmem_base + ((uint32_t)(q4 * 32) << 16);
+      const uint32_t t_oh = t_lane + TA_COL_O + h * TA_D;    // the accumulator row of this half (64 columns)
       const int64_t gr = grow_s[r];
 
-      float m = -INFINITY, l = 0.f;
-      float o[TA_D];
+      float m = -INFINITY, l = 0.f;     // softmax base (log2 domain, scaled) and row sum of this half
+      bool ok = true;
+      if (p.read_partial && ntiles > 0) {
+        // Start from the state an earlier pass left: it becomes the state of the lower half, the upper half starts
+        // empty.  Thread (q4, h) writes channels 32h .. 32h+31 of both accumulators.
+        uint32_t w[32], z[32];
 #pragma unroll
-      for (int d = 0; d < TA_D; ++d) o[d] = 0.f;
-      if (p.read_partial && present) {
-        const float mw = p.ws_m[gr];
-        m = (mw == -INFINITY) ? -INFINITY : mw * 1.4426950408889634f;
-        l = p.ws_l[gr];
+        for (int i = 0; i < 32; ++i) w[i] = z[i] = 0u;
+        if (present) {
+          if (h == 0) {
+            const float mw = p.ws_m[gr];
+            m = (mw == -INFINITY) ? -INFINITY : mw * 1.4426950408889634f;
+            l = p.ws_l[gr];
+          }
 #pragma unroll
-        for (int d = 0; d < TA_D; d += 2) {   // the workspace rows start on 8-byte boundaries only
-          const float2 f = *reinterpret_cast<const float2*>(p.ws_o + gr * TA_D + d);
-          o[d] = f.x; o[d + 1] = f.y;
+          for (int d = 0; d < 32; d += 2) {   // the workspace rows start on 8-byte boundaries only
+            const float2 f = *reinterpret_cast<const float2*>(p.ws_o + gr * TA_D + h * 32 + d);
+            w[d] = __float_as_uint(f.x); w[d + 1] = __float_as_uint(f.y);
+          }
         }
+        tmem_st32(t_lane + TA_COL_O + h * 32, w);
+        tmem_st32(t_lane + TA_COL_O + TA_D + h * 32, z);
+        tmem_wait_st();
       }
-      float c_prev = 1.f;
-      bool prev_active = false, ok = true;
-      auto fold = [&](uint32_t itp) {   // o = o * c_prev + O_{itp}
-        const uint32_t bp = itp & 1u;
-        if (!mbar_wait(o_full0 + 8 * bp, (itp >> 1) & 1u, spin)) {
-          atomicExch(abort_flag, 1); atomicExch(&g_attn_tc_status, 5); ok = false; return;
-        }
-        tc_fence_after();
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          float v[32];
-          tmem_ld32(t_lane + 2 * TA_BN + bp * TA_D + h * 32, v);
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[h * 32 + i] = fmaf(o[h * 32 + i], c_prev, v[i]);
-        }
-      };
       for (int j = 0; j < ntiles && ok; ++j) {
         const uint32_t it = g_it + j, b = it & 1u;
-        const int kb = (kt_begin + j) * TA_BN;
-        const bool active = w_any && kb <= w_last && kb + TA_BN - 1 >= w_lo;   // warp-uniform
-        float c_j = 1.f;
+        const int kb = (kt_begin + j) * TA_BN + h * 64;      // first key of this half tile
+        const bool active = w_any && kb <= w_last && kb + 63 >= w_lo;   // warp-uniform
         if (aborted(abort_flag)) { ok = false; break; }
-        // Every warp waits for S_j, also one that skips the tile: S_j is issued only after P_{j-2} was signalled by all
-        // 128 threads, so passing this wait is what tells a warp that its next arrival on that barrier belongs to the
-        // phase of tile j and not to the one of tile j-2 (a warp running ahead would be counted twice in one phase).
+        // Every warp waits for S_j, also one that skips the tile: S_j is issued only after P_{j-2} was signalled by
+        // every softmax thread, so passing this wait is what tells a warp that its next arrival on that barrier
+        // belongs to the phase of tile j and not to the one of tile j-2.  S_j complete also means that every
+        // earlier instruction is: P_{j-2} has been read, so its columns may be written again.
         if (!mbar_wait(s_full0 + 8 * b, (it >> 1) & 1u, spin)) {
           atomicExch(abort_flag, 1); atomicExch(&g_attn_tc_status, 6); ok = false; break;
         }
+        const uint32_t t_p = t_lane + TA_COL_P + b * (TA_BN / 2) + h * 32;   // this thread's 64 probabilities
+        uint32_t pw[32];
         if (active) {
           tc_fence_after();
-          const uint32_t t_s = t_lane + b * TA_BN;
-          // valid columns of this row inside the tile: [clo, clo + span]; an empty range is (huge, 0)
-          const bool some = hi_key >= lo_key && hi_key >= kb && lo_key <= kb + TA_BN - 1;
+          // valid columns of this row inside the half tile: [clo, clo + span]; an empty range is (huge, 0)
+          const bool some = hi_key >= lo_key && hi_key >= kb && lo_key <= kb + 63;
           const int clo = some ? max(lo_key - kb, 0) : (1 << 20);
-          const uint32_t span = some ? (uint32_t)(min(hi_key - kb, TA_BN - 1) - clo) : 0u;
-          const bool all_full = __all_sync(0xffffffffu, some && clo == 0 && span == TA_BN - 1);
-          unsigned chunk_live = 0;
-          float mx = -INFINITY;
+          const uint32_t span = some ? (uint32_t)(min(hi_key - kb, 63) - clo) : 0u;
+          const bool all_full = __all_sync(0xffffffffu, some && clo == 0 && span == 63);
+          uint32_t a[32], c[32];
+          tmem_ld32_nowait(t_lane + b * TA_BN + h * 64, a);
+          tmem_ld32_nowait(t_lane + b * TA_BN + h * 64 + 32, c);
+          tmem_wait_ld();
+          if (!all_full) {
 #pragma unroll
-          for (int c4 = 0; c4 < 4; ++c4) {
-            const bool live = all_full || __any_sync(0xffffffffu, some && clo <= c4 * 32 + 31 && clo + (int)span >= c4 * 32);
-            if (!live) continue;
-            chunk_live |= 1u << c4;
-            float v[32];
-            tmem_ld32(t_s + c4 * 32, v);
-            if (all_full) {
-#pragma unroll
-              for (int i = 0; i < 32; ++i) mx = fmaxf(mx, v[i]);
-            } else {
-              const int cb = c4 * 32 - clo;
-#pragma unroll
-              for (int i = 0; i < 32; ++i) mx = fmaxf(mx, (uint32_t)(cb + i) <= span ? v[i] : -INFINITY);
+            for (int i = 0; i < 32; ++i) {
+              a[i] = (uint32_t)(i - clo) <= span ? a[i] : 0xff800000u;          // -inf
+              c[i] = (uint32_t)(32 + i - clo) <= span ? c[i] : 0xff800000u;
             }
           }
-          const float m_new = fmaxf(m, mx * sc_log2);
-          c_j = (m == -INFINITY) ? 0.f : ex2_approx(m - m_new);
-          const float base = (m_new == -INFINITY) ? 0.f : m_new;
-          unsigned char* prow = p_s + b * TA_P_BYTES + r * 128;
-          float sum = 0.f;
+          float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-          for (int c4 = 0; c4 < 4; ++c4) {
-            uint32_t w[16];
-            if (chunk_live & (1u << c4)) {
-              float v[32];
-              tmem_ld32(t_s + c4 * 32, v);
-              const int cb = c4 * 32 - clo;
-#pragma unroll
-              for (int i = 0; i < 32; ++i) {
-                float sv = fmaf(v[i], sc_log2, -base);
-                if (!all_full) sv = (uint32_t)(cb + i) <= span ? sv : -INFINITY;
-                v[i] = ex2_approx(sv);
-                sum += v[i];
-              }
-#pragma unroll
-              for (int i = 0; i < 16; ++i) w[i] = pack_p<T>(v[2 * i], v[2 * i + 1]);
-            } else {
-#pragma unroll
-              for (int i = 0; i < 16; ++i) w[i] = 0u;
-            }
-#pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {   // 16-byte chunk cc of the 256-byte P row: block cc / 8, chunk cc % 8
-              const int cc = c4 * 4 + q4;
-              *reinterpret_cast<uint4*>(prow + (cc >> 3) * (TA_BM * 128) + (((cc & 7) ^ (r & 7)) << 4)) =
-                  make_uint4(w[4 * q4], w[4 * q4 + 1], w[4 * q4 + 2], w[4 * q4 + 3]);
-            }
+          for (int i = 0; i < 32; i += 2) {
+            mx0 = fmax3(mx0, __uint_as_float(a[i]), __uint_as_float(a[i + 1]));
+            mx1 = fmax3(mx1, __uint_as_float(c[i]), __uint_as_float(c[i + 1]));
           }
-          l = l * c_j + sum;
-          m = m_new;
+          const float m_cand = fmaxf(mx0, mx1) * sc_log2;
+          // Lazy base: move it only when the maximum has outgrown it by 2^TA_LAZY (or there was none).
+          const bool need = m_cand > m + TA_LAZY || (m == -INFINITY && m_cand > -INFINITY);
+          if (__any_sync(0xffffffffu, need)) {
+            // O must be at rest: P_{j-1} V_{j-1} was issued when the last thread signalled P_{j-1}, moments ago.  (The
+            // wait is occasional, which is safe: this barrier cannot complete another phase before this thread has
+            // signalled P_{j+1}.)
+            if (j > 0 && !mbar_wait(pv_done0 + 8 * ((it - 1) & 1u), ((it - 1) >> 1) & 1u, spin)) {
+              atomicExch(abort_flag, 1); atomicExch(&g_attn_tc_status, 8); ok = false; break;
+            }
+            tc_fence_after();
+            const float cf = !need ? 1.f : (m == -INFINITY ? 0.f : ex2_approx(m - m_cand));
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+              uint32_t w[32];
+              tmem_ld32_nowait(t_oh + hh * 32, w);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) w[i] = cf == 0.f ? 0u : __float_as_uint(__uint_as_float(w[i]) * cf);
+              tmem_st32(t_oh + hh * 32, w);
+            }
+            l *= cf;
+            if (need) m = m_cand;
+          }
+          const float base = (m == -INFINITY) ? 0.f : m;
+          const float2 sc2 = make_float2(sc_log2, sc_log2), nb2 = make_float2(-base, -base);
+          float2 sa = make_float2(0.f, 0.f), sb = make_float2(0.f, 0.f);
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float2 ea = __ffma2_rn(make_float2(__uint_as_float(a[i]), __uint_as_float(a[i + 1])), sc2, nb2);
+            float2 ec = __ffma2_rn(make_float2(__uint_as_float(c[i]), __uint_as_float(c[i + 1])), sc2, nb2);
+            ea.x = ex2_approx(ea.x); ea.y = ex2_approx(ea.y);
+            ec.x = ex2_approx(ec.x); ec.y = ex2_approx(ec.y);
+            sa = __fadd2_rn(sa, ea);
+            sb = __fadd2_rn(sb, ec);
+            pw[i >> 1] = pack_p<T>(ea.x, ea.y);
+            pw[16 + (i >> 1)] = pack_p<T>(ec.x, ec.y);
+          }
+          l += (sa.x + sa.y) + (sb.x + sb.y);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) pw[i] = 0u;   // the tensor core multiplies all 128 rows: rows that see nothing add zero
         }
-        fence_proxy_async();     // P of this row (if written) is visible to the tensor core's reads
-        tc_fence_before();       // ... and this thread's reads of S[b] are complete
+        tmem_st32(t_p, pw);
+        tmem_wait_st();
+        tc_fence_before();       // the writes of P_j (and of a rescaled O) and the reads of S[b] are complete
         mbar_arrive(p_ready0 + 8 * b);
-        if (prev_active) fold(it - 1);
-        c_prev = c_j;
-        prev_active = active;
       }
-      if (ok && prev_active) fold(g_it + ntiles - 1);
+      // ---- result of the row tile: merge the two halves (m, l, O)_lo and (m, l, O)_hi -----------------------------------
+      if (ntiles == 0 && p.read_partial && present && h == 0) {   // no key tile at all: the state passes through
+        const float mw = p.ws_m[gr];
+        m = (mw == -INFINITY) ? -INFINITY : mw * 1.4426950408889634f;
+        l = p.ws_l[gr];
+      }
+      msum_s[h * TA_BM + r] = m;
+      lsum_s[h * TA_BM + r] = l;
+      mbar_arrive(pair0 + 8 * q4);
+      if (!mbar_wait(pair0 + 8 * q4, pair_uses & 1u, spin)) { atomicExch(abort_flag, 1); atomicExch(&g_attn_tc_status, 7); ok = false; }
+      ++pair_uses;
+      const float m_other = msum_s[(h ^ 1) * TA_BM + r], l_other = lsum_s[(h ^ 1) * TA_BM + r];
+      const float m_lo = h == 0 ? m : m_other, m_hi = h == 0 ? m_other : m;
+      const float l_lo = h == 0 ? l : l_other, l_hi = h == 0 ? l_other : l;
+      const float m_all = fmaxf(m_lo, m_hi);
+      const float a_lo = m_lo == -INFINITY ? 0.f : ex2_approx(m_lo - m_all), a_hi = m_hi == -INFINITY ? 0.f : ex2_approx(m_hi - m_all);
+      const float l_tot = l_lo * a_lo + l_hi * a_hi;
+      float o[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) o[i] = 0.f;
+      if (ntiles > 0) {
+        if (ok && !mbar_wait(o_final, g_rt & 1u, spin)) { atomicExch(abort_flag, 1); atomicExch(&g_attn_tc_status, 5); ok = false; }
+        if (ok) {   // channels 32h .. 32h+31 of both accumulators
+          tc_fence_after();
+          uint32_t w0[32], w1[32];
+          tmem_ld32_nowait(t_lane + TA_COL_O + h * 32, w0);
+          tmem_ld32_nowait(t_lane + TA_COL_O + TA_D + h * 32, w1);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            // a weight of zero means that half never saw a key; its accumulator may hold anything then
+            const float x0 = a_lo == 0.f ? 0.f : __uint_as_float(w0[i]) * a_lo;
+            const float x1 = a_hi == 0.f ? 0.f : __uint_as_float(w1[i]) * a_hi;
+            o[i] = x0 + x1;
+          }
+        }
+      } else if (p.read_partial && present) {
+#pragma unroll
+        for (int d = 0; d < 32; d += 2) {
+          const float2 f = *reinterpret_cast<const float2*>(p.ws_o + gr * TA_D + h * 32 + d);
+          o[d] = f.x; o[d + 1] = f.y;
+        }
+      }
+      mbar_arrive(pair0 + 8 * q4);   // both halves have read the exchange slots: the next row tile may overwrite them
+      if (!mbar_wait(pair0 + 8 * q4, pair_uses & 1u, spin)) { atomicExch(abort_flag, 1); atomicExch(&g_attn_tc_status, 7); ok = false; }
+      ++pair_uses;
       if (ok && present) {
         if (p.write_partial) {
-          p.ws_m[gr] = (m == -INFINITY) ? -INFINITY : m * 0.6931471805599453f;   // natural-log domain
-          p.ws_l[gr] = l;
+          if (h == 0) {
+            p.ws_m[gr] = (m_all == -INFINITY) ? -INFINITY : m_all * 0.6931471805599453f;   // natural-log domain
+            p.ws_l[gr] = l_tot;
+          }
 #pragma unroll
-          for (int d = 0; d < TA_D; d += 2)
-            *reinterpret_cast<float2*>(p.ws_o + gr * TA_D + d) = make_float2(o[d], o[d + 1]);
+          for (int d = 0; d < 32; d += 2)
+            *reinterpret_cast<float2*>(p.ws_o + gr * TA_D + h * 32 + d) = make_float2(o[d], o[d + 1]);
         } else {
-          float inv = l > 0.f ? 1.f / l : 0.f;
+          float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
           if (kI8) inv *= p.v_scale[bh];
           const int tok = anchor ? p.token_idx[gr] : tr;
-          const int64_t ob = out_row_base(p, bh, tok);
+          const int64_t ob = out_row_base(p, bh, tok) + h * 32;
           if (p.out_dtype == ASPA_BF16) {
             __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + ob;
 #pragma unroll
-            for (int d = 0; d < TA_D; d += 8)
+            for (int d = 0; d < 32; d += 8)
               *reinterpret_cast<uint4*>(dst + d) =
                   make_uint4(pack_bf16(o[d] * inv, o[d + 1] * inv), pack_bf16(o[d + 2] * inv, o[d + 3] * inv),
                              pack_bf16(o[d + 4] * inv, o[d + 5] * inv), pack_bf16(o[d + 6] * inv, o[d + 7] * inv));
           } else {
             float* dst = reinterpret_cast<float*>(p.out) + ob;
 #pragma unroll
-            for (int d = 0; d < TA_D; d += 4)
+            for (int d = 0; d < 32; d += 4)
               *reinterpret_cast<float4*>(dst + d) = make_float4(o[d] * inv, o[d + 1] * inv, o[d + 2] * inv, o[d + 3] * inv);
           }
         }
       }
     }
     g_it += (uint32_t)ntiles;
+    g_rt += ntiles > 0 ? 1u : 0u;
   }
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 8) {
+  if (warp == 11) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TA_TMEM_COLS);
   }
