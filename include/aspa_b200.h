@@ -327,7 +327,7 @@ int aspa_gather_attn_fwd_prepared(const void* q, const void* k, const void* v, i
 /* Tile kernel of the window passes (head_dim 64, bf16 or int8).  Two kernels replace the Triton kernel's tiled
  * products (sa.py:597-919): a tcgen05 / tensor-memory kernel on 128-row x 128-key tiles and a warp-MMA kernel on
  * 16-row groups for rows too sparse to fill 128-row tiles.  aspa_attn_tc_mode selects: 0 never the tcgen05 kernel,
- * 1 (default) when window >= 32 * mean token gap between the rows of a head, 2 whenever the shape allows; returns the
+ * 1 (default) when window >= 64 * mean token gap between the rows of a head, 2 whenever the shape allows; returns the
  * previous mode (any other argument only queries).  aspa_attn_tc_status reads (reset != 0: and clears) the word a
  * bounded device-side wait of the tcgen05 kernel raises: ASPA_OK, or ASPA_ERR_TIMEOUT when a wait ran out since
  * the last reset (outputs of that call are invalid).  Synchronises `stream`. */

@@ -7,19 +7,21 @@
 //     S_j = Q K_j^T  (M 128, N 128, K 64: four instructions, both operands from shared memory)  -> S[j & 1]
 //     O  += P_j V_j  (M 128, N 64, K 128: eight instructions, A = P_j from tensor memory, B = V where it lies
 //                     in shared memory, as the MN-major operand)                                -> O, accumulated
-// Tensor-memory columns: S0 [0,128) S1 [128,256) P0 [256,320) P1 [320,384) O_lo [384,448) O_hi [448,512): the two
-// 64-key halves of a tile keep separate softmax states and separate accumulators, merged when the row tile ends.
+// Tensor-memory columns: S0 [0,128) S1 [128,256) S2 [256,384) O0 [384,448) O1 [448,512).  Key tile j uses score
+// buffer j % 3, whose first 64 columns become P_j once the row has been read (a thread overwrites only its own lane),
+// and accumulator j % 2: two softmax states and two accumulators per row (split-K over the tile parity), merged when
+// the row tile ends.  Three score buffers let S_{j+3} be issued right behind P_j V_j, so a softmax warp finds its next
+// tile waiting.
 // Roles (twelve warps: with thirteen the register file would allow 128 registers per thread instead of 168):
-//   warps 0..7  softmax.  Warp w owns tensor-memory lanes 32*(w % 4) .. +31 (one row each) and the key columns
-//               64*(w / 4) .. +63 of every tile, so two warps share a row and every scheduler has two softmax warps to
-//               hide the tensor-memory and special-function latencies of each other.  The two halves of a row never
-//               talk during the key loop: each keeps its own base, row sum and accumulator (split-K style).  A thread
-//               reads its 64 scores once, takes their maximum, exponentiates, packs to 16-bit pairs and writes them with
-//               tcgen05.st.  The softmax base moves lazily: only when the maximum outgrows it by 2^8 does the thread
-//               rescale its accumulator row in tensor memory (probabilities stay below 256, sums in fp32), so in
-//               steady state nobody touches O but the tensor core.  A warp whose rows cannot see a 64-key half tile
-//               writes zeros for it and waits for nothing but its turn.
-//   warps 8..10 producers: K and V tiles into a four-stage ring.  bf16 rows arrive by cp.async into the swizzled
+//   warps 0..7  softmax.  Warp w owns tensor-memory lanes 32*(w % 4) .. +31 (one row each) and the key tiles of
+//               parity w / 4, so two warps share a row but never a tile: while one exponentiates tile j the other
+//               waits for S_{j+1} or writes P_{j-1}, which keeps the special-function unit busy across the latencies
+//               of either.  A thread reads the 128 scores of its row once, takes their maximum, exponentiates, packs
+//               to 16-bit pairs and writes them with tcgen05.st.  The softmax base moves lazily: only when the
+//               maximum outgrows it by 2^8 does the thread rescale its accumulator row in tensor memory
+//               (probabilities stay below 256, sums in fp32), so in steady state nobody touches O but the tensor
+//               core.  A warp whose rows cannot see a key tile writes zeros for it and waits for nothing but its turn.
+//   warps 8..10 producers: K and V tiles into a six-stage ring.  bf16 rows arrive by cp.async into the swizzled
 //               layout; int8 rows are loaded one tile ahead into registers and widened to fp16 on the way (0x6400 | byte
 //               is the half 1024 + byte, one subtraction gives the signed value: exact).  Rows may have any
 //               16-byte-aligned stride (the anchor pass reads every stride-th key), which is why this is not a TMA box.
@@ -41,7 +43,7 @@ namespace aspa {
 constexpr int TA_BM = 128;                 // packed rows per tile = tensor-memory lanes
 constexpr int TA_BN = 128;                 // keys per tile
 constexpr int TA_D = 64;
-constexpr int TA_STAGES = 4;
+constexpr int TA_STAGES = 6;             // S_{j+3} is issued with P_j V_j: its K tile must have had three tile periods to arrive
 constexpr int TA_TILE = TA_BN * 128;       // bytes of one K or V tile: 128 rows of 128 bytes
 constexpr int TA_Q_BYTES = TA_BM * 128;
 constexpr int TA_PROD = 3 * 32;             // producer threads
@@ -49,11 +51,25 @@ constexpr int TA_THREADS = 12 * 32;
 constexpr int TA_TAIL = 4096;              // row tables (2 x 128 ints), half-row exchange (4 x 128 floats), mbarriers, flags
 constexpr int TA_SMEM = 1024 + TA_Q_BYTES + TA_STAGES * 2 * TA_TILE + TA_TAIL;
 constexpr uint32_t TA_TMEM_COLS = 512;
-constexpr uint32_t TA_COL_P = 256, TA_COL_O = 384;
+constexpr uint32_t TA_COL_O = 384;
+constexpr int TA_SBUF = 3;                 // score buffers
 constexpr int TA_ABSENT = -2147483647;
 constexpr float TA_LAZY = 8.f;             // the softmax base follows the row maximum once it is this far (log2) behind
 
 __device__ int g_attn_tc_status;           // non-zero after a bounded wait ran out in any CTA of any launch
+
+#ifdef TA_TIMING
+// Diagnostics build only: cycles spent per role and phase, summed over every CTA.
+__device__ unsigned long long g_ta_cycles[16];
+__device__ int g_ta_debug;   // bit 0: producers skip the copies; bit 1: softmax skips exponentials; bit 2: softmax skips tensor memory
+#define TA_DBG(bit) ((g_ta_debug >> (bit)) & 1)
+#define TA_T0() long long ta_t = clock64()
+#define TA_ACC(slot) do { const long long n_ = clock64(); atomicAdd(&g_ta_cycles[slot], (unsigned long long)(n_ - ta_t)); ta_t = n_; } while (0)
+#else
+#define TA_DBG(bit) 0
+#define TA_T0() do {} while (0)
+#define TA_ACC(slot) do {} while (0)
+#endif
 
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
@@ -106,10 +122,9 @@ __global__ void __launch_bounds__(TA_THREADS, 1) attn_window_tc_kernel(const Att
   float* lsum_s = reinterpret_cast<float*>(grow_s + TA_BM);   // [2][128] row sums of the two column halves, exchanged at the end
   float* msum_s = lsum_s + 2 * TA_BM;                          // [2][128] their softmax bases
   uint64_t* bars = reinterpret_cast<uint64_t*>(tail + 3072);
-  // kv_full[S], kv_empty[S], s_full[2], p_ready[2], o_final, pair[4], pv_done[2]
+  // kv_full[S], kv_empty[S], s_full[3], p_ready[3], o_final, pair[4]
   const uint32_t kv_full0 = s_addr(bars), kv_empty0 = s_addr(bars + S), s_full0 = s_addr(bars + 2 * S),
-                 p_ready0 = s_addr(bars + 2 * S + 2), o_final = s_addr(bars + 2 * S + 4), pair0 = s_addr(bars + 2 * S + 5),
-                 pv_done0 = s_addr(bars + 2 * S + 9);
+                 p_ready0 = s_addr(bars + 2 * S + 3), o_final = s_addr(bars + 2 * S + 6), pair0 = s_addr(bars + 2 * S + 7);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 11);
   int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
 
@@ -128,10 +143,9 @@ __global__ void __launch_bounds__(TA_THREADS, 1) attn_window_tc_kernel(const Att
       mbar_init(kv_full0 + 8 * s, TA_PROD);        // every producer thread
       mbar_init(kv_empty0 + 8 * s, 1);             // one tcgen05.commit
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < TA_SBUF; ++b) {
       mbar_init(s_full0 + 8 * b, 1);
-      mbar_init(p_ready0 + 8 * b, 2 * TA_BM);      // every softmax thread
-      mbar_init(pv_done0 + 8 * b, 1);
+      mbar_init(p_ready0 + 8 * b, TA_BM);          // every softmax thread of the parity the tile belongs to
     }
     mbar_init(o_final, 1);
     for (int q = 0; q < 4; ++q) mbar_init(pair0 + 8 * q, 64);   // the two warps that share a lane quarter
@@ -230,7 +244,7 @@ __global__ void __launch_bounds__(TA_THREADS, 1) attn_window_tc_kernel(const Att
 #pragma unroll
           for (int c = 0; c < (TA_BN * 8 + TA_PROD - 1) / TA_PROD; ++c) {
             const int id = pt + TA_PROD * c, row = id >> 3, ch = id & 7;
-            if (id < TA_BN * 8) {
+            if (id < TA_BN * 8 && !TA_DBG(0)) {
               if (whole) {
                 cp_async16(smem_u32(ks + ta_swz(row, ch)), kt_ptr + row * k_ts + ch * 8, 16);
                 cp_async16(smem_u32(ks + TA_TILE + ta_swz(row, ch)), vt_ptr + row * v_ts + ch * 8, 16);
@@ -307,55 +321,61 @@ __global__ void __launch_bounds__(TA_THREADS, 1) attn_window_tc_kernel(const Att
     } else if (warp == 11) {
       // ---- MMA issuer ----------------------------------------------------------------------------------------
       if (lane == 0 && ntiles > 0) {
-        const uint32_t q_addr = s_addr(q_s);
+        // Descriptors differ from one instruction to the next only in their start-address field (bits 0..13, in
+        // 16-byte units, never carrying out of it: shared memory is smaller than 256 KB), so each one is a 32-bit add.
+        const uint64_t q_desc = umma_desc_k_sw128(s_addr(q_s));
+        const uint64_t kv_desc = umma_desc_k_sw128(s_addr(kv_s));
         bool ok = true;
-        auto issue_qk = [&](int i) {     // S[it & 1] = Q K_i^T
+        auto issue_qk = [&](int i) {     // S[it % 3] = Q K_i^T
           const uint32_t it = g_it + i;
           const int s = (int)(it % S);
           if (!mbar_wait(kv_full0 + 8 * s, (it / S) & 1u, spin)) {
             atomicExch(abort_flag, 1); atomicExch(&g_attn_tc_status, 2); ok = false; return;
           }
           tc_fence_after();
-          const uint32_t k_addr = s_addr(kv_s + s * 2 * TA_TILE);
-          const uint32_t d_tmem = tmem_base + (it & 1u) * TA_BN;
+          const uint64_t k_desc = kv_desc + (uint64_t)(s * (2 * TA_TILE / 16));
+          const uint32_t d_tmem = tmem_base + (it % TA_SBUF) * TA_BN;
 #pragma unroll
           for (int k = 0; k < TA_D / 16; ++k)
-            umma_f16(d_tmem, umma_desc_k_sw128(q_addr + k * 32), umma_desc_k_sw128(k_addr + k * 32), idesc_qk, k > 0 ? 1u : 0u);
-          umma_commit(s_full0 + 8 * (it & 1u));
+            umma_f16(d_tmem, q_desc + (uint64_t)(k * 2), k_desc + (uint64_t)(k * 2), idesc_qk, k > 0 ? 1u : 0u);
+          umma_commit(s_full0 + 8 * (it % TA_SBUF));
         };
+        TA_T0();
         issue_qk(0);
         if (ok && ntiles > 1) issue_qk(1);
+        if (ok && ntiles > 2) issue_qk(2);
+        TA_ACC(0);   // prologue: first two S tiles issued (includes the wait for the first K tiles)
         for (int j = 0; j < ntiles && ok; ++j) {
           const uint32_t it = g_it + j, b = it & 1u;
           const int s = (int)(it % S);
           if (aborted(abort_flag)) { ok = false; break; }
-          if (!mbar_wait(p_ready0 + 8 * b, (it >> 1) & 1u, spin)) {
+          const uint32_t b3 = it % TA_SBUF;
+          if (!mbar_wait(p_ready0 + 8 * b3, (it / TA_SBUF) & 1u, spin)) {
             atomicExch(abort_flag, 1); atomicExch(&g_attn_tc_status, 3); ok = false; break;
           }
+          TA_ACC(1);   // MMA thread waiting for P_j
           tc_fence_after();
-          const uint32_t p_tmem = tmem_base + TA_COL_P + b * (TA_BN / 2);
-          const uint32_t v_addr = s_addr(kv_s + s * 2 * TA_TILE + TA_TILE);
-          const uint32_t acc0 = (j > 0 || p.read_partial) ? 1u : 0u;
+          const uint32_t p_tmem = tmem_base + b3 * TA_BN;               // P_j lies over the first half of S_j
+          const uint64_t v_desc = kv_desc + (uint64_t)((s * 2 * TA_TILE + TA_TILE) / 16);
+          const uint32_t o_tmem = tmem_base + TA_COL_O + b * TA_D;      // the accumulator of this tile parity
+          const uint32_t acc0 = (j >= 2 || p.read_partial) ? 1u : 0u;
 #pragma unroll
-          for (int hh = 0; hh < 2; ++hh) {       // keys 64*hh .. +63 accumulate into their own O
-            const uint32_t o_tmem = tmem_base + TA_COL_O + hh * TA_D;
-#pragma unroll
-            for (int k = 0; k < 4; ++k)          // 16 keys per instruction: 8 columns of P, 16 rows of V
-              umma_f16_ts(o_tmem, p_tmem + hh * 32 + k * 8, umma_desc_k_sw128(v_addr + (hh * 4 + k) * 16 * 128), idesc_pv,
-                          k > 0 ? 1u : acc0);
-          }
-          umma_commit(pv_done0 + 8 * b);       // O holds the sum up to tile j
-          umma_commit(kv_empty0 + 8 * s);      // K_j and V_j have been read: the stage may be refilled
-          if (j + 2 < ntiles) issue_qk(j + 2); // S[b] was read by the softmax warps before they signalled P_j
+          for (int k = 0; k < TA_BN / 16; ++k)   // 16 keys per instruction: 8 columns of P, 16 rows of V
+            umma_f16_ts(o_tmem, p_tmem + k * 8, v_desc + (uint64_t)(k * (16 * 128 / 16)), idesc_pv, k > 0 ? 1u : acc0);
+          umma_commit(kv_empty0 + 8 * s);      // P_j V_j done: O holds the sum up to tile j, the ring stage may be refilled
+          TA_ACC(2);   // issuing P V
+          if (j + 3 < ntiles) issue_qk(j + 3); // into the buffer of tile j: queued behind P_j V_j, which reads it first
+          TA_ACC(3);   // issuing Q K (includes the wait for the K tile)
         }
         if (ok) {
           umma_commit(o_final);                // everything issued for this row tile has finished
           if (!mbar_wait(o_final, g_rt & 1u, spin)) { atomicExch(abort_flag, 1); atomicExch(&g_attn_tc_status, 4); }
+          TA_ACC(4);   // draining the tensor pipe at the end of the row tile
         }
       }
     } else {
-      // ---- softmax warps: lane quarter q4, column half h; thread (q4, lane) owns the half row (r, keys 64h .. 64h+63) ------
-      const int q4 = warp & 3, h = warp >> 2;
+      // ---- softmax warps: lane quarter q4, tile parity g; thread (q4, lane) owns row r for the key tiles of parity g --------
+      const int q4 = warp & 3, h = warp >> 2;   // h: tile parity this warp serves, and the output channels 32h .. 32h+31
       const int r = q4 * 32 + lane;
       const int tr_raw = ts[r];
       const bool present = tr_raw != TA_ABSENT;
@@ -366,14 +386,14 @@ __global__ void __launch_bounds__(TA_THREADS, 1) attn_window_tc_kernel(const Att
       const bool w_any = w_last >= 0;
       const int w_lo = w_any ? max(0, w_first - window + 1) : 0;
       const uint32_t t_lane = tmem_base + ((uint32_t)(q4 * 32) << 16);
-      const uint32_t t_oh = t_lane + TA_COL_O + h * TA_D;    // the accumulator row of this half (64 columns)
+      const uint32_t t_oh = t_lane + TA_COL_O + h * TA_D;    // the accumulator row of this tile parity (64 columns)
       const int64_t gr = grow_s[r];
 
-      float m = -INFINITY, l = 0.f;     // softmax base (log2 domain, scaled) and row sum of this half
+      float m = -INFINITY, l = 0.f;     // softmax base (log2 domain, scaled) and row sum over the tiles of this parity
       bool ok = true;
       if (p.read_partial && ntiles > 0) {
-        // Start from the state an earlier pass left: it becomes the state of the lower half, the upper half starts
-        // empty.  Thread (q4, h) writes channels 32h .. 32h+31 of both accumulators.
+        // Start from the state an earlier pass left: it becomes the state of parity 0, parity 1 starts empty.
+        // Thread (q4, h) writes channels 32h .. 32h+31 of both accumulators.
         uint32_t w[32], z[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) w[i] = z[i] = 0u;
@@ -392,94 +412,122 @@ __global__ void __launch_bounds__(TA_THREADS, 1) attn_window_tc_kernel(const Att
         tmem_st32(t_lane + TA_COL_O + h * 32, w);
         tmem_st32(t_lane + TA_COL_O + TA_D + h * 32, z);
         tmem_wait_st();
+        // both warps of a lane quarter wrote parts of both accumulators: neither may signal a P before both are done
+        tc_fence_before();
+        mbar_arrive(pair0 + 8 * q4);
+        if (!mbar_wait(pair0 + 8 * q4, pair_uses & 1u, spin)) { atomicExch(abort_flag, 1); atomicExch(&g_attn_tc_status, 7); ok = false; }
+        ++pair_uses;
+        tc_fence_after();
       }
+      TA_T0();
       for (int j = 0; j < ntiles && ok; ++j) {
         const uint32_t it = g_it + j, b = it & 1u;
-        const int kb = (kt_begin + j) * TA_BN + h * 64;      // first key of this half tile
-        const bool active = w_any && kb <= w_last && kb + 63 >= w_lo;   // warp-uniform
+        if ((int)b != h) continue;                            // the other warp of this lane quarter has this tile
+        const int kb = (kt_begin + j) * TA_BN;
+        const bool active = w_any && kb <= w_last && kb + TA_BN - 1 >= w_lo;   // warp-uniform
         if (aborted(abort_flag)) { ok = false; break; }
-        // Every warp waits for S_j, also one that skips the tile: S_j is issued only after P_{j-2} was signalled by
-        // every softmax thread, so passing this wait is what tells a warp that its next arrival on that barrier
-        // belongs to the phase of tile j and not to the one of tile j-2.  S_j complete also means that every
-        // earlier instruction is: P_{j-2} has been read, so its columns may be written again.
-        if (!mbar_wait(s_full0 + 8 * b, (it >> 1) & 1u, spin)) {
+        // Every warp waits for its S_j, also one that skips the tile: S_j is issued only after P_{j-3}, which shares
+        // its buffer and its barriers, was signalled by all 128 threads of the other parity, so passing this wait is
+        // what tells a warp that its arrival belongs to the phase of tile j.  The tensor pipe runs in order: S_j
+        // complete means P_{j-3} V_{j-3} has read its operand, so these columns may be written again.
+        const uint32_t b3 = it % TA_SBUF;
+        if (!mbar_wait(s_full0 + 8 * b3, (it / TA_SBUF) & 1u, spin)) {
           atomicExch(abort_flag, 1); atomicExch(&g_attn_tc_status, 6); ok = false; break;
         }
-        const uint32_t t_p = t_lane + TA_COL_P + b * (TA_BN / 2) + h * 32;   // this thread's 64 probabilities
-        uint32_t pw[32];
+        const uint32_t t_p = t_lane + b3 * TA_BN;   // the 128 probabilities of this row: 64 columns over the start of S_j
+        if (lane == 0 && q4 == 0) TA_ACC(5);   // softmax warp waiting for S_j
+        if (TA_DBG(2)) {
+          tc_fence_before();
+          mbar_arrive(p_ready0 + 8 * b3);
+          continue;
+        }
         if (active) {
           tc_fence_after();
-          // valid columns of this row inside the half tile: [clo, clo + span]; an empty range is (huge, 0)
-          const bool some = hi_key >= lo_key && hi_key >= kb && lo_key <= kb + 63;
+          // valid columns of this row inside the tile: [clo, clo + span]; an empty range is (huge, 0)
+          const bool some = hi_key >= lo_key && hi_key >= kb && lo_key <= kb + TA_BN - 1;
           const int clo = some ? max(lo_key - kb, 0) : (1 << 20);
-          const uint32_t span = some ? (uint32_t)(min(hi_key - kb, 63) - clo) : 0u;
-          const bool all_full = __all_sync(0xffffffffu, some && clo == 0 && span == 63);
-          uint32_t a[32], c[32];
-          tmem_ld32_nowait(t_lane + b * TA_BN + h * 64, a);
-          tmem_ld32_nowait(t_lane + b * TA_BN + h * 64 + 32, c);
+          const uint32_t span = some ? (uint32_t)(min(hi_key - kb, TA_BN - 1) - clo) : 0u;
+          const bool all_full = __all_sync(0xffffffffu, some && clo == 0 && span == TA_BN - 1);
+          uint32_t sv[4][32];
+#pragma unroll
+          for (int c4 = 0; c4 < 4; ++c4) tmem_ld32_nowait(t_lane + b3 * TA_BN + c4 * 32, sv[c4]);
           tmem_wait_ld();
+          if (lane == 0 && q4 == 0) TA_ACC(6);   // loading the score row from tensor memory
           if (!all_full) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              a[i] = (uint32_t)(i - clo) <= span ? a[i] : 0xff800000u;          // -inf
-              c[i] = (uint32_t)(32 + i - clo) <= span ? c[i] : 0xff800000u;
-            }
+            for (int c4 = 0; c4 < 4; ++c4)
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                sv[c4][i] = (uint32_t)(c4 * 32 + i - clo) <= span ? sv[c4][i] : 0xff800000u;   // -inf
           }
-          float mx0 = -INFINITY, mx1 = -INFINITY;
+          float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            mx0 = fmax3(mx0, __uint_as_float(a[i]), __uint_as_float(a[i + 1]));
-            mx1 = fmax3(mx1, __uint_as_float(c[i]), __uint_as_float(c[i + 1]));
+            mx0 = fmax3(mx0, __uint_as_float(sv[0][i]), __uint_as_float(sv[0][i + 1]));
+            mx1 = fmax3(mx1, __uint_as_float(sv[1][i]), __uint_as_float(sv[1][i + 1]));
+            mx2 = fmax3(mx2, __uint_as_float(sv[2][i]), __uint_as_float(sv[2][i + 1]));
+            mx3 = fmax3(mx3, __uint_as_float(sv[3][i]), __uint_as_float(sv[3][i + 1]));
           }
-          const float m_cand = fmaxf(mx0, mx1) * sc_log2;
+          const float m_cand = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sc_log2;
           // Lazy base: move it only when the maximum has outgrown it by 2^TA_LAZY (or there was none).
           const bool need = m_cand > m + TA_LAZY || (m == -INFINITY && m_cand > -INFINITY);
           if (__any_sync(0xffffffffu, need)) {
-            // O must be at rest: P_{j-1} V_{j-1} was issued when the last thread signalled P_{j-1}, moments ago.  (The
-            // wait is occasional, which is safe: this barrier cannot complete another phase before this thread has
-            // signalled P_{j+1}.)
-            if (j > 0 && !mbar_wait(pv_done0 + 8 * ((it - 1) & 1u), ((it - 1) >> 1) & 1u, spin)) {
+            // O must be at rest: P_{j-2} V_{j-2}, the last product into this accumulator, signals the ring-stage
+            // barrier of its tile when it is done.  (The wait is occasional, which is safe: that barrier completes its
+            // next phase S tiles later, long after this thread has signalled P_j.)
+            if (j >= 2 && !mbar_wait(kv_empty0 + 8 * (int)((it - 2) % S), ((it - 2) / S) & 1u, spin)) {
               atomicExch(abort_flag, 1); atomicExch(&g_attn_tc_status, 8); ok = false; break;
             }
             tc_fence_after();
             const float cf = !need ? 1.f : (m == -INFINITY ? 0.f : ex2_approx(m - m_cand));
+#pragma unroll 1
+            for (int hh = 0; hh < 8; ++hh) {   // eight columns at a time: the score row occupies most registers
+              uint32_t w[8];
+              tmem_ld8(t_oh + hh * 8, w);
 #pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-              uint32_t w[32];
-              tmem_ld32_nowait(t_oh + hh * 32, w);
-              tmem_wait_ld();
-#pragma unroll
-              for (int i = 0; i < 32; ++i) w[i] = cf == 0.f ? 0u : __float_as_uint(__uint_as_float(w[i]) * cf);
-              tmem_st32(t_oh + hh * 32, w);
+              for (int i = 0; i < 8; ++i) w[i] = cf == 0.f ? 0u : __float_as_uint(__uint_as_float(w[i]) * cf);
+              tmem_st8(t_oh + hh * 8, w);
             }
             l *= cf;
             if (need) m = m_cand;
           }
+          if (lane == 0 && q4 == 0) TA_ACC(7);   // mask, maximum, (rare) rescale
           const float base = (m == -INFINITY) ? 0.f : m;
           const float2 sc2 = make_float2(sc_log2, sc_log2), nb2 = make_float2(-base, -base);
           float2 sa = make_float2(0.f, 0.f), sb = make_float2(0.f, 0.f);
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float2 ea = __ffma2_rn(make_float2(__uint_as_float(a[i]), __uint_as_float(a[i + 1])), sc2, nb2);
-            float2 ec = __ffma2_rn(make_float2(__uint_as_float(c[i]), __uint_as_float(c[i + 1])), sc2, nb2);
-            ea.x = ex2_approx(ea.x); ea.y = ex2_approx(ea.y);
-            ec.x = ex2_approx(ec.x); ec.y = ex2_approx(ec.y);
-            sa = __fadd2_rn(sa, ea);
-            sb = __fadd2_rn(sb, ec);
-            pw[i >> 1] = pack_p<T>(ea.x, ea.y);
-            pw[16 + (i >> 1)] = pack_p<T>(ec.x, ec.y);
+          for (int c2 = 0; c2 < 2; ++c2) {   // 64 keys = 32 columns of P at a time
+            uint32_t pw[32];
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              float2 ea = __ffma2_rn(make_float2(__uint_as_float(sv[2 * c2][i]), __uint_as_float(sv[2 * c2][i + 1])), sc2, nb2);
+              float2 ec = __ffma2_rn(make_float2(__uint_as_float(sv[2 * c2 + 1][i]), __uint_as_float(sv[2 * c2 + 1][i + 1])), sc2, nb2);
+              if (!TA_DBG(1)) {
+                ea.x = ex2_approx(ea.x); ea.y = ex2_approx(ea.y);
+                ec.x = ex2_approx(ec.x); ec.y = ex2_approx(ec.y);
+              }
+              sa = __fadd2_rn(sa, ea);
+              sb = __fadd2_rn(sb, ec);
+              pw[i >> 1] = pack_p<T>(ea.x, ea.y);
+              pw[16 + (i >> 1)] = pack_p<T>(ec.x, ec.y);
+            }
+            tmem_st32(t_p + c2 * 32, pw);
           }
           l += (sa.x + sa.y) + (sb.x + sb.y);
+          if (lane == 0 && q4 == 0) TA_ACC(8);   // exponentials, packing, tcgen05.st issue
         } else {
+          uint32_t pw[32];
 #pragma unroll
           for (int i = 0; i < 32; ++i) pw[i] = 0u;   // the tensor core multiplies all 128 rows: rows that see nothing add zero
+          tmem_st32(t_p, pw);
+          tmem_st32(t_p + 32, pw);
         }
-        tmem_st32(t_p, pw);
         tmem_wait_st();
         tc_fence_before();       // the writes of P_j (and of a rescaled O) and the reads of S[b] are complete
-        mbar_arrive(p_ready0 + 8 * b);
+        mbar_arrive(p_ready0 + 8 * b3);
+        if (lane == 0 && q4 == 0) TA_ACC(9);   // waiting for the stores, signalling P_j
       }
-      // ---- result of the row tile: merge the two halves (m, l, O)_lo and (m, l, O)_hi -----------------------------------
+      // ---- result of the row tile: merge the two parities (m, l, O)_0 and (m, l, O)_1 -----------------------------------
       if (ntiles == 0 && p.read_partial && present && h == 0) {   // no key tile at all: the state passes through
         const float mw = p.ws_m[gr];
         m = (mw == -INFINITY) ? -INFINITY : mw * 1.4426950408889634f;
@@ -594,6 +642,22 @@ bool launch_window_tc(const AttnParams& p, int qkv_dtype, int max_rows, int grou
 }  // namespace aspa
 
 using namespace aspa;
+
+#ifdef TA_TIMING
+extern "C" int aspa_attn_tc_debug(int flags) {
+  cudaMemcpyToSymbol(g_ta_debug, &flags, sizeof(int));
+  return ASPA_OK;
+}
+extern "C" int aspa_attn_tc_timing(unsigned long long* host16, int reset) {
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(host16, g_ta_cycles, sizeof(unsigned long long) * 16);
+  if (reset) {
+    unsigned long long z[16] = {};
+    cudaMemcpyToSymbol(g_ta_cycles, z, sizeof(z));
+  }
+  return ASPA_OK;
+}
+#endif
 
 extern "C" int aspa_attn_tc_status(int reset, void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
