@@ -19,8 +19,9 @@ What is different from the reference, on purpose:
   * no host synchronisation per chunk: per-chunk summaries are built after the loop from
     one device-to-host copy;
   * chunks can be sharded over the ranks of a ``torch.distributed`` process group: rank r
-    owns a contiguous range of chunks, records and kept rows are exchanged with
-    all-gather, the merge and pass 2 run replicated (see ``distributed.py``).
+    owns a contiguous range of chunks, the promotion records (one packed buffer) and the
+    promoted rows (one pool per rank) are exchanged with two all-gathers, the merge and pass 2
+    run replicated (see ``distributed.py``).
 """
 from __future__ import annotations
 
@@ -247,9 +248,9 @@ class _Pass1Records:
 
     def __init__(self, n_slots: int, budget: int, device: torch.device, top_p: float):
         self.n_slots, self.budget, self.top_p = n_slots, budget, top_p
-        self.scores = torch.zeros((n_slots, budget), dtype=torch.float32, device=device)
-        self.idx = torch.full((n_slots, budget), -1, dtype=torch.int64, device=device)
-        self.count = torch.zeros((n_slots,), dtype=torch.int32, device=device)
+        self.packed = dist_utils.PackedRecords(n_slots, budget, device)   # one buffer: one all-gather moves all three
+        self.scores, self.idx, self.count = self.packed.scores, self.packed.idx, self.packed.count
+        self.idx.fill_(-1)
         # two slot numbers: two chunks can be in flight at once, each on its own lane (stream + captured graph)
         self.slots = [torch.zeros((1,), dtype=torch.int32, device=device) for _ in range(PASS1_LANES)]
         self.slot = self.slots[0]
@@ -517,13 +518,15 @@ class ChunkedShortlistRunner:
 
         n_local = c_hi - c_lo
         budget = cfg.per_chunk_budget
-        records = self._records(max(n_local, 1))
+        cap = dist_utils.max_chunks_per_rank(n_chunks, world)   # slots per rank: the same on every rank (fixed-size exchange)
+        records = self._records(max(cap, 1))
         rec_scores, rec_idx, rec_count = records.scores, records.idx, records.count
         # Host-resident input: the rows of every promoted token are set aside while their chunk is on the device,
         # so that the reduced sequence is assembled from device memory instead of a second trip to the host.
+        # Sharded runs do the same whatever the source: each rank then contributes exactly the rows it promoted.
         pool = None
-        if not source.is_cuda and n_chunks * budget <= ops.MERGE_POS_MAX:
-            pool = torch.empty((max(n_local, 1) * budget, cfg.d_model), dtype=base_dtype, device=device)
+        if (not source.is_cuda or world > 1) and n_chunks * budget <= ops.MERGE_POS_MAX:
+            pool = torch.empty((max(cap, 1) * budget, cfg.d_model), dtype=base_dtype, device=device)
 
         ev_a = torch.cuda.Event(enable_timing=True)
         ev_b = torch.cuda.Event(enable_timing=True)
@@ -564,8 +567,8 @@ class ChunkedShortlistRunner:
                 main.wait_stream(lane)
 
         # exchange: every rank ends up with the records of all chunks, in chunk order
-        all_scores, all_idx, all_count = dist_utils.all_gather_records(self.group, rec_scores, rec_idx, rec_count,
-                                                                      n_chunks, world)
+        all_scores, all_idx, all_count = dist_utils.all_gather_packed_records(self.group, records.packed, n_chunks, world)
+        all_pool = dist_utils.all_gather_pool(self.group, pool, world) if (pool is not None and world > 1) else pool
         keep_pos = None
         if pool is not None:
             keep_idx, keep_sc, keep_count, keep_pos = ops.merge_finalise(all_scores.view(-1), all_idx.view(-1), cfg.seq_len,
@@ -579,7 +582,7 @@ class ChunkedShortlistRunner:
             """Gather the kept rows and run pass 2 for a kept count of ``k_host``."""
             kidx, ksc = keep_idx[:k_host], keep_sc[:k_host]
             if pool is not None:
-                red = self._gather_pooled(pool, keep_pos[:k_host], k_host, budget, world, c_lo, c_hi)
+                red = self._gather_pooled(all_pool, keep_pos[:k_host], k_host, budget, world, n_chunks)
             else:
                 red = self._gather_reduced(source, source_off, kidx, k_host, device, world, rank, c_lo, c_hi)
             out = info = stats = None
@@ -670,17 +673,18 @@ class ChunkedShortlistRunner:
                                       reduced_sequence=reduced, metrics=metrics, chunks=summaries,
                                       final_output=final_output, final_stats=final_stats, backend_info=backend_info)
 
-    def _gather_pooled(self, pool: torch.Tensor, keep_pos: torch.Tensor, k: int, budget: int, world: int, c_lo: int,
-                       c_hi: int) -> torch.Tensor:
-        """(1, k, C) rows of the kept tokens from the per-chunk pools of promoted rows.  ``keep_pos`` holds, for every
-        kept index, its position in the chunk-major list of all promotions (chunk * budget + rank within the chunk)."""
-        if world == 1:
-            return ops.gather_rows(pool, keep_pos, None, k).unsqueeze(0)
-        # every rank fills the rows it holds and leaves zeros elsewhere; the sum over ranks is the full sequence
-        lo, hi = c_lo * budget, c_hi * budget
-        local = torch.where((keep_pos >= lo) & (keep_pos < hi), keep_pos - lo, torch.full_like(keep_pos, -1))
-        rows = ops.gather_rows(pool, local, None, k)
-        return dist_utils.sum_disjoint_rows(self.group, rows, world).unsqueeze(0)
+    def _gather_pooled(self, pool: torch.Tensor, keep_pos: torch.Tensor, k: int, budget: int, world: int,
+                       n_chunks: int) -> torch.Tensor:
+        """(1, k, C) rows of the kept tokens from the pool of promoted rows (all ranks' pools after the all-gather).
+        ``keep_pos`` holds, for every kept index, its position in the chunk-major list of all promotions
+        (chunk * budget + rank within the chunk); the gathered pool is rank-major, which is the same order whenever
+        every rank owns the same number of chunks."""
+        if world > 1:
+            off = dist_utils.pool_row_of_position(n_chunks, world, budget, pool.device)
+            if off is not None:
+                chunk = torch.div(keep_pos.clamp(min=0), budget, rounding_mode="floor")
+                keep_pos = torch.where(keep_pos >= 0, keep_pos + off[chunk], keep_pos)
+        return ops.gather_rows(pool, keep_pos, None, k).unsqueeze(0)
 
     def _gather_reduced(self, source: torch.Tensor, source_off: int, keep_idx: torch.Tensor, k: int,
                         device: torch.device, world: int, rank: int, c_lo: int, c_hi: int) -> torch.Tensor:

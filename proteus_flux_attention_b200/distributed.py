@@ -7,7 +7,7 @@ definition these functions must reproduce.  Received data always lands in this r
 before any kernel reads it: no kernel here touches peer memory."""
 from __future__ import annotations
 
-from typing import Any, Tuple
+from typing import Any, Optional, Tuple
 
 import torch
 import torch.distributed as dist
@@ -81,6 +81,74 @@ def _padding_free_rows(n_chunks: int, world: int, cap: int, device: torch.device
         sel = torch.tensor(keep, dtype=torch.long, device=device)
         _SEL_CACHE[key] = sel
     return sel
+
+
+class PackedRecords:
+    """The promotion records of up to ``n_slots`` chunks in ONE int64 buffer, so that a single all-gather moves them:
+    ``[idx (n_slots, budget) int64 | scores (n_slots, budget) fp32 | count (n_slots) int32]``, each region contiguous
+    and handed to the kernels as an ordinary tensor view."""
+
+    def __init__(self, n_slots: int, budget: int, device: torch.device):
+        self.n_slots, self.budget = n_slots, budget
+        nb = n_slots * budget
+        self._n_idx, self._n_sc, self._n_ct = nb, (nb + 1) // 2, (n_slots + 1) // 2
+        self.buf = torch.zeros(self._n_idx + self._n_sc + self._n_ct, dtype=torch.int64, device=device)
+        self.idx, self.scores, self.count = self.views(self.buf)
+
+    def views(self, buf: torch.Tensor):
+        """(idx, scores, count) views of a buffer with this layout (1-D, or 2-D with one buffer per row)."""
+        lead = buf.shape[:-1]
+        a, b = self._n_idx, self._n_idx + self._n_sc
+        idx = buf[..., :a].reshape(*lead, self.n_slots, self.budget)
+        sc = buf[..., a:b].view(torch.float32)[..., : self.n_slots * self.budget].reshape(*lead, self.n_slots, self.budget)
+        ct = buf[..., b:].view(torch.int32)[..., : self.n_slots]
+        return idx, sc, ct
+
+
+def all_gather_packed_records(group: Any, rec: PackedRecords, n_chunks: int, world: int):
+    """One all-gather of every rank's ``PackedRecords`` buffer (each rank holds ``rec.n_slots`` = the per-rank maximum
+    of chunk slots; unused slots carry index -1 / count 0) -> (scores, idx, count) of all chunks in chunk order."""
+    if world == 1:
+        return rec.scores, rec.idx, rec.count
+    cap, budget = rec.n_slots, rec.budget
+    recv = torch.empty((world, rec.buf.numel()), dtype=rec.buf.dtype, device=rec.buf.device)
+    dist.all_gather_into_tensor(recv.view(-1), rec.buf, group=group)
+    idx, sc, ct = rec.views(recv)                                      # (world, cap, budget) x2, (world, cap)
+    idx, sc, ct = idx.reshape(world * cap, budget), sc.reshape(world * cap, budget), ct.reshape(world * cap)
+    if cap * world != n_chunks:
+        sel = _padding_free_rows(n_chunks, world, cap, rec.buf.device)
+        idx, sc, ct = idx[sel], sc[sel], ct[sel]
+    return sc.contiguous(), idx.contiguous(), ct.contiguous()
+
+
+def all_gather_pool(group: Any, pool: torch.Tensor, world: int) -> torch.Tensor:
+    """Per-rank pools of promoted rows ``(cap * budget, C)`` -> ``(world * cap * budget, C)``, rank-major.  Each rank
+    sends only the rows it promoted (8 MiB per rank for 2 chunks x 2048 rows x 1024 bf16 channels), where summing
+    zero-padded copies of the whole reduced sequence would move all of it through every rank."""
+    if world == 1:
+        return pool
+    recv = torch.empty((world * pool.size(0), pool.size(1)), dtype=pool.dtype, device=pool.device)
+    dist.all_gather_into_tensor(recv, pool.contiguous(), group=group)
+    return recv
+
+
+def pool_row_of_position(n_chunks: int, world: int, budget: int, device: torch.device) -> Optional[torch.Tensor]:
+    """Where chunk-major promotion position ``c * budget + i`` lies in the rank-major gathered pool: ``None`` when the
+    two orders coincide (every rank owns the same number of chunks), else the int64 offset to ADD per chunk
+    (n_chunks,), built once per shape."""
+    cap = max_chunks_per_rank(n_chunks, world)
+    if cap * world == n_chunks:
+        return None
+    key = ("pool", n_chunks, world, budget, str(device))
+    off = _SEL_CACHE.get(key)
+    if off is None:
+        vals = []
+        for r in range(world):
+            lo, hi = partition_chunks(n_chunks, world, r)
+            vals.extend((r * cap + (c - lo) - c) * budget for c in range(lo, hi))
+        off = torch.tensor(vals, dtype=torch.int64, device=device)
+        _SEL_CACHE[key] = off
+    return off
 
 
 def sum_disjoint_rows(group: Any, rows: torch.Tensor, world: int) -> torch.Tensor:

@@ -67,6 +67,25 @@ def _worker(rank, world, port, n_chunks, chunk_len, budget, buffer_tokens, seed,
         filled[mine] = rows
         summed = D.sum_disjoint_rows(None, filled, world)
         assert torch.equal(summed, reduced)
+        # the exchange of the sharded runner: one packed record buffer and one pool of promoted rows per rank
+        cap = D.max_chunks_per_rank(n_chunks, world)
+        rec = D.PackedRecords(cap, budget, torch.device("cpu"))
+        rec.idx.fill_(-1)
+        rec.scores[:n_local], rec.idx[:n_local], rec.count[:n_local] = sc[:n_local], ix[:n_local], ct[:n_local]
+        p_sc, p_ix, p_ct = D.all_gather_packed_records(None, rec, n_chunks, world)
+        assert torch.equal(p_sc, a_sc) and torch.equal(p_ix, a_ix) and torch.equal(p_ct, a_ct)
+        pool = torch.zeros(cap * budget, seq.size(2))
+        for j in range(n_local):
+            n = int(ct[j])
+            pool[j * budget: j * budget + n] = seq[0, ix[j, :n]]
+        all_pool = D.all_gather_pool(None, pool, world)
+        # position of every kept index in the chunk-major promotion list, then in the rank-major gathered pool
+        flat_ix = a_ix.view(-1)
+        pos = torch.tensor([int((flat_ix == t).nonzero()[0]) for t in keep_idx.tolist()], dtype=torch.int64)
+        off = D.pool_row_of_position(n_chunks, world, budget, torch.device("cpu"))
+        if off is not None:
+            pos = pos + off[pos // budget]
+        assert torch.equal(all_pool[pos], reduced)
         out_q.put((rank, a_ct.tolist(), keep_idx.tolist(), reduced.clone()))
     finally:
         dist.destroy_process_group()
