@@ -244,33 +244,25 @@ class LayerWorkload:
     def __init__(self, name, device):
         import proteus_flux_attention_b200 as P
         self.name, self.device = name, device
-        if name == "sparse_16k":
-            self.B, self.T = 4, 16384
-            cfg = dict(d_model=1024, n_head=16, attn_h_total=16, attn_gates=16, attn_h_active=4, attn_h_active_min=4,
-                       attn_h_active_max=4, attn_linear_head_k=4, attn_token_sparse=True, attn_token_keep_ratio=0.2,
-                       attn_mode="auto", attn_small_seq_dense=0, attn_router_top_p=0.0, attn_use_rope=True,
-                       attn_rope_base=10000.0, n_ctx=16384, attn_track_latency=False, attn_proto_enable=True)
-        else:
-            self.B, self.T = 1, 262144
-            cfg = dict(d_model=1024, n_head=16, attn_h_total=16, attn_mode="linear", attn_quantize_int8=True,
-                       attn_linear_L=4096, attn_linear_L_base=4096, attn_linear_L_max=4096, attn_linear_window=4096,
-                       attn_linear_anchor_stride=128, attn_linear_policy="local+anchors+proto", attn_h_active=2,
-                       attn_h_active_min=2, attn_h_active_max=2, attn_token_sparse=True, attn_token_keep_ratio=0.2,
-                       n_ctx=262144, attn_track_latency=False, attn_proto_enable=True)
+        self.B, self.T = {"sparse_16k": (4, 16384), "shortlist_256k": (1, 262144), "sparse_4k_fp32": (1, 4096)}[name]
+        cfg = dict(LAYER_CFGS[name])
+        self.dtype = torch.float32 if name == "sparse_4k_fp32" else torch.bfloat16
         self.tokens = self.B * self.T
         layer = P.AdaptiveSparseProtoAttention(P.ModelConfig(**cfg))
-        self.state = xavier_state(layer, torch.bfloat16, 0)
-        self.layer = layer.to(torch.bfloat16)
+        C = cfg["d_model"]
+        self.state = xavier_state(layer, self.dtype, 0)
+        self.layer = layer.to(self.dtype)
         self.layer.load_state_dict(self.state)
         self.layer = self.layer.to(device).eval()
         g = torch.Generator(device=device).manual_seed(0)
-        x = torch.randn(self.B, self.T, 1024, generator=g, device=device)
+        x = torch.randn(self.B, self.T, C, generator=g, device=device)
         if name == "shortlist_256k":
             pos = torch.randperm(self.T, generator=torch.Generator().manual_seed(1))[:64].to(device)
             x[:, pos] *= 4.0
-        self.x = x.to(torch.bfloat16)
+        self.x = x.to(self.dtype)
         self.host_x = None
         self.hp = torch.cuda.Stream(device=device, priority=-2) if self.high_priority else None
+        self.step_events = []
         self.captured = None
         if self.use_graph:
             try:
@@ -278,8 +270,9 @@ class LayerWorkload:
                 self.x = self.captured.static_in   # the resident input is the graph's own input: no copy per step
             except RuntimeError as e:
                 print(f"[bench] {name}: layer call not capturable ({e}); eager calls", file=sys.stderr)
-        self.config = {"workload": name, "batch": self.B, "seq_len": self.T, "d_model": 1024, "heads": 16,
-                       "l2": "activations (>= 128 MiB per tensor) larger than L2",
+        self.config = {"workload": name, "batch": self.B, "seq_len": self.T, "d_model": C, "heads": cfg["attn_h_total"],
+                       "l2": ("activations (>= 128 MiB per tensor) larger than L2" if self.B * self.T * C * 2 >= (128 << 20)
+                              else "L2 flushed between steps (a 256 MiB buffer is rewritten)"),
                        "stream": "layer call on a priority -2 stream" if self.high_priority else "default priority",
                        "launch": "CUDA graph replay" if self.captured is not None else "eager"}
 
@@ -303,6 +296,17 @@ class LayerWorkload:
 
     def step(self):
         self._reset()
+        if self.B * self.T * self.x.size(2) * 2 < (128 << 20):   # inputs fit in L2: flush it between steps
+            if not hasattr(self, "_flush"):
+                self._flush = torch.empty(256 << 20, dtype=torch.uint8, device=self.device)
+            self._flush.zero_()
+            # the flush is not part of the step: bracket the call itself; the caller sums these instead of one bracket
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            y = self._call(self.x)
+            b.record()
+            self.step_events.append((a, b))
+            return y
         return self._call(self.x)
 
     def step_e2e(self):
@@ -313,7 +317,127 @@ class LayerWorkload:
         y = self._call(self.host_x.to(self.device, non_blocking=True))
         self.host_y.copy_(y, non_blocking=True)
         torch.cuda.synchronize()
-        return self.host_x.numel() * 2, y.numel() * 2
+        return self.host_x.numel() * self.host_x.element_size(), y.numel() * y.element_size()
+
+
+class LMWorkload:
+    """BASELINE configuration 5: a 12-layer decoder (d_model 768, 12 heads x 64, RMSNorm, SwiGLU 3072, vocabulary
+    32000) with the drop-in attention module in every layer and its automatic mode choice (dense fast path up to
+    1024 tokens, dense / sparse below 16K, linear shortlist above), bf16, forward only, random N(0, 0.02) weights.
+    Everything around the attention module is plain PyTorch, as it would be in a model that adopts the module."""
+    name = "lm_12l"
+
+    def __init__(self, device, B=2, T=32768):
+        import torch.nn as nn
+        import proteus_flux_attention_b200 as P
+        self.device, self.B, self.T = device, B, T
+        self.tokens = B * T
+        d, H, L, V, F_ = 768, 12, 12, 32000, 3072
+
+        class Block(nn.Module):
+            def __init__(self):
+                super().__init__()
+                self.n1, self.n2 = nn.RMSNorm(d), nn.RMSNorm(d)
+                self.attn = P.CausalASPAMultiheadAttention(d, H, bias=False, max_seq_len=32768, attn_small_seq_dense=1024,
+                                                           attn_active_seq_low=1024, attn_linear_switch_ctx=16384,
+                                                           attn_use_rope=True, attn_track_latency=False)
+                self.w1, self.w3, self.w2 = nn.Linear(d, F_, bias=False), nn.Linear(d, F_, bias=False), nn.Linear(F_, d, bias=False)
+
+            def forward(self, x):
+                x = x + self.attn(self.n1(x), need_weights=False)[0]
+                h = self.n2(x)
+                return x + self.w2(torch.nn.functional.silu(self.w1(h)) * self.w3(h))
+
+        class LM(nn.Module):
+            def __init__(self):
+                super().__init__()
+                self.emb = nn.Embedding(V, d)
+                self.blocks = nn.ModuleList(Block() for _ in range(L))
+                self.norm, self.head = nn.RMSNorm(d), nn.Linear(d, V, bias=False)
+
+            def forward(self, ids):
+                x = self.emb(ids)
+                for blk in self.blocks:
+                    x = blk(x)
+                return self.head(self.norm(x))
+
+        torch.manual_seed(0)
+        model = LM()
+        with torch.no_grad():
+            for prm in model.parameters():
+                if prm.dim() >= 2:
+                    prm.normal_(0.0, 0.02)
+        self.model = model.to(torch.bfloat16).to(device).eval()
+        self.ids = torch.randint(0, V, (B, T), generator=torch.Generator().manual_seed(0)).to(device)
+        self.host_ids = None
+        self.config = {"workload": self.name, "layers": L, "d_model": d, "heads": H, "mlp": "SwiGLU 3072", "vocab": V,
+                       "batch": B, "seq_len": T, "l2": "activations (96 MiB per layer tensor, 4 GiB of logits) larger than L2"}
+
+    @torch.no_grad()
+    def step(self):
+        return self.model(self.ids)
+
+    @torch.no_grad()
+    def step_e2e(self):
+        if self.host_ids is None:
+            self.host_ids = self.ids.cpu().pin_memory()
+            self.host_last = torch.empty((self.B, 32000), dtype=torch.bfloat16, pin_memory=True)
+        logits = self.model(self.host_ids.to(self.device, non_blocking=True))
+        self.host_last.copy_(logits[:, -1], non_blocking=True)     # what a caller reads back: next-token logits
+        torch.cuda.synchronize()
+        return self.host_ids.numel() * 8, self.host_last.numel() * 2
+
+    @torch.no_grad()
+    def mode_sweep(self):
+        """Attention mode the first layer picks at 512 / 2048 / 8192 / 32768 tokens, with the forward time of the model."""
+        out = {}
+        for T in (512, 2048, 8192, 32768):
+            ids = self.ids[:, :T].contiguous()
+            for _ in range(2):
+                self.model(ids)
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(3):
+                self.model(ids)
+            b.record()
+            torch.cuda.synchronize()
+            st = self.model.blocks[0].attn.attention._last_sparse_state or {}
+            out[str(T)] = {"mode": st.get("mode"), "ms_per_forward": round(a.elapsed_time(b) / 3, 3),
+                           "tokens_per_s": round(self.B * T / (a.elapsed_time(b) / 3e3))}
+        return out
+
+
+class AttentionWorkload:
+    """The window-attention kernel alone, for profiling (--profile-mode): dense causal attention over 16 heads x 8192
+    tokens x 64 channels, bf16 - 50 MB of q, k, v, resident in L2, which is the regime in which the tile products
+    rather than HBM bound the kernel.  `--attn-kernel` forces the tcgen05 or the warp-MMA kernel."""
+    name = "attn_dense_8k"
+
+    def __init__(self, device, kernel="auto"):
+        from proteus_flux_attention_b200 import _native as N
+        from proteus_flux_attention_b200.sparse_attn import attention_packed
+        self.device, self.call = device, attention_packed
+        heads, T = 16, 8192
+        self.heads, self.T, self.tokens = heads, T, T
+        g = torch.Generator(device=device).manual_seed(0)
+        self.q, self.k, self.v = (torch.randn(heads, T, 64, generator=g, device=device).to(torch.bfloat16) for _ in range(3))
+        self.offs = torch.arange(0, (heads + 1) * T, T, dtype=torch.int32, device=device)
+        self.tok = torch.arange(T, dtype=torch.int32, device=device).repeat(heads)
+        self.out = torch.zeros(heads, T, 64, dtype=torch.bfloat16, device=device)
+        N.lib().aspa_attn_tc_mode({"auto": 1, "tcgen05": 2, "warp_mma": 0}[kernel])
+        self.flops = 4 * 64 * heads * T * (T + 1) / 2
+        self.config = {"workload": self.name, "heads": heads, "seq_len": T, "head_dim": 64, "kernel": kernel,
+                       "useful_flops_per_step": self.flops, "l2": "q, k, v (50 MB) resident in L2 on purpose"}
+
+    def step(self):
+        return self.call(self.q, self.k, self.v, row_offsets=self.offs, token_idx=self.tok, max_rows=self.T,
+                         total_rows=self.heads * self.T, H=self.heads, plan=None, out=self.out)
+
+    def step_e2e(self):
+        self.step()
+        torch.cuda.synchronize()
+        return 0, 0
 
 
 class RouterWorkload:
@@ -522,9 +646,13 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="chunked_1m", choices=["chunked_1m", "shortlist_256k", "sparse_16k", "router_64k"])
+    ap.add_argument("--workload", default="chunked_1m", choices=["chunked_1m", "shortlist_256k", "sparse_16k", "sparse_4k_fp32", "lm_12l", "attn_dense_8k", "router_64k"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--attn-kernel", default="auto", choices=["auto", "tcgen05", "warp_mma"],
+                    help="attn_dense_8k only: which tile kernel runs the window pass")
+    ap.add_argument("--no-parity-check", action="store_true",
+                    help="multi-GPU runs: skip the untimed comparison of the N-rank result with a 1-rank run on rank 0")
     ap.add_argument("--no-other-workloads", action="store_true",
                     help="skip the shortlist_256k / sparse_16k side measurements of the default run")
     ap.add_argument("--clock-sampler", default="nvml", choices=["nvml", "smi", "none"],
@@ -560,7 +688,32 @@ def main():
     else:
         if world > 1:
             raise SystemExit("layer workloads do not shard: run them with --gpus 1 (replicas only)")
-        wl = RouterWorkload(device) if args.workload == "router_64k" else LayerWorkload(args.workload, device)
+        if args.workload == "router_64k":
+            wl = RouterWorkload(device)
+        elif args.workload == "lm_12l":
+            wl = LMWorkload(device)
+        elif args.workload == "attn_dense_8k":
+            wl = AttentionWorkload(device, args.attn_kernel)
+        else:
+            wl = LayerWorkload(args.workload, device)
+    # Sharded runs: outside the timed region, rank 0 repeats the whole job alone (a one-member process group, the full
+    # sequence regenerated from the same per-chunk seeds) and the kept indices and the final output of the N-rank run
+    # must be bit-equal to it.
+    if world > 1 and args.workload == "chunked_1m" and not args.no_parity_check:
+        solo = dist.new_group([0])
+        res_n = wl.step()
+        torch.cuda.synchronize()
+        ok = True
+        if rank == 0:
+            wl1 = ChunkedWorkload(device, 1, 0, solo)
+            res_1 = wl1.step()
+            torch.cuda.synchronize()
+            ok = (torch.equal(res_n.keep_indices, res_1.keep_indices) and torch.equal(res_n.final_output, res_1.final_output)
+                  and torch.equal(res_n.reduced_sequence, res_1.reduced_sequence))
+            del wl1, res_1
+            torch.cuda.empty_cache()
+        wl.config["parity_vs_1rank"] = bool(ok)
+        dist.barrier()
     if cpu_affinity is not None:
         wl.config["host_binding"] = f"each rank pinned to the {cpu_affinity} CPUs local to its GPU (NVML affinity)"
 
@@ -591,6 +744,8 @@ def main():
     sync()
     clocks.end()
     ms = e0.elapsed_time(e1)
+    if getattr(wl, "step_events", None):   # steps that flush L2 in between time each call on its own
+        ms = sum(a.elapsed_time(b) for a, b in wl.step_events[-args.steps:])
     launches = ops.LAUNCHES - launches0
     clock_summary = clocks.summary()
     if hasattr(wl, "phases_ms"):  # device time of the two halves of the last timed step, on this rank
@@ -611,11 +766,17 @@ def main():
     if captured is not None:
         wl.captured = None
     launches0 = ops.LAUNCHES
+    for _ in range(args.steps):     # launch count of a step as it really runs (forked streams, lanes), eagerly
+        wl.step()
+    launches = ops.LAUNCHES - launches0
+    # ... and the kernel times from a strictly serial pass (nothing forked onto other streams): an event bracket around
+    # a kernel that shares the GPU with another stream's GEMM would time the queueing, not the kernel
+    ops.SERIAL_STREAMS = True
     ops.start_timing()
     for _ in range(args.steps):
         wl.step()
     kt = ops.stop_timing()
-    launches = ops.LAUNCHES - launches0
+    ops.SERIAL_STREAMS = False
     if hasattr(wl, "runner"):
         wl.runner.config.use_cuda_graph = True
     if captured is not None:
@@ -633,6 +794,14 @@ def main():
                     "launch_ms": tot_ms / n, "algorithmic_bytes_per_launch": nbytes / n,
                     "kernels_ms_per_step": {k: round(v[1] / args.steps, 4) for k, v in sorted(kt.items(), key=lambda kv: -kv[1][1])}}
 
+    if args.workload == "attn_dense_8k":   # the tile products bound this one: useful flops against the measured GEMM peak
+        pk = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())["bf16_tflops"] if (ROOT / "MEASURED_PEAKS.json").exists() else 1590.0
+        ach = wl.flops / (ms_per_step * 1e-3) / 1e12
+        roofline = {"bound": "tensor", "kernel": "attention", "achieved": ach, "peak": pk, "unit": "TFLOP/s", "frac": ach / pk,
+                    "peak_kind": "of measured" if (ROOT / "MEASURED_PEAKS.json").exists() else "of fallback", "traffic": None,
+                    "note": "useful flops 4 * D * sum of row lengths; the kernel also multiplies the masked half of diagonal tiles"}
+    if args.workload == "lm_12l":
+        wl.config["mode_sweep"] = wl.mode_sweep()
     e2e = None
     if not args.no_e2e:
         for _ in range(2):
@@ -648,11 +817,24 @@ def main():
         e2e = {"value": wl.tokens / (float(dt.item()) / args.steps), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
                "d2h_bytes_per_step": int(d2h)}
 
+    # one cold number: the first run() on a sequence at a NEW address (per-chunk graphs are keyed by address, so all
+    # of pass 1 is captured afresh); layers stay cached.  Outside every timed region above.
+    if args.workload == "chunked_1m" and not args.no_e2e:
+        fresh = wl.shard.clone()
+        sync()
+        t0 = time.perf_counter()
+        wl.runner.run(fresh, chunk_state=wl.chunk_state, final_state=wl.final_state, sequence_is_local_shard=True)
+        torch.cuda.synchronize()
+        wl.config["cold_first_run_ms"] = round((time.perf_counter() - t0) * 1e3, 2)
+        wl.runner.run(wl.shard, chunk_state=wl.chunk_state, final_state=wl.final_state, sequence_is_local_shard=True)
+        del fresh
+        sync()
+
     # the single-layer workloads of the same metric, measured in the same run (one GPU; they do not shard)
     others = None
     if rank == 0 and world == 1 and args.workload == "chunked_1m" and not args.no_other_workloads:
         others = {}
-        for name, k in (("shortlist_256k", 5), ("sparse_16k", 20)):
+        for name, k in (("shortlist_256k", 5), ("sparse_16k", 20), ("sparse_4k_fp32", 20)):
             lw = LayerWorkload(name, device)
             for _ in range(3):
                 lw.step()
@@ -664,21 +846,39 @@ def main():
             b.record()
             torch.cuda.synchronize()
             ms_l = a.elapsed_time(b) / k
+            if lw.step_events:
+                ms_l = sum(x.elapsed_time(y) for x, y in lw.step_events[-k:]) / k
             others[name] = {"tokens_per_s": lw.tokens / (ms_l / 1e3), "ms_per_step": ms_l, "steps": k, "warmup": 3,
                             "config": lw.config}
             del lw
             torch.cuda.empty_cache()
+        lm = LMWorkload(device)
+        for _ in range(2):
+            lm.step()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(3):
+            lm.step()
+        b.record()
+        torch.cuda.synchronize()
+        ms_l = a.elapsed_time(b) / 3
+        others["lm_12l"] = {"tokens_per_s": lm.tokens / (ms_l / 1e3), "ms_per_step": ms_l, "steps": 3, "warmup": 2,
+                            "config": lm.config, "mode_sweep": lm.mode_sweep()}
+        del lm
+        torch.cuda.empty_cache()
         wl.config["other_workloads"] = others
 
     cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline and args.workload != "router_64k":
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and args.workload in ("chunked_1m", *LAYER_CFGS):
         v, _, cores, kind, desc = cpu_sample(args.workload, 2)
         cpu = {"value": v, "unit": "tokens/s", "cores": cores, "kind": kind, "sample": desc}
     if rank == 0:
         print(json.dumps({"metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
                           "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True,
                           "scaling": "strong" if args.workload == "chunked_1m" else "replicas", "vs_baseline": None,
-                          "dtype": "bf16", "data": "synthetic", "config": wl.config, "clocks": clock_summary,
+                          "dtype": "f32" if args.workload == "sparse_4k_fp32" else "bf16", "data": "synthetic",
+                          "config": wl.config, "clocks": clock_summary,
                           "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline, "cpu_baseline": cpu}))
     if world > 1:
         dist.destroy_process_group()

@@ -586,6 +586,8 @@ class AdaptiveSparseAttention(nn.Module):
         side = _SIDE_STREAMS.get((str(dev), prio))
         if side is None:
             side = _SIDE_STREAMS[(str(dev), prio)] = torch.cuda.Stream(device=dev, priority=prio)
+        if ops.SERIAL_STREAMS:
+            side = main
         ready, done = torch.cuda.Event(), torch.cuda.Event()
         ready.record(main)
         side.wait_event(ready)
@@ -618,6 +620,8 @@ class AdaptiveSparseAttention(nn.Module):
         side = _SIDE_STREAMS.get((str(dev), prio))
         if side is None:
             side = _SIDE_STREAMS[(str(dev), prio)] = torch.cuda.Stream(device=dev, priority=prio)
+        if ops.SERIAL_STREAMS:
+            side = main
         ready, done = torch.cuda.Event(), torch.cuda.Event()
         ready.record(main)
         side.wait_event(ready)

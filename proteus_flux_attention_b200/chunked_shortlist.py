@@ -274,7 +274,7 @@ class _Pass1Records:
         ready.record(main)
         self.stream.wait_event(ready)
         mask = layer._last_token_mask
-        with torch.cuda.stream(self.stream):
+        with torch.cuda.stream(main if ops.SERIAL_STREAMS else self.stream):
             ops.chunk_select_slot(layer._last_token_importance.view(-1),
                                   mask.view(torch.uint8).view(-1) if mask is not None else None, self.budget, self.top_p,
                                   self.slot, self.offsets, self.scores, self.idx, self.count)

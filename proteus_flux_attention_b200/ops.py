@@ -74,6 +74,7 @@ def reduce_partials(partials: torch.Tensor, n_series: int) -> torch.Tensor:
     return out
 
 
+SERIAL_STREAMS = False           # True: nothing is forked onto side streams (per-kernel timing passes need one serial stream)
 USE_ANCHOR_TILES = True          # strided anchor keys of a plan go through the tile kernel when groups are large enough
 USE_TC_ROUTER = True             # bf16 activations take the tcgen05 router when the shape allows
 _ROUTER_STATUS: dict = {}        # device -> int32[1], raised by the tensor-core router if a bounded wait ran out
