@@ -224,8 +224,18 @@ int aspa_rope_quantize(const void* qkv, int B, int T, int H, int D, const float*
 /* max |x| per head of a (heads, T*D) tensor (aspa.py:1328). amax is overwritten. */
 int aspa_head_amax(const void* x, int dtype, int heads, int64_t per_head, float* amax, void* stream);
 
+/* Per-head quantile of |x| for the percentile modes of the quantiser (aspa.py:1330-1338): base[h] =
+ * torch.quantile(|x_h|, q) with linear interpolation between the two neighbouring order statistics (rank = q*(n-1)
+ * evaluated in float32, as torch does), replaced by amax[h] where it is not positive.  Exact order statistics by a
+ * four-pass radix select.  x (heads, per_head) F32 or BF16; 0 < q <= 1; amax from aspa_head_amax; scratch of
+ * aspa_head_abs_quantile_scratch(heads) bytes; base (heads) fp32 out, usable as the `amax` of aspa_quantize_int8. */
+int64_t aspa_head_abs_quantile_scratch(int heads);
+int aspa_head_abs_quantile(const void* x, int dtype, int heads, int64_t per_head, double q, const float* amax,
+                           void* scratch, float* base, void* stream);
+
 /* Symmetric per-head INT8: scale = max(amax/127, 1e-6); q = clamp(rint(x/scale), +-127).
- * Replaces _quantize_per_head_int8 in "max" mode (aspa.py:1312-1363). */
+ * Replaces _quantize_per_head_int8 (aspa.py:1312-1363); `amax` is the per-head base of whichever mode: the maximum,
+ * the percentile of aspa_head_abs_quantile, or its running average. */
 int aspa_quantize_int8(const void* x, int dtype, int heads, int64_t per_head, const float* amax,
                        int8_t* out, float* scales, void* stream);
 

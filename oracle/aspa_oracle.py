@@ -666,7 +666,10 @@ def memory_candidates(s, mem, active_heads: torch.Tensor, token_idx: torch.Tenso
 # INT8 per-head quantiser (aspa.py:1312-1363)
 # ----------------------------------------------------------------------------
 
-def quantize_per_head_int8(t: torch.Tensor, mode: str = "max", percentile: float = 1.0):
+def quantize_per_head_int8(t: torch.Tensor, mode: str = "max", percentile: float = 1.0, ema: Optional[dict] = None,
+                           ema_key: str = "", ema_decay: float = 0.9):
+    """``ema`` (mode "ema_percentile") is the layer's dictionary of running bases; an entry that is missing or has
+    another head count starts from this call's maximum (aspa.py:1339-1356)."""
     flat = t.to(torch.float32).reshape(t.size(0), -1)
     a = flat.abs()
     amax = a.amax(dim=1, keepdim=True)
@@ -675,6 +678,13 @@ def quantize_per_head_int8(t: torch.Tensor, mode: str = "max", percentile: float
     else:
         q = torch.quantile(a, percentile, dim=1, keepdim=True)
         base = torch.where(q > 0.0, q, amax)
+    if mode == "ema_percentile" and ema is not None:
+        prev = ema.get(ema_key)
+        if prev is None or prev.numel() != flat.size(0):
+            prev = amax.squeeze(1)
+        updated = ema_decay * prev + (1.0 - ema_decay) * base.squeeze(1)
+        ema[ema_key] = updated
+        base = updated.unsqueeze(1)
     scales = torch.clamp(base / 127.0, min=1e-6)
     quant = torch.clamp((flat / scales).round(), -127.0, 127.0).to(torch.int8).view_as(t)
     return quant.contiguous(), scales.squeeze(1).contiguous()
@@ -786,6 +796,7 @@ class OracleLayer:
         self.state = SimpleNamespace(latency_ema=None, current_alpha=0.0, L_scale=s.linear_L_scale_init,
                                      alpha_override=None, last_target_k=None)
         self.memory = new_memory_bank(s) if s.memory_enabled else None
+        self.quant_ema: Dict[str, torch.Tensor] = {}
         self.trace: Dict[str, Any] = {}
 
     def set_shortlist_alpha(self, v: float) -> None:
@@ -889,9 +900,11 @@ class OracleLayer:
                     extra_candidates=extra, extra_lengths=extra_len)
                 tr["candidates"], tr["lengths"], tr["packed"] = cands, lens, packed
                 if s.quantize_int8:
-                    qq, qs_ = quantize_per_head_int8(qf, s.quantize_mode, s.quantize_percentile)
-                    kq, ks_ = quantize_per_head_int8(kf, s.quantize_mode, s.quantize_percentile)
-                    vq, vs_ = quantize_per_head_int8(vf, s.quantize_mode, s.quantize_percentile)
+                    kw = dict(ema=self.quant_ema, ema_decay=s.quantize_ema_decay)
+                    qq, qs_ = quantize_per_head_int8(qf, s.quantize_mode, s.quantize_percentile, ema_key="q", **kw)
+                    kq, ks_ = quantize_per_head_int8(kf, s.quantize_mode, s.quantize_percentile, ema_key="k", **kw)
+                    vq, vs_ = quantize_per_head_int8(vf, s.quantize_mode, s.quantize_percentile, ema_key="v", **kw)
+                    tr["quant_scales"] = (qs_, ks_, vs_)
                     att = sparse_attention(qq, kq, vq, packed=packed, candidates=cands, lengths=lens,
                                            q_scale=qs_, k_scale=ks_, v_scale=vs_, out_dtype=qf.dtype)
                 else:

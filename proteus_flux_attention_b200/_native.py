@@ -57,6 +57,8 @@ SIGNATURES = {
     "aspa_rope_quantize": (_i, [_p, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p]),
     "aspa_head_amax": (_i, [_p, _i, _i, _l, _p, _p]),
     "aspa_quantize_int8": (_i, [_p, _i, _i, _l, _p, _p, _p, _p]),
+    "aspa_head_abs_quantile_scratch": (_l, [_i]),
+    "aspa_head_abs_quantile": (_i, [_p, _i, _i, _l, _d, _p, _p, _p, _p]),
     "aspa_proto_plan_scratch": (_l, [_i, _i, _i]),
     "aspa_proto_plan": (_i, [_p, _i, _i, _i, _p, _p, _p, _p]),
     "aspa_build_candidates": (_i, [_p, _p, _l, _i, _i, _i, _i, _i, _i, _p, _i, _i, _i, _p, _p, _p]),

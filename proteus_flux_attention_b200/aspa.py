@@ -259,6 +259,9 @@ class AdaptiveSparseAttention(nn.Module):
         self.quantize_sparse_int8_mode = qmode if qmode in {"max", "percentile", "ema_percentile"} else "max"
         self.quantize_sparse_int8_percentile = min(max(_num(config, "attn_quantize_int8_percentile", 1.0), 0.0), 1.0)
         self.quantize_sparse_int8_ema_decay = min(max(_num(config, "attn_quantize_int8_ema_decay", 0.9), 0.0), 0.9999)
+        for name in ("_quant_ema_q", "_quant_ema_k", "_quant_ema_v"):
+            self.register_buffer(name, torch.zeros(heads, dtype=torch.float32), persistent=False)
+        self._quant_ema_flags = {"_quant_ema_q": False, "_quant_ema_k": False, "_quant_ema_v": False}
 
         seq_low, seq_high = _num(config, "attn_active_seq_low", 0, int), _num(config, "attn_active_seq_high", 0, int)
         if seq_low <= 0:
@@ -630,6 +633,26 @@ class AdaptiveSparseAttention(nn.Module):
             ops.rope_quantize(self.qkv(x).contiguous(), H, D, cos, sin, out=pack)
             done.record(side)
         return {"pack": pack, "done": done}
+
+    def _percentile_bases(self, tensors, amax: torch.Tensor) -> torch.Tensor:
+        """Per-head quantisation bases of q, k, v in the "percentile" and "ema_percentile" modes (reference
+        aspa.py:1329-1356): the percentile of |x| (the maximum when the percentile is 0 or the quantile is 0), and in
+        the EMA mode its running average, which starts from the maximum of the first call (or of any call whose head
+        count differs from the stored one)."""
+        pct = float(self.quantize_sparse_int8_percentile)
+        out = []
+        for i, (t_, name) in enumerate(zip(tensors, ("_quant_ema_q", "_quant_ema_k", "_quant_ema_v"))):
+            base = amax[i].contiguous() if pct <= 0.0 else ops.head_abs_quantile(t_, pct, amax[i].contiguous())
+            if self.quantize_sparse_int8_mode == "ema_percentile":
+                ema = getattr(self, name)
+                if ema is None or ema.numel() != base.numel() or not self._quant_ema_flags.get(name, False):
+                    ema = amax[i]
+                base = self.quantize_sparse_int8_ema_decay * ema.to(torch.float32) + \
+                    (1.0 - self.quantize_sparse_int8_ema_decay) * base
+                setattr(self, name, base.detach())
+                self._quant_ema_flags[name] = True
+            out.append(base)
+        return torch.stack(out)
 
     def _project_compact_q(self, x: torch.Tensor, compact: dict) -> torch.Tensor:
         """q for the kept tokens only; the q rows of dropped tokens stay unwritten."""
@@ -1083,10 +1106,13 @@ class AdaptiveSparseAttention(nn.Module):
                 qa, ka, va, sc3 = quant_pack
                 scales = (sc3[0], sc3[1], sc3[2])
             elif use_quant:
-                if self.quantize_sparse_int8_mode != "max" and self.quantize_sparse_int8_percentile < 1.0:
-                    raise NotImplementedError("INT8 percentile scaling below 1.0 is not built in the sm_100a path")
                 if amax is None:
                     amax = torch.stack([ops.head_amax(t_) for t_ in (q, k, v)])
+                if self.quantize_sparse_int8_mode != "max":
+                    if self.memory_enabled:
+                        raise NotImplementedError("INT8 percentile scaling together with the key/value memory bank is not "
+                                                  "built in the sm_100a path")
+                    amax = self._percentile_bases((q, k, v), amax)
                 if self.memory_enabled:   # k and v are quantised with the ring appended (aspa.py:1226-1272)
                     amax = amax.clone()
                     ops.memory_fold_amax(self.memory_keys, self.memory_values, self.memory_counts, self.memory_ptr, B,

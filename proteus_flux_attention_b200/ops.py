@@ -239,6 +239,17 @@ def quantize_int8(x: torch.Tensor, amax: torch.Tensor):
     return out, scales
 
 
+def head_abs_quantile(x: torch.Tensor, q: float, amax: torch.Tensor) -> torch.Tensor:
+    """(heads,) fp32: torch.quantile(|x_h|, q) per head (linear interpolation), the head's maximum where that is zero."""
+    heads = x.size(0)
+    base = _empty((heads,), torch.float32, x.device)
+    scratch = _empty((int(N.lib().aspa_head_abs_quantile_scratch(heads)),), torch.uint8, x.device)
+    with _timed('head_abs_quantile', 10, 4 * _nb(x)):
+        N.check(N.lib().aspa_head_abs_quantile(N.ptr(x), N.dtype_code(x.dtype), heads, x.numel() // heads, float(q),
+                                               N.ptr(amax), N.ptr(scratch), N.ptr(base), N.stream()), "head_abs_quantile")
+    return base
+
+
 PROTO_BLOCK = 128
 
 

@@ -3,7 +3,7 @@
 Run in the development container, where the reference source tree is
 mounted read-only:
 
-    PROTEUS_REF_SRC=<reference>/src python tests/golden/make_golden.py [--memory-only | --config1-only]
+    PROTEUS_REF_SRC=<reference>/src python tests/golden/make_golden.py [--memory-only | --config1-only | --quant-only]
 
 The reference is imported unmodified from PROTEUS_REF_SRC.  Every case stores
 the seeded inputs, the module weights and the outputs the reference produced,
@@ -320,6 +320,17 @@ def memory_cases():
                B=2, T=192, dtype=torch.bfloat16, calls=3, outliers=8)
 
 
+def quant_cases():
+    # percentile and running-percentile INT8 bases (aspa.py:1329-1356): three calls, so the running base moves twice
+    q = dict(BASE, attn_mode="linear", attn_quantize_int8=True, attn_linear_L=40, attn_linear_L_max=40,
+             attn_linear_window=40, attn_linear_policy="local+anchors+proto", attn_gates=8)
+    layer_case("layer_bf16_int8_percentile", dict(q, attn_quantize_int8_mode="percentile", attn_quantize_int8_percentile=0.98),
+               B=1, T=224, dtype=torch.bfloat16, outliers=8, calls=2)
+    layer_case("layer_bf16_int8_ema", dict(q, attn_quantize_int8_mode="ema_percentile", attn_quantize_int8_percentile=0.995,
+                                           attn_quantize_int8_ema_decay=0.8),
+               B=2, T=192, dtype=torch.bfloat16, outliers=6, calls=3)
+
+
 def config1_case():
     """BASELINE configuration 1 at full size (1 x 4096 x 512 fp32, 8 heads, 8 gates, top-2, keep 0.25).  Weights and
     input come from seeds (``seeded.py``), so only what the reference produced is stored: token mask, packed rows,
@@ -357,7 +368,11 @@ def main():
     if "--config1-only" in sys.argv:
         config1_case()
         return
+    if "--quant-only" in sys.argv:
+        quant_cases()
+        return
     config1_case()
+    quant_cases()
     schedule_case()
     candidate_case()
     attention_case()

@@ -859,3 +859,28 @@ def test_router_bounded_wait_runs_out_and_reports_timeout(dev):
     d = (gate - ref[0]).abs()
     assert float(d.max()) < 1.0 / 64 and float((d > 1e-5).float().mean()) < 2e-3
     assert torch.allclose(sim, ref[2], atol=2e-6)
+
+
+# ---------------------------------------------------------------------------------------------- INT8 percentile bases
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n,q", [(64 * 37, 0.98), (4096 * 64, 0.999), (1000, 0.5), (7, 1.0), (300 * 64, 0.9375)])
+def test_head_abs_quantile_equals_torch_quantile(dev, dtype, n, q):
+    """The radix-select quantile of |x| per head is torch.quantile's (linear interpolation, float32 rank arithmetic);
+    a head whose quantile is zero falls back to its maximum (aspa.py:1330-1338)."""
+    from proteus_flux_attention_b200 import ops
+    g = torch.Generator().manual_seed(n)
+    x = torch.randn(5, n, generator=g)
+    x[1] *= 100.0
+    x[2, : int(n * 0.99)] = 0.0            # quantile 0 -> maximum
+    x[3] = x[3].round()                    # many duplicates
+    x = x.to(dtype)
+    a = x.float().abs()
+    amax = a.amax(dim=1)
+    want = torch.quantile(a, q, dim=1)
+    want = torch.where(want > 0, want, amax)
+    got = ops.head_abs_quantile(x.to(dev), q, amax.to(dev)).cpu()
+    # the two order statistics are exact; the interpolation may differ from the host's by one rounding (fused or not)
+    assert torch.allclose(got, want, rtol=3e-7, atol=0.0), (got, want)
+    qd, _ = ops.quantize_int8(x.to(dev).view(5, n, 1), got.to(dev))
+    qo = torch.clamp((x.float() / torch.clamp(want / 127.0, min=1e-6).unsqueeze(1)).round(), -127, 127).to(torch.int8)
+    assert (qd.cpu().view(5, n) != qo).float().mean() < 1e-4

@@ -80,7 +80,7 @@ def test_chunk_selection_matches_reference(golden_dir):
 
 LAYER_CASES = ["layer_fp32_auto", "layer_fp32_proto", "layer_bf16_rope", "layer_bf16_int8",
                "layer_fp32_dense_fastpath", "layer_fp32_dense_density", "layer_fp32_nucleus",
-               "layer_fp32_memory", "layer_bf16_int8_memory"]
+               "layer_fp32_memory", "layer_bf16_int8_memory", "layer_bf16_int8_percentile", "layer_bf16_int8_ema"]
 
 
 def _tie_only(imp_row, a, b):
