@@ -217,8 +217,7 @@ class ChunkedWorkload:
     def step(self):
         res = self.runner.run(self.shard, chunk_state=self.chunk_state, final_state=self.final_state,
                               sequence_is_local_shard=True)
-        self.phases_ms = {"pass1_exchange_merge": round(res.metrics.chunk_time_ms, 3),
-                          "gather_pass2": round(res.metrics.final_time_ms, 3)}
+        self.phases_ms = dict(getattr(self.runner, "last_phase_ms", {}), pass1_exchange_merge=round(res.metrics.chunk_time_ms, 3))
         return res
 
     def step_e2e(self):
@@ -714,6 +713,20 @@ def main():
             torch.cuda.empty_cache()
         wl.config["parity_vs_1rank"] = bool(ok)
         dist.barrier()
+    # One GPU: outside the timed region, the run as it is timed (graph replay, lanes, speculative pass 2) must give
+    # exactly what the same job gives eagerly on one stream, and a well-formed result.
+    if world == 1 and args.workload == "chunked_1m" and not args.profile_mode:
+        res_g = wl.step()
+        wl.runner.config.use_cuda_graph = False
+        res_e = wl.step()
+        wl.runner.config.use_cuda_graph = True
+        ki = res_g.keep_indices
+        wl.config["self_check"] = bool(
+            torch.equal(ki, res_e.keep_indices) and torch.equal(res_g.final_output, res_e.final_output)
+            and ki.numel() == BUFFER and bool((ki[1:] > ki[:-1]).all()) and int(ki.min()) >= 0 and int(ki.max()) < SEQ_1M
+            and bool(torch.isfinite(res_g.final_output.float()).all()) and bool(torch.isfinite(res_g.keep_scores).all())
+            and torch.equal(res_g.reduced_sequence[0], wl.shard[0][ki.to(device)]))
+        del res_g, res_e
     if cpu_affinity is not None:
         wl.config["host_binding"] = f"each rank pinned to the {cpu_affinity} CPUs local to its GPU (NVML affinity)"
 

@@ -141,7 +141,8 @@ class ChunkedShortlistConfig:
     freeze_prototypes: bool = False      # EMA decay 1.0 in pass 1: chunks become independent (needed for sharding)
     pass1_full_forward: bool = True      # False: pass 1 runs only router + token keep (its attention output is unused)
     warmup: bool = True                  # the reference's untimed warm-up forward on noise (:583-589)
-    collect_summaries: bool = True       # build per-chunk python lists after the loop
+    collect_summaries: bool = True       # build the python-side summaries after the run: per-chunk lists and final_stats
+                                         # (False: the final layer's telemetry stays readable on the layer object)
     use_cuda_graph: bool = False         # replay pass 1's per-chunk layer call from a captured CUDA graph
 
     def validate(self) -> None:
@@ -255,14 +256,26 @@ class _Pass1Records:
         self.slots = [torch.zeros((1,), dtype=torch.int32, device=device) for _ in range(PASS1_LANES)]
         self.slot = self.slots[0]
         self.offsets = torch.zeros((n_slots,), dtype=torch.int64, device=device)
+        self._template = None
+        self._offsets_template = torch.zeros((n_slots,), dtype=torch.int64, device=device)
+        self._offsets_for = None
         self.stream = torch.cuda.Stream(device=device, priority=-2)
 
     def reset(self, first_chunk: int, chunk_len: int) -> None:
-        self.scores.zero_()
-        self.idx.fill_(-1)
-        self.count.zero_()
-        torch.arange(first_chunk, first_chunk + self.n_slots, out=self.offsets)
-        self.offsets.mul_(chunk_len)
+        """Empty records (scores 0, indices -1, counts 0) and the global offset of every slot: two copies from
+        templates built once (this runs at the head of every call, with the GPU idle until the first chunk starts)."""
+        if self._template is None:
+            self._template = self.packed.buf.clone()
+            idx_t, _, _ = self.packed.views(self._template)
+            self._template.zero_()
+            idx_t.fill_(-1)
+        key = (first_chunk, chunk_len)
+        if self._offsets_for != key:
+            torch.arange(first_chunk, first_chunk + self.n_slots, out=self._offsets_template)
+            self._offsets_template.mul_(chunk_len)
+            self._offsets_for = key
+        self.packed.buf.copy_(self._template)
+        self.offsets.copy_(self._offsets_template)
 
     def use_lane(self, lane: int) -> None:
         self.slot = self.slots[lane]
@@ -567,8 +580,14 @@ class ChunkedShortlistRunner:
                 main.wait_stream(lane)
 
         # exchange: every rank ends up with the records of all chunks, in chunk order
+        ev_p1 = torch.cuda.Event(enable_timing=True)
+        ev_x1 = torch.cuda.Event(enable_timing=True)
+        ev_x2 = torch.cuda.Event(enable_timing=True)
+        ev_p1.record()
         all_scores, all_idx, all_count = dist_utils.all_gather_packed_records(self.group, records.packed, n_chunks, world)
+        ev_x1.record()
         all_pool = dist_utils.all_gather_pool(self.group, pool, world) if (pool is not None and world > 1) else pool
+        ev_x2.record()
         keep_pos = None
         if pool is not None:
             keep_idx, keep_sc, keep_count, keep_pos = ops.merge_finalise(all_scores.view(-1), all_idx.view(-1), cfg.seq_len,
@@ -577,6 +596,9 @@ class ChunkedShortlistRunner:
             keep_idx, keep_sc, keep_count = ops.merge_finalise(all_scores.view(-1), all_idx.view(-1), cfg.seq_len,
                                                                cfg.buffer_tokens)
         ev_b.record()
+
+        # the allocator's statistics cost the host 0.1-0.2 ms per call: kept for eager runs and on request
+        track_peak = cfg.report_latency or not cfg.use_cuda_graph
 
         def second_half(k_host: int):
             """Gather the kept rows and run pass 2 for a kept count of ``k_host``."""
@@ -588,7 +610,8 @@ class ChunkedShortlistRunner:
             out = info = stats = None
             if cfg.run_final_pass:
                 final_model = self._make_layer(k_host, cfg.final_sparse_ratio, base_dtype, final_state, cfg.freeze_prototypes)
-                torch.cuda.reset_peak_memory_stats(device)
+                if track_peak:
+                    torch.cuda.reset_peak_memory_stats(device)
                 if cfg.use_cuda_graph:
                     out = self._final_replay(final_model, red)
                 else:
@@ -627,25 +650,37 @@ class ChunkedShortlistRunner:
         chunk_time_ms = None
         final_stats = None
         final_time_ms = peak_mb = None
-        if fm is not None:
+        ev_c.record()
+        # Everything the host reads back travels to pinned memory behind the last kernel, so that ONE wait for the
+        # device ends the call: router status, kept indices and scores (the telemetry record of pass 2 is pinned already).
+        status_pin = self.__dict__.get("_status_pin")
+        if status_pin is None:
+            status_pin = self.__dict__["_status_pin"] = torch.zeros(1, dtype=torch.int32, pin_memory=True)
+        status_pin.copy_(ops.router_status(device), non_blocking=True)
+        keep_pin = self.__dict__.get("_keep_pin")
+        if keep_pin is None or keep_pin[0].numel() < keep_idx.numel():
+            keep_pin = self.__dict__["_keep_pin"] = (torch.empty(max(keep_idx.numel(), cfg.buffer_tokens), dtype=torch.int64, pin_memory=True),
+                                                     torch.empty(max(keep_idx.numel(), cfg.buffer_tokens), dtype=torch.float32, pin_memory=True))
+        keep_pin[0][: keep_idx.numel()].copy_(keep_idx, non_blocking=True)
+        keep_pin[1][: keep_sc.numel()].copy_(keep_sc, non_blocking=True)
+        torch.cuda.synchronize(device)
+        if int(status_pin.item()) != 0:   # a bounded wait ran out in some chunk's router: nothing of this run is valid
+            ops.check_router_status(device)
+        t1 = time.perf_counter()
+        keep_idx_host, keep_sc_host = keep_pin[0][: keep_idx.numel()].clone(), keep_pin[1][: keep_sc.numel()].clone()
+        if fm is not None and cfg.collect_summaries:
             final_model = fm[0]
             final_stats = _sanitize_mapping(dict(final_model.last_head_stats or {}))
             st = {k: v for k, v in (final_model._last_sparse_state or {}).items() if not isinstance(v, torch.Tensor)}
             if st:
                 final_stats["sparse_state"] = _sanitize_mapping(st)
-        ev_c.record()
-        status_pin = self.__dict__.get("_status_pin")
-        if status_pin is None:
-            status_pin = self.__dict__["_status_pin"] = torch.zeros(1, dtype=torch.int32, pin_memory=True)
-        status_pin.copy_(ops.router_status(device), non_blocking=True)
-        torch.cuda.synchronize(device)
-        if int(status_pin.item()) != 0:   # a bounded wait ran out in some chunk's router: nothing of this run is valid
-            ops.check_router_status(device)
-        t1 = time.perf_counter()
         chunk_time_ms = float(ev_a.elapsed_time(ev_b))
+        self.last_phase_ms = {"pass1": round(ev_a.elapsed_time(ev_p1), 3), "exchange_records": round(ev_p1.elapsed_time(ev_x1), 3),
+                              "exchange_rows": round(ev_x1.elapsed_time(ev_x2), 3), "merge": round(ev_x2.elapsed_time(ev_b), 3),
+                              "gather_pass2": round(ev_b.elapsed_time(ev_c), 3), "host_wall": round((t1 - t0) * 1e3, 3)}
         if cfg.run_final_pass:
             final_time_ms = float(ev_b.elapsed_time(ev_c))
-            peak_mb = torch.cuda.max_memory_allocated(device) / BYTES_PER_MB
+            peak_mb = torch.cuda.max_memory_allocated(device) / BYTES_PER_MB if track_peak else None
         total_s = t1 - t0
 
         summaries: List[ChunkSummary] = []
@@ -669,7 +704,7 @@ class ChunkedShortlistRunner:
             host_limit_mb=None, storage_reason=None, world_size=world)
         self.logger.info("Chunked Shortlist retained %s/%s tokens (%.3f) across %s chunks", metrics.retained_tokens,
                          metrics.original_tokens, metrics.retention_ratio, n_chunks)
-        return ChunkedShortlistResult(keep_indices=keep_idx.to("cpu"), keep_scores=keep_sc.to("cpu"),
+        return ChunkedShortlistResult(keep_indices=keep_idx_host, keep_scores=keep_sc_host,
                                       reduced_sequence=reduced, metrics=metrics, chunks=summaries,
                                       final_output=final_output, final_stats=final_stats, backend_info=backend_info)
 

@@ -13,6 +13,11 @@ import torch
 import torch.distributed as dist
 
 
+import os
+
+POOL_EXCHANGE = os.environ.get("ASPA_POOL_EXCHANGE", "allgather")   # "allgather" (one NCCL all-gather) or "p2p" (grouped send/recv)
+
+
 def world_and_rank(group: Any = None) -> Tuple[int, int]:
     if not (dist.is_available() and dist.is_initialized()):
         return 1, 0
@@ -128,6 +133,21 @@ def all_gather_pool(group: Any, pool: torch.Tensor, world: int) -> torch.Tensor:
     if world == 1:
         return pool
     recv = torch.empty((world * pool.size(0), pool.size(1)), dtype=pool.dtype, device=pool.device)
+    if POOL_EXCHANGE == "p2p" and pool.is_cuda:
+        # one send and one receive per peer in a single group call: through NVSwitch every pair has its own full-rate
+        # path, so the pools cross in one hop instead of travelling round a ring
+        rank = dist.get_rank(group)
+        n = pool.size(0)
+        recv[rank * n:(rank + 1) * n].copy_(pool)
+        ops_ = []
+        for step in range(1, world):
+            dst, src = (rank + step) % world, (rank - step) % world
+            ops_.append(dist.P2POp(dist.isend, pool, dist.get_global_rank(group, dst) if group is not None else dst, group))
+            ops_.append(dist.P2POp(dist.irecv, recv[src * n:(src + 1) * n],
+                                   dist.get_global_rank(group, src) if group is not None else src, group))
+        for req in dist.batch_isend_irecv(ops_):
+            req.wait()
+        return recv
     dist.all_gather_into_tensor(recv, pool.contiguous(), group=group)
     return recv
 
