@@ -136,11 +136,11 @@ class ClockSampler:
 
 
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the main kernels of one 65536-token chunk
-# of the chunked_1m workload, from ncu captures on B200 (summaries: profiles/ncu_traffic_chunked_1m_kernels.md, profiles/ncu_full_attn_rows64_chunked_1m.md,
-# profiles/ncu_full_router_tc_65536x1024.md).
+# of the chunked_1m workload, from one-kernel ncu captures on B200 of the chunk_64k workload (the same chunk step alone;
+# summaries: profiles/ncu_attn_rows64_chunk_64k.md, ncu_rope_inplace_chunk_64k.md, ncu_router_tc_chunk_64k.md,
+# ncu_chunk_select_cluster_chunk_64k.md).
 NCU_DRAM_BYTES_PER_LAUNCH = {
-    "chunked_1m": {"attention": 245.4e6, "rope_inplace": 234.8e6, "router_tc": 134.9e6, "scatter_rows_fill": 78.4e6,
-                   "token_select": 0.3e6},
+    "chunked_1m": {"attention": 224.7e6, "rope_inplace": 237.2e6, "router_tc": 139.0e6, "chunk_select": 0.4e6},
 }
 
 
@@ -240,10 +240,12 @@ class LayerWorkload:
     # 4 x 16384 tokens the host cost of the few dozen launches exceeds their device time.
     use_graph = True
 
-    def __init__(self, name, device):
+    def __init__(self, name, device, seq_len=None):
         import proteus_flux_attention_b200 as P
         self.name, self.device = name, device
         self.B, self.T = {"sparse_16k": (4, 16384), "shortlist_256k": (1, 262144), "sparse_4k_fp32": (1, 4096)}[name]
+        if seq_len:   # a shorter sequence through the same kernels, for profiler captures
+            self.T = int(seq_len)
         cfg = dict(LAYER_CFGS[name])
         self.dtype = torch.float32 if name == "sparse_4k_fp32" else torch.bfloat16
         self.tokens = self.B * self.T
@@ -432,6 +434,47 @@ class AttentionWorkload:
     def step(self):
         return self.call(self.q, self.k, self.v, row_offsets=self.offs, token_idx=self.tok, max_rows=self.T,
                          total_rows=self.heads * self.T, H=self.heads, plan=None, out=self.out)
+
+    def step_e2e(self):
+        self.step()
+        torch.cuda.synchronize()
+        return 0, 0
+
+
+class ChunkStepWorkload:
+    """One pass-1 chunk of the chunked pipeline alone, eagerly on one stream: the chunk layer over 65536 tokens plus
+    the promotion of 2048 of them.  Holds about 1 GB on the device: the case profiler captures of the chunk kernels
+    (`--profile-mode`) are taken on."""
+    name = "chunk_64k"
+
+    def __init__(self, device):
+        import proteus_flux_attention_b200 as P
+        from proteus_flux_attention_b200 import ops
+        from proteus_flux_attention_b200.chunked_shortlist import _build_model_config
+        self.ops, self.device, self.tokens = ops, device, CHUNK
+        mc = _build_model_config(CHUNK, D_MODEL, heads=HEADS, sparse_ratio=0.05, shortlist_alpha=1.0, router_top_p=0.9)
+        mc.attn_proto_decay = 1.0
+        layer = P.AdaptiveSparseAttention(mc)
+        layer.load_state_dict(xavier_state(layer, torch.bfloat16, 0))
+        self.layer = layer.to(device=device, dtype=torch.bfloat16).eval()
+        self.layer.set_shortlist_alpha(1.0)
+        self.x = chunk_data(0, device, torch.bfloat16).view(1, CHUNK, D_MODEL)
+        self.rec = (torch.zeros(1, BUDGET, device=device), torch.full((1, BUDGET), -1, dtype=torch.int64, device=device),
+                    torch.zeros(1, dtype=torch.int32, device=device), torch.zeros(1, dtype=torch.int32, device=device),
+                    torch.zeros(1, dtype=torch.int64, device=device))
+        self.config = {"workload": self.name, "tokens": CHUNK, "d_model": D_MODEL, "heads": HEADS,
+                       "l2": "activations (128 MiB per tensor) larger than L2"}
+
+    def step(self):
+        self.ops.SERIAL_STREAMS = True
+        try:
+            y = self.layer(self.x)
+            sc, ix, ct, slot, offs = self.rec
+            self.ops.chunk_select_slot(self.layer._last_token_importance.view(-1),
+                                       self.layer._last_token_mask.view(torch.uint8).view(-1), BUDGET, 0.9, slot, offs, sc, ix, ct)
+        finally:
+            self.ops.SERIAL_STREAMS = False
+        return y
 
     def step_e2e(self):
         self.step()
@@ -645,9 +688,11 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="chunked_1m", choices=["chunked_1m", "shortlist_256k", "sparse_16k", "sparse_4k_fp32", "lm_12l", "attn_dense_8k", "router_64k"])
+    ap.add_argument("--workload", default="chunked_1m", choices=["chunked_1m", "shortlist_256k", "sparse_16k", "sparse_4k_fp32", "lm_12l", "attn_dense_8k", "chunk_64k", "router_64k"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--layer-seq-len", type=int, default=None,
+                    help="single-layer workloads: run the same layer on a shorter sequence (for profiler captures)")
     ap.add_argument("--attn-kernel", default="auto", choices=["auto", "tcgen05", "warp_mma"],
                     help="attn_dense_8k only: which tile kernel runs the window pass")
     ap.add_argument("--no-parity-check", action="store_true",
@@ -693,8 +738,10 @@ def main():
             wl = LMWorkload(device)
         elif args.workload == "attn_dense_8k":
             wl = AttentionWorkload(device, args.attn_kernel)
+        elif args.workload == "chunk_64k":
+            wl = ChunkStepWorkload(device)
         else:
-            wl = LayerWorkload(args.workload, device)
+            wl = LayerWorkload(args.workload, device, args.layer_seq_len)
     # Sharded runs: outside the timed region, rank 0 repeats the whole job alone (a one-member process group, the full
     # sequence regenerated from the same per-chunk seeds) and the kept indices and the final output of the N-rank run
     # must be bit-equal to it.
