@@ -79,8 +79,9 @@ static inline TcPlan tc_plan(int N, int G, int C, bool has_proto) {
 // GT = number of gates when it is 16 or 32 (epilogue in registers), 0 = any other count (epilogue through shared memory)
 template <int GT>
 __global__ void __launch_bounds__(TC_THREADS, 1)
-router_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
-                 const __nv_bfloat16* __restrict__ x, int64_t n,
+router_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_xt,
+                 const __grid_constant__ CUtensorMap tmap_w, const __nv_bfloat16* __restrict__ x, int64_t n,
+                 const int rows_per_cta,
                  int C, int G, int N, int has_proto, const float* __restrict__ conf_eps,
                  const float* __restrict__ usage_bias, float proto_temp, float proto_threshold, float proto_span,
                  float proto_blend, float usage_boost, float* __restrict__ gate_probs,
@@ -106,7 +107,14 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
   }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_k = C / TC_BK;
-  const int64_t ntiles = (n + TC_BM - 1) / TC_BM;
+  // This CTA's token range [cta_row0, cta_end): rows_per_cta (a multiple of 32) rows as 128-row tiles, the last of
+  // them shorter when rows_per_cta is no multiple of 128 (copied with its own tensor map, tmap_xt: a shorter box costs
+  // proportionally less of the stream, so every SM gets the same share of the bytes and none runs a whole tile longer).
+  const int64_t cta_row0 = (int64_t)blockIdx.x * rows_per_cta;
+  const int64_t cta_end = cta_row0 + rows_per_cta < n ? cta_row0 + rows_per_cta : n;
+  const int tiles_per_cta = (rows_per_cta + TC_BM - 1) / TC_BM;
+  const int tail_rows = rows_per_cta - (tiles_per_cta - 1) * TC_BM;            // rows of the last tile of a full range
+  const int ntiles = cta_end > cta_row0 ? (int)((cta_end - cta_row0 + TC_BM - 1) / TC_BM) : 0;   // tiles of this CTA
   const uint32_t buf_cols = (uint32_t)N;   // one accumulator buffer
   uint32_t tmem_cols = 32;
   while (tmem_cols < 2 * buf_cols) tmem_cols <<= 1;
@@ -137,36 +145,42 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
 
   if (warp == 12) {
     // ---- TMA producer ------------------------------------------------------------------------------------
+    // (this loop and the MMA loop below are single threads: every instruction in them is exposed latency, so ring
+    // positions are carried, not divided out, and the abort flag is only looked at inside a wait that does not
+    // succeed at once)
     if (lane == 0) {
-      uint32_t it = 0, withheld = 0xffffffffu;
+      uint32_t issued = 0, withheld = 0xffffffffu;
+      RingPos pos{0, 0u};
       bool ok = true;
       const uint32_t w_tile = (uint32_t)N * TC_BK * 2;
+      const uint32_t ring0 = s_addr(smem);
       if (plan.w_resident) {  // the whole weight operand, once: num_k tiles of N x 64 on one barrier
         mbar_expect_tx(wbar, w_tile * (uint32_t)num_k);
         for (int kb = 0; kb < num_k; ++kb) tma_load_2d(s_addr(smem + plan.w_off) + kb * w_tile, &tmap_w, kb * TC_BK, 0, wbar);
       }
-      for (int64_t tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-        for (int kb = 0; kb < num_k; ++kb, ++it) {
-          const int s = (int)(it % (uint32_t)S);
-          const uint32_t ph = (it / (uint32_t)S) & 1u;
-          if (aborted(abort_flag)) { ok = false; break; }
-          if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, spin)) { atomicExch(abort_flag, 1); atomicExch(status, 1); ok = false; break; }
-          const uint32_t a_dst = s_addr(smem + s * plan.stage_bytes), b_dst = a_dst + TC_A_BYTES;
-          if (tile == withhold_tile && kb == 0) {   // test hook: this stage is never filled, its consumers must give up
-            withheld = it;
+      for (int tile = 0; tile < ntiles && ok; ++tile) {
+        const int row0 = (int)(cta_row0 + (int64_t)tile * TC_BM);
+        const bool short_tile = tile == tiles_per_cta - 1 && tail_rows < TC_BM;
+        const CUtensorMap* map_x = short_tile ? &tmap_xt : &tmap_x;
+        const uint32_t stage_tx = (short_tile ? (uint32_t)tail_rows * TC_BK * 2 : (uint32_t)TC_A_BYTES) + (plan.w_resident ? 0u : w_tile);
+        for (int kb = 0; kb < num_k; ++kb, ++issued, pos.next(S)) {
+          if (!mbar_wait_abortable(empty0 + 8 * pos.s, pos.ph ^ 1u, abort_flag, spin)) { raise_abort(abort_flag, status, 1); ok = false; break; }
+          if ((int64_t)blockIdx.x * tiles_per_cta + tile == withhold_tile && kb == 0) {   // test hook: this stage is never filled, its consumers must give up
+            withheld = issued;
             continue;
           }
-          mbar_expect_tx(full0 + 8 * s, TC_A_BYTES + (plan.w_resident ? 0u : w_tile));
-          tma_load_2d(a_dst, &tmap_x, kb * TC_BK, (int)(tile * TC_BM), full0 + 8 * s);
-          if (!plan.w_resident) tma_load_2d(b_dst, &tmap_w, kb * TC_BK, 0, full0 + 8 * s);
+          const uint32_t a_dst = ring0 + (uint32_t)pos.s * (uint32_t)plan.stage_bytes, bar = full0 + 8 * pos.s;
+          mbar_expect_tx(bar, stage_tx);
+          tma_load_2d(a_dst, map_x, kb * TC_BK, row0, bar);
+          if (!plan.w_resident) tma_load_2d(a_dst + TC_A_BYTES, &tmap_w, kb * TC_BK, 0, bar);
         }
       }
       if (plan.w_resident) mbar_wait(wbar, 0, spin);  // the weight copies, too, must have landed before shared memory goes away
       // Shared memory must outlive every copy this thread started.  On the normal path the consumers have already
       // waited for all of them; after an abort they may have left early, so wait here (bounded) for the last
       // copy issued into each stage.
-      const uint32_t first = it > (uint32_t)S ? it - (uint32_t)S : 0u;
-      for (uint32_t j = first; j < it; ++j)
+      const uint32_t first = issued > (uint32_t)S ? issued - (uint32_t)S : 0u;
+      for (uint32_t j = first; j < issued; ++j)
         if (j != withheld) mbar_wait(full0 + 8 * (j % (uint32_t)S), (j / (uint32_t)S) & 1u, spin);
     }
   } else if (warp == 13) {
@@ -174,30 +188,27 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     if (lane == 0) {
       // instruction descriptor: D fp32, A/B bf16, both K-major, N/8 at bit 17, M/16 at bit 24
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
-      uint32_t it = 0, t = 0;
+      // operand descriptors by 64-bit adds on the start-address field (16-byte units; shared memory ends below 2^18)
+      const uint64_t a_desc0 = umma_desc_k_sw128(s_addr(smem));
+      const uint64_t b_desc0 = umma_desc_k_sw128(plan.w_resident ? s_addr(smem + plan.w_off) : s_addr(smem) + TC_A_BYTES);
+      const uint64_t stage_step = (uint64_t)(plan.stage_bytes >> 4), w_step = (uint64_t)((N * TC_BK * 2) >> 4);
+      RingPos pos{0, 0u};
+      uint32_t t = 0;
       bool ok = true;
-      if (plan.w_resident && !mbar_wait(wbar, 0, spin)) { atomicExch(abort_flag, 1); atomicExch(status, 8); ok = false; }
-      for (int64_t tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++t) {
+      if (plan.w_resident && !mbar_wait_abortable(wbar, 0, abort_flag, spin)) { raise_abort(abort_flag, status, 8); ok = false; }
+      for (int tile = 0; tile < ntiles && ok; ++tile, ++t) {
         const uint32_t buf = t & 1u, aph = (t >> 1) & 1u;
-        if (aborted(abort_flag)) break;
-        if (!mbar_wait(acc_empty0 + 8 * buf, aph ^ 1u, spin)) { atomicExch(abort_flag, 1); atomicExch(status, 5); break; }
+        if (!mbar_wait_abortable(acc_empty0 + 8 * buf, aph ^ 1u, abort_flag, spin)) { raise_abort(abort_flag, status, 5); break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t d_tmem = tmem_base + buf * buf_cols;
-        for (int kb = 0; kb < num_k; ++kb, ++it) {
-          const int s = (int)(it % (uint32_t)S);
-          const uint32_t ph = (it / (uint32_t)S) & 1u;
-          if (aborted(abort_flag)) { ok = false; break; }
-          if (!mbar_wait(full0 + 8 * s, ph, spin)) { atomicExch(abort_flag, 1); atomicExch(status, 2); ok = false; break; }
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t a_addr = s_addr(smem + s * plan.stage_bytes);
-          const uint32_t b_addr = plan.w_resident ? s_addr(smem + plan.w_off) + (uint32_t)kb * (uint32_t)N * TC_BK * 2
-                                                  : a_addr + TC_A_BYTES;
+        for (int kb = 0; kb < num_k; ++kb, pos.next(S)) {
+          if (!mbar_wait_abortable(full0 + 8 * pos.s, pos.ph, abort_flag, spin)) { raise_abort(abort_flag, status, 2); ok = false; break; }
+          const uint64_t da = a_desc0 + (uint64_t)pos.s * stage_step;
+          const uint64_t db = plan.w_resident ? b_desc0 + (uint64_t)kb * w_step : b_desc0 + (uint64_t)pos.s * stage_step;
 #pragma unroll
-          for (int k = 0; k < TC_BK / 16; ++k) {
-            umma_bf16(d_tmem, umma_desc_k_sw128(a_addr + k * 32), umma_desc_k_sw128(b_addr + k * 32), idesc,
-                      (kb > 0 || k > 0) ? 1u : 0u);
-          }
-          umma_commit(empty0 + 8 * s);  // arrives once the MMAs above have finished reading this stage
+          for (int k = 0; k < TC_BK / 16; ++k)   // 32 bytes = 2 address units per 16-element step along K
+            umma_bf16(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          umma_commit(empty0 + 8 * pos.s);  // arrives once the MMAs above have finished reading this stage
         }
         if (ok) umma_commit(acc_full0 + 8 * buf);  // arrives once every MMA of the tile has landed in tensor memory
       }
@@ -205,17 +216,16 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
   } else if (warp < 4) {
     // ---- norm warps: thread r owns token row r of every tile ------------------------------------------------
     const int r = threadIdx.x;
-    uint32_t it = 0, t = 0;
+    RingPos pos{0, 0u};
+    uint32_t t = 0;
     bool ok = true;
-    for (int64_t tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++t) {
-      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-      for (int kb = 0; kb < num_k; ++kb, ++it) {
-        const int s = (int)(it % (uint32_t)S);
-        const uint32_t ph = (it / (uint32_t)S) & 1u;
-        if (aborted(abort_flag)) { ok = false; break; }
-        if (!mbar_wait(full0 + 8 * s, ph, spin)) { atomicExch(abort_flag, 1); atomicExch(status, 3); ok = false; break; }
+    const unsigned char* row0 = smem + r * 128;
+    for (int tile = 0; tile < ntiles && ok; ++tile, ++t) {
+      float2 acc_a = make_float2(0.f, 0.f), acc_b = make_float2(0.f, 0.f);
+      for (int kb = 0; kb < num_k; ++kb, pos.next(S)) {
+        if (!mbar_wait_abortable(full0 + 8 * pos.s, pos.ph, abort_flag, spin)) { raise_abort(abort_flag, status, 3); ok = false; break; }
         if (has_proto) {
-          const unsigned char* row = smem + s * plan.stage_bytes + r * 128;
+          const unsigned char* row = row0 + pos.s * plan.stage_bytes;
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             // the swizzle only permutes 16-byte chunks inside a row; rotate the start so lanes hit different banks
@@ -223,19 +233,19 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
             const float2 f0 = __bfloat1622float2(h2[0]), f1 = __bfloat1622float2(h2[1]);
             const float2 f2 = __bfloat1622float2(h2[2]), f3 = __bfloat1622float2(h2[3]);
-            a0 = fmaf(f0.x, f0.x, a0); a1 = fmaf(f0.y, f0.y, a1);
-            a2 = fmaf(f1.x, f1.x, a2); a3 = fmaf(f1.y, f1.y, a3);
-            a0 = fmaf(f2.x, f2.x, a0); a1 = fmaf(f2.y, f2.y, a1);
-            a2 = fmaf(f3.x, f3.x, a2); a3 = fmaf(f3.y, f3.y, a3);
+            acc_a = __ffma2_rn(f0, f0, acc_a);   // four fp32 chains, two per packed FMA
+            acc_b = __ffma2_rn(f1, f1, acc_b);
+            acc_a = __ffma2_rn(f2, f2, acc_a);
+            acc_b = __ffma2_rn(f3, f3, acc_b);
           }
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(empty0 + 8 * s);
+        if (lane == 0) mbar_arrive(empty0 + 8 * pos.s);
       }
       if (!ok) break;
       const uint32_t buf = t & 1u, nph = (t >> 1) & 1u;
-      if (!mbar_wait(nrm_empty0 + 8 * buf, nph ^ 1u, spin)) { atomicExch(abort_flag, 1); atomicExch(status, 6); break; }
-      norm_s[buf * TC_BM + r] = (a0 + a1) + (a2 + a3);
+      if (!mbar_wait_abortable(nrm_empty0 + 8 * buf, nph ^ 1u, abort_flag, spin)) { raise_abort(abort_flag, status, 6); break; }
+      norm_s[buf * TC_BM + r] = (acc_a.x + acc_a.y) + (acc_b.x + acc_b.y);
       mbar_arrive(nrm_full0 + 8 * buf);  // release: the store above is visible to whoever observes the phase flip
     }
   } else {
@@ -247,15 +257,15 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     float* row = reinterpret_cast<float*>(smem + plan.scratch_off) + (grp * TC_BM + r) * stride;
     const int64_t nb = (n + 31) / 32;         // statistics: one partial per 32 tokens
     uint32_t t = 0;
-    for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++t) {
+    for (int tile = 0; tile < ntiles; ++tile, ++t) {
       if ((int)(t & 1u) != grp) continue;
       const uint32_t ph = (t >> 1) & 1u;
-      if (aborted(abort_flag)) break;
-      if (!mbar_wait(acc_full0 + 8 * grp, ph, spin)) { atomicExch(abort_flag, 1); atomicExch(status, 4); break; }
-      if (!mbar_wait(nrm_full0 + 8 * grp, ph, spin)) { atomicExch(abort_flag, 1); atomicExch(status, 7); break; }
+      if (!mbar_wait_abortable(acc_full0 + 8 * grp, ph, abort_flag, spin)) { raise_abort(abort_flag, status, 4); break; }
+      if (!mbar_wait_abortable(nrm_full0 + 8 * grp, ph, abort_flag, spin)) { raise_abort(abort_flag, status, 7); break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)grp * buf_cols;
-      const int64_t tok = tile * TC_BM + r;
+      const int64_t tok = cta_row0 + (int64_t)tile * TC_BM + r;
+      const bool mine = tok < cta_end;   // rows past the range belong to the next CTA (or lie beyond n)
       float st_sim = 0.f, st_bs = 0.f;
       if (GT > 0) {
         constexpr int GR = GT > 0 ? GT : 16;
@@ -285,7 +295,7 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         mbar_arrive(acc_empty0 + 8 * grp);   // the MMA warp may overwrite this accumulator buffer
         mbar_arrive(nrm_empty0 + 8 * grp);   // the norm warps may overwrite this norm buffer
-        if (tok < n) {
+        if (mine) {
           float imp;
           router_epilogue_regs<GR>(lg, pd, true, has_proto != 0, nsq, conf_eps ? conf_s : nullptr,
                                    usage_bias ? ub_s : nullptr, proto_temp, proto_threshold, proto_span, proto_blend,
@@ -308,7 +318,7 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         mbar_arrive(acc_empty0 + 8 * grp);
         mbar_arrive(nrm_empty0 + 8 * grp);
-        if (tok < n) {
+        if (mine) {
           float imp;
           router_epilogue(row, 1, G, true, has_proto != 0, nsq, conf_eps ? conf_s : nullptr, usage_bias ? ub_s : nullptr,
                           proto_temp, proto_threshold, proto_span, proto_blend, usage_boost, gate_probs + tok * G, &imp,
@@ -318,8 +328,8 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
       }
       if (stat_partials) {  // fixed order inside the warp: shuffle tree
         const float a = warp_sum(st_sim), b = warp_sum(st_bs), c = warp_sum(st_bs > 0.f ? 1.f : 0.f);
-        const int64_t blk = tile * (TC_BM / 32) + quarter;
-        if (lane == 0 && blk < nb) {
+        const int64_t blk = (cta_row0 + (int64_t)tile * TC_BM) / 32 + quarter;   // ranges and tiles start on multiples of 32
+        if (lane == 0 && blk < nb && blk * 32 < cta_end) {
           stat_partials[blk] = a;
           stat_partials[nb + blk] = b;
           stat_partials[2 * nb + blk] = c;
@@ -436,8 +446,17 @@ static int router_tc_launch(const void* x, int64_t n, int C, const void* w_route
   router_wcat_kernel<<<(unsigned)ceil_div((int64_t)N * C, 256), 256, 0, st>>>((const __nv_bfloat16*)w_router, proto_hat,
                                                                              G, C, N, wcat);
   ASPA_CHECK_LAUNCH();
-  CUtensorMap mx, mw;   // host-side encoding of two descriptors (no driver round trip, no device work)
-  if (!make_map(&mx, x, (uint64_t)n, (uint64_t)C, TC_BM) || !make_map(&mw, wcat, (uint64_t)N, (uint64_t)C, (uint32_t)N)) {
+  TcDeviceInfo* di = tc_device_info();
+  ASPA_CHECK_ARG(di != nullptr, "cannot identify the current device");
+  // Every SM gets the same number of rows (a multiple of 32, at least one tile): 65536 tokens on 148 SMs are 448 rows
+  // each, three tiles and a half, instead of four tiles on some SMs and three on the others.
+  const int64_t share = ceil_div(ceil_div(n, (int64_t)di->sms), 32) * 32;
+  const int rows_per_cta = (int)std::max<int64_t>(share, TC_BM);
+  const unsigned grid = (unsigned)ceil_div(n, (int64_t)rows_per_cta);
+  const int tail_rows = rows_per_cta - (int)(ceil_div((int64_t)rows_per_cta, TC_BM) - 1) * TC_BM;
+  CUtensorMap mx, mxt, mw;   // host-side encoding of the descriptors (no driver round trip, no device work)
+  if (!make_map(&mx, x, (uint64_t)n, (uint64_t)C, TC_BM) || !make_map(&mxt, x, (uint64_t)n, (uint64_t)C, (uint32_t)tail_rows) ||
+      !make_map(&mw, wcat, (uint64_t)N, (uint64_t)C, (uint32_t)N)) {
     set_error("aspa_router_fwd_tc: cuTensorMapEncodeTiled failed");
     return ASPA_ERR_CUDA;
   }
@@ -446,19 +465,15 @@ static int router_tc_launch(const void* x, int64_t n, int C, const void* w_route
     set_error("aspa_router_fwd_tc: shared memory holds fewer than two ring stages for this shape");
     return ASPA_ERR_UNSUPPORTED;
   }
-  TcDeviceInfo* di = tc_device_info();
-  ASPA_CHECK_ARG(di != nullptr, "cannot identify the current device");
-  const int64_t ntiles = ceil_div(n, TC_BM);
-  const unsigned grid = (unsigned)std::min<int64_t>(ntiles, di->sms);
   auto launch = [&](auto kernel, int variant) {
     if (!di->attr[variant]) {
       cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_LIMIT + 2048);
       di->attr[variant] = true;
     }
-    kernel<<<grid, TC_THREADS, plan.total, st>>>(mx, mw, (const __nv_bfloat16*)x, n, C, G, N, has_proto ? 1 : 0, conf_eps, usage_bias, proto_temp,
-                                                 proto_threshold, proto_span, proto_blend, usage_boost, gate_probs,
-                                                 importance, proto_sim, blend, stat_partials, status, plan, spin,
-                                                 withhold_tile);
+    kernel<<<grid, TC_THREADS, plan.total, st>>>(mx, mxt, mw, (const __nv_bfloat16*)x, n, rows_per_cta, C, G, N, has_proto ? 1 : 0,
+                                                 conf_eps, usage_bias, proto_temp, proto_threshold, proto_span, proto_blend,
+                                                 usage_boost, gate_probs, importance, proto_sim, blend, stat_partials, status,
+                                                 plan, spin, withhold_tile);
   };
   if (tc_reg_epilogue(N, G, has_proto) && G == 16) launch(router_tc_kernel<16>, 0);
   else if (tc_reg_epilogue(N, G, has_proto)) launch(router_tc_kernel<32>, 1);

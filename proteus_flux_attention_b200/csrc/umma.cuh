@@ -35,6 +35,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_
   }
   return false;
 }
+// One try_wait (the hardware may suspend the thread for a bounded time inside it).
+__device__ __forceinline__ bool mbar_test_wait_once(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
 // One poll of a barrier phase.
 __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
   uint32_t ok;
@@ -82,6 +92,32 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
 }
 
 __device__ __forceinline__ bool aborted(const int* flag) { return *reinterpret_cast<const volatile int*>(flag) != 0; }
+
+// Bounded wait that also ends (false) once the CTA's abort flag is up.  The flag is looked at every 32 failed polls,
+// so a wait that succeeds at once costs one try_wait and nothing else: the issuing loops of the tensor-core kernels are
+// single threads whose every instruction is exposed latency.
+__device__ __forceinline__ bool mbar_wait_abortable(uint32_t bar, uint32_t parity, const int* abort_flag, uint32_t limit) {
+  for (uint32_t it = 0; it < limit; ++it) {
+    if (mbar_test_wait_once(bar, parity)) return true;
+    if ((it & 31u) == 31u && aborted(abort_flag)) return false;
+  }
+  return false;
+}
+// First failure wins: the status word names the wait that ran out, the abort flag makes every other role leave.
+static __device__ __noinline__ void raise_abort(int* abort_flag, int* status, int code) {
+  if (aborted(abort_flag)) return;
+  atomicCAS(status, 0, code);
+  __threadfence();
+  atomicExch(abort_flag, 1);
+}
+// Position in a ring of S stages: stage index and the parity of the pass over the ring.
+struct RingPos {
+  int s;
+  uint32_t ph;
+  __device__ __forceinline__ void next(int S) {
+    if (++s == S) { s = 0; ph ^= 1u; }
+  }
+};
 
 
 // 32 consecutive fp32 columns of this thread's tensor-memory lane.
