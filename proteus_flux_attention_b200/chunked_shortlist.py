@@ -144,6 +144,8 @@ class ChunkedShortlistConfig:
     collect_summaries: bool = True       # build the python-side summaries after the run: per-chunk lists and final_stats
                                          # (False: the final layer's telemetry stays readable on the layer object)
     use_cuda_graph: bool = False         # replay pass 1's per-chunk layer call from a captured CUDA graph
+    whole_run_graph: bool = False        # with use_cuda_graph, a device-resident sequence and a caching runner: the whole
+                                         # run (both passes, the exchange between ranks, the read-backs) is ONE graph
 
     def validate(self) -> None:
         if self.seq_len <= 0:
@@ -307,6 +309,15 @@ class ChunkedShortlistRunner:
         self.logger = logger or LOGGER
         self.group = process_group
         self._layer_cache: Optional[Dict[Tuple, AdaptiveSparseAttention]] = {} if cache_layers else None
+
+    def close(self) -> None:
+        """Drop the cached layers and captured graphs.  A sharded runner with ``whole_run_graph`` must be closed before
+        its process group is destroyed: a captured graph that holds collectives keeps the communicator busy, and the
+        communicator's teardown waits for it."""
+        if self._layer_cache is not None:
+            self._layer_cache.clear()
+        self.__dict__.pop("_graph_tmp", None)
+        torch.cuda.synchronize(torch.device(self.config.device))
 
     def _make_layer(self, seq_len: int, ratio: float, dtype: torch.dtype, state: Optional[Dict[str, torch.Tensor]],
                     frozen: bool) -> AdaptiveSparseAttention:
@@ -534,6 +545,29 @@ class ChunkedShortlistRunner:
         cap = dist_utils.max_chunks_per_rank(n_chunks, world)   # slots per rank: the same on every rank (fixed-size exchange)
         records = self._records(max(cap, 1))
         rec_scores, rec_idx, rec_count = records.scores, records.idx, records.count
+        bounds = [(c * cfg.chunk_len, min(cfg.seq_len, (c + 1) * cfg.chunk_len)) for c in range(c_lo, c_hi)]
+        if (cfg.whole_run_graph and cfg.use_cuda_graph and cfg.freeze_prototypes and self._layer_cache is not None
+                and source.is_cuda and source.is_contiguous() and not cfg.collect_summaries and not cfg.report_latency
+                and n_local >= 1 and all(e - s == cfg.chunk_len for s, e in bounds)
+                and n_chunks * budget <= ops.MERGE_POS_MAX and not ops.SERIAL_STREAMS):
+            t0 = time.perf_counter()
+            wr = self._whole_run(source=source, source_off=source_off, bounds=bounds, c_lo=c_lo, c_hi=c_hi,
+                                 chunk_model=chunk_model, final_state=final_state, base_dtype=base_dtype, records=records,
+                                 n_chunks=n_chunks, world=world, rank=rank, device=device)
+            if wr is not None:
+                total_s = time.perf_counter() - t0
+                self.last_phase_ms = {"whole_run_graph": round(wr["device_ms"], 3), "host_wall": round(total_s * 1e3, 3)}
+                metrics = ChunkedShortlistMetrics(
+                    original_tokens=cfg.seq_len, retained_tokens=wr["k"], retention_ratio=float(wr["k"] / max(cfg.seq_len, 1)),
+                    chunk_count=n_chunks, device=str(device), chunk_time_ms=None, final_time_ms=None,
+                    total_time_ms=float(total_s * 1e3), peak_memory_mb=None, used_fallback=False, chunk_tokens_per_s=None,
+                    final_tokens_per_s=None, total_tokens_per_s=float(cfg.seq_len / total_s) if total_s > 0 else None,
+                    storage_mode=storage_mode, host_required_mb=host_bytes / BYTES_PER_MB, host_allocated_mb=None,
+                    host_limit_mb=None, storage_reason=None, world_size=world)
+                return ChunkedShortlistResult(keep_indices=wr["keep_idx_host"], keep_scores=wr["keep_sc_host"],
+                                              reduced_sequence=wr["reduced"], metrics=metrics, chunks=[],
+                                              final_output=wr["final_output"], final_stats=None,
+                                              backend_info=wr["backend_info"])
         # Host-resident input: the rows of every promoted token are set aside while their chunk is on the device,
         # so that the reduced sequence is assembled from device memory instead of a second trip to the host.
         # Sharded runs do the same whatever the source: each rank then contributes exactly the rows it promoted.
@@ -546,7 +580,6 @@ class ChunkedShortlistRunner:
         ev_c = torch.cuda.Event(enable_timing=True)
         t0 = time.perf_counter()
         ev_a.record()
-        bounds = [(c * cfg.chunk_len, min(cfg.seq_len, (c + 1) * cfg.chunk_len)) for c in range(c_lo, c_hi)]
         graph = None
         if cfg.use_cuda_graph:
             resident = None
@@ -707,6 +740,109 @@ class ChunkedShortlistRunner:
         return ChunkedShortlistResult(keep_indices=keep_idx_host, keep_scores=keep_sc_host,
                                       reduced_sequence=reduced, metrics=metrics, chunks=summaries,
                                       final_output=final_output, final_stats=final_stats, backend_info=backend_info)
+
+    def _whole_run(self, *, source: torch.Tensor, source_off: int, bounds, c_lo: int, c_hi: int,
+                   chunk_model: AdaptiveSparseAttention, final_state, base_dtype: torch.dtype, records: _Pass1Records,
+                   n_chunks: int, world: int, rank: int, device: torch.device):
+        """The whole run as ONE captured CUDA graph, replayed: record reset, pass 1 of this rank's chunks on two lanes,
+        both exchanges (NCCL collectives are captured like kernels), merge, row gather, pass 2 and the copies of
+        everything the host reads into pinned memory.  Per run the host then launches one graph and waits once, where
+        the chunk-by-chunk path enqueues a few dozen operations - about 0.4 ms of host time, which at eight ranks (two
+        chunks each) is a fifth of the step.  Valid for one sequence address, one rank layout and frozen prototypes; the
+        kept count is assumed to be ``min(buffer_tokens, chunks * budget)`` (true whenever the chunks promote that
+        many tokens) and checked after the replay: on a mismatch ``None`` is returned and the caller runs the
+        chunk-by-chunk path.  Output tensors live in the graph's memory and are cloned for the caller."""
+        cfg = self.config
+        budget = cfg.per_chunk_budget
+        k_guess = min(cfg.buffer_tokens, n_chunks * budget)
+        cache = self._layer_cache
+        key = ("run_graph", int(source.data_ptr()), tuple(source.shape), base_dtype, world, rank, c_lo, c_hi, id(records))
+        entry = cache.get(key)
+        if entry is None:
+            use_pool = world > 1
+            pool = torch.empty((max(records.n_slots, 1) * budget, cfg.d_model), dtype=base_dtype, device=device) if use_pool else None
+            final_model = self._make_layer(k_guess, cfg.final_sparse_ratio, base_dtype, final_state, cfg.freeze_prototypes) \
+                if cfg.run_final_pass else None
+            lanes = [torch.cuda.Stream(device=device, priority=-2) for _ in range(PASS1_LANES)]
+            pins = {"count": torch.zeros(1, dtype=torch.int32, pin_memory=True),
+                    "status": torch.zeros(1, dtype=torch.int32, pin_memory=True),
+                    "idx": torch.empty(k_guess, dtype=torch.int64, pin_memory=True),
+                    "sc": torch.empty(k_guess, dtype=torch.float32, pin_memory=True)}
+
+            def enqueue():
+                main = torch.cuda.current_stream()
+                records.reset(c_lo, cfg.chunk_len)
+                for lane in lanes:
+                    lane.wait_stream(main)
+                for i, (start, end) in enumerate(bounds):
+                    k = i % len(lanes)
+                    records.use_lane(k)
+                    with torch.cuda.stream(lanes[k]):
+                        xc = source[:, start - source_off:end - source_off]
+                        records.slot.fill_(i)
+                        self._chunk_step(chunk_model, xc, records)
+                        if pool is not None:
+                            ops.gather_rows(xc[0], (records.idx[i] - start).clamp_(min=0), records.count[i:i + 1], budget,
+                                            out=pool[i * budget:(i + 1) * budget])
+                records.use_lane(0)
+                for lane in lanes:
+                    main.wait_stream(lane)
+                all_scores, all_idx, _ = dist_utils.all_gather_packed_records(self.group, records.packed, n_chunks, world)
+                all_pool = dist_utils.all_gather_pool(self.group, pool, world) if pool is not None else None
+                if pool is not None:
+                    keep_idx, keep_sc, keep_count, keep_pos = ops.merge_finalise(all_scores.view(-1), all_idx.view(-1), cfg.seq_len,
+                                                                                 cfg.buffer_tokens, want_pos=True)
+                    red = self._gather_pooled(all_pool, keep_pos[:k_guess], k_guess, budget, world, n_chunks)
+                else:
+                    keep_idx, keep_sc, keep_count = ops.merge_finalise(all_scores.view(-1), all_idx.view(-1), cfg.seq_len,
+                                                                       cfg.buffer_tokens)
+                    red = self._gather_reduced(source, source_off, keep_idx[:k_guess], k_guess, device, world, rank, c_lo, c_hi)
+                out = final_model(red).detach() if final_model is not None else None
+                pins["count"].copy_(keep_count, non_blocking=True)
+                pins["status"].copy_(ops.router_status(device), non_blocking=True)
+                pins["idx"].copy_(keep_idx[:k_guess], non_blocking=True)
+                pins["sc"].copy_(keep_sc[:k_guess], non_blocking=True)
+                return keep_idx[:k_guess], keep_sc[:k_guess], red, out
+
+            side = torch.cuda.Stream(device=device, priority=-2)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):   # eager warm-up on the capture stream: communicators, workspaces, caches
+                for _ in range(2):
+                    enqueue()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize(device)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side, capture_error_mode="thread_local"):
+                outs = enqueue()
+            ctx = [(m, m.__dict__.get("_pending")) for m in (chunk_model, final_model) if m is not None]
+            info = get_last_backend_info() if final_model is not None else None
+            if world > 1 and not self.__dict__.get("_close_at_exit"):
+                import atexit
+                import weakref
+                ref = weakref.ref(self)
+                atexit.register(lambda: ref() is not None and ref().close())   # best effort for callers that never close
+                self.__dict__["_close_at_exit"] = True
+            entry = cache[key] = {"graph": g, "outs": outs, "pins": pins, "final_model": final_model, "ctx": ctx, "info": info,
+                                  "ev": (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))}
+        ev0, ev1 = entry["ev"]
+        ev0.record()
+        entry["graph"].replay()
+        ev1.record()
+        torch.cuda.synchronize(device)
+        for m, pending in entry["ctx"]:   # the replay refreshed the pinned telemetry records: decode on next access
+            if pending is not None:
+                m.__dict__["_pending"] = dict(pending)
+                m.__dict__["_head_stats_value"] = None
+                m.__dict__["_sparse_state_value"] = None
+        pins = entry["pins"]
+        if int(pins["status"].item()) != 0:
+            ops.check_router_status(device)
+        if int(pins["count"].item()) != k_guess:
+            return None
+        keep_idx, keep_sc, red, out = entry["outs"]
+        return {"k": k_guess, "keep_idx_host": pins["idx"].clone(), "keep_sc_host": pins["sc"].clone(), "reduced": red.clone(),
+                "final_output": out.clone() if out is not None else None, "backend_info": entry["info"],
+                "final_model": entry["final_model"], "device_ms": float(ev0.elapsed_time(ev1))}
 
     def _gather_pooled(self, pool: torch.Tensor, keep_pos: torch.Tensor, k: int, budget: int, world: int,
                        n_chunks: int) -> torch.Tensor:

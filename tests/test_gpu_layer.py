@@ -410,6 +410,48 @@ def test_chunked_pipeline_graph_replay_equals_eager(dev):
         P.ChunkedShortlistConfig(**{**base, "freeze_prototypes": False}, use_cuda_graph=True).validate()
 
 
+def test_chunked_pipeline_whole_run_graph_equals_eager(dev):
+    """The whole run replayed from ONE captured graph (reset, pass 1 on two lanes, merge, gather, pass 2, read-backs)
+    gives what the eager pipeline gives, replay after replay; a sequence at another address is captured afresh, a
+    buffer the promotions cannot fill falls back to the chunk-by-chunk path, and so does a ragged last chunk."""
+    import proteus_flux_attention_b200 as P
+    from proteus_flux_attention_b200.chunked_shortlist import _build_model_config
+    torch.manual_seed(12)
+    mk = lambda n, r: P.AdaptiveSparseAttention(_build_model_config(n, 256, heads=4, sparse_ratio=r, shortlist_alpha=1.0,  # noqa: E731
+                                                                   router_top_p=0.9))
+    cast = lambda sd: {k: v.to(torch.bfloat16) if v.dtype == torch.float32 and "routing" not in k else v for k, v in sd.items()}  # noqa: E731
+    cs, fs = cast(mk(2048, 0.05).state_dict()), cast(mk(512, 0.5).state_dict())
+    seq = torch.randn(1, 6 * 2048, 256, generator=torch.Generator().manual_seed(5)).to(torch.bfloat16)
+    base = dict(seq_len=seq.size(1), d_model=256, chunk_len=2048, buffer_tokens=512, per_chunk_budget=128, device=dev, heads=4,
+                freeze_prototypes=True, warmup=False)
+    want = P.ChunkedShortlistRunner(P.ChunkedShortlistConfig(**base)).run(seq.to(dev), chunk_state=cs, final_state=fs)
+    cfg = P.ChunkedShortlistConfig(**base, use_cuda_graph=True, whole_run_graph=True, collect_summaries=False)
+    runner = P.ChunkedShortlistRunner(cfg, cache_layers=True)
+    a, b = seq.to(dev), seq.to(dev).clone()
+    for source in (a, a, b, a):
+        got = runner.run(source, chunk_state=cs, final_state=fs)
+        assert "whole_run_graph" in runner.last_phase_ms
+        assert torch.equal(got.keep_indices, want.keep_indices)
+        assert torch.equal(got.keep_scores, want.keep_scores)
+        assert torch.equal(got.reduced_sequence.cpu(), want.reduced_sequence.cpu())
+        assert torch.equal(got.final_output.cpu(), want.final_output.cpu())
+    # a host sequence, a ragged last chunk and an unfillable buffer take the chunk-by-chunk path and still agree
+    got = runner.run(seq.pin_memory(), chunk_state=cs, final_state=fs)
+    assert "whole_run_graph" not in runner.last_phase_ms and torch.equal(got.keep_indices, want.keep_indices)
+    wide = dict(base, buffer_tokens=1024)
+    ragged = {**wide, "seq_len": seq.size(1) - 100}
+    want = P.ChunkedShortlistRunner(P.ChunkedShortlistConfig(**ragged)).run(seq[:, :-100].to(dev), chunk_state=cs, final_state=fs)
+    cfgw = P.ChunkedShortlistConfig(**ragged, use_cuda_graph=True, whole_run_graph=True, collect_summaries=False)
+    got = P.ChunkedShortlistRunner(cfgw, cache_layers=True).run(seq[:, :-100].to(dev), chunk_state=cs, final_state=fs)
+    assert torch.equal(got.keep_indices, want.keep_indices) and torch.equal(got.final_output.cpu(), want.final_output.cpu())
+    want = P.ChunkedShortlistRunner(P.ChunkedShortlistConfig(**wide)).run(seq.to(dev), chunk_state=cs, final_state=fs)
+    runner = P.ChunkedShortlistRunner(P.ChunkedShortlistConfig(**wide, use_cuda_graph=True, whole_run_graph=True,
+                                                               collect_summaries=False), cache_layers=True)
+    for _ in range(2):
+        got = runner.run(a, chunk_state=cs, final_state=fs)
+        assert torch.equal(got.keep_indices, want.keep_indices) and torch.equal(got.final_output.cpu(), want.final_output.cpu())
+
+
 def test_captured_layer_call_equals_eager(dev):
     """A layer call replayed from a captured graph gives what the eager call gives, state updates included (the
     prototype EMA moves with every replay); a call that must wait for the host refuses to be captured."""

@@ -54,6 +54,17 @@ def _worker(rank, world, port, q):
                 src, chunk_state=cs, final_state=fs, sequence_is_local_shard=True)
             q.put((rank, where, res.keep_indices.clone(), res.final_output.float().cpu(),
                    res.reduced_sequence.float().cpu()))
+        # the whole sharded run (both collectives included) replayed from one captured graph, twice
+        import dataclasses
+        gcfg = dataclasses.replace(_cfg(dev), use_cuda_graph=True, whole_run_graph=True, collect_summaries=False)
+        runner = P.ChunkedShortlistRunner(gcfg, process_group=dist.group.WORLD, cache_layers=True)
+        src = shard.to(dev)
+        for _ in range(2):
+            res = runner.run(src, chunk_state=cs, final_state=fs, sequence_is_local_shard=True)
+            assert "whole_run_graph" in runner.last_phase_ms
+        q.put((rank, "graph", res.keep_indices.clone(), res.final_output.float().cpu(), res.reduced_sequence.float().cpu()))
+        del res
+        runner.close()   # graphs that hold collectives go before the process group does
     except BaseException:   # the parent fails fast on this and tears the peer down
         q.put(("error", rank, traceback.format_exc()))
         raise
@@ -83,7 +94,7 @@ def test_two_gpu_sharding_equals_single_gpu():
         # a worker that dies leaves its peer blocked in a collective: collect with a deadline, fail on the first
         # reported error or dead child, and never leave a child behind
         deadline = time.monotonic() + 300
-        while len(results) < 2 * len(procs):
+        while len(results) < 3 * len(procs):
             assert time.monotonic() < deadline, "workers did not report within 300 s"
             try:
                 item = q.get(timeout=5)
@@ -105,7 +116,7 @@ def test_two_gpu_sharding_equals_single_gpu():
             if p.is_alive():
                 p.kill()
                 p.join(timeout=10)
-    assert sorted((r[0], r[1]) for r in results) == [(0, "hbm"), (0, "host"), (1, "hbm"), (1, "host")]
+    assert sorted((r[0], r[1]) for r in results) == [(0, "graph"), (0, "hbm"), (0, "host"), (1, "graph"), (1, "hbm"), (1, "host")]
     for rank, where, keep, out, red in results:
         assert torch.equal(keep, want.keep_indices)
         assert torch.equal(red, want.reduced_sequence.float().cpu())
