@@ -788,10 +788,11 @@ class ChunkedShortlistRunner:
                 for lane in lanes:
                     main.wait_stream(lane)
                 all_scores, all_idx, _ = dist_utils.all_gather_packed_records(self.group, records.packed, n_chunks, world)
-                all_pool = dist_utils.all_gather_pool(self.group, pool, world) if pool is not None else None
                 if pool is not None:
+                    all_pool, rows_arrived = dist_utils.all_gather_pool(self.group, pool, world, deferred=True)
                     keep_idx, keep_sc, keep_count, keep_pos = ops.merge_finalise(all_scores.view(-1), all_idx.view(-1), cfg.seq_len,
                                                                                  cfg.buffer_tokens, want_pos=True)
+                    rows_arrived()   # the merge ran beside the row exchange
                     red = self._gather_pooled(all_pool, keep_pos[:k_guess], k_guess, budget, world, n_chunks)
                 else:
                     keep_idx, keep_sc, keep_count = ops.merge_finalise(all_scores.view(-1), all_idx.view(-1), cfg.seq_len,

@@ -35,6 +35,7 @@ __device__ __forceinline__ float rope_mix(float a, float c, float rot, float s, 
 // advances in the loop.  bf16 uses packed bf16x2 multiply/add (each rounds to nearest even, like the reference's
 // eager bf16 ops); fp32 keeps separate fp32 multiplies and adds.
 constexpr int ROPE_TPB = 32;
+constexpr int ROPE_MAX_HALF = 64;   // head_dim up to 128 takes the packed (cos, sin) table in shared memory
 
 // rintf(v / scale), the quantiser's rounding, without a division per element: for |v / scale| < 256 the product with
 // the rounded reciprocal is within 2^-15 of the correctly rounded quotient, so both round to the same integer unless
@@ -60,6 +61,69 @@ __device__ __forceinline__ uint32_t rope_word_bf16(uint32_t x, float c, float s)
 // MODE 0: write the rotated / relaid-out values (and optionally their per-head amax); MODE 1: amax only, nothing
 // written; MODE 2: write symmetric per-head INT8 of the rotated values using the amax of an earlier MODE 1 pass
 // (bf16 only: q8/k8/v8 are passed through the q, k, v pointers).
+// The same rotation with the factors of a channel pair ready in two words, (cos, cos) and (-sin, sin) as bf16 pairs:
+// out = x * (c, c) + (odd, even) * (-s, s); (-s) * odd rounds to the same bf16 as -(odd * s).
+__device__ __forceinline__ uint32_t rope_word_bf16_packed(uint32_t x, uint32_t cc, uint32_t ss) {
+  const uint32_t swapped = __byte_perm(x, 0, 0x1032);
+  const __nv_bfloat162 xv = *reinterpret_cast<const __nv_bfloat162*>(&x);
+  const __nv_bfloat162 rv = *reinterpret_cast<const __nv_bfloat162*>(&swapped);
+  const __nv_bfloat162 cv = *reinterpret_cast<const __nv_bfloat162*>(&cc), sv = *reinterpret_cast<const __nv_bfloat162*>(&ss);
+  const __nv_bfloat162 o = __hadd2_rn(__hmul2_rn(xv, cv), __hmul2_rn(rv, sv));
+  return *reinterpret_cast<const uint32_t*>(&o);
+}
+
+// max(a, |b|, |c|) that keeps a NaN
+__device__ __forceinline__ float max3_abs_nan(float a, float b, float c) {
+  float d;
+  asm("{\n\t.reg .f32 t, u;\n\tabs.f32 t, %2;\n\tabs.f32 u, %3;\n\tmax.NaN.f32 %0, %1, t, u;\n\t}" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+// The quantiser's bytes for one 16-byte vector of bf16, on the FMA pipe only: adding 1.5 * 2^23 rounds to the nearest
+// integer (ties to even, as rintf does) and leaves that integer in the low mantissa bits, whose low byte is the
+// two's-complement int8.  Where the product with the reciprocal lies close to a tie (see quant_round) the exact
+// quotient decides: that path is a call, so that its division and rounding instructions stay out of the common path
+// (inlined and predicated they kept the conversion pipe 86 % busy).
+constexpr float QUANT_MAGIC = 12582912.f;
+
+__device__ __noinline__ uint2 quant_vector_exact(uint4 raw, float scale) {
+  const uint32_t* w = reinterpret_cast<const uint32_t*>(&raw);
+  uint32_t out[2] = {0u, 0u};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float v = __uint_as_float((i & 1) ? (w[i >> 1] & 0xffff0000u) : (w[i >> 1] << 16));
+    const float r = fminf(fmaxf(rintf(__fdiv_rn(v, scale)), -127.f), 127.f);
+    out[i >> 2] |= (__float_as_uint(__fadd_rn(r, QUANT_MAGIC)) & 0xffu) << (8 * (i & 3));
+  }
+  return make_uint2(out[0], out[1]);
+}
+
+__device__ __forceinline__ uint2 quant_vector(uint4 raw, float scale, float inv) {
+  // Two values per packed fp32 instruction: y = v * inv + MAGIC in one rounding (the integer nearest to the exact
+  // product), -r = MAGIC - y, d = v * inv - r.  A product within 0.001 of a tie, or an integer outside [-127, 127]
+  // (only the percentile bases produce those; the exact path clamps them), sends the vector to the exact path.
+  const uint32_t* w = reinterpret_cast<const uint32_t*>(&raw);
+  const float2 inv2 = make_float2(inv, inv), magic2 = make_float2(QUANT_MAGIC, QUANT_MAGIC), minus2 = make_float2(-1.f, -1.f);
+  uint32_t yb[8];
+  float dmax = 0.f, rmax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 v2 = make_float2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xffff0000u));
+    const float2 y2 = __ffma2_rn(v2, inv2, magic2);
+    const float2 nr2 = __ffma2_rn(y2, minus2, magic2);
+    const float2 d2 = __ffma2_rn(v2, inv2, nr2);
+    dmax = max3_abs_nan(dmax, d2.x, d2.y);
+    rmax = max3_abs_nan(rmax, nr2.x, nr2.y);
+    yb[2 * i] = __float_as_uint(y2.x);
+    yb[2 * i + 1] = __float_as_uint(y2.y);
+  }
+  if (!(dmax <= 0.499f) || !(rmax <= 127.f)) return quant_vector_exact(raw, scale);
+  // the low byte of each y is the two's-complement int8
+  const uint32_t lo = __byte_perm(__byte_perm(yb[0], yb[1], 0x0040), __byte_perm(yb[2], yb[3], 0x0040), 0x5410);
+  const uint32_t hi = __byte_perm(__byte_perm(yb[4], yb[5], 0x0040), __byte_perm(yb[6], yb[7], 0x0040), 0x5410);
+  return make_uint2(lo, hi);
+}
+
 template <typename T, int MODE>
 __global__ void __launch_bounds__(512) rope_relayout_kernel(const T* __restrict__ qkv, int B, int Tn, int H, int D,
                                                             const float* __restrict__ cos_t,
@@ -75,6 +139,18 @@ __global__ void __launch_bounds__(512) rope_relayout_kernel(const T* __restrict_
   const int t0 = blockIdx.x * ROPE_TPB;
   const int t1 = min(Tn, t0 + ROPE_TPB);
   const int half = D / 2;
+  // bf16: (cos, sin) of this CTA's tokens once, packed two bf16 to a word, instead of two conversions per word of data
+  __shared__ __align__(16) uint32_t cs_s[sizeof(T) == 2 ? 2 * ROPE_TPB * ROPE_MAX_HALF : 1];   // (c, c) words, then (-s, s) words
+  const bool packed = sizeof(T) == 2 && cos_t != nullptr && half <= ROPE_MAX_HALF && half % 4 == 0;
+  if (packed) {
+    for (int i = threadIdx.x; i < (t1 - t0) * half; i += blockDim.x) {
+      const float c = cos_t[(int64_t)t0 * half + i], sn = sin_t[(int64_t)t0 * half + i];
+      const __nv_bfloat162 wc = __floats2bfloat162_rn(c, c), ws = __floats2bfloat162_rn(-sn, sn);
+      cs_s[i] = *reinterpret_cast<const uint32_t*>(&wc);
+      cs_s[ROPE_TPB * ROPE_MAX_HALF + i] = *reinterpret_cast<const uint32_t*>(&ws);
+    }
+    __syncthreads();
+  }
   for (int vi = threadIdx.x; vi < vec_per_tok; vi += blockDim.x) {
     const int ch = vi * E;
     const int sec = sec0 + ch / C;
@@ -87,6 +163,7 @@ __global__ void __launch_bounds__(512) rope_relayout_kernel(const T* __restrict_
     const float* cr = cos_t ? cos_t + (int64_t)t0 * half + d0 / 2 : nullptr;
     const float* sr = sin_t ? sin_t + (int64_t)t0 * half + d0 / 2 : nullptr;
     float local_max = 0.f;
+    __nv_bfloat162 local_max2 = __floats2bfloat162_rn(0.f, 0.f);
     float qscale = 1.f, qinv = 1.f;
     int8_t* dst8 = nullptr;
     if (MODE == 2) {
@@ -95,59 +172,69 @@ __global__ void __launch_bounds__(512) rope_relayout_kernel(const T* __restrict_
       dst8 = reinterpret_cast<int8_t*>(sec == 0 ? q : (sec == 1 ? k : v)) + ((int64_t)bh * Tn + t0) * D + d0;
     }
     const uint8_t* keep = (sec == 0 && q_keep != nullptr) ? q_keep + (int64_t)b * Tn : nullptr;
-#pragma unroll 8
-    for (int t = t0; t < t1; ++t) {
-      if (keep != nullptr && !keep[t]) {  // queries of dropped tokens are never read: neither load nor store them
-        src += nsec * (int64_t)C;
-        dst += D;
-        if (MODE == 2) dst8 += D;
-        if (cr) { cr += half; sr += half; }
-        continue;
-      }
-      uint4 raw = *reinterpret_cast<const uint4*>(src);
-      if (sizeof(T) == 2) {
-        if (rotate) {
-          const float4 c4 = *reinterpret_cast<const float4*>(cr), s4 = *reinterpret_cast<const float4*>(sr);
-          raw.x = rope_word_bf16(raw.x, c4.x, s4.x);
-          raw.y = rope_word_bf16(raw.y, c4.y, s4.y);
-          raw.z = rope_word_bf16(raw.z, c4.z, s4.z);
-          raw.w = rope_word_bf16(raw.w, c4.w, s4.w);
-        }
-        if (MODE != 2 && amax) {
-          const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    // Tokens in batches of eight: all loads of a batch are issued before the first of them is used, so that eight
+    // 16-byte loads per thread are in flight (the plain loop left the stream latency-bound at 2.6 TB/s).
+    constexpr int RB = MODE == 2 ? 4 : 8;
+    const int64_t src_step = nsec * (int64_t)C;
+    for (int tb = t0; tb < t1; tb += RB) {
+      uint4 buf[RB];
+      bool on[RB];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float2 f = __bfloat1622float2(h2[i]);
-            local_max = fmaxf(local_max, fmaxf(fabsf(f.x), fabsf(f.y)));
-          }
-        }
-        if (MODE == 2) {
-          const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&raw);
-          union { int8_t b8[8]; uint2 u; } pk;
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const float r = quant_round(__bfloat162float(e[i]), qscale, qinv);
-            pk.b8[i] = (int8_t)fminf(fmaxf(r, -127.f), 127.f);
-          }
-          *reinterpret_cast<uint2*>(dst8) = pk.u;
-          dst8 += D;
-        }
-      } else {
-        float* f = reinterpret_cast<float*>(&raw);
-        if (rotate) {
-          const float2 c2 = *reinterpret_cast<const float2*>(cr), s2 = *reinterpret_cast<const float2*>(sr);
-          const float e0 = f[0], o0 = f[1], e1 = f[2], o1 = f[3];
-          f[0] = rope_mix(e0, c2.x, -o0, s2.x, false);
-          f[1] = rope_mix(o0, c2.x, e0, s2.x, false);
-          f[2] = rope_mix(e1, c2.y, -o1, s2.y, false);
-          f[3] = rope_mix(o1, c2.y, e1, s2.y, false);
-        }
-        if (amax) local_max = fmaxf(fmaxf(fabsf(f[0]), fabsf(f[1])), fmaxf(local_max, fmaxf(fabsf(f[2]), fabsf(f[3]))));
+      for (int u = 0; u < RB; ++u) {
+        const int t = tb + u;
+        // queries of dropped tokens are never read: neither load nor store them
+        on[u] = t < t1 && (keep == nullptr || keep[t] != 0);
+        if (on[u]) buf[u] = *reinterpret_cast<const uint4*>(src + u * src_step);
       }
-      if (MODE == 0) *reinterpret_cast<uint4*>(dst) = raw;
-      src += nsec * (int64_t)C;
-      dst += D;
-      if (cr) { cr += half; sr += half; }
+#pragma unroll
+      for (int u = 0; u < RB; ++u) {
+        if (!on[u]) continue;
+        const int t = tb + u;
+        uint4 raw = buf[u];
+        if (sizeof(T) == 2) {
+          if (rotate) {
+            if (packed) {
+              const uint4 wc = *reinterpret_cast<const uint4*>(cs_s + (t - t0) * half + d0 / 2);
+              const uint4 ws = *reinterpret_cast<const uint4*>(cs_s + ROPE_TPB * ROPE_MAX_HALF + (t - t0) * half + d0 / 2);
+              raw.x = rope_word_bf16_packed(raw.x, wc.x, ws.x);
+              raw.y = rope_word_bf16_packed(raw.y, wc.y, ws.y);
+              raw.z = rope_word_bf16_packed(raw.z, wc.z, ws.z);
+              raw.w = rope_word_bf16_packed(raw.w, wc.w, ws.w);
+            } else {
+              const float4 c4 = *reinterpret_cast<const float4*>(cr + u * half), s4 = *reinterpret_cast<const float4*>(sr + u * half);
+              raw.x = rope_word_bf16(raw.x, c4.x, s4.x);
+              raw.y = rope_word_bf16(raw.y, c4.y, s4.y);
+              raw.z = rope_word_bf16(raw.z, c4.z, s4.z);
+              raw.w = rope_word_bf16(raw.w, c4.w, s4.w);
+            }
+          }
+          if (MODE != 2 && amax) {   // |x| and max on packed bf16 pairs: exact, no conversions
+            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+            local_max2 = __hmax2(__hmax2(local_max2, __habs2(h2[0])), __hmax2(__habs2(h2[1]), __hmax2(__habs2(h2[2]), __habs2(h2[3]))));
+          }
+          if (MODE == 2) *reinterpret_cast<uint2*>(dst8 + u * D) = quant_vector(raw, qscale, qinv);
+        } else {
+          float* f = reinterpret_cast<float*>(&raw);
+          if (rotate) {
+            const float2 c2 = *reinterpret_cast<const float2*>(cr + u * half), s2 = *reinterpret_cast<const float2*>(sr + u * half);
+            const float e0 = f[0], o0 = f[1], e1 = f[2], o1 = f[3];
+            f[0] = rope_mix(e0, c2.x, -o0, s2.x, false);
+            f[1] = rope_mix(o0, c2.x, e0, s2.x, false);
+            f[2] = rope_mix(e1, c2.y, -o1, s2.y, false);
+            f[3] = rope_mix(o1, c2.y, e1, s2.y, false);
+          }
+          if (amax) local_max = fmaxf(fmaxf(fabsf(f[0]), fabsf(f[1])), fmaxf(local_max, fmaxf(fabsf(f[2]), fabsf(f[3]))));
+        }
+        if (MODE == 0) *reinterpret_cast<uint4*>(dst + u * D) = raw;
+      }
+      src += RB * src_step;
+      dst += RB * D;
+      if (MODE == 2) dst8 += RB * D;
+      if (cr) { cr += RB * half; sr += RB * half; }
+    }
+    if (sizeof(T) == 2) {
+      const float2 m2 = __bfloat1622float2(local_max2);
+      local_max = fmaxf(m2.x, m2.y);
     }
     if (MODE != 2 && amax) {
       // lanes of a warp may belong to different (section, bh) groups: the lowest lane of every group folds in
@@ -197,16 +284,13 @@ __global__ void __launch_bounds__(256) quantize_int8_kernel(const T* __restrict_
   int8_t* o = out + (int64_t)head * per_head;
   const int64_t nvec = (per_head % 8 == 0) ? per_head / 8 : 0;  // vector path needs 16-byte aligned heads
   for (int64_t vi = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; vi < nvec; vi += (int64_t)gridDim.x * blockDim.x) {
-    float val[8];
     if (sizeof(T) == 2) {
-      const uint4 raw = reinterpret_cast<const uint4*>(p)[vi];
-      const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&raw);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) val[i] = __bfloat162float(e[i]);
-    } else {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) val[i] = ld_as_float<T>(p, vi * 8 + i);
+      reinterpret_cast<uint2*>(o)[vi] = quant_vector(reinterpret_cast<const uint4*>(p)[vi], scale, inv);
+      continue;
     }
+    float val[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) val[i] = ld_as_float<T>(p, vi * 8 + i);
     union { int8_t b[8]; uint2 u; } pk;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {

@@ -126,12 +126,15 @@ def all_gather_packed_records(group: Any, rec: PackedRecords, n_chunks: int, wor
     return sc.contiguous(), idx.contiguous(), ct.contiguous()
 
 
-def all_gather_pool(group: Any, pool: torch.Tensor, world: int) -> torch.Tensor:
+def all_gather_pool(group: Any, pool: torch.Tensor, world: int, deferred: bool = False):
     """Per-rank pools of promoted rows ``(cap * budget, C)`` -> ``(world * cap * budget, C)``, rank-major.  Each rank
     sends only the rows it promoted (8 MiB per rank for 2 chunks x 2048 rows x 1024 bf16 channels), where summing
-    zero-padded copies of the whole reduced sequence would move all of it through every rank."""
+    zero-padded copies of the whole reduced sequence would move all of it through every rank.
+
+    With ``deferred`` the collective is only started: the return value is ``(rows, wait)`` and the current stream sees
+    the rows after ``wait()``, so that work which does not need them (the merge of the records) runs beside the transfer."""
     if world == 1:
-        return pool
+        return (pool, lambda: None) if deferred else pool
     recv = torch.empty((world * pool.size(0), pool.size(1)), dtype=pool.dtype, device=pool.device)
     if POOL_EXCHANGE == "p2p" and pool.is_cuda:
         # one send and one receive per peer in a single group call: through NVSwitch every pair has its own full-rate
@@ -145,9 +148,18 @@ def all_gather_pool(group: Any, pool: torch.Tensor, world: int) -> torch.Tensor:
             ops_.append(dist.P2POp(dist.isend, pool, dist.get_global_rank(group, dst) if group is not None else dst, group))
             ops_.append(dist.P2POp(dist.irecv, recv[src * n:(src + 1) * n],
                                    dist.get_global_rank(group, src) if group is not None else src, group))
-        for req in dist.batch_isend_irecv(ops_):
-            req.wait()
+        reqs = dist.batch_isend_irecv(ops_)
+
+        def wait_all():
+            for req in reqs:
+                req.wait()
+        if deferred:
+            return recv, wait_all
+        wait_all()
         return recv
+    if deferred:
+        work = dist.all_gather_into_tensor(recv, pool.contiguous(), group=group, async_op=True)
+        return recv, work.wait
     dist.all_gather_into_tensor(recv, pool.contiguous(), group=group)
     return recv
 
