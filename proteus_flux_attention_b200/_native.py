@@ -75,6 +75,7 @@ SIGNATURES = {
                                      C.POINTER(ShortlistPlan), _p, _p, _i, _i, _p, C.POINTER(KVLayout), _p, _p, _p]),
     "aspa_attn_regroup_bytes": (_l, [_l, _i, _i]),
     "aspa_attn_tc_mode": (_i, [_i]),
+    "aspa_attn_picks_mode": (_i, [_i]),
     "aspa_attn_tc_status": (_i, [_i, _p]),
     "aspa_gather_attn_fwd_prepared": (_i, [_p, _p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _p, _p, _i, _l, _p, _p, _i,
                                            C.POINTER(ShortlistPlan), _p, _p, _i, _i, _p, C.POINTER(KVLayout), _p, _p, _i,

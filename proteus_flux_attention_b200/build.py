@@ -15,7 +15,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libaspa_b200.so"
-SOURCES = ["router.cu", "router_tc.cu", "select.cu", "rope_quant.cu", "plan.cu", "attention.cu", "attention_tc.cu", "ema_chunk.cu",
+SOURCES = ["router.cu", "router_tc.cu", "select.cu", "rope_quant.cu", "plan.cu", "attention.cu", "attention_tc.cu", "attention_picks.cu", "ema_chunk.cu",
            "memory_bank.cu", "quantile.cu"]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC", "--use_fast_math=false"]

@@ -891,6 +891,7 @@ using namespace aspa;
 // count: gather instead.  total_rows may be a host-side upper bound, which only makes the estimate of the gap
 // conservative.
 static int g_attn_tc_mode = 1;   // see tc_tiles_wanted
+static int g_attn_picks_mode = 1;   // 0: prototype picks always on the row kernel; 1: on warp-MMA tiles where covered
 static bool tile_path_ok(int qkv_dtype, int D, bool has_cand, bool has_mask, const aspa_shortlist_plan* plan, int heads,
                          int T, int64_t total_rows) {
   if (!(D == WK_D && (qkv_dtype == ASPA_BF16 || qkv_dtype == ASPA_I8) && !has_cand && !has_mask)) return false;
@@ -960,6 +961,12 @@ extern "C" int aspa_attn_regroup_rows(int qkv_dtype, int heads, int T, int D, co
 extern "C" int64_t aspa_attn_regroup_bytes(int64_t total_rows, int heads, int anchor_stride) {
   if (anchor_stride <= 0) return 0;
   return (int64_t)sizeof(int32_t) * ((int64_t)heads * anchor_stride + 1 + 2 * total_rows);
+}
+
+extern "C" int aspa_attn_picks_mode(int mode) {
+  const int old = g_attn_picks_mode;
+  if (mode == 0 || mode == 1) g_attn_picks_mode = mode;
+  return old;
 }
 
 extern "C" int aspa_attn_tc_mode(int mode) {
@@ -1129,7 +1136,9 @@ extern "C" int aspa_gather_attn_fwd_prepared(const void* q, const void* k, const
     if (extras) {
       p.write_partial = 0;
       p.extras_only = 1;
-      if (qkv_dtype == ASPA_BF16) launch_generic<__nv_bfloat16>(p, max_rows, st); else launch_generic<int8_t>(p, max_rows, st);
+      if (g_attn_picks_mode != 0 && picks_tiles_ok(p, qkv_dtype)) launch_picks_tiles(p, st);
+      else if (qkv_dtype == ASPA_BF16) launch_generic<__nv_bfloat16>(p, max_rows, st);
+      else launch_generic<int8_t>(p, max_rows, st);
       ASPA_CHECK_LAUNCH();
     }
     return ASPA_OK;

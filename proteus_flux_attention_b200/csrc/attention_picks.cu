@@ -1,0 +1,269 @@
+// Prototype-pick pass of the INT8 shortlist on warp-level tensor-core tiles (head_dim 64).
+//
+// The picks of a row are a prefix of the score-sorted list of its 128-token block (aspa_proto_plan), filtered by the
+// row's own window, anchors and length (reference kernels/sparse_attn.py:260-596: the dedup of the candidate
+// builder).  All rows of one (head, block) pair therefore walk the SAME list: one warp takes such a pair, up to 16 of
+// its rows at a time as the M dimension of mma.sync tiles, and reads every key and value row once for all of them,
+// where the row kernel reads them once per row and spends about 700 CUDA-core instructions per 32 keys of one row.
+//
+//   S = Q K^T   mma.sync m16n8k32 s8 x s8 -> s32 (the exact integer dot the row kernel computes with dp4a)
+//   O += P V    mma.sync m16n8k16 f16 x f16 -> f32, P rounded to fp16, V widened exactly from int8 to fp16
+//
+// No shared memory: fragments are loaded straight from global memory.  The K dimension of S (channels) and the N
+// dimension of O (channels) may be permuted freely as long as both operands agree, so a thread takes the 16 contiguous
+// bytes [16q, 16q+16) of a key row (q = lane % 4) and the 8 contiguous bytes [8g, 8g+8) of a value row (g = lane / 4)
+// instead of the scattered elements the canonical fragment layout would ask for.
+#include "attn_params.cuh"
+
+namespace aspa {
+
+constexpr int PK_WARPS = 4;
+
+__device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+  const __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+// bytes (lo, hi) = two int8 with their sign bits flipped -> the two values as an fp16 pair: 0x6400 | u is 1024 + u,
+// and 1024 + u - 1152 = u - 128 is the signed value (exact)
+__device__ __forceinline__ uint32_t flipped_bytes_to_half2(uint32_t pair_word, uint32_t sel) {
+  const uint32_t w = __byte_perm(pair_word, 0x64646464u, sel);
+  const __half2 v = __hsub2(*reinterpret_cast<const __half2*>(&w), __floats2half2_rn(1152.f, 1152.f));
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// First index in tok[0, n) (ascending) whose value is >= target; all lanes take part and get the answer.
+__device__ __forceinline__ int warp_lower_bound(const int32_t* __restrict__ tok, int n, int target, int lane) {
+  int lo = 0, hi = n;   // the answer lies in [lo, hi]
+  while (lo < hi) {
+    const int stride = (hi - lo + 31) >> 5;
+    const int pos = lo + (lane + 1) * stride - 1;
+    const int v = pos < hi ? tok[pos] : 0x7fffffff;
+    const unsigned ge = __ballot_sync(0xffffffffu, v >= target);
+    if (ge == 0u) return hi;
+    const int f = __ffs(ge) - 1;
+    const int top = lo + (f + 1) * stride - 1;
+    lo += f * stride;
+    hi = top < hi ? top : hi;
+  }
+  return lo;
+}
+
+struct PickRow {
+  int t, loc_start, limit, tmod, alo;
+  bool present, clamp_slot, aclamps;
+};
+
+__global__ void __launch_bounds__(PK_WARPS * 32) attn_picks_tile_kernel(const AttnParams p) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
+  const int bh = blockIdx.y;
+  const int PB = p.plan.proto_block;
+  const int nblk = (p.T + PB - 1) / PB;
+  const int blk = blockIdx.x * PK_WARPS + warp;
+  if (blk >= nblk) return;
+  const int start = p.row_offsets[bh];
+  const int cnt = p.row_offsets[bh + 1] - start;
+  if (cnt <= 0) return;
+  const int32_t* toks = p.token_idx + start;
+  const int r_lo = warp_lower_bound(toks, cnt, blk * PB, lane);
+  if (r_lo >= cnt) return;
+  const int span = min(cnt - r_lo, PB);   // a block holds at most PB rows of one head
+  const int r_hi = r_lo + warp_lower_bound(toks + r_lo, span, (blk + 1) * PB, lane);
+  if (r_hi == r_lo) return;
+
+  const int Tn = p.T;
+  const int b = bh / p.H;
+  const int8_t* qh = reinterpret_cast<const int8_t*>(p.q) + (int64_t)bh * Tn * 64;
+  const int8_t* kh = reinterpret_cast<const int8_t*>(p.k) + (int64_t)b * p.kv.k_batch + (int64_t)(bh % p.H) * p.kv.k_head;
+  const int8_t* vh = reinterpret_cast<const int8_t*>(p.v) + (int64_t)b * p.kv.v_batch + (int64_t)(bh % p.H) * p.kv.v_head;
+  const int64_t k_ts = p.kv.k_token, v_ts = p.kv.v_token;
+  const float LOG2E = 1.4426950408889634f;
+  const float sc2 = p.scale * p.q_scale[bh] * p.k_scale[bh] * LOG2E;   // scores in the log2 domain
+  const float vscale = p.v_scale[bh];
+  const int32_t* plist = p.plan.proto_lists + ((int64_t)b * nblk + blk) * p.plan.proto_list_stride;
+  const int astride = max(1, p.plan.anchor_stride);
+  const int n_at = p.plan.anchor_stride > 0 ? p.plan.anchor_slots : 0;
+  const bool pow2 = (astride & (astride - 1)) == 0;
+  const int window = p.plan.window;
+
+  for (int rt = r_lo; rt < r_hi; rt += 16) {
+    // rows g and g + 8 of this sub-tile
+    PickRow row[2];
+    uint32_t qa[2][4];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int r = rt + g + 8 * h;
+      PickRow& R = row[h];
+      R.present = r < r_hi;
+      R.t = R.present ? toks[r] : 0;
+      const int n_loc = window > 0 ? min(R.t + 1, window) : 1;
+      R.loc_start = R.t - n_loc + 1;
+      R.limit = R.present ? p.plan.proto_limit[(int64_t)b * Tn + R.t] : 0;
+      R.tmod = pow2 ? (R.t & (astride - 1)) : (R.t % astride);
+      R.alo = R.t - n_at * astride;
+      R.aclamps = n_at > 0 && R.alo < 0;
+      // the one anchor slot the tile pass leaves to this pass: the slot that clamps to key 0
+      const int j0 = R.t / astride + 1;
+      R.clamp_slot = R.present && p.anchors_done && n_at > 0 && j0 <= n_at && R.tmod != 0 && R.loc_start > 0;
+      uint4 w = make_uint4(0u, 0u, 0u, 0u);
+      if (R.present) w = *reinterpret_cast<const uint4*>(qh + (int64_t)R.t * 64 + 16 * q);
+      qa[h][0] = w.x; qa[h][1] = w.y; qa[h][2] = w.z; qa[h][3] = w.w;
+    }
+    int max_limit = max(row[0].limit, row[1].limit);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) max_limit = max(max_limit, __shfl_xor_sync(0xffffffffu, max_limit, off));
+    const int n_slots = max_limit + 1;   // slot 0: key 0 for the rows with the clamping anchor slot; slot i + 1: list entry i
+
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float o[8][4];
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
+
+    for (int s0 = 0; s0 < n_slots; s0 += 32) {
+      // ---- S = Q K^T for 32 slots: n-tile nt covers slots s0 + 8 nt + (0..7); this thread loads the key of column g
+      int u_own[4];
+      int c[4][4];
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+        const int slot = s0 + 8 * nt + g;
+        u_own[nt] = slot == 0 ? 0 : (slot <= max_limit ? plist[slot - 1] : -1);
+        const uint4 kw = *reinterpret_cast<const uint4*>(kh + (int64_t)max(u_own[nt], 0) * k_ts + 16 * q);
+        c[nt][0] = c[nt][1] = c[nt][2] = c[nt][3] = 0;
+        mma_s8(c[nt], qa[0][0], qa[1][0], qa[0][1], qa[1][1], kw.x, kw.y);
+        mma_s8(c[nt], qa[0][2], qa[1][2], qa[0][3], qa[1][3], kw.z, kw.w);
+      }
+      // ---- masks and scores: this thread holds columns 2q, 2q+1 of every n-tile for rows g (c0, c1) and g+8 (c2, c3)
+      int ucol[4][2];
+      float s[4][4];
+      float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int u = __shfl_sync(0xffffffffu, u_own[nt], 4 * (2 * q + j));
+          ucol[nt][j] = u;
+          const int slot = s0 + 8 * nt + 2 * q + j;
+          const int umod = pow2 ? (u & (astride - 1)) : (u >= 0 ? u % astride : 0);
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const PickRow& R = row[h];
+            bool ok;
+            if (slot == 0) {
+              ok = R.clamp_slot;
+            } else {
+              ok = R.present && slot <= R.limit && u >= 0 && u < R.loc_start;
+              if (n_at > 0) ok = ok && !((umod == R.tmod && u >= R.alo) || (u == 0 && R.aclamps));
+            }
+            const float v = ok ? (float)c[nt][2 * h + j] * sc2 : -INFINITY;
+            s[nt][2 * h + j] = v;
+            mx[h] = fmaxf(mx[h], v);
+          }
+        }
+      }
+      float corr[2], msafe[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+        const float m_new = fmaxf(m[h], mx[h]);
+        msafe[h] = m_new == -INFINITY ? 0.f : m_new;
+        corr[h] = exp2f(m[h] - msafe[h]);   // 0 while the row has seen nothing
+        m[h] = m_new;
+        l[h] *= corr[h];
+      }
+      // ---- P (fp16 fragments) and the row sums
+      uint32_t pa[4][2];
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const float p0 = exp2f(s[nt][2 * h] - msafe[h]), p1 = exp2f(s[nt][2 * h + 1] - msafe[h]);
+          l[h] += p0 + p1;
+          pa[nt][h] = pack_half2(p0, p1);
+        }
+      }
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        o[nt][0] *= corr[0]; o[nt][1] *= corr[0];
+        o[nt][2] *= corr[1]; o[nt][3] *= corr[1];
+      }
+      // ---- O += P V: two k16 steps; the keys of step kk are the columns this thread already knows
+#pragma unroll
+      for (int kk = 0; kk < 2; ++kk) {
+        uint2 vr[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int u = ucol[2 * kk + (i >> 1)][i & 1];   // k index 2q, 2q+1, 2q+8, 2q+9 of this step
+          vr[i] = *reinterpret_cast<const uint2*>(vh + (int64_t)max(u, 0) * v_ts + 8 * g);
+          vr[i].x ^= 0x80808080u;
+          vr[i].y ^= 0x80808080u;
+        }
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {   // channels 8g + 4 half + (0..3): n-tiles 4 half + (0..3)
+          const uint32_t k0 = half ? vr[0].y : vr[0].x, k1 = half ? vr[1].y : vr[1].x;
+          const uint32_t k2 = half ? vr[2].y : vr[2].x, k3 = half ? vr[3].y : vr[3].x;
+          const uint32_t lo01 = __byte_perm(k0, k1, 0x5140), hi01 = __byte_perm(k0, k1, 0x7362);   // (k0c, k1c) byte pairs
+          const uint32_t lo23 = __byte_perm(k2, k3, 0x5140), hi23 = __byte_perm(k2, k3, 0x7362);
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc) {
+            const uint32_t w01 = cc < 2 ? lo01 : hi01, w23 = cc < 2 ? lo23 : hi23;
+            const uint32_t sel = (cc & 1) ? 0x4342u : 0x4140u;
+            const uint32_t b0 = flipped_bytes_to_half2(w01, sel), b1 = flipped_bytes_to_half2(w23, sel);
+            mma_f16(o[4 * half + cc], pa[2 * kk][0], pa[2 * kk][1], pa[2 * kk + 1][0], pa[2 * kk + 1][1], b0, b1);
+          }
+        }
+      }
+    }
+
+    // ---- merge with the state the window and anchor passes left, normalise, store
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+      l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+      const PickRow& R = row[h];
+      if (!R.present) continue;
+      const int64_t grow = (int64_t)start + rt + g + 8 * h;
+      const float m1n = p.ws_m[grow], l1 = p.ws_l[grow];
+      const float m1 = m1n == -INFINITY ? -INFINITY : m1n * LOG2E;
+      const float mm = fmaxf(m[h], m1);
+      const float c1 = m1 == -INFINITY ? 0.f : exp2f(m1 - mm);
+      const float c2 = m[h] == -INFINITY ? 0.f : exp2f(m[h] - mm);
+      const float lt = l1 * c1 + l[h] * c2;
+      const float inv = lt > 0.f ? 1.f / lt : 0.f;
+      const int64_t ob = out_row_base(p, bh, R.t);
+      const float* wo = p.ws_o + grow * 64;
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+          const int ch = 8 * (2 * q + j) + nt;   // column 2q + j of n-tile nt is channel 8 (2q + j) + nt
+          store_out(p, ob + ch, (wo[ch] * c1 + o[nt][2 * h + j] * c2) * inv * vscale);
+        }
+      }
+    }
+  }
+}
+
+// Whether the pick pass of this call can run on the tile kernel: INT8, head_dim 64, a structural plan with prototype
+// lists, and no anchor slots left to this pass other than the one that clamps to key 0.
+bool picks_tiles_ok(const AttnParams& p, int qkv_dtype) {
+  if (qkv_dtype != ASPA_I8 || p.D != 64 || !p.has_plan || p.add_mask != nullptr) return false;
+  if (p.plan.proto_cap <= 0 || p.plan.proto_lists == nullptr || p.plan.proto_limit == nullptr || p.plan.proto_block <= 0) return false;
+  const bool anchors = p.plan.anchor_stride > 0 && p.plan.anchor_slots > 0;
+  return !anchors || p.anchors_done != 0;
+}
+
+void launch_picks_tiles(const AttnParams& p, cudaStream_t st) {
+  const int nblk = (p.T + p.plan.proto_block - 1) / p.plan.proto_block;
+  const dim3 grid((unsigned)ceil_div(nblk, PK_WARPS), (unsigned)p.heads);
+  attn_picks_tile_kernel<<<grid, PK_WARPS * 32, 0, st>>>(p);
+}
+
+}  // namespace aspa

@@ -63,4 +63,9 @@ __device__ __forceinline__ void store_out(const AttnParams& p, int64_t idx, floa
 // attn_window_kernel; returns false when the shape is not one it covers (head_dim 64, bf16 or int8 only).
 bool launch_window_tc(const AttnParams& p, int qkv_dtype, int max_rows, int groups, cudaStream_t st);
 
+// Warp-MMA tile version of the prototype-pick pass of the INT8 shortlist (attention_picks.cu): rows of one (head,
+// 128-token block) pair share their pick list.  picks_tiles_ok says whether the call is one it covers.
+bool picks_tiles_ok(const AttnParams& p, int qkv_dtype);
+void launch_picks_tiles(const AttnParams& p, cudaStream_t st);
+
 }  // namespace aspa

@@ -369,6 +369,28 @@ def test_planned_attention_int8(dev):
                       proto_cap=10, H=4, seed=13, quant=True)
 
 
+@pytest.mark.parametrize("case", [
+    # (anchor cases are sized so that the anchors go through the tile pass: >= 64 strided keys, >= 8 rows per group)
+    dict(T=1500, L=320, window=60, stride=16, local_cap=60, anchor_cap=80, proto_cap=150),   # picks over five 32-slot steps
+    dict(T=700, L=128, window=40, stride=0, local_cap=40, anchor_cap=0, proto_cap=80),       # no anchors at all
+    dict(T=900, L=200, window=50, stride=12, local_cap=50, anchor_cap=70, proto_cap=70),     # anchors clamp to key 0
+    dict(T=300, L=400, window=8, stride=0, local_cap=8, anchor_cap=0, proto_cap=300),        # cap beyond the prefix
+])
+def test_prototype_picks_on_tiles_int8(dev, case):
+    """The warp-MMA tile kernel of the prototype-pick pass (rows of a head and 128-token block share their list) against
+    the explicit reference table, and against the per-row kernel it replaces."""
+    from proteus_flux_attention_b200 import _native as N
+    old = N.lib().aspa_attn_picks_mode(1)
+    try:
+        tiles = _planned_vs_table(dev, torch.bfloat16, heads=8, D=64, H=4, seed=23, quant=True, **case)
+        N.lib().aspa_attn_picks_mode(0)
+        rows = _planned_vs_table(dev, torch.bfloat16, heads=8, D=64, H=4, seed=23, quant=True, **case)
+    finally:
+        N.lib().aspa_attn_picks_mode(old)
+    assert float((tiles - rows).abs().max()) < 1e-2 and float((tiles - rows).abs().mean()) < 5e-4
+    assert not torch.equal(tiles, rows)   # the two kernels round differently: equal outputs would mean one path ran twice
+
+
 @pytest.mark.parametrize("D", [5, 16, 128])
 def test_planned_attention_other_head_dims(dev, D):
     _planned_vs_table(dev, torch.float32, heads=4, T=150, D=D, L=32, window=12, stride=6, local_cap=12, anchor_cap=10,
