@@ -18,6 +18,9 @@
 namespace aspa {
 
 constexpr int PK_WARPS = 4;
+#ifndef PK_MIN_BLOCKS
+#define PK_MIN_BLOCKS 5
+#endif
 
 __device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -61,7 +64,7 @@ struct PickRow {
   bool present, clamp_slot, aclamps;
 };
 
-__global__ void __launch_bounds__(PK_WARPS * 32) attn_picks_tile_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(PK_WARPS * 32, PK_MIN_BLOCKS) attn_picks_tile_kernel(const AttnParams p) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
   const int bh = blockIdx.y;
   const int PB = p.plan.proto_block;
@@ -189,10 +192,12 @@ __global__ void __launch_bounds__(PK_WARPS * 32) attn_picks_tile_kernel(const At
           pa[nt][h] = pack_half2(p0, p1);
         }
       }
+      if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {   // most steps move no row's maximum
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
-        o[nt][0] *= corr[0]; o[nt][1] *= corr[0];
-        o[nt][2] *= corr[1]; o[nt][3] *= corr[1];
+        for (int nt = 0; nt < 8; ++nt) {
+          o[nt][0] *= corr[0]; o[nt][1] *= corr[0];
+          o[nt][2] *= corr[1]; o[nt][3] *= corr[1];
+        }
       }
       // ---- O += P V: two k16 steps; the keys of step kk are the columns this thread already knows
 #pragma unroll
