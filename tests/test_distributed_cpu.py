@@ -79,6 +79,10 @@ def _worker(rank, world, port, n_chunks, chunk_len, budget, buffer_tokens, seed,
             n = int(ct[j])
             pool[j * budget: j * budget + n] = seq[0, ix[j, :n]]
         all_pool = D.all_gather_pool(None, pool, world)
+        # the deferred form (started, then waited for after other work) moves the same rows
+        later, arrived = D.all_gather_pool(None, pool, world, deferred=True)
+        arrived()
+        assert torch.equal(later, all_pool)
         # position of every kept index in the chunk-major promotion list, then in the rank-major gathered pool
         flat_ix = a_ix.view(-1)
         pos = torch.tensor([int((flat_ix == t).nonzero()[0]) for t in keep_idx.tolist()], dtype=torch.int64)
