@@ -851,18 +851,28 @@ __global__ void __launch_bounds__(256) anchor_regroup_kernel(const int32_t* __re
   const int start = row_offsets[bh], cnt = row_offsets[bh + 1] - start;
   int n = 0;
   const int base = fill ? grp_offsets[warp] : 0;
-  for (int r0 = 0; r0 < cnt; r0 += 32) {
-    const int r = r0 + lane;
-    const int t = r < cnt ? token_idx[start + r] : -1;
-    const bool mine = t >= 0 && (t % stride) == rho;
-    const unsigned bal = __ballot_sync(0xffffffffu, mine);
-    if (fill && mine) {
-      const int pos = base + n + __popc(bal & ((1u << lane) - 1u));
-      // rows whose local window already reaches key 0 have no anchor key at all
-      grp_tok[pos] = (t + 1 >= window) ? t / stride - jmin : ANCHOR_NO_KEYS;
-      grp_row[pos] = start + r;
+  const bool pow2 = (stride & (stride - 1)) == 0;
+  // four loads of the token list in flight per lane: the walk is a chain of L2 round trips otherwise
+  for (int r0 = 0; r0 < cnt; r0 += 128) {
+    int tk[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int r = r0 + 32 * u + lane;
+      tk[u] = r < cnt ? token_idx[start + r] : -1;
     }
-    n += __popc(bal);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int r = r0 + 32 * u + lane, t = tk[u];
+      const bool mine = t >= 0 && (pow2 ? (t & (stride - 1)) : (t % stride)) == rho;
+      const unsigned bal = __ballot_sync(0xffffffffu, mine);
+      if (fill && mine) {
+        const int pos = base + n + __popc(bal & ((1u << lane) - 1u));
+        // rows whose local window already reaches key 0 have no anchor key at all
+        grp_tok[pos] = (t + 1 >= window) ? t / stride - jmin : ANCHOR_NO_KEYS;
+        grp_row[pos] = start + r;
+      }
+      n += __popc(bal);
+    }
   }
   if (!fill && lane == 0) grp_offsets[warp] = n;
 }

@@ -76,6 +76,7 @@ __global__ void __launch_bounds__(256) ema_partial_tc_kernel(const __nv_bfloat16
   unsigned char* xs = etc_smem;                                              // ETC_STAGES x [32 tokens][512 B], swizzled
   float* ps = reinterpret_cast<float*>(etc_smem + ETC_STAGES * ETC_X_BYTES);  // ETC_STAGES x [32 tokens][MT*16]
   constexpr int GP = MT * 16;
+  uint32_t* as_ = reinterpret_cast<uint32_t*>(ps + ETC_STAGES * ETC_STEP * GP);  // [k16][m][term][lane] x 4 words: A fragments of the step
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int chunk = blockIdx.x, c0 = blockIdx.y * ETC_CH;
   const int64_t t_begin = (int64_t)chunk * ETC_TOK;
@@ -137,6 +138,32 @@ __global__ void __launch_bounds__(256) ema_partial_tc_kernel(const __nv_bfloat16
     if (blockIdx.y == 0 && tid < G) {
       for (int r = 0; r < ETC_STEP; ++r) cnt += pd[r * GP + tid];
     }
+    // A = probs^T as bf16 fragments, three terms each (hi + mid + lo carry the fp32 probability): every warp needs
+    // the same ones, so they are split ONCE per step into shared memory - one thread per (k16, m, lane) fragment -
+    // instead of by each of the eight warps (the splitting was three quarters of the kernel's instructions).
+    if (tid < (ETC_STEP / 16) * MT * 32) {
+      const int fl = tid & 31, fm = (tid >> 5) % MT, fk = tid / (32 * MT);
+      const int fgq = fl >> 2, fq = fl & 3;
+      const int g0 = fm * 16 + fgq, tk = fk * 16 + 2 * fq;
+      float pv[8];
+      pv[0] = pd[(tk) * GP + g0];          pv[1] = pd[(tk + 1) * GP + g0];
+      pv[2] = pd[(tk) * GP + g0 + 8];      pv[3] = pd[(tk + 1) * GP + g0 + 8];
+      pv[4] = pd[(tk + 8) * GP + g0];      pv[5] = pd[(tk + 9) * GP + g0];
+      pv[6] = pd[(tk + 8) * GP + g0 + 8];  pv[7] = pd[(tk + 9) * GP + g0 + 8];
+#pragma unroll
+      for (int term = 0; term < 3; ++term) {
+        uint32_t af[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float h0 = bf16_round(pv[2 * i]), h1 = bf16_round(pv[2 * i + 1]);
+          pv[2 * i] -= h0;       // exact: what this term does not represent
+          pv[2 * i + 1] -= h1;
+          af[i] = pack_bf16(h0, h1);
+        }
+        *reinterpret_cast<uint4*>(as_ + (((fk * MT + fm) * 3 + term) * 32 + fl) * 4) = make_uint4(af[0], af[1], af[2], af[3]);
+      }
+    }
+    __syncthreads();
 #pragma unroll
     for (int k16 = 0; k16 < ETC_STEP / 16; ++k16) {
       // B fragments: this warp's 32 channels = chunks 4*warp .. 4*warp+3, two n-tiles per ldmatrix
@@ -150,25 +177,10 @@ __global__ void __launch_bounds__(256) ema_partial_tc_kernel(const __nv_bfloat16
       }
 #pragma unroll
       for (int m = 0; m < MT; ++m) {
-        // A = probs^T: A[gate][token]; fragment rows gq, gq+8, token pairs 2q, 2q+1 and +8
-        float pv[8];
-        const int g0 = m * 16 + gq, tk = k16 * 16 + 2 * q;
-        pv[0] = pd[(tk) * GP + g0];          pv[1] = pd[(tk + 1) * GP + g0];
-        pv[2] = pd[(tk) * GP + g0 + 8];      pv[3] = pd[(tk + 1) * GP + g0 + 8];
-        pv[4] = pd[(tk + 8) * GP + g0];      pv[5] = pd[(tk + 9) * GP + g0];
-        pv[6] = pd[(tk + 8) * GP + g0 + 8];  pv[7] = pd[(tk + 9) * GP + g0 + 8];
-        float res[8];
 #pragma unroll
         for (int term = 0; term < 3; ++term) {
-          uint32_t af[4];
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float v0 = term == 0 ? pv[2 * i] : res[2 * i], v1 = term == 0 ? pv[2 * i + 1] : res[2 * i + 1];
-            const float h0 = bf16_round(v0), h1 = bf16_round(v1);
-            res[2 * i] = v0 - h0;       // exact: what this term does not represent
-            res[2 * i + 1] = v1 - h1;
-            af[i] = pack_bf16(h0, h1);
-          }
+          const uint4 a4 = *reinterpret_cast<const uint4*>(as_ + (((k16 * MT + m) * 3 + term) * 32 + lane) * 4);
+          const uint32_t af[4] = {a4.x, a4.y, a4.z, a4.w};
 #pragma unroll
           for (int j = 0; j < 4; ++j) mma_bf16(acc[m][j], af, bf[j][0], bf[j][1]);
         }
@@ -817,7 +829,7 @@ extern "C" int aspa_proto_ema_update(const void* x, int x_dtype, int64_t n, int 
   if (tc) {
     const int MT = (int)ceil_div(G, 16);
     const dim3 grid((unsigned)nchunk, (unsigned)ceil_div(C, ETC_CH));
-    const size_t smem = ETC_STAGES * (ETC_X_BYTES + ETC_STEP * MT * 16 * sizeof(float));
+    const size_t smem = ETC_STAGES * (ETC_X_BYTES + ETC_STEP * MT * 16 * sizeof(float)) + (ETC_STEP / 16) * MT * 3 * 32 * 16;
     auto launch = [&](auto kernel) {
       cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       kernel<<<grid, 256, smem, st>>>((const __nv_bfloat16*)x, n, C, gate_probs, G, pw, pc);
