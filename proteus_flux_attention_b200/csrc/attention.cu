@@ -1146,7 +1146,7 @@ extern "C" int aspa_gather_attn_fwd_prepared(const void* q, const void* k, const
     if (extras) {
       p.write_partial = 0;
       p.extras_only = 1;
-      if (g_attn_picks_mode != 0 && picks_tiles_ok(p, qkv_dtype)) launch_picks_tiles(p, st);
+      if (g_attn_picks_mode != 0 && picks_tiles_ok(p, qkv_dtype)) launch_picks_tiles(p, qkv_dtype, st);
       else if (qkv_dtype == ASPA_BF16) launch_generic<__nv_bfloat16>(p, max_rows, st);
       else launch_generic<int8_t>(p, max_rows, st);
       ASPA_CHECK_LAUNCH();

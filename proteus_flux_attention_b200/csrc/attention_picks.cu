@@ -1,4 +1,4 @@
-// Prototype-pick pass of the INT8 shortlist on warp-level tensor-core tiles (head_dim 64).
+// Prototype-pick pass of the shortlist on warp-level tensor-core tiles (head_dim 64, int8 or bf16 q / k / v).
 //
 // The picks of a row are a prefix of the score-sorted list of its 128-token block (aspa_proto_plan), filtered by the
 // row's own window, anchors and length (reference kernels/sparse_attn.py:260-596: the dedup of the candidate
@@ -6,13 +6,14 @@
 // its rows at a time as the M dimension of mma.sync tiles, and reads every key and value row once for all of them,
 // where the row kernel reads them once per row and spends about 700 CUDA-core instructions per 32 keys of one row.
 //
-//   S = Q K^T   mma.sync m16n8k32 s8 x s8 -> s32 (the exact integer dot the row kernel computes with dp4a)
-//   O += P V    mma.sync m16n8k16 f16 x f16 -> f32, P rounded to fp16, V widened exactly from int8 to fp16
+//   int8:  S = Q K^T   mma.sync m16n8k32 s8 x s8 -> s32 (the exact integer dot the row kernel computes with dp4a)
+//          O += P V    mma.sync m16n8k16 f16 x f16 -> f32, P rounded to fp16, V widened exactly from int8 to fp16
+//   bf16:  both products mma.sync m16n8k16 bf16 x bf16 -> f32, P rounded to bf16 (as in the window tile kernel)
 //
 // No shared memory: fragments are loaded straight from global memory.  The K dimension of S (channels) and the N
 // dimension of O (channels) may be permuted freely as long as both operands agree, so a thread takes the 16 contiguous
-// bytes [16q, 16q+16) of a key row (q = lane % 4) and the 8 contiguous bytes [8g, 8g+8) of a value row (g = lane / 4)
-// instead of the scattered elements the canonical fragment layout would ask for.
+// channels [16q, 16q+16) of a key row (q = lane % 4) and the 8 contiguous channels [8g, 8g+8) of a value row
+// (g = lane / 4) instead of the scattered elements the canonical fragment layout would ask for.
 #include "attn_params.cuh"
 
 namespace aspa {
@@ -29,6 +30,14 @@ __device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, ui
 __device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_bf16_f32(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf162(float lo, float hi) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&h);
 }
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
   const __half2 h = __floats2half2_rn(lo, hi);
@@ -64,7 +73,10 @@ struct PickRow {
   bool present, clamp_slot, aclamps;
 };
 
-__global__ void __launch_bounds__(PK_WARPS * 32, PK_MIN_BLOCKS) attn_picks_tile_kernel(const AttnParams p) {
+template <typename T>
+__global__ void __launch_bounds__(PK_WARPS * 32, sizeof(T) == 1 ? PK_MIN_BLOCKS : 4) attn_picks_tile_kernel(const AttnParams p) {
+  constexpr bool I8 = sizeof(T) == 1;
+  constexpr int QW = I8 ? 4 : 8;   // 32-bit words of a thread's 16 channels of a q or k row
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
   const int bh = blockIdx.y;
   const int PB = p.plan.proto_block;
@@ -83,13 +95,13 @@ __global__ void __launch_bounds__(PK_WARPS * 32, PK_MIN_BLOCKS) attn_picks_tile_
 
   const int Tn = p.T;
   const int b = bh / p.H;
-  const int8_t* qh = reinterpret_cast<const int8_t*>(p.q) + (int64_t)bh * Tn * 64;
-  const int8_t* kh = reinterpret_cast<const int8_t*>(p.k) + (int64_t)b * p.kv.k_batch + (int64_t)(bh % p.H) * p.kv.k_head;
-  const int8_t* vh = reinterpret_cast<const int8_t*>(p.v) + (int64_t)b * p.kv.v_batch + (int64_t)(bh % p.H) * p.kv.v_head;
+  const T* qh = reinterpret_cast<const T*>(p.q) + (int64_t)bh * Tn * 64;
+  const T* kh = reinterpret_cast<const T*>(p.k) + (int64_t)b * p.kv.k_batch + (int64_t)(bh % p.H) * p.kv.k_head;
+  const T* vh = reinterpret_cast<const T*>(p.v) + (int64_t)b * p.kv.v_batch + (int64_t)(bh % p.H) * p.kv.v_head;
   const int64_t k_ts = p.kv.k_token, v_ts = p.kv.v_token;
   const float LOG2E = 1.4426950408889634f;
-  const float sc2 = p.scale * p.q_scale[bh] * p.k_scale[bh] * LOG2E;   // scores in the log2 domain
-  const float vscale = p.v_scale[bh];
+  const float sc2 = (I8 ? p.scale * p.q_scale[bh] * p.k_scale[bh] : p.scale) * LOG2E;   // scores in the log2 domain
+  const float vscale = I8 ? p.v_scale[bh] : 1.f;
   const int32_t* plist = p.plan.proto_lists + ((int64_t)b * nblk + blk) * p.plan.proto_list_stride;
   const int astride = max(1, p.plan.anchor_stride);
   const int n_at = p.plan.anchor_stride > 0 ? p.plan.anchor_slots : 0;
@@ -99,7 +111,7 @@ __global__ void __launch_bounds__(PK_WARPS * 32, PK_MIN_BLOCKS) attn_picks_tile_
   for (int rt = r_lo; rt < r_hi; rt += 16) {
     // rows g and g + 8 of this sub-tile
     PickRow row[2];
-    uint32_t qa[2][4];
+    uint32_t qa[2][QW];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       const int r = rt + g + 8 * h;
@@ -115,9 +127,12 @@ __global__ void __launch_bounds__(PK_WARPS * 32, PK_MIN_BLOCKS) attn_picks_tile_
       // the one anchor slot the tile pass leaves to this pass: the slot that clamps to key 0
       const int j0 = R.t / astride + 1;
       R.clamp_slot = R.present && p.anchors_done && n_at > 0 && j0 <= n_at && R.tmod != 0 && R.loc_start > 0;
-      uint4 w = make_uint4(0u, 0u, 0u, 0u);
-      if (R.present) w = *reinterpret_cast<const uint4*>(qh + (int64_t)R.t * 64 + 16 * q);
-      qa[h][0] = w.x; qa[h][1] = w.y; qa[h][2] = w.z; qa[h][3] = w.w;
+#pragma unroll
+      for (int i = 0; i < QW / 4; ++i) {
+        uint4 w = make_uint4(0u, 0u, 0u, 0u);
+        if (R.present) w = reinterpret_cast<const uint4*>(qh + (int64_t)R.t * 64 + 16 * q)[i];
+        qa[h][4 * i] = w.x; qa[h][4 * i + 1] = w.y; qa[h][4 * i + 2] = w.z; qa[h][4 * i + 3] = w.w;
+      }
     }
     int max_limit = max(row[0].limit, row[1].limit);
 #pragma unroll
@@ -132,15 +147,27 @@ __global__ void __launch_bounds__(PK_WARPS * 32, PK_MIN_BLOCKS) attn_picks_tile_
     for (int s0 = 0; s0 < n_slots; s0 += 32) {
       // ---- S = Q K^T for 32 slots: n-tile nt covers slots s0 + 8 nt + (0..7); this thread loads the key of column g
       int u_own[4];
-      int c[4][4];
+      float c[4][4];
 #pragma unroll
       for (int nt = 0; nt < 4; ++nt) {
         const int slot = s0 + 8 * nt + g;
         u_own[nt] = slot == 0 ? 0 : (slot <= max_limit ? plist[slot - 1] : -1);
-        const uint4 kw = *reinterpret_cast<const uint4*>(kh + (int64_t)max(u_own[nt], 0) * k_ts + 16 * q);
-        c[nt][0] = c[nt][1] = c[nt][2] = c[nt][3] = 0;
-        mma_s8(c[nt], qa[0][0], qa[1][0], qa[0][1], qa[1][1], kw.x, kw.y);
-        mma_s8(c[nt], qa[0][2], qa[1][2], qa[0][3], qa[1][3], kw.z, kw.w);
+        const uint4* krow = reinterpret_cast<const uint4*>(kh + (int64_t)max(u_own[nt], 0) * k_ts + 16 * q);
+        if (I8) {
+          const uint4 kw = krow[0];
+          int ci[4] = {0, 0, 0, 0};
+          mma_s8(ci, qa[0][0], qa[1][0], qa[0][1], qa[1][1], kw.x, kw.y);
+          mma_s8(ci, qa[0][2], qa[1][2], qa[0][3], qa[1][3], kw.z, kw.w);
+          c[nt][0] = (float)ci[0]; c[nt][1] = (float)ci[1]; c[nt][2] = (float)ci[2]; c[nt][3] = (float)ci[3];
+        } else {
+          const uint4 k0 = krow[0], k1 = krow[1];
+          const uint32_t kw[8] = {k0.x, k0.y, k0.z, k0.w, k1.x, k1.y, k1.z, k1.w};
+          c[nt][0] = c[nt][1] = c[nt][2] = c[nt][3] = 0.f;
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks)   // 16 channels per step: words 2 ks and 2 ks + 1 of both operands
+            mma_bf16_f32(c[nt], qa[0][(2 * ks) % QW], qa[1][(2 * ks) % QW], qa[0][(2 * ks + 1) % QW], qa[1][(2 * ks + 1) % QW],
+                         kw[2 * ks], kw[2 * ks + 1]);
+        }
       }
       // ---- masks and scores: this thread holds columns 2q, 2q+1 of every n-tile for rows g (c0, c1) and g+8 (c2, c3)
       int ucol[4][2];
@@ -164,7 +191,7 @@ __global__ void __launch_bounds__(PK_WARPS * 32, PK_MIN_BLOCKS) attn_picks_tile_
               ok = R.present && slot <= R.limit && u >= 0 && u < R.loc_start;
               if (n_at > 0) ok = ok && !((umod == R.tmod && u >= R.alo) || (u == 0 && R.aclamps));
             }
-            const float v = ok ? (float)c[nt][2 * h + j] * sc2 : -INFINITY;
+            const float v = ok ? c[nt][2 * h + j] * sc2 : -INFINITY;
             s[nt][2 * h + j] = v;
             mx[h] = fmaxf(mx[h], v);
           }
@@ -189,7 +216,7 @@ __global__ void __launch_bounds__(PK_WARPS * 32, PK_MIN_BLOCKS) attn_picks_tile_
         for (int h = 0; h < 2; ++h) {
           const float p0 = exp2f(s[nt][2 * h] - msafe[h]), p1 = exp2f(s[nt][2 * h + 1] - msafe[h]);
           l[h] += p0 + p1;
-          pa[nt][h] = pack_half2(p0, p1);
+          pa[nt][h] = I8 ? pack_half2(p0, p1) : pack_bf162(p0, p1);
         }
       }
       if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {   // most steps move no row's maximum
@@ -202,26 +229,47 @@ __global__ void __launch_bounds__(PK_WARPS * 32, PK_MIN_BLOCKS) attn_picks_tile_
       // ---- O += P V: two k16 steps; the keys of step kk are the columns this thread already knows
 #pragma unroll
       for (int kk = 0; kk < 2; ++kk) {
-        uint2 vr[4];
+        if (I8) {
+          uint2 vr[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int u = ucol[2 * kk + (i >> 1)][i & 1];   // k index 2q, 2q+1, 2q+8, 2q+9 of this step
-          vr[i] = *reinterpret_cast<const uint2*>(vh + (int64_t)max(u, 0) * v_ts + 8 * g);
-          vr[i].x ^= 0x80808080u;
-          vr[i].y ^= 0x80808080u;
-        }
+          for (int i = 0; i < 4; ++i) {
+            const int u = ucol[2 * kk + (i >> 1)][i & 1];   // k index 2q, 2q+1, 2q+8, 2q+9 of this step
+            vr[i] = *reinterpret_cast<const uint2*>(vh + (int64_t)max(u, 0) * v_ts + 8 * g);
+            vr[i].x ^= 0x80808080u;
+            vr[i].y ^= 0x80808080u;
+          }
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {   // channels 8g + 4 half + (0..3): n-tiles 4 half + (0..3)
-          const uint32_t k0 = half ? vr[0].y : vr[0].x, k1 = half ? vr[1].y : vr[1].x;
-          const uint32_t k2 = half ? vr[2].y : vr[2].x, k3 = half ? vr[3].y : vr[3].x;
-          const uint32_t lo01 = __byte_perm(k0, k1, 0x5140), hi01 = __byte_perm(k0, k1, 0x7362);   // (k0c, k1c) byte pairs
-          const uint32_t lo23 = __byte_perm(k2, k3, 0x5140), hi23 = __byte_perm(k2, k3, 0x7362);
+          for (int half = 0; half < 2; ++half) {   // channels 8g + 4 half + (0..3): n-tiles 4 half + (0..3)
+            const uint32_t k0 = half ? vr[0].y : vr[0].x, k1 = half ? vr[1].y : vr[1].x;
+            const uint32_t k2 = half ? vr[2].y : vr[2].x, k3 = half ? vr[3].y : vr[3].x;
+            const uint32_t lo01 = __byte_perm(k0, k1, 0x5140), hi01 = __byte_perm(k0, k1, 0x7362);   // (k0c, k1c) byte pairs
+            const uint32_t lo23 = __byte_perm(k2, k3, 0x5140), hi23 = __byte_perm(k2, k3, 0x7362);
 #pragma unroll
-          for (int cc = 0; cc < 4; ++cc) {
-            const uint32_t w01 = cc < 2 ? lo01 : hi01, w23 = cc < 2 ? lo23 : hi23;
-            const uint32_t sel = (cc & 1) ? 0x4342u : 0x4140u;
-            const uint32_t b0 = flipped_bytes_to_half2(w01, sel), b1 = flipped_bytes_to_half2(w23, sel);
-            mma_f16(o[4 * half + cc], pa[2 * kk][0], pa[2 * kk][1], pa[2 * kk + 1][0], pa[2 * kk + 1][1], b0, b1);
+            for (int cc = 0; cc < 4; ++cc) {
+              const uint32_t w01 = cc < 2 ? lo01 : hi01, w23 = cc < 2 ? lo23 : hi23;
+              const uint32_t sel = (cc & 1) ? 0x4342u : 0x4140u;
+              const uint32_t b0 = flipped_bytes_to_half2(w01, sel), b1 = flipped_bytes_to_half2(w23, sel);
+              mma_f16(o[4 * half + cc], pa[2 * kk][0], pa[2 * kk][1], pa[2 * kk + 1][0], pa[2 * kk + 1][1], b0, b1);
+            }
+          }
+        } else {
+          uint4 vr[4];   // channels 8g .. 8g+7 of the four value rows, two bf16 per word
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int u = ucol[2 * kk + (i >> 1)][i & 1];
+            vr[i] = *reinterpret_cast<const uint4*>(vh + (int64_t)max(u, 0) * v_ts + 8 * g);
+          }
+#pragma unroll
+          for (int cw = 0; cw < 4; ++cw) {   // word cw holds channels 8g + 2 cw and 8g + 2 cw + 1: n-tiles 2 cw, 2 cw + 1
+            const uint32_t a0 = cw == 0 ? vr[0].x : cw == 1 ? vr[0].y : cw == 2 ? vr[0].z : vr[0].w;
+            const uint32_t a1 = cw == 0 ? vr[1].x : cw == 1 ? vr[1].y : cw == 2 ? vr[1].z : vr[1].w;
+            const uint32_t a2 = cw == 0 ? vr[2].x : cw == 1 ? vr[2].y : cw == 2 ? vr[2].z : vr[2].w;
+            const uint32_t a3 = cw == 0 ? vr[3].x : cw == 1 ? vr[3].y : cw == 2 ? vr[3].z : vr[3].w;
+            // (key 2q, key 2q+1) of the even channel, then of the odd one
+            mma_bf16_f32(o[2 * cw], pa[2 * kk][0], pa[2 * kk][1], pa[2 * kk + 1][0], pa[2 * kk + 1][1],
+                         __byte_perm(a0, a1, 0x5410), __byte_perm(a2, a3, 0x5410));
+            mma_bf16_f32(o[2 * cw + 1], pa[2 * kk][0], pa[2 * kk][1], pa[2 * kk + 1][0], pa[2 * kk + 1][1],
+                         __byte_perm(a0, a1, 0x7632), __byte_perm(a2, a3, 0x7632));
           }
         }
       }
@@ -256,19 +304,20 @@ __global__ void __launch_bounds__(PK_WARPS * 32, PK_MIN_BLOCKS) attn_picks_tile_
   }
 }
 
-// Whether the pick pass of this call can run on the tile kernel: INT8, head_dim 64, a structural plan with prototype
+// Whether the pick pass of this call can run on the tile kernel: int8 or bf16, head_dim 64, a structural plan with prototype
 // lists, and no anchor slots left to this pass other than the one that clamps to key 0.
 bool picks_tiles_ok(const AttnParams& p, int qkv_dtype) {
-  if (qkv_dtype != ASPA_I8 || p.D != 64 || !p.has_plan || p.add_mask != nullptr) return false;
+  if ((qkv_dtype != ASPA_I8 && qkv_dtype != ASPA_BF16) || p.D != 64 || !p.has_plan || p.add_mask != nullptr) return false;
   if (p.plan.proto_cap <= 0 || p.plan.proto_lists == nullptr || p.plan.proto_limit == nullptr || p.plan.proto_block <= 0) return false;
   const bool anchors = p.plan.anchor_stride > 0 && p.plan.anchor_slots > 0;
   return !anchors || p.anchors_done != 0;
 }
 
-void launch_picks_tiles(const AttnParams& p, cudaStream_t st) {
+void launch_picks_tiles(const AttnParams& p, int qkv_dtype, cudaStream_t st) {
   const int nblk = (p.T + p.plan.proto_block - 1) / p.plan.proto_block;
   const dim3 grid((unsigned)ceil_div(nblk, PK_WARPS), (unsigned)p.heads);
-  attn_picks_tile_kernel<<<grid, PK_WARPS * 32, 0, st>>>(p);
+  if (qkv_dtype == ASPA_I8) attn_picks_tile_kernel<int8_t><<<grid, PK_WARPS * 32, 0, st>>>(p);
+  else attn_picks_tile_kernel<__nv_bfloat16><<<grid, PK_WARPS * 32, 0, st>>>(p);
 }
 
 }  // namespace aspa

@@ -66,6 +66,6 @@ bool launch_window_tc(const AttnParams& p, int qkv_dtype, int max_rows, int grou
 // Warp-MMA tile version of the prototype-pick pass of the INT8 shortlist (attention_picks.cu): rows of one (head,
 // 128-token block) pair share their pick list.  picks_tiles_ok says whether the call is one it covers.
 bool picks_tiles_ok(const AttnParams& p, int qkv_dtype);
-void launch_picks_tiles(const AttnParams& p, cudaStream_t st);
+void launch_picks_tiles(const AttnParams& p, int qkv_dtype, cudaStream_t st);
 
 }  // namespace aspa

@@ -376,15 +376,16 @@ def test_planned_attention_int8(dev):
     dict(T=900, L=200, window=50, stride=12, local_cap=50, anchor_cap=70, proto_cap=70),     # anchors clamp to key 0
     dict(T=300, L=400, window=8, stride=0, local_cap=8, anchor_cap=0, proto_cap=300),        # cap beyond the prefix
 ])
-def test_prototype_picks_on_tiles_int8(dev, case):
-    """The warp-MMA tile kernel of the prototype-pick pass (rows of a head and 128-token block share their list) against
-    the explicit reference table, and against the per-row kernel it replaces."""
+@pytest.mark.parametrize("quant", [True, False])
+def test_prototype_picks_on_tiles(dev, case, quant):
+    """The warp-MMA tile kernel of the prototype-pick pass (rows of a head and 128-token block share their list), int8
+    and bf16, against the explicit reference table and against the per-row kernel it replaces."""
     from proteus_flux_attention_b200 import _native as N
     old = N.lib().aspa_attn_picks_mode(1)
     try:
-        tiles = _planned_vs_table(dev, torch.bfloat16, heads=8, D=64, H=4, seed=23, quant=True, **case)
+        tiles = _planned_vs_table(dev, torch.bfloat16, heads=8, D=64, H=4, seed=23, quant=quant, **case)
         N.lib().aspa_attn_picks_mode(0)
-        rows = _planned_vs_table(dev, torch.bfloat16, heads=8, D=64, H=4, seed=23, quant=True, **case)
+        rows = _planned_vs_table(dev, torch.bfloat16, heads=8, D=64, H=4, seed=23, quant=quant, **case)
     finally:
         N.lib().aspa_attn_picks_mode(old)
     assert float((tiles - rows).abs().max()) < 1e-2 and float((tiles - rows).abs().mean()) < 5e-4
