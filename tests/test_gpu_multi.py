@@ -1,5 +1,6 @@
 """Two-GPU test of the sharded chunked pipeline: ranks own disjoint chunk ranges, exchange promotion
-records with NCCL all-gather and kept rows with an all-reduce of disjoint rows, and must reproduce the single-GPU result bit for bit.
+records and promoted rows with NCCL all-gathers (eagerly, and captured inside one graph for the whole run), and must
+reproduce the single-GPU result bit for bit.
 Skipped when fewer than two CUDA devices are visible.  NVLS is switched off for the child processes."""
 import os
 import socket
