@@ -2,9 +2,8 @@
 
 Same flags, log lines and JSON report layout as the reference's ``scripts/chunked_shortlist.py`` (:70-101 flags,
 :186-197 report), on the sm_100a runner.  Differences: the device must be a CUDA device (there is no CPU path),
-``--storage device`` keeps the sequence in HBM, ``--storage disk`` is refused (the sequence of every supported size
-fits in host memory or HBM; the reference's disk staging is host I/O around the same chunk loop), and three
-additions of this runner are exposed: ``--cuda-graph``, ``--freeze-prototypes`` and ``--score-only``."""
+``--storage device`` keeps the sequence in HBM (``disk`` stages it in a float32 memory-mapped file as the reference
+does, ``--temp-dir`` and ``--ram-limit-mb`` included), and three additions of this runner are exposed: ``--cuda-graph``, ``--freeze-prototypes`` and ``--score-only``."""
 from __future__ import annotations
 
 import argparse
@@ -59,9 +58,9 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--report-latency", action="store_true", help="Accepted for compatibility; CUDA-event metrics are always on.")
     p.add_argument("--no-final-pass", action="store_true", help="Skip the final attention pass.")
     p.add_argument("--storage", choices=["auto", "cpu", "disk", "device"], default="auto",
-                   help="Where the sequence lives while it is streamed (cpu: pinned host memory; device: HBM).")
-    p.add_argument("--temp-dir", type=Path, help="Accepted for compatibility (disk staging is not built).")
-    p.add_argument("--ram-limit-mb", type=int, help="Accepted for compatibility (disk staging is not built).")
+                   help="Where the sequence lives while it is streamed (cpu: pinned host memory; disk: memory-mapped file; device: HBM).")
+    p.add_argument("--temp-dir", type=Path, help="Directory for the memory-mapped file of disk staging.")
+    p.add_argument("--ram-limit-mb", type=int, help="Host memory above which auto / cpu storage falls back to disk.")
     p.add_argument("--input", type=Path, help="Optional input tensor (.pt or .npy) with shape (1, seq_len, d_model).")
     p.add_argument("--save-indices", type=Path, help="Optional path to save the retained indices (.pt).")
     p.add_argument("--save-reduced", type=Path, help="Optional path to save the reduced sequence (.pt).")
@@ -80,8 +79,6 @@ def main(argv: Optional[list] = None) -> dict:
     args = build_parser().parse_args(argv)
     logging.basicConfig(level=getattr(logging, args.log_level.upper(), logging.INFO),
                         format="%(asctime)s | %(levelname)s | %(name)s | %(message)s")
-    if args.storage == "disk":
-        raise SystemExit("--storage disk is not built in the sm_100a runner: use cpu (pinned host memory) or device (HBM)")
     device = torch.device(args.device if args.device else "cuda")
     dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float32
     sequence: Optional[torch.Tensor] = None

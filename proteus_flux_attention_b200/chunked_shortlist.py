@@ -61,6 +61,20 @@ def _build_model_config(seq_len: int, d_model: int, *, heads: int, sparse_ratio:
         attn_router_top_p=router_top_p)
 
 
+def _system_available_ram() -> Optional[int]:
+    """Best-effort estimate of the available host memory in bytes (psutil, else sysconf)."""
+    try:
+        import psutil
+        return int(psutil.virtual_memory().available)
+    except Exception:
+        pass
+    try:
+        import os
+        return int(os.sysconf("SC_PAGE_SIZE") * os.sysconf("SC_AVPHYS_PAGES"))
+    except (AttributeError, ValueError, TypeError, OSError):
+        return None
+
+
 def _sanitize_mapping(mapping: Dict[str, Any]) -> Dict[str, Any]:
     out: Dict[str, Any] = {}
     for key, value in mapping.items():
@@ -190,7 +204,8 @@ class _ChunkFeeder:
     runs while chunks i and i+1 are being worked on."""
 
     def __init__(self, source: torch.Tensor, local_start: int, device: torch.device, chunk_len: int,
-                 targets: Optional[List[torch.Tensor]] = None):
+                 targets: Optional[List[torch.Tensor]] = None, dtype: Optional[torch.dtype] = None):
+        dtype = dtype or source.dtype   # a disk-staged sequence is float32 and is converted while it is staged
         self.src = source
         self.off = local_start  # global index of source[:, 0]
         self.device = device
@@ -199,11 +214,11 @@ class _ChunkFeeder:
         if self.copying:
             self.copy_stream = torch.cuda.Stream(device=device)
             shape = (1, chunk_len, source.size(2))
-            self.dev = targets if targets is not None else [torch.empty(shape, dtype=source.dtype, device=device) for _ in range(2)]
+            self.dev = targets if targets is not None else [torch.empty(shape, dtype=dtype, device=device) for _ in range(2)]
             self.nbuf = len(self.dev)
             self.ahead = max(1, self.nbuf // 2)
-            self.pinned_source = self.on_device or source.is_pinned()  # uploads straight from the caller's buffer
-            self.stage = [] if self.pinned_source else [torch.empty(shape, dtype=source.dtype, pin_memory=True)
+            self.pinned_source = self.on_device or (source.is_pinned() and source.dtype == dtype)  # uploads straight from the caller's buffer
+            self.stage = [] if self.pinned_source else [torch.empty(shape, dtype=dtype, pin_memory=True)
                                                         for _ in range(self.nbuf)]
             self.ready = [torch.cuda.Event() for _ in range(self.nbuf)]
             self.consumed = [torch.cuda.Event() for _ in range(self.nbuf)]
@@ -477,8 +492,11 @@ class ChunkedShortlistRunner:
         whatever was captured against them - graphs, record buffers - lives for this call only: a graph replayed
         after its layer is gone would read freed weights."""
         if self._layer_cache is not None:
-            return self._run(sequence, chunk_state=chunk_state, final_state=final_state, warmup_input=warmup_input,
-                             sequence_is_local_shard=sequence_is_local_shard)
+            try:
+                return self._run(sequence, chunk_state=chunk_state, final_state=final_state, warmup_input=warmup_input,
+                                 sequence_is_local_shard=sequence_is_local_shard)
+            finally:
+                self._drop_disk_stage()
         self.__dict__["_graph_tmp"] = {}
         try:
             return self._run(sequence, chunk_state=chunk_state, final_state=final_state, warmup_input=warmup_input,
@@ -487,6 +505,73 @@ class ChunkedShortlistRunner:
             if torch.device(self.config.device).type == "cuda":   # nothing of this call is still replaying
                 torch.cuda.synchronize(torch.device(self.config.device))
             self.__dict__.pop("_graph_tmp", None)
+            self._drop_disk_stage()
+
+    # ------------------------------------------------------------------------------------------ host staging
+    def _resolve_storage(self, required_bytes: int, on_device: bool):
+        """Where the sequence lives while it is streamed: the reference's rules (cs.py:420-451) for host sequences -
+        ``auto`` goes to disk when the sequence exceeds ``ram_limit_bytes`` (or the available RAM), ``cpu`` when it
+        exceeds an explicit limit, ``disk`` always - plus ``device`` for a sequence that is (or is asked to be) resident
+        in HBM.  Returns (mode, reason, limit in bytes)."""
+        cfg = self.config
+        available = _system_available_ram()
+        limit = cfg.ram_limit_bytes
+        host_limit = limit if limit is not None else available
+        if cfg.storage == "device" or (on_device and cfg.storage != "disk"):
+            return "device", None, host_limit
+        mode, reason = cfg.storage, None
+        if mode == "auto":
+            if host_limit is not None and required_bytes > host_limit:
+                mode, reason = "disk", f"required={required_bytes:,}B exceeds limit={host_limit:,}B; staging on disk"
+            else:
+                mode = "cpu"
+                if limit is not None:
+                    reason = f"limit={limit:,}B, required={required_bytes:,}B"
+                elif available is not None:
+                    reason = f"available≈{available:,}B, required={required_bytes:,}B"
+        elif mode == "cpu" and limit is not None and required_bytes > limit:
+            mode, reason = "disk", f"required={required_bytes:,}B exceeds ram_limit={limit:,}B; staging on disk"
+        return mode, reason, host_limit
+
+    def _stage_on_disk(self, source: Optional[torch.Tensor], n_tokens: int):
+        """The sequence as a float32 memory-mapped file (cs.py:497-541): written in blocks of at most 64 MiB, seeded
+        noise block by block when no sequence was given.  Returns (a CPU tensor over the mapping, bytes of one
+        block); the file is removed when the call ends."""
+        import tempfile
+        import numpy as np
+        cfg = self.config
+        tmp_dir = Path(cfg.temp_dir) if cfg.temp_dir is not None else Path(tempfile.gettempdir())
+        tmp_dir.mkdir(parents=True, exist_ok=True)
+        handle = tempfile.NamedTemporaryFile(dir=tmp_dir, prefix="chunked_shortlist_", suffix=".mmap", delete=False)
+        handle.close()
+        path = Path(handle.name)
+        array = np.memmap(path, dtype=np.float32, mode="w+", shape=(n_tokens, cfg.d_model))
+        self.__dict__.setdefault("_disk_stage", []).append((path, array))
+        rows_per_block = max(1, min(cfg.chunk_len, int((64 * 1024 * 1024) / max(cfg.d_model * 4, 1))))
+        gen = None
+        if source is None:
+            gen = torch.Generator(device="cpu")
+            if cfg.seed is not None:
+                gen.manual_seed(int(cfg.seed))
+        for start in range(0, n_tokens, rows_per_block):
+            end = min(n_tokens, start + rows_per_block)
+            if source is not None:
+                block = source[0, start:end].to("cpu", dtype=torch.float32)
+            else:
+                block = torch.randn(end - start, cfg.d_model, generator=gen, device="cpu").to(torch.float32)
+            array[start:end] = block.numpy()
+        array.flush()
+        return torch.from_numpy(array).unsqueeze(0), rows_per_block * cfg.d_model * 4
+
+    def _drop_disk_stage(self) -> None:
+        import contextlib
+        import os
+        for path, array in self.__dict__.pop("_disk_stage", []):
+            with contextlib.suppress(Exception):
+                array.flush()
+            del array
+            with contextlib.suppress(OSError):
+                os.remove(path)
 
     def _run(self, sequence: Optional[torch.Tensor] = None, *, chunk_state: Optional[Dict[str, torch.Tensor]] = None,
              final_state: Optional[Dict[str, torch.Tensor]] = None, warmup_input: Optional[torch.Tensor] = None,
@@ -523,15 +608,28 @@ class ChunkedShortlistRunner:
             base_dtype = sequence.dtype
         else:
             base_dtype = torch.get_default_dtype()
+            source, source_off = None, 0
+        self.__dict__["_base_dtype"] = base_dtype
+        elem = torch.tensor([], dtype=base_dtype).element_size()
+        host_bytes = int(cfg.seq_len * cfg.d_model * elem)
+        storage_mode, storage_reason, host_limit = self._resolve_storage(host_bytes, source is not None and source.is_cuda)
+        host_allocated = None
+        if storage_mode == "disk":
+            # float32 on disk, converted to the activation dtype chunk by chunk on the way to the device (cs.py:543-552)
+            n_stage = source.size(1) if source is not None else cfg.seq_len
+            source, host_allocated = self._stage_on_disk(source, n_stage)
+            host_bytes = int(cfg.seq_len * cfg.d_model * 4)
+        elif source is None:
             gen = torch.Generator(device="cpu")
             if cfg.seed is not None:
                 gen.manual_seed(int(cfg.seed))
             source = torch.randn(1, cfg.seq_len, cfg.d_model, generator=gen, device="cpu").to(base_dtype)
-            source_off = 0
-        if cfg.storage == "device" and not source.is_cuda:
+        if storage_mode == "device" and not source.is_cuda:
             source = source.to(device)
-        storage_mode = "device" if source.is_cuda else "cpu"
-        host_bytes = int(cfg.seq_len * cfg.d_model * source.element_size())
+        if storage_mode == "cpu":
+            host_allocated = int(source.numel() * source.element_size())
+        if storage_reason is not None:
+            self.logger.info("Host staging: %s (%s)", storage_mode, storage_reason)
 
         chunk_model = self._make_layer(cfg.chunk_len, cfg.chunk_sparse_ratio, base_dtype, chunk_state, cfg.freeze_prototypes)
         if cfg.warmup:
@@ -586,7 +684,8 @@ class ChunkedShortlistRunner:
             if source.is_cuda and source.is_contiguous():
                 resident = [source[:, s - source_off:e - source_off] for s, e in bounds if e - s == cfg.chunk_len]
             graph = self._chunk_graph(chunk_model, base_dtype, records, resident)
-        feeder = _ChunkFeeder(source, source_off, device, cfg.chunk_len, targets=graph[1] if graph is not None else None)
+        feeder = _ChunkFeeder(source, source_off, device, cfg.chunk_len, targets=graph[1] if graph is not None else None,
+                              dtype=base_dtype)
         records.reset(c_lo, cfg.chunk_len)  # after a possible capture, whose warm-up calls wrote into slot 0
         main = torch.cuda.current_stream()
         lanes = graph[2] if graph is not None else [main]
@@ -733,8 +832,10 @@ class ChunkedShortlistRunner:
             chunk_tokens_per_s=float(cfg.seq_len * 1e3 / chunk_time_ms) if chunk_time_ms and chunk_time_ms > 0 else None,
             final_tokens_per_s=float(k_host * 1e3 / final_time_ms) if final_time_ms and final_time_ms > 0 else None,
             total_tokens_per_s=float(cfg.seq_len / total_s) if total_s > 0 else None, storage_mode=storage_mode,
-            host_required_mb=host_bytes / BYTES_PER_MB, host_allocated_mb=None if source.is_cuda else host_bytes / BYTES_PER_MB,
-            host_limit_mb=None, storage_reason=None, world_size=world)
+            host_required_mb=host_bytes / BYTES_PER_MB,
+            host_allocated_mb=host_allocated / BYTES_PER_MB if host_allocated is not None else None,
+            host_limit_mb=host_limit / BYTES_PER_MB if host_limit is not None else None, storage_reason=storage_reason,
+            world_size=world)
         self.logger.info("Chunked Shortlist retained %s/%s tokens (%.3f) across %s chunks", metrics.retained_tokens,
                          metrics.original_tokens, metrics.retention_ratio, n_chunks)
         return ChunkedShortlistResult(keep_indices=keep_idx_host, keep_scores=keep_sc_host,
@@ -858,6 +959,10 @@ class ChunkedShortlistRunner:
                 keep_pos = torch.where(keep_pos >= 0, keep_pos + off[chunk], keep_pos)
         return ops.gather_rows(pool, keep_pos, None, k).unsqueeze(0)
 
+    def _activation_dtype(self, source: torch.Tensor) -> torch.dtype:
+        """dtype of the rows handed to the layers: the source's own, except for a disk-staged (float32) sequence."""
+        return self.__dict__.get("_base_dtype", source.dtype)
+
     def _gather_reduced(self, source: torch.Tensor, source_off: int, keep_idx: torch.Tensor, k: int,
                         device: torch.device, world: int, rank: int, c_lo: int, c_hi: int) -> torch.Tensor:
         """(1, k, C) rows of the kept tokens, in ascending index order (reference :688-689)."""
@@ -866,7 +971,7 @@ class ChunkedShortlistRunner:
         if full_local:
             if source.is_cuda:
                 return ops.gather_rows(source[0], keep_idx, None, k).unsqueeze(0)
-            return source[:, keep_idx.cpu()].to(device, non_blocking=True)
+            return source[:, keep_idx.cpu()].to(self._activation_dtype(source)).to(device, non_blocking=True)
         # sharded input: every rank fills the kept rows that fall inside its own chunks and leaves zeros elsewhere;
         # the sum over ranks is the full reduced sequence
         lo, hi = c_lo * cfg.chunk_len, min(cfg.seq_len, c_hi * cfg.chunk_len)
@@ -875,8 +980,8 @@ class ChunkedShortlistRunner:
             rows = ops.gather_rows(source[0], local_idx, None, k)
         else:
             li = local_idx.cpu()
-            rows = torch.zeros((k, cfg.d_model), dtype=source.dtype)
-            rows[li >= 0] = source[0, li[li >= 0]]
+            rows = torch.zeros((k, cfg.d_model), dtype=self._activation_dtype(source))
+            rows[li >= 0] = source[0, li[li >= 0]].to(rows.dtype)
             rows = rows.to(device)
         return dist_utils.sum_disjoint_rows(self.group, rows, world).unsqueeze(0)
 

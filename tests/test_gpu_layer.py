@@ -560,8 +560,46 @@ def test_chunked_cli_flags_and_report_layout(dev, tmp_path):
     assert on_disk["keep_indices"] == sorted(on_disk["keep_indices"]) == report["keep_indices"]
     assert {"index", "start", "end", "promoted", "scores"} <= set(on_disk["chunks"][0])
     assert torch.load(idx_path).tolist() == on_disk["keep_indices"]
-    with pytest.raises(SystemExit):
-        chunked_cli.main(["--storage", "disk"])
+
+
+def test_chunked_pipeline_disk_staging(dev, tmp_path):
+    """storage="disk" stages the sequence in a float32 memory-mapped file (the reference's layout) and streams it from
+    there: same kept tokens and outputs as the host-memory run, the reference's storage metrics, the file gone afterwards;
+    "auto" and "cpu" fall back to disk when the sequence exceeds ram_limit_bytes."""
+    import proteus_flux_attention_b200 as P
+    from proteus_flux_attention_b200 import chunked_cli
+    from proteus_flux_attention_b200.chunked_shortlist import _build_model_config
+    torch.manual_seed(14)
+    mk = lambda n, r: P.AdaptiveSparseAttention(_build_model_config(n, 128, heads=4, sparse_ratio=r, shortlist_alpha=1.0,  # noqa: E731
+                                                                   router_top_p=0.9))
+    cast = lambda sd: {k: v.to(torch.bfloat16) if v.dtype == torch.float32 and "routing" not in k else v for k, v in sd.items()}  # noqa: E731
+    cs, fs = cast(mk(2048, 0.05).state_dict()), cast(mk(256, 0.5).state_dict())
+    seq = torch.randn(1, 4 * 2048 + 500, 128, generator=torch.Generator().manual_seed(6)).to(torch.bfloat16)
+    base = dict(seq_len=seq.size(1), d_model=128, chunk_len=2048, buffer_tokens=256, per_chunk_budget=64, device=dev, heads=4,
+                freeze_prototypes=True, warmup=False)
+    want = P.ChunkedShortlistRunner(P.ChunkedShortlistConfig(**base, storage="cpu")).run(seq, chunk_state=cs, final_state=fs)
+    assert want.metrics.storage_mode == "cpu" and want.metrics.host_allocated_mb > 0
+    stage = tmp_path / "stage"
+    for kw in (dict(storage="disk"), dict(storage="auto", ram_limit_bytes=1 << 16), dict(storage="cpu", ram_limit_bytes=1 << 16),
+               dict(storage="disk", use_cuda_graph=True)):
+        got = P.ChunkedShortlistRunner(P.ChunkedShortlistConfig(**base, temp_dir=stage, **kw)).run(seq, chunk_state=cs, final_state=fs)
+        assert got.metrics.storage_mode == "disk"
+        assert got.metrics.host_required_mb == pytest.approx(seq.size(1) * 128 * 4 / (1024 * 1024))
+        assert got.metrics.host_allocated_mb == pytest.approx(2048 * 128 * 4 / (1024 * 1024))
+        if "ram_limit_bytes" in kw:
+            assert "staging on disk" in got.metrics.storage_reason and got.metrics.host_limit_mb == pytest.approx(1 / 16)
+        assert torch.equal(got.keep_indices, want.keep_indices) and torch.equal(got.keep_scores, want.keep_scores)
+        assert torch.equal(got.reduced_sequence.cpu(), want.reduced_sequence.cpu())
+        assert torch.equal(got.final_output.cpu(), want.final_output.cpu())
+        assert list(stage.glob("*.mmap")) == []
+    # a device-resident sequence asked onto disk goes there too; generated noise is staged block by block
+    got = P.ChunkedShortlistRunner(P.ChunkedShortlistConfig(**base, temp_dir=stage, storage="disk")).run(seq.to(dev), chunk_state=cs, final_state=fs)
+    assert got.metrics.storage_mode == "disk" and torch.equal(got.keep_indices, want.keep_indices)
+    report = chunked_cli.main(["--seq-len", "8192", "--d-model", "128", "--chunk-len", "2048", "--buffer-tokens", "256",
+                               "--per-chunk-budget", "64", "--heads", "4", "--seed", "3", "--device", "cuda:0", "--storage", "disk",
+                               "--temp-dir", str(stage), "--dtype", "bf16", "--log-level", "ERROR"])
+    assert report["metrics"]["storage_mode"] == "disk" and 0 < len(report["keep_indices"]) <= 256
+    assert list(stage.glob("*.mmap")) == []
 
 
 def test_tinytoy_sweep_report_layout(dev, tmp_path):

@@ -119,3 +119,30 @@ def test_chunk_config_validation():
                 dict(storage="tape"), dict(per_chunk_budget=0)):
         with pytest.raises(ValueError):
             P.ChunkedShortlistConfig(**{**ok, **bad}).validate()
+
+
+def test_storage_rules_and_disk_stage(tmp_path):
+    """Where a host sequence is staged follows the reference's rules (tools/chunked_shortlist.py:420-451), and the
+    memory-mapped stage holds the sequence as float32, written block by block, and disappears with the call."""
+    base = dict(seq_len=5000, d_model=32, chunk_len=2048, buffer_tokens=64, per_chunk_budget=16, device=torch.device("cuda"),
+                temp_dir=tmp_path)
+    need = 5000 * 32 * 2
+    mode = lambda on_device=False, **kw: P.ChunkedShortlistRunner(P.ChunkedShortlistConfig(**base, **kw))._resolve_storage(need, on_device)  # noqa: E731
+    assert mode(storage="auto", ram_limit_bytes=1000)[0] == "disk" and "exceeds limit=1,000B" in mode(storage="auto", ram_limit_bytes=1000)[1]
+    assert mode(storage="auto", ram_limit_bytes=10 ** 9)[:2] == ("cpu", f"limit=1,000,000,000B, required={need:,}B")
+    assert mode(storage="cpu", ram_limit_bytes=1000)[0] == "disk" and mode(storage="cpu")[0] == "cpu"
+    assert mode(storage="disk")[0] == "disk" and mode(True, storage="disk")[0] == "disk"
+    assert mode(True, storage="auto")[0] == "device" and mode(True, storage="cpu")[0] == "device" and mode(storage="device")[0] == "device"
+    runner = P.ChunkedShortlistRunner(P.ChunkedShortlistConfig(**base, storage="disk", seed=5))
+    x = torch.randn(1, 5000, 32).to(torch.bfloat16)
+    staged, block_bytes = runner._stage_on_disk(x, 5000)
+    assert staged.dtype == torch.float32 and staged.shape == (1, 5000, 32) and block_bytes == 2048 * 32 * 4
+    assert torch.equal(staged.to(torch.bfloat16), x)
+    noise, _ = runner._stage_on_disk(None, 5000)     # seeded noise, generated block by block as the reference does
+    gen = torch.Generator().manual_seed(5)
+    want = torch.cat([torch.randn(n, 32, generator=gen) for n in (2048, 2048, 904)])
+    assert torch.equal(noise[0], want)
+    assert len(list(tmp_path.glob("chunked_shortlist_*.mmap"))) == 2
+    del staged, noise
+    runner._drop_disk_stage()
+    assert list(tmp_path.glob("*.mmap")) == []
