@@ -865,7 +865,11 @@ def main():
                     "frac_of_nominal_8tbs": achieved / 8000.0,
                     "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(args.workload, {}).get(name) if world == 1 else None,
                     "launch_ms": tot_ms / n, "algorithmic_bytes_per_launch": nbytes / n,
-                    "kernels_ms_per_step": {k: round(v[1] / args.steps, 4) for k, v in sorted(kt.items(), key=lambda kv: -kv[1][1])}}
+                    "kernels_ms_per_step": {k: round(v[1] / args.steps, 4) for k, v in sorted(kt.items(), key=lambda kv: -kv[1][1])},
+                    # the same serial pass per kernel: algorithmic bytes of its launches over their CUDA-event time, as a
+                    # fraction of the peak (kernels that move next to nothing - selections, scans - read near zero here)
+                    "kernels_frac_of_peak": {k: round((v[2] / max(v[1], 1e-9) / 1e6) / peak, 3)
+                                             for k, v in sorted(kt.items(), key=lambda kv: -kv[1][1]) if v[2] > 0}}
 
     if args.workload == "attn_dense_8k":   # the tile products bound this one: useful flops against the measured GEMM peak
         pk = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())["bf16_tflops"] if (ROOT / "MEASURED_PEAKS.json").exists() else 1590.0
