@@ -924,12 +924,23 @@ class ChunkedShortlistRunner:
                 ref = weakref.ref(self)
                 atexit.register(lambda: ref() is not None and ref().close())   # best effort for callers that never close
                 self.__dict__["_close_at_exit"] = True
+            # one graph per sequence address: keep the two most recent (each holds its intermediates in a memory pool)
+            stale = [k for k in cache if isinstance(k, tuple) and k and k[0] == "run_graph"]
+            for k in stale[:-1]:
+                del cache[k]
+            # everything the captured kernels address by raw pointer stays alive with the graph: the pool of promoted
+            # rows, the pinned read-back buffers, both layers, the lanes (the sequence itself belongs to the caller)
             entry = cache[key] = {"graph": g, "outs": outs, "pins": pins, "final_model": final_model, "ctx": ctx, "info": info,
+                                  "pool": pool, "lanes": lanes, "side": side, "chunk_model": chunk_model,
                                   "ev": (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))}
         ev0, ev1 = entry["ev"]
         ev0.record()
         entry["graph"].replay()
         ev1.record()
+        # the caller's copies of the two large outputs are enqueued behind the graph, before the one wait of the run
+        keep_idx, keep_sc, red, out = entry["outs"]
+        red_copy = red.clone()
+        out_copy = out.clone() if out is not None else None
         torch.cuda.synchronize(device)
         for m, pending in entry["ctx"]:   # the replay refreshed the pinned telemetry records: decode on next access
             if pending is not None:
@@ -941,9 +952,8 @@ class ChunkedShortlistRunner:
             ops.check_router_status(device)
         if int(pins["count"].item()) != k_guess:
             return None
-        keep_idx, keep_sc, red, out = entry["outs"]
-        return {"k": k_guess, "keep_idx_host": pins["idx"].clone(), "keep_sc_host": pins["sc"].clone(), "reduced": red.clone(),
-                "final_output": out.clone() if out is not None else None, "backend_info": entry["info"],
+        return {"k": k_guess, "keep_idx_host": pins["idx"].clone(), "keep_sc_host": pins["sc"].clone(), "reduced": red_copy,
+                "final_output": out_copy, "backend_info": entry["info"],
                 "final_model": entry["final_model"], "device_ms": float(ev0.elapsed_time(ev1))}
 
     def _gather_pooled(self, pool: torch.Tensor, keep_pos: torch.Tensor, k: int, budget: int, world: int,
