@@ -342,12 +342,18 @@ int aspa_gather_attn_fwd_prepared(const void* q, const void* k, const void* v, i
  * bounded device-side wait of the tcgen05 kernel raises: ASPA_OK, or ASPA_ERR_TIMEOUT when a wait ran out since
  * the last reset (outputs of that call are invalid).  Synchronises `stream`. */
 int aspa_attn_tc_mode(int mode);
-/* Prototype-pick pass of the INT8 shortlist (the dedup of sa.py:260-596 applied to the block lists of
- * aspa_proto_plan): rows of one (head, 128-token block) pair walk the same list, so a warp takes the pair with up to
- * 16 rows as the M dimension of mma.sync tiles (s8 x s8 for Q K^T, f16 for P V) and reads each key and value row once
- * for all of them.  Covers int8 q/k/v, head_dim 64, a structural plan whose anchors were folded in by the tile pass (or
- * has none).  mode 0: always the per-row kernel; 1 (default): the tile kernel where covered.  Returns the previous
- * mode (any other argument only queries). */
+/* Passes that follow the window tiles of a structural plan (the candidate pieces of sa.py:260-596), on warp-MMA tiles
+ * where rows share their keys (int8 or bf16 q/k/v, head_dim 64):
+ *  - prototype picks: the rows of one (head, 128-token block) pair walk the same score-sorted list of
+ *    aspa_proto_plan, so a warp takes the pair with up to 16 rows as the M dimension of mma.sync tiles (s8 x s8 for
+ *    Q K^T of int8 inputs, f16 / bf16 for P V) and reads each key and value row once for all of them;
+ *  - anchors of (head, token % stride) groups too small for the 64-row tile pass: the same kernel over the strided key
+ *    sequence of the residue class, the slot that clamps to key 0 included;
+ *  - when the 64-row tile passes took window and anchors and the plan has no picks, a one-warp-per-row finaliser for the
+ *    clamping slot and the normalisation.
+ * mode 0: always the per-row kernel; 1 (default): these kernels where they apply.  Returns the previous mode (any
+ * other argument only queries).  The environment variable ASPA_ATTN_PICKS_MODE sets it when the Python binding loads
+ * the library. */
 int aspa_attn_picks_mode(int mode);
 int aspa_attn_tc_status(int reset, void* stream);
 

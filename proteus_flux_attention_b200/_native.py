@@ -115,6 +115,11 @@ def lib() -> C.CDLL:
             fn = getattr(handle, name)  # AttributeError if the symbol is not exported
             fn.restype = res
             fn.argtypes = args
+        # kernel-choice switches for A/B measurements: ASPA_ATTN_TC_MODE=0|1|2, ASPA_ATTN_PICKS_MODE=0|1
+        import os
+        for var, setter in (("ASPA_ATTN_TC_MODE", handle.aspa_attn_tc_mode), ("ASPA_ATTN_PICKS_MODE", handle.aspa_attn_picks_mode)):
+            if os.environ.get(var, "").strip().isdigit():
+                setter(int(os.environ[var]))
         _lib = handle
     return _lib
 

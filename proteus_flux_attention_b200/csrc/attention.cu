@@ -124,7 +124,7 @@ struct RowCands {
       j0 = t / astride + 1;  // first anchor slot that clamps to key 0
       anchor_clamps = n_anchor > 0 && (t - (long long)n_anchor * astride) < 0;
       n_anchor_true = n_anchor;
-      if (anchors_done && n_anchor > 0) n_anchor = 1;  // only the slot that clamps to key 0 is left to this pass
+      if (anchors_done && n_anchor > 0) n_anchor = p.anchors_done == 2 ? 0 : 1;  // at most the slot that clamps to key 0 is left to this pass
       if (p.plan.proto_cap > 0 && p.plan.proto_lists != nullptr) {
         const int b = bh / p.H;
         const int nblk = (Tn + p.plan.proto_block - 1) / p.plan.proto_block;
@@ -928,17 +928,19 @@ static bool tc_tiles_wanted(int window, int heads, int T, int64_t total_rows) {
 // Anchors t - j*stride of the rows of one residue class t % stride are a window over the strided key sequence of that
 // class: with enough rows per (head, residue) group they go through the tile kernel too, regrouped.
 struct AnchorTiles {
-  bool use;
+  bool use;      // 64-row tiles over regrouped rows
+  bool groups;   // one warp per (head, residue) group (attention_picks.cu): groups too small for 64-row tiles
   int n_loc_full, jmin, an_window;
 };
 static AnchorTiles anchor_tiles_for(const aspa_shortlist_plan* plan, bool has_ws, int heads, int64_t total_rows) {
-  AnchorTiles a = {false, 1, 1, 0};
+  AnchorTiles a = {false, false, 1, 1, 0};
   if (plan == nullptr || !(plan->anchor_slots > 0 && plan->anchor_stride > 0)) return a;
   a.n_loc_full = plan->window > 0 ? plan->window : 1;
   a.jmin = (a.n_loc_full - 1) / plan->anchor_stride + 1;   // first anchor slot outside the window
   a.an_window = plan->anchor_slots - a.jmin + 1;
   a.use = has_ws && plan->anchor_stride <= 1024 && a.an_window >= 64 &&
           total_rows >= (int64_t)8 * heads * plan->anchor_stride;
+  a.groups = has_ws && !a.use && plan->anchor_stride <= 1024 && a.an_window >= 1 && g_attn_picks_mode != 0;
   return a;
 }
 static void launch_regroup(const int32_t* row_offsets, const int32_t* token_idx, int heads, int R, const AnchorTiles& a,
@@ -961,7 +963,7 @@ extern "C" int aspa_attn_regroup_rows(int qkv_dtype, int heads, int T, int D, co
   if (total_rows <= 0 || regroup_ws == nullptr) return ASPA_OK;
   if (!tile_path_ok(qkv_dtype, D, false, false, plan, heads, T, total_rows)) return ASPA_OK;
   const AnchorTiles a = anchor_tiles_for(plan, true, heads, total_rows);
-  if (!a.use) return ASPA_OK;
+  if (!a.use && !(a.groups && D == 64 && (qkv_dtype == ASPA_BF16 || qkv_dtype == ASPA_I8))) return ASPA_OK;
   launch_regroup(row_offsets, token_idx, heads, plan->anchor_stride, a, total_rows, regroup_ws, (cudaStream_t)stream);
   ASPA_CHECK_LAUNCH();
   *prepared = 1;
@@ -1143,10 +1145,36 @@ extern "C" int aspa_gather_attn_fwd_prepared(const void* q, const void* k, const
       ASPA_CHECK_LAUNCH();
       p.anchors_done = 1;
     }
+    const bool has_picks = extras && plan->proto_cap > 0 && plan->proto_lists != nullptr;
+    if (!at.use && at.groups && anchor_groups_ok(p, qkv_dtype)) {
+      const int R = plan->anchor_stride, n_groups = heads * R;
+      int32_t* goffs = reinterpret_cast<int32_t*>(regroup_ws);
+      int32_t* gtok = goffs + n_groups + 1;
+      int32_t* grow_ = gtok + total_rows;
+      if (!regroup_prepared) {
+        launch_regroup(row_offsets, token_idx, heads, R, at, total_rows, regroup_ws, st);
+        ASPA_CHECK_LAUNCH();
+      }
+      AttnParams pa = p;
+      pa.an_stride = R;
+      pa.an_window = at.an_window;
+      pa.an_jmin = at.jmin;
+      pa.an_offsets = goffs;
+      pa.an_tok = gtok;
+      pa.an_row = grow_;
+      pa.read_partial = 1;
+      pa.write_partial = has_picks ? 1 : 0;   // without picks this pass writes the final output
+      launch_anchor_groups(pa, qkv_dtype, st);
+      ASPA_CHECK_LAUNCH();
+      if (!has_picks) return ASPA_OK;
+      p.anchors_done = 2;
+    }
     if (extras) {
       p.write_partial = 0;
       p.extras_only = 1;
-      if (g_attn_picks_mode != 0 && picks_tiles_ok(p, qkv_dtype)) launch_picks_tiles(p, qkv_dtype, st);
+      if (g_attn_picks_mode != 0 && !has_picks && p.anchors_done == 1 && p.add_mask == nullptr && p.D == 64)
+        launch_finalise_rows(p, qkv_dtype, max_rows, st);   // nothing but the clamping slot and the normalisation is left
+      else if (g_attn_picks_mode != 0 && picks_tiles_ok(p, qkv_dtype)) launch_picks_tiles(p, qkv_dtype, st);
       else if (qkv_dtype == ASPA_BF16) launch_generic<__nv_bfloat16>(p, max_rows, st);
       else launch_generic<int8_t>(p, max_rows, st);
       ASPA_CHECK_LAUNCH();

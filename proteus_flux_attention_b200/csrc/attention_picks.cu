@@ -69,29 +69,40 @@ __device__ __forceinline__ int warp_lower_bound(const int32_t* __restrict__ tok,
 }
 
 struct PickRow {
-  int t, loc_start, limit, tmod, alo;
+  int t, loc_start, limit, tmod, alo;   // anchor groups: limit = last strided key index of the row, alo = its first
   bool present, clamp_slot, aclamps;
 };
 
-template <typename T>
+// What the rows of a warp's group share: MODE 0 the score-sorted pick list of their 128-token block (rows of one head
+// and block), MODE 1 the strided key sequence K[rho + stride * i] of their residue class rho = token % stride (rows of
+// one head and residue, regrouped by anchor_regroup_kernel) - the anchors t - j * stride of such rows are windows over it.
+constexpr int PK_PICKS = 0, PK_ANCHORS = 1;
+
+template <typename T, int MODE>
 __global__ void __launch_bounds__(PK_WARPS * 32, sizeof(T) == 1 ? PK_MIN_BLOCKS : 4) attn_picks_tile_kernel(const AttnParams p) {
   constexpr bool I8 = sizeof(T) == 1;
   constexpr int QW = I8 ? 4 : 8;   // 32-bit words of a thread's 16 channels of a q or k row
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
   const int bh = blockIdx.y;
-  const int PB = p.plan.proto_block;
-  const int nblk = (p.T + PB - 1) / PB;
-  const int blk = blockIdx.x * PK_WARPS + warp;
+  const int PB = MODE == PK_PICKS ? p.plan.proto_block : 1;
+  const int nblk = MODE == PK_PICKS ? (p.T + PB - 1) / PB : p.an_stride;   // groups per head
+  const int blk = blockIdx.x * PK_WARPS + warp;                             // block of the sequence, or residue class
   if (blk >= nblk) return;
   const int start = p.row_offsets[bh];
   const int cnt = p.row_offsets[bh + 1] - start;
   if (cnt <= 0) return;
   const int32_t* toks = p.token_idx + start;
-  const int r_lo = warp_lower_bound(toks, cnt, blk * PB, lane);
-  if (r_lo >= cnt) return;
-  const int span = min(cnt - r_lo, PB);   // a block holds at most PB rows of one head
-  const int r_hi = r_lo + warp_lower_bound(toks + r_lo, span, (blk + 1) * PB, lane);
-  if (r_hi == r_lo) return;
+  int r_lo, r_hi;   // MODE 0: rows of the head (positions in its packing); MODE 1: positions in the regrouped arrays
+  if (MODE == PK_PICKS) {
+    r_lo = warp_lower_bound(toks, cnt, blk * PB, lane);
+    if (r_lo >= cnt) return;
+    const int span = min(cnt - r_lo, PB);   // a block holds at most PB rows of one head
+    r_hi = r_lo + warp_lower_bound(toks + r_lo, span, (blk + 1) * PB, lane);
+  } else {
+    r_lo = p.an_offsets[bh * nblk + blk];
+    r_hi = p.an_offsets[bh * nblk + blk + 1];
+  }
+  if (r_hi <= r_lo) return;
 
   const int Tn = p.T;
   const int b = bh / p.H;
@@ -102,7 +113,7 @@ __global__ void __launch_bounds__(PK_WARPS * 32, sizeof(T) == 1 ? PK_MIN_BLOCKS 
   const float LOG2E = 1.4426950408889634f;
   const float sc2 = (I8 ? p.scale * p.q_scale[bh] * p.k_scale[bh] : p.scale) * LOG2E;   // scores in the log2 domain
   const float vscale = I8 ? p.v_scale[bh] : 1.f;
-  const int32_t* plist = p.plan.proto_lists + ((int64_t)b * nblk + blk) * p.plan.proto_list_stride;
+  const int32_t* plist = MODE == PK_PICKS ? p.plan.proto_lists + ((int64_t)b * nblk + blk) * p.plan.proto_list_stride : nullptr;
   const int astride = max(1, p.plan.anchor_stride);
   const int n_at = p.plan.anchor_stride > 0 ? p.plan.anchor_slots : 0;
   const bool pow2 = (astride & (astride - 1)) == 0;
@@ -112,21 +123,33 @@ __global__ void __launch_bounds__(PK_WARPS * 32, sizeof(T) == 1 ? PK_MIN_BLOCKS 
     // rows g and g + 8 of this sub-tile
     PickRow row[2];
     uint32_t qa[2][QW];
+    int64_t grow[2];   // row of the head-grouped packing = workspace row
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       const int r = rt + g + 8 * h;
       PickRow& R = row[h];
       R.present = r < r_hi;
-      R.t = R.present ? toks[r] : 0;
+      grow[h] = !R.present ? 0 : (MODE == PK_PICKS ? (int64_t)start + r : (int64_t)p.an_row[r]);
+      R.t = R.present ? p.token_idx[grow[h]] : 0;
       const int n_loc = window > 0 ? min(R.t + 1, window) : 1;
       R.loc_start = R.t - n_loc + 1;
-      R.limit = R.present ? p.plan.proto_limit[(int64_t)b * Tn + R.t] : 0;
       R.tmod = pow2 ? (R.t & (astride - 1)) : (R.t % astride);
-      R.alo = R.t - n_at * astride;
-      R.aclamps = n_at > 0 && R.alo < 0;
-      // the one anchor slot the tile pass leaves to this pass: the slot that clamps to key 0
-      const int j0 = R.t / astride + 1;
-      R.clamp_slot = R.present && p.anchors_done && n_at > 0 && j0 <= n_at && R.tmod != 0 && R.loc_start > 0;
+      const int j0 = R.t / astride + 1;   // the anchor slot that clamps to key 0
+      const bool clamp_row = R.present && n_at > 0 && j0 <= n_at && R.tmod != 0 && R.loc_start > 0;
+      if (MODE == PK_PICKS) {
+        R.limit = R.present ? p.plan.proto_limit[(int64_t)b * Tn + R.t] : 0;
+        R.alo = R.t - n_at * astride;
+        R.aclamps = n_at > 0 && R.alo < 0;
+        // the one anchor slot the 64-row tile pass leaves to this pass (the group pass takes it itself: anchors_done 2)
+        R.clamp_slot = clamp_row && p.anchors_done == 1;
+      } else {
+        // strided key indices [alo, limit]: the last anchor outside the window back to slot n_at (an_tok holds
+        // token / stride - jmin, or ANCHOR_NO_KEYS for a row whose window reaches key 0)
+        R.limit = R.present ? p.an_tok[r] : ANCHOR_NO_KEYS;
+        R.alo = max(0, R.t / astride - n_at);
+        R.aclamps = false;
+        R.clamp_slot = clamp_row;
+      }
 #pragma unroll
       for (int i = 0; i < QW / 4; ++i) {
         uint4 w = make_uint4(0u, 0u, 0u, 0u);
@@ -135,9 +158,16 @@ __global__ void __launch_bounds__(PK_WARPS * 32, sizeof(T) == 1 ? PK_MIN_BLOCKS 
       }
     }
     int max_limit = max(row[0].limit, row[1].limit);
+    int min_lo = 0x7fffffff;
+    if (MODE == PK_ANCHORS) min_lo = min(row[0].limit >= row[0].alo ? row[0].alo : min_lo, row[1].limit >= row[1].alo ? row[1].alo : min_lo);
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) max_limit = max(max_limit, __shfl_xor_sync(0xffffffffu, max_limit, off));
-    const int n_slots = max_limit + 1;   // slot 0: key 0 for the rows with the clamping anchor slot; slot i + 1: list entry i
+    for (int off = 16; off > 0; off >>= 1) {
+      max_limit = max(max_limit, __shfl_xor_sync(0xffffffffu, max_limit, off));
+      min_lo = min(min_lo, __shfl_xor_sync(0xffffffffu, min_lo, off));
+    }
+    // slot 0: key 0 for the rows with the clamping anchor slot; slot s >= 1: list entry s - 1, or strided key min_lo + s - 1
+    const int n_slots = MODE == PK_PICKS ? max_limit + 1 : (max_limit >= min_lo ? max_limit - min_lo + 2 : 1);
+    if (MODE == PK_ANCHORS && max_limit < min_lo) min_lo = 0;   // no row of the sub-tile has an anchor key
 
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
     float o[8][4];
@@ -151,7 +181,8 @@ __global__ void __launch_bounds__(PK_WARPS * 32, sizeof(T) == 1 ? PK_MIN_BLOCKS 
 #pragma unroll
       for (int nt = 0; nt < 4; ++nt) {
         const int slot = s0 + 8 * nt + g;
-        u_own[nt] = slot == 0 ? 0 : (slot <= max_limit ? plist[slot - 1] : -1);
+        if (MODE == PK_PICKS) u_own[nt] = slot == 0 ? 0 : (slot <= max_limit ? plist[slot - 1] : -1);
+        else u_own[nt] = slot == 0 ? 0 : (slot < n_slots ? blk + astride * (min_lo + slot - 1) : -1);
         const uint4* krow = reinterpret_cast<const uint4*>(kh + (int64_t)max(u_own[nt], 0) * k_ts + 16 * q);
         if (I8) {
           const uint4 kw = krow[0];
@@ -187,9 +218,12 @@ __global__ void __launch_bounds__(PK_WARPS * 32, sizeof(T) == 1 ? PK_MIN_BLOCKS 
             bool ok;
             if (slot == 0) {
               ok = R.clamp_slot;
-            } else {
+            } else if (MODE == PK_PICKS) {
               ok = R.present && slot <= R.limit && u >= 0 && u < R.loc_start;
               if (n_at > 0) ok = ok && !((umod == R.tmod && u >= R.alo) || (u == 0 && R.aclamps));
+            } else {
+              const int i = min_lo + slot - 1;
+              ok = R.present && u >= 0 && i >= R.alo && i <= R.limit;
             }
             const float v = ok ? c[nt][2 * h + j] * sc2 : -INFINITY;
             s[nt][2 * h + j] = v;
@@ -282,16 +316,31 @@ __global__ void __launch_bounds__(PK_WARPS * 32, sizeof(T) == 1 ? PK_MIN_BLOCKS 
       l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
       const PickRow& R = row[h];
       if (!R.present) continue;
-      const int64_t grow = (int64_t)start + rt + g + 8 * h;
-      const float m1n = p.ws_m[grow], l1 = p.ws_l[grow];
+      const int64_t gr = grow[h];
+      const float m1n = p.ws_m[gr], l1 = p.ws_l[gr];
       const float m1 = m1n == -INFINITY ? -INFINITY : m1n * LOG2E;
       const float mm = fmaxf(m[h], m1);
       const float c1 = m1 == -INFINITY ? 0.f : exp2f(m1 - mm);
       const float c2 = m[h] == -INFINITY ? 0.f : exp2f(m[h] - mm);
       const float lt = l1 * c1 + l[h] * c2;
+      float* wo = p.ws_o + gr * 64;
+      if (p.write_partial) {   // another pass follows: leave the merged state (natural-log maximum, raw P.V) behind
+        if (q == 0) {
+          p.ws_m[gr] = mm == -INFINITY ? -INFINITY : mm * 0.6931471805599453f;
+          p.ws_l[gr] = lt;
+        }
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+#pragma unroll
+          for (int nt = 0; nt < 8; ++nt) {
+            const int ch = 8 * (2 * q + j) + nt;
+            wo[ch] = wo[ch] * c1 + o[nt][2 * h + j] * c2;
+          }
+        }
+        continue;
+      }
       const float inv = lt > 0.f ? 1.f / lt : 0.f;
       const int64_t ob = out_row_base(p, bh, R.t);
-      const float* wo = p.ws_o + grow * 64;
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
 #pragma unroll
@@ -302,6 +351,67 @@ __global__ void __launch_bounds__(PK_WARPS * 32, sizeof(T) == 1 ? PK_MIN_BLOCKS 
       }
     }
   }
+}
+
+// What is left when the 64-row tile passes have taken window and anchors and the plan has no prototype picks: the one
+// anchor slot that clamps to key 0 (rows whose last anchor would fall below the sequence start) and the normalisation of
+// the state in the workspace.  One warp per row, two channels per lane.
+template <typename T>
+__global__ void __launch_bounds__(256) attn_finalise_rows_kernel(const AttnParams p) {
+  constexpr bool I8 = sizeof(T) == 1;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bh = blockIdx.y;
+  const int start = p.row_offsets[bh];
+  const int cnt = p.row_offsets[bh + 1] - start;
+  const int r = blockIdx.x * 8 + warp;
+  if (r >= cnt) return;
+  const int64_t grow = (int64_t)start + r;
+  const int t = p.token_idx[grow];
+  const int b = bh / p.H;
+  const int astride = max(1, p.plan.anchor_stride);
+  const int n_at = p.plan.anchor_stride > 0 ? p.plan.anchor_slots : 0;
+  const int n_loc = p.plan.window > 0 ? min(t + 1, p.plan.window) : 1;
+  const bool clamp = p.anchors_done == 1 && n_at > 0 && t / astride + 1 <= n_at && (t % astride) != 0 && t - n_loc + 1 > 0;
+  const float m1 = p.ws_m[grow], l1 = p.ws_l[grow];
+  float c1 = 1.f, c2 = 0.f, lt = l1;
+  float v0 = 0.f, v1 = 0.f;
+  if (clamp) {   // warp-uniform
+    const T* qr = reinterpret_cast<const T*>(p.q) + ((int64_t)bh * p.T + t) * 64;
+    const T* k0 = reinterpret_cast<const T*>(p.k) + (int64_t)b * p.kv.k_batch + (int64_t)(bh % p.H) * p.kv.k_head;
+    const T* vr = reinterpret_cast<const T*>(p.v) + (int64_t)b * p.kv.v_batch + (int64_t)(bh % p.H) * p.kv.v_head;
+    float dot;
+    if (I8) {
+      const char2 a = reinterpret_cast<const char2*>(qr)[lane], kk = reinterpret_cast<const char2*>(k0)[lane];
+      const char2 vv = reinterpret_cast<const char2*>(vr)[lane];
+      dot = (float)((int)a.x * (int)kk.x + (int)a.y * (int)kk.y);
+      v0 = (float)vv.x; v1 = (float)vv.y;
+    } else {
+      const float2 a = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(qr)[lane]);
+      const float2 kk = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(k0)[lane]);
+      const float2 vv = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(vr)[lane]);
+      dot = a.x * kk.x + a.y * kk.y;
+      v0 = vv.x; v1 = vv.y;
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+    const float s = dot * (I8 ? p.scale * p.q_scale[bh] * p.k_scale[bh] : p.scale);
+    const float mm = fmaxf(s, m1);
+    c1 = m1 == -INFINITY ? 0.f : __expf(m1 - mm);
+    c2 = __expf(s - mm);
+    lt = l1 * c1 + c2;
+  }
+  const float inv = lt > 0.f ? 1.f / lt : 0.f;
+  const float vscale = I8 ? p.v_scale[bh] : 1.f;
+  const float2 wo = *reinterpret_cast<const float2*>(p.ws_o + grow * 64 + 2 * lane);
+  const int64_t ob = out_row_base(p, bh, t) + 2 * lane;
+  store_out(p, ob, (wo.x * c1 + v0 * c2) * inv * vscale);
+  store_out(p, ob + 1, (wo.y * c1 + v1 * c2) * inv * vscale);
+}
+
+void launch_finalise_rows(const AttnParams& p, int qkv_dtype, int max_rows, cudaStream_t st) {
+  const dim3 grid((unsigned)ceil_div(max_rows, 8), (unsigned)p.heads);
+  if (qkv_dtype == ASPA_I8) attn_finalise_rows_kernel<int8_t><<<grid, 256, 0, st>>>(p);
+  else attn_finalise_rows_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p);
 }
 
 // Whether the pick pass of this call can run on the tile kernel: int8 or bf16, head_dim 64, a structural plan with prototype
@@ -316,8 +426,22 @@ bool picks_tiles_ok(const AttnParams& p, int qkv_dtype) {
 void launch_picks_tiles(const AttnParams& p, int qkv_dtype, cudaStream_t st) {
   const int nblk = (p.T + p.plan.proto_block - 1) / p.plan.proto_block;
   const dim3 grid((unsigned)ceil_div(nblk, PK_WARPS), (unsigned)p.heads);
-  if (qkv_dtype == ASPA_I8) attn_picks_tile_kernel<int8_t><<<grid, PK_WARPS * 32, 0, st>>>(p);
-  else attn_picks_tile_kernel<__nv_bfloat16><<<grid, PK_WARPS * 32, 0, st>>>(p);
+  if (qkv_dtype == ASPA_I8) attn_picks_tile_kernel<int8_t, PK_PICKS><<<grid, PK_WARPS * 32, 0, st>>>(p);
+  else attn_picks_tile_kernel<__nv_bfloat16, PK_PICKS><<<grid, PK_WARPS * 32, 0, st>>>(p);
+}
+
+// The anchors of a call whose (head, residue) groups are too small for the 64-row tile pass: same kernel, one warp per
+// group, keys = the strided sequence of the residue class.  `p` carries the regrouped rows (an_*) and says through
+// write_partial whether another pass follows.
+bool anchor_groups_ok(const AttnParams& p, int qkv_dtype) {
+  if ((qkv_dtype != ASPA_I8 && qkv_dtype != ASPA_BF16) || p.D != 64 || !p.has_plan || p.add_mask != nullptr) return false;
+  return p.plan.anchor_stride > 0 && p.plan.anchor_slots > 0;
+}
+
+void launch_anchor_groups(const AttnParams& p, int qkv_dtype, cudaStream_t st) {
+  const dim3 grid((unsigned)ceil_div(p.an_stride, PK_WARPS), (unsigned)p.heads);
+  if (qkv_dtype == ASPA_I8) attn_picks_tile_kernel<int8_t, PK_ANCHORS><<<grid, PK_WARPS * 32, 0, st>>>(p);
+  else attn_picks_tile_kernel<__nv_bfloat16, PK_ANCHORS><<<grid, PK_WARPS * 32, 0, st>>>(p);
 }
 
 }  // namespace aspa

@@ -32,7 +32,8 @@ struct AttnParams {
   float* ws_l;  // [total_rows] running denominator
   float* ws_o;  // [total_rows][D] unnormalised output
   int extras_only;  // second pass: skip the local window, merge with ws_*
-  int anchors_done; // extras pass: the strided anchor keys were already folded into ws_* by the tile pass
+  int anchors_done; // extras pass: 1 = the strided anchor keys were already folded into ws_* by the 64-row tile pass (the
+                    // slot that clamps to key 0 is still open), 2 = by the group pass, clamping slot included
   int read_partial; // tile pass: start from the state in ws_* instead of an empty one
   // anchor tile pass: rows regrouped by (head, token % stride); keys are the strided view K[rho + stride * i]
   int an_stride;            // 0 = ordinary window pass
@@ -67,5 +68,12 @@ bool launch_window_tc(const AttnParams& p, int qkv_dtype, int max_rows, int grou
 // 128-token block) pair share their pick list.  picks_tiles_ok says whether the call is one it covers.
 bool picks_tiles_ok(const AttnParams& p, int qkv_dtype);
 void launch_picks_tiles(const AttnParams& p, int qkv_dtype, cudaStream_t st);
+// The same kernel over the rows of a (head, token % stride) group and the strided key sequence of that residue class:
+// the anchor pass for groups too small for the 64-row tile pass.  `p` carries the regrouped rows (an_*).
+// After 64-row tile passes for window and anchors of a plan without picks: the slot that clamps to key 0, and the final
+// normalisation of the workspace state (int8 or bf16, head_dim 64).
+void launch_finalise_rows(const AttnParams& p, int qkv_dtype, int max_rows, cudaStream_t st);
+bool anchor_groups_ok(const AttnParams& p, int qkv_dtype);
+void launch_anchor_groups(const AttnParams& p, int qkv_dtype, cudaStream_t st);
 
 }  // namespace aspa
