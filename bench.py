@@ -376,9 +376,19 @@ class LMWorkload:
         self.host_ids = None
         self.config = {"workload": self.name, "layers": L, "d_model": d, "heads": H, "mlp": "SwiGLU 3072", "vocab": V,
                        "batch": B, "seq_len": T, "l2": "activations (96 MiB per layer tensor, 4 GiB of logits) larger than L2"}
+        # The whole forward from one CUDA graph where every attention call is one that never waits for the host
+        # (shortlist mode at this length); eager otherwise.  `captured` is switched off by the kernel-timing passes.
+        self.captured = None
+        try:
+            self.captured = P.CapturedModelCall(self.model, self.ids)
+            self.config["launch"] = "one CUDA graph for the whole forward"
+        except RuntimeError as err:
+            self.config["launch"] = f"eager ({str(err)[:80]})"
 
     @torch.no_grad()
     def step(self):
+        if self.captured is not None:
+            return self.captured(self.ids)
         return self.model(self.ids)
 
     @torch.no_grad()
@@ -386,7 +396,8 @@ class LMWorkload:
         if self.host_ids is None:
             self.host_ids = self.ids.cpu().pin_memory()
             self.host_last = torch.empty((self.B, 32000), dtype=torch.bfloat16, pin_memory=True)
-        logits = self.model(self.host_ids.to(self.device, non_blocking=True))
+        ids = self.host_ids.to(self.device, non_blocking=True)
+        logits = self.captured(ids) if self.captured is not None else self.model(ids)
         self.host_last.copy_(logits[:, -1], non_blocking=True)     # what a caller reads back: next-token logits
         torch.cuda.synchronize()
         return self.host_ids.numel() * 8, self.host_last.numel() * 2

@@ -3,14 +3,14 @@ from .aspa import (AdaptiveSparseAttention, AdaptiveSparseAttentionBlock, Adapti
                    ModelConfig)
 from .chunked_shortlist import (ChunkedShortlistConfig, ChunkedShortlistMetrics, ChunkedShortlistResult,
                                 ChunkedShortlistRunner)
-from .graph_call import CapturedLayerCall
+from .graph_call import CapturedLayerCall, CapturedModelCall
 from .multihead import CausalASPAMultiheadAttention
 from .sparse_attn import (aspa_sparse_attention, build_packed_shortlist_candidates, build_shortlist_candidates,
                           get_last_backend, get_last_backend_info)
 from .sparse_ctl import SparseHeadController
 from .transformer_block import CausalASPATransformerBlock
 
-__all__ = ["CapturedLayerCall", "AdaptiveSparseAttentionBlock", "AdaptiveSparseAttention", "AdaptiveSparseProtoAttention",
+__all__ = ["CapturedLayerCall", "CapturedModelCall", "AdaptiveSparseAttentionBlock", "AdaptiveSparseAttention", "AdaptiveSparseProtoAttention",
            "aspa_sparse_attention", "build_shortlist_candidates", "build_packed_shortlist_candidates",
            "CausalASPAMultiheadAttention", "CausalASPATransformerBlock", "SparseHeadController", "MLP", "ModelConfig",
            "get_last_backend", "get_last_backend_info", "ChunkedShortlistConfig", "ChunkedShortlistMetrics",

@@ -62,3 +62,61 @@ class CapturedLayerCall:
             self.layer.__dict__["_head_stats_value"] = None
             self.layer.__dict__["_sparse_state_value"] = None
         return self.static_out
+
+
+class CapturedModelCall:
+    """The same for any module that contains ASPA layers (a transformer block, a whole decoder): ``CapturedModelCall(
+    model, example)(x)`` == ``model(x)`` for inputs of the example's shape and dtype, replayed from one CUDA graph.
+
+    Every ``AdaptiveSparseAttention`` inside must make a call that never waits for the host at this shape (see
+    ``CapturedLayerCall``); otherwise a ``RuntimeError`` is raised before anything is captured and the model is left as
+    it was.  Buffers the calls move (prototype EMAs, memory banks) are restored after warm-up and capture; from then on
+    every replay moves them as an eager call would.  The static output is overwritten by the next call."""
+
+    def __init__(self, model: torch.nn.Module, example: torch.Tensor, *, priority: int = -2) -> None:
+        if not example.is_cuda:
+            raise RuntimeError("the example input must live on the CUDA device the model is on")
+        self.model = model
+        self.layers = [m for m in model.modules() if isinstance(m, AdaptiveSparseAttention)]
+        self.static_in = example.detach().clone()
+        stream = torch.cuda.Stream(device=example.device, priority=priority)
+        stream.wait_stream(torch.cuda.current_stream())
+        state = {n: b.detach().clone() for n, b in model.named_buffers()}
+        with torch.no_grad(), torch.cuda.stream(stream):
+            for _ in range(2):
+                model(self.static_in)
+        torch.cuda.current_stream().wait_stream(stream)
+        torch.cuda.synchronize(example.device)
+        for layer in self.layers:
+            pending = layer.__dict__.get("_pending")
+            if not (isinstance(pending, dict) and pending.get("lazy")):
+                self._restore(state)
+                raise RuntimeError("a layer of this model waits for row counts on the host at this shape (dense modes, "
+                                   "alpha < 0.95, a keep threshold, or candidate pieces that may exceed L): the model "
+                                   "cannot be captured into a CUDA graph")
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.no_grad(), torch.cuda.graph(self.graph, stream=stream):
+            self.static_out = model(self.static_in)
+        self._pending = [layer.__dict__.get("_pending") for layer in self.layers]
+        torch.cuda.synchronize(example.device)
+        self._restore(state)
+
+    def _restore(self, state) -> None:
+        with torch.no_grad():
+            for n, b in self.model.named_buffers():
+                b.copy_(state[n])
+
+    def __call__(self, x: torch.Tensor):
+        if x.shape != self.static_in.shape or x.dtype != self.static_in.dtype:
+            raise ValueError(f"captured for {tuple(self.static_in.shape)} {self.static_in.dtype}, got {tuple(x.shape)} {x.dtype}")
+        for layer in self.layers:
+            layer.check_previous_call()
+        if x.data_ptr() != self.static_in.data_ptr():
+            self.static_in.copy_(x, non_blocking=True)
+        self.graph.replay()
+        for layer, pending in zip(self.layers, self._pending):
+            if pending is not None:
+                layer.__dict__["_pending"] = dict(pending)
+                layer.__dict__["_head_stats_value"] = None
+                layer.__dict__["_sparse_state_value"] = None
+        return self.static_out

@@ -542,6 +542,47 @@ def test_rope_table_survives_a_longer_eager_call_between_replays(dev):
     del junk
 
 
+def test_captured_model_call_equals_eager(dev):
+    """A model with two ASPA layers inside replayed from one captured graph gives what the eager model gives, state
+    updates included; a model with a layer that must wait for the host refuses to be captured and is left untouched."""
+    import proteus_flux_attention_b200 as P
+    cfg = dict(d_model=256, n_head=4, attn_h_total=4, attn_gates=8, attn_h_active=2, attn_h_active_min=2,
+               attn_h_active_max=2, attn_token_sparse=True, attn_token_keep_ratio=0.3, attn_router_top_p=0.0,
+               attn_mode="linear", attn_linear_L=96, attn_linear_window=64, attn_linear_anchor_stride=16, n_ctx=2048,
+               attn_track_latency=False, attn_proto_enable=True)
+
+    class Two(torch.nn.Module):
+        def __init__(self, **over):
+            super().__init__()
+            self.a = P.AdaptiveSparseProtoAttention(P.ModelConfig(**{**cfg, **over}))
+            self.b = P.AdaptiveSparseProtoAttention(P.ModelConfig(**cfg))
+            self.norm = torch.nn.LayerNorm(256)
+
+        def forward(self, x):
+            return x + self.b(self.norm(x + self.a(x)))
+
+    torch.manual_seed(21)
+    eager = Two().to(torch.bfloat16).to(dev).eval()
+    twin = Two().to(torch.bfloat16).to(dev).eval()
+    twin.load_state_dict(eager.state_dict())
+    x = torch.randn(2, 1024, 256, device=dev).to(torch.bfloat16)
+    call = P.CapturedModelCall(twin, x)
+    for step in range(3):
+        xs = torch.randn(2, 1024, 256, generator=torch.Generator().manual_seed(step)).to(dev).to(torch.bfloat16)
+        with torch.no_grad():
+            want = eager(xs)
+        got = call(xs)
+        assert torch.equal(got, want)
+        for (n, p_e), (_, p_t) in zip(eager.named_buffers(), twin.named_buffers()):
+            assert torch.equal(p_e, p_t), n   # prototype EMAs moved alike
+    assert twin.b.last_head_stats is not None   # telemetry of the replayed call decodes
+    needs_host = Two(attn_token_keep_threshold=0.5).to(torch.bfloat16).to(dev).eval()   # a keep threshold: counts on the host
+    before = {n: b.clone() for n, b in needs_host.named_buffers()}
+    with pytest.raises(RuntimeError, match="cannot be captured"):
+        P.CapturedModelCall(needs_host, torch.randn(1, 256, 256, device=dev).to(torch.bfloat16))
+    assert all(torch.equal(b, before[n]) for n, b in needs_host.named_buffers())
+
+
 # ------------------------------------------------------------------------------------------ command lines
 def test_chunked_cli_flags_and_report_layout(dev, tmp_path):
     """The chunk tool's command line takes the reference's flags and writes the reference's report layout."""
