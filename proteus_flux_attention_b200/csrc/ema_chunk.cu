@@ -70,7 +70,7 @@ constexpr int ETC_X_BYTES = ETC_STEP * ETC_CH * 2;   // 16 KB
 
 template <int MT>  // MT = ceil(G / 16) m-tiles of 16 gates
 __global__ void __launch_bounds__(256) ema_partial_tc_kernel(const __nv_bfloat16* __restrict__ x, int64_t n, int C,
-                                                             const float* __restrict__ gate_probs, int G,
+                                                             const float* __restrict__ gate_probs, int G, int tok_per_cta,
                                                              float* __restrict__ part_w, float* __restrict__ part_c) {
   extern __shared__ __align__(128) unsigned char etc_smem[];
   unsigned char* xs = etc_smem;                                              // ETC_STAGES x [32 tokens][512 B], swizzled
@@ -79,8 +79,8 @@ __global__ void __launch_bounds__(256) ema_partial_tc_kernel(const __nv_bfloat16
   uint32_t* as_ = reinterpret_cast<uint32_t*>(ps + ETC_STAGES * ETC_STEP * GP);  // [k16][m][term][lane] x 4 words: A fragments of the step
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int chunk = blockIdx.x, c0 = blockIdx.y * ETC_CH;
-  const int64_t t_begin = (int64_t)chunk * ETC_TOK;
-  const int64_t t_end = min(n, t_begin + ETC_TOK);
+  const int64_t t_begin = (int64_t)chunk * tok_per_cta;
+  const int64_t t_end = min(n, t_begin + tok_per_cta);
   const int nsteps = (int)((t_end - t_begin + ETC_STEP - 1) / ETC_STEP);
 
   auto issue = [&](int step) {
@@ -822,7 +822,11 @@ extern "C" int aspa_proto_ema_update(const void* x, int x_dtype, int64_t n, int 
   // bf16 activations with 8-element aligned rows go through the tensor cores (larger token chunks, fewer partials)
   const bool tc = x_dtype == ASPA_BF16 && C % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
                   (reinterpret_cast<uintptr_t>(gate_probs) & 15) == 0;
-  const int64_t nchunk = ceil_div(n, tc ? ETC_TOK : EMA_TOK);
+  // tokens per CTA of the tensor-core kernel: as many as keep at least two CTAs per SM busy (fewer partial sums to add
+  // up), never fewer than the CUDA-core kernel's, for which the scratch is sized
+  int etc_tok = ETC_TOK;
+  while (tc && etc_tok > EMA_TOK && ceil_div(n, etc_tok) * ceil_div(C, ETC_CH) < 2 * 148) etc_tok >>= 1;
+  const int64_t nchunk = ceil_div(n, tc ? etc_tok : EMA_TOK);
   float* pw = reinterpret_cast<float*>(scratch);
   float* pc = pw + nchunk * G * C;
   if (updated) cudaMemsetAsync(updated, 0, sizeof(int32_t), st);
@@ -832,7 +836,7 @@ extern "C" int aspa_proto_ema_update(const void* x, int x_dtype, int64_t n, int 
     const size_t smem = ETC_STAGES * (ETC_X_BYTES + ETC_STEP * MT * 16 * sizeof(float)) + (ETC_STEP / 16) * MT * 3 * 32 * 16;
     auto launch = [&](auto kernel) {
       cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      kernel<<<grid, 256, smem, st>>>((const __nv_bfloat16*)x, n, C, gate_probs, G, pw, pc);
+      kernel<<<grid, 256, smem, st>>>((const __nv_bfloat16*)x, n, C, gate_probs, G, etc_tok, pw, pc);
     };
     if (MT == 1) launch(ema_partial_tc_kernel<1>);
     else if (MT == 2) launch(ema_partial_tc_kernel<2>);
