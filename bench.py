@@ -92,6 +92,15 @@ class ClockSampler:
                                              text=True)
         except Exception:
             self.proc = None
+        # the child's lines are collected as they come, so that summary() can tell whether a sample exists yet
+        self.lines = []
+        if self.proc is not None:
+            import threading
+
+            def pump(stream, sink):
+                for line in stream:
+                    sink.append(line)
+            threading.Thread(target=pump, args=(self.proc.stdout, self.lines), daemon=True).start()
 
     def begin(self):
         self.t0 = self.dt.datetime.now()
@@ -102,15 +111,19 @@ class ClockSampler:
     def summary(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        # a timed region of a few tens of milliseconds can end before the child's first line: wait for one (the sample
+        # nearest to the region is then reported, and says so)
+        deadline = time.time() + 5.0
         time.sleep(0.05)
+        while not self.lines and time.time() < deadline and self.proc.poll() is None:
+            time.sleep(0.02)
         self.proc.terminate()
         try:
-            out, _ = self.proc.communicate(timeout=10)
+            self.proc.wait(timeout=10)
         except Exception:
             self.proc.kill()
-            out = ""
         rows, near = [], []
-        for line in out.splitlines():
+        for line in list(self.lines):
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 8:
                 continue
@@ -740,6 +753,9 @@ def main():
     _native.lib()  # no fallback: fail here if the CUDA library is missing
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
+    # started this early because its child needs about a second before its first sample, and the timed region of a
+    # sharded run lasts a few tens of milliseconds
+    clocks = ClockSampler(local_rank, args.clock_sampler, args.clock_period_ms)
     cpu_affinity = bind_to_gpu_node(local_rank) if (world > 1 and args.bind_numa) else None
     group = None
     if world > 1:
@@ -801,13 +817,14 @@ def main():
         torch.cuda.synchronize()
 
     if args.profile_mode:
+        if clocks.proc is not None:   # no sampling under a profiler
+            clocks.proc.terminate()
         for _ in range(args.warmup + args.steps):
             wl.step()
         sync()
         if rank == 0:
             print(json.dumps({"profile_mode": True, "workload": args.workload, "passes": args.warmup + args.steps}))
         return
-    clocks = ClockSampler(local_rank, args.clock_sampler, args.clock_period_ms)
     for _ in range(max(3, args.warmup)):
         wl.step()
     sync()
