@@ -310,14 +310,21 @@ __global__ void __launch_bounds__(PK_WARPS * 32, sizeof(T) == 1 ? PK_MIN_BLOCKS 
     }
 
     // ---- merge with the state the window and anchor passes left, normalise, store
+    float m1_in[2], l1_in[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
       l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+      m1_in[h] = row[h].present ? p.ws_m[grow[h]] : -INFINITY;
+      l1_in[h] = row[h].present ? p.ws_l[grow[h]] : 0.f;
+    }
+    __syncwarp();   // every lane of a row has read its old maximum and sum before one of them replaces them (write_partial)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
       const PickRow& R = row[h];
       if (!R.present) continue;
       const int64_t gr = grow[h];
-      const float m1n = p.ws_m[gr], l1 = p.ws_l[gr];
+      const float m1n = m1_in[h], l1 = l1_in[h];
       const float m1 = m1n == -INFINITY ? -INFINITY : m1n * LOG2E;
       const float mm = fmaxf(m[h], m1);
       const float c1 = m1 == -INFINITY ? 0.f : exp2f(m1 - mm);
