@@ -7,9 +7,21 @@ Workloads (synthetic, seeded; shapes of the reference's headline configurations)
                  the merged 32,768-token shortlist, bf16.  Chunks are sharded over the N ranks (strong scaling).
   shortlist_256k one INT8 shortlist layer, 262,144 tokens, L = 4096 (local + anchors + prototype picks), bf16.
   sparse_16k     one sparse layer, batch 4 x 16,384 tokens, top-4 of 16 heads, keep 0.2, RoPE, bf16.
+  sparse_4k_fp32 the reference's CPU-runnable case on the GPU: one sparse layer, 1 x 4096 x 512, fp32.
+  lm_12l         a 12-layer decoder (d_model 768, 12 heads) around the drop-in module, 2 x 32,768 tokens, with a sweep
+                 over sequence lengths naming the mode each resolves to.
+  attn_dense_8k  the tile attention kernel alone (--attn-kernel auto|tcgen05|warp_mma), tensor roofline.
+  chunk_64k, router_64k   one chunk step of pass 1 / the router alone, for profiler captures (--profile-mode).
 A step is one pass of the hot path over one batch.  `value` is measured with inputs resident in HBM; `e2e` goes
 through the public API with host buffers (host->device copies of the inputs and device->host reads of the results
-inside the timed region).  One JSON line is printed by rank 0.
+inside the timed region).  One JSON line is printed by rank 0.  Besides the contract's keys it carries: `roofline`
+(dominant kernel; `kernels_ms_per_step` and `kernels_frac_of_peak` from a strictly serial pass of the same steps),
+`cpu_baseline`, `config.phases_ms_last_step` (CUDA-event phases of the last timed step; for sharded runs also
+`phases_ms_chunk_by_chunk`), `config.self_check` (N = 1: the timed path against an eager run) or
+`config.parity_vs_1rank` (N > 1: against a 1-rank run on rank 0), `config.cold_first_run_ms`.
+
+`--run-graph auto|on|off` (chunked_1m): the whole sharded run from one CUDA graph (auto: on for N > 1).  The
+environment variables ASPA_ATTN_TC_MODE and ASPA_ATTN_PICKS_MODE select attention kernels for A/B runs.
 
 `--impl reference` times the reference's own CPU implementation on the host cores, all threads, on a bounded sample
 of the same workload: the unmodified reference package out of `oracle/_ref` (installed there by `oracle/build_ref.py`;
