@@ -216,7 +216,7 @@ def chunk_data(c: int, device, dtype):
 class ChunkedWorkload:
     name = "chunked_1m"
 
-    def __init__(self, device, world, rank, group, run_graph=True):
+    def __init__(self, device, world, rank, group, run_graph=True, full_forward=True, shard=None):
         import proteus_flux_attention_b200 as P
         from proteus_flux_attention_b200 import distributed as D
         from proteus_flux_attention_b200.chunked_shortlist import _build_model_config
@@ -224,7 +224,7 @@ class ChunkedWorkload:
         self.tokens = SEQ_1M
         cfg = P.ChunkedShortlistConfig(seq_len=SEQ_1M, d_model=D_MODEL, chunk_len=CHUNK, buffer_tokens=BUFFER,
                                        per_chunk_budget=BUDGET, device=device, heads=HEADS, freeze_prototypes=True,
-                                       warmup=False, collect_summaries=False, pass1_full_forward=True,
+                                       warmup=False, collect_summaries=False, pass1_full_forward=bool(full_forward),
                                        use_cuda_graph=True, whole_run_graph=bool(run_graph))
         self.runner = P.ChunkedShortlistRunner(cfg, process_group=group, cache_layers=True)
         mk = lambda n, r: P.AdaptiveSparseAttention(_build_model_config(n, D_MODEL, heads=HEADS, sparse_ratio=r,  # noqa: E731
@@ -232,10 +232,12 @@ class ChunkedWorkload:
         self.chunk_state = xavier_state(mk(CHUNK, 0.05), torch.bfloat16, 0)
         self.final_state = xavier_state(mk(BUFFER, 0.5), torch.bfloat16, 1)
         lo, hi = D.partition_chunks(SEQ_1M // CHUNK, world, rank)
-        self.shard = torch.stack([chunk_data(c, device, torch.bfloat16) for c in range(lo, hi)]).view(1, -1, D_MODEL)
+        self.shard = shard if shard is not None else \
+            torch.stack([chunk_data(c, device, torch.bfloat16) for c in range(lo, hi)]).view(1, -1, D_MODEL)
         self.host_shard = None
         self.config = {"workload": self.name, "seq_len": SEQ_1M, "d_model": D_MODEL, "heads": HEADS, "chunk_len": CHUNK,
-                       "per_chunk_budget": BUDGET, "buffer_tokens": BUFFER, "pass1": "full layer forward per chunk",
+                       "per_chunk_budget": BUDGET, "buffer_tokens": BUFFER,
+                       "pass1": "full layer forward per chunk" if full_forward else "router + token keep per chunk",
                        "prototypes": "frozen during pass 1",
                        "pass1_launch": "one CUDA graph per run (both passes and the exchange)" if run_graph else "CUDA graph replay per chunk", "sharding": f"chunks over {world} rank(s)",
                        "l2": "inputs (2 GiB) larger than L2"}
@@ -945,6 +947,36 @@ def main():
         wl.config["cold_first_run_ms"] = round((time.perf_counter() - t0) * 1e3, 2)
         wl.runner.run(wl.shard, chunk_state=wl.chunk_state, final_state=wl.final_state, sequence_is_local_shard=True)
         del fresh
+        sync()
+
+    # Beside the headline (never in its place): the same job with pass 1 reduced to what its result depends on.  The
+    # reference runs a full layer forward per chunk and throws the output away (tools/chunked_shortlist.py:624-625);
+    # router + token keep alone give the same promotions, hence the same kept tokens and the same final output, which
+    # is checked here before the variant is timed.
+    if args.workload == "chunked_1m" and not args.no_e2e:
+        wl_so = ChunkedWorkload(device, world, rank, group, run_graph=wl.runner.config.whole_run_graph, full_forward=False,
+                                shard=wl.shard)
+        res_full, res_so = wl.step(), wl_so.step()
+        same = bool(torch.equal(res_full.keep_indices, res_so.keep_indices) and torch.equal(res_full.final_output, res_so.final_output))
+        del res_full, res_so
+        for _ in range(3):
+            wl_so.step()
+        sync()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for _ in range(args.steps):
+            wl_so.step()
+        s1.record()
+        sync()
+        st = torch.tensor([s0.elapsed_time(s1) / args.steps], device=device)
+        if world > 1:
+            dist.all_reduce(st, op=dist.ReduceOp.MAX)
+        wl.config["pass1_score_only_variant"] = {"ms_per_step": round(float(st.item()), 4),
+                                                 "tokens_per_s": round(wl.tokens / (float(st.item()) * 1e-3), 1),
+                                                 "same_kept_tokens_and_output": same,
+                                                 "note": "not the headline: pass 1 without the attention whose output the reference discards"}
+        wl_so.runner.close()
+        del wl_so
         sync()
 
     # the single-layer workloads of the same metric, measured in the same run (one GPU; they do not shard)
