@@ -4,6 +4,7 @@ stream and never synchronises."""
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -13,6 +14,8 @@ from . import _native as N
 # ---- optional instrumentation (used by bench.py): launch counter and per-op CUDA-event timing ----------
 LAUNCHES = 0                      # kernels of libaspa_b200.so launched through this module
 _TIMING: Optional[dict] = None    # name -> list of (start_event, end_event, algorithmic_bytes)
+# ASPA_NVTX=1: every op of this module is wrapped in an NVTX range named after it (off by default: two host calls per op)
+NVTX = os.environ.get("ASPA_NVTX", "0") not in ("", "0")
 
 
 def start_timing() -> None:
@@ -37,12 +40,16 @@ class _timed:
     def __enter__(self):
         global LAUNCHES
         LAUNCHES += self.launches
+        if NVTX:
+            torch.cuda.nvtx.range_push("aspa:" + self.name)
         if _TIMING is not None:
             self.e0 = torch.cuda.Event(enable_timing=True)
             self.e0.record()
         return self
 
     def __exit__(self, *exc):
+        if NVTX:
+            torch.cuda.nvtx.range_pop()
         if _TIMING is not None and exc[0] is None:
             e1 = torch.cuda.Event(enable_timing=True)
             e1.record()
