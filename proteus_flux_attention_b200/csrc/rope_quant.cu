@@ -413,19 +413,21 @@ __global__ void __launch_bounds__(256) rope_inplace_kernel(T* __restrict__ x, in
   }
 }
 
-// dst row i = src[slot_of[i]] for kept rows, `fill` (or zeros) for the others.
+// dst row i = src[slot_of[i]] for kept rows, `fill` (or zeros) for the others.  One warp per row at a time, lanes over
+// the 16-byte vectors of the row: no index arithmetic per vector (a flat index cost two 64-bit divisions per 16 bytes
+// stored and kept this store stream at 0.57 of the copy bandwidth).
 __global__ void __launch_bounds__(256) scatter_rows_fill_kernel(const uint4* __restrict__ src,
                                                                 const int32_t* __restrict__ slot_of,
                                                                 const uint8_t* __restrict__ mask,
                                                                 const uint4* __restrict__ fill, int64_t n,
                                                                 int64_t vec_per_row, uint4* __restrict__ dst) {
-  const int64_t total = n * vec_per_row;
-  for (int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; g < total; g += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t r = g / vec_per_row, c = g % vec_per_row;
-    uint4 val = make_uint4(0u, 0u, 0u, 0u);
-    if (mask[r]) val = src[(int64_t)slot_of[r] * vec_per_row + c];
-    else if (fill) val = fill[c];
-    dst[g] = val;
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  for (int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < n; r += warps) {
+    const bool kept = mask[r] != 0;
+    const uint4* from = kept ? src + (int64_t)slot_of[r] * vec_per_row : fill;
+    uint4* to = dst + r * vec_per_row;
+    for (int64_t c = lane; c < vec_per_row; c += 32) to[c] = from != nullptr ? from[c] : make_uint4(0u, 0u, 0u, 0u);
   }
 }
 
@@ -434,11 +436,13 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const uint4* __restric
                                                           const int32_t* __restrict__ count_dev, int64_t max_rows,
                                                           int64_t vec_per_row, uint4* __restrict__ dst) {
   const int64_t rows = count_dev ? min((int64_t)count_dev[0], max_rows) : max_rows;
-  const int64_t total = rows * vec_per_row;
-  for (int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; g < total; g += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t r = g / vec_per_row, c = g % vec_per_row;
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  for (int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < rows; r += warps) {
     const int64_t i = idx[r];
-    dst[g] = i >= 0 ? src[i * vec_per_row + c] : make_uint4(0u, 0u, 0u, 0u);
+    const uint4* from = i >= 0 ? src + i * vec_per_row : nullptr;
+    uint4* to = dst + r * vec_per_row;
+    for (int64_t c = lane; c < vec_per_row; c += 32) to[c] = from != nullptr ? from[c] : make_uint4(0u, 0u, 0u, 0u);
   }
 }
 
@@ -517,8 +521,7 @@ extern "C" int aspa_gather_rows(const void* src, const int64_t* idx, const int32
   ASPA_CHECK_ARG(src && idx && dst, "null pointer");
   ASPA_CHECK_ARG(max_rows >= 0 && row_bytes > 0 && row_bytes % 16 == 0, "row_bytes must be a multiple of 16");
   if (max_rows == 0) return ASPA_OK;
-  const int64_t total = max_rows * (row_bytes / 16);
-  gather_rows_kernel<<<(unsigned)std::min<int64_t>(ceil_div(total, 256), 148 * 16), 256, 0, (cudaStream_t)stream>>>(
+  gather_rows_kernel<<<(unsigned)std::min<int64_t>(ceil_div(max_rows, 8), 148 * 16), 256, 0, (cudaStream_t)stream>>>(
       (const uint4*)src, idx, count_dev, max_rows, row_bytes / 16, (uint4*)dst);
   ASPA_CHECK_LAUNCH();
   return ASPA_OK;
@@ -573,8 +576,7 @@ extern "C" int aspa_scatter_rows_fill(const void* src, const int32_t* slot_of, c
   ASPA_CHECK_ARG(src && slot_of && mask && dst, "null pointer");
   ASPA_CHECK_ARG(n >= 0 && row_bytes > 0 && row_bytes % 16 == 0, "row_bytes must be a multiple of 16");
   if (n == 0) return ASPA_OK;
-  const int64_t total = n * (row_bytes / 16);
-  scatter_rows_fill_kernel<<<(unsigned)std::min<int64_t>(ceil_div(total, 256), 148 * 32), 256, 0, (cudaStream_t)stream>>>(
+  scatter_rows_fill_kernel<<<(unsigned)std::min<int64_t>(ceil_div(n, 8), 148 * 32), 256, 0, (cudaStream_t)stream>>>(
       (const uint4*)src, slot_of, mask, (const uint4*)fill, n, row_bytes / 16, (uint4*)dst);
   ASPA_CHECK_LAUNCH();
   return ASPA_OK;
